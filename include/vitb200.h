@@ -1,0 +1,133 @@
+/*
+ * vitb200 — a Blackwell (sm_100a) execution backend for the Vision Transformer
+ * training step of transformer-in-c.
+ *
+ * Part 1 is the drop-in boundary: the five functions the reference's host code
+ * already calls (reference include/cuda_backend.h:12-16, implemented there by
+ * src/cuda_backend.cu:2015-2091).  A program that used to link
+ * build/cuda_backend.o links this library instead and is otherwise unchanged;
+ * ops.c keeps dispatching op by op through the table this backend installs
+ * with ops_set_device_backend (reference src/ops.c:66-74), and tensors are
+ * allocated through the hook installed with tensor_set_allocator
+ * (reference src/autodiff.c:11-17).  Those two host functions are looked up
+ * at run time, so the library loads on its own as well.
+ *
+ * Part 2 exposes individual device kernels on plain device pointers; it exists
+ * for kernel-level parity tests and for timing a kernel against its roofline.
+ *
+ * Everything is single-threaded by contract, like the host code it serves
+ * (reference include/ops.h:15).
+ */
+#ifndef VITB200_H
+#define VITB200_H
+
+#include <stddef.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+/* ------------------------------------------------------------------ part 1 */
+
+typedef struct CudaBackend CudaBackend;
+
+/* Replaces cuda_backend_create (reference src/cuda_backend.cu:2015-2049).
+ * 0 = ready; 1 = no usable device (callers treat this as "skip");
+ * -1 = error.  The device is cuda:0 unless VITB200_DEVICE (or LOCAL_RANK when
+ * VITB200_DEVICE_FROM_RANK=1) selects another one. */
+int cuda_backend_create(CudaBackend **backend);
+
+/* Replaces cuda_backend_free (reference src/cuda_backend.cu:2051-2065).
+ * NULL-safe; disables device execution first.  Tensors allocated while the
+ * backend was enabled stay valid and may be freed afterwards. */
+void cuda_backend_free(CudaBackend *backend);
+
+/* Replaces cuda_backend_available (reference src/cuda_backend.cu:2067-2069). */
+int cuda_backend_available(const CudaBackend *backend);
+
+/* Replaces cuda_backend_enable_device_execution (reference
+ * src/cuda_backend.cu:2071-2081): installs the op table and the allocator.
+ * 0 on success, -1 if the backend is unusable or the host's
+ * ops_set_device_backend / tensor_set_allocator cannot be found. */
+int cuda_backend_enable_device_execution(CudaBackend *backend);
+
+/* Replaces cuda_backend_disable_device_execution (reference
+ * src/cuda_backend.cu:2083-2091): synchronises, then uninstalls both hooks.
+ * Idempotent. */
+void cuda_backend_disable_device_execution(CudaBackend *backend);
+
+/* ---- additions with no counterpart in the reference ---- */
+
+/* Kernels launched by this library since it was loaded. */
+unsigned long long vitb200_kernel_launches(void);
+
+/* Coherence counters; any pointer may be NULL. */
+void vitb200_memory_counters(size_t *live_allocations, size_t *mirror_bytes,
+                             size_t *device_bytes, size_t *h2d_copies,
+                             size_t *h2d_bytes, size_t *d2h_copies,
+                             size_t *d2h_bytes, size_t *faults);
+
+/* Makes a tensor buffer obtained through the backend allocator plainly
+ * readable and writable by the host (copying it back from the device if
+ * needed).  Required before passing it to read()/fread()/write()/fwrite(),
+ * which fail with EFAULT on protected pages instead of faulting.  0 / -1. */
+int vitb200_make_host_coherent(const void *tensor_memory);
+
+/* Device timing of the work enqueued between begin and end, in milliseconds
+ * (CUDA events on the backend's stream).  end() synchronises. */
+int vitb200_timer_begin(CudaBackend *backend);
+float vitb200_timer_end(CudaBackend *backend);
+
+/* ------------------------------------------------------------------ part 2 */
+/* Every function below takes device pointers, enqueues on the given CUDA
+ * stream handle (a cudaStream_t passed as void*, NULL = default stream) and
+ * returns 0, or -1 for arguments the kernel does not support.  Semantics are
+ * those of the like-named host op (reference src/ops.c), including "+=" into
+ * gradient buffers. */
+
+int vitb200_k_gemm(const float *x, const float *w, float *y, size_t m,
+                   size_t k, size_t n, int precision, void *stream);
+int vitb200_k_gemm_backward(const float *x, const float *w, const float *dy,
+                            float *dx, float *dw, size_t m, size_t k, size_t n,
+                            int precision, void *stream);
+int vitb200_k_bias_add(const float *in, const float *bias, float *out,
+                       size_t rows, size_t cols, void *stream);
+int vitb200_k_column_sums(const float *in, float *out, size_t rows,
+                          size_t cols, void *stream);
+int vitb200_k_layer_norm(const float *x, const float *gamma, const float *beta,
+                         float epsilon, float *y, size_t rows, size_t cols,
+                         void *stream);
+int vitb200_k_layer_norm_backward(const float *x, const float *gamma,
+                                  float epsilon, const float *dy, float *dx,
+                                  float *dgamma, float *dbeta, size_t rows,
+                                  size_t cols, void *stream);
+int vitb200_k_gelu(const float *in, float *out, size_t n, void *stream);
+int vitb200_k_gelu_backward(const float *x, const float *dy, float *dx,
+                            size_t n, void *stream);
+int vitb200_k_attention(const float *q, const float *k, const float *v,
+                        float *probabilities, float *out, size_t groups,
+                        size_t seq, size_t head_dim, float scale, void *stream);
+/* row_dots: scratch, groups*seq floats. */
+int vitb200_k_attention_backward(const float *q, const float *k, const float *v,
+                                 const float *probabilities, const float *out,
+                                 const float *dout, float *dq, float *dk,
+                                 float *dv, float *row_dots, size_t groups,
+                                 size_t seq, size_t head_dim, float scale,
+                                 void *stream);
+/* row_losses: scratch, rows floats. */
+int vitb200_k_softmax_cross_entropy(const float *logits, const float *targets,
+                                    const float *class_weights,
+                                    float label_smoothing, float *loss,
+                                    float *logits_grad, float *row_losses,
+                                    size_t rows, size_t cols, void *stream);
+
+/* GEMM operand precision selectors for part 2 and VITB200_GEMM. */
+#define VITB200_PRECISION_AUTO 0  /* backend default for the shape          */
+#define VITB200_PRECISION_FP32 1  /* FP32 FMA                                */
+#define VITB200_PRECISION_TF32 2  /* tcgen05 kind::tf32, FP32 accumulate     */
+
+#ifdef __cplusplus
+}
+#endif
+
+#endif

@@ -1,0 +1,62 @@
+"""Builds the reference's own CPU implementation into oracle/_ref/.
+
+TEST INFRASTRUCTURE ONLY.  Nothing here is part of the shipped library; the
+outputs are used as the checker in tests/, __graft_entry__.smoke() and the
+cpu_baseline / --impl reference legs of bench.py.
+
+The reference sources are compiled where they lie (they are never copied into
+this repository) with the flags of the reference Makefile:2
+(-std=c99 -O2).  Outputs, all under oracle/_ref/ (git-ignored):
+
+  libvithost.so   ops.c vit.c autodiff.c arena.c  +  our flat ctypes-friendly
+                  entry points (transformer-in-c_b200/host/vit_host.c)
+  test_device     the reference's CPU-vs-device acceptance test
+                  (tests/test_device.c, -DENABLE_CUDA) linked against
+                  libvitb200.so instead of the reference's cuda_backend.o
+  test_vision     the reference's CPU unit tests (oracle sanity)
+
+Usage: python oracle/build_ref.py [reference_root]
+"""
+import os
+import subprocess
+import sys
+
+REPO = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+OUT = os.path.join(REPO, "oracle", "_ref")
+PACKAGE = os.path.join(REPO, "transformer-in-c_b200")
+CORE = ["ops.c", "vit.c", "autodiff.c", "arena.c"]
+EXTRA = ["dataset.c", "augmentation.c", "transformer.c"]  # test_vision needs them
+
+
+def run(command):
+    subprocess.run(command, check=True)
+
+
+def build(reference_root="/root/reference"):
+    """Returns True when the outputs were (re)built, False when the reference
+    tree is not present (the GPU box: prebuilt files are used as they are)."""
+    source = os.path.join(reference_root, "src")
+    include = os.path.join(reference_root, "include")
+    if not os.path.isdir(source):
+        return False
+    os.makedirs(OUT, exist_ok=True)
+    flags = ["-std=c99", "-O2", "-fPIC", "-I" + include]
+    core = [os.path.join(source, name) for name in CORE]
+    run(["gcc", *flags, "-shared", "-o", os.path.join(OUT, "libvithost.so"),
+         *core, os.path.join(PACKAGE, "host", "vit_host.c"), "-lm"])
+    run(["gcc", *flags, "-o", os.path.join(OUT, "test_vision"),
+         os.path.join(reference_root, "tests", "test_vision.c"), *core,
+         *[os.path.join(source, name) for name in EXTRA], "-lm"])
+    library = os.path.join(PACKAGE, "libvitb200.so")
+    if os.path.exists(library):
+        run(["gcc", *flags, "-DENABLE_CUDA", "-o",
+             os.path.join(OUT, "test_device"),
+             os.path.join(reference_root, "tests", "test_device.c"), *core,
+             "-L" + PACKAGE, "-lvitb200",
+             "-Wl,-rpath,$ORIGIN/../../transformer-in-c_b200", "-lm"])
+    return True
+
+
+if __name__ == "__main__":
+    built = build(*sys.argv[1:2])
+    print("built" if built else "reference tree not found; nothing built")

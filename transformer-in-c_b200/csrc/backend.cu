@@ -1,0 +1,1043 @@
+// The drop-in boundary: the five cuda_backend_* functions, the op table that
+// ops.c dispatches through, and the argument checks in front of each kernel.
+//
+// Every slot follows the host's convention (reference src/ops.c:61-64): return
+// 0 once the work is enqueued, non-zero to decline, in which case the host
+// synchronises and runs its own loop.  A slot declines when a buffer was not
+// allocated by this backend (tensors created before device execution was
+// enabled live in plain calloc memory) or when a shape is outside what the
+// kernels index; it never declines half-way through.
+#include "../../include/vitb200.h"
+#include "../../include/vitb200_host_abi.h"
+
+#include "coherence.h"
+#include "gemm.h"
+#include "kernels.h"
+
+#include <climits>
+#include <cmath>
+#include <cstdio>
+#include <cstdlib>
+#include <cstring>
+#include <dlfcn.h>
+#include <vector>
+
+// Host functions this backend calls into.  They live in the host program
+// (reference src/ops.c:66, src/autodiff.c:11); weak references keep this
+// library loadable on its own, and a dlsym lookup covers hosts that were
+// loaded after it.
+extern "C" {
+void ops_set_device_backend(const vitb200_op_table *table)
+    __attribute__((weak));
+void tensor_set_allocator(vitb200_allocate_fn allocate,
+                          vitb200_release_fn release, void *context)
+    __attribute__((weak));
+}
+
+using namespace vitb200;
+
+namespace {
+
+struct Scratch {
+    void *memory = nullptr;
+    size_t bytes = 0;
+};
+
+constexpr int kStagingSlots = 8;
+constexpr size_t kStagingBytes = 64 * 1024;
+
+}  // namespace
+
+struct CudaBackend {
+    int device = 0;
+    cudaStream_t stream = nullptr;
+    vitb200_op_table table = {};
+    int enabled = 0;
+    Scratch rows_scratch;      // per-row floats: CE row losses, attention dots
+    Scratch norm_partials;
+    Scratch clip_scale;
+    Scratch slice_table;
+    // Pinned ring for small host-to-device tables (the optimiser's slices).
+    char *staging[kStagingSlots] = {};
+    cudaEvent_t staging_done[kStagingSlots] = {};
+    int staging_next = 0;
+    cudaEvent_t timer_begin = nullptr, timer_end = nullptr;
+    void (*set_table)(const vitb200_op_table *) = nullptr;
+    void (*set_allocator)(vitb200_allocate_fn, vitb200_release_fn,
+                          void *) = nullptr;
+};
+
+namespace {
+
+[[noreturn]] void die(const char *what, cudaError_t status) {
+    fprintf(stderr, "vitb200: %s failed: %s\n", what,
+            cudaGetErrorString(status));
+    abort();
+}
+
+void check(cudaError_t status, const char *what) {
+    if (status != cudaSuccess) {
+        die(what, status);
+    }
+}
+
+void check_launch(const char *what) {
+    check(cudaGetLastError(), what);
+}
+
+template <typename T>
+T *scratch(CudaBackend *backend, Scratch &buffer, size_t count) {
+    const size_t bytes = (count ? count : 1) * sizeof(T);
+    if (buffer.bytes < bytes) {
+        if (buffer.memory) {
+            check(cudaStreamSynchronize(backend->stream), "cudaStreamSynchronize");
+            check(cudaFree(buffer.memory), "cudaFree");
+        }
+        const size_t grown = bytes + bytes / 2;
+        check(cudaMalloc(&buffer.memory, grown), "cudaMalloc");
+        buffer.bytes = grown;
+    }
+    return static_cast<T *>(buffer.memory);
+}
+
+void free_scratch(Scratch &buffer) {
+    if (buffer.memory) {
+        cudaFree(buffer.memory);
+    }
+    buffer = Scratch{};
+}
+
+size_t numel(const vitb200_tensor *tensor) {
+    size_t count = 1;
+    for (size_t i = 0; i < tensor->ndim; ++i) {
+        count *= tensor->shape[i];
+    }
+    return tensor->ndim ? count : 0;
+}
+
+bool ours(std::initializer_list<const void *> pointers) {
+    for (const void *pointer : pointers) {
+        if (!coherent_owns(pointer)) {
+            return false;
+        }
+    }
+    return true;
+}
+
+bool fits_int(size_t value) {
+    return value > 0 && value <= size_t(INT_MAX);
+}
+
+CudaBackend *self(void *context) {
+    return static_cast<CudaBackend *>(context);
+}
+
+float *view(CudaBackend *backend, const void *pointer, Access access) {
+    return device_view(pointer, access, backend->stream);
+}
+
+// ---------------------------------------------------------------- op slots
+
+int op_gemm(void *context, const vitb200_tensor *left,
+            const vitb200_tensor *right, vitb200_tensor *output) {
+    CudaBackend *backend = self(context);
+    if (!ours({left->data, right->data, output->data}) ||
+        !fits_int(left->rows) || !fits_int(left->cols) ||
+        !fits_int(right->cols)) {
+        return -1;
+    }
+    const float *x = view(backend, left->data, Access::Read);
+    const float *w = view(backend, right->data, Access::Read);
+    float *y = view(backend, output->data, Access::Overwrite);
+    gemm_forward(x, w, y, int(left->rows), int(left->cols), int(right->cols),
+                 VITB200_PRECISION_AUTO, backend->stream);
+    check_launch("gemm");
+    return 0;
+}
+
+int op_gemm_backward(void *context, vitb200_tensor *left, vitb200_tensor *right,
+                     const vitb200_tensor *output) {
+    CudaBackend *backend = self(context);
+    if (!ours({left->data, left->grad, right->data, right->grad,
+               output->grad}) ||
+        !fits_int(left->rows) || !fits_int(left->cols) ||
+        !fits_int(right->cols)) {
+        return -1;
+    }
+    const float *x = view(backend, left->data, Access::Read);
+    const float *w = view(backend, right->data, Access::Read);
+    const float *dy = view(backend, output->grad, Access::Read);
+    float *dx = view(backend, left->grad, Access::ReadWrite);
+    float *dw = view(backend, right->grad, Access::ReadWrite);
+    gemm_backward(x, w, dy, dx, dw, int(left->rows), int(left->cols),
+                  int(right->cols), VITB200_PRECISION_AUTO, backend->stream);
+    check_launch("gemm_backward");
+    return 0;
+}
+
+int op_residual(void *context, const vitb200_tensor *left,
+                const vitb200_tensor *right, vitb200_tensor *output) {
+    CudaBackend *backend = self(context);
+    if (!ours({left->data, right->data, output->data})) {
+        return -1;
+    }
+    const float *a = view(backend, left->data, Access::Read);
+    const float *b = view(backend, right->data, Access::Read);
+    float *out = view(backend, output->data, Access::Overwrite);
+    launch_add(a, b, out, numel(output), backend->stream);
+    check_launch("residual");
+    return 0;
+}
+
+int op_residual_backward(void *context, vitb200_tensor *left,
+                         vitb200_tensor *right, const vitb200_tensor *output) {
+    CudaBackend *backend = self(context);
+    // One pass updates both branches, which needs them to be distinct.
+    if (!ours({left->grad, right->grad, output->grad}) ||
+        left->grad == right->grad) {
+        return -1;
+    }
+    float *a = view(backend, left->grad, Access::ReadWrite);
+    float *b = view(backend, right->grad, Access::ReadWrite);
+    const float *g = view(backend, output->grad, Access::Read);
+    launch_accumulate2(a, b, g, numel(output), backend->stream);
+    check_launch("residual_backward");
+    return 0;
+}
+
+int op_accumulate_gradient(void *context, vitb200_tensor *destination,
+                           const vitb200_tensor *source) {
+    CudaBackend *backend = self(context);
+    if (!ours({destination->grad, source->grad}) ||
+        destination->grad == source->grad) {
+        return -1;
+    }
+    float *dst = view(backend, destination->grad, Access::ReadWrite);
+    const float *src = view(backend, source->grad, Access::Read);
+    launch_accumulate(dst, src, numel(destination), backend->stream);
+    check_launch("accumulate_gradient");
+    return 0;
+}
+
+int op_bias_add(void *context, const vitb200_tensor *input,
+                const vitb200_tensor *bias, vitb200_tensor *output) {
+    CudaBackend *backend = self(context);
+    if (!ours({input->data, bias->data, output->data})) {
+        return -1;
+    }
+    const float *b = view(backend, bias->data, Access::Read);
+    const bool in_place = input->data == output->data;
+    const float *in =
+        view(backend, input->data, in_place ? Access::ReadWrite : Access::Read);
+    float *out = in_place ? const_cast<float *>(in)
+                          : view(backend, output->data, Access::Overwrite);
+    launch_bias_add(in, b, out, input->rows, input->cols, backend->stream);
+    check_launch("bias_add");
+    return 0;
+}
+
+int op_bias_add_backward(void *context, const vitb200_tensor *output,
+                         vitb200_tensor *bias_grad) {
+    CudaBackend *backend = self(context);
+    if (!ours({output->grad, bias_grad->grad})) {
+        return -1;
+    }
+    const float *dy = view(backend, output->grad, Access::Read);
+    float *db = view(backend, bias_grad->grad, Access::ReadWrite);
+    launch_column_sums(dy, db, output->rows, output->cols, output->cols,
+                       backend->stream);
+    check_launch("bias_add_backward");
+    return 0;
+}
+
+int op_layer_norm(void *context, const vitb200_tensor *input,
+                  const vitb200_tensor *gamma, const vitb200_tensor *beta,
+                  float epsilon, vitb200_tensor *output) {
+    CudaBackend *backend = self(context);
+    if (!ours({input->data, gamma->data, beta->data, output->data}) ||
+        input->data == output->data) {
+        return -1;
+    }
+    const float *x = view(backend, input->data, Access::Read);
+    const float *g = view(backend, gamma->data, Access::Read);
+    const float *b = view(backend, beta->data, Access::Read);
+    float *y = view(backend, output->data, Access::Overwrite);
+    launch_layer_norm(x, g, b, epsilon, y, input->rows, input->cols,
+                      backend->stream);
+    check_launch("layer_norm");
+    return 0;
+}
+
+int op_layer_norm_backward(void *context, const vitb200_tensor *input,
+                           const vitb200_tensor *gamma, float epsilon,
+                           const vitb200_tensor *output,
+                           vitb200_tensor *input_grad,
+                           vitb200_tensor *gamma_grad,
+                           vitb200_tensor *beta_grad) {
+    CudaBackend *backend = self(context);
+    if (!ours({input->data, gamma->data, output->grad, input_grad->grad,
+               gamma_grad->grad, beta_grad->grad}) ||
+        output->grad == input_grad->grad) {
+        return -1;
+    }
+    const float *x = view(backend, input->data, Access::Read);
+    const float *g = view(backend, gamma->data, Access::Read);
+    const float *dy = view(backend, output->grad, Access::Read);
+    float *dx = view(backend, input_grad->grad, Access::ReadWrite);
+    float *dg = view(backend, gamma_grad->grad, Access::ReadWrite);
+    float *db = view(backend, beta_grad->grad, Access::ReadWrite);
+    launch_layer_norm_backward(x, g, epsilon, dy, dx, dg, db, input->rows,
+                               input->cols, backend->stream);
+    check_launch("layer_norm_backward");
+    return 0;
+}
+
+int op_gelu(void *context, const vitb200_tensor *input,
+            vitb200_tensor *output) {
+    CudaBackend *backend = self(context);
+    if (!ours({input->data, output->data}) || input->data == output->data) {
+        return -1;
+    }
+    const float *in = view(backend, input->data, Access::Read);
+    float *out = view(backend, output->data, Access::Overwrite);
+    launch_gelu(in, out, numel(input), backend->stream);
+    check_launch("gelu");
+    return 0;
+}
+
+int op_gelu_backward(void *context, const vitb200_tensor *input,
+                     const vitb200_tensor *output) {
+    CudaBackend *backend = self(context);
+    if (!ours({input->data, input->grad, output->grad})) {
+        return -1;
+    }
+    const float *x = view(backend, input->data, Access::Read);
+    const float *dy = view(backend, output->grad, Access::Read);
+    float *dx = view(backend, input->grad, Access::ReadWrite);
+    launch_gelu_backward(x, dy, dx, numel(input), backend->stream);
+    check_launch("gelu_backward");
+    return 0;
+}
+
+int op_split_heads(void *context, const vitb200_tensor *projected,
+                   vitb200_tensor *query, vitb200_tensor *key,
+                   vitb200_tensor *value, size_t batch, size_t seq,
+                   size_t d_model, size_t heads) {
+    CudaBackend *backend = self(context);
+    if (!ours({projected->data, query->data, key->data, value->data})) {
+        return -1;
+    }
+    const float *p = view(backend, projected->data, Access::Read);
+    float *q = view(backend, query->data, Access::Overwrite);
+    float *k = view(backend, key->data, Access::Overwrite);
+    float *v = view(backend, value->data, Access::Overwrite);
+    launch_split_heads(p, q, k, v, batch, seq, d_model, heads, backend->stream);
+    check_launch("split_heads");
+    return 0;
+}
+
+int op_split_heads_backward(void *context, vitb200_tensor *projected,
+                            const vitb200_tensor *query,
+                            const vitb200_tensor *key,
+                            const vitb200_tensor *value, size_t batch,
+                            size_t seq, size_t d_model, size_t heads) {
+    CudaBackend *backend = self(context);
+    if (!ours({projected->grad, query->grad, key->grad, value->grad})) {
+        return -1;
+    }
+    float *p = view(backend, projected->grad, Access::ReadWrite);
+    const float *q = view(backend, query->grad, Access::Read);
+    const float *k = view(backend, key->grad, Access::Read);
+    const float *v = view(backend, value->grad, Access::Read);
+    launch_split_heads_backward(p, q, k, v, batch, seq, d_model, heads,
+                                backend->stream);
+    check_launch("split_heads_backward");
+    return 0;
+}
+
+int op_merge_heads(void *context, const vitb200_tensor *attended,
+                   vitb200_tensor *merged, size_t batch, size_t seq,
+                   size_t d_model, size_t heads) {
+    CudaBackend *backend = self(context);
+    if (!ours({attended->data, merged->data})) {
+        return -1;
+    }
+    const float *a = view(backend, attended->data, Access::Read);
+    float *m = view(backend, merged->data, Access::Overwrite);
+    launch_merge_heads(a, m, batch, seq, d_model, heads, backend->stream);
+    check_launch("merge_heads");
+    return 0;
+}
+
+int op_merge_heads_backward(void *context, vitb200_tensor *attended,
+                            const vitb200_tensor *merged, size_t batch,
+                            size_t seq, size_t d_model, size_t heads) {
+    CudaBackend *backend = self(context);
+    if (!ours({attended->grad, merged->grad})) {
+        return -1;
+    }
+    float *a = view(backend, attended->grad, Access::ReadWrite);
+    const float *m = view(backend, merged->grad, Access::Read);
+    launch_merge_heads_backward(a, m, batch, seq, d_model, heads,
+                                backend->stream);
+    check_launch("merge_heads_backward");
+    return 0;
+}
+
+constexpr size_t kMaxHeadDim = 128;
+
+int op_attention(void *context, const vitb200_tensor *query,
+                 const vitb200_tensor *key, const vitb200_tensor *value,
+                 size_t batch, size_t heads, size_t seq, float scale,
+                 vitb200_tensor *probabilities, vitb200_tensor *output) {
+    CudaBackend *backend = self(context);
+    if (!ours({query->data, key->data, value->data, probabilities->data,
+               output->data}) ||
+        query->cols > kMaxHeadDim || value->cols != query->cols ||
+        !fits_int(seq) || !fits_int(batch * heads)) {
+        return -1;
+    }
+    const float *q = view(backend, query->data, Access::Read);
+    const float *k = view(backend, key->data, Access::Read);
+    const float *v = view(backend, value->data, Access::Read);
+    float *p = view(backend, probabilities->data, Access::Overwrite);
+    float *o = view(backend, output->data, Access::Overwrite);
+    launch_attention_forward(q, k, v, p, o, batch * heads, seq, query->cols,
+                             scale, backend->stream);
+    check_launch("multi_head_attention");
+    return 0;
+}
+
+int op_attention_backward(void *context, const vitb200_tensor *query,
+                          const vitb200_tensor *key,
+                          const vitb200_tensor *value, size_t batch,
+                          size_t heads, size_t seq, float scale,
+                          const vitb200_tensor *probabilities,
+                          const vitb200_tensor *output,
+                          vitb200_tensor *query_grad, vitb200_tensor *key_grad,
+                          vitb200_tensor *value_grad) {
+    CudaBackend *backend = self(context);
+    if (!ours({query->data, key->data, value->data, probabilities->data,
+               output->data, output->grad, query_grad->grad, key_grad->grad,
+               value_grad->grad}) ||
+        query->cols > kMaxHeadDim || value->cols != query->cols ||
+        !fits_int(seq) || !fits_int(batch * heads)) {
+        return -1;
+    }
+    const size_t groups = batch * heads;
+    float *dots = scratch<float>(backend, backend->rows_scratch, groups * seq);
+    const float *q = view(backend, query->data, Access::Read);
+    const float *k = view(backend, key->data, Access::Read);
+    const float *v = view(backend, value->data, Access::Read);
+    const float *p = view(backend, probabilities->data, Access::Read);
+    const float *o = view(backend, output->data, Access::Read);
+    const float *go = view(backend, output->grad, Access::Read);
+    float *dq = view(backend, query_grad->grad, Access::ReadWrite);
+    float *dk = view(backend, key_grad->grad, Access::ReadWrite);
+    float *dv = view(backend, value_grad->grad, Access::ReadWrite);
+    launch_attention_backward(q, k, v, p, o, go, dq, dk, dv, dots, groups, seq,
+                              query->cols, scale, backend->stream);
+    check_launch("multi_head_attention_backward");
+    return 0;
+}
+
+int op_zero_gradient(void *context, vitb200_tensor *tensor) {
+    CudaBackend *backend = self(context);
+    if (!ours({tensor->grad})) {
+        return -1;
+    }
+    float *g = view(backend, tensor->grad, Access::Overwrite);
+    check(cudaMemsetAsync(g, 0, numel(tensor) * sizeof(float), backend->stream),
+          "cudaMemsetAsync");
+    return 0;
+}
+
+int op_zero_gradients(void *context, vitb200_tensor *const *tensors,
+                      size_t count) {
+    CudaBackend *backend = self(context);
+    for (size_t i = 0; i < count; ++i) {
+        if (!coherent_owns(tensors[i]->grad)) {
+            return -1;
+        }
+    }
+    for (size_t i = 0; i < count; ++i) {
+        float *g = view(backend, tensors[i]->grad, Access::Overwrite);
+        check(cudaMemsetAsync(g, 0, numel(tensors[i]) * sizeof(float),
+                              backend->stream),
+              "cudaMemsetAsync");
+    }
+    return 0;
+}
+
+int op_extract_patches(void *context, const vitb200_tensor *images,
+                       vitb200_tensor *patches, size_t channels, size_t height,
+                       size_t width, size_t patch) {
+    CudaBackend *backend = self(context);
+    if (!ours({images->data, patches->data})) {
+        return -1;
+    }
+    const float *in = view(backend, images->data, Access::Read);
+    float *out = view(backend, patches->data, Access::Overwrite);
+    launch_extract_patches(in, out, images->rows, channels, height, width,
+                           patch, backend->stream);
+    check_launch("extract_patches");
+    return 0;
+}
+
+int op_token_embedding(void *context, const vitb200_tensor *patch_tokens,
+                       const vitb200_tensor *cls, const vitb200_tensor *pos,
+                       vitb200_tensor *tokens, size_t batch) {
+    CudaBackend *backend = self(context);
+    if (!ours({patch_tokens->data, cls->data, pos->data, tokens->data})) {
+        return -1;
+    }
+    const float *p = view(backend, patch_tokens->data, Access::Read);
+    const float *c = view(backend, cls->data, Access::Read);
+    const float *e = view(backend, pos->data, Access::Read);
+    float *t = view(backend, tokens->data, Access::Overwrite);
+    launch_token_embedding(p, c, e, t, batch, pos->rows, tokens->cols,
+                           backend->stream);
+    check_launch("token_embedding");
+    return 0;
+}
+
+int op_token_embedding_backward(void *context, vitb200_tensor *patch_tokens,
+                                vitb200_tensor *cls, vitb200_tensor *pos,
+                                const vitb200_tensor *tokens, size_t batch) {
+    CudaBackend *backend = self(context);
+    if (!ours({patch_tokens->grad, cls->grad, pos->grad, tokens->grad})) {
+        return -1;
+    }
+    float *p = view(backend, patch_tokens->grad, Access::ReadWrite);
+    float *c = view(backend, cls->grad, Access::ReadWrite);
+    float *e = view(backend, pos->grad, Access::ReadWrite);
+    const float *t = view(backend, tokens->grad, Access::Read);
+    launch_token_embedding_backward(p, c, e, t, batch, pos->rows, tokens->cols,
+                                    backend->stream);
+    check_launch("token_embedding_backward");
+    return 0;
+}
+
+int op_gather_rows(void *context, const vitb200_tensor *source,
+                   vitb200_tensor *destination, size_t row_stride) {
+    CudaBackend *backend = self(context);
+    if (!ours({source->data, destination->data})) {
+        return -1;
+    }
+    const float *s = view(backend, source->data, Access::Read);
+    float *d = view(backend, destination->data, Access::Overwrite);
+    launch_gather_rows(s, d, destination->rows, destination->cols, row_stride,
+                       backend->stream);
+    check_launch("gather_rows");
+    return 0;
+}
+
+int op_gather_rows_backward(void *context, vitb200_tensor *source,
+                            const vitb200_tensor *destination,
+                            size_t row_stride) {
+    CudaBackend *backend = self(context);
+    if (!ours({source->grad, destination->grad})) {
+        return -1;
+    }
+    float *s = view(backend, source->grad, Access::ReadWrite);
+    const float *d = view(backend, destination->grad, Access::Read);
+    launch_gather_rows_backward(s, d, destination->rows, destination->cols,
+                                row_stride, backend->stream);
+    check_launch("gather_rows_backward");
+    return 0;
+}
+
+int op_softmax_cross_entropy(void *context, const vitb200_tensor *logits,
+                             const vitb200_tensor *targets,
+                             const vitb200_tensor *class_weights,
+                             float label_smoothing, vitb200_tensor *loss,
+                             vitb200_tensor *logits_grad) {
+    CudaBackend *backend = self(context);
+    if (!ours({logits->data, targets->data, loss->data, logits_grad->grad}) ||
+        (class_weights && !coherent_owns(class_weights->data))) {
+        return -1;
+    }
+    float *row_losses =
+        scratch<float>(backend, backend->rows_scratch, logits->rows);
+    const float *z = view(backend, logits->data, Access::Read);
+    const float *t = view(backend, targets->data, Access::Read);
+    const float *w = class_weights
+        ? view(backend, class_weights->data, Access::Read)
+        : nullptr;
+    float *l = view(backend, loss->data, Access::Overwrite);
+    float *g = view(backend, logits_grad->grad, Access::ReadWrite);
+    launch_softmax_cross_entropy(z, t, w, label_smoothing, l, g, row_losses,
+                                 logits->rows, logits->cols, backend->stream);
+    check_launch("softmax_cross_entropy");
+    return 0;
+}
+
+// Copies `bytes` from host memory into a device buffer through the pinned
+// ring, without waiting for earlier work on the stream.
+void upload_small(CudaBackend *backend, void *device, const void *host,
+                  size_t bytes) {
+    const int slot = backend->staging_next;
+    backend->staging_next = (slot + 1) % kStagingSlots;
+    check(cudaEventSynchronize(backend->staging_done[slot]),
+          "cudaEventSynchronize");
+    memcpy(backend->staging[slot], host, bytes);
+    check(cudaMemcpyAsync(device, backend->staging[slot], bytes,
+                          cudaMemcpyHostToDevice, backend->stream),
+          "cudaMemcpyAsync");
+    check(cudaEventRecord(backend->staging_done[slot], backend->stream),
+          "cudaEventRecord");
+}
+
+struct SliceTable {
+    const ParameterSlice *device = nullptr;
+    unsigned slices = 0;
+    unsigned blocks = 0;
+};
+
+// with_moments = false builds a gradient-only table (for clipping alone).
+int build_slice_table(CudaBackend *backend,
+                      vitb200_parameter *const *parameters,
+                      const float *weight_decays, size_t count, float beta1,
+                      float beta2, bool with_moments, SliceTable *table) {
+    if (count == 0 || count * sizeof(ParameterSlice) > kStagingBytes) {
+        return -1;
+    }
+    for (size_t i = 0; i < count; ++i) {
+        const vitb200_parameter *p = parameters[i];
+        if (!ours({p->value.grad}) ||
+            (with_moments && !ours({p->value.data, p->m, p->v}))) {
+            return -1;
+        }
+    }
+    std::vector<ParameterSlice> slices(count);
+    unsigned long long blocks = 0;
+    for (size_t i = 0; i < count; ++i) {
+        vitb200_parameter *p = parameters[i];
+        ParameterSlice &slice = slices[i];
+        slice.value = with_moments
+            ? view(backend, p->value.data, Access::ReadWrite) : nullptr;
+        slice.grad = view(backend, p->value.grad, Access::ReadWrite);
+        slice.m = with_moments ? view(backend, p->m, Access::ReadWrite) : nullptr;
+        slice.v = with_moments ? view(backend, p->v, Access::ReadWrite) : nullptr;
+        slice.count = numel(&p->value);
+        slice.first_block = blocks;
+        slice.weight_decay = weight_decays ? weight_decays[i] : 0.0f;
+        // The host has already advanced `step` (reference src/ops.c:1140-1142).
+        slice.correction1 = 1.0f - powf(beta1, float(p->step));
+        slice.correction2 = 1.0f - powf(beta2, float(p->step));
+        slice.pad = 0.0f;
+        blocks += (slice.count + kSliceBlockElements - 1) / kSliceBlockElements;
+    }
+    if (blocks == 0 || blocks > unsigned(INT_MAX)) {
+        return -1;
+    }
+    ParameterSlice *device =
+        scratch<ParameterSlice>(backend, backend->slice_table, count);
+    upload_small(backend, device, slices.data(),
+                 count * sizeof(ParameterSlice));
+    table->device = device;
+    table->slices = unsigned(count);
+    table->blocks = unsigned(blocks);
+    return 0;
+}
+
+int op_clip_gradient_norm(void *context, vitb200_parameter *const *parameters,
+                          size_t count, float max_norm) {
+    CudaBackend *backend = self(context);
+    SliceTable table;
+    if (build_slice_table(backend, parameters, nullptr, count, 0.0f, 0.0f,
+                          false, &table) != 0) {
+        return -1;
+    }
+    float *partials =
+        scratch<float>(backend, backend->norm_partials, table.blocks);
+    float *scale = scratch<float>(backend, backend->clip_scale, 1);
+    launch_gradient_clip_scale(table.device, table.slices, table.blocks,
+                               max_norm, partials, scale, backend->stream);
+    launch_scale_gradients(table.device, table.slices, table.blocks, scale,
+                           backend->stream);
+    check_launch("clip_gradient_norm");
+    return 0;
+}
+
+int op_adamw_step(void *context, vitb200_parameter *parameter, float lr,
+                  float beta1, float beta2, float epsilon, float weight_decay,
+                  float correction1, float correction2) {
+    CudaBackend *backend = self(context);
+    if (!ours({parameter->value.data, parameter->value.grad, parameter->m,
+               parameter->v})) {
+        return -1;
+    }
+    float *w = view(backend, parameter->value.data, Access::ReadWrite);
+    float *g = view(backend, parameter->value.grad, Access::ReadWrite);
+    float *m = view(backend, parameter->m, Access::ReadWrite);
+    float *v = view(backend, parameter->v, Access::ReadWrite);
+    launch_adamw_single(w, g, m, v, numel(&parameter->value), lr, beta1, beta2,
+                        epsilon, weight_decay, correction1, correction2,
+                        backend->stream);
+    check_launch("adamw_step");
+    return 0;
+}
+
+int op_adamw_step_parameters(void *context,
+                             vitb200_parameter *const *parameters,
+                             const float *weight_decays, size_t count, float lr,
+                             float beta1, float beta2, float epsilon,
+                             float max_gradient_norm) {
+    CudaBackend *backend = self(context);
+    SliceTable table;
+    if (build_slice_table(backend, parameters, weight_decays, count, beta1,
+                          beta2, true, &table) != 0) {
+        return -1;
+    }
+    const float *scale = nullptr;
+    if (max_gradient_norm > 0.0f) {
+        float *partials =
+            scratch<float>(backend, backend->norm_partials, table.blocks);
+        float *scale_out = scratch<float>(backend, backend->clip_scale, 1);
+        launch_gradient_clip_scale(table.device, table.slices, table.blocks,
+                                   max_gradient_norm, partials, scale_out,
+                                   backend->stream);
+        scale = scale_out;
+    }
+    launch_adamw(table.device, table.slices, table.blocks, scale, lr, beta1,
+                 beta2, epsilon, backend->stream);
+    check_launch("adamw_step_parameters");
+    return 0;
+}
+
+void op_synchronize(void *context) {
+    check(cudaStreamSynchronize(self(context)->stream), "cudaStreamSynchronize");
+}
+
+vitb200_op_table make_table(CudaBackend *backend) {
+    vitb200_op_table table = {};
+    table.context = backend;
+    table.gemm = op_gemm;
+    table.gemm_backward = op_gemm_backward;
+    table.residual = op_residual;
+    table.residual_backward = op_residual_backward;
+    table.accumulate_gradient = op_accumulate_gradient;
+    table.bias_add = op_bias_add;
+    table.bias_add_backward = op_bias_add_backward;
+    table.layer_norm = op_layer_norm;
+    table.layer_norm_backward = op_layer_norm_backward;
+    table.gelu = op_gelu;
+    table.gelu_backward = op_gelu_backward;
+    table.split_heads = op_split_heads;
+    table.split_heads_backward = op_split_heads_backward;
+    table.merge_heads = op_merge_heads;
+    table.merge_heads_backward = op_merge_heads_backward;
+    table.multi_head_attention = op_attention;
+    table.multi_head_attention_backward = op_attention_backward;
+    table.zero_gradient = op_zero_gradient;
+    table.extract_patches = op_extract_patches;
+    table.token_embedding = op_token_embedding;
+    table.token_embedding_backward = op_token_embedding_backward;
+    table.gather_rows = op_gather_rows;
+    table.gather_rows_backward = op_gather_rows_backward;
+    table.softmax_cross_entropy = op_softmax_cross_entropy;
+    table.clip_gradient_norm = op_clip_gradient_norm;
+    table.adamw_step = op_adamw_step;
+    table.zero_gradients = op_zero_gradients;
+    table.adamw_step_parameters = op_adamw_step_parameters;
+    table.synchronize = op_synchronize;
+    return table;
+}
+
+int pick_device(int device_count) {
+    const char *explicit_device = getenv("VITB200_DEVICE");
+    const char *from_rank = getenv("VITB200_DEVICE_FROM_RANK");
+    const char *local_rank = getenv("LOCAL_RANK");
+    int device = 0;
+    if (explicit_device) {
+        device = atoi(explicit_device);
+    } else if (from_rank && atoi(from_rank) != 0 && local_rank) {
+        device = atoi(local_rank);
+    }
+    return device >= 0 && device < device_count ? device : -1;
+}
+
+cudaStream_t as_stream(void *stream) {
+    return static_cast<cudaStream_t>(stream);
+}
+
+}  // namespace
+
+// ------------------------------------------------------------------ part 1
+
+extern "C" int cuda_backend_create(CudaBackend **backend) {
+    if (!backend) {
+        return -1;
+    }
+    *backend = nullptr;
+    int device_count = 0;
+    if (cudaGetDeviceCount(&device_count) != cudaSuccess || device_count == 0) {
+        cudaGetLastError();
+        return 1;
+    }
+    const int device = pick_device(device_count);
+    cudaDeviceProp properties = {};
+    if (device < 0 || cudaSetDevice(device) != cudaSuccess ||
+        cudaGetDeviceProperties(&properties, device) != cudaSuccess) {
+        cudaGetLastError();
+        return 1;
+    }
+    if (properties.major != 10) {
+        fprintf(stderr,
+                "vitb200: device %d is sm_%d%d; this library carries sm_100a "
+                "code only\n",
+                device, properties.major, properties.minor);
+        return 1;
+    }
+    CudaBackend *result = new CudaBackend();
+    result->device = device;
+    if (cudaStreamCreateWithFlags(&result->stream, cudaStreamNonBlocking) !=
+        cudaSuccess) {
+        delete result;
+        return -1;
+    }
+    bool ok = cudaEventCreate(&result->timer_begin) == cudaSuccess &&
+              cudaEventCreate(&result->timer_end) == cudaSuccess;
+    for (int i = 0; ok && i < kStagingSlots; ++i) {
+        ok = cudaHostAlloc(reinterpret_cast<void **>(&result->staging[i]),
+                           kStagingBytes, cudaHostAllocDefault) == cudaSuccess &&
+             cudaEventCreateWithFlags(&result->staging_done[i],
+                                      cudaEventDisableTiming) == cudaSuccess;
+    }
+    if (!ok) {
+        cuda_backend_free(result);
+        return -1;
+    }
+    coherence_set_stream(result->stream, nullptr);
+    *backend = result;
+    return 0;
+}
+
+extern "C" void cuda_backend_free(CudaBackend *backend) {
+    if (!backend) {
+        return;
+    }
+    cuda_backend_disable_device_execution(backend);
+    if (backend->stream) {
+        cudaStreamSynchronize(backend->stream);
+    }
+    free_scratch(backend->rows_scratch);
+    free_scratch(backend->norm_partials);
+    free_scratch(backend->clip_scale);
+    free_scratch(backend->slice_table);
+    for (int i = 0; i < kStagingSlots; ++i) {
+        if (backend->staging[i]) {
+            cudaFreeHost(backend->staging[i]);
+        }
+        if (backend->staging_done[i]) {
+            cudaEventDestroy(backend->staging_done[i]);
+        }
+    }
+    if (backend->timer_begin) {
+        cudaEventDestroy(backend->timer_begin);
+    }
+    if (backend->timer_end) {
+        cudaEventDestroy(backend->timer_end);
+    }
+    // Tensors that outlive the backend are copied back on the legacy default
+    // stream from here on.
+    coherence_set_stream(nullptr, nullptr);
+    if (backend->stream) {
+        cudaStreamDestroy(backend->stream);
+    }
+    delete backend;
+}
+
+extern "C" int cuda_backend_available(const CudaBackend *backend) {
+    return backend && backend->stream ? 1 : 0;
+}
+
+extern "C" int cuda_backend_enable_device_execution(CudaBackend *backend) {
+    if (!cuda_backend_available(backend)) {
+        return -1;
+    }
+    backend->set_table = ops_set_device_backend;
+    backend->set_allocator = tensor_set_allocator;
+    if (!backend->set_table) {
+        backend->set_table = reinterpret_cast<void (*)(const vitb200_op_table *)>(
+            dlsym(RTLD_DEFAULT, "ops_set_device_backend"));
+    }
+    if (!backend->set_allocator) {
+        backend->set_allocator = reinterpret_cast<void (*)(
+            vitb200_allocate_fn, vitb200_release_fn, void *)>(
+            dlsym(RTLD_DEFAULT, "tensor_set_allocator"));
+    }
+    if (!backend->set_table || !backend->set_allocator) {
+        fprintf(stderr,
+                "vitb200: host functions ops_set_device_backend / "
+                "tensor_set_allocator not found in this process\n");
+        return -1;
+    }
+    check(cudaSetDevice(backend->device), "cudaSetDevice");
+    coherence_install_fault_handler();
+    coherence_set_stream(backend->stream, nullptr);
+    backend->table = make_table(backend);
+    backend->set_table(&backend->table);
+    backend->set_allocator(coherent_allocate, coherent_release, backend);
+    backend->enabled = 1;
+    return 0;
+}
+
+extern "C" void cuda_backend_disable_device_execution(CudaBackend *backend) {
+    if (!backend || !backend->enabled) {
+        return;
+    }
+    check(cudaStreamSynchronize(backend->stream), "cudaStreamSynchronize");
+    // ops_set_device_backend synchronises the outgoing table first
+    // (reference src/ops.c:66-74).
+    backend->set_table(nullptr);
+    backend->set_allocator(nullptr, nullptr, nullptr);
+    backend->enabled = 0;
+}
+
+extern "C" unsigned long long vitb200_kernel_launches(void) {
+    return g_kernel_launches;
+}
+
+extern "C" void vitb200_memory_counters(size_t *live_allocations,
+                                        size_t *mirror_bytes,
+                                        size_t *device_bytes,
+                                        size_t *h2d_copies, size_t *h2d_bytes,
+                                        size_t *d2h_copies, size_t *d2h_bytes,
+                                        size_t *faults) {
+    const CoherenceStats s = coherence_stats();
+    if (live_allocations) *live_allocations = s.live_allocations;
+    if (mirror_bytes) *mirror_bytes = s.mirror_bytes;
+    if (device_bytes) *device_bytes = s.device_bytes;
+    if (h2d_copies) *h2d_copies = s.host_to_device_copies;
+    if (h2d_bytes) *h2d_bytes = s.host_to_device_bytes;
+    if (d2h_copies) *d2h_copies = s.device_to_host_copies;
+    if (d2h_bytes) *d2h_bytes = s.device_to_host_bytes;
+    if (faults) *faults = s.faults_served;
+}
+
+extern "C" int vitb200_make_host_coherent(const void *tensor_memory) {
+    return coherent_make_host_owned(tensor_memory);
+}
+
+extern "C" int vitb200_timer_begin(CudaBackend *backend) {
+    if (!cuda_backend_available(backend)) {
+        return -1;
+    }
+    return cudaEventRecord(backend->timer_begin, backend->stream) == cudaSuccess
+        ? 0 : -1;
+}
+
+extern "C" float vitb200_timer_end(CudaBackend *backend) {
+    if (!cuda_backend_available(backend) ||
+        cudaEventRecord(backend->timer_end, backend->stream) != cudaSuccess ||
+        cudaEventSynchronize(backend->timer_end) != cudaSuccess) {
+        return -1.0f;
+    }
+    float ms = -1.0f;
+    cudaEventElapsedTime(&ms, backend->timer_begin, backend->timer_end);
+    return ms;
+}
+
+// ------------------------------------------------------------------ part 2
+
+extern "C" int vitb200_k_gemm(const float *x, const float *w, float *y,
+                              size_t m, size_t k, size_t n, int precision,
+                              void *stream) {
+    if (!fits_int(m) || !fits_int(k) || !fits_int(n)) {
+        return -1;
+    }
+    return gemm_forward(x, w, y, int(m), int(k), int(n), precision,
+                        as_stream(stream));
+}
+
+extern "C" int vitb200_k_gemm_backward(const float *x, const float *w,
+                                       const float *dy, float *dx, float *dw,
+                                       size_t m, size_t k, size_t n,
+                                       int precision, void *stream) {
+    if (!fits_int(m) || !fits_int(k) || !fits_int(n)) {
+        return -1;
+    }
+    return gemm_backward(x, w, dy, dx, dw, int(m), int(k), int(n), precision,
+                         as_stream(stream));
+}
+
+extern "C" int vitb200_k_bias_add(const float *in, const float *bias,
+                                  float *out, size_t rows, size_t cols,
+                                  void *stream) {
+    launch_bias_add(in, bias, out, rows, cols, as_stream(stream));
+    return 0;
+}
+
+extern "C" int vitb200_k_column_sums(const float *in, float *out, size_t rows,
+                                     size_t cols, void *stream) {
+    launch_column_sums(in, out, rows, cols, cols, as_stream(stream));
+    return 0;
+}
+
+extern "C" int vitb200_k_layer_norm(const float *x, const float *gamma,
+                                    const float *beta, float epsilon, float *y,
+                                    size_t rows, size_t cols, void *stream) {
+    launch_layer_norm(x, gamma, beta, epsilon, y, rows, cols,
+                      as_stream(stream));
+    return 0;
+}
+
+extern "C" int vitb200_k_layer_norm_backward(const float *x, const float *gamma,
+                                             float epsilon, const float *dy,
+                                             float *dx, float *dgamma,
+                                             float *dbeta, size_t rows,
+                                             size_t cols, void *stream) {
+    launch_layer_norm_backward(x, gamma, epsilon, dy, dx, dgamma, dbeta, rows,
+                               cols, as_stream(stream));
+    return 0;
+}
+
+extern "C" int vitb200_k_gelu(const float *in, float *out, size_t n,
+                              void *stream) {
+    launch_gelu(in, out, n, as_stream(stream));
+    return 0;
+}
+
+extern "C" int vitb200_k_gelu_backward(const float *x, const float *dy,
+                                       float *dx, size_t n, void *stream) {
+    launch_gelu_backward(x, dy, dx, n, as_stream(stream));
+    return 0;
+}
+
+extern "C" int vitb200_k_attention(const float *q, const float *k,
+                                   const float *v, float *probabilities,
+                                   float *out, size_t groups, size_t seq,
+                                   size_t head_dim, float scale, void *stream) {
+    if (head_dim > kMaxHeadDim || !fits_int(seq) || !fits_int(groups)) {
+        return -1;
+    }
+    launch_attention_forward(q, k, v, probabilities, out, groups, seq, head_dim,
+                             scale, as_stream(stream));
+    return 0;
+}
+
+extern "C" int vitb200_k_attention_backward(
+    const float *q, const float *k, const float *v, const float *probabilities,
+    const float *out, const float *dout, float *dq, float *dk, float *dv,
+    float *row_dots, size_t groups, size_t seq, size_t head_dim, float scale,
+    void *stream) {
+    if (head_dim > kMaxHeadDim || !fits_int(seq) || !fits_int(groups)) {
+        return -1;
+    }
+    launch_attention_backward(q, k, v, probabilities, out, dout, dq, dk, dv,
+                              row_dots, groups, seq, head_dim, scale,
+                              as_stream(stream));
+    return 0;
+}
+
+extern "C" int vitb200_k_softmax_cross_entropy(
+    const float *logits, const float *targets, const float *class_weights,
+    float label_smoothing, float *loss, float *logits_grad, float *row_losses,
+    size_t rows, size_t cols, void *stream) {
+    launch_softmax_cross_entropy(logits, targets, class_weights,
+                                 label_smoothing, loss, logits_grad, row_losses,
+                                 rows, cols, as_stream(stream));
+    return 0;
+}

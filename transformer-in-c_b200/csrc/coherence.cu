@@ -1,0 +1,266 @@
+#include "coherence.h"
+
+#include <cerrno>
+#include <csignal>
+#include <cstdint>
+#include <cstdio>
+#include <cstdlib>
+#include <cstring>
+#include <map>
+
+#include <sys/mman.h>
+#include <ucontext.h>
+#include <unistd.h>
+
+namespace vitb200 {
+namespace {
+
+enum class Owner { Host, Shared, Device };
+
+struct Region {
+    char *mirror = nullptr;
+    size_t bytes = 0;         // size the host asked for
+    size_t mapped = 0;        // page-rounded size of the mapping
+    float *device = nullptr;  // created on first device use
+    Owner owner = Owner::Host;
+};
+
+// Process-global on purpose: the host keeps the release function inside every
+// tensor and may call it long after the backend object is gone.
+std::map<uintptr_t, Region> &registry() {
+    static std::map<uintptr_t, Region> *regions =
+        new std::map<uintptr_t, Region>();
+    return *regions;
+}
+
+CoherenceStats g_stats = {};
+cudaStream_t g_stream = nullptr;
+void (*g_flush)(void) = nullptr;
+struct sigaction g_previous_action;
+bool g_handler_installed = false;
+size_t g_page = 4096;
+
+// Mirrors at least this large give their pages back to the kernel while the
+// device owns the contents; they are re-populated on copy-back.
+constexpr size_t kDropPagesThreshold = size_t(1) << 21;
+
+[[noreturn]] void die(const char *what, const char *detail) {
+    fprintf(stderr, "vitb200: %s failed: %s\n", what, detail);
+    abort();
+}
+
+void check(cudaError_t status, const char *what) {
+    if (status != cudaSuccess) {
+        die(what, cudaGetErrorString(status));
+    }
+}
+
+void protect(Region &region, int protection) {
+    if (mprotect(region.mirror, region.mapped, protection) != 0) {
+        die("mprotect", strerror(errno));
+    }
+}
+
+Region *find_base(const void *pointer) {
+    auto &regions = registry();
+    auto it = regions.find(reinterpret_cast<uintptr_t>(pointer));
+    return it == regions.end() ? nullptr : &it->second;
+}
+
+Region *find_containing(uintptr_t address) {
+    auto &regions = registry();
+    auto it = regions.upper_bound(address);
+    if (it == regions.begin()) {
+        return nullptr;
+    }
+    --it;
+    Region &region = it->second;
+    return address < it->first + region.mapped ? &region : nullptr;
+}
+
+void ensure_device_buffer(Region &region) {
+    if (!region.device) {
+        void *memory = nullptr;
+        check(cudaMalloc(&memory, region.mapped), "cudaMalloc");
+        region.device = static_cast<float *>(memory);
+        g_stats.device_bytes += region.mapped;
+    }
+}
+
+// Brings the mirror up to date and hands ownership back to the host side.
+// `for_write` selects HOST (exclusive) over SHARED (both valid).
+void serve_host_access(Region &region, bool for_write) {
+    if (region.owner == Owner::Device) {
+        if (g_flush) {
+            g_flush();
+        }
+        check(cudaStreamSynchronize(g_stream), "cudaStreamSynchronize");
+        protect(region, PROT_READ | PROT_WRITE);
+        check(cudaMemcpy(region.mirror, region.device, region.bytes,
+                         cudaMemcpyDeviceToHost),
+              "cudaMemcpy(device to host)");
+        g_stats.device_to_host_copies += 1;
+        g_stats.device_to_host_bytes += region.bytes;
+        if (for_write) {
+            region.owner = Owner::Host;
+        } else {
+            protect(region, PROT_READ);
+            region.owner = Owner::Shared;
+        }
+        return;
+    }
+    if (region.owner == Owner::Shared && for_write) {
+        // Queued kernels may still want the device copy as it is now; they
+        // read device memory, which a host write to the mirror cannot disturb,
+        // but anything not yet launched must go out before the next upload.
+        if (g_flush) {
+            g_flush();
+        }
+        protect(region, PROT_READ | PROT_WRITE);
+        region.owner = Owner::Host;
+    }
+}
+
+void on_fault(int signal_number, siginfo_t *info, void *context) {
+    const uintptr_t address = reinterpret_cast<uintptr_t>(info->si_addr);
+    Region *region = find_containing(address);
+    if (region && region->owner != Owner::Host) {
+        bool is_write = true;
+#if defined(__x86_64__)
+        const ucontext_t *machine = static_cast<const ucontext_t *>(context);
+        is_write = (machine->uc_mcontext.gregs[REG_ERR] & 0x2) != 0;
+#endif
+        g_stats.faults_served += 1;
+        serve_host_access(*region, is_write);
+        return;
+    }
+    // Not ours: behave as if we had never been installed.
+    if (g_previous_action.sa_flags & SA_SIGINFO) {
+        if (g_previous_action.sa_sigaction) {
+            g_previous_action.sa_sigaction(signal_number, info, context);
+            return;
+        }
+    } else if (g_previous_action.sa_handler != SIG_DFL &&
+               g_previous_action.sa_handler != SIG_IGN) {
+        g_previous_action.sa_handler(signal_number);
+        return;
+    }
+    signal(signal_number, SIG_DFL);
+}
+
+}  // namespace
+
+void coherence_install_fault_handler() {
+    if (g_handler_installed) {
+        return;
+    }
+    g_page = static_cast<size_t>(sysconf(_SC_PAGESIZE));
+    struct sigaction action;
+    memset(&action, 0, sizeof(action));
+    action.sa_sigaction = on_fault;
+    action.sa_flags = SA_SIGINFO | SA_NODEFER;
+    sigemptyset(&action.sa_mask);
+    if (sigaction(SIGSEGV, &action, &g_previous_action) != 0) {
+        die("sigaction", strerror(errno));
+    }
+    g_handler_installed = true;
+}
+
+void coherence_set_stream(cudaStream_t stream, void (*flush)(void)) {
+    g_stream = stream;
+    g_flush = flush;
+}
+
+void *coherent_allocate(void *context, size_t bytes) {
+    (void)context;
+    if (bytes == 0) {
+        return nullptr;
+    }
+    coherence_install_fault_handler();
+    const size_t mapped = (bytes + g_page - 1) / g_page * g_page;
+    void *mirror = mmap(nullptr, mapped, PROT_READ | PROT_WRITE,
+                        MAP_PRIVATE | MAP_ANONYMOUS, -1, 0);
+    if (mirror == MAP_FAILED) {
+        return nullptr;
+    }
+    Region region;
+    region.mirror = static_cast<char *>(mirror);
+    region.bytes = bytes;
+    region.mapped = mapped;
+    registry()[reinterpret_cast<uintptr_t>(mirror)] = region;
+    g_stats.live_allocations += 1;
+    g_stats.mirror_bytes += mapped;
+    return mirror;
+}
+
+void coherent_release(void *context, void *memory) {
+    (void)context;
+    auto &regions = registry();
+    auto it = regions.find(reinterpret_cast<uintptr_t>(memory));
+    if (it == regions.end()) {
+        return;
+    }
+    Region region = it->second;
+    regions.erase(it);
+    if (region.device) {
+        // cudaFree waits for every kernel that may still use the buffer.
+        cudaFree(region.device);
+        g_stats.device_bytes -= region.mapped;
+    }
+    munmap(region.mirror, region.mapped);
+    g_stats.live_allocations -= 1;
+    g_stats.mirror_bytes -= region.mapped;
+}
+
+bool coherent_owns(const void *host_pointer) {
+    return host_pointer && find_base(host_pointer) != nullptr;
+}
+
+float *device_view(const void *host_pointer, Access access,
+                   cudaStream_t stream) {
+    Region *region = host_pointer ? find_base(host_pointer) : nullptr;
+    if (!region) {
+        return nullptr;
+    }
+    ensure_device_buffer(*region);
+    if (region->owner == Owner::Host && access != Access::Overwrite) {
+        // Launch everything recorded so far first: the upload must not
+        // overtake kernels that were recorded against the old contents.
+        if (g_flush) {
+            g_flush();
+        }
+        check(cudaMemcpyAsync(region->device, region->mirror, region->bytes,
+                              cudaMemcpyHostToDevice, stream),
+              "cudaMemcpyAsync(host to device)");
+        g_stats.host_to_device_copies += 1;
+        g_stats.host_to_device_bytes += region->bytes;
+    }
+    if (access == Access::Read) {
+        if (region->owner == Owner::Host) {
+            protect(*region, PROT_READ);
+            region->owner = Owner::Shared;
+        }
+    } else if (region->owner != Owner::Device) {
+        protect(*region, PROT_NONE);
+        region->owner = Owner::Device;
+        if (region->mapped >= kDropPagesThreshold) {
+            madvise(region->mirror, region->mapped, MADV_DONTNEED);
+        }
+    }
+    return region->device;
+}
+
+int coherent_make_host_owned(const void *host_pointer) {
+    Region *region = host_pointer ? find_base(host_pointer) : nullptr;
+    if (!region) {
+        return -1;
+    }
+    serve_host_access(*region, true);
+    return 0;
+}
+
+CoherenceStats coherence_stats() {
+    return g_stats;
+}
+
+}  // namespace vitb200

@@ -1,0 +1,63 @@
+// Host-visible tensor memory backed by explicit device allocations.
+//
+// The host program dereferences tensor memory directly (weight initialisation,
+// input upload, loss read-back, CPU fallbacks, gradient checks), while every
+// kernel works on plain cudaMalloc'd buffers.  Each allocation handed to the
+// host is an anonymous private mapping (the "mirror"); a device buffer of the
+// same size is created the first time a kernel needs it.  Exactly one side is
+// authoritative at a time and page protection on the mirror tells us when the
+// host touches a mirror whose current contents live on the device:
+//
+//   HOST    mirror read+write, device copy stale or absent
+//   SHARED  mirror read-only, both copies identical
+//   DEVICE  mirror inaccessible, device copy authoritative
+//
+// A host access that the protection forbids raises SIGSEGV; the handler drains
+// the stream, copies the allocation back if needed, relaxes the protection and
+// returns, so the faulting instruction simply re-executes.  In steady-state
+// training only the images, the labels and the four loss bytes ever move.
+#pragma once
+
+#include <cstddef>
+#include <cuda_runtime.h>
+
+namespace vitb200 {
+
+enum class Access { Read, ReadWrite, Overwrite };
+
+struct CoherenceStats {
+    size_t live_allocations;
+    size_t mirror_bytes;
+    size_t device_bytes;
+    size_t host_to_device_copies;
+    size_t host_to_device_bytes;
+    size_t device_to_host_copies;
+    size_t device_to_host_bytes;
+    size_t faults_served;
+};
+
+// Allocator pair installed through tensor_set_allocator
+// (reference src/autodiff.c:11-17).  Both ignore `context`: tensors may be
+// released after the backend object that was current at allocation time has
+// been destroyed (reference examples/organ_smnist.c:996-997).
+void *coherent_allocate(void *context, size_t bytes);
+void coherent_release(void *context, void *memory);
+
+// True when `host_pointer` is the base address of a live mirror.
+bool coherent_owns(const void *host_pointer);
+
+// Device pointer for a mirror base address, after making the device copy valid
+// for `access` on `stream`.  Returns nullptr for memory we did not allocate.
+float *device_view(const void *host_pointer, Access access, cudaStream_t stream);
+
+// Makes the mirror readable and writable by the host again (copying back if
+// the device holds the current contents).  Needed before handing a mirror to a
+// system call such as fread/fwrite, which reports EFAULT instead of faulting.
+int coherent_make_host_owned(const void *host_pointer);
+
+// Called by the backend so the fault handler can drain work before copying.
+void coherence_set_stream(cudaStream_t stream, void (*flush)(void));
+void coherence_install_fault_handler();
+CoherenceStats coherence_stats();
+
+}  // namespace vitb200

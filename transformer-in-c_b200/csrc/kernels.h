@@ -1,0 +1,147 @@
+// Launchers for the device kernels.  Every function takes plain device
+// pointers and enqueues on `stream`; none of them allocates or synchronises.
+// Each launcher adds the number of kernels it started to g_kernel_launches.
+#pragma once
+
+#include <cstddef>
+#include <cstdint>
+#include <cuda_runtime.h>
+
+namespace vitb200 {
+
+extern unsigned long long g_kernel_launches;
+
+// ---- elementwise (elementwise.cu) ----------------------------------------
+void launch_add(const float *a, const float *b, float *out, size_t n,
+                cudaStream_t stream);                       // out = a + b
+void launch_accumulate(float *dst, const float *src, size_t n,
+                       cudaStream_t stream);                // dst += src
+void launch_accumulate2(float *dst_a, float *dst_b, const float *src, size_t n,
+                        cudaStream_t stream);               // both += src
+void launch_bias_add(const float *in, const float *bias, float *out,
+                     size_t rows, size_t cols, cudaStream_t stream);
+void launch_gelu(const float *in, float *out, size_t n, cudaStream_t stream);
+void launch_gelu_backward(const float *x, const float *dy, float *dx, size_t n,
+                          cudaStream_t stream);             // dx += dy*gelu'(x)
+void launch_scale_by_device_scalar(float *values, size_t n, const float *scale,
+                                   cudaStream_t stream);
+
+// ---- layout (layout.cu) ---------------------------------------------------
+void launch_split_heads(const float *projected, float *q, float *k, float *v,
+                        size_t batch, size_t seq, size_t d_model, size_t heads,
+                        cudaStream_t stream);
+void launch_split_heads_backward(float *projected_grad, const float *dq,
+                                 const float *dk, const float *dv, size_t batch,
+                                 size_t seq, size_t d_model, size_t heads,
+                                 cudaStream_t stream);
+void launch_merge_heads(const float *attended, float *merged, size_t batch,
+                        size_t seq, size_t d_model, size_t heads,
+                        cudaStream_t stream);
+void launch_merge_heads_backward(float *attended_grad, const float *merged_grad,
+                                 size_t batch, size_t seq, size_t d_model,
+                                 size_t heads, cudaStream_t stream);
+void launch_extract_patches(const float *images, float *patches, size_t batch,
+                            size_t channels, size_t height, size_t width,
+                            size_t patch, cudaStream_t stream);
+void launch_token_embedding(const float *patch_tokens, const float *cls,
+                            const float *positional, float *tokens,
+                            size_t batch, size_t seq, size_t d_model,
+                            cudaStream_t stream);
+void launch_token_embedding_backward(float *patch_grad, float *cls_grad,
+                                     float *positional_grad,
+                                     const float *tokens_grad, size_t batch,
+                                     size_t seq, size_t d_model,
+                                     cudaStream_t stream);
+void launch_gather_rows(const float *source, float *destination, size_t rows,
+                        size_t cols, size_t row_stride, cudaStream_t stream);
+void launch_gather_rows_backward(float *source_grad,
+                                 const float *destination_grad, size_t rows,
+                                 size_t cols, size_t row_stride,
+                                 cudaStream_t stream);
+
+// ---- reductions over rows (reduce.cu) ------------------------------------
+// out[c] += sum_r in[r * ld + c] for c < cols.
+void launch_column_sums(const float *in, float *out, size_t rows, size_t cols,
+                        size_t ld, cudaStream_t stream);
+
+// ---- layer norm (layernorm.cu) -------------------------------------------
+void launch_layer_norm(const float *x, const float *gamma, const float *beta,
+                       float epsilon, float *y, size_t rows, size_t cols,
+                       cudaStream_t stream);
+// dx += ...; dgamma += ...; dbeta += ...   (all accumulate)
+void launch_layer_norm_backward(const float *x, const float *gamma,
+                                float epsilon, const float *dy, float *dx,
+                                float *dgamma, float *dbeta, size_t rows,
+                                size_t cols, cudaStream_t stream);
+
+// ---- attention (attention.cu) --------------------------------------------
+// q, k, v, out: [groups * seq, head_dim]; probabilities: [groups * seq, seq].
+void launch_attention_forward(const float *q, const float *k, const float *v,
+                              float *probabilities, float *out, size_t groups,
+                              size_t seq, size_t head_dim, float scale,
+                              cudaStream_t stream);
+// out / dout: forward result and its gradient; row_dots: scratch of
+// groups * seq floats.  dq, dk, dv accumulate.
+void launch_attention_backward(const float *q, const float *k, const float *v,
+                               const float *probabilities, const float *out,
+                               const float *dout, float *dq, float *dk,
+                               float *dv, float *row_dots, size_t groups,
+                               size_t seq, size_t head_dim, float scale,
+                               cudaStream_t stream);
+
+// ---- loss (loss.cu) -------------------------------------------------------
+// row_losses: scratch of `rows` floats.
+void launch_softmax_cross_entropy(const float *logits, const float *targets,
+                                  const float *class_weights,
+                                  float label_smoothing, float *loss,
+                                  float *logits_grad, float *row_losses,
+                                  size_t rows, size_t cols,
+                                  cudaStream_t stream);
+
+// ---- optimiser (optimizer.cu) --------------------------------------------
+struct ParameterSlice {
+    float *value;
+    float *grad;
+    float *m;
+    float *v;
+    unsigned long long count;
+    unsigned long long first_block;  // prefix sum of blocks before this slice
+    float weight_decay;
+    float correction1;
+    float correction2;
+    float pad;
+};
+constexpr unsigned kSliceBlockElements = 4096;
+
+// partials: scratch of total_blocks floats; scale_out: 1 float.
+void launch_gradient_clip_scale(const ParameterSlice *slices, unsigned slices_n,
+                                unsigned total_blocks, float max_norm,
+                                float *partials, float *scale_out,
+                                cudaStream_t stream);
+void launch_scale_gradients(const ParameterSlice *slices, unsigned slices_n,
+                            unsigned total_blocks, const float *scale,
+                            cudaStream_t stream);
+// scale may be nullptr (no clipping).  Zeroes the gradients afterwards.
+void launch_adamw(const ParameterSlice *slices, unsigned slices_n,
+                  unsigned total_blocks, const float *scale, float lr,
+                  float beta1, float beta2, float epsilon, cudaStream_t stream);
+void launch_adamw_single(float *value, float *grad, float *m, float *v,
+                         size_t n, float lr, float beta1, float beta2,
+                         float epsilon, float weight_decay, float correction1,
+                         float correction2, cudaStream_t stream);
+
+// ---- dense products (gemm_simt.cu, gemm_tc.cu) ---------------------------
+// C[M,N] (+)= A[M,K] * B[K,N] with arbitrary element strides, FP32 FMA.
+struct GemmOperands {
+    const float *a;
+    long long a_row, a_col;  // strides, in elements, of A(m,k)
+    const float *b;
+    long long b_row, b_col;  // strides of B(k,n)
+    float *c;
+    long long c_row;         // C is always unit stride along n
+    int m, n, k;
+    int accumulate;          // 0: C = AB, 1: C += AB
+};
+void launch_gemm_simt(const GemmOperands &operands, cudaStream_t stream);
+
+}  // namespace vitb200

@@ -1,0 +1,327 @@
+// LayerNorm forward and backward, one warp per row, the row held in registers
+// (128-bit loads, one HBM read of each input), statistics by warp shuffles.
+//
+// Formulas follow the host implementation (reference src/ops.c:773-815 and
+// :845-904): mean, then the biased variance of the centred values in a second
+// pass, inverse_std = 1 / sqrtf(variance + epsilon).  The backward pass
+// recomputes the statistics from x instead of reading saved ones, and folds
+// the gamma / beta gradients (column sums over all rows) into the same pass:
+// each lane keeps running sums for the columns it owns, warps of a block
+// combine through shared memory, and one atomic per column and block lands
+// the result.
+#include "kernels.h"
+#include "device_util.cuh"
+
+namespace vitb200 {
+namespace {
+
+constexpr int kWarpsPerBlock = 8;
+
+// Lane `lane` owns float4 slots j = 0..NV-1 at columns j*128 + lane*4.
+template <int NV>
+__device__ __forceinline__ void load_row(const float *row, size_t cols,
+                                         int lane, float4 (&v)[NV]) {
+#pragma unroll
+    for (int j = 0; j < NV; ++j) {
+        const size_t col = size_t(j) * 128 + lane * 4;
+        v[j] = col < cols
+            ? __ldcs(reinterpret_cast<const float4 *>(row + col))
+            : make_float4(0.f, 0.f, 0.f, 0.f);
+    }
+}
+
+template <int NV>
+__device__ __forceinline__ void row_statistics(const float4 (&v)[NV],
+                                               size_t cols, int lane,
+                                               float epsilon, float &mean,
+                                               float &inverse_std) {
+    float sum = 0.0f;
+#pragma unroll
+    for (int j = 0; j < NV; ++j) {
+        sum += (v[j].x + v[j].y) + (v[j].z + v[j].w);
+    }
+    mean = warp_sum(sum) / float(cols);
+    float squares = 0.0f;
+#pragma unroll
+    for (int j = 0; j < NV; ++j) {
+        if (size_t(j) * 128 + lane * 4 < cols) {
+            const float a = v[j].x - mean, b = v[j].y - mean;
+            const float c = v[j].z - mean, d = v[j].w - mean;
+            squares += (a * a + b * b) + (c * c + d * d);
+        }
+    }
+    const float variance = warp_sum(squares) / float(cols);
+    inverse_std = 1.0f / sqrtf(variance + epsilon);
+}
+
+template <int NV>
+__global__ void __launch_bounds__(kWarpsPerBlock * 32)
+layer_norm_kernel(const float *__restrict__ x, const float *__restrict__ gamma,
+                  const float *__restrict__ beta, float epsilon,
+                  float *__restrict__ y, size_t rows, size_t cols) {
+    const int lane = threadIdx.x & 31;
+    const size_t warp = size_t(blockIdx.x) * kWarpsPerBlock + (threadIdx.x >> 5);
+    const size_t warps = size_t(gridDim.x) * kWarpsPerBlock;
+    float4 g[NV], b[NV];
+#pragma unroll
+    for (int j = 0; j < NV; ++j) {
+        const size_t col = size_t(j) * 128 + lane * 4;
+        if (col < cols) {
+            g[j] = __ldg(reinterpret_cast<const float4 *>(gamma + col));
+            b[j] = __ldg(reinterpret_cast<const float4 *>(beta + col));
+        }
+    }
+    for (size_t row = warp; row < rows; row += warps) {
+        float4 v[NV];
+        load_row<NV>(x + row * cols, cols, lane, v);
+        float mean, inverse_std;
+        row_statistics<NV>(v, cols, lane, epsilon, mean, inverse_std);
+#pragma unroll
+        for (int j = 0; j < NV; ++j) {
+            const size_t col = size_t(j) * 128 + lane * 4;
+            if (col < cols) {
+                float4 out;
+                out.x = (v[j].x - mean) * inverse_std * g[j].x + b[j].x;
+                out.y = (v[j].y - mean) * inverse_std * g[j].y + b[j].y;
+                out.z = (v[j].z - mean) * inverse_std * g[j].z + b[j].z;
+                out.w = (v[j].w - mean) * inverse_std * g[j].w + b[j].w;
+                *reinterpret_cast<float4 *>(y + row * cols + col) = out;
+            }
+        }
+    }
+}
+
+template <int NV>
+__global__ void __launch_bounds__(kWarpsPerBlock * 32)
+layer_norm_backward_kernel(const float *__restrict__ x,
+                           const float *__restrict__ gamma, float epsilon,
+                           const float *__restrict__ dy, float *__restrict__ dx,
+                           float *__restrict__ dgamma, float *__restrict__ dbeta,
+                           size_t rows, size_t cols) {
+    __shared__ float4 fold[kWarpsPerBlock][32];
+    const int lane = threadIdx.x & 31;
+    const int warp_in_block = threadIdx.x >> 5;
+    const size_t warp = size_t(blockIdx.x) * kWarpsPerBlock + warp_in_block;
+    const size_t warps = size_t(gridDim.x) * kWarpsPerBlock;
+    float4 g[NV], sum_gamma[NV], sum_beta[NV];
+#pragma unroll
+    for (int j = 0; j < NV; ++j) {
+        const size_t col = size_t(j) * 128 + lane * 4;
+        g[j] = col < cols ? __ldg(reinterpret_cast<const float4 *>(gamma + col))
+                          : make_float4(0.f, 0.f, 0.f, 0.f);
+        sum_gamma[j] = make_float4(0.f, 0.f, 0.f, 0.f);
+        sum_beta[j] = make_float4(0.f, 0.f, 0.f, 0.f);
+    }
+    const float inverse_cols = 1.0f / float(cols);
+    for (size_t row = warp; row < rows; row += warps) {
+        float4 v[NV], u[NV];
+        load_row<NV>(x + row * cols, cols, lane, v);
+        load_row<NV>(dy + row * cols, cols, lane, u);
+        float mean, inverse_std;
+        row_statistics<NV>(v, cols, lane, epsilon, mean, inverse_std);
+        float s1 = 0.0f, s2 = 0.0f;
+#pragma unroll
+        for (int j = 0; j < NV; ++j) {
+            // Out-of-range slots hold x = 0 and dy = 0, so they add nothing.
+            v[j].x = (v[j].x - mean) * inverse_std;
+            v[j].y = (v[j].y - mean) * inverse_std;
+            v[j].z = (v[j].z - mean) * inverse_std;
+            v[j].w = (v[j].w - mean) * inverse_std;
+            sum_gamma[j].x += u[j].x * v[j].x;
+            sum_gamma[j].y += u[j].y * v[j].y;
+            sum_gamma[j].z += u[j].z * v[j].z;
+            sum_gamma[j].w += u[j].w * v[j].w;
+            sum_beta[j].x += u[j].x;
+            sum_beta[j].y += u[j].y;
+            sum_beta[j].z += u[j].z;
+            sum_beta[j].w += u[j].w;
+            u[j].x *= g[j].x;
+            u[j].y *= g[j].y;
+            u[j].z *= g[j].z;
+            u[j].w *= g[j].w;
+            s1 += (u[j].x + u[j].y) + (u[j].z + u[j].w);
+            s2 += (u[j].x * v[j].x + u[j].y * v[j].y) +
+                  (u[j].z * v[j].z + u[j].w * v[j].w);
+        }
+        s1 = warp_sum(s1) * inverse_cols;
+        s2 = warp_sum(s2) * inverse_cols;
+#pragma unroll
+        for (int j = 0; j < NV; ++j) {
+            const size_t col = size_t(j) * 128 + lane * 4;
+            if (col < cols) {
+                float4 *target =
+                    reinterpret_cast<float4 *>(dx + row * cols + col);
+                float4 d = *target;
+                d.x += inverse_std * (u[j].x - s1 - v[j].x * s2);
+                d.y += inverse_std * (u[j].y - s1 - v[j].y * s2);
+                d.z += inverse_std * (u[j].z - s1 - v[j].z * s2);
+                d.w += inverse_std * (u[j].w - s1 - v[j].w * s2);
+                *target = d;
+            }
+        }
+    }
+    // Fold the per-lane column sums over the block's warps.
+#pragma unroll
+    for (int j = 0; j < NV; ++j) {
+        const size_t col = size_t(j) * 128 + lane * 4;
+#pragma unroll
+        for (int which = 0; which < 2; ++which) {
+            __syncthreads();
+            fold[warp_in_block][lane] = which == 0 ? sum_gamma[j] : sum_beta[j];
+            __syncthreads();
+            if (warp_in_block == 0 && col < cols) {
+                float4 total = fold[0][lane];
+#pragma unroll
+                for (int w = 1; w < kWarpsPerBlock; ++w) {
+                    const float4 other = fold[w][lane];
+                    total.x += other.x;
+                    total.y += other.y;
+                    total.z += other.z;
+                    total.w += other.w;
+                }
+                float *target = (which == 0 ? dgamma : dbeta) + col;
+                atomicAdd(target + 0, total.x);
+                atomicAdd(target + 1, total.y);
+                atomicAdd(target + 2, total.z);
+                atomicAdd(target + 3, total.w);
+            }
+        }
+    }
+}
+
+// Any width: three passes over global memory, one warp per row.
+__global__ void __launch_bounds__(kWarpsPerBlock * 32)
+layer_norm_generic_kernel(const float *__restrict__ x,
+                          const float *__restrict__ gamma,
+                          const float *__restrict__ beta, float epsilon,
+                          float *__restrict__ y, size_t rows, size_t cols) {
+    const int lane = threadIdx.x & 31;
+    const size_t warp = size_t(blockIdx.x) * kWarpsPerBlock + (threadIdx.x >> 5);
+    const size_t warps = size_t(gridDim.x) * kWarpsPerBlock;
+    for (size_t row = warp; row < rows; row += warps) {
+        const float *values = x + row * cols;
+        float sum = 0.0f;
+        for (size_t c = lane; c < cols; c += 32) {
+            sum += values[c];
+        }
+        const float mean = warp_sum(sum) / float(cols);
+        float squares = 0.0f;
+        for (size_t c = lane; c < cols; c += 32) {
+            const float centred = values[c] - mean;
+            squares += centred * centred;
+        }
+        const float inverse_std =
+            1.0f / sqrtf(warp_sum(squares) / float(cols) + epsilon);
+        for (size_t c = lane; c < cols; c += 32) {
+            y[row * cols + c] =
+                (values[c] - mean) * inverse_std * gamma[c] + beta[c];
+        }
+    }
+}
+
+__global__ void __launch_bounds__(kWarpsPerBlock * 32)
+layer_norm_backward_generic_kernel(const float *__restrict__ x,
+                                   const float *__restrict__ gamma,
+                                   float epsilon, const float *__restrict__ dy,
+                                   float *__restrict__ dx,
+                                   float *__restrict__ dgamma,
+                                   float *__restrict__ dbeta, size_t rows,
+                                   size_t cols) {
+    const int lane = threadIdx.x & 31;
+    const size_t warp = size_t(blockIdx.x) * kWarpsPerBlock + (threadIdx.x >> 5);
+    const size_t warps = size_t(gridDim.x) * kWarpsPerBlock;
+    for (size_t row = warp; row < rows; row += warps) {
+        const float *values = x + row * cols;
+        const float *upstream = dy + row * cols;
+        float sum = 0.0f;
+        for (size_t c = lane; c < cols; c += 32) {
+            sum += values[c];
+        }
+        const float mean = warp_sum(sum) / float(cols);
+        float squares = 0.0f;
+        for (size_t c = lane; c < cols; c += 32) {
+            const float centred = values[c] - mean;
+            squares += centred * centred;
+        }
+        const float inverse_std =
+            1.0f / sqrtf(warp_sum(squares) / float(cols) + epsilon);
+        float s1 = 0.0f, s2 = 0.0f;
+        for (size_t c = lane; c < cols; c += 32) {
+            const float normalised = (values[c] - mean) * inverse_std;
+            const float dxhat = upstream[c] * gamma[c];
+            s1 += dxhat;
+            s2 += dxhat * normalised;
+            atomicAdd(dgamma + c, upstream[c] * normalised);
+            atomicAdd(dbeta + c, upstream[c]);
+        }
+        s1 = warp_sum(s1) / float(cols);
+        s2 = warp_sum(s2) / float(cols);
+        for (size_t c = lane; c < cols; c += 32) {
+            const float normalised = (values[c] - mean) * inverse_std;
+            const float dxhat = upstream[c] * gamma[c];
+            dx[row * cols + c] += inverse_std * (dxhat - s1 - normalised * s2);
+        }
+    }
+}
+
+unsigned row_grid(size_t rows, unsigned blocks_per_sm) {
+    const size_t wanted = (rows + kWarpsPerBlock - 1) / kWarpsPerBlock;
+    const size_t wave = size_t(kSmCount) * blocks_per_sm;
+    return static_cast<unsigned>(wanted < wave ? (wanted ? wanted : 1) : wave);
+}
+
+}  // namespace
+
+void launch_layer_norm(const float *x, const float *gamma, const float *beta,
+                       float epsilon, float *y, size_t rows, size_t cols,
+                       cudaStream_t stream) {
+    const unsigned grid = row_grid(rows, 8);
+    const unsigned block = kWarpsPerBlock * 32;
+    const size_t slots = (cols + 127) / 128;
+    if (cols % 4 != 0 || slots > 8) {
+        layer_norm_generic_kernel<<<grid, block, 0, stream>>>(x, gamma, beta,
+                                                              epsilon, y, rows,
+                                                              cols);
+    } else if (slots <= 1) {
+        layer_norm_kernel<1><<<grid, block, 0, stream>>>(x, gamma, beta, epsilon,
+                                                         y, rows, cols);
+    } else if (slots <= 2) {
+        layer_norm_kernel<2><<<grid, block, 0, stream>>>(x, gamma, beta, epsilon,
+                                                         y, rows, cols);
+    } else if (slots <= 4) {
+        layer_norm_kernel<4><<<grid, block, 0, stream>>>(x, gamma, beta, epsilon,
+                                                         y, rows, cols);
+    } else {
+        layer_norm_kernel<8><<<grid, block, 0, stream>>>(x, gamma, beta, epsilon,
+                                                         y, rows, cols);
+    }
+    ++g_kernel_launches;
+}
+
+void launch_layer_norm_backward(const float *x, const float *gamma,
+                                float epsilon, const float *dy, float *dx,
+                                float *dgamma, float *dbeta, size_t rows,
+                                size_t cols, cudaStream_t stream) {
+    const unsigned grid = row_grid(rows, 4);
+    const unsigned block = kWarpsPerBlock * 32;
+    const size_t slots = (cols + 127) / 128;
+    if (cols % 4 != 0 || slots > 8) {
+        layer_norm_backward_generic_kernel<<<grid, block, 0, stream>>>(
+            x, gamma, epsilon, dy, dx, dgamma, dbeta, rows, cols);
+    } else if (slots <= 1) {
+        layer_norm_backward_kernel<1><<<grid, block, 0, stream>>>(
+            x, gamma, epsilon, dy, dx, dgamma, dbeta, rows, cols);
+    } else if (slots <= 2) {
+        layer_norm_backward_kernel<2><<<grid, block, 0, stream>>>(
+            x, gamma, epsilon, dy, dx, dgamma, dbeta, rows, cols);
+    } else if (slots <= 4) {
+        layer_norm_backward_kernel<4><<<grid, block, 0, stream>>>(
+            x, gamma, epsilon, dy, dx, dgamma, dbeta, rows, cols);
+    } else {
+        layer_norm_backward_kernel<8><<<grid, block, 0, stream>>>(
+            x, gamma, epsilon, dy, dx, dgamma, dbeta, rows, cols);
+    }
+    ++g_kernel_launches;
+}
+
+}  // namespace vitb200

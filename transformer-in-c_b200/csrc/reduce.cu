@@ -1,0 +1,106 @@
+// Column sums of a row-major matrix: out[c] += sum_r in[r*ld + c].
+// Used for bias gradients and for the positional / CLS gradients.
+//
+// A block owns a strip of columns (32 threads wide, each thread 1 or 4
+// adjacent columns) and a slice of the rows; its 32 row lanes walk the slice
+// with fully coalesced 128- or 512-byte row segments, fold through shared
+// memory, and one lane per column adds the block's partial with a single
+// atomic.  Row slices are sized so the whole grid is about two waves.
+#include "kernels.h"
+#include "device_util.cuh"
+
+namespace vitb200 {
+namespace {
+
+constexpr int kLanesX = 32;
+constexpr int kLanesY = 32;
+
+template <int V>
+__global__ void __launch_bounds__(kLanesX *kLanesY)
+column_sums_kernel(const float *__restrict__ in, float *__restrict__ out,
+                   size_t rows, size_t cols, size_t ld, size_t rows_per_block) {
+    __shared__ float partial[kLanesY][kLanesX * V + 1];
+    const size_t col = (size_t(blockIdx.x) * kLanesX + threadIdx.x) * V;
+    const size_t row_begin = size_t(blockIdx.y) * rows_per_block;
+    const size_t row_end = min(rows, row_begin + rows_per_block);
+    float sum[V];
+#pragma unroll
+    for (int j = 0; j < V; ++j) {
+        sum[j] = 0.0f;
+    }
+    if (col < cols) {
+        for (size_t row = row_begin + threadIdx.y; row < row_end;
+             row += kLanesY) {
+            const float *p = in + row * ld + col;
+            if (V == 4) {
+                const float4 v = __ldcs(reinterpret_cast<const float4 *>(p));
+                sum[0] += v.x;
+                sum[V > 1 ? 1 : 0] += v.y;
+                sum[V > 2 ? 2 : 0] += v.z;
+                sum[V > 3 ? 3 : 0] += v.w;
+            } else {
+                sum[0] += __ldcs(p);
+            }
+        }
+    }
+#pragma unroll
+    for (int j = 0; j < V; ++j) {
+        partial[threadIdx.y][threadIdx.x * V + j] = sum[j];
+    }
+    __syncthreads();
+    // Fold the 32 row lanes: thread (x, y) reduces column slot y*?.. simple
+    // tree over y keeps the code independent of V.
+    for (int stride = kLanesY / 2; stride > 0; stride >>= 1) {
+        if (threadIdx.y < stride) {
+#pragma unroll
+            for (int j = 0; j < V; ++j) {
+                partial[threadIdx.y][threadIdx.x * V + j] +=
+                    partial[threadIdx.y + stride][threadIdx.x * V + j];
+            }
+        }
+        __syncthreads();
+    }
+    if (threadIdx.y == 0 && col < cols) {
+#pragma unroll
+        for (int j = 0; j < V; ++j) {
+            atomicAdd(out + col + j, partial[0][threadIdx.x * V + j]);
+        }
+    }
+}
+
+}  // namespace
+
+void launch_column_sums(const float *in, float *out, size_t rows, size_t cols,
+                        size_t ld, cudaStream_t stream) {
+    if (rows == 0 || cols == 0) {
+        return;
+    }
+    const bool vec = cols % 4 == 0 && ld % 4 == 0;
+    const size_t cols_per_block = kLanesX * (vec ? 4 : 1);
+    const unsigned grid_x =
+        static_cast<unsigned>((cols + cols_per_block - 1) / cols_per_block);
+    size_t slices = (2 * kSmCount + grid_x - 1) / grid_x;
+    const size_t max_slices = (rows + 4 * kLanesY - 1) / (4 * kLanesY);
+    if (slices > max_slices) {
+        slices = max_slices;
+    }
+    if (slices < 1) {
+        slices = 1;
+    }
+    if (slices > 65535) {
+        slices = 65535;
+    }
+    const size_t rows_per_block = (rows + slices - 1) / slices;
+    const dim3 grid(grid_x, static_cast<unsigned>(slices));
+    const dim3 block(kLanesX, kLanesY);
+    if (vec) {
+        column_sums_kernel<4><<<grid, block, 0, stream>>>(in, out, rows, cols,
+                                                          ld, rows_per_block);
+    } else {
+        column_sums_kernel<1><<<grid, block, 0, stream>>>(in, out, rows, cols,
+                                                          ld, rows_per_block);
+    }
+    ++g_kernel_launches;
+}
+
+}  // namespace vitb200
