@@ -1,0 +1,349 @@
+"""Throughput of the ViT training step (forward + backward + clip + AdamW).
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--workload cfg2]
+    python bench.py --impl reference ...      # the reference's CPU path
+
+One step = one call of the reference's vit_model_train_batch_smoothed on one
+synthetic batch.  The host side is the reference's unmodified C code
+(oracle/_ref/libvithost.so, built from the reference sources); with the B200
+backend enabled every op it dispatches runs as one of this repository's CUDA
+kernels.  Prints ONE JSON line (rank 0).
+
+Timed quantities
+  e2e    wall clock over K steps called with HOST buffers: per step the host
+         copies images + labels in, the backend uploads them, and the loss is
+         read back (one device->host sync per step).
+  value  the same K steps, counting only the time the device stream was busy
+         between the first kernel after the uploads and the final synchronise
+         (CUDA events on the backend's stream): throughput with the batch
+         already resident in HBM.
+  roofline  the op with the largest share of device time, timed with CUDA
+         event pairs around each of its launches inside the same K steps;
+         achieved = its algorithmic bytes (or flops) / that time.
+"""
+import argparse
+import ctypes
+import json
+import os
+import subprocess
+import sys
+import threading
+import time
+
+import numpy as np
+
+REPO = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, os.path.join(REPO, "tests"))
+from conftest import HOST_LIBRARY, PACKAGE, load_module  # noqa: E402
+
+# (channels, height, width, patch, d_model, heads, layers, classes), batch
+WORKLOADS = {
+    "cfg1": ((1, 28, 28, 4, 128, 8, 4, 11), 32),
+    "cfg2": ((1, 28, 28, 4, 128, 8, 4, 11), 2048),
+    "cfg3": ((1, 28, 28, 2, 256, 8, 6, 11), 512),
+    "cfg4": ((1, 64, 64, 2, 384, 6, 12, 11), 64),
+    "cfg5": ((1, 28, 28, 2, 512, 8, 12, 11), 512),
+}
+LR, WD, SMOOTHING = 1e-3, 0.05, 0.1
+TENSOR_OPS = {"gemm", "gemm_backward", "multi_head_attention",
+              "multi_head_attention_backward"}
+
+
+def measured_peaks():
+    path = os.path.join(REPO, "MEASURED_PEAKS.json")
+    if os.path.exists(path):
+        peaks = json.load(open(path))
+        return (float(peaks["hbm_gbs"]),
+                float(peaks.get("bf16_tflops_sustained", peaks["bf16_tflops"])),
+                "measured")
+    return 6650.0, 1400.0, "fallback"
+
+
+class ClockSampler:
+    """Samples SM clocks and throttle reasons with nvidia-smi while a region
+    runs (read-only query; nothing is changed on the GPU)."""
+
+    FIELDS = ("clocks.sm,clocks.max.sm,clocks_event_reasons.hw_slowdown,"
+              "clocks_event_reasons.hw_thermal_slowdown,"
+              "clocks_event_reasons.sw_thermal_slowdown,"
+              "clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, device):
+        self.device = device
+        self.process = None
+
+    def __enter__(self):
+        try:
+            self.process = subprocess.Popen(
+                ["nvidia-smi", "-i", str(self.device),
+                 "--query-gpu=" + self.FIELDS, "--format=csv,noheader,nounits",
+                 "-lms", "100"], stdout=subprocess.PIPE, text=True)
+        except OSError:
+            self.process = None
+        return self
+
+    def __exit__(self, *unused):
+        self.summary = {"sm_mhz": None, "sm_max_mhz": None, "reasons": []}
+        if not self.process:
+            return
+        time.sleep(0.15)
+        self.process.terminate()
+        out, _ = self.process.communicate()
+        clocks, reasons, maximum = [], set(), None
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown",
+                 "sw_power_cap"]
+        for line in out.splitlines():
+            parts = [p.strip() for p in line.split(",")]
+            if len(parts) < 6:
+                continue
+            try:
+                clocks.append(float(parts[0]))
+                maximum = float(parts[1])
+            except ValueError:
+                continue
+            for name, state in zip(names, parts[2:6]):
+                if state.lower().startswith("active"):
+                    reasons.add(name)
+        if clocks:
+            self.summary = {"sm_mhz": float(np.median(clocks)),
+                            "sm_max_mhz": maximum, "reasons": sorted(reasons)}
+
+
+def pinned_like(array):
+    """Copy of `array` in page-locked host memory (torch owns the pages)."""
+    import torch
+    tensor = torch.from_numpy(array).pin_memory()
+    return tensor, tensor.numpy()
+
+
+def cpu_reference_rate(vh, host_lib, config, seconds_budget, max_batch=32):
+    """images/s of the reference's CPU code on one core, on a bounded sample:
+    a batch sized from a one-image probe so the timed steps fit the budget."""
+    probe = vh.VitHost(host_lib, config, 1)
+    images, labels = vh.synthetic_batch(1, config[1], config[2], config[7], 77)
+    start = time.perf_counter()
+    probe.train_step(images, labels, LR, WD, None, SMOOTHING)
+    per_image = time.perf_counter() - start
+    probe.close()
+    batch = int(max(1, min(max_batch, seconds_budget / (2.0 * per_image))))
+    host = vh.VitHost(host_lib, config, batch)
+    images, labels = vh.synthetic_batch(batch, config[1], config[2], config[7], 78)
+    steps = 2
+    start = time.perf_counter()
+    for _ in range(steps):
+        host.train_step(images, labels, LR, WD, None, SMOOTHING)
+    elapsed = time.perf_counter() - start
+    host.close()
+    return batch * steps / elapsed, batch, steps
+
+
+def run_reference(args, vh, config, batch, rank, world):
+    """The reference's own CPU implementation of the step, timed on this
+    machine's host cores.  The code is single-threaded on Linux
+    (reference src/ops.c:52-55), so all cores are used as independent
+    replicas, each stepping its own model on its own sample."""
+    if rank != 0:
+        return None
+    host_lib = vh.load_host_library(HOST_LIBRARY)
+    probe = vh.VitHost(host_lib, config, 1)
+    images, labels = vh.synthetic_batch(1, config[1], config[2], config[7], 77)
+    start = time.perf_counter()
+    probe.train_step(images, labels, LR, WD, None, SMOOTHING)
+    per_image = time.perf_counter() - start
+    probe.close()
+    total_steps = args.steps + args.warmup
+    budget = 150.0
+    sample = int(max(1, min(batch, 32, budget / (total_steps * per_image))))
+    replicas = max(1, min(os.cpu_count() or 1, 64))
+    code = (
+        "import sys, time, json; sys.path.insert(0, %r); "
+        "from conftest import HOST_LIBRARY, PACKAGE, load_module; import os; "
+        "vh = load_module('vitb200_vit_host', os.path.join(PACKAGE, 'vit_host.py')); "
+        "lib = vh.load_host_library(HOST_LIBRARY); "
+        "cfg = %r; b = %d; "
+        "h = vh.VitHost(lib, cfg, b); "
+        "x, y = vh.synthetic_batch(b, cfg[1], cfg[2], cfg[7], 100 + int(sys.argv[1])); "
+        "[h.train_step(x, y, %r, %r, None, %r) for _ in range(%d)]; "
+        "t = time.perf_counter(); "
+        "[h.train_step(x, y, %r, %r, None, %r) for _ in range(%d)]; "
+        "print(json.dumps(time.perf_counter() - t))"
+    ) % (os.path.join(REPO, "tests"), tuple(config), sample, LR, WD, SMOOTHING,
+         args.warmup, LR, WD, SMOOTHING, args.steps)
+    start = time.perf_counter()
+    children = [subprocess.Popen([sys.executable, "-c", code, str(i)],
+                                 stdout=subprocess.PIPE, text=True)
+                for i in range(replicas)]
+    times = [float(json.loads(child.communicate()[0].strip().splitlines()[-1]))
+             for child in children]
+    elapsed = max(times)
+    value = replicas * sample * args.steps / elapsed
+    line = {
+        "impl": "reference", "metric": "train images/s", "value": value,
+        "unit": "images/s", "n_gpus": args.gpus, "steps": args.steps,
+        "warmup": args.warmup, "ms_per_step": 1e3 * elapsed / args.steps,
+        "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+        "dtype": "f32", "data": "synthetic",
+        "config": {"workload": args.workload, "vit": list(config),
+                   "batch": batch},
+        "cpu_baseline": {
+            "value": value, "unit": "images/s", "cores": replicas,
+            "kind": "reference",
+            "sample": f"{replicas} independent replicas of the reference's "
+                      f"single-threaded CPU train step, batch {sample} each, "
+                      f"{args.steps} steps (per-image cost is batch-independent)"},
+        "e2e": {"value": value, "unit": "images/s", "h2d_bytes_per_step": 0,
+                "d2h_bytes_per_step": 0},
+    }
+    return line
+
+
+def main():
+    parser = argparse.ArgumentParser()
+    parser.add_argument("--gpus", type=int, default=1)
+    parser.add_argument("--steps", type=int, default=20)
+    parser.add_argument("--warmup", type=int, default=3)
+    parser.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    parser.add_argument("--workload", default="cfg2", choices=sorted(WORKLOADS))
+    parser.add_argument("--batch", type=int, default=0,
+                        help="override the workload's batch (per GPU)")
+    parser.add_argument("--no-cpu-baseline", action="store_true")
+    args = parser.parse_args()
+    args.warmup = max(args.warmup, 3) if args.impl == "ours" else args.warmup
+
+    rank = int(os.environ.get("RANK", "0"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    config, batch = WORKLOADS[args.workload]
+    if args.batch:
+        batch = args.batch
+
+    vh = load_module("vitb200_vit_host", os.path.join(PACKAGE, "vit_host.py"))
+    if args.impl == "reference":
+        line = run_reference(args, vh, config, batch, rank, world)
+        if line is not None:
+            print(json.dumps(line), flush=True)
+        return
+
+    import torch
+    import torch.distributed as dist
+    if world > 1:
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
+    torch.cuda.set_device(local_rank)
+    os.environ["VITB200_DEVICE"] = str(local_rank)
+
+    host_lib = vh.load_host_library(HOST_LIBRARY)
+    backend = vh.Backend()          # raises without the library or a B200
+    backend.enable()
+    host = vh.VitHost(host_lib, config, batch)
+    images, labels = vh.synthetic_batch(batch, config[1], config[2], config[7],
+                                        1234 + rank)
+    keep_images, images = pinned_like(images)
+    keep_labels, labels = pinned_like(labels.astype(np.int64))
+    labels = labels.view(np.uintp)
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    def step():
+        return host.train_step_raw(images, labels, LR, WD, None, SMOOTHING)
+
+    for _ in range(args.warmup):
+        step()
+
+    # ---- e2e: host buffers in, loss out, wall clock ----------------------
+    barrier()
+    counters = backend.memory_counters()
+    start = time.perf_counter()
+    for _ in range(args.steps):
+        loss = step()
+    barrier()
+    e2e_seconds = time.perf_counter() - start
+    moved = backend.memory_counters()
+    h2d_per_step = (moved["h2d_bytes"] - counters["h2d_bytes"]) / args.steps
+    d2h_per_step = (moved["d2h_bytes"] - counters["d2h_bytes"]) / args.steps
+
+    # ---- value + per-op roofline: device-busy time over K steps ----------
+    barrier()
+    backend.device_busy_ms(reset=True)
+    backend.profile(True)
+    launches = backend.kernel_launches()
+    with ClockSampler(local_rank) as clocks:
+        for _ in range(args.steps):
+            loss = step()
+        busy_ms = backend.device_busy_ms(reset=True)
+    barrier()
+    launches = backend.kernel_launches() - launches
+    entries = backend.profile_entries()
+    backend.profile(False)
+
+    busy = torch.tensor([busy_ms, e2e_seconds], dtype=torch.float64, device="cuda")
+    if world > 1:
+        dist.all_reduce(busy, op=dist.ReduceOp.MAX)
+    busy_ms, e2e_seconds = float(busy[0]), float(busy[1])
+    images_per_step = batch * world
+    value = images_per_step * args.steps / (busy_ms / 1e3)
+    e2e_value = images_per_step * args.steps / e2e_seconds
+
+    hbm_peak, tensor_peak, peak_source = measured_peaks()
+    top = max(entries, key=lambda e: e["ms"])
+    seconds = top["ms"] / 1e3
+    tensor_bound = (top["name"] in TENSOR_OPS and
+                    top["flops"] / (tensor_peak * 1e12) >
+                    top["bytes"] / (hbm_peak * 1e9))
+    if tensor_bound:
+        achieved, peak, unit = top["flops"] / seconds / 1e12, tensor_peak, "TFLOP/s"
+    else:
+        achieved, peak, unit = top["bytes"] / seconds / 1e9, hbm_peak, "GB/s"
+    roofline = {
+        "bound": "tensor" if tensor_bound else "hbm", "kernel": top["name"],
+        "achieved": achieved, "peak": peak, "unit": unit,
+        "frac": achieved / peak, "peak_source": peak_source, "traffic": None,
+        "launch_ms": top["ms"] / top["calls"],
+        "share_of_device_time": top["ms"] / sum(e["ms"] for e in entries),
+    }
+    breakdown = {e["name"]: round(e["ms"] / args.steps, 4)
+                 for e in sorted(entries, key=lambda e: -e["ms"])[:8]}
+
+    line = {
+        "metric": "train images/s", "value": value, "unit": "images/s",
+        "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
+        "ms_per_step": busy_ms / args.steps, "higher_is_better": True,
+        "scaling": "weak", "vs_baseline": None, "dtype": "f32",
+        "data": "synthetic",
+        "config": {"workload": args.workload, "vit": list(config),
+                   "batch_per_gpu": batch, "global_batch": images_per_step,
+                   "parallelism": f"dp{world}",
+                   "l2": "per-step working set (activations + gradients) far "
+                         "exceeds the 126 MB L2; no explicit flush"},
+        "clocks": clocks.summary,
+        "e2e": {"value": e2e_value, "unit": "images/s",
+                "h2d_bytes_per_step": h2d_per_step,
+                "d2h_bytes_per_step": d2h_per_step,
+                "ms_per_step": 1e3 * e2e_seconds / args.steps},
+        "gpu_launches": launches,
+        "roofline": roofline,
+        "ms_per_step_by_op": breakdown,
+        "loss": loss,
+    }
+    if rank == 0 and not args.no_cpu_baseline and world == 1:
+        backend.disable()
+        rate, sample_batch, sample_steps = cpu_reference_rate(
+            vh, host_lib, config, seconds_budget=12.0)
+        backend.enable()
+        line["cpu_baseline"] = {
+            "value": rate, "unit": "images/s", "cores": 1, "kind": "reference",
+            "sample": f"reference CPU train step (single-threaded on Linux), "
+                      f"batch {sample_batch}, {sample_steps} steps"}
+    host.close()
+    backend.disable()
+    backend.close()
+    if rank == 0:
+        print(json.dumps(line), flush=True)
+    if world > 1:
+        dist.destroy_process_group()
+
+
+if __name__ == "__main__":
+    main()

@@ -78,6 +78,22 @@ int vitb200_make_host_coherent(const void *tensor_memory);
 int vitb200_timer_begin(CudaBackend *backend);
 float vitb200_timer_end(CudaBackend *backend);
 
+/* Milliseconds the backend's stream spent between the first kernel after a
+ * synchronise and that next synchronise, summed since the last reset (CUDA
+ * events; uploads issued before the first kernel are outside the spans).
+ * Synchronises. */
+double vitb200_device_busy_ms(CudaBackend *backend, int reset);
+
+/* Per-op device timing.  While enabled every op is bracketed by a pair of
+ * CUDA events on the backend's stream; entries accumulate per op name with
+ * the op's algorithmic HBM bytes and floating-point operations, so a caller
+ * can place each op on its roofline.  Enabling clears earlier entries. */
+void vitb200_profile_enable(CudaBackend *backend, int on);
+size_t vitb200_profile_entries(CudaBackend *backend);
+int vitb200_profile_entry(CudaBackend *backend, size_t index, const char **name,
+                          unsigned long long *calls, double *milliseconds,
+                          double *bytes, double *flops);
+
 /* ------------------------------------------------------------------ part 2 */
 /* Every function below takes device pointers, enqueues on the given CUDA
  * stream handle (a cudaStream_t passed as void*, NULL = default stream) and

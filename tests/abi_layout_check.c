@@ -1,0 +1,56 @@
+/* Compiled by tests/test_abi_layout.py with -I<reference>/include -I<repo>/include.
+ * Fails to compile if the mirrored structures drift from the host's. */
+#include "ops.h"
+#include "tensor.h"
+#include "vitb200_host_abi.h"
+
+#include <stddef.h>
+
+#define SAME_SIZE(a, b) _Static_assert(sizeof(a) == sizeof(b), "size " #a)
+#define SAME_FIELD(a, fa, b, fb) \
+    _Static_assert(offsetof(a, fa) == offsetof(b, fb), "offset " #a "." #fa)
+
+SAME_SIZE(Tensor, vitb200_tensor);
+SAME_FIELD(Tensor, data, vitb200_tensor, data);
+SAME_FIELD(Tensor, grad, vitb200_tensor, grad);
+SAME_FIELD(Tensor, ndim, vitb200_tensor, ndim);
+SAME_FIELD(Tensor, shape, vitb200_tensor, shape);
+SAME_FIELD(Tensor, strides, vitb200_tensor, strides);
+SAME_FIELD(Tensor, owns_memory, vitb200_tensor, owns_memory);
+SAME_FIELD(Tensor, release_memory, vitb200_tensor, release_memory);
+SAME_FIELD(Tensor, release_context, vitb200_tensor, release_context);
+SAME_FIELD(Tensor, rows, vitb200_tensor, rows);
+SAME_FIELD(Tensor, cols, vitb200_tensor, cols);
+
+SAME_SIZE(Parameter, vitb200_parameter);
+SAME_FIELD(Parameter, value, vitb200_parameter, value);
+SAME_FIELD(Parameter, first_moment, vitb200_parameter, first_moment);
+SAME_FIELD(Parameter, second_moment, vitb200_parameter, second_moment);
+SAME_FIELD(Parameter, m, vitb200_parameter, m);
+SAME_FIELD(Parameter, v, vitb200_parameter, v);
+SAME_FIELD(Parameter, step, vitb200_parameter, step);
+
+SAME_SIZE(OpsDeviceBackend, vitb200_op_table);
+#define SLOT(name) SAME_FIELD(OpsDeviceBackend, name, vitb200_op_table, name)
+SLOT(context); SLOT(gemm); SLOT(gemm_backward); SLOT(residual);
+SLOT(residual_backward); SLOT(accumulate_gradient); SLOT(bias_add);
+SLOT(bias_add_backward); SLOT(layer_norm); SLOT(layer_norm_backward);
+SLOT(gelu); SLOT(gelu_backward); SLOT(split_heads); SLOT(split_heads_backward);
+SLOT(merge_heads); SLOT(merge_heads_backward); SLOT(multi_head_attention);
+SLOT(multi_head_attention_backward); SLOT(zero_gradient); SLOT(extract_patches);
+SLOT(token_embedding); SLOT(token_embedding_backward); SLOT(gather_rows);
+SLOT(gather_rows_backward); SLOT(softmax_cross_entropy);
+SLOT(clip_gradient_norm); SLOT(adamw_step); SLOT(zero_gradients);
+SLOT(adamw_step_parameters); SLOT(synchronize);
+
+/* Assigning the host's function-pointer types to ours checks the signatures. */
+static void signatures(const OpsDeviceBackend *host, vitb200_op_table *ours) {
+    ours->gemm = (int (*)(void *, const vitb200_tensor *, const vitb200_tensor *,
+                          vitb200_tensor *))host->gemm;
+    (void)ours;
+}
+
+int main(void) {
+    (void)signatures;
+    return 0;
+}

@@ -1,0 +1,186 @@
+"""Kernel-level parity: each device kernel, called through the C-ABI on plain
+device pointers, against the numpy restatement of the host loop it replaces
+(oracle/vit_oracle.py).  torch is used only to own device memory.
+
+Tolerances: 1e-5 relative to the largest reference entry for FP32 elementwise
+and reduction kernels; GEMM tolerances depend on the operand precision and are
+stated at the test.
+"""
+import ctypes
+import os
+
+import numpy as np
+import pytest
+import torch
+
+from conftest import PACKAGE
+from oracle import vit_oracle as vo
+
+pytestmark = pytest.mark.gpu
+
+FP32, TF32 = 1, 2
+
+
+@pytest.fixture(scope="module")
+def lib():
+    library = ctypes.CDLL(os.path.join(PACKAGE, "libvitb200.so"))
+    for name in dir(library):
+        pass
+    return library
+
+
+def dev(array):
+    return torch.from_numpy(np.ascontiguousarray(array, dtype=np.float32)).cuda()
+
+
+def ptr(tensor):
+    return ctypes.c_void_p(tensor.data_ptr())
+
+
+def host(tensor):
+    torch.cuda.synchronize()
+    return tensor.cpu().numpy()
+
+
+def close(actual, expected, tolerance):
+    scale = max(float(np.abs(expected).max()), 1e-6)
+    error = float(np.abs(actual - expected).max()) / scale
+    assert error <= tolerance, error
+
+
+def size(value):
+    return ctypes.c_size_t(value)
+
+
+@pytest.mark.parametrize("m,k,n", [
+    (1, 1, 1), (7, 4, 11), (1568, 16, 128), (32, 128, 11), (100, 33, 65),
+    (1600, 128, 384), (257, 512, 128), (300, 130, 70),
+])
+def test_gemm_fp32_forward_and_backward(lib, m, k, n):
+    rng = np.random.RandomState(m + k + n)
+    x, w, dy = rng.randn(m, k), rng.randn(k, n), rng.randn(m, n)
+    dx0, dw0 = rng.randn(m, k), rng.randn(k, n)  # backward accumulates
+    tx, tw, tdy, ty = dev(x), dev(w), dev(dy), torch.empty(m, n, device="cuda")
+    tdx, tdw = dev(dx0), dev(dw0)
+    assert lib.vitb200_k_gemm(ptr(tx), ptr(tw), ptr(ty), size(m), size(k),
+                              size(n), FP32, None) == 0
+    assert lib.vitb200_k_gemm_backward(ptr(tx), ptr(tw), ptr(tdy), ptr(tdx),
+                                       ptr(tdw), size(m), size(k), size(n),
+                                       FP32, None) == 0
+    close(host(ty), vo.gemm(x, w), 1e-5)
+    dx, dw = vo.gemm_backward(x, w, dy)
+    close(host(tdx), dx0 + dx, 1e-5)
+    close(host(tdw), dw0 + dw, 2e-5)
+
+
+@pytest.mark.parametrize("rows,cols", [
+    (1, 4), (5, 32), (33, 100), (100, 128), (1600, 128), (77, 256), (64, 384),
+    (50, 512), (9, 1024), (3, 2048), (10, 11),
+])
+def test_layer_norm_forward_and_backward(lib, rows, cols):
+    rng = np.random.RandomState(rows * cols)
+    x = rng.randn(rows, cols) * 2 + 0.5
+    gamma, beta = rng.randn(1, cols), rng.randn(1, cols)
+    dy = rng.randn(rows, cols)
+    dx0, dg0, db0 = rng.randn(rows, cols), rng.randn(1, cols), rng.randn(1, cols)
+    tx, tg, tb, tdy = dev(x), dev(gamma), dev(beta), dev(dy)
+    ty = torch.empty(rows, cols, device="cuda")
+    tdx, tdg, tdb = dev(dx0), dev(dg0), dev(db0)
+    eps = ctypes.c_float(1e-5)
+    lib.vitb200_k_layer_norm(ptr(tx), ptr(tg), ptr(tb), eps, ptr(ty),
+                             size(rows), size(cols), None)
+    lib.vitb200_k_layer_norm_backward(ptr(tx), ptr(tg), eps, ptr(tdy), ptr(tdx),
+                                      ptr(tdg), ptr(tdb), size(rows),
+                                      size(cols), None)
+    close(host(ty), vo.layer_norm(x, gamma, beta), 1e-5)
+    dx, dg, db = vo.layer_norm_backward(x, gamma, dy)
+    close(host(tdx), dx0 + dx, 1e-5)
+    close(host(tdg), dg0 + dg, 1e-5)
+    close(host(tdb), db0 + db, 1e-5)
+
+
+@pytest.mark.parametrize("n", [1, 3, 4, 1023, 4096 * 50 + 2])
+def test_gelu_forward_and_backward(lib, n):
+    rng = np.random.RandomState(n)
+    x, dy, dx0 = rng.randn(n) * 3, rng.randn(n), rng.randn(n)
+    tx, tdy, tdx = dev(x), dev(dy), dev(dx0)
+    ty = torch.empty(n, device="cuda")
+    lib.vitb200_k_gelu(ptr(tx), ptr(ty), size(n), None)
+    lib.vitb200_k_gelu_backward(ptr(tx), ptr(tdy), ptr(tdx), size(n), None)
+    close(host(ty), vo.gelu(x), 1e-5)
+    close(host(tdx), dx0 + vo.gelu_backward(x, dy), 1e-5)
+
+
+@pytest.mark.parametrize("rows,cols", [(1, 1), (7, 11), (1000, 384), (40000, 128), (3, 2052)])
+def test_bias_add_and_column_sums(lib, rows, cols):
+    rng = np.random.RandomState(rows + cols)
+    x, b, acc0 = rng.randn(rows, cols), rng.randn(1, cols), rng.randn(1, cols)
+    tx, tb, tacc = dev(x), dev(b), dev(acc0)
+    lib.vitb200_k_column_sums(ptr(tx), ptr(tacc), size(rows), size(cols), None)
+    close(host(tacc), acc0 + x.sum(axis=0, keepdims=True), 1e-5)
+    lib.vitb200_k_bias_add(ptr(tx), ptr(tb), ptr(tx), size(rows), size(cols), None)  # in place
+    close(host(tx), (x + b).astype(np.float32), 1e-6)
+
+
+@pytest.mark.parametrize("groups,seq,hd", [
+    (1, 1, 8), (3, 5, 4), (8, 50, 8), (16, 50, 16), (4, 197, 32), (2, 197, 64),
+    (2, 50, 128), (1, 257, 64), (2, 33, 24),
+])
+def test_attention_forward_and_backward(lib, groups, seq, hd):
+    rng = np.random.RandomState(groups * seq + hd)
+    rows = groups * seq
+    q, k, v, dout = (rng.randn(rows, hd) for _ in range(4))
+    dq0, dk0, dv0 = (rng.randn(rows, hd) for _ in range(3))
+    scale = 1.0 / np.sqrt(hd)
+    tq, tk, tv, tdo = dev(q), dev(k), dev(v), dev(dout)
+    tp = torch.empty(rows, seq, device="cuda")
+    to = torch.empty(rows, hd, device="cuda")
+    tdq, tdk, tdv = dev(dq0), dev(dk0), dev(dv0)
+    dots = torch.empty(rows, device="cuda")
+    assert lib.vitb200_k_attention(ptr(tq), ptr(tk), ptr(tv), ptr(tp), ptr(to),
+                                   size(groups), size(seq), size(hd),
+                                   ctypes.c_float(scale), None) == 0
+    assert lib.vitb200_k_attention_backward(
+        ptr(tq), ptr(tk), ptr(tv), ptr(tp), ptr(to), ptr(tdo), ptr(tdq),
+        ptr(tdk), ptr(tdv), ptr(dots), size(groups), size(seq), size(hd),
+        ctypes.c_float(scale), None) == 0
+    p, o = vo.multi_head_attention(q, k, v, groups, seq, scale)
+    close(host(tp), p, 1e-5)
+    close(host(to), o, 1e-5)
+    dq, dk, dv = vo.multi_head_attention_backward(q, k, v, p, dout, groups, seq, scale)
+    close(host(tdq), dq0 + dq, 2e-5)
+    close(host(tdk), dk0 + dk, 2e-5)
+    close(host(tdv), dv0 + dv, 2e-5)
+    np.testing.assert_allclose(host(tp).sum(axis=1), 1.0, atol=1e-5)
+
+
+def test_attention_rejects_unsupported_head_dim(lib):
+    dummy = torch.zeros(1, device="cuda")
+    assert lib.vitb200_k_attention(ptr(dummy), ptr(dummy), ptr(dummy),
+                                   ptr(dummy), ptr(dummy), size(1), size(1),
+                                   size(129), ctypes.c_float(1.0), None) == -1
+
+
+@pytest.mark.parametrize("rows,cols,smoothing,weighted", [
+    (1, 11, 0.0, False), (32, 11, 0.1, False), (2048, 11, 0.1, True),
+    (7, 5, 0.3, True), (9, 40, 0.05, False),
+])
+def test_softmax_cross_entropy(lib, rows, cols, smoothing, weighted):
+    rng = np.random.RandomState(rows + cols)
+    logits = rng.randn(rows, cols) * 3
+    labels = rng.randint(0, cols, rows)
+    weights = (0.5 + 0.1 * np.arange(cols)) if weighted else None
+    grad0 = rng.randn(rows, cols) * 0.01
+    tz, tt, tg = dev(logits), dev(labels.astype(np.float32)), dev(grad0)
+    tw = dev(weights) if weighted else None
+    tl = torch.zeros(1, device="cuda")
+    scratch = torch.empty(rows, device="cuda")
+    lib.vitb200_k_softmax_cross_entropy(
+        ptr(tz), ptr(tt), ptr(tw) if weighted else None,
+        ctypes.c_float(smoothing), ptr(tl), ptr(tg), ptr(scratch), size(rows),
+        size(cols), None)
+    loss, grad = vo.softmax_cross_entropy(logits, labels, weights, smoothing)
+    assert abs(float(host(tl)[0]) - float(loss)) <= 1e-5 * max(1.0, abs(float(loss)))
+    # Existing gradient content is folded in before the division by rows
+    # (reference src/ops.c:1063-1070).
+    close(host(tg), grad0 / rows + grad, 1e-5)

@@ -43,6 +43,19 @@ struct Scratch {
     size_t bytes = 0;
 };
 
+struct OpStat {
+    const char *name;
+    unsigned long long calls;
+    double ms;
+    double bytes;   // algorithmic HBM bytes
+    double flops;   // algorithmic floating-point operations
+};
+
+struct PendingOp {
+    int stat;
+    cudaEvent_t begin, end;
+};
+
 constexpr int kStagingSlots = 8;
 constexpr size_t kStagingBytes = 64 * 1024;
 
@@ -62,6 +75,16 @@ struct CudaBackend {
     cudaEvent_t staging_done[kStagingSlots] = {};
     int staging_next = 0;
     cudaEvent_t timer_begin = nullptr, timer_end = nullptr;
+    // Device-busy accounting: a span opens at the first kernel after a
+    // synchronise and closes at the next synchronise.
+    cudaEvent_t span_begin = nullptr, span_end = nullptr;
+    bool span_open = false;
+    double busy_ms = 0.0;
+    // Optional per-op timing (vitb200_profile_enable).
+    bool profiling = false;
+    std::vector<OpStat> op_stats;
+    std::vector<PendingOp> pending_ops;
+    std::vector<cudaEvent_t> free_events;
     void (*set_table)(const vitb200_op_table *) = nullptr;
     void (*set_allocator)(vitb200_allocate_fn, vitb200_release_fn,
                           void *) = nullptr;
@@ -83,6 +106,89 @@ void check(cudaError_t status, const char *what) {
 
 void check_launch(const char *what) {
     check(cudaGetLastError(), what);
+}
+
+cudaEvent_t take_event(CudaBackend *backend) {
+    if (!backend->free_events.empty()) {
+        cudaEvent_t event = backend->free_events.back();
+        backend->free_events.pop_back();
+        return event;
+    }
+    cudaEvent_t event = nullptr;
+    check(cudaEventCreate(&event), "cudaEventCreate");
+    return event;
+}
+
+int stat_index(CudaBackend *backend, const char *name) {
+    for (size_t i = 0; i < backend->op_stats.size(); ++i) {
+        if (backend->op_stats[i].name == name) {  // string literals: same pointer
+            return int(i);
+        }
+    }
+    backend->op_stats.push_back(OpStat{name, 0, 0.0, 0.0, 0.0});
+    return int(backend->op_stats.size() - 1);
+}
+
+// Brackets the launches of one op: opens the device-busy span, and when
+// profiling is on, times the op with a pair of events on the backend stream.
+// `bytes` and `flops` are the op's algorithmic traffic and arithmetic.
+class OpScope {
+public:
+    OpScope(CudaBackend *backend, const char *name, double bytes, double flops)
+        : backend_(backend), name_(name) {
+        if (!backend->span_open) {
+            check(cudaEventRecord(backend->span_begin, backend->stream),
+                  "cudaEventRecord");
+            backend->span_open = true;
+        }
+        if (backend->profiling) {
+            pending_.stat = stat_index(backend, name);
+            OpStat &stat = backend->op_stats[pending_.stat];
+            stat.calls += 1;
+            stat.bytes += bytes;
+            stat.flops += flops;
+            pending_.begin = take_event(backend);
+            pending_.end = take_event(backend);
+            check(cudaEventRecord(pending_.begin, backend->stream),
+                  "cudaEventRecord");
+        }
+    }
+    ~OpScope() {
+        check_launch(name_);
+        if (backend_->profiling) {
+            check(cudaEventRecord(pending_.end, backend_->stream),
+                  "cudaEventRecord");
+            backend_->pending_ops.push_back(pending_);
+        }
+    }
+private:
+    CudaBackend *backend_;
+    const char *name_;
+    PendingOp pending_ = {};
+};
+
+void settle_timers(CudaBackend *backend) {
+    if (backend->span_open) {
+        check(cudaEventRecord(backend->span_end, backend->stream),
+              "cudaEventRecord");
+    }
+    check(cudaStreamSynchronize(backend->stream), "cudaStreamSynchronize");
+    if (backend->span_open) {
+        float ms = 0.0f;
+        check(cudaEventElapsedTime(&ms, backend->span_begin, backend->span_end),
+              "cudaEventElapsedTime");
+        backend->busy_ms += ms;
+        backend->span_open = false;
+    }
+    for (const PendingOp &op : backend->pending_ops) {
+        float ms = 0.0f;
+        check(cudaEventElapsedTime(&ms, op.begin, op.end),
+              "cudaEventElapsedTime");
+        backend->op_stats[op.stat].ms += ms;
+        backend->free_events.push_back(op.begin);
+        backend->free_events.push_back(op.end);
+    }
+    backend->pending_ops.clear();
 }
 
 template <typename T>
@@ -149,9 +255,12 @@ int op_gemm(void *context, const vitb200_tensor *left,
     const float *x = view(backend, left->data, Access::Read);
     const float *w = view(backend, right->data, Access::Read);
     float *y = view(backend, output->data, Access::Overwrite);
-    gemm_forward(x, w, y, int(left->rows), int(left->cols), int(right->cols),
-                 VITB200_PRECISION_AUTO, backend->stream);
-    check_launch("gemm");
+    {
+        OpScope scope(backend, "gemm", 4.0 * (double(left->rows) * left->cols + double(right->rows) * right->cols + double(output->rows) * output->cols),
+                      2.0 * double(left->rows) * left->cols * right->cols);
+        gemm_forward(x, w, y, int(left->rows), int(left->cols), int(right->cols),
+                     VITB200_PRECISION_AUTO, backend->stream);
+    }
     return 0;
 }
 
@@ -169,9 +278,12 @@ int op_gemm_backward(void *context, vitb200_tensor *left, vitb200_tensor *right,
     const float *dy = view(backend, output->grad, Access::Read);
     float *dx = view(backend, left->grad, Access::ReadWrite);
     float *dw = view(backend, right->grad, Access::ReadWrite);
-    gemm_backward(x, w, dy, dx, dw, int(left->rows), int(left->cols),
-                  int(right->cols), VITB200_PRECISION_AUTO, backend->stream);
-    check_launch("gemm_backward");
+    {
+        OpScope scope(backend, "gemm_backward", 4.0 * (double(output->rows) * output->cols + 3.0 * double(right->rows) * right->cols + 3.0 * double(left->rows) * left->cols),
+                      4.0 * double(left->rows) * left->cols * right->cols);
+        gemm_backward(x, w, dy, dx, dw, int(left->rows), int(left->cols),
+                      int(right->cols), VITB200_PRECISION_AUTO, backend->stream);
+    }
     return 0;
 }
 
@@ -184,8 +296,11 @@ int op_residual(void *context, const vitb200_tensor *left,
     const float *a = view(backend, left->data, Access::Read);
     const float *b = view(backend, right->data, Access::Read);
     float *out = view(backend, output->data, Access::Overwrite);
-    launch_add(a, b, out, numel(output), backend->stream);
-    check_launch("residual");
+    {
+        OpScope scope(backend, "residual", 12.0 * double(numel(output)),
+                      0.0);
+        launch_add(a, b, out, numel(output), backend->stream);
+    }
     return 0;
 }
 
@@ -200,8 +315,11 @@ int op_residual_backward(void *context, vitb200_tensor *left,
     float *a = view(backend, left->grad, Access::ReadWrite);
     float *b = view(backend, right->grad, Access::ReadWrite);
     const float *g = view(backend, output->grad, Access::Read);
-    launch_accumulate2(a, b, g, numel(output), backend->stream);
-    check_launch("residual_backward");
+    {
+        OpScope scope(backend, "residual_backward", 20.0 * double(numel(output)),
+                      0.0);
+        launch_accumulate2(a, b, g, numel(output), backend->stream);
+    }
     return 0;
 }
 
@@ -214,8 +332,11 @@ int op_accumulate_gradient(void *context, vitb200_tensor *destination,
     }
     float *dst = view(backend, destination->grad, Access::ReadWrite);
     const float *src = view(backend, source->grad, Access::Read);
-    launch_accumulate(dst, src, numel(destination), backend->stream);
-    check_launch("accumulate_gradient");
+    {
+        OpScope scope(backend, "accumulate_gradient", 12.0 * double(numel(destination)),
+                      0.0);
+        launch_accumulate(dst, src, numel(destination), backend->stream);
+    }
     return 0;
 }
 
@@ -231,8 +352,11 @@ int op_bias_add(void *context, const vitb200_tensor *input,
         view(backend, input->data, in_place ? Access::ReadWrite : Access::Read);
     float *out = in_place ? const_cast<float *>(in)
                           : view(backend, output->data, Access::Overwrite);
-    launch_bias_add(in, b, out, input->rows, input->cols, backend->stream);
-    check_launch("bias_add");
+    {
+        OpScope scope(backend, "bias_add", 8.0 * double(numel(input)),
+                      0.0);
+        launch_bias_add(in, b, out, input->rows, input->cols, backend->stream);
+    }
     return 0;
 }
 
@@ -244,9 +368,12 @@ int op_bias_add_backward(void *context, const vitb200_tensor *output,
     }
     const float *dy = view(backend, output->grad, Access::Read);
     float *db = view(backend, bias_grad->grad, Access::ReadWrite);
-    launch_column_sums(dy, db, output->rows, output->cols, output->cols,
-                       backend->stream);
-    check_launch("bias_add_backward");
+    {
+        OpScope scope(backend, "bias_add_backward", 4.0 * double(numel(output)),
+                      0.0);
+        launch_column_sums(dy, db, output->rows, output->cols, output->cols,
+                           backend->stream);
+    }
     return 0;
 }
 
@@ -262,9 +389,12 @@ int op_layer_norm(void *context, const vitb200_tensor *input,
     const float *g = view(backend, gamma->data, Access::Read);
     const float *b = view(backend, beta->data, Access::Read);
     float *y = view(backend, output->data, Access::Overwrite);
-    launch_layer_norm(x, g, b, epsilon, y, input->rows, input->cols,
-                      backend->stream);
-    check_launch("layer_norm");
+    {
+        OpScope scope(backend, "layer_norm", 8.0 * double(numel(input)),
+                      0.0);
+        launch_layer_norm(x, g, b, epsilon, y, input->rows, input->cols,
+                          backend->stream);
+    }
     return 0;
 }
 
@@ -286,9 +416,12 @@ int op_layer_norm_backward(void *context, const vitb200_tensor *input,
     float *dx = view(backend, input_grad->grad, Access::ReadWrite);
     float *dg = view(backend, gamma_grad->grad, Access::ReadWrite);
     float *db = view(backend, beta_grad->grad, Access::ReadWrite);
-    launch_layer_norm_backward(x, g, epsilon, dy, dx, dg, db, input->rows,
-                               input->cols, backend->stream);
-    check_launch("layer_norm_backward");
+    {
+        OpScope scope(backend, "layer_norm_backward", 16.0 * double(numel(input)),
+                      0.0);
+        launch_layer_norm_backward(x, g, epsilon, dy, dx, dg, db, input->rows,
+                                   input->cols, backend->stream);
+    }
     return 0;
 }
 
@@ -300,8 +433,11 @@ int op_gelu(void *context, const vitb200_tensor *input,
     }
     const float *in = view(backend, input->data, Access::Read);
     float *out = view(backend, output->data, Access::Overwrite);
-    launch_gelu(in, out, numel(input), backend->stream);
-    check_launch("gelu");
+    {
+        OpScope scope(backend, "gelu", 8.0 * double(numel(input)),
+                      0.0);
+        launch_gelu(in, out, numel(input), backend->stream);
+    }
     return 0;
 }
 
@@ -314,8 +450,11 @@ int op_gelu_backward(void *context, const vitb200_tensor *input,
     const float *x = view(backend, input->data, Access::Read);
     const float *dy = view(backend, output->grad, Access::Read);
     float *dx = view(backend, input->grad, Access::ReadWrite);
-    launch_gelu_backward(x, dy, dx, numel(input), backend->stream);
-    check_launch("gelu_backward");
+    {
+        OpScope scope(backend, "gelu_backward", 16.0 * double(numel(input)),
+                      0.0);
+        launch_gelu_backward(x, dy, dx, numel(input), backend->stream);
+    }
     return 0;
 }
 
@@ -331,8 +470,11 @@ int op_split_heads(void *context, const vitb200_tensor *projected,
     float *q = view(backend, query->data, Access::Overwrite);
     float *k = view(backend, key->data, Access::Overwrite);
     float *v = view(backend, value->data, Access::Overwrite);
-    launch_split_heads(p, q, k, v, batch, seq, d_model, heads, backend->stream);
-    check_launch("split_heads");
+    {
+        OpScope scope(backend, "split_heads", 8.0 * double(numel(projected)),
+                      0.0);
+        launch_split_heads(p, q, k, v, batch, seq, d_model, heads, backend->stream);
+    }
     return 0;
 }
 
@@ -349,9 +491,12 @@ int op_split_heads_backward(void *context, vitb200_tensor *projected,
     const float *q = view(backend, query->grad, Access::Read);
     const float *k = view(backend, key->grad, Access::Read);
     const float *v = view(backend, value->grad, Access::Read);
-    launch_split_heads_backward(p, q, k, v, batch, seq, d_model, heads,
-                                backend->stream);
-    check_launch("split_heads_backward");
+    {
+        OpScope scope(backend, "split_heads_backward", 12.0 * double(numel(projected)),
+                      0.0);
+        launch_split_heads_backward(p, q, k, v, batch, seq, d_model, heads,
+                                    backend->stream);
+    }
     return 0;
 }
 
@@ -364,8 +509,11 @@ int op_merge_heads(void *context, const vitb200_tensor *attended,
     }
     const float *a = view(backend, attended->data, Access::Read);
     float *m = view(backend, merged->data, Access::Overwrite);
-    launch_merge_heads(a, m, batch, seq, d_model, heads, backend->stream);
-    check_launch("merge_heads");
+    {
+        OpScope scope(backend, "merge_heads", 8.0 * double(numel(merged)),
+                      0.0);
+        launch_merge_heads(a, m, batch, seq, d_model, heads, backend->stream);
+    }
     return 0;
 }
 
@@ -378,9 +526,12 @@ int op_merge_heads_backward(void *context, vitb200_tensor *attended,
     }
     float *a = view(backend, attended->grad, Access::ReadWrite);
     const float *m = view(backend, merged->grad, Access::Read);
-    launch_merge_heads_backward(a, m, batch, seq, d_model, heads,
-                                backend->stream);
-    check_launch("merge_heads_backward");
+    {
+        OpScope scope(backend, "merge_heads_backward", 12.0 * double(numel(merged)),
+                      0.0);
+        launch_merge_heads_backward(a, m, batch, seq, d_model, heads,
+                                    backend->stream);
+    }
     return 0;
 }
 
@@ -402,9 +553,12 @@ int op_attention(void *context, const vitb200_tensor *query,
     const float *v = view(backend, value->data, Access::Read);
     float *p = view(backend, probabilities->data, Access::Overwrite);
     float *o = view(backend, output->data, Access::Overwrite);
-    launch_attention_forward(q, k, v, p, o, batch * heads, seq, query->cols,
-                             scale, backend->stream);
-    check_launch("multi_head_attention");
+    {
+        OpScope scope(backend, "multi_head_attention", 4.0 * (4.0 * double(numel(query)) + double(numel(probabilities))),
+                      4.0 * double(numel(probabilities)) * double(query->cols));
+        launch_attention_forward(q, k, v, p, o, batch * heads, seq, query->cols,
+                                 scale, backend->stream);
+    }
     return 0;
 }
 
@@ -435,9 +589,12 @@ int op_attention_backward(void *context, const vitb200_tensor *query,
     float *dq = view(backend, query_grad->grad, Access::ReadWrite);
     float *dk = view(backend, key_grad->grad, Access::ReadWrite);
     float *dv = view(backend, value_grad->grad, Access::ReadWrite);
-    launch_attention_backward(q, k, v, p, o, go, dq, dk, dv, dots, groups, seq,
-                              query->cols, scale, backend->stream);
-    check_launch("multi_head_attention_backward");
+    {
+        OpScope scope(backend, "multi_head_attention_backward", 4.0 * (11.0 * double(numel(query)) + double(numel(probabilities))),
+                      8.0 * double(numel(probabilities)) * double(query->cols));
+        launch_attention_backward(q, k, v, p, o, go, dq, dk, dv, dots, groups, seq,
+                                  query->cols, scale, backend->stream);
+    }
     return 0;
 }
 
@@ -447,6 +604,7 @@ int op_zero_gradient(void *context, vitb200_tensor *tensor) {
         return -1;
     }
     float *g = view(backend, tensor->grad, Access::Overwrite);
+    OpScope scope(backend, "zero_gradient", 4.0 * double(numel(tensor)), 0.0);
     check(cudaMemsetAsync(g, 0, numel(tensor) * sizeof(float), backend->stream),
           "cudaMemsetAsync");
     return 0;
@@ -460,6 +618,11 @@ int op_zero_gradients(void *context, vitb200_tensor *const *tensors,
             return -1;
         }
     }
+    double bytes = 0.0;
+    for (size_t i = 0; i < count; ++i) {
+        bytes += 4.0 * double(numel(tensors[i]));
+    }
+    OpScope scope(backend, "zero_gradients", bytes, 0.0);
     for (size_t i = 0; i < count; ++i) {
         float *g = view(backend, tensors[i]->grad, Access::Overwrite);
         check(cudaMemsetAsync(g, 0, numel(tensors[i]) * sizeof(float),
@@ -478,9 +641,12 @@ int op_extract_patches(void *context, const vitb200_tensor *images,
     }
     const float *in = view(backend, images->data, Access::Read);
     float *out = view(backend, patches->data, Access::Overwrite);
-    launch_extract_patches(in, out, images->rows, channels, height, width,
-                           patch, backend->stream);
-    check_launch("extract_patches");
+    {
+        OpScope scope(backend, "extract_patches", 8.0 * double(numel(patches)),
+                      0.0);
+        launch_extract_patches(in, out, images->rows, channels, height, width,
+                               patch, backend->stream);
+    }
     return 0;
 }
 
@@ -495,9 +661,12 @@ int op_token_embedding(void *context, const vitb200_tensor *patch_tokens,
     const float *c = view(backend, cls->data, Access::Read);
     const float *e = view(backend, pos->data, Access::Read);
     float *t = view(backend, tokens->data, Access::Overwrite);
-    launch_token_embedding(p, c, e, t, batch, pos->rows, tokens->cols,
-                           backend->stream);
-    check_launch("token_embedding");
+    {
+        OpScope scope(backend, "token_embedding", 8.0 * double(numel(tokens)),
+                      0.0);
+        launch_token_embedding(p, c, e, t, batch, pos->rows, tokens->cols,
+                               backend->stream);
+    }
     return 0;
 }
 
@@ -512,9 +681,12 @@ int op_token_embedding_backward(void *context, vitb200_tensor *patch_tokens,
     float *c = view(backend, cls->grad, Access::ReadWrite);
     float *e = view(backend, pos->grad, Access::ReadWrite);
     const float *t = view(backend, tokens->grad, Access::Read);
-    launch_token_embedding_backward(p, c, e, t, batch, pos->rows, tokens->cols,
-                                    backend->stream);
-    check_launch("token_embedding_backward");
+    {
+        OpScope scope(backend, "token_embedding_backward", 12.0 * double(numel(tokens)),
+                      0.0);
+        launch_token_embedding_backward(p, c, e, t, batch, pos->rows, tokens->cols,
+                                        backend->stream);
+    }
     return 0;
 }
 
@@ -526,9 +698,12 @@ int op_gather_rows(void *context, const vitb200_tensor *source,
     }
     const float *s = view(backend, source->data, Access::Read);
     float *d = view(backend, destination->data, Access::Overwrite);
-    launch_gather_rows(s, d, destination->rows, destination->cols, row_stride,
-                       backend->stream);
-    check_launch("gather_rows");
+    {
+        OpScope scope(backend, "gather_rows", 8.0 * double(numel(destination)),
+                      0.0);
+        launch_gather_rows(s, d, destination->rows, destination->cols, row_stride,
+                           backend->stream);
+    }
     return 0;
 }
 
@@ -541,9 +716,12 @@ int op_gather_rows_backward(void *context, vitb200_tensor *source,
     }
     float *s = view(backend, source->grad, Access::ReadWrite);
     const float *d = view(backend, destination->grad, Access::Read);
-    launch_gather_rows_backward(s, d, destination->rows, destination->cols,
-                                row_stride, backend->stream);
-    check_launch("gather_rows_backward");
+    {
+        OpScope scope(backend, "gather_rows_backward", 12.0 * double(numel(destination)),
+                      0.0);
+        launch_gather_rows_backward(s, d, destination->rows, destination->cols,
+                                    row_stride, backend->stream);
+    }
     return 0;
 }
 
@@ -566,9 +744,12 @@ int op_softmax_cross_entropy(void *context, const vitb200_tensor *logits,
         : nullptr;
     float *l = view(backend, loss->data, Access::Overwrite);
     float *g = view(backend, logits_grad->grad, Access::ReadWrite);
-    launch_softmax_cross_entropy(z, t, w, label_smoothing, l, g, row_losses,
-                                 logits->rows, logits->cols, backend->stream);
-    check_launch("softmax_cross_entropy");
+    {
+        OpScope scope(backend, "softmax_cross_entropy", 16.0 * double(numel(logits)),
+                      0.0);
+        launch_softmax_cross_entropy(z, t, w, label_smoothing, l, g, row_losses,
+                                     logits->rows, logits->cols, backend->stream);
+    }
     return 0;
 }
 
@@ -592,6 +773,7 @@ struct SliceTable {
     const ParameterSlice *device = nullptr;
     unsigned slices = 0;
     unsigned blocks = 0;
+    double elements = 0.0;
 };
 
 // with_moments = false builds a gradient-only table (for clipping alone).
@@ -638,6 +820,9 @@ int build_slice_table(CudaBackend *backend,
     table->device = device;
     table->slices = unsigned(count);
     table->blocks = unsigned(blocks);
+    for (const ParameterSlice &slice : slices) {
+        table->elements += double(slice.count);
+    }
     return 0;
 }
 
@@ -652,11 +837,11 @@ int op_clip_gradient_norm(void *context, vitb200_parameter *const *parameters,
     float *partials =
         scratch<float>(backend, backend->norm_partials, table.blocks);
     float *scale = scratch<float>(backend, backend->clip_scale, 1);
+    OpScope scope(backend, "clip_gradient_norm", 12.0 * table.elements, 0.0);
     launch_gradient_clip_scale(table.device, table.slices, table.blocks,
                                max_norm, partials, scale, backend->stream);
     launch_scale_gradients(table.device, table.slices, table.blocks, scale,
                            backend->stream);
-    check_launch("clip_gradient_norm");
     return 0;
 }
 
@@ -672,10 +857,13 @@ int op_adamw_step(void *context, vitb200_parameter *parameter, float lr,
     float *g = view(backend, parameter->value.grad, Access::ReadWrite);
     float *m = view(backend, parameter->m, Access::ReadWrite);
     float *v = view(backend, parameter->v, Access::ReadWrite);
-    launch_adamw_single(w, g, m, v, numel(&parameter->value), lr, beta1, beta2,
-                        epsilon, weight_decay, correction1, correction2,
-                        backend->stream);
-    check_launch("adamw_step");
+    {
+        OpScope scope(backend, "adamw_step", 28.0 * double(numel(&parameter->value)),
+                      0.0);
+        launch_adamw_single(w, g, m, v, numel(&parameter->value), lr, beta1, beta2,
+                            epsilon, weight_decay, correction1, correction2,
+                            backend->stream);
+    }
     return 0;
 }
 
@@ -691,10 +879,15 @@ int op_adamw_step_parameters(void *context,
         return -1;
     }
     const float *scale = nullptr;
+    float *partials = nullptr, *scale_out = nullptr;
     if (max_gradient_norm > 0.0f) {
-        float *partials =
-            scratch<float>(backend, backend->norm_partials, table.blocks);
-        float *scale_out = scratch<float>(backend, backend->clip_scale, 1);
+        partials = scratch<float>(backend, backend->norm_partials, table.blocks);
+        scale_out = scratch<float>(backend, backend->clip_scale, 1);
+    }
+    OpScope scope(backend, "adamw_step_parameters",
+                  (max_gradient_norm > 0.0f ? 32.0 : 28.0) * table.elements,
+                  0.0);
+    if (max_gradient_norm > 0.0f) {
         launch_gradient_clip_scale(table.device, table.slices, table.blocks,
                                    max_gradient_norm, partials, scale_out,
                                    backend->stream);
@@ -702,12 +895,11 @@ int op_adamw_step_parameters(void *context,
     }
     launch_adamw(table.device, table.slices, table.blocks, scale, lr, beta1,
                  beta2, epsilon, backend->stream);
-    check_launch("adamw_step_parameters");
     return 0;
 }
 
 void op_synchronize(void *context) {
-    check(cudaStreamSynchronize(self(context)->stream), "cudaStreamSynchronize");
+    settle_timers(self(context));
 }
 
 vitb200_op_table make_table(CudaBackend *backend) {
@@ -798,7 +990,9 @@ extern "C" int cuda_backend_create(CudaBackend **backend) {
         return -1;
     }
     bool ok = cudaEventCreate(&result->timer_begin) == cudaSuccess &&
-              cudaEventCreate(&result->timer_end) == cudaSuccess;
+              cudaEventCreate(&result->timer_end) == cudaSuccess &&
+              cudaEventCreate(&result->span_begin) == cudaSuccess &&
+              cudaEventCreate(&result->span_end) == cudaSuccess;
     for (int i = 0; ok && i < kStagingSlots; ++i) {
         ok = cudaHostAlloc(reinterpret_cast<void **>(&result->staging[i]),
                            kStagingBytes, cudaHostAllocDefault) == cudaSuccess &&
@@ -820,7 +1014,7 @@ extern "C" void cuda_backend_free(CudaBackend *backend) {
     }
     cuda_backend_disable_device_execution(backend);
     if (backend->stream) {
-        cudaStreamSynchronize(backend->stream);
+        settle_timers(backend);
     }
     free_scratch(backend->rows_scratch);
     free_scratch(backend->norm_partials);
@@ -839,6 +1033,15 @@ extern "C" void cuda_backend_free(CudaBackend *backend) {
     }
     if (backend->timer_end) {
         cudaEventDestroy(backend->timer_end);
+    }
+    if (backend->span_begin) {
+        cudaEventDestroy(backend->span_begin);
+    }
+    if (backend->span_end) {
+        cudaEventDestroy(backend->span_end);
+    }
+    for (cudaEvent_t event : backend->free_events) {
+        cudaEventDestroy(event);
     }
     // Tensors that outlive the backend are copied back on the legacy default
     // stream from here on.
@@ -888,7 +1091,7 @@ extern "C" void cuda_backend_disable_device_execution(CudaBackend *backend) {
     if (!backend || !backend->enabled) {
         return;
     }
-    check(cudaStreamSynchronize(backend->stream), "cudaStreamSynchronize");
+    settle_timers(backend);
     // ops_set_device_backend synchronises the outgoing table first
     // (reference src/ops.c:66-74).
     backend->set_table(nullptr);
@@ -938,6 +1141,54 @@ extern "C" float vitb200_timer_end(CudaBackend *backend) {
     float ms = -1.0f;
     cudaEventElapsedTime(&ms, backend->timer_begin, backend->timer_end);
     return ms;
+}
+
+extern "C" double vitb200_device_busy_ms(CudaBackend *backend, int reset) {
+    if (!cuda_backend_available(backend)) {
+        return -1.0;
+    }
+    settle_timers(backend);
+    const double ms = backend->busy_ms;
+    if (reset) {
+        backend->busy_ms = 0.0;
+    }
+    return ms;
+}
+
+extern "C" void vitb200_profile_enable(CudaBackend *backend, int on) {
+    if (!cuda_backend_available(backend)) {
+        return;
+    }
+    settle_timers(backend);
+    backend->profiling = on != 0;
+    if (on) {
+        backend->op_stats.clear();
+    }
+}
+
+extern "C" size_t vitb200_profile_entries(CudaBackend *backend) {
+    if (!cuda_backend_available(backend)) {
+        return 0;
+    }
+    settle_timers(backend);
+    return backend->op_stats.size();
+}
+
+extern "C" int vitb200_profile_entry(CudaBackend *backend, size_t index,
+                                     const char **name,
+                                     unsigned long long *calls,
+                                     double *milliseconds, double *bytes,
+                                     double *flops) {
+    if (!cuda_backend_available(backend) || index >= backend->op_stats.size()) {
+        return -1;
+    }
+    const OpStat &stat = backend->op_stats[index];
+    if (name) *name = stat.name;
+    if (calls) *calls = stat.calls;
+    if (milliseconds) *milliseconds = stat.ms;
+    if (bytes) *bytes = stat.bytes;
+    if (flops) *flops = stat.flops;
+    return 0;
 }
 
 // ------------------------------------------------------------------ part 2

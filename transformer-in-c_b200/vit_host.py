@@ -1,0 +1,294 @@
+"""ctypes bindings for driving the ViT host code with the B200 backend.
+
+Two shared libraries are involved:
+
+* the *host* library: the reference's unmodified ops.c / vit.c / autodiff.c
+  compiled together with host/vit_host.c (flat entry points over its structs).
+  Its path is supplied by the caller; this package does not know where it is.
+* ``libvitb200.so`` (next to this file): the backend.  It exports the five
+  ``cuda_backend_*`` functions of the reference's include/cuda_backend.h and
+  plugs itself into the host library through ops_set_device_backend /
+  tensor_set_allocator when enabled.
+
+There is no CPU fallback in here: if the backend library is missing or no
+B200 is visible, `Backend()` raises.
+"""
+import ctypes
+import os
+
+import numpy as np
+
+_HERE = os.path.dirname(os.path.abspath(__file__))
+BACKEND_LIBRARY = os.path.join(_HERE, "libvitb200.so")
+
+_size_t = ctypes.c_size_t
+_float_p = ctypes.POINTER(ctypes.c_float)
+
+
+def load_host_library(path):
+    """Loads the host library so that its symbols are visible to the backend
+    (RTLD_GLOBAL), and declares the flat entry points."""
+    lib = ctypes.CDLL(path, mode=ctypes.RTLD_GLOBAL)
+    lib.vithost_create.restype = ctypes.c_void_p
+    lib.vithost_create.argtypes = [_size_t] * 9 + [ctypes.c_uint64]
+    lib.vithost_destroy.argtypes = [ctypes.c_void_p]
+    lib.vithost_destroy.restype = None
+    lib.vithost_parameter_count.restype = _size_t
+    lib.vithost_parameter_count.argtypes = [ctypes.c_void_p]
+    lib.vithost_parameter_name.restype = ctypes.c_char_p
+    lib.vithost_parameter_name.argtypes = [ctypes.c_void_p, _size_t]
+    lib.vithost_parameter_view.restype = _size_t
+    lib.vithost_parameter_view.argtypes = [
+        ctypes.c_void_p, _size_t, ctypes.c_int, ctypes.POINTER(_float_p),
+        ctypes.POINTER(_size_t), ctypes.POINTER(_size_t)]
+    lib.vithost_parameter_step.restype = _size_t
+    lib.vithost_parameter_step.argtypes = [ctypes.c_void_p, _size_t]
+    lib.vithost_gradients.restype = ctypes.c_int
+    lib.vithost_gradients.argtypes = [
+        ctypes.c_void_p, _float_p, ctypes.POINTER(_size_t), _float_p,
+        ctypes.c_float, _float_p]
+    lib.vithost_train_step.restype = ctypes.c_int
+    lib.vithost_train_step.argtypes = [
+        ctypes.c_void_p, _float_p, ctypes.POINTER(_size_t), ctypes.c_float,
+        ctypes.c_float, _float_p, ctypes.c_float, _float_p]
+    lib.vithost_forward.restype = ctypes.c_int
+    lib.vithost_forward.argtypes = [ctypes.c_void_p, _float_p, _float_p]
+    lib.vithost_set_parameter.restype = ctypes.c_int
+    lib.vithost_set_parameter.argtypes = [ctypes.c_void_p, _size_t, _float_p]
+    lib.vithost_block_tensor.restype = _size_t
+    lib.vithost_block_tensor.argtypes = [
+        ctypes.c_void_p, _size_t, ctypes.c_char_p, ctypes.c_int,
+        ctypes.POINTER(_float_p), ctypes.POINTER(_size_t),
+        ctypes.POINTER(_size_t)]
+    lib.ops_synchronize.restype = None
+    return lib
+
+
+def load_backend_library():
+    if not os.path.exists(BACKEND_LIBRARY):
+        raise RuntimeError(
+            f"{BACKEND_LIBRARY} is missing: build it with "
+            "`python transformer-in-c_b200/build.py` (there is no CPU fallback)")
+    lib = ctypes.CDLL(BACKEND_LIBRARY, mode=ctypes.RTLD_GLOBAL)
+    lib.cuda_backend_create.restype = ctypes.c_int
+    lib.cuda_backend_create.argtypes = [ctypes.POINTER(ctypes.c_void_p)]
+    lib.cuda_backend_free.restype = None
+    lib.cuda_backend_free.argtypes = [ctypes.c_void_p]
+    lib.cuda_backend_available.restype = ctypes.c_int
+    lib.cuda_backend_available.argtypes = [ctypes.c_void_p]
+    lib.cuda_backend_enable_device_execution.restype = ctypes.c_int
+    lib.cuda_backend_enable_device_execution.argtypes = [ctypes.c_void_p]
+    lib.cuda_backend_disable_device_execution.restype = None
+    lib.cuda_backend_disable_device_execution.argtypes = [ctypes.c_void_p]
+    lib.vitb200_kernel_launches.restype = ctypes.c_ulonglong
+    lib.vitb200_memory_counters.restype = None
+    lib.vitb200_memory_counters.argtypes = [ctypes.POINTER(_size_t)] * 8
+    lib.vitb200_timer_begin.restype = ctypes.c_int
+    lib.vitb200_timer_begin.argtypes = [ctypes.c_void_p]
+    lib.vitb200_timer_end.restype = ctypes.c_float
+    lib.vitb200_timer_end.argtypes = [ctypes.c_void_p]
+    lib.vitb200_device_busy_ms.restype = ctypes.c_double
+    lib.vitb200_device_busy_ms.argtypes = [ctypes.c_void_p, ctypes.c_int]
+    lib.vitb200_profile_enable.restype = None
+    lib.vitb200_profile_enable.argtypes = [ctypes.c_void_p, ctypes.c_int]
+    lib.vitb200_profile_entries.restype = _size_t
+    lib.vitb200_profile_entries.argtypes = [ctypes.c_void_p]
+    lib.vitb200_profile_entry.restype = ctypes.c_int
+    lib.vitb200_profile_entry.argtypes = [
+        ctypes.c_void_p, _size_t, ctypes.POINTER(ctypes.c_char_p),
+        ctypes.POINTER(ctypes.c_ulonglong), ctypes.POINTER(ctypes.c_double),
+        ctypes.POINTER(ctypes.c_double), ctypes.POINTER(ctypes.c_double)]
+    return lib
+
+
+class Backend:
+    """Owns one CudaBackend.  `enable()` / `disable()` mirror the reference's
+    cuda_backend_enable_device_execution / _disable_device_execution."""
+
+    def __init__(self):
+        self.lib = load_backend_library()
+        handle = ctypes.c_void_p()
+        status = self.lib.cuda_backend_create(ctypes.byref(handle))
+        if status != 0 or not self.lib.cuda_backend_available(handle):
+            raise RuntimeError(
+                f"cuda_backend_create returned {status}: no usable B200")
+        self.handle = handle
+        self.enabled = False
+
+    def enable(self):
+        if self.lib.cuda_backend_enable_device_execution(self.handle) != 0:
+            raise RuntimeError("cuda_backend_enable_device_execution failed")
+        self.enabled = True
+
+    def disable(self):
+        self.lib.cuda_backend_disable_device_execution(self.handle)
+        self.enabled = False
+
+    def close(self):
+        if self.handle:
+            self.lib.cuda_backend_free(self.handle)
+            self.handle = None
+
+    def kernel_launches(self):
+        return int(self.lib.vitb200_kernel_launches())
+
+    def memory_counters(self):
+        values = [_size_t() for _ in range(8)]
+        self.lib.vitb200_memory_counters(*[ctypes.byref(v) for v in values])
+        names = ["live_allocations", "mirror_bytes", "device_bytes",
+                 "h2d_copies", "h2d_bytes", "d2h_copies", "d2h_bytes", "faults"]
+        return {n: int(v.value) for n, v in zip(names, values)}
+
+    def device_busy_ms(self, reset=False):
+        return float(self.lib.vitb200_device_busy_ms(self.handle, int(reset)))
+
+    def profile(self, on):
+        self.lib.vitb200_profile_enable(self.handle, int(on))
+
+    def profile_entries(self):
+        """[{name, calls, ms, bytes, flops}] accumulated since profile(True)."""
+        entries = []
+        for i in range(int(self.lib.vitb200_profile_entries(self.handle))):
+            name = ctypes.c_char_p()
+            calls = ctypes.c_ulonglong()
+            ms, nbytes, flops = ctypes.c_double(), ctypes.c_double(), ctypes.c_double()
+            self.lib.vitb200_profile_entry(
+                self.handle, i, ctypes.byref(name), ctypes.byref(calls),
+                ctypes.byref(ms), ctypes.byref(nbytes), ctypes.byref(flops))
+            entries.append({"name": name.value.decode(), "calls": int(calls.value),
+                            "ms": ms.value, "bytes": nbytes.value,
+                            "flops": flops.value})
+        return entries
+
+    def timer_begin(self):
+        self.lib.vitb200_timer_begin(self.handle)
+
+    def timer_end(self):
+        return float(self.lib.vitb200_timer_end(self.handle))
+
+
+class VitHost:
+    """A model plus its activation cache, created through the reference's
+    vit_model_init_seeded / vit_model_cache_init.  Tensors land on the device
+    iff a backend is enabled at construction time (reference
+    tests/test_device.c:141-170 relies on the same rule)."""
+
+    def __init__(self, host_lib, config, batch, seed=42):
+        self.lib = host_lib
+        self.config = tuple(int(v) for v in config)
+        self.batch = int(batch)
+        self.handle = host_lib.vithost_create(*self.config, self.batch, seed)
+        if not self.handle:
+            raise RuntimeError("vithost_create failed")
+        self.count = int(host_lib.vithost_parameter_count(self.handle))
+        self.names = []
+        layer = -1
+        for i in range(self.count):
+            name = host_lib.vithost_parameter_name(self.handle, i).decode()
+            if name == "query_key_value":
+                layer += 1
+            per_layer = i >= 4 and i < self.count - 4
+            self.names.append(f"{layer}.{name}" if per_layer else name)
+
+    def close(self):
+        if self.handle:
+            self.lib.vithost_destroy(self.handle)
+            self.handle = None
+
+    def _view(self, index, what):
+        data = _float_p()
+        rows, cols = _size_t(), _size_t()
+        count = self.lib.vithost_parameter_view(
+            self.handle, index, what, ctypes.byref(data), ctypes.byref(rows),
+            ctypes.byref(cols))
+        array = np.ctypeslib.as_array(data, shape=(int(count),))
+        return array.reshape(int(rows.value), int(cols.value))
+
+    def parameters(self, what=0):
+        """Copies of every parameter's value (0), gradient (1), first (2) or
+        second (3) moment, keyed like oracle.vit_oracle.parameter_names."""
+        return {name: self._view(i, what).copy()
+                for i, name in enumerate(self.names)}
+
+    def set_parameters(self, values):
+        for i, name in enumerate(self.names):
+            array = np.ascontiguousarray(values[name], dtype=np.float32)
+            if self.lib.vithost_set_parameter(
+                    self.handle, i, array.ctypes.data_as(_float_p)) != 0:
+                raise RuntimeError(f"set_parameter({name}) failed")
+
+    def steps(self):
+        return [int(self.lib.vithost_parameter_step(self.handle, i))
+                for i in range(self.count)]
+
+    @staticmethod
+    def _inputs(images, labels, class_weights):
+        images = np.ascontiguousarray(images, dtype=np.float32)
+        labels = np.ascontiguousarray(labels, dtype=np.uintp)
+        weights = None
+        if class_weights is not None:
+            weights = np.ascontiguousarray(class_weights, dtype=np.float32)
+        return images, labels, weights
+
+    def gradients(self, images, labels, class_weights=None, label_smoothing=0.0):
+        images, labels, weights = self._inputs(images, labels, class_weights)
+        loss = ctypes.c_float()
+        status = self.lib.vithost_gradients(
+            self.handle, images.ctypes.data_as(_float_p),
+            labels.ctypes.data_as(ctypes.POINTER(_size_t)),
+            weights.ctypes.data_as(_float_p) if weights is not None else None,
+            label_smoothing, ctypes.byref(loss))
+        if status != 0:
+            raise RuntimeError("vithost_gradients failed")
+        return float(loss.value)
+
+    def train_step(self, images, labels, lr, weight_decay, class_weights=None,
+                   label_smoothing=0.0):
+        images, labels, weights = self._inputs(images, labels, class_weights)
+        return self.train_step_raw(images, labels, lr, weight_decay, weights,
+                                   label_smoothing)
+
+    def train_step_raw(self, images, labels, lr, weight_decay, weights,
+                       label_smoothing):
+        """Same as train_step for inputs that are already contiguous float32 /
+        uintp arrays (no conversions inside a timed loop)."""
+        loss = ctypes.c_float()
+        status = self.lib.vithost_train_step(
+            self.handle, images.ctypes.data_as(_float_p),
+            labels.ctypes.data_as(ctypes.POINTER(_size_t)), lr, weight_decay,
+            weights.ctypes.data_as(_float_p) if weights is not None else None,
+            label_smoothing, ctypes.byref(loss))
+        if status != 0:
+            raise RuntimeError("vit_model_train_batch_smoothed failed")
+        return float(loss.value)
+
+    def forward(self, images):
+        images = np.ascontiguousarray(images, dtype=np.float32)
+        logits = np.empty((self.batch, self.config[7]), np.float32)
+        if self.lib.vithost_forward(self.handle,
+                                    images.ctypes.data_as(_float_p),
+                                    logits.ctypes.data_as(_float_p)) != 0:
+            raise RuntimeError("vit_model_forward failed")
+        return logits
+
+    def block_tensor(self, layer, name, grad=False):
+        data = _float_p()
+        rows, cols = _size_t(), _size_t()
+        count = self.lib.vithost_block_tensor(
+            self.handle, layer, name.encode(), int(grad), ctypes.byref(data),
+            ctypes.byref(rows), ctypes.byref(cols))
+        if count == 0:
+            raise KeyError(name)
+        array = np.ctypeslib.as_array(data, shape=(int(count),))
+        return array.reshape(int(rows.value), int(cols.value)).copy()
+
+
+def synthetic_batch(batch, height, width, classes, seed):
+    """Stand-in for an OrganSMNIST batch: uint8 pixels uniform in 0..255,
+    scaled to [0,1] and standardised over the batch; labels uniform."""
+    rng = np.random.RandomState(seed)
+    pixels = rng.randint(0, 256, size=(batch, height * width)).astype(np.float32)
+    pixels /= 255.0
+    images = (pixels - pixels.mean()) / pixels.std()
+    labels = rng.randint(0, classes, size=batch).astype(np.uintp)
+    return images.astype(np.float32), labels
