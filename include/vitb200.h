@@ -78,6 +78,12 @@ int vitb200_make_host_coherent(const void *tensor_memory);
 int vitb200_timer_begin(CudaBackend *backend);
 float vitb200_timer_end(CudaBackend *backend);
 
+/* Every wait inside the tensor-core kernels is bounded; this returns 0, or the
+ * code of the first wait that expired (1 producer, 2 MMA issuer, 3 epilogue).
+ * Read it after synchronising.  The backend aborts on a non-zero code at its
+ * next synchronise. */
+int vitb200_tensor_core_status(void);
+
 /* Milliseconds the backend's stream spent between the first kernel after a
  * synchronise and that next synchronise, summed since the last reset (CUDA
  * events; uploads issued before the first kernel are outside the spans).

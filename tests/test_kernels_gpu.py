@@ -73,6 +73,42 @@ def test_gemm_fp32_forward_and_backward(lib, m, k, n):
     close(host(tdw), dw0 + dw, 2e-5)
 
 
+@pytest.mark.parametrize("m,k,n", [
+    (128, 32, 128), (128, 128, 128), (200, 96, 160), (1600, 128, 384),
+    (1000, 512, 128), (4096, 128, 512), (333, 36, 44), (102400, 128, 128),
+    (257, 1024, 256),
+])
+def test_gemm_tf32_tensor_cores(lib, m, k, n):
+    """tcgen05 kind::tf32 path: operands keep 10 mantissa bits, accumulation is
+    FP32.  Bound: 2e-3 of the largest reference entry (the tolerance stated for
+    TF32 products), checked against float64."""
+    rng = np.random.RandomState(m + k + n)
+    x, w, dy = rng.randn(m, k), rng.randn(k, n), rng.randn(m, n)
+    dx0, dw0 = rng.randn(m, k), rng.randn(k, n)
+    tx, tw, tdy, ty = dev(x), dev(w), dev(dy), torch.empty(m, n, device="cuda")
+    tdx, tdw = dev(dx0), dev(dw0)
+    assert lib.vitb200_k_gemm(ptr(tx), ptr(tw), ptr(ty), size(m), size(k),
+                              size(n), TF32, None) == 0
+    assert lib.vitb200_k_gemm_backward(ptr(tx), ptr(tw), ptr(tdy), ptr(tdx),
+                                       ptr(tdw), size(m), size(k), size(n),
+                                       TF32, None) == 0
+    torch.cuda.synchronize()
+    assert lib.vitb200_tensor_core_status() == 0
+    close(host(ty), x @ w, 2e-3)
+    close(host(tdx), dx0 + dy @ w.T, 2e-3)
+    close(host(tdw), dw0 + x.T @ dy, 2e-3)
+
+
+def test_gemm_tf32_declines_unaligned_shapes(lib):
+    """Row pitches that are not multiples of 16 bytes cannot be described to
+    TMA; an explicit TF32 request is refused rather than silently changed."""
+    t = torch.zeros(64 * 130, device="cuda")
+    assert lib.vitb200_k_gemm(ptr(t), ptr(t), ptr(t), size(64), size(33),
+                              size(130), TF32, None) == -1
+    assert lib.vitb200_k_gemm(ptr(t), ptr(t), ptr(t), size(64), size(8),
+                              size(64), TF32, None) == -1
+
+
 @pytest.mark.parametrize("rows,cols", [
     (1, 4), (5, 32), (33, 100), (100, 128), (1600, 128), (77, 256), (64, 384),
     (50, 512), (9, 1024), (3, 2048), (10, 11),

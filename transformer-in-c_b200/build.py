@@ -50,7 +50,7 @@ def build(force=False, verbose=False):
     if failed:
         raise RuntimeError("nvcc failed")
     subprocess.run(["nvcc", "-gencode", "arch=compute_100a,code=sm_100a", "-shared", "-o", LIBRARY, *objects, "-lcudart",
-                    "-lcuda", "-ldl"], check=True)
+                    "-ldl"], check=True)
     return LIBRARY
 
 

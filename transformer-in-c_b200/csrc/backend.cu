@@ -12,6 +12,7 @@
 
 #include "coherence.h"
 #include "gemm.h"
+#include "gemm_tc.h"
 #include "kernels.h"
 
 #include <climits>
@@ -173,6 +174,12 @@ void settle_timers(CudaBackend *backend) {
               "cudaEventRecord");
     }
     check(cudaStreamSynchronize(backend->stream), "cudaStreamSynchronize");
+    if (const int code = gemm_tc_status()) {
+        fprintf(stderr,
+                "vitb200: a tensor-core kernel gave up waiting (code %d)\n",
+                code);
+        abort();
+    }
     if (backend->span_open) {
         float ms = 0.0f;
         check(cudaEventElapsedTime(&ms, backend->span_begin, backend->span_end),
@@ -1141,6 +1148,10 @@ extern "C" float vitb200_timer_end(CudaBackend *backend) {
     float ms = -1.0f;
     cudaEventElapsedTime(&ms, backend->timer_begin, backend->timer_end);
     return ms;
+}
+
+extern "C" int vitb200_tensor_core_status(void) {
+    return gemm_tc_status();
 }
 
 extern "C" double vitb200_device_busy_ms(CudaBackend *backend, int reset) {

@@ -1,47 +1,101 @@
 #include "gemm.h"
+#include "gemm_tc.h"
 #include "kernels.h"
 #include "../../include/vitb200.h"
 
-namespace vitb200 {
+#include <cstdlib>
+#include <cstring>
 
-int gemm_forward(const float *x, const float *w, float *y, int m, int k, int n,
-                 int precision, cudaStream_t stream) {
+namespace vitb200 {
+namespace {
+
+// Below this many multiply-adds a product is latency-bound either way and the
+// exact FP32 kernel is used, which also keeps very small models (the host's
+// own device test runs d_model = 32) at FP32 accuracy.
+constexpr double kTensorCoreMinimumWork = 16.0 * 1024 * 1024;
+
+int default_precision() {
+    static int chosen = []() {
+        const char *text = getenv("VITB200_GEMM");
+        if (text && strcmp(text, "fp32") == 0) {
+            return VITB200_PRECISION_FP32;
+        }
+        if (text && strcmp(text, "tf32") == 0) {
+            return VITB200_PRECISION_TF32;
+        }
+        return VITB200_PRECISION_AUTO;
+    }();
+    return chosen;
+}
+
+// Decides whether `gemm` goes to the tensor cores; -1 = impossible as asked.
+int use_tensor_cores(const TcGemm &gemm, int precision) {
+    if (precision == VITB200_PRECISION_AUTO) {
+        precision = default_precision();
+    }
+    if (precision == VITB200_PRECISION_FP32) {
+        return 0;
+    }
+    const bool supported = gemm_tc_supported(gemm);
+    if (precision == VITB200_PRECISION_TF32) {
+        return supported ? 1 : -1;
+    }
+    const double work = double(gemm.m) * gemm.n * gemm.k;
+    return supported && work >= kTensorCoreMinimumWork ? 1 : 0;
+}
+
+void simt(const TcGemm &g, cudaStream_t stream) {
+    GemmOperands op;
+    op.a = g.a;
+    op.a_row = g.a_mn_major ? 1 : g.lda;
+    op.a_col = g.a_mn_major ? g.lda : 1;
+    op.b = g.b;
+    op.b_row = g.b_mn_major ? g.ldb : 1;
+    op.b_col = g.b_mn_major ? 1 : g.ldb;
+    op.c = g.d;
+    op.c_row = g.ldd;
+    op.m = g.m;
+    op.n = g.n;
+    op.k = g.k;
+    op.accumulate = g.accumulate ? 1 : 0;
+    launch_gemm_simt(op, stream);
+}
+
+int run(const TcGemm &gemm, int precision, cudaStream_t stream) {
+    const int tensor = use_tensor_cores(gemm, precision);
+    if (tensor < 0) {
+        return -1;
+    }
+    if (tensor == 1 && launch_gemm_tc(gemm, stream) == 0) {
+        return 0;
+    }
     if (precision == VITB200_PRECISION_TF32) {
         return -1;
     }
-    GemmOperands op;
-    op.a = x;  op.a_row = k; op.a_col = 1;
-    op.b = w;  op.b_row = n; op.b_col = 1;
-    op.c = y;  op.c_row = n;
-    op.m = m;  op.n = n;     op.k = k;
-    op.accumulate = 0;
-    launch_gemm_simt(op, stream);
+    simt(gemm, stream);
     return 0;
+}
+
+}  // namespace
+
+int gemm_forward(const float *x, const float *w, float *y, int m, int k, int n,
+                 int precision, cudaStream_t stream) {
+    // Y[m,n] = X[m,k] W[k,n]: X has the reduction contiguous, W the output.
+    TcGemm g = {x, w, y, nullptr, m, n, k, k, n, n, false, true, false};
+    return run(g, precision, stream);
 }
 
 int gemm_backward(const float *x, const float *w, const float *dy, float *dx,
                   float *dw, int m, int k, int n, int precision,
                   cudaStream_t stream) {
-    if (precision == VITB200_PRECISION_TF32) {
+    // dX[m,k] += dY[m,n] W^T: both operands have the reduction (n) contiguous.
+    TcGemm gx = {dy, w, dx, nullptr, m, k, n, n, n, k, false, false, true};
+    if (run(gx, precision, stream) != 0) {
         return -1;
     }
-    // dX[M,K] += dY[M,N] * W^T : B(n,k) = w[k*n_cols + n].
-    GemmOperands dx_op;
-    dx_op.a = dy; dx_op.a_row = n; dx_op.a_col = 1;
-    dx_op.b = w;  dx_op.b_row = 1; dx_op.b_col = n;
-    dx_op.c = dx; dx_op.c_row = k;
-    dx_op.m = m;  dx_op.n = k;     dx_op.k = n;
-    dx_op.accumulate = 1;
-    launch_gemm_simt(dx_op, stream);
-    // dW[K,N] += X^T * dY : A(kk,m) = x[m*k_cols + kk].
-    GemmOperands dw_op;
-    dw_op.a = x;  dw_op.a_row = 1; dw_op.a_col = k;
-    dw_op.b = dy; dw_op.b_row = n; dw_op.b_col = 1;
-    dw_op.c = dw; dw_op.c_row = n;
-    dw_op.m = k;  dw_op.n = n;     dw_op.k = m;
-    dw_op.accumulate = 1;
-    launch_gemm_simt(dw_op, stream);
-    return 0;
+    // dW[k,n] += X^T dY: both operands have their output index contiguous.
+    TcGemm gw = {x, dy, dw, nullptr, k, n, m, k, n, n, true, true, true};
+    return run(gw, precision, stream);
 }
 
 }  // namespace vitb200

@@ -1,0 +1,605 @@
+// Tensor-core matrix products for sm_100a: tcgen05.mma (kind::tf32, FP32
+// accumulation in tensor memory) fed by TMA.
+//
+//   D[M,N] (+)= A[M,K] * B[K,N],  all FP32 in global memory, row-major.
+//
+// Either operand may be stored with the reduction index contiguous ("K-major":
+// X in X*W, dY and W in dY*W^T) or with the output index contiguous
+// ("MN-major": W in X*W, X and dY in X^T*dY), so the same kernel serves the
+// forward product and both gradients of reference src/ops.c:107-165 without a
+// transposed copy.  TF32 reads the FP32 words as they are; nothing is
+// converted or re-laid-out in global memory.
+//
+// One CTA computes one 128 x 128 output tile over a slice of the reduction:
+//
+//   warp 0      TMA producer: per 32-deep reduction block, one 128B-swizzled
+//               box (K-major) or four 32x32 boxes (MN-major) per operand into
+//               a ring of shared-memory stages, signalled through mbarriers
+//   warp 1      allocates 128 TMEM columns, issues four K=8 tcgen05.mma per
+//               block from one lane, releases stages with tcgen05.commit
+//   warps 2-5   epilogue: tcgen05.ld the accumulator (one TMEM lane quarter
+//               per warp), add the bias if asked, write a 128B-swizzled tile
+//               into the (now idle) stage memory and hand it to TMA, as a
+//               plain store or as an FP32 reduce-add (for "+=" outputs and for
+//               reductions split across CTAs)
+//
+// Partial tiles need no special code: TMA zero-fills out-of-range loads and
+// clips out-of-range stores.  Every wait on an mbarrier is bounded in time;
+// on expiry the kernel records a code in `*status` and all roles fall through
+// to the common teardown, which frees the tensor memory.
+#include "gemm_tc.h"
+#include "kernels.h"
+
+#include <cuda.h>
+#include <cstdio>
+#include <cstdlib>
+#include <cstring>
+#include <unordered_map>
+
+namespace vitb200 {
+namespace {
+
+constexpr int kTileM = 128;
+constexpr int kTileN = 128;
+constexpr int kBlockK = 32;                 // 128 bytes of FP32 per row
+constexpr int kMmaK = 8;                    // tf32 K per instruction
+constexpr int kOperandBytes = kTileM * kBlockK * 4;   // 16 KiB
+constexpr int kStageBytes = 2 * kOperandBytes;
+constexpr int kStages = 3;
+constexpr int kSmemBytes = kStages * kStageBytes + 1024;  // + alignment slack
+constexpr int kThreads = 192;
+constexpr int kTmemColumns = 128;
+constexpr unsigned long long kWaitLimitNs = 2000000000ull;  // 2 s
+
+// ---- PTX wrappers ----------------------------------------------------------
+
+__device__ __forceinline__ uint32_t smem_address(const void *pointer) {
+    return static_cast<uint32_t>(__cvta_generic_to_shared(pointer));
+}
+
+__device__ __forceinline__ unsigned long long global_timer_ns() {
+    unsigned long long t;
+    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+    return t;
+}
+
+__device__ __forceinline__ void mbarrier_init(uint64_t *bar, uint32_t count) {
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_address(bar)),
+                 "r"(count));
+}
+
+__device__ __forceinline__ void mbarrier_expect_tx(uint64_t *bar, uint32_t bytes) {
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(
+                     smem_address(bar)),
+                 "r"(bytes)
+                 : "memory");
+}
+
+__device__ __forceinline__ bool mbarrier_try_wait(uint64_t *bar, uint32_t parity) {
+    uint32_t done;
+    asm volatile(
+        "{\n\t"
+        ".reg .pred p;\n\t"
+        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+        "selp.u32 %0, 1, 0, p;\n\t"
+        "}"
+        : "=r"(done)
+        : "r"(smem_address(bar)), "r"(parity)
+        : "memory");
+    return done != 0;
+}
+
+// Returns false if the phase did not complete within kWaitLimitNs.
+__device__ __forceinline__ bool mbarrier_wait(uint64_t *bar, uint32_t parity) {
+    if (mbarrier_try_wait(bar, parity)) {
+        return true;
+    }
+    const unsigned long long start = global_timer_ns();
+    while (!mbarrier_try_wait(bar, parity)) {
+        if (global_timer_ns() - start > kWaitLimitNs) {
+            return false;
+        }
+    }
+    return true;
+}
+
+__device__ __forceinline__ void tma_load_2d(void *smem, const CUtensorMap *map,
+                                            int x, int y, uint64_t *bar) {
+    asm volatile(
+        "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes"
+        " [%0], [%1, {%2, %3}], [%4];" ::"r"(smem_address(smem)),
+        "l"(reinterpret_cast<uint64_t>(map)), "r"(x), "r"(y),
+        "r"(smem_address(bar))
+        : "memory");
+}
+
+__device__ __forceinline__ void tma_store_2d(const void *smem,
+                                             const CUtensorMap *map, int x,
+                                             int y) {
+    asm volatile(
+        "cp.async.bulk.tensor.2d.global.shared::cta.bulk_group [%0, {%2, %3}], [%1];" ::
+            "l"(reinterpret_cast<uint64_t>(map)),
+        "r"(smem_address(smem)), "r"(x), "r"(y)
+        : "memory");
+}
+
+__device__ __forceinline__ void tma_reduce_add_2d(const void *smem,
+                                                  const CUtensorMap *map, int x,
+                                                  int y) {
+    asm volatile(
+        "cp.reduce.async.bulk.tensor.2d.global.shared::cta.add.bulk_group"
+        " [%0, {%2, %3}], [%1];" ::"l"(reinterpret_cast<uint64_t>(map)),
+        "r"(smem_address(smem)), "r"(x), "r"(y)
+        : "memory");
+}
+
+__device__ __forceinline__ void tma_store_commit_and_wait() {
+    asm volatile("cp.async.bulk.commit_group;" ::: "memory");
+    asm volatile("cp.async.bulk.wait_group 0;" ::: "memory");
+}
+
+__device__ __forceinline__ void tcgen05_fence_before() {
+    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+}
+
+__device__ __forceinline__ void tcgen05_fence_after() {
+    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+}
+
+__device__ __forceinline__ void tcgen05_commit(uint64_t *bar) {
+    asm volatile(
+        "tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::
+            "r"(smem_address(bar))
+        : "memory");
+}
+
+__device__ __forceinline__ void tcgen05_mma_tf32(uint32_t tmem_d, uint64_t desc_a,
+                                                 uint64_t desc_b, uint32_t idesc,
+                                                 uint32_t accumulate) {
+    asm volatile(
+        "{\n\t"
+        ".reg .pred p;\n\t"
+        "setp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::1.kind::tf32 [%0], %1, %2, %3, p;\n\t"
+        "}" ::"r"(tmem_d),
+        "l"(desc_a), "l"(desc_b), "r"(idesc), "r"(accumulate)
+        : "memory");
+}
+
+__device__ __forceinline__ void tcgen05_load_32(uint32_t tmem_address,
+                                                uint32_t (&r)[32]) {
+    asm volatile(
+        "tcgen05.ld.sync.aligned.32x32b.x32.b32"
+        "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15,"
+        " %16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29,"
+        " %30, %31}, [%32];"
+        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]),
+          "=r"(r[6]), "=r"(r[7]), "=r"(r[8]), "=r"(r[9]), "=r"(r[10]),
+          "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]),
+          "=r"(r[16]), "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]),
+          "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]), "=r"(r[25]),
+          "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]),
+          "=r"(r[31])
+        : "r"(tmem_address));
+    asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+}
+
+// Shared-memory operand descriptor with the Blackwell version field.  Offsets
+// are in bytes; the hardware fields drop the low four bits.  Layout types:
+// 2 = 128-byte swizzle of 16-byte chunks (K-major operands), 1 = 128-byte
+// swizzle of 32-byte chunks, the only layout tcgen05 accepts for 32-bit
+// operands whose output index is the contiguous one.
+constexpr uint32_t kLayoutSwizzle128 = 2;
+constexpr uint32_t kLayoutSwizzle128Base32 = 1;
+__device__ __forceinline__ uint64_t operand_descriptor(uint32_t smem_byte_address,
+                                                       uint32_t leading_bytes,
+                                                       uint32_t stride_bytes,
+                                                       uint32_t layout_type) {
+    uint64_t desc = 0;
+    desc |= uint64_t((smem_byte_address >> 4) & 0x3fff);
+    desc |= uint64_t((leading_bytes >> 4) & 0x3fff) << 16;
+    desc |= uint64_t((stride_bytes >> 4) & 0x3fff) << 32;
+    desc |= uint64_t(1) << 46;   // descriptor version
+    desc |= uint64_t(layout_type) << 61;
+    return desc;
+}
+
+struct TcParams {
+    int m, n;                 // output extents
+    int k_blocks;             // ceil(reduction / 32)
+    int k_blocks_per_split;
+    int n_tiles;
+    int a_mn_major, b_mn_major;
+    int reduce_add;           // 1: TMA reduce-add into D, 0: plain store
+    const float *bias;        // nullable, length n
+    int *status;              // device-visible word, 0 = ok
+};
+
+__global__ void __launch_bounds__(kThreads, 1)
+gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a,
+               const __grid_constant__ CUtensorMap map_b,
+               const __grid_constant__ CUtensorMap map_d, const TcParams p) {
+    extern __shared__ uint8_t raw_smem[];
+    __shared__ __align__(8) uint64_t full_bar[kStages];
+    __shared__ __align__(8) uint64_t empty_bar[kStages];
+    __shared__ __align__(8) uint64_t accumulator_bar;
+    __shared__ uint32_t tmem_base_slot;
+
+    uint8_t *smem = reinterpret_cast<uint8_t *>(
+        (reinterpret_cast<uintptr_t>(raw_smem) + 1023) & ~uintptr_t(1023));
+    const int warp = threadIdx.x >> 5;
+    const int lane = threadIdx.x & 31;
+    const int tile = blockIdx.x;
+    const int m0 = (tile / p.n_tiles) * kTileM;
+    const int n0 = (tile % p.n_tiles) * kTileN;
+    const int kb_begin = blockIdx.z * p.k_blocks_per_split;
+    const int kb_end = min(p.k_blocks, kb_begin + p.k_blocks_per_split);
+    const int kb_count = kb_end - kb_begin;
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < kStages; ++s) {
+            mbarrier_init(&full_bar[s], 1);
+            mbarrier_init(&empty_bar[s], 1);
+        }
+        mbarrier_init(&accumulator_bar, 1);
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    if (warp == 1) {
+        asm volatile(
+            "tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::
+                "r"(smem_address(&tmem_base_slot)),
+            "r"(kTmemColumns)
+            : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::
+                         : "memory");
+    }
+    tcgen05_fence_before();
+    __syncthreads();
+    tcgen05_fence_after();
+    const uint32_t tmem_base = tmem_base_slot;
+    bool ok = true;
+
+    if (kb_count > 0) {
+        if (warp == 0) {
+            if (lane == 0) {
+                for (int i = 0; i < kb_count && ok; ++i) {
+                    const int s = i % kStages;
+                    const uint32_t phase = (i / kStages) & 1;
+                    ok = mbarrier_wait(&empty_bar[s], phase ^ 1);
+                    if (!ok) {
+                        atomicExch(p.status, 1);
+                        break;
+                    }
+                    uint8_t *a_tile = smem + s * kStageBytes;
+                    uint8_t *b_tile = a_tile + kOperandBytes;
+                    const int k0 = (kb_begin + i) * kBlockK;
+                    mbarrier_expect_tx(&full_bar[s], kStageBytes);
+                    if (p.a_mn_major) {
+                        for (int j = 0; j < 4; ++j) {
+                            tma_load_2d(a_tile + j * 4096, &map_a, m0 + 32 * j, k0,
+                                        &full_bar[s]);
+                        }
+                    } else {
+                        tma_load_2d(a_tile, &map_a, k0, m0, &full_bar[s]);
+                    }
+                    if (p.b_mn_major) {
+                        for (int j = 0; j < 4; ++j) {
+                            tma_load_2d(b_tile + j * 4096, &map_b, n0 + 32 * j, k0,
+                                        &full_bar[s]);
+                        }
+                    } else {
+                        tma_load_2d(b_tile, &map_b, k0, n0, &full_bar[s]);
+                    }
+                }
+            }
+        } else if (warp == 1) {
+            if (lane == 0) {
+                // kind::tf32, FP32 accumulator, M = 128, N = 128.
+                const uint32_t idesc = (1u << 4) | (2u << 7) | (2u << 10) |
+                                       (uint32_t(p.a_mn_major) << 15) |
+                                       (uint32_t(p.b_mn_major) << 16) |
+                                       (uint32_t(kTileN >> 3) << 17) |
+                                       (uint32_t(kTileM >> 4) << 24);
+                // K-major: 8-row groups 1024 B apart, K steps of 32 B inside the
+                // swizzled row.  MN-major: 32-wide MN atoms one box (4096 B)
+                // apart, groups of four 128 B reduction rows 512 B apart, K
+                // steps of eight rows.
+                const uint32_t a_lead = p.a_mn_major ? 4096 : 16;
+                const uint32_t b_lead = p.b_mn_major ? 4096 : 16;
+                const uint32_t a_stride = p.a_mn_major ? 512 : 1024;
+                const uint32_t b_stride = p.b_mn_major ? 512 : 1024;
+                const uint32_t a_step = p.a_mn_major ? 1024 : kMmaK * 4;
+                const uint32_t b_step = p.b_mn_major ? 1024 : kMmaK * 4;
+                const uint32_t a_layout =
+                    p.a_mn_major ? kLayoutSwizzle128Base32 : kLayoutSwizzle128;
+                const uint32_t b_layout =
+                    p.b_mn_major ? kLayoutSwizzle128Base32 : kLayoutSwizzle128;
+                for (int i = 0; i < kb_count; ++i) {
+                    const int s = i % kStages;
+                    const uint32_t phase = (i / kStages) & 1;
+                    ok = mbarrier_wait(&full_bar[s], phase);
+                    if (!ok) {
+                        atomicExch(p.status, 2);
+                        break;
+                    }
+                    tcgen05_fence_after();
+                    const uint32_t a_base = smem_address(smem + s * kStageBytes);
+                    const uint32_t b_base = a_base + kOperandBytes;
+#pragma unroll
+                    for (int ks = 0; ks < kBlockK / kMmaK; ++ks) {
+                        const uint64_t da = operand_descriptor(
+                            a_base + ks * a_step, a_lead, a_stride, a_layout);
+                        const uint64_t db = operand_descriptor(
+                            b_base + ks * b_step, b_lead, b_stride, b_layout);
+                        tcgen05_mma_tf32(tmem_base, da, db, idesc,
+                                         (i > 0 || ks > 0) ? 1u : 0u);
+                    }
+                    tcgen05_commit(&empty_bar[s]);
+                }
+                if (ok) {
+                    tcgen05_commit(&accumulator_bar);
+                }
+            }
+        } else {
+            // Epilogue warps 2..5 own TMEM lane quarters 2, 3, 0, 1.
+            const int quarter = warp & 3;
+            const int row = quarter * 32 + lane;
+            ok = mbarrier_wait(&accumulator_bar, 0);
+            ok = __all_sync(0xffffffffu, ok);   // keep the warp in step
+            if (!ok) {
+                atomicExch(p.status, 3);
+            }
+            tcgen05_fence_after();
+            if (ok) {
+#pragma unroll 1
+                for (int chunk = 0; chunk < kTileN / 32; ++chunk) {
+                    if (n0 + chunk * 32 >= p.n) {
+                        break;
+                    }
+                    uint32_t r[32];
+                    tcgen05_load_32(tmem_base + (uint32_t(quarter * 32) << 16) +
+                                        chunk * 32,
+                                    r);
+                    float *stage_row = reinterpret_cast<float *>(
+                        smem + chunk * kOperandBytes + row * 128);
+#pragma unroll
+                    for (int c = 0; c < 8; ++c) {
+                        float4 v;
+                        v.x = __uint_as_float(r[4 * c + 0]);
+                        v.y = __uint_as_float(r[4 * c + 1]);
+                        v.z = __uint_as_float(r[4 * c + 2]);
+                        v.w = __uint_as_float(r[4 * c + 3]);
+                        if (p.bias) {
+                            const int col = n0 + chunk * 32 + 4 * c;
+                            if (col + 3 < p.n) {
+                                const float4 b = __ldg(
+                                    reinterpret_cast<const float4 *>(p.bias + col));
+                                v.x += b.x; v.y += b.y; v.z += b.z; v.w += b.w;
+                            } else {
+                                if (col + 0 < p.n) v.x += __ldg(p.bias + col + 0);
+                                if (col + 1 < p.n) v.y += __ldg(p.bias + col + 1);
+                                if (col + 2 < p.n) v.z += __ldg(p.bias + col + 2);
+                            }
+                        }
+                        // 128-byte swizzle: 16-byte chunk c of row r lives at
+                        // chunk position c ^ (r % 8).
+                        *reinterpret_cast<float4 *>(
+                            stage_row + 4 * (c ^ (row & 7))) = v;
+                    }
+                }
+                // Make the generic-proxy writes visible to the TMA engine.
+                asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+            }
+            tcgen05_fence_before();
+            asm volatile("bar.sync 1, 128;" ::: "memory");
+            if (ok && warp == 2 && lane == 0) {
+                for (int chunk = 0; chunk < kTileN / 32; ++chunk) {
+                    const int col = n0 + chunk * 32;
+                    if (col >= p.n) {
+                        break;
+                    }
+                    if (p.reduce_add) {
+                        tma_reduce_add_2d(smem + chunk * kOperandBytes, &map_d,
+                                          col, m0);
+                    } else {
+                        tma_store_2d(smem + chunk * kOperandBytes, &map_d, col,
+                                     m0);
+                    }
+                }
+                tma_store_commit_and_wait();
+            }
+        }
+    }
+    tcgen05_fence_before();
+    __syncthreads();
+    if (warp == 1) {
+        __syncwarp();
+        tcgen05_fence_after();
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(
+                         tmem_base),
+                     "r"(kTmemColumns)
+                     : "memory");
+    }
+}
+
+// ---- host side -------------------------------------------------------------
+
+using EncodeTiled = CUresult (*)(CUtensorMap *, CUtensorMapDataType, cuuint32_t,
+                                 void *, const cuuint64_t *, const cuuint64_t *,
+                                 const cuuint32_t *, const cuuint32_t *,
+                                 CUtensorMapInterleave, CUtensorMapSwizzle,
+                                 CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+EncodeTiled encode_tiled() {
+    static EncodeTiled function = []() -> EncodeTiled {
+        void *entry = nullptr;
+        cudaDriverEntryPointQueryResult result;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &entry,
+                                    cudaEnableDefault, &result) != cudaSuccess ||
+            result != cudaDriverEntryPointSuccess) {
+            return nullptr;
+        }
+        return reinterpret_cast<EncodeTiled>(entry);
+    }();
+    return function;
+}
+
+struct MapKey {
+    const void *base;
+    unsigned long long inner, outer, pitch;
+    unsigned box_inner, box_outer;
+    int swizzle;
+    bool operator==(const MapKey &o) const {
+        return base == o.base && inner == o.inner && outer == o.outer &&
+               pitch == o.pitch && box_inner == o.box_inner &&
+               box_outer == o.box_outer && swizzle == o.swizzle;
+    }
+};
+
+struct MapKeyHash {
+    size_t operator()(const MapKey &k) const {
+        size_t h = reinterpret_cast<size_t>(k.base);
+        h = h * 1000003u ^ k.inner;
+        h = h * 1000003u ^ k.outer;
+        h = h * 1000003u ^ k.pitch;
+        h = h * 1000003u ^ (size_t(k.box_inner) << 16 | k.box_outer);
+        h = h * 1000003u ^ size_t(k.swizzle);
+        return h;
+    }
+};
+
+// 2-D FP32 tensor map over a row-major matrix: `inner` contiguous elements per
+// row, `outer` rows `pitch` elements apart, with the given 128-byte swizzle
+// flavour.  Encoded maps are cached: the training step presents the same
+// buffers every iteration.
+bool tensor_map(const float *base, unsigned long long inner,
+                unsigned long long outer, unsigned long long pitch,
+                unsigned box_inner, unsigned box_outer,
+                CUtensorMapSwizzle swizzle, CUtensorMap *out) {
+    static std::unordered_map<MapKey, CUtensorMap, MapKeyHash> cache;
+    const MapKey key{base, inner, outer, pitch, box_inner, box_outer,
+                     int(swizzle)};
+    auto found = cache.find(key);
+    if (found != cache.end()) {
+        *out = found->second;
+        return true;
+    }
+    EncodeTiled encode = encode_tiled();
+    if (!encode) {
+        return false;
+    }
+    const cuuint64_t dims[2] = {inner, outer};
+    const cuuint64_t strides[1] = {pitch * sizeof(float)};
+    const cuuint32_t box[2] = {box_inner, box_outer};
+    const cuuint32_t element_strides[2] = {1, 1};
+    const CUresult status = encode(
+        out, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 2, const_cast<float *>(base), dims,
+        strides, box, element_strides, CU_TENSOR_MAP_INTERLEAVE_NONE,
+        swizzle, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+        CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (status != CUDA_SUCCESS) {
+        return false;
+    }
+    if (cache.size() > 4096) {
+        cache.clear();
+    }
+    cache.emplace(key, *out);
+    return true;
+}
+
+int *status_word() {
+    static int *word = []() -> int * {
+        int *memory = nullptr;
+        if (cudaHostAlloc(reinterpret_cast<void **>(&memory), sizeof(int),
+                          cudaHostAllocMapped) != cudaSuccess) {
+            return nullptr;
+        }
+        *memory = 0;
+        return memory;
+    }();
+    return word;
+}
+
+}  // namespace
+
+bool gemm_tc_supported(const TcGemm &g) {
+    // TMA needs 16-byte aligned bases and row pitches; tiny extents are left
+    // to the FP32 kernel.
+    auto aligned = [](const void *p) {
+        return (reinterpret_cast<uintptr_t>(p) & 15) == 0;
+    };
+    return g.m >= 32 && g.n >= 32 && g.k >= 32 && g.lda % 4 == 0 &&
+           g.ldb % 4 == 0 && g.ldd % 4 == 0 && aligned(g.a) && aligned(g.b) &&
+           aligned(g.d) && (!g.bias || aligned(g.bias)) && status_word() &&
+           encode_tiled();
+}
+
+int launch_gemm_tc(const TcGemm &g, cudaStream_t stream) {
+    if (!gemm_tc_supported(g)) {
+        return -1;
+    }
+    static bool configured = false;
+    if (!configured) {
+        if (cudaFuncSetAttribute(gemm_tc_kernel,
+                                 cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                 kSmemBytes) != cudaSuccess) {
+            return -1;
+        }
+        configured = true;
+    }
+    CUtensorMap map_a, map_b, map_d;
+    // K-major operand: rows = output index, inner = reduction index.
+    // MN-major operand: rows = reduction index, inner = output index.
+    const CUtensorMapSwizzle chunks16 = CU_TENSOR_MAP_SWIZZLE_128B;
+    const CUtensorMapSwizzle chunks32 = CU_TENSOR_MAP_SWIZZLE_128B_ATOM_32B;
+    const bool ok_a = g.a_mn_major
+        ? tensor_map(g.a, g.m, g.k, g.lda, 32, 32, chunks32, &map_a)
+        : tensor_map(g.a, g.k, g.m, g.lda, 32, kTileM, chunks16, &map_a);
+    const bool ok_b = g.b_mn_major
+        ? tensor_map(g.b, g.n, g.k, g.ldb, 32, 32, chunks32, &map_b)
+        : tensor_map(g.b, g.k, g.n, g.ldb, 32, kTileN, chunks16, &map_b);
+    const bool ok_d =
+        tensor_map(g.d, g.n, g.m, g.ldd, 32, kTileM, chunks16, &map_d);
+    if (!ok_a || !ok_b || !ok_d) {
+        return -1;
+    }
+    TcParams p;
+    p.m = g.m;
+    p.n = g.n;
+    p.k_blocks = (g.k + kBlockK - 1) / kBlockK;
+    p.n_tiles = (g.n + kTileN - 1) / kTileN;
+    const int m_tiles = (g.m + kTileM - 1) / kTileM;
+    const int tiles = m_tiles * p.n_tiles;
+    int splits = 1;
+    if (g.accumulate) {
+        // Long reductions onto few output tiles (weight gradients): spread the
+        // reduction over about two waves of CTAs, at least 8 blocks each.
+        const int wanted = (2 * 148 + tiles - 1) / tiles;
+        const int most = (p.k_blocks + 7) / 8;
+        splits = wanted < most ? wanted : most;
+        if (splits < 1) {
+            splits = 1;
+        }
+    }
+    p.k_blocks_per_split = (p.k_blocks + splits - 1) / splits;
+    splits = (p.k_blocks + p.k_blocks_per_split - 1) / p.k_blocks_per_split;
+    p.a_mn_major = g.a_mn_major ? 1 : 0;
+    p.b_mn_major = g.b_mn_major ? 1 : 0;
+    p.reduce_add = g.accumulate ? 1 : 0;
+    p.bias = g.bias;
+    int *device_status = nullptr;
+    cudaHostGetDevicePointer(reinterpret_cast<void **>(&device_status),
+                             status_word(), 0);
+    p.status = device_status;
+    gemm_tc_kernel<<<dim3(tiles, 1, splits), kThreads, kSmemBytes, stream>>>(
+        map_a, map_b, map_d, p);
+    ++g_kernel_launches;
+    return 0;
+}
+
+int gemm_tc_status() {
+    int *word = status_word();
+    return word ? *word : 0;
+}
+
+}  // namespace vitb200

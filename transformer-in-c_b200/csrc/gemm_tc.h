@@ -1,0 +1,29 @@
+// tcgen05 / TMA matrix product (gemm_tc.cu).
+#pragma once
+
+#include <cuda_runtime.h>
+
+namespace vitb200 {
+
+// D[m,n] (+)= A * B over a reduction of length k, FP32 row-major storage.
+//   a_mn_major = false: A is stored [m rows][k contiguous], pitch lda
+//   a_mn_major = true : A is stored [k rows][m contiguous], pitch lda
+//   b_mn_major = false: B is stored [n rows][k contiguous], pitch ldb
+//   b_mn_major = true : B is stored [k rows][n contiguous], pitch ldb
+// accumulate adds into D (atomically, so the reduction may be split).
+struct TcGemm {
+    const float *a;
+    const float *b;
+    float *d;
+    const float *bias;  // nullable; added per output column (not with accumulate)
+    int m, n, k;
+    long long lda, ldb, ldd;
+    bool a_mn_major, b_mn_major, accumulate;
+};
+
+bool gemm_tc_supported(const TcGemm &gemm);
+int launch_gemm_tc(const TcGemm &gemm, cudaStream_t stream);
+// 0, or the code of the first bounded wait that expired inside the kernel.
+int gemm_tc_status();
+
+}  // namespace vitb200
