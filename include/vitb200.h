@@ -78,6 +78,14 @@ int vitb200_make_host_coherent(const void *tensor_memory);
 int vitb200_timer_begin(CudaBackend *backend);
 float vitb200_timer_end(CudaBackend *backend);
 
+/* Operand precision of the dense products issued through the op table:
+ * VITB200_PRECISION_AUTO (default: TF32 tensor cores for products of at least
+ * 16 Mi multiply-adds whose layout TMA can describe, FP32 FMA otherwise),
+ * VITB200_PRECISION_FP32 (always FP32 FMA) or VITB200_PRECISION_TF32 (tensor
+ * cores wherever the layout allows).  The environment variable VITB200_GEMM
+ * (fp32 | tf32) sets the same thing at start-up; -1 returns to it. */
+void vitb200_set_gemm_precision(int precision);
+
 /* Every wait inside the tensor-core kernels is bounded; this returns 0, or the
  * code of the first wait that expired (1 producer, 2 MMA issuer, 3 epilogue).
  * Read it after synchronising.  The backend aborts on a non-zero code at its

@@ -364,6 +364,11 @@ void launch_attention_forward(const float *q, const float *k, const float *v,
                               float *probabilities, float *out, size_t groups,
                               size_t seq, size_t head_dim, float scale,
                               cudaStream_t stream) {
+    if (attention_small_supported(seq, head_dim) &&
+        launch_attention_small_forward(q, k, v, probabilities, out, groups, seq,
+                                       head_dim, scale, stream)) {
+        return;
+    }
     const dim3 grid(static_cast<unsigned>(groups),
                     static_cast<unsigned>((seq + kTile - 1) / kTile));
     const size_t pitch = head_dim + 1;
@@ -383,6 +388,12 @@ void launch_attention_backward(const float *q, const float *k, const float *v,
                                float *dv, float *row_dots, size_t groups,
                                size_t seq, size_t head_dim, float scale,
                                cudaStream_t stream) {
+    if (attention_small_supported(seq, head_dim) &&
+        launch_attention_small_backward(q, k, v, probabilities, out, dout, dq,
+                                        dk, dv, groups, seq, head_dim, scale,
+                                        stream)) {
+        return;
+    }
     const size_t rows = groups * seq;
     row_dots_kernel<<<stream_grid(rows * 32), kStreamThreads, 0, stream>>>(
         dout, out, row_dots, rows, int(head_dim));

@@ -1150,6 +1150,10 @@ extern "C" float vitb200_timer_end(CudaBackend *backend) {
     return ms;
 }
 
+extern "C" void vitb200_set_gemm_precision(int precision) {
+    gemm_set_default_precision(precision);
+}
+
 extern "C" int vitb200_tensor_core_status(void) {
     return gemm_tc_status();
 }

@@ -14,7 +14,12 @@ namespace {
 // own device test runs d_model = 32) at FP32 accuracy.
 constexpr double kTensorCoreMinimumWork = 16.0 * 1024 * 1024;
 
+int g_forced_precision = -1;
+
 int default_precision() {
+    if (g_forced_precision >= 0) {
+        return g_forced_precision;
+    }
     static int chosen = []() {
         const char *text = getenv("VITB200_GEMM");
         if (text && strcmp(text, "fp32") == 0) {
@@ -28,9 +33,13 @@ int default_precision() {
     return chosen;
 }
 
-// Decides whether `gemm` goes to the tensor cores; -1 = impossible as asked.
+// Decides whether `gemm` goes to the tensor cores: 1 yes, 0 no, -1 when the
+// caller asked for TF32 explicitly and the layout cannot be served.  A TF32
+// *default* (environment or vitb200_set_gemm_precision) means "wherever the
+// layout allows" and falls back to FP32 quietly.
 int use_tensor_cores(const TcGemm &gemm, int precision) {
-    if (precision == VITB200_PRECISION_AUTO) {
+    const bool explicit_request = precision != VITB200_PRECISION_AUTO;
+    if (!explicit_request) {
         precision = default_precision();
     }
     if (precision == VITB200_PRECISION_FP32) {
@@ -38,7 +47,7 @@ int use_tensor_cores(const TcGemm &gemm, int precision) {
     }
     const bool supported = gemm_tc_supported(gemm);
     if (precision == VITB200_PRECISION_TF32) {
-        return supported ? 1 : -1;
+        return supported ? 1 : (explicit_request ? -1 : 0);
     }
     const double work = double(gemm.m) * gemm.n * gemm.k;
     return supported && work >= kTensorCoreMinimumWork ? 1 : 0;
@@ -66,17 +75,23 @@ int run(const TcGemm &gemm, int precision, cudaStream_t stream) {
     if (tensor < 0) {
         return -1;
     }
-    if (tensor == 1 && launch_gemm_tc(gemm, stream) == 0) {
-        return 0;
-    }
-    if (precision == VITB200_PRECISION_TF32) {
-        return -1;
+    if (tensor == 1) {
+        if (launch_gemm_tc(gemm, stream) == 0) {
+            return 0;
+        }
+        if (precision == VITB200_PRECISION_TF32) {
+            return -1;
+        }
     }
     simt(gemm, stream);
     return 0;
 }
 
 }  // namespace
+
+void gemm_set_default_precision(int precision) {
+    g_forced_precision = precision;
+}
 
 int gemm_forward(const float *x, const float *w, float *y, int m, int k, int n,
                  int precision, cudaStream_t stream) {

@@ -17,4 +17,8 @@ int gemm_backward(const float *x, const float *w, const float *dy, float *dx,
                   float *dw, int m, int k, int n, int precision,
                   cudaStream_t stream);
 
+// Overrides what VITB200_PRECISION_AUTO means (and the VITB200_GEMM
+// environment variable); -1 restores the default policy.
+void gemm_set_default_precision(int precision);
+
 }  // namespace vitb200

@@ -7,8 +7,8 @@
 // X in X*W, dY and W in dY*W^T) or with the output index contiguous
 // ("MN-major": W in X*W, X and dY in X^T*dY), so the same kernel serves the
 // forward product and both gradients of reference src/ops.c:107-165 without a
-// transposed copy.  TF32 reads the FP32 words as they are; nothing is
-// converted or re-laid-out in global memory.
+// transposed copy.  Nothing is converted or re-laid-out in global memory: TMA
+// rounds FP32 to TF32 while it fills the shared-memory stages.
 //
 // One CTA computes one 128 x 128 output tile over a slice of the reduction:
 //
@@ -470,15 +470,18 @@ struct MapKeyHash {
 
 // 2-D FP32 tensor map over a row-major matrix: `inner` contiguous elements per
 // row, `outer` rows `pitch` elements apart, with the given 128-byte swizzle
-// flavour.  Encoded maps are cached: the training step presents the same
-// buffers every iteration.
+// flavour.  Operand maps use the TFLOAT32 element type, which makes the copy
+// engine round the FP32 words to TF32 (nearest) on their way into shared
+// memory instead of leaving the truncation to the MMA; the output map is plain
+// FP32.  Encoded maps are cached: the training step presents the same buffers
+// every iteration.
 bool tensor_map(const float *base, unsigned long long inner,
                 unsigned long long outer, unsigned long long pitch,
                 unsigned box_inner, unsigned box_outer,
-                CUtensorMapSwizzle swizzle, CUtensorMap *out) {
+                CUtensorMapSwizzle swizzle, bool as_tf32, CUtensorMap *out) {
     static std::unordered_map<MapKey, CUtensorMap, MapKeyHash> cache;
     const MapKey key{base, inner, outer, pitch, box_inner, box_outer,
-                     int(swizzle)};
+                     int(swizzle) * 2 + int(as_tf32)};
     auto found = cache.find(key);
     if (found != cache.end()) {
         *out = found->second;
@@ -493,7 +496,8 @@ bool tensor_map(const float *base, unsigned long long inner,
     const cuuint32_t box[2] = {box_inner, box_outer};
     const cuuint32_t element_strides[2] = {1, 1};
     const CUresult status = encode(
-        out, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 2, const_cast<float *>(base), dims,
+        out, as_tf32 ? CU_TENSOR_MAP_DATA_TYPE_TFLOAT32
+                     : CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 2, const_cast<float *>(base), dims,
         strides, box, element_strides, CU_TENSOR_MAP_INTERLEAVE_NONE,
         swizzle, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
         CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
@@ -553,13 +557,13 @@ int launch_gemm_tc(const TcGemm &g, cudaStream_t stream) {
     const CUtensorMapSwizzle chunks16 = CU_TENSOR_MAP_SWIZZLE_128B;
     const CUtensorMapSwizzle chunks32 = CU_TENSOR_MAP_SWIZZLE_128B_ATOM_32B;
     const bool ok_a = g.a_mn_major
-        ? tensor_map(g.a, g.m, g.k, g.lda, 32, 32, chunks32, &map_a)
-        : tensor_map(g.a, g.k, g.m, g.lda, 32, kTileM, chunks16, &map_a);
+        ? tensor_map(g.a, g.m, g.k, g.lda, 32, 32, chunks32, true, &map_a)
+        : tensor_map(g.a, g.k, g.m, g.lda, 32, kTileM, chunks16, true, &map_a);
     const bool ok_b = g.b_mn_major
-        ? tensor_map(g.b, g.n, g.k, g.ldb, 32, 32, chunks32, &map_b)
-        : tensor_map(g.b, g.k, g.n, g.ldb, 32, kTileN, chunks16, &map_b);
+        ? tensor_map(g.b, g.n, g.k, g.ldb, 32, 32, chunks32, true, &map_b)
+        : tensor_map(g.b, g.k, g.n, g.ldb, 32, kTileN, chunks16, true, &map_b);
     const bool ok_d =
-        tensor_map(g.d, g.n, g.m, g.ldd, 32, kTileM, chunks16, &map_d);
+        tensor_map(g.d, g.n, g.m, g.ldd, 32, kTileM, chunks16, false, &map_d);
     if (!ok_a || !ok_b || !ok_d) {
         return -1;
     }

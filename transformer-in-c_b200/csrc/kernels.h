@@ -89,6 +89,22 @@ void launch_attention_backward(const float *q, const float *k, const float *v,
                                size_t seq, size_t head_dim, float scale,
                                cudaStream_t stream);
 
+// Short sequences with the whole (sample, head) group in shared memory
+// (attention_small.cu).  The launchers return false when the shape is outside
+// what they cover; the tiled kernels above take over then.
+bool attention_small_supported(size_t seq, size_t head_dim);
+bool launch_attention_small_forward(const float *q, const float *k,
+                                    const float *v, float *probabilities,
+                                    float *out, size_t groups, size_t seq,
+                                    size_t head_dim, float scale,
+                                    cudaStream_t stream);
+bool launch_attention_small_backward(const float *q, const float *k,
+                                     const float *v, const float *probabilities,
+                                     const float *out, const float *dout,
+                                     float *dq, float *dk, float *dv,
+                                     size_t groups, size_t seq, size_t head_dim,
+                                     float scale, cudaStream_t stream);
+
 // ---- loss (loss.cu) -------------------------------------------------------
 // row_losses: scratch of `rows` floats.
 void launch_softmax_cross_entropy(const float *logits, const float *targets,

@@ -87,6 +87,9 @@ def load_backend_library():
     lib.vitb200_timer_begin.argtypes = [ctypes.c_void_p]
     lib.vitb200_timer_end.restype = ctypes.c_float
     lib.vitb200_timer_end.argtypes = [ctypes.c_void_p]
+    lib.vitb200_set_gemm_precision.restype = None
+    lib.vitb200_set_gemm_precision.argtypes = [ctypes.c_int]
+    lib.vitb200_tensor_core_status.restype = ctypes.c_int
     lib.vitb200_device_busy_ms.restype = ctypes.c_double
     lib.vitb200_device_busy_ms.argtypes = [ctypes.c_void_p, ctypes.c_int]
     lib.vitb200_profile_enable.restype = None
@@ -138,6 +141,13 @@ class Backend:
         names = ["live_allocations", "mirror_bytes", "device_bytes",
                  "h2d_copies", "h2d_bytes", "d2h_copies", "d2h_bytes", "faults"]
         return {n: int(v.value) for n, v in zip(names, values)}
+
+    def set_gemm_precision(self, precision):
+        """0 auto, 1 FP32 FMA, 2 TF32 tensor cores, -1 start-up default."""
+        self.lib.vitb200_set_gemm_precision(int(precision))
+
+    def tensor_core_status(self):
+        return int(self.lib.vitb200_tensor_core_status())
 
     def device_busy_ms(self, reset=False):
         return float(self.lib.vitb200_device_busy_ms(self.handle, int(reset)))
