@@ -151,6 +151,27 @@ int vitb200_k_softmax_cross_entropy(const float *logits, const float *targets,
                                     float *logits_grad, float *row_losses,
                                     size_t rows, size_t cols, void *stream);
 
+/* No counterpart in the reference.  The same loss and gradient as
+ * vitb200_k_softmax_cross_entropy, for callers that must not trigger a device
+ * allocation: a latency-sensitive serving or training loop in which a
+ * cudaMalloc would stall every stream of the device, a plug-in running under a
+ * host that has handed out its whole memory budget up front, or code that is
+ * not allowed to call the CUDA allocator at all.  The per-row scratch lives in
+ * a fixed 256 KiB array inside the library (each GPU that loads the library
+ * holds it until the process ends), so rows is limited to 65536; more rows
+ * return -2 and print why.  The caller still owns every input and output.
+ * The first call on a device looks the array's address up once
+ * (cudaGetSymbolAddress); make that call outside any stream capture.  All
+ * calls share the one array: two calls whose kernels may overlap on the GPU
+ * (different streams without ordering) race on it.  The array keeps whatever
+ * the previous call left, which is harmless: each call overwrites every entry
+ * it later reads.  Never calls cudaMalloc, cudaFree or an allocating library
+ * routine.  Returns 0 on success, -1 on other errors. */
+int vitb200_k_softmax_cross_entropy_static(
+    const float *logits, const float *targets, const float *class_weights,
+    float label_smoothing, float *loss, float *logits_grad, size_t rows,
+    size_t cols, void *stream);
+
 /* GEMM operand precision selectors for part 2 and VITB200_GEMM. */
 #define VITB200_PRECISION_AUTO 0  /* backend default for the shape          */
 #define VITB200_PRECISION_FP32 1  /* FP32 FMA                                */

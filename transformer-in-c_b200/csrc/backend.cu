@@ -1307,3 +1307,13 @@ extern "C" int vitb200_k_softmax_cross_entropy(
                                  rows, cols, as_stream(stream));
     return 0;
 }
+
+extern "C" int vitb200_k_softmax_cross_entropy_static(
+    const float *logits, const float *targets, const float *class_weights,
+    float label_smoothing, float *loss, float *logits_grad, size_t rows,
+    size_t cols, void *stream) {
+    return launch_softmax_cross_entropy_static(logits, targets, class_weights,
+                                               label_smoothing, loss,
+                                               logits_grad, rows, cols,
+                                               as_stream(stream));
+}

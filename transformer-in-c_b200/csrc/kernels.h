@@ -114,6 +114,17 @@ void launch_softmax_cross_entropy(const float *logits, const float *targets,
                                   size_t rows, size_t cols,
                                   cudaStream_t stream);
 
+// Same computation with the row-loss scratch in a fixed array inside the
+// library (no allocation anywhere); at most kStaticLossMaxRows rows.
+// Returns 0, -2 if rows exceeds the limit, -1 on other errors.
+constexpr size_t kStaticLossMaxRows = 65536;
+int launch_softmax_cross_entropy_static(const float *logits,
+                                        const float *targets,
+                                        const float *class_weights,
+                                        float label_smoothing, float *loss,
+                                        float *logits_grad, size_t rows,
+                                        size_t cols, cudaStream_t stream);
+
 // ---- optimiser (optimizer.cu) --------------------------------------------
 struct ParameterSlice {
     float *value;

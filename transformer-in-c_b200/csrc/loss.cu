@@ -13,6 +13,7 @@
 #include "device_util.cuh"
 
 #include <cfloat>
+#include <cstdio>
 
 namespace vitb200 {
 namespace {
@@ -80,7 +81,61 @@ __global__ void mean_of_rows_kernel(const float *__restrict__ row_losses,
     }
 }
 
+// Row-loss scratch for launch_softmax_cross_entropy_static.  It lives in the
+// library image, so every GPU that loads the library carries these 256 KiB
+// until the process exits.  In host code this name is only a handle for
+// cudaGetSymbolAddress, never a device address.
+static __device__ __align__(256) float g_static_row_losses[kStaticLossMaxRows];
+
+constexpr int kMaxDevices = 64;
+float *g_static_row_losses_address[kMaxDevices] = {};
+
 }  // namespace
+
+int launch_softmax_cross_entropy_static(const float *logits,
+                                        const float *targets,
+                                        const float *class_weights,
+                                        float label_smoothing, float *loss,
+                                        float *logits_grad, size_t rows,
+                                        size_t cols, cudaStream_t stream) {
+    if (rows == 0 || cols == 0) {
+        return -1;
+    }
+    if (rows > kStaticLossMaxRows) {
+        fprintf(stderr,
+                "vitb200: softmax_cross_entropy_static handles at most %zu rows "
+                "(got %zu); use the variant that takes a scratch buffer\n",
+                size_t(kStaticLossMaxRows), rows);
+        return -2;
+    }
+    int device = 0;
+    if (cudaGetDevice(&device) != cudaSuccess || device < 0 ||
+        device >= kMaxDevices) {
+        return -1;
+    }
+    // First call on this device: resolve where the array sits in this
+    // device's memory.  The lookup is done once and must not happen while a
+    // stream is being captured.
+    if (!g_static_row_losses_address[device]) {
+        void *address = nullptr;
+        const cudaError_t status =
+            cudaGetSymbolAddress(&address, g_static_row_losses);
+        if (status != cudaSuccess || !address) {
+            fprintf(stderr, "vitb200: cudaGetSymbolAddress failed: %s\n",
+                    cudaGetErrorString(status));
+            return -1;
+        }
+        g_static_row_losses_address[device] = static_cast<float *>(address);
+    }
+    // Every row the reduction reads is written by the row kernel first, so
+    // nothing left over from the previous call is ever observed and no
+    // clearing is needed.
+    launch_softmax_cross_entropy(logits, targets, class_weights,
+                                 label_smoothing, loss, logits_grad,
+                                 g_static_row_losses_address[device], rows, cols,
+                                 stream);
+    return 0;
+}
 
 void launch_softmax_cross_entropy(const float *logits, const float *targets,
                                   const float *class_weights,
