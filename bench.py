@@ -233,6 +233,12 @@ def main():
 
     host_lib = vh.load_host_library(HOST_LIBRARY)
     backend = vh.Backend()          # raises without the library or a B200
+    if world > 1:
+        # One NCCL communicator of our own for the gradient exchange; its id
+        # travels through torch.distributed.
+        holder = [backend.dp_unique_id() if rank == 0 else None]
+        dist.broadcast_object_list(holder, src=0)
+        backend.dp_init(rank, world, holder[0])
     backend.enable()
     host = vh.VitHost(host_lib, config, batch)
     images, labels = vh.synthetic_batch(batch, config[1], config[2], config[7],
@@ -314,7 +320,9 @@ def main():
         "data": "synthetic",
         "config": {"workload": args.workload, "vit": list(config),
                    "batch_per_gpu": batch, "global_batch": images_per_step,
-                   "parallelism": f"dp{world}",
+                   "parallelism": f"dp{world}" + (
+                       " (batch sharded by sample, NCCL all-reduce of gradients "
+                       "overlapped with backward)" if world > 1 else ""),
                    "l2": "per-step working set (activations + gradients) far "
                          "exceeds the 126 MB L2; no explicit flush"},
         "clocks": clocks.summary,
@@ -336,8 +344,11 @@ def main():
             "value": rate, "unit": "images/s", "cores": 1, "kind": "reference",
             "sample": f"reference CPU train step (single-threaded on Linux), "
                       f"batch {sample_batch}, {sample_steps} steps"}
+    if world > 1:
+        line["dp"] = backend.dp_counters()
     host.close()
     backend.disable()
+    backend.dp_shutdown()
     backend.close()
     if rank == 0:
         print(json.dumps(line), flush=True)

@@ -78,6 +78,25 @@ int vitb200_make_host_coherent(const void *tensor_memory);
 int vitb200_timer_begin(CudaBackend *backend);
 float vitb200_timer_end(CudaBackend *backend);
 
+/* Data parallelism (no counterpart in the reference, which is single-GPU:
+ * README.md:229).  One process per GPU, each with its own backend and its own
+ * shard of the batch.  Rank 0 obtains 128 id bytes and passes them to the
+ * other ranks by any means; every rank then calls vitb200_dp_init
+ * (collective).  From then on the optimiser slot all-reduces the parameter
+ * gradients (NCCL, FP32 sum, overlapped with the backward pass from the third
+ * step on) and applies their mean; the loss each rank reports stays the mean
+ * over its own shard.  NCCL (libnccl.so.2) is loaded at this point, not
+ * before.  0 on success, -1 on failure. */
+int vitb200_dp_unique_id(void *out128);
+int vitb200_dp_init(CudaBackend *backend, int rank, int world,
+                    const void *id128);
+void vitb200_dp_shutdown(CudaBackend *backend);
+void vitb200_dp_counters(CudaBackend *backend,
+                         unsigned long long *all_reduce_calls,
+                         unsigned long long *overlapped_tensors,
+                         unsigned long long *late_tensors,
+                         unsigned long long *bytes);
+
 /* Operand precision of the dense products issued through the op table:
  * VITB200_PRECISION_AUTO (default: TF32 tensor cores for products of at least
  * 16 Mi multiply-adds whose layout TMA can describe, FP32 FMA otherwise),

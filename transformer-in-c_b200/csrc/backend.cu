@@ -11,10 +11,12 @@
 #include "../../include/vitb200_host_abi.h"
 
 #include "coherence.h"
+#include "data_parallel.h"
 #include "gemm.h"
 #include "gemm_tc.h"
 #include "kernels.h"
 
+#include <cfloat>
 #include <climits>
 #include <cmath>
 #include <cstdio>
@@ -86,6 +88,7 @@ struct CudaBackend {
     std::vector<OpStat> op_stats;
     std::vector<PendingOp> pending_ops;
     std::vector<cudaEvent_t> free_events;
+    DataParallel *dp = nullptr;
     void (*set_table)(const vitb200_op_table *) = nullptr;
     void (*set_allocator)(vitb200_allocate_fn, vitb200_release_fn,
                           void *) = nullptr;
@@ -291,6 +294,7 @@ int op_gemm_backward(void *context, vitb200_tensor *left, vitb200_tensor *right,
         gemm_backward(x, w, dy, dx, dw, int(left->rows), int(left->cols),
                       int(right->cols), VITB200_PRECISION_AUTO, backend->stream);
     }
+    dp_gradient_produced(backend->dp, right->grad, dw, numel(right));
     return 0;
 }
 
@@ -381,6 +385,7 @@ int op_bias_add_backward(void *context, const vitb200_tensor *output,
         launch_column_sums(dy, db, output->rows, output->cols, output->cols,
                            backend->stream);
     }
+    dp_gradient_produced(backend->dp, bias_grad->grad, db, numel(bias_grad));
     return 0;
 }
 
@@ -429,6 +434,8 @@ int op_layer_norm_backward(void *context, const vitb200_tensor *input,
         launch_layer_norm_backward(x, g, epsilon, dy, dx, dg, db, input->rows,
                                    input->cols, backend->stream);
     }
+    dp_gradient_produced(backend->dp, gamma_grad->grad, dg, numel(gamma_grad));
+    dp_gradient_produced(backend->dp, beta_grad->grad, db, numel(beta_grad));
     return 0;
 }
 
@@ -694,6 +701,8 @@ int op_token_embedding_backward(void *context, vitb200_tensor *patch_tokens,
         launch_token_embedding_backward(p, c, e, t, batch, pos->rows, tokens->cols,
                                         backend->stream);
     }
+    dp_gradient_produced(backend->dp, cls->grad, c, numel(cls));
+    dp_gradient_produced(backend->dp, pos->grad, e, numel(pos));
     return 0;
 }
 
@@ -846,7 +855,8 @@ int op_clip_gradient_norm(void *context, vitb200_parameter *const *parameters,
     float *scale = scratch<float>(backend, backend->clip_scale, 1);
     OpScope scope(backend, "clip_gradient_norm", 12.0 * table.elements, 0.0);
     launch_gradient_clip_scale(table.device, table.slices, table.blocks,
-                               max_norm, partials, scale, backend->stream);
+                               max_norm, 1.0f, partials, scale,
+                               backend->stream);
     launch_scale_gradients(table.device, table.slices, table.blocks, scale,
                            backend->stream);
     return 0;
@@ -885,19 +895,37 @@ int op_adamw_step_parameters(void *context,
                           beta2, true, &table) != 0) {
         return -1;
     }
+    // Data parallel: finish the gradient exchange first; the summed gradients
+    // are turned into their mean by the scale the update multiplies by.
+    float inverse_world = 1.0f;
+    if (backend->dp && dp_world(backend->dp) > 1) {
+        std::vector<const void *> host_grads(count);
+        std::vector<float *> device_grads(count);
+        std::vector<size_t> counts(count);
+        for (size_t i = 0; i < count; ++i) {
+            host_grads[i] = parameters[i]->value.grad;
+            device_grads[i] =
+                view(backend, parameters[i]->value.grad, Access::ReadWrite);
+            counts[i] = numel(&parameters[i]->value);
+        }
+        inverse_world = dp_before_optimizer(backend->dp, host_grads.data(),
+                                            device_grads.data(), counts.data(),
+                                            count);
+    }
+    const bool needs_scale = max_gradient_norm > 0.0f || inverse_world != 1.0f;
     const float *scale = nullptr;
     float *partials = nullptr, *scale_out = nullptr;
-    if (max_gradient_norm > 0.0f) {
+    if (needs_scale) {
         partials = scratch<float>(backend, backend->norm_partials, table.blocks);
         scale_out = scratch<float>(backend, backend->clip_scale, 1);
     }
     OpScope scope(backend, "adamw_step_parameters",
-                  (max_gradient_norm > 0.0f ? 32.0 : 28.0) * table.elements,
-                  0.0);
-    if (max_gradient_norm > 0.0f) {
-        launch_gradient_clip_scale(table.device, table.slices, table.blocks,
-                                   max_gradient_norm, partials, scale_out,
-                                   backend->stream);
+                  (needs_scale ? 32.0 : 28.0) * table.elements, 0.0);
+    if (needs_scale) {
+        launch_gradient_clip_scale(
+            table.device, table.slices, table.blocks,
+            max_gradient_norm > 0.0f ? max_gradient_norm : FLT_MAX,
+            inverse_world, partials, scale_out, backend->stream);
         scale = scale_out;
     }
     launch_adamw(table.device, table.slices, table.blocks, scale, lr, beta1,
@@ -1023,6 +1051,8 @@ extern "C" void cuda_backend_free(CudaBackend *backend) {
     if (backend->stream) {
         settle_timers(backend);
     }
+    dp_destroy(backend->dp);
+    backend->dp = nullptr;
     free_scratch(backend->rows_scratch);
     free_scratch(backend->norm_partials);
     free_scratch(backend->clip_scale);
@@ -1148,6 +1178,37 @@ extern "C" float vitb200_timer_end(CudaBackend *backend) {
     float ms = -1.0f;
     cudaEventElapsedTime(&ms, backend->timer_begin, backend->timer_end);
     return ms;
+}
+
+extern "C" int vitb200_dp_unique_id(void *out128) {
+    return dp_unique_id(out128);
+}
+
+extern "C" int vitb200_dp_init(CudaBackend *backend, int rank, int world,
+                               const void *id128) {
+    if (!cuda_backend_available(backend) || backend->dp) {
+        return -1;
+    }
+    check(cudaSetDevice(backend->device), "cudaSetDevice");
+    backend->dp = dp_create(rank, world, id128, backend->stream);
+    return backend->dp ? 0 : -1;
+}
+
+extern "C" void vitb200_dp_shutdown(CudaBackend *backend) {
+    if (backend && backend->dp) {
+        settle_timers(backend);
+        dp_destroy(backend->dp);
+        backend->dp = nullptr;
+    }
+}
+
+extern "C" void vitb200_dp_counters(CudaBackend *backend,
+                                    unsigned long long *all_reduce_calls,
+                                    unsigned long long *overlapped_tensors,
+                                    unsigned long long *late_tensors,
+                                    unsigned long long *bytes) {
+    dp_counters(backend ? backend->dp : nullptr, all_reduce_calls,
+                overlapped_tensors, late_tensors, bytes);
 }
 
 extern "C" void vitb200_set_gemm_precision(int precision) {

@@ -1,0 +1,56 @@
+// Data-parallel gradient exchange: one process per GPU, batch sharded by
+// sample, parameters replicated, one sum-all-reduce of every parameter gradient
+// per step (NCCL over NVLink / NVSwitch), overlapped with the backward pass.
+//
+// The host program is unaware of it.  It keeps calling the op table; the
+// backend learns which gradient buffers belong to parameters from the
+// optimiser call (`adamw_step_parameters` lists them), and from the second step
+// on it starts reducing a gradient as soon as the single op that produces it
+// has been enqueued:
+//
+//   compute stream   ... dW GEMM | record event ........ | wait comm | clip + AdamW
+//   comm stream                  | wait event, all-reduce bucket ... |
+//
+// Gradients are summed; the 1/world factor is folded into the clip scale the
+// optimiser kernel already multiplies by, so no extra pass touches them.
+// NCCL is loaded with dlopen when data parallelism is switched on, so single
+// GPU users need no NCCL at all.
+#pragma once
+
+#include <cstddef>
+#include <cuda_runtime.h>
+
+namespace vitb200 {
+
+struct DataParallel;
+
+// Fills 128 bytes with a fresh NCCL unique id (rank 0 calls this and sends the
+// bytes to the other ranks by any means).  0 on success.
+int dp_unique_id(void *out128);
+
+// Collective over all ranks.  Returns nullptr on failure.
+DataParallel *dp_create(int rank, int world, const void *id128,
+                        cudaStream_t compute_stream);
+void dp_destroy(DataParallel *dp);
+int dp_world(const DataParallel *dp);
+
+// Called after the op that wrote `device_grad` (the gradient whose host mirror
+// is `host_grad`, `count` floats) has been enqueued on the compute stream.
+// Does nothing for buffers that are not known parameter gradients.
+void dp_gradient_produced(DataParallel *dp, const void *host_grad,
+                          float *device_grad, size_t count);
+
+// Called by the optimiser slot with the full parameter list, before the norm
+// and update kernels are enqueued: reduces whatever has not been reduced yet,
+// makes the compute stream wait for the exchange, and remembers the list for
+// the next step.  Returns 1/world.
+float dp_before_optimizer(DataParallel *dp, const void *const *host_grads,
+                          float *const *device_grads, const size_t *counts,
+                          size_t parameters);
+
+// Counters for tests and the bench line.
+void dp_counters(const DataParallel *dp, unsigned long long *all_reduce_calls,
+                 unsigned long long *overlapped_tensors,
+                 unsigned long long *late_tensors, unsigned long long *bytes);
+
+}  // namespace vitb200

@@ -140,11 +140,12 @@ struct ParameterSlice {
 };
 constexpr unsigned kSliceBlockElements = 4096;
 
-// partials: scratch of total_blocks floats; scale_out: 1 float.
+// partials: scratch of total_blocks floats; scale_out: 1 float.  The gradients
+// are taken to be sums over 1/inverse_world ranks (1 for a single GPU).
 void launch_gradient_clip_scale(const ParameterSlice *slices, unsigned slices_n,
                                 unsigned total_blocks, float max_norm,
-                                float *partials, float *scale_out,
-                                cudaStream_t stream);
+                                float inverse_world, float *partials,
+                                float *scale_out, cudaStream_t stream);
 void launch_scale_gradients(const ParameterSlice *slices, unsigned slices_n,
                             unsigned total_blocks, const float *scale,
                             cudaStream_t stream);

@@ -85,8 +85,13 @@ squared_norm_partials_kernel(const ParameterSlice *__restrict__ slices,
 
 // scale = norm > max_norm ? max_norm / norm : 1, with the norm summed in
 // double precision in a fixed order (the host sums in double too).
+//
+// With data parallelism the gradients hold the sum over `1 / inverse_world`
+// ranks; the norm of their mean is the summed norm times inverse_world, and the
+// same factor is folded into the scale so the optimiser sees the mean.
 __global__ void clip_scale_kernel(const float *__restrict__ partials,
                                   unsigned count, float max_norm,
+                                  float inverse_world,
                                   float *__restrict__ scale_out) {
     __shared__ double scratch[32];
     double sum = 0.0;
@@ -105,10 +110,11 @@ __global__ void clip_scale_kernel(const float *__restrict__ partials,
         for (unsigned w = 0; w < (blockDim.x >> 5); ++w) {
             total += scratch[w];
         }
-        const double norm = sqrt(total);
-        scale_out[0] = (norm <= double(max_norm) || norm == 0.0)
+        const double norm = sqrt(total) * double(inverse_world);
+        const float clip = (norm <= double(max_norm) || norm == 0.0)
             ? 1.0f
             : float(double(max_norm) / norm);
+        scale_out[0] = inverse_world == 1.0f ? clip : clip * inverse_world;
     }
 }
 
@@ -194,12 +200,12 @@ __global__ void adamw_single_kernel(float *__restrict__ value,
 
 void launch_gradient_clip_scale(const ParameterSlice *slices, unsigned slices_n,
                                 unsigned total_blocks, float max_norm,
-                                float *partials, float *scale_out,
-                                cudaStream_t stream) {
+                                float inverse_world, float *partials,
+                                float *scale_out, cudaStream_t stream) {
     squared_norm_partials_kernel<<<total_blocks, kThreads, 0, stream>>>(
         slices, slices_n, partials);
     clip_scale_kernel<<<1, 1024, 0, stream>>>(partials, total_blocks, max_norm,
-                                              scale_out);
+                                              inverse_world, scale_out);
     g_kernel_launches += 2;
 }
 

@@ -87,6 +87,16 @@ def load_backend_library():
     lib.vitb200_timer_begin.argtypes = [ctypes.c_void_p]
     lib.vitb200_timer_end.restype = ctypes.c_float
     lib.vitb200_timer_end.argtypes = [ctypes.c_void_p]
+    lib.vitb200_dp_unique_id.restype = ctypes.c_int
+    lib.vitb200_dp_unique_id.argtypes = [ctypes.c_void_p]
+    lib.vitb200_dp_init.restype = ctypes.c_int
+    lib.vitb200_dp_init.argtypes = [ctypes.c_void_p, ctypes.c_int, ctypes.c_int,
+                                    ctypes.c_void_p]
+    lib.vitb200_dp_shutdown.restype = None
+    lib.vitb200_dp_shutdown.argtypes = [ctypes.c_void_p]
+    lib.vitb200_dp_counters.restype = None
+    lib.vitb200_dp_counters.argtypes = [ctypes.c_void_p] + \
+        [ctypes.POINTER(ctypes.c_ulonglong)] * 4
     lib.vitb200_set_gemm_precision.restype = None
     lib.vitb200_set_gemm_precision.argtypes = [ctypes.c_int]
     lib.vitb200_tensor_core_status.restype = ctypes.c_int
@@ -140,6 +150,29 @@ class Backend:
         self.lib.vitb200_memory_counters(*[ctypes.byref(v) for v in values])
         names = ["live_allocations", "mirror_bytes", "device_bytes",
                  "h2d_copies", "h2d_bytes", "d2h_copies", "d2h_bytes", "faults"]
+        return {n: int(v.value) for n, v in zip(names, values)}
+
+    def dp_unique_id(self):
+        """128 opaque bytes from rank 0, to be handed to every rank's dp_init."""
+        buffer = ctypes.create_string_buffer(128)
+        if self.lib.vitb200_dp_unique_id(buffer) != 0:
+            raise RuntimeError("NCCL is not available (libnccl.so.2 not found)")
+        return buffer.raw
+
+    def dp_init(self, rank, world, unique_id):
+        """Collective: joins this backend to a data-parallel group."""
+        buffer = ctypes.create_string_buffer(bytes(unique_id), 128)
+        if self.lib.vitb200_dp_init(self.handle, rank, world, buffer) != 0:
+            raise RuntimeError("vitb200_dp_init failed")
+
+    def dp_shutdown(self):
+        self.lib.vitb200_dp_shutdown(self.handle)
+
+    def dp_counters(self):
+        values = [ctypes.c_ulonglong() for _ in range(4)]
+        self.lib.vitb200_dp_counters(self.handle,
+                                     *[ctypes.byref(v) for v in values])
+        names = ["all_reduce_calls", "overlapped_tensors", "late_tensors", "bytes"]
         return {n: int(v.value) for n, v in zip(names, values)}
 
     def set_gemm_precision(self, precision):
