@@ -187,7 +187,7 @@ attention_backward_query_kernel(const float *__restrict__ k,
                                 const float *__restrict__ dout,
                                 const float *__restrict__ row_dots,
                                 float *__restrict__ dq, int seq, int head_dim,
-                                float scale) {
+                                float scale, bool add_q) {
     extern __shared__ float shared[];
     const int pitch = head_dim + 1;
     float *do_tile = shared;
@@ -245,7 +245,8 @@ attention_backward_query_kernel(const float *__restrict__ k,
         for (int i = 0; i < NI; ++i) {
             const int d = sub + kLanesPerRow * i;
             if (d < head_dim) {
-                dq[base + size_t(row) * head_dim + d] += acc[i];
+                float *target = dq + base + size_t(row) * head_dim + d;
+                *target = (add_q ? *target : 0.0f) + acc[i];
             }
         }
     }
@@ -259,7 +260,8 @@ attention_backward_key_kernel(const float *__restrict__ q,
                               const float *__restrict__ dout,
                               const float *__restrict__ row_dots,
                               float *__restrict__ dk, float *__restrict__ dv,
-                              int seq, int head_dim, float scale) {
+                              int seq, int head_dim, float scale, bool add_k,
+                              bool add_v) {
     extern __shared__ float shared[];
     const int pitch = head_dim + 1;
     float *v_tile = shared;                     // this block's keys
@@ -333,8 +335,10 @@ attention_backward_key_kernel(const float *__restrict__ q,
         for (int i = 0; i < NI; ++i) {
             const int d = sub + kLanesPerRow * i;
             if (d < head_dim) {
-                dk[base + size_t(key) * head_dim + d] += acc_k[i];
-                dv[base + size_t(key) * head_dim + d] += acc_v[i];
+                float *target_k = dk + base + size_t(key) * head_dim + d;
+                float *target_v = dv + base + size_t(key) * head_dim + d;
+                *target_k = (add_k ? *target_k : 0.0f) + acc_k[i];
+                *target_v = (add_v ? *target_v : 0.0f) + acc_v[i];
             }
         }
     }
@@ -387,11 +391,12 @@ void launch_attention_backward(const float *q, const float *k, const float *v,
                                const float *dout, float *dq, float *dk,
                                float *dv, float *row_dots, size_t groups,
                                size_t seq, size_t head_dim, float scale,
+                               bool add_q, bool add_k, bool add_v,
                                cudaStream_t stream) {
     if (attention_small_supported(seq, head_dim) &&
         launch_attention_small_backward(q, k, v, probabilities, out, dout, dq,
                                         dk, dv, groups, seq, head_dim, scale,
-                                        stream)) {
+                                        add_q, add_k, add_v, stream)) {
         return;
     }
     const size_t rows = groups * seq;
@@ -408,11 +413,11 @@ void launch_attention_backward(const float *q, const float *k, const float *v,
     allow_shared(attention_backward_query_kernel<NI>, query_bytes);            \
     attention_backward_query_kernel<NI><<<grid, kThreads, query_bytes, stream>>>(\
         k, v, probabilities, dout, row_dots, dq, int(seq), int(head_dim),      \
-        scale);                                                                \
+        scale, add_q);                                                              \
     allow_shared(attention_backward_key_kernel<NI>, key_bytes);                \
     attention_backward_key_kernel<NI><<<grid, kThreads, key_bytes, stream>>>(  \
         q, v, probabilities, dout, row_dots, dk, dv, int(seq), int(head_dim),  \
-        scale)
+        scale, add_k, add_v)
     VITB200_DISPATCH_NI(head_dim, CALL);
 #undef CALL
     g_kernel_launches += 3;

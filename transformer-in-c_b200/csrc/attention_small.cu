@@ -112,7 +112,7 @@ __global__ void attention_small_backward_kernel(
     const float *__restrict__ v, const float *__restrict__ p,
     const float *__restrict__ out, const float *__restrict__ dout,
     float *__restrict__ dq, float *__restrict__ dk, float *__restrict__ dv,
-    int seq, float scale) {
+    int seq, float scale, bool add_q, bool add_k, bool add_v) {
     extern __shared__ __align__(16) float shared[];
     const int pitch = seq | 1;
     float *q_tile = shared;
@@ -161,7 +161,7 @@ __global__ void attention_small_backward_kernel(
 #pragma unroll
         for (int d = 0; d < HD; d += 4) {
             float4 *target = reinterpret_cast<float4 *>(dv + base + row * HD + d);
-            float4 t = *target;
+            float4 t = add_v ? *target : make_float4(0.f, 0.f, 0.f, 0.f);
             t.x += acc[d]; t.y += acc[d + 1]; t.z += acc[d + 2]; t.w += acc[d + 3];
             *target = t;
         }
@@ -194,7 +194,7 @@ __global__ void attention_small_backward_kernel(
 #pragma unroll
         for (int d = 0; d < HD; d += 4) {
             float4 *target = reinterpret_cast<float4 *>(dq + base + row * HD + d);
-            float4 t = *target;
+            float4 t = add_q ? *target : make_float4(0.f, 0.f, 0.f, 0.f);
             t.x += acc[d]; t.y += acc[d + 1]; t.z += acc[d + 2]; t.w += acc[d + 3];
             *target = t;
         }
@@ -217,7 +217,7 @@ __global__ void attention_small_backward_kernel(
 #pragma unroll
         for (int d = 0; d < HD; d += 4) {
             float4 *target = reinterpret_cast<float4 *>(dk + base + row * HD + d);
-            float4 t = *target;
+            float4 t = add_k ? *target : make_float4(0.f, 0.f, 0.f, 0.f);
             t.x += acc[d]; t.y += acc[d + 1]; t.z += acc[d + 2]; t.w += acc[d + 3];
             *target = t;
         }
@@ -278,7 +278,8 @@ bool launch_attention_small_backward(const float *q, const float *k,
                                      const float *out, const float *dout,
                                      float *dq, float *dk, float *dv,
                                      size_t groups, size_t seq, size_t head_dim,
-                                     float scale, cudaStream_t stream) {
+                                     float scale, bool add_q, bool add_k,
+                                     bool add_v, cudaStream_t stream) {
     const unsigned threads = unsigned((seq + 31) / 32 * 32);
     const size_t bytes = (4 * seq * head_dim + seq * (seq | 1)) * sizeof(float);
     bool launched = false;
@@ -287,7 +288,7 @@ bool launch_attention_small_backward(const float *q, const float *k,
         attention_small_backward_kernel<HD>                                    \
             <<<unsigned(groups), threads, bytes, stream>>>(                    \
                 q, k, v, probabilities, out, dout, dq, dk, dv, int(seq),       \
-                scale);                                                        \
+                scale, add_q, add_k, add_v);                                                      \
         launched = true;                                                       \
     }
     VITB200_DISPATCH_HD(head_dim, CALL)

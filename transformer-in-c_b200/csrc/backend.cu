@@ -252,6 +252,15 @@ float *view(CudaBackend *backend, const void *pointer, Access access) {
     return device_view(pointer, access, backend->stream);
 }
 
+// View of a buffer about to be added into; *add comes back false when the
+// buffer is a pending zero fill, in which case the kernel must store.
+float *accumulate_view(CudaBackend *backend, const void *pointer, bool *add) {
+    bool was_zero = false;
+    float *device = device_view_accumulate(pointer, backend->stream, &was_zero);
+    *add = !was_zero;
+    return device;
+}
+
 // ---------------------------------------------------------------- op slots
 
 int op_gemm(void *context, const vitb200_tensor *left,
@@ -286,13 +295,15 @@ int op_gemm_backward(void *context, vitb200_tensor *left, vitb200_tensor *right,
     const float *x = view(backend, left->data, Access::Read);
     const float *w = view(backend, right->data, Access::Read);
     const float *dy = view(backend, output->grad, Access::Read);
-    float *dx = view(backend, left->grad, Access::ReadWrite);
+    bool dx_add = true;
+    float *dx = accumulate_view(backend, left->grad, &dx_add);
     float *dw = view(backend, right->grad, Access::ReadWrite);
     {
         OpScope scope(backend, "gemm_backward", 4.0 * (double(output->rows) * output->cols + 3.0 * double(right->rows) * right->cols + 3.0 * double(left->rows) * left->cols),
                       4.0 * double(left->rows) * left->cols * right->cols);
         gemm_backward(x, w, dy, dx, dw, int(left->rows), int(left->cols),
-                      int(right->cols), VITB200_PRECISION_AUTO, backend->stream);
+                      int(right->cols), VITB200_PRECISION_AUTO, dx_add,
+                      backend->stream);
     }
     dp_gradient_produced(backend->dp, right->grad, dw, numel(right));
     return 0;
@@ -323,13 +334,15 @@ int op_residual_backward(void *context, vitb200_tensor *left,
         left->grad == right->grad) {
         return -1;
     }
-    float *a = view(backend, left->grad, Access::ReadWrite);
-    float *b = view(backend, right->grad, Access::ReadWrite);
+    bool add_a = true, add_b = true;
     const float *g = view(backend, output->grad, Access::Read);
+    float *a = accumulate_view(backend, left->grad, &add_a);
+    float *b = accumulate_view(backend, right->grad, &add_b);
     {
         OpScope scope(backend, "residual_backward", 20.0 * double(numel(output)),
                       0.0);
-        launch_accumulate2(a, b, g, numel(output), backend->stream);
+        launch_accumulate2(a, b, g, numel(output), add_a, add_b,
+                           backend->stream);
     }
     return 0;
 }
@@ -341,12 +354,13 @@ int op_accumulate_gradient(void *context, vitb200_tensor *destination,
         destination->grad == source->grad) {
         return -1;
     }
-    float *dst = view(backend, destination->grad, Access::ReadWrite);
+    bool add = true;
     const float *src = view(backend, source->grad, Access::Read);
+    float *dst = accumulate_view(backend, destination->grad, &add);
     {
         OpScope scope(backend, "accumulate_gradient", 12.0 * double(numel(destination)),
                       0.0);
-        launch_accumulate(dst, src, numel(destination), backend->stream);
+        launch_accumulate(dst, src, numel(destination), add, backend->stream);
     }
     return 0;
 }
@@ -425,14 +439,15 @@ int op_layer_norm_backward(void *context, const vitb200_tensor *input,
     const float *x = view(backend, input->data, Access::Read);
     const float *g = view(backend, gamma->data, Access::Read);
     const float *dy = view(backend, output->grad, Access::Read);
-    float *dx = view(backend, input_grad->grad, Access::ReadWrite);
+    bool add_dx = true;
+    float *dx = accumulate_view(backend, input_grad->grad, &add_dx);
     float *dg = view(backend, gamma_grad->grad, Access::ReadWrite);
     float *db = view(backend, beta_grad->grad, Access::ReadWrite);
     {
         OpScope scope(backend, "layer_norm_backward", 16.0 * double(numel(input)),
                       0.0);
         launch_layer_norm_backward(x, g, epsilon, dy, dx, dg, db, input->rows,
-                                   input->cols, backend->stream);
+                                   input->cols, add_dx, backend->stream);
     }
     dp_gradient_produced(backend->dp, gamma_grad->grad, dg, numel(gamma_grad));
     dp_gradient_produced(backend->dp, beta_grad->grad, db, numel(beta_grad));
@@ -463,11 +478,12 @@ int op_gelu_backward(void *context, const vitb200_tensor *input,
     }
     const float *x = view(backend, input->data, Access::Read);
     const float *dy = view(backend, output->grad, Access::Read);
-    float *dx = view(backend, input->grad, Access::ReadWrite);
+    bool add = true;
+    float *dx = accumulate_view(backend, input->grad, &add);
     {
         OpScope scope(backend, "gelu_backward", 16.0 * double(numel(input)),
                       0.0);
-        launch_gelu_backward(x, dy, dx, numel(input), backend->stream);
+        launch_gelu_backward(x, dy, dx, numel(input), add, backend->stream);
     }
     return 0;
 }
@@ -501,7 +517,8 @@ int op_split_heads_backward(void *context, vitb200_tensor *projected,
     if (!ours({projected->grad, query->grad, key->grad, value->grad})) {
         return -1;
     }
-    float *p = view(backend, projected->grad, Access::ReadWrite);
+    bool add = true;
+    float *p = accumulate_view(backend, projected->grad, &add);
     const float *q = view(backend, query->grad, Access::Read);
     const float *k = view(backend, key->grad, Access::Read);
     const float *v = view(backend, value->grad, Access::Read);
@@ -509,7 +526,7 @@ int op_split_heads_backward(void *context, vitb200_tensor *projected,
         OpScope scope(backend, "split_heads_backward", 12.0 * double(numel(projected)),
                       0.0);
         launch_split_heads_backward(p, q, k, v, batch, seq, d_model, heads,
-                                    backend->stream);
+                                    add, backend->stream);
     }
     return 0;
 }
@@ -538,12 +555,13 @@ int op_merge_heads_backward(void *context, vitb200_tensor *attended,
     if (!ours({attended->grad, merged->grad})) {
         return -1;
     }
-    float *a = view(backend, attended->grad, Access::ReadWrite);
+    bool add = true;
+    float *a = accumulate_view(backend, attended->grad, &add);
     const float *m = view(backend, merged->grad, Access::Read);
     {
         OpScope scope(backend, "merge_heads_backward", 12.0 * double(numel(merged)),
                       0.0);
-        launch_merge_heads_backward(a, m, batch, seq, d_model, heads,
+        launch_merge_heads_backward(a, m, batch, seq, d_model, heads, add,
                                     backend->stream);
     }
     return 0;
@@ -600,14 +618,16 @@ int op_attention_backward(void *context, const vitb200_tensor *query,
     const float *p = view(backend, probabilities->data, Access::Read);
     const float *o = view(backend, output->data, Access::Read);
     const float *go = view(backend, output->grad, Access::Read);
-    float *dq = view(backend, query_grad->grad, Access::ReadWrite);
-    float *dk = view(backend, key_grad->grad, Access::ReadWrite);
-    float *dv = view(backend, value_grad->grad, Access::ReadWrite);
+    bool add_q = true, add_k = true, add_v = true;
+    float *dq = accumulate_view(backend, query_grad->grad, &add_q);
+    float *dk = accumulate_view(backend, key_grad->grad, &add_k);
+    float *dv = accumulate_view(backend, value_grad->grad, &add_v);
     {
         OpScope scope(backend, "multi_head_attention_backward", 4.0 * (11.0 * double(numel(query)) + double(numel(probabilities))),
                       8.0 * double(numel(probabilities)) * double(query->cols));
         launch_attention_backward(q, k, v, p, o, go, dq, dk, dv, dots, groups, seq,
-                                  query->cols, scale, backend->stream);
+                                  query->cols, scale, add_q, add_k, add_v,
+                                  backend->stream);
     }
     return 0;
 }
@@ -617,10 +637,10 @@ int op_zero_gradient(void *context, vitb200_tensor *tensor) {
     if (!ours({tensor->grad})) {
         return -1;
     }
-    float *g = view(backend, tensor->grad, Access::Overwrite);
-    OpScope scope(backend, "zero_gradient", 4.0 * double(numel(tensor)), 0.0);
-    check(cudaMemsetAsync(g, 0, numel(tensor) * sizeof(float), backend->stream),
-          "cudaMemsetAsync");
+    // Nothing is written here: the buffer is declared zero, the first kernel
+    // that adds into it stores instead, and a fill is issued only if somebody
+    // reads the zeros first.
+    coherent_mark_zero(tensor->grad, backend->stream);
     return 0;
 }
 
@@ -632,16 +652,8 @@ int op_zero_gradients(void *context, vitb200_tensor *const *tensors,
             return -1;
         }
     }
-    double bytes = 0.0;
     for (size_t i = 0; i < count; ++i) {
-        bytes += 4.0 * double(numel(tensors[i]));
-    }
-    OpScope scope(backend, "zero_gradients", bytes, 0.0);
-    for (size_t i = 0; i < count; ++i) {
-        float *g = view(backend, tensors[i]->grad, Access::Overwrite);
-        check(cudaMemsetAsync(g, 0, numel(tensors[i]) * sizeof(float),
-                              backend->stream),
-              "cudaMemsetAsync");
+        coherent_mark_zero(tensors[i]->grad, backend->stream);
     }
     return 0;
 }
@@ -691,7 +703,8 @@ int op_token_embedding_backward(void *context, vitb200_tensor *patch_tokens,
     if (!ours({patch_tokens->grad, cls->grad, pos->grad, tokens->grad})) {
         return -1;
     }
-    float *p = view(backend, patch_tokens->grad, Access::ReadWrite);
+    bool add_patch = true;
+    float *p = accumulate_view(backend, patch_tokens->grad, &add_patch);
     float *c = view(backend, cls->grad, Access::ReadWrite);
     float *e = view(backend, pos->grad, Access::ReadWrite);
     const float *t = view(backend, tokens->grad, Access::Read);
@@ -699,7 +712,7 @@ int op_token_embedding_backward(void *context, vitb200_tensor *patch_tokens,
         OpScope scope(backend, "token_embedding_backward", 12.0 * double(numel(tokens)),
                       0.0);
         launch_token_embedding_backward(p, c, e, t, batch, pos->rows, tokens->cols,
-                                        backend->stream);
+                                        add_patch, backend->stream);
     }
     dp_gradient_produced(backend->dp, cls->grad, c, numel(cls));
     dp_gradient_produced(backend->dp, pos->grad, e, numel(pos));
@@ -1287,7 +1300,7 @@ extern "C" int vitb200_k_gemm_backward(const float *x, const float *w,
         return -1;
     }
     return gemm_backward(x, w, dy, dx, dw, int(m), int(k), int(n), precision,
-                         as_stream(stream));
+                         true, as_stream(stream));
 }
 
 extern "C" int vitb200_k_bias_add(const float *in, const float *bias,
@@ -1317,7 +1330,7 @@ extern "C" int vitb200_k_layer_norm_backward(const float *x, const float *gamma,
                                              float *dbeta, size_t rows,
                                              size_t cols, void *stream) {
     launch_layer_norm_backward(x, gamma, epsilon, dy, dx, dgamma, dbeta, rows,
-                               cols, as_stream(stream));
+                               cols, true, as_stream(stream));
     return 0;
 }
 
@@ -1329,7 +1342,7 @@ extern "C" int vitb200_k_gelu(const float *in, float *out, size_t n,
 
 extern "C" int vitb200_k_gelu_backward(const float *x, const float *dy,
                                        float *dx, size_t n, void *stream) {
-    launch_gelu_backward(x, dy, dx, n, as_stream(stream));
+    launch_gelu_backward(x, dy, dx, n, true, as_stream(stream));
     return 0;
 }
 
@@ -1354,8 +1367,8 @@ extern "C" int vitb200_k_attention_backward(
         return -1;
     }
     launch_attention_backward(q, k, v, probabilities, out, dout, dq, dk, dv,
-                              row_dots, groups, seq, head_dim, scale,
-                              as_stream(stream));
+                              row_dots, groups, seq, head_dim, scale, true,
+                              true, true, as_stream(stream));
     return 0;
 }
 

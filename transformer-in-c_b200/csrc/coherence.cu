@@ -23,6 +23,7 @@ struct Region {
     size_t mapped = 0;        // page-rounded size of the mapping
     float *device = nullptr;  // created on first device use
     Owner owner = Owner::Host;
+    bool zero_pending = false;  // device contents are an unmaterialised zero fill
 };
 
 // Process-global on purpose: the host keeps the release function inside every
@@ -87,6 +88,15 @@ void ensure_device_buffer(Region &region) {
     }
 }
 
+void materialise_zero(Region &region, cudaStream_t stream) {
+    if (region.zero_pending) {
+        check(cudaMemsetAsync(region.device, 0, region.bytes, stream),
+              "cudaMemsetAsync");
+        region.zero_pending = false;
+        g_stats.zero_fills_materialised += 1;
+    }
+}
+
 // Brings the mirror up to date and hands ownership back to the host side.
 // `for_write` selects HOST (exclusive) over SHARED (both valid).
 void serve_host_access(Region &region, bool for_write) {
@@ -94,6 +104,7 @@ void serve_host_access(Region &region, bool for_write) {
         if (g_flush) {
             g_flush();
         }
+        materialise_zero(region, g_stream);
         check(cudaStreamSynchronize(g_stream), "cudaStreamSynchronize");
         protect(region, PROT_READ | PROT_WRITE);
         check(cudaMemcpy(region.mirror, region.device, region.bytes,
@@ -223,6 +234,14 @@ float *device_view(const void *host_pointer, Access access,
         return nullptr;
     }
     ensure_device_buffer(*region);
+    if (region->zero_pending) {
+        if (access == Access::Overwrite) {
+            region->zero_pending = false;
+            g_stats.zero_fills_elided += 1;
+        } else {
+            materialise_zero(*region, stream);
+        }
+    }
     if (region->owner == Owner::Host && access != Access::Overwrite) {
         // Launch everything recorded so far first: the upload must not
         // overtake kernels that were recorded against the old contents.
@@ -248,6 +267,39 @@ float *device_view(const void *host_pointer, Access access,
         }
     }
     return region->device;
+}
+
+bool coherent_mark_zero(const void *host_pointer, cudaStream_t stream) {
+    (void)stream;
+    Region *region = host_pointer ? find_base(host_pointer) : nullptr;
+    if (!region) {
+        return false;
+    }
+    ensure_device_buffer(*region);
+    if (region->owner != Owner::Device) {
+        protect(*region, PROT_NONE);
+        region->owner = Owner::Device;
+        if (region->mapped >= kDropPagesThreshold) {
+            madvise(region->mirror, region->mapped, MADV_DONTNEED);
+        }
+    }
+    region->zero_pending = true;
+    return true;
+}
+
+float *device_view_accumulate(const void *host_pointer, cudaStream_t stream,
+                              bool *was_zero) {
+    Region *region = host_pointer ? find_base(host_pointer) : nullptr;
+    *was_zero = false;
+    if (!region) {
+        return nullptr;
+    }
+    if (region->zero_pending) {
+        // Same transition as a full overwrite.
+        *was_zero = true;
+        return device_view(host_pointer, Access::Overwrite, stream);
+    }
+    return device_view(host_pointer, Access::ReadWrite, stream);
 }
 
 int coherent_make_host_owned(const void *host_pointer) {

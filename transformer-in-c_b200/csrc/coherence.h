@@ -34,6 +34,8 @@ struct CoherenceStats {
     size_t device_to_host_copies;
     size_t device_to_host_bytes;
     size_t faults_served;
+    size_t zero_fills_elided;
+    size_t zero_fills_materialised;
 };
 
 // Allocator pair installed through tensor_set_allocator
@@ -49,6 +51,20 @@ bool coherent_owns(const void *host_pointer);
 // Device pointer for a mirror base address, after making the device copy valid
 // for `access` on `stream`.  Returns nullptr for memory we did not allocate.
 float *device_view(const void *host_pointer, Access access, cudaStream_t stream);
+
+// Declares the buffer to be all zeros without touching memory ("zero
+// pending").  The fill is materialised only if somebody reads the buffer
+// before overwriting it; an accumulating kernel that asks through
+// device_view_accumulate is told to store instead of add.  Returns false for
+// memory we did not allocate.
+bool coherent_mark_zero(const void *host_pointer, cudaStream_t stream);
+
+// Device pointer for a buffer the caller is about to add into.  *was_zero is
+// set when the buffer's current contents are a pending zero fill, in which
+// case the caller must overwrite every element (value = 0 + increment) and the
+// pending fill is dropped.
+float *device_view_accumulate(const void *host_pointer, cudaStream_t stream,
+                              bool *was_zero);
 
 // Makes the mirror readable and writable by the host again (copying back if
 // the device holds the current contents).  Needed before handing a mirror to a

@@ -28,41 +28,44 @@ __global__ void add_kernel(const float *__restrict__ a,
     }
 }
 
+// add = false turns "+=" into "=" (the destination is known to be zero).
 __global__ void accumulate_kernel(float *__restrict__ dst,
-                                  const float *__restrict__ src, size_t n) {
+                                  const float *__restrict__ src, size_t n,
+                                  bool add) {
     const size_t vectors = n / 4;
     float4 *d4 = reinterpret_cast<float4 *>(dst);
     const float4 *s4 = reinterpret_cast<const float4 *>(src);
     for (size_t i = global_thread(); i < vectors; i += grid_threads()) {
-        float4 d = d4[i];
+        float4 d = add ? d4[i] : make_float4(0.f, 0.f, 0.f, 0.f);
         const float4 s = ld_stream(s4 + i);
         d.x += s.x; d.y += s.y; d.z += s.z; d.w += s.w;
         d4[i] = d;
     }
     for (size_t i = vectors * 4 + global_thread(); i < n; i += grid_threads()) {
-        dst[i] += src[i];
+        dst[i] = (add ? dst[i] : 0.0f) + src[i];
     }
 }
 
 __global__ void accumulate2_kernel(float *__restrict__ dst_a,
                                    float *__restrict__ dst_b,
-                                   const float *__restrict__ src, size_t n) {
+                                   const float *__restrict__ src, size_t n,
+                                   bool add_a, bool add_b) {
     const size_t vectors = n / 4;
     float4 *a4 = reinterpret_cast<float4 *>(dst_a);
     float4 *b4 = reinterpret_cast<float4 *>(dst_b);
     const float4 *s4 = reinterpret_cast<const float4 *>(src);
     for (size_t i = global_thread(); i < vectors; i += grid_threads()) {
         const float4 s = ld_stream(s4 + i);
-        float4 a = a4[i];
-        float4 b = b4[i];
+        float4 a = add_a ? a4[i] : make_float4(0.f, 0.f, 0.f, 0.f);
+        float4 b = add_b ? b4[i] : make_float4(0.f, 0.f, 0.f, 0.f);
         a.x += s.x; a.y += s.y; a.z += s.z; a.w += s.w;
         b.x += s.x; b.y += s.y; b.z += s.z; b.w += s.w;
         a4[i] = a;
         b4[i] = b;
     }
     for (size_t i = vectors * 4 + global_thread(); i < n; i += grid_threads()) {
-        dst_a[i] += src[i];
-        dst_b[i] += src[i];
+        dst_a[i] = (add_a ? dst_a[i] : 0.0f) + src[i];
+        dst_b[i] = (add_b ? dst_b[i] : 0.0f) + src[i];
     }
 }
 
@@ -108,7 +111,8 @@ __global__ void gelu_kernel(const float *__restrict__ in,
 
 __global__ void gelu_backward_kernel(const float *__restrict__ x,
                                      const float *__restrict__ dy,
-                                     float *__restrict__ dx, size_t n) {
+                                     float *__restrict__ dx, size_t n,
+                                     bool add) {
     const size_t vectors = n / 4;
     const float4 *x4 = reinterpret_cast<const float4 *>(x);
     const float4 *g4 = reinterpret_cast<const float4 *>(dy);
@@ -116,7 +120,7 @@ __global__ void gelu_backward_kernel(const float *__restrict__ x,
     for (size_t i = global_thread(); i < vectors; i += grid_threads()) {
         const float4 v = ld_stream(x4 + i);
         const float4 g = ld_stream(g4 + i);
-        float4 d = d4[i];
+        float4 d = add ? d4[i] : make_float4(0.f, 0.f, 0.f, 0.f);
         d.x += g.x * gelu_slope(v.x);
         d.y += g.y * gelu_slope(v.y);
         d.z += g.z * gelu_slope(v.z);
@@ -124,7 +128,7 @@ __global__ void gelu_backward_kernel(const float *__restrict__ x,
         d4[i] = d;
     }
     for (size_t i = vectors * 4 + global_thread(); i < n; i += grid_threads()) {
-        dx[i] += dy[i] * gelu_slope(x[i]);
+        dx[i] = (add ? dx[i] : 0.0f) + dy[i] * gelu_slope(x[i]);
     }
 }
 
@@ -156,17 +160,17 @@ void launch_add(const float *a, const float *b, float *out, size_t n,
     ++g_kernel_launches;
 }
 
-void launch_accumulate(float *dst, const float *src, size_t n,
+void launch_accumulate(float *dst, const float *src, size_t n, bool add,
                        cudaStream_t stream) {
     accumulate_kernel<<<stream_grid(n / 4 + 1), kStreamThreads, 0, stream>>>(
-        dst, src, n);
+        dst, src, n, add);
     ++g_kernel_launches;
 }
 
 void launch_accumulate2(float *dst_a, float *dst_b, const float *src, size_t n,
-                        cudaStream_t stream) {
+                        bool add_a, bool add_b, cudaStream_t stream) {
     accumulate2_kernel<<<stream_grid(n / 4 + 1), kStreamThreads, 0, stream>>>(
-        dst_a, dst_b, src, n);
+        dst_a, dst_b, src, n, add_a, add_b);
     ++g_kernel_launches;
 }
 
@@ -189,9 +193,9 @@ void launch_gelu(const float *in, float *out, size_t n, cudaStream_t stream) {
 }
 
 void launch_gelu_backward(const float *x, const float *dy, float *dx, size_t n,
-                          cudaStream_t stream) {
+                          bool add, cudaStream_t stream) {
     gelu_backward_kernel<<<stream_grid(n / 4 + 1), kStreamThreads, 0, stream>>>(
-        x, dy, dx, n);
+        x, dy, dx, n, add);
     ++g_kernel_launches;
 }
 

@@ -101,10 +101,10 @@ int gemm_forward(const float *x, const float *w, float *y, int m, int k, int n,
 }
 
 int gemm_backward(const float *x, const float *w, const float *dy, float *dx,
-                  float *dw, int m, int k, int n, int precision,
+                  float *dw, int m, int k, int n, int precision, bool dx_add,
                   cudaStream_t stream) {
     // dX[m,k] += dY[m,n] W^T: both operands have the reduction (n) contiguous.
-    TcGemm gx = {dy, w, dx, nullptr, m, k, n, n, n, k, false, false, true};
+    TcGemm gx = {dy, w, dx, nullptr, m, k, n, n, n, k, false, false, dx_add};
     if (run(gx, precision, stream) != 0) {
         return -1;
     }

@@ -13,8 +13,9 @@ namespace vitb200 {
 // the requested precision cannot serve the shape.
 int gemm_forward(const float *x, const float *w, float *y, int m, int k, int n,
                  int precision, cudaStream_t stream);
+// dx_add = false stores dX instead of adding to it (dX known to be zero).
 int gemm_backward(const float *x, const float *w, const float *dy, float *dx,
-                  float *dw, int m, int k, int n, int precision,
+                  float *dw, int m, int k, int n, int precision, bool dx_add,
                   cudaStream_t stream);
 
 // Overrides what VITB200_PRECISION_AUTO means (and the VITB200_GEMM

@@ -14,15 +14,19 @@ extern unsigned long long g_kernel_launches;
 // ---- elementwise (elementwise.cu) ----------------------------------------
 void launch_add(const float *a, const float *b, float *out, size_t n,
                 cudaStream_t stream);                       // out = a + b
-void launch_accumulate(float *dst, const float *src, size_t n,
-                       cudaStream_t stream);                // dst += src
+// The accumulating launchers take `add` flags: true is the host op's "+=",
+// false stores the increment (used when the destination is known to be zero,
+// which saves reading it and lets the zero fill be skipped altogether).
+void launch_accumulate(float *dst, const float *src, size_t n, bool add,
+                       cudaStream_t stream);                // dst (+)= src
 void launch_accumulate2(float *dst_a, float *dst_b, const float *src, size_t n,
-                        cudaStream_t stream);               // both += src
+                        bool add_a, bool add_b,
+                        cudaStream_t stream);               // both (+)= src
 void launch_bias_add(const float *in, const float *bias, float *out,
                      size_t rows, size_t cols, cudaStream_t stream);
 void launch_gelu(const float *in, float *out, size_t n, cudaStream_t stream);
 void launch_gelu_backward(const float *x, const float *dy, float *dx, size_t n,
-                          cudaStream_t stream);             // dx += dy*gelu'(x)
+                          bool add, cudaStream_t stream);   // dx (+)= dy*gelu'(x)
 void launch_scale_by_device_scalar(float *values, size_t n, const float *scale,
                                    cudaStream_t stream);
 
@@ -33,13 +37,13 @@ void launch_split_heads(const float *projected, float *q, float *k, float *v,
 void launch_split_heads_backward(float *projected_grad, const float *dq,
                                  const float *dk, const float *dv, size_t batch,
                                  size_t seq, size_t d_model, size_t heads,
-                                 cudaStream_t stream);
+                                 bool add, cudaStream_t stream);
 void launch_merge_heads(const float *attended, float *merged, size_t batch,
                         size_t seq, size_t d_model, size_t heads,
                         cudaStream_t stream);
 void launch_merge_heads_backward(float *attended_grad, const float *merged_grad,
                                  size_t batch, size_t seq, size_t d_model,
-                                 size_t heads, cudaStream_t stream);
+                                 size_t heads, bool add, cudaStream_t stream);
 void launch_extract_patches(const float *images, float *patches, size_t batch,
                             size_t channels, size_t height, size_t width,
                             size_t patch, cudaStream_t stream);
@@ -50,7 +54,7 @@ void launch_token_embedding(const float *patch_tokens, const float *cls,
 void launch_token_embedding_backward(float *patch_grad, float *cls_grad,
                                      float *positional_grad,
                                      const float *tokens_grad, size_t batch,
-                                     size_t seq, size_t d_model,
+                                     size_t seq, size_t d_model, bool add_patch,
                                      cudaStream_t stream);
 void launch_gather_rows(const float *source, float *destination, size_t rows,
                         size_t cols, size_t row_stride, cudaStream_t stream);
@@ -72,7 +76,7 @@ void launch_layer_norm(const float *x, const float *gamma, const float *beta,
 void launch_layer_norm_backward(const float *x, const float *gamma,
                                 float epsilon, const float *dy, float *dx,
                                 float *dgamma, float *dbeta, size_t rows,
-                                size_t cols, cudaStream_t stream);
+                                size_t cols, bool add_dx, cudaStream_t stream);
 
 // ---- attention (attention.cu) --------------------------------------------
 // q, k, v, out: [groups * seq, head_dim]; probabilities: [groups * seq, seq].
@@ -87,6 +91,7 @@ void launch_attention_backward(const float *q, const float *k, const float *v,
                                const float *dout, float *dq, float *dk,
                                float *dv, float *row_dots, size_t groups,
                                size_t seq, size_t head_dim, float scale,
+                               bool add_q, bool add_k, bool add_v,
                                cudaStream_t stream);
 
 // Short sequences with the whole (sample, head) group in shared memory
@@ -103,7 +108,8 @@ bool launch_attention_small_backward(const float *q, const float *k,
                                      const float *out, const float *dout,
                                      float *dq, float *dk, float *dv,
                                      size_t groups, size_t seq, size_t head_dim,
-                                     float scale, cudaStream_t stream);
+                                     float scale, bool add_q, bool add_k,
+                                     bool add_v, cudaStream_t stream);
 
 // ---- loss (loss.cu) -------------------------------------------------------
 // row_losses: scratch of `rows` floats.

@@ -97,7 +97,7 @@ layer_norm_backward_kernel(const float *__restrict__ x,
                            const float *__restrict__ gamma, float epsilon,
                            const float *__restrict__ dy, float *__restrict__ dx,
                            float *__restrict__ dgamma, float *__restrict__ dbeta,
-                           size_t rows, size_t cols) {
+                           size_t rows, size_t cols, bool add) {
     __shared__ float4 fold[kWarpsPerBlock][32];
     const int lane = threadIdx.x & 31;
     const int warp_in_block = threadIdx.x >> 5;
@@ -151,7 +151,7 @@ layer_norm_backward_kernel(const float *__restrict__ x,
             if (col < cols) {
                 float4 *target =
                     reinterpret_cast<float4 *>(dx + row * cols + col);
-                float4 d = *target;
+                float4 d = add ? *target : make_float4(0.f, 0.f, 0.f, 0.f);
                 d.x += inverse_std * (u[j].x - s1 - v[j].x * s2);
                 d.y += inverse_std * (u[j].y - s1 - v[j].y * s2);
                 d.z += inverse_std * (u[j].z - s1 - v[j].z * s2);
@@ -226,7 +226,7 @@ layer_norm_backward_generic_kernel(const float *__restrict__ x,
                                    float *__restrict__ dx,
                                    float *__restrict__ dgamma,
                                    float *__restrict__ dbeta, size_t rows,
-                                   size_t cols) {
+                                   size_t cols, bool add) {
     const int lane = threadIdx.x & 31;
     const size_t warp = size_t(blockIdx.x) * kWarpsPerBlock + (threadIdx.x >> 5);
     const size_t warps = size_t(gridDim.x) * kWarpsPerBlock;
@@ -259,7 +259,8 @@ layer_norm_backward_generic_kernel(const float *__restrict__ x,
         for (size_t c = lane; c < cols; c += 32) {
             const float normalised = (values[c] - mean) * inverse_std;
             const float dxhat = upstream[c] * gamma[c];
-            dx[row * cols + c] += inverse_std * (dxhat - s1 - normalised * s2);
+            dx[row * cols + c] = (add ? dx[row * cols + c] : 0.0f) +
+                                 inverse_std * (dxhat - s1 - normalised * s2);
         }
     }
 }
@@ -301,25 +302,25 @@ void launch_layer_norm(const float *x, const float *gamma, const float *beta,
 void launch_layer_norm_backward(const float *x, const float *gamma,
                                 float epsilon, const float *dy, float *dx,
                                 float *dgamma, float *dbeta, size_t rows,
-                                size_t cols, cudaStream_t stream) {
+                                size_t cols, bool add_dx, cudaStream_t stream) {
     const unsigned grid = row_grid(rows, 4);
     const unsigned block = kWarpsPerBlock * 32;
     const size_t slots = (cols + 127) / 128;
     if (cols % 4 != 0 || slots > 8) {
         layer_norm_backward_generic_kernel<<<grid, block, 0, stream>>>(
-            x, gamma, epsilon, dy, dx, dgamma, dbeta, rows, cols);
+            x, gamma, epsilon, dy, dx, dgamma, dbeta, rows, cols, add_dx);
     } else if (slots <= 1) {
         layer_norm_backward_kernel<1><<<grid, block, 0, stream>>>(
-            x, gamma, epsilon, dy, dx, dgamma, dbeta, rows, cols);
+            x, gamma, epsilon, dy, dx, dgamma, dbeta, rows, cols, add_dx);
     } else if (slots <= 2) {
         layer_norm_backward_kernel<2><<<grid, block, 0, stream>>>(
-            x, gamma, epsilon, dy, dx, dgamma, dbeta, rows, cols);
+            x, gamma, epsilon, dy, dx, dgamma, dbeta, rows, cols, add_dx);
     } else if (slots <= 4) {
         layer_norm_backward_kernel<4><<<grid, block, 0, stream>>>(
-            x, gamma, epsilon, dy, dx, dgamma, dbeta, rows, cols);
+            x, gamma, epsilon, dy, dx, dgamma, dbeta, rows, cols, add_dx);
     } else {
         layer_norm_backward_kernel<8><<<grid, block, 0, stream>>>(
-            x, gamma, epsilon, dy, dx, dgamma, dbeta, rows, cols);
+            x, gamma, epsilon, dy, dx, dgamma, dbeta, rows, cols, add_dx);
     }
     ++g_kernel_launches;
 }

@@ -62,7 +62,8 @@ __global__ void split_heads_backward_kernel(float *__restrict__ projected_grad,
                                             const float *__restrict__ dk,
                                             const float *__restrict__ dv,
                                             size_t batch, size_t seq,
-                                            size_t d_model, size_t heads) {
+                                            size_t d_model, size_t heads,
+                                            bool add) {
     using T = typename Vec<V>::type;
     const size_t head_dim = d_model / heads;
     const size_t row_vectors = 3 * d_model / V;
@@ -80,8 +81,8 @@ __global__ void split_heads_backward_kernel(float *__restrict__ projected_grad,
         const size_t source =
             (((sample * heads + head) * seq + position) * head_dim + dim) / V;
         const float *from = which == 0 ? dq : (which == 1 ? dk : dv);
-        destination[i] =
-            vadd(destination[i], reinterpret_cast<const T *>(from)[source]);
+        const T value = reinterpret_cast<const T *>(from)[source];
+        destination[i] = add ? vadd(destination[i], value) : value;
     }
 }
 
@@ -111,7 +112,8 @@ template <int V>
 __global__ void merge_heads_backward_kernel(float *__restrict__ attended_grad,
                                             const float *__restrict__ merged_grad,
                                             size_t batch, size_t seq,
-                                            size_t d_model, size_t heads) {
+                                            size_t d_model, size_t heads,
+                                            bool add) {
     using T = typename Vec<V>::type;
     const size_t head_dim = d_model / heads;
     const size_t total = batch * seq * d_model / V;
@@ -119,8 +121,8 @@ __global__ void merge_heads_backward_kernel(float *__restrict__ attended_grad,
     for (size_t i = global_thread(); i < total; i += grid_threads()) {
         const size_t s =
             token_major_index<V>(i, seq, heads, head_dim, d_model, 0);
-        destination[i] =
-            vadd(destination[i], reinterpret_cast<const T *>(merged_grad)[s]);
+        const T value = reinterpret_cast<const T *>(merged_grad)[s];
+        destination[i] = add ? vadd(destination[i], value) : value;
     }
 }
 
@@ -181,7 +183,7 @@ template <int V>
 __global__ void token_patch_grad_kernel(float *__restrict__ patch_grad,
                                         const float *__restrict__ tokens_grad,
                                         size_t batch, size_t seq,
-                                        size_t d_model) {
+                                        size_t d_model, bool add) {
     using T = typename Vec<V>::type;
     const size_t row_vectors = d_model / V;
     const size_t patches = seq - 1;
@@ -192,10 +194,9 @@ __global__ void token_patch_grad_kernel(float *__restrict__ patch_grad,
         const size_t col = i % row_vectors;
         const size_t sample = row / patches;
         const size_t position = row % patches + 1;
-        destination[i] = vadd(
-            destination[i],
-            reinterpret_cast<const T *>(tokens_grad)
-                [(sample * seq + position) * row_vectors + col]);
+        const T value = reinterpret_cast<const T *>(tokens_grad)
+            [(sample * seq + position) * row_vectors + col];
+        destination[i] = add ? vadd(destination[i], value) : value;
     }
 }
 
@@ -247,11 +248,11 @@ void launch_split_heads(const float *projected, float *q, float *k, float *v,
 void launch_split_heads_backward(float *projected_grad, const float *dq,
                                  const float *dk, const float *dv, size_t batch,
                                  size_t seq, size_t d_model, size_t heads,
-                                 cudaStream_t stream) {
+                                 bool add, cudaStream_t stream) {
     const bool vec = (d_model / heads) % 4 == 0;
     VITB200_LAUNCH_V(vec, split_heads_backward_kernel,
                      batch * seq * 3 * d_model, projected_grad, dq, dk, dv,
-                     batch, seq, d_model, heads);
+                     batch, seq, d_model, heads, add);
 }
 
 void launch_merge_heads(const float *attended, float *merged, size_t batch,
@@ -264,10 +265,11 @@ void launch_merge_heads(const float *attended, float *merged, size_t batch,
 
 void launch_merge_heads_backward(float *attended_grad, const float *merged_grad,
                                  size_t batch, size_t seq, size_t d_model,
-                                 size_t heads, cudaStream_t stream) {
+                                 size_t heads, bool add, cudaStream_t stream) {
     const bool vec = (d_model / heads) % 4 == 0;
     VITB200_LAUNCH_V(vec, merge_heads_backward_kernel, batch * seq * d_model,
-                     attended_grad, merged_grad, batch, seq, d_model, heads);
+                     attended_grad, merged_grad, batch, seq, d_model, heads,
+                     add);
 }
 
 void launch_extract_patches(const float *images, float *patches, size_t batch,
@@ -293,11 +295,11 @@ void launch_token_embedding(const float *patch_tokens, const float *cls,
 void launch_token_embedding_backward(float *patch_grad, float *cls_grad,
                                      float *positional_grad,
                                      const float *tokens_grad, size_t batch,
-                                     size_t seq, size_t d_model,
+                                     size_t seq, size_t d_model, bool add_patch,
                                      cudaStream_t stream) {
     VITB200_LAUNCH_V(d_model % 4 == 0, token_patch_grad_kernel,
                      batch * (seq - 1) * d_model, patch_grad, tokens_grad,
-                     batch, seq, d_model);
+                     batch, seq, d_model, add_patch);
     // Seen as a [batch, seq*d_model] matrix, the positional gradient is the
     // column sum over the batch and the CLS gradient the column sum of its
     // first d_model columns (reference src/ops.c:497-511).
