@@ -184,7 +184,8 @@ def run_reference(args, vh, config, batch, rank, world):
         "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
         "dtype": "f32", "data": "synthetic",
         "config": {"workload": args.workload, "vit": list(config),
-                   "batch": batch},
+                   "batch_per_gpu": batch, "global_batch": batch,
+                   "parallelism": "dp1"},
         "cpu_baseline": {
             "value": value, "unit": "images/s", "cores": replicas,
             "kind": "reference",

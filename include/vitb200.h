@@ -155,14 +155,15 @@ int vitb200_k_gelu_backward(const float *x, const float *dy, float *dx,
                             size_t n, void *stream);
 int vitb200_k_attention(const float *q, const float *k, const float *v,
                         float *probabilities, float *out, size_t groups,
-                        size_t seq, size_t head_dim, float scale, void *stream);
+                        size_t seq, size_t head_dim, float scale, int precision,
+                        void *stream);
 /* row_dots: scratch, groups*seq floats. */
 int vitb200_k_attention_backward(const float *q, const float *k, const float *v,
                                  const float *probabilities, const float *out,
                                  const float *dout, float *dq, float *dk,
                                  float *dv, float *row_dots, size_t groups,
                                  size_t seq, size_t head_dim, float scale,
-                                 void *stream);
+                                 int precision, void *stream);
 /* row_losses: scratch, rows floats. */
 int vitb200_k_softmax_cross_entropy(const float *logits, const float *targets,
                                     const float *class_weights,

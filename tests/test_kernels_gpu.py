@@ -158,11 +158,19 @@ def test_bias_add_and_column_sums(lib, rows, cols):
     close(host(tx), (x + b).astype(np.float32), 1e-6)
 
 
+@pytest.mark.parametrize("precision", [FP32, TF32], ids=["fp32", "tf32"])
 @pytest.mark.parametrize("groups,seq,hd", [
     (1, 1, 8), (3, 5, 4), (8, 50, 8), (16, 50, 16), (4, 197, 32), (2, 197, 64),
-    (2, 50, 128), (1, 257, 64), (2, 33, 24),
+    (2, 50, 128), (1, 257, 64), (2, 33, 24), (3, 64, 16), (2, 65, 32),
+    (1, 1025, 64),
 ])
-def test_attention_forward_and_backward(lib, groups, seq, hd):
+def test_attention_forward_and_backward(lib, groups, seq, hd, precision):
+    """FP32 kernels to 1e-5 / 2e-5; TF32 tensor-core kernels (operands rounded
+    to 10 mantissa bits, FP32 accumulation and softmax) to 2e-3 of the largest
+    reference entry."""
+    if precision == TF32 and hd not in (8, 16, 32, 64, 128):
+        pytest.skip("tensor-core attention covers head dims 8..128, powers of 2")
+    forward_tol, backward_tol = (1e-5, 2e-5) if precision == FP32 else (2e-3, 2e-3)
     rng = np.random.RandomState(groups * seq + hd)
     rows = groups * seq
     q, k, v, dout = (rng.randn(rows, hd) for _ in range(4))
@@ -175,18 +183,20 @@ def test_attention_forward_and_backward(lib, groups, seq, hd):
     dots = torch.empty(rows, device="cuda")
     assert lib.vitb200_k_attention(ptr(tq), ptr(tk), ptr(tv), ptr(tp), ptr(to),
                                    size(groups), size(seq), size(hd),
-                                   ctypes.c_float(scale), None) == 0
+                                   ctypes.c_float(scale), precision, None) == 0
     assert lib.vitb200_k_attention_backward(
         ptr(tq), ptr(tk), ptr(tv), ptr(tp), ptr(to), ptr(tdo), ptr(tdq),
         ptr(tdk), ptr(tdv), ptr(dots), size(groups), size(seq), size(hd),
-        ctypes.c_float(scale), None) == 0
+        ctypes.c_float(scale), precision, None) == 0
     p, o = vo.multi_head_attention(q, k, v, groups, seq, scale)
-    close(host(tp), p, 1e-5)
-    close(host(to), o, 1e-5)
-    dq, dk, dv = vo.multi_head_attention_backward(q, k, v, p, dout, groups, seq, scale)
-    close(host(tdq), dq0 + dq, 2e-5)
-    close(host(tdk), dk0 + dk, 2e-5)
-    close(host(tdv), dv0 + dv, 2e-5)
+    close(host(tp), p, forward_tol)
+    close(host(to), o, forward_tol)
+    # The backward kernels are given the device's own P and O, as in training.
+    dq, dk, dv = vo.multi_head_attention_backward(
+        q, k, v, host(tp).astype(np.float64), dout, groups, seq, scale)
+    close(host(tdq), dq0 + dq, backward_tol)
+    close(host(tdk), dk0 + dk, backward_tol)
+    close(host(tdv), dv0 + dv, backward_tol)
     np.testing.assert_allclose(host(tp).sum(axis=1), 1.0, atol=1e-5)
 
 
@@ -194,7 +204,8 @@ def test_attention_rejects_unsupported_head_dim(lib):
     dummy = torch.zeros(1, device="cuda")
     assert lib.vitb200_k_attention(ptr(dummy), ptr(dummy), ptr(dummy),
                                    ptr(dummy), ptr(dummy), size(1), size(1),
-                                   size(129), ctypes.c_float(1.0), None) == -1
+                                   size(129), ctypes.c_float(1.0), FP32,
+                                   None) == -1
 
 
 @pytest.mark.parametrize("rows,cols,smoothing,weighted", [

@@ -13,6 +13,8 @@
 //             query-major kernel: dP = dO V^T, dS = scale P (dP - D), dQ += dS K
 //             key-major kernel:   same dS recomputed,  dK += dS^T Q, dV += P^T dO
 #include "kernels.h"
+#include "gemm.h"
+#include "../../include/vitb200.h"
 #include "device_util.cuh"
 
 #include <cfloat>
@@ -367,7 +369,19 @@ void allow_shared(Kernel kernel, size_t bytes) {
 void launch_attention_forward(const float *q, const float *k, const float *v,
                               float *probabilities, float *out, size_t groups,
                               size_t seq, size_t head_dim, float scale,
-                              cudaStream_t stream) {
+                              int precision, cudaStream_t stream) {
+    // Short sequences are limited by shared-memory and instruction traffic,
+    // not by arithmetic: the FP32 whole-group kernel is as fast there and
+    // exact, so tensor cores are used for them only on explicit request.
+    const double work = double(groups) * seq * seq * head_dim;
+    const bool short_sequence = attention_small_supported(seq, head_dim);
+    if (attention_mma_supported(head_dim) &&
+        (precision == VITB200_PRECISION_TF32 ||
+         (!short_sequence && prefer_tensor_cores(precision, work))) &&
+        launch_attention_mma_forward(q, k, v, probabilities, out, groups, seq,
+                                     head_dim, scale, stream)) {
+        return;
+    }
     if (attention_small_supported(seq, head_dim) &&
         launch_attention_small_forward(q, k, v, probabilities, out, groups, seq,
                                        head_dim, scale, stream)) {
@@ -392,7 +406,17 @@ void launch_attention_backward(const float *q, const float *k, const float *v,
                                float *dv, float *row_dots, size_t groups,
                                size_t seq, size_t head_dim, float scale,
                                bool add_q, bool add_k, bool add_v,
-                               cudaStream_t stream) {
+                               int precision, cudaStream_t stream) {
+    const double work = double(groups) * seq * seq * head_dim;
+    const bool short_sequence = attention_small_supported(seq, head_dim);
+    if (attention_mma_supported(head_dim) &&
+        (precision == VITB200_PRECISION_TF32 ||
+         (!short_sequence && prefer_tensor_cores(precision, work))) &&
+        launch_attention_mma_backward(q, k, v, probabilities, out, dout, dq, dk,
+                                      dv, row_dots, groups, seq, head_dim,
+                                      scale, add_q, add_k, add_v, stream)) {
+        return;
+    }
     if (attention_small_supported(seq, head_dim) &&
         launch_attention_small_backward(q, k, v, probabilities, out, dout, dq,
                                         dk, dv, groups, seq, head_dim, scale,

@@ -34,6 +34,123 @@ __device__ __forceinline__ void load_rows(const float *__restrict__ source,
     }
 }
 
+// Packed FP32 arithmetic: Blackwell issues two FP32 FMAs per instruction on
+// register pairs (fma.rn.f32x2), which halves the instruction count of the
+// short dot products and row updates below.  Rows live in registers as HD/2
+// packed pairs.
+typedef unsigned long long pair_t;
+
+__device__ __forceinline__ pair_t pack(float lo, float hi) {
+    pair_t p;
+    asm("mov.b64 %0, {%1, %2};" : "=l"(p) : "f"(lo), "f"(hi));
+    return p;
+}
+
+__device__ __forceinline__ void unpack(pair_t p, float &lo, float &hi) {
+    asm("mov.b64 {%0, %1}, %2;" : "=f"(lo), "=f"(hi) : "l"(p));
+}
+
+__device__ __forceinline__ pair_t fma2(pair_t a, pair_t b, pair_t c) {
+    pair_t d;
+    asm("fma.rn.f32x2 %0, %1, %2, %3;" : "=l"(d) : "l"(a), "l"(b), "l"(c));
+    return d;
+}
+
+// row . tile_row; the tile row is read with 128-bit shared-memory loads (every
+// thread of the warp reads the same address: one broadcast per load).
+template <int HD>
+__device__ __forceinline__ float dot_tile(const pair_t (&row)[HD / 2],
+                                          const float *tile_row) {
+    const float4 *t = reinterpret_cast<const float4 *>(tile_row);
+    pair_t sum = pack(0.0f, 0.0f);
+#pragma unroll
+    for (int c = 0; c < HD / 4; ++c) {
+        const float4 x = t[c];
+        sum = fma2(row[2 * c], pack(x.x, x.y), sum);
+        sum = fma2(row[2 * c + 1], pack(x.z, x.w), sum);
+    }
+    float lo, hi;
+    unpack(sum, lo, hi);
+    return lo + hi;
+}
+
+// row += a * tile_row.
+template <int HD>
+__device__ __forceinline__ void axpy_tile(pair_t (&row)[HD / 2], float a,
+                                          const float *tile_row) {
+    const float4 *t = reinterpret_cast<const float4 *>(tile_row);
+    const pair_t a2 = pack(a, a);
+#pragma unroll
+    for (int c = 0; c < HD / 4; ++c) {
+        const float4 x = t[c];
+        row[2 * c] = fma2(a2, pack(x.x, x.y), row[2 * c]);
+        row[2 * c + 1] = fma2(a2, pack(x.z, x.w), row[2 * c + 1]);
+    }
+}
+
+template <int HD>
+__device__ __forceinline__ void clear_row(pair_t (&row)[HD / 2]) {
+#pragma unroll
+    for (int c = 0; c < HD / 2; ++c) {
+        row[c] = pack(0.0f, 0.0f);
+    }
+}
+
+// Loads a row of HD floats (global or shared) into packed registers.
+template <int HD>
+__device__ __forceinline__ void load_row_pairs(pair_t (&row)[HD / 2],
+                                               const float *source) {
+    const float4 *t = reinterpret_cast<const float4 *>(source);
+#pragma unroll
+    for (int c = 0; c < HD / 4; ++c) {
+        const float4 x = t[c];
+        row[2 * c] = pack(x.x, x.y);
+        row[2 * c + 1] = pack(x.z, x.w);
+    }
+}
+
+// target (+)= row, 128-bit global accesses.
+template <int HD>
+__device__ __forceinline__ void store_row_pairs(float *target,
+                                                const pair_t (&row)[HD / 2],
+                                                bool add) {
+#pragma unroll
+    for (int c = 0; c < HD / 4; ++c) {
+        float4 *t = reinterpret_cast<float4 *>(target) + c;
+        float4 value = add ? *t : make_float4(0.f, 0.f, 0.f, 0.f);
+        float a, b, d, e;
+        unpack(row[2 * c], a, b);
+        unpack(row[2 * c + 1], d, e);
+        value.x += a; value.y += b; value.z += d; value.w += e;
+        *t = value;
+    }
+}
+
+// exp for softmax arguments (<= 0 after subtracting the row maximum):
+// ex2.approx on x * log2(e), relative error about 2e-7 in this range.
+__device__ __forceinline__ float softmax_exp(float x) {
+    return __expf(x);
+}
+
+// Copies the group's [seq, seq] probability block between global memory
+// (contiguous rows) and the padded shared tile, one row per warp at a time.
+template <bool kToGlobal>
+__device__ __forceinline__ void move_probabilities(float *global_block,
+                                                   float *tile, int seq,
+                                                   int pitch) {
+    const int lane = threadIdx.x & 31;
+    const int warps = blockDim.x >> 5;
+    for (int r = threadIdx.x >> 5; r < seq; r += warps) {
+        for (int c = lane; c < seq; c += 32) {
+            if (kToGlobal) {
+                global_block[r * seq + c] = tile[r * pitch + c];
+            } else {
+                tile[r * pitch + c] = __ldcs(global_block + r * seq + c);
+            }
+        }
+    }
+}
+
 template <int HD>
 __global__ void attention_small_forward_kernel(
     const float *__restrict__ q, const float *__restrict__ k,
@@ -49,61 +166,37 @@ __global__ void attention_small_forward_kernel(
     load_rows<HD>(k + base, k_tile, seq);
     load_rows<HD>(v + base, v_tile, seq);
     const int row = threadIdx.x;
-    float query[HD];
+    pair_t query[HD / 2];
     if (row < seq) {
-#pragma unroll
-        for (int d = 0; d < HD; d += 4) {
-            const float4 x =
-                __ldcs(reinterpret_cast<const float4 *>(q + base + row * HD + d));
-            query[d] = x.x; query[d + 1] = x.y; query[d + 2] = x.z; query[d + 3] = x.w;
-        }
+        load_row_pairs<HD>(query, q + base + row * HD);
     }
     __syncthreads();
     if (row < seq) {
         float *scores = p_tile + row * pitch;
         float maximum = -FLT_MAX;
         for (int j = 0; j < seq; ++j) {
-            const float *key = k_tile + j * HD;
-            float dot = 0.0f;
-#pragma unroll
-            for (int d = 0; d < HD; ++d) {
-                dot += query[d] * key[d];
-            }
-            dot *= scale;
+            const float dot = scale * dot_tile<HD>(query, k_tile + j * HD);
             scores[j] = dot;
             maximum = fmaxf(maximum, dot);
         }
         float denominator = 0.0f;
         for (int j = 0; j < seq; ++j) {
-            const float e = expf(scores[j] - maximum);
+            const float e = softmax_exp(scores[j] - maximum);
             scores[j] = e;
             denominator += e;
         }
-        float result[HD];
-#pragma unroll
-        for (int d = 0; d < HD; ++d) {
-            result[d] = 0.0f;
-        }
+        const float inverse = 1.0f / denominator;
+        pair_t result[HD / 2];
+        clear_row<HD>(result);
         for (int j = 0; j < seq; ++j) {
-            const float probability = scores[j] / denominator;
+            const float probability = scores[j] * inverse;
             scores[j] = probability;
-            const float *value = v_tile + j * HD;
-#pragma unroll
-            for (int d = 0; d < HD; ++d) {
-                result[d] += probability * value[d];
-            }
+            axpy_tile<HD>(result, probability, v_tile + j * HD);
         }
-#pragma unroll
-        for (int d = 0; d < HD; d += 4) {
-            *reinterpret_cast<float4 *>(out + base + row * HD + d) =
-                make_float4(result[d], result[d + 1], result[d + 2], result[d + 3]);
-        }
+        store_row_pairs<HD>(out + base + row * HD, result, false);
     }
     __syncthreads();
-    float *p_group = p + group * seq * seq;
-    for (int i = threadIdx.x; i < seq * seq; i += blockDim.x) {
-        p_group[i] = p_tile[(i / seq) * pitch + i % seq];
-    }
+    move_probabilities<true>(p + group * seq * seq, p_tile, seq, pitch);
 }
 
 template <int HD>
@@ -126,10 +219,8 @@ __global__ void attention_small_backward_kernel(
     load_rows<HD>(k + base, k_tile, seq);
     load_rows<HD>(v + base, v_tile, seq);
     load_rows<HD>(dout + base, do_tile, seq);
-    const float *p_group = p + group * seq * seq;
-    for (int i = threadIdx.x; i < seq * seq; i += blockDim.x) {
-        p_tile[(i / seq) * pitch + i % seq] = __ldcs(p_group + i);
-    }
+    move_probabilities<false>(const_cast<float *>(p) + group * seq * seq,
+                              p_tile, seq, pitch);
     const int row = threadIdx.x;
     float row_dot = 0.0f;
     if (row < seq) {
@@ -143,84 +234,38 @@ __global__ void attention_small_backward_kernel(
         }
     }
     __syncthreads();
-    float acc[HD];
+    pair_t acc[HD / 2];
     // Columns: dV_j = sum_i P_ij dO_i.
     if (row < seq) {
-#pragma unroll
-        for (int d = 0; d < HD; ++d) {
-            acc[d] = 0.0f;
-        }
+        clear_row<HD>(acc);
         for (int i = 0; i < seq; ++i) {
-            const float probability = p_tile[i * pitch + row];
-            const float *g = do_tile + i * HD;
-#pragma unroll
-            for (int d = 0; d < HD; ++d) {
-                acc[d] += probability * g[d];
-            }
+            axpy_tile<HD>(acc, p_tile[i * pitch + row], do_tile + i * HD);
         }
-#pragma unroll
-        for (int d = 0; d < HD; d += 4) {
-            float4 *target = reinterpret_cast<float4 *>(dv + base + row * HD + d);
-            float4 t = add_v ? *target : make_float4(0.f, 0.f, 0.f, 0.f);
-            t.x += acc[d]; t.y += acc[d + 1]; t.z += acc[d + 2]; t.w += acc[d + 3];
-            *target = t;
-        }
+        store_row_pairs<HD>(dv + base + row * HD, acc, add_v);
     }
     __syncthreads();
     // Rows: score gradients in place over P, then dQ_i.
     if (row < seq) {
-        float g[HD];
-#pragma unroll
-        for (int d = 0; d < HD; ++d) {
-            g[d] = do_tile[row * HD + d];
-            acc[d] = 0.0f;
-        }
+        pair_t g[HD / 2];
+        load_row_pairs<HD>(g, do_tile + row * HD);
+        clear_row<HD>(acc);
         float *scores = p_tile + row * pitch;
         for (int j = 0; j < seq; ++j) {
-            const float *value = v_tile + j * HD;
-            float dp = 0.0f;
-#pragma unroll
-            for (int d = 0; d < HD; ++d) {
-                dp += g[d] * value[d];
-            }
+            const float dp = dot_tile<HD>(g, v_tile + j * HD);
             const float ds = scale * scores[j] * (dp - row_dot);
             scores[j] = ds;
-            const float *key = k_tile + j * HD;
-#pragma unroll
-            for (int d = 0; d < HD; ++d) {
-                acc[d] += ds * key[d];
-            }
+            axpy_tile<HD>(acc, ds, k_tile + j * HD);
         }
-#pragma unroll
-        for (int d = 0; d < HD; d += 4) {
-            float4 *target = reinterpret_cast<float4 *>(dq + base + row * HD + d);
-            float4 t = add_q ? *target : make_float4(0.f, 0.f, 0.f, 0.f);
-            t.x += acc[d]; t.y += acc[d + 1]; t.z += acc[d + 2]; t.w += acc[d + 3];
-            *target = t;
-        }
+        store_row_pairs<HD>(dq + base + row * HD, acc, add_q);
     }
     __syncthreads();
     // Columns: dK_j = sum_i dS_ij Q_i.
     if (row < seq) {
-#pragma unroll
-        for (int d = 0; d < HD; ++d) {
-            acc[d] = 0.0f;
-        }
+        clear_row<HD>(acc);
         for (int i = 0; i < seq; ++i) {
-            const float ds = p_tile[i * pitch + row];
-            const float *query = q_tile + i * HD;
-#pragma unroll
-            for (int d = 0; d < HD; ++d) {
-                acc[d] += ds * query[d];
-            }
+            axpy_tile<HD>(acc, p_tile[i * pitch + row], q_tile + i * HD);
         }
-#pragma unroll
-        for (int d = 0; d < HD; d += 4) {
-            float4 *target = reinterpret_cast<float4 *>(dk + base + row * HD + d);
-            float4 t = add_k ? *target : make_float4(0.f, 0.f, 0.f, 0.f);
-            t.x += acc[d]; t.y += acc[d + 1]; t.z += acc[d + 2]; t.w += acc[d + 3];
-            *target = t;
-        }
+        store_row_pairs<HD>(dk + base + row * HD, acc, add_k);
     }
 }
 

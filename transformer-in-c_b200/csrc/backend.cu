@@ -589,7 +589,8 @@ int op_attention(void *context, const vitb200_tensor *query,
         OpScope scope(backend, "multi_head_attention", 4.0 * (4.0 * double(numel(query)) + double(numel(probabilities))),
                       4.0 * double(numel(probabilities)) * double(query->cols));
         launch_attention_forward(q, k, v, p, o, batch * heads, seq, query->cols,
-                                 scale, backend->stream);
+                                 scale, VITB200_PRECISION_AUTO,
+                                 backend->stream);
     }
     return 0;
 }
@@ -627,7 +628,7 @@ int op_attention_backward(void *context, const vitb200_tensor *query,
                       8.0 * double(numel(probabilities)) * double(query->cols));
         launch_attention_backward(q, k, v, p, o, go, dq, dk, dv, dots, groups, seq,
                                   query->cols, scale, add_q, add_k, add_v,
-                                  backend->stream);
+                                  VITB200_PRECISION_AUTO, backend->stream);
     }
     return 0;
 }
@@ -1349,12 +1350,17 @@ extern "C" int vitb200_k_gelu_backward(const float *x, const float *dy,
 extern "C" int vitb200_k_attention(const float *q, const float *k,
                                    const float *v, float *probabilities,
                                    float *out, size_t groups, size_t seq,
-                                   size_t head_dim, float scale, void *stream) {
+                                   size_t head_dim, float scale, int precision,
+                                   void *stream) {
     if (head_dim > kMaxHeadDim || !fits_int(seq) || !fits_int(groups)) {
         return -1;
     }
+    if (precision == VITB200_PRECISION_TF32 &&
+        !attention_mma_supported(head_dim)) {
+        return -1;
+    }
     launch_attention_forward(q, k, v, probabilities, out, groups, seq, head_dim,
-                             scale, as_stream(stream));
+                             scale, precision, as_stream(stream));
     return 0;
 }
 
@@ -1362,13 +1368,13 @@ extern "C" int vitb200_k_attention_backward(
     const float *q, const float *k, const float *v, const float *probabilities,
     const float *out, const float *dout, float *dq, float *dk, float *dv,
     float *row_dots, size_t groups, size_t seq, size_t head_dim, float scale,
-    void *stream) {
+    int precision, void *stream) {
     if (head_dim > kMaxHeadDim || !fits_int(seq) || !fits_int(groups)) {
         return -1;
     }
     launch_attention_backward(q, k, v, probabilities, out, dout, dq, dk, dv,
                               row_dots, groups, seq, head_dim, scale, true,
-                              true, true, as_stream(stream));
+                              true, true, precision, as_stream(stream));
     return 0;
 }
 

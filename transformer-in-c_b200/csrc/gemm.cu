@@ -89,6 +89,19 @@ int run(const TcGemm &gemm, int precision, cudaStream_t stream) {
 
 }  // namespace
 
+bool prefer_tensor_cores(int precision, double multiply_adds) {
+    if (precision == VITB200_PRECISION_AUTO) {
+        precision = default_precision();
+    }
+    if (precision == VITB200_PRECISION_FP32) {
+        return false;
+    }
+    if (precision == VITB200_PRECISION_TF32) {
+        return true;
+    }
+    return multiply_adds >= kTensorCoreMinimumWork;
+}
+
 void gemm_set_default_precision(int precision) {
     g_forced_precision = precision;
 }

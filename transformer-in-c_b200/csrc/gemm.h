@@ -18,6 +18,10 @@ int gemm_backward(const float *x, const float *w, const float *dy, float *dx,
                   float *dw, int m, int k, int n, int precision, bool dx_add,
                   cudaStream_t stream);
 
+// The same policy for other tensor-core capable ops (attention): true when an
+// op of `multiply_adds` should use TF32 under `precision`.
+bool prefer_tensor_cores(int precision, double multiply_adds);
+
 // Overrides what VITB200_PRECISION_AUTO means (and the VITB200_GEMM
 // environment variable); -1 restores the default policy.
 void gemm_set_default_precision(int precision);

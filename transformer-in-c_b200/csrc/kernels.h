@@ -80,10 +80,12 @@ void launch_layer_norm_backward(const float *x, const float *gamma,
 
 // ---- attention (attention.cu) --------------------------------------------
 // q, k, v, out: [groups * seq, head_dim]; probabilities: [groups * seq, seq].
+// precision: a VITB200_PRECISION_* selector (FP32 kernels, or TF32 tensor
+// cores in attention_mma.cu).
 void launch_attention_forward(const float *q, const float *k, const float *v,
                               float *probabilities, float *out, size_t groups,
                               size_t seq, size_t head_dim, float scale,
-                              cudaStream_t stream);
+                              int precision, cudaStream_t stream);
 // out / dout: forward result and its gradient; row_dots: scratch of
 // groups * seq floats.  dq, dk, dv accumulate.
 void launch_attention_backward(const float *q, const float *k, const float *v,
@@ -92,7 +94,22 @@ void launch_attention_backward(const float *q, const float *k, const float *v,
                                float *dv, float *row_dots, size_t groups,
                                size_t seq, size_t head_dim, float scale,
                                bool add_q, bool add_k, bool add_v,
-                               cudaStream_t stream);
+                               int precision, cudaStream_t stream);
+
+// Tensor-core kernels (attention_mma.cu); false = shape not covered.
+bool attention_mma_supported(size_t head_dim);
+bool launch_attention_mma_forward(const float *q, const float *k,
+                                  const float *v, float *probabilities,
+                                  float *out, size_t groups, size_t seq,
+                                  size_t head_dim, float scale,
+                                  cudaStream_t stream);
+bool launch_attention_mma_backward(const float *q, const float *k,
+                                   const float *v, const float *probabilities,
+                                   const float *out, const float *dout,
+                                   float *dq, float *dk, float *dv,
+                                   float *row_dots, size_t groups, size_t seq,
+                                   size_t head_dim, float scale, bool add_q,
+                                   bool add_k, bool add_v, cudaStream_t stream);
 
 // Short sequences with the whole (sample, head) group in shared memory
 // (attention_small.cu).  The launchers return false when the shape is outside
