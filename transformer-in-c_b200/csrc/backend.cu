@@ -59,6 +59,19 @@ struct PendingOp {
     cudaEvent_t begin, end;
 };
 
+// A forward product whose launch is held back for one or two ops so that the
+// bias add, and then a GELU or a residual add, that the host issues right
+// after it (reference src/vit.c:493-535) can ride on its epilogue.
+struct PendingGemm {
+    bool active = false;
+    const float *x = nullptr, *w = nullptr;
+    float *y = nullptr;
+    const void *y_host = nullptr;   // host address of the output values
+    int m = 0, k = 0, n = 0;
+    GemmEpilogue epilogue;
+    double bytes = 0.0, flops = 0.0;
+};
+
 constexpr int kStagingSlots = 8;
 constexpr size_t kStagingBytes = 64 * 1024;
 
@@ -89,6 +102,8 @@ struct CudaBackend {
     std::vector<PendingOp> pending_ops;
     std::vector<cudaEvent_t> free_events;
     DataParallel *dp = nullptr;
+    PendingGemm pending;
+    unsigned long long fused_epilogues = 0;
     void (*set_table)(const vitb200_op_table *) = nullptr;
     void (*set_allocator)(vitb200_allocate_fn, vitb200_release_fn,
                           void *) = nullptr;
@@ -171,7 +186,31 @@ private:
     PendingOp pending_ = {};
 };
 
+// Launches the held-back product, with whatever was attached to it.
+void flush_pending(CudaBackend *backend) {
+    PendingGemm &pending = backend->pending;
+    if (!pending.active) {
+        return;
+    }
+    pending.active = false;
+    OpScope scope(backend, "gemm", pending.bytes, pending.flops);
+    gemm_forward_fused(pending.x, pending.w, pending.y, pending.m, pending.k,
+                       pending.n, pending.epilogue, VITB200_PRECISION_AUTO,
+                       backend->stream);
+}
+
+CudaBackend *g_flush_backend = nullptr;
+
+// Hook for the coherence layer: called before an upload is enqueued and
+// before a host access to device-owned memory is served.
+void flush_hook() {
+    if (g_flush_backend) {
+        flush_pending(g_flush_backend);
+    }
+}
+
 void settle_timers(CudaBackend *backend) {
+    flush_pending(backend);
     if (backend->span_open) {
         check(cudaEventRecord(backend->span_end, backend->stream),
               "cudaEventRecord");
@@ -266,6 +305,7 @@ float *accumulate_view(CudaBackend *backend, const void *pointer, bool *add) {
 int op_gemm(void *context, const vitb200_tensor *left,
             const vitb200_tensor *right, vitb200_tensor *output) {
     CudaBackend *backend = self(context);
+    flush_pending(backend);
     if (!ours({left->data, right->data, output->data}) ||
         !fits_int(left->rows) || !fits_int(left->cols) ||
         !fits_int(right->cols)) {
@@ -274,18 +314,29 @@ int op_gemm(void *context, const vitb200_tensor *left,
     const float *x = view(backend, left->data, Access::Read);
     const float *w = view(backend, right->data, Access::Read);
     float *y = view(backend, output->data, Access::Overwrite);
-    {
-        OpScope scope(backend, "gemm", 4.0 * (double(left->rows) * left->cols + double(right->rows) * right->cols + double(output->rows) * output->cols),
-                      2.0 * double(left->rows) * left->cols * right->cols);
-        gemm_forward(x, w, y, int(left->rows), int(left->cols), int(right->cols),
-                     VITB200_PRECISION_AUTO, backend->stream);
-    }
+    // Not launched yet: the next op or two may join its epilogue.  The output
+    // is already device-owned, so a host access to it faults and flushes.
+    PendingGemm &pending = backend->pending;
+    pending = PendingGemm();
+    pending.active = true;
+    pending.x = x;
+    pending.w = w;
+    pending.y = y;
+    pending.y_host = output->data;
+    pending.m = int(left->rows);
+    pending.k = int(left->cols);
+    pending.n = int(right->cols);
+    pending.bytes = 4.0 * (double(left->rows) * left->cols +
+                           double(right->rows) * right->cols +
+                           double(output->rows) * output->cols);
+    pending.flops = 2.0 * double(left->rows) * left->cols * right->cols;
     return 0;
 }
 
 int op_gemm_backward(void *context, vitb200_tensor *left, vitb200_tensor *right,
                      const vitb200_tensor *output) {
     CudaBackend *backend = self(context);
+    flush_pending(backend);
     if (!ours({left->data, left->grad, right->data, right->grad,
                output->grad}) ||
         !fits_int(left->rows) || !fits_int(left->cols) ||
@@ -313,8 +364,29 @@ int op_residual(void *context, const vitb200_tensor *left,
                 const vitb200_tensor *right, vitb200_tensor *output) {
     CudaBackend *backend = self(context);
     if (!ours({left->data, right->data, output->data})) {
+        flush_pending(backend);
         return -1;
     }
+    PendingGemm &pending = backend->pending;
+    const bool left_is_product = left->data == pending.y_host;
+    const bool right_is_product = right->data == pending.y_host;
+    if (pending.active && left_is_product != right_is_product &&
+        !pending.epilogue.gelu_out && !pending.epilogue.residual_out &&
+        output->data != pending.y_host &&
+        numel(output) == size_t(pending.m) * pending.n) {
+        const vitb200_tensor *other = left_is_product ? right : left;
+        const float *residual = view(backend, other->data, Access::Read);
+        float *sum = view(backend, output->data, Access::Overwrite);
+        if (pending.active) {   // an upload above may have flushed it
+            pending.epilogue.residual = residual;
+            pending.epilogue.residual_out = sum;
+            pending.bytes += 8.0 * double(numel(output));
+            backend->fused_epilogues += 1;
+            flush_pending(backend);
+            return 0;
+        }
+    }
+    flush_pending(backend);
     const float *a = view(backend, left->data, Access::Read);
     const float *b = view(backend, right->data, Access::Read);
     float *out = view(backend, output->data, Access::Overwrite);
@@ -329,6 +401,7 @@ int op_residual(void *context, const vitb200_tensor *left,
 int op_residual_backward(void *context, vitb200_tensor *left,
                          vitb200_tensor *right, const vitb200_tensor *output) {
     CudaBackend *backend = self(context);
+    flush_pending(backend);
     // One pass updates both branches, which needs them to be distinct.
     if (!ours({left->grad, right->grad, output->grad}) ||
         left->grad == right->grad) {
@@ -350,6 +423,7 @@ int op_residual_backward(void *context, vitb200_tensor *left,
 int op_accumulate_gradient(void *context, vitb200_tensor *destination,
                            const vitb200_tensor *source) {
     CudaBackend *backend = self(context);
+    flush_pending(backend);
     if (!ours({destination->grad, source->grad}) ||
         destination->grad == source->grad) {
         return -1;
@@ -369,9 +443,20 @@ int op_bias_add(void *context, const vitb200_tensor *input,
                 const vitb200_tensor *bias, vitb200_tensor *output) {
     CudaBackend *backend = self(context);
     if (!ours({input->data, bias->data, output->data})) {
+        flush_pending(backend);
         return -1;
     }
     const float *b = view(backend, bias->data, Access::Read);
+    PendingGemm &pending = backend->pending;
+    if (pending.active && input->data == pending.y_host &&
+        output->data == pending.y_host && !pending.epilogue.bias &&
+        !pending.epilogue.gelu_out && !pending.epilogue.residual_out &&
+        input->cols == size_t(pending.n) && input->rows == size_t(pending.m)) {
+        pending.epilogue.bias = b;
+        backend->fused_epilogues += 1;
+        return 0;   // stays pending: a GELU or a residual add may follow
+    }
+    flush_pending(backend);
     const bool in_place = input->data == output->data;
     const float *in =
         view(backend, input->data, in_place ? Access::ReadWrite : Access::Read);
@@ -388,6 +473,7 @@ int op_bias_add(void *context, const vitb200_tensor *input,
 int op_bias_add_backward(void *context, const vitb200_tensor *output,
                          vitb200_tensor *bias_grad) {
     CudaBackend *backend = self(context);
+    flush_pending(backend);
     if (!ours({output->grad, bias_grad->grad})) {
         return -1;
     }
@@ -407,6 +493,7 @@ int op_layer_norm(void *context, const vitb200_tensor *input,
                   const vitb200_tensor *gamma, const vitb200_tensor *beta,
                   float epsilon, vitb200_tensor *output) {
     CudaBackend *backend = self(context);
+    flush_pending(backend);
     if (!ours({input->data, gamma->data, beta->data, output->data}) ||
         input->data == output->data) {
         return -1;
@@ -431,6 +518,7 @@ int op_layer_norm_backward(void *context, const vitb200_tensor *input,
                            vitb200_tensor *gamma_grad,
                            vitb200_tensor *beta_grad) {
     CudaBackend *backend = self(context);
+    flush_pending(backend);
     if (!ours({input->data, gamma->data, output->grad, input_grad->grad,
                gamma_grad->grad, beta_grad->grad}) ||
         output->grad == input_grad->grad) {
@@ -458,8 +546,23 @@ int op_gelu(void *context, const vitb200_tensor *input,
             vitb200_tensor *output) {
     CudaBackend *backend = self(context);
     if (!ours({input->data, output->data}) || input->data == output->data) {
+        flush_pending(backend);
         return -1;
     }
+    PendingGemm &pending = backend->pending;
+    if (pending.active && input->data == pending.y_host &&
+        !pending.epilogue.gelu_out && !pending.epilogue.residual_out &&
+        numel(input) == size_t(pending.m) * pending.n) {
+        float *activated = view(backend, output->data, Access::Overwrite);
+        if (pending.active) {
+            pending.epilogue.gelu_out = activated;
+            pending.bytes += 4.0 * double(numel(output));
+            backend->fused_epilogues += 1;
+            flush_pending(backend);
+            return 0;
+        }
+    }
+    flush_pending(backend);
     const float *in = view(backend, input->data, Access::Read);
     float *out = view(backend, output->data, Access::Overwrite);
     {
@@ -473,6 +576,7 @@ int op_gelu(void *context, const vitb200_tensor *input,
 int op_gelu_backward(void *context, const vitb200_tensor *input,
                      const vitb200_tensor *output) {
     CudaBackend *backend = self(context);
+    flush_pending(backend);
     if (!ours({input->data, input->grad, output->grad})) {
         return -1;
     }
@@ -493,6 +597,7 @@ int op_split_heads(void *context, const vitb200_tensor *projected,
                    vitb200_tensor *value, size_t batch, size_t seq,
                    size_t d_model, size_t heads) {
     CudaBackend *backend = self(context);
+    flush_pending(backend);
     if (!ours({projected->data, query->data, key->data, value->data})) {
         return -1;
     }
@@ -514,6 +619,7 @@ int op_split_heads_backward(void *context, vitb200_tensor *projected,
                             const vitb200_tensor *value, size_t batch,
                             size_t seq, size_t d_model, size_t heads) {
     CudaBackend *backend = self(context);
+    flush_pending(backend);
     if (!ours({projected->grad, query->grad, key->grad, value->grad})) {
         return -1;
     }
@@ -535,6 +641,7 @@ int op_merge_heads(void *context, const vitb200_tensor *attended,
                    vitb200_tensor *merged, size_t batch, size_t seq,
                    size_t d_model, size_t heads) {
     CudaBackend *backend = self(context);
+    flush_pending(backend);
     if (!ours({attended->data, merged->data})) {
         return -1;
     }
@@ -552,6 +659,7 @@ int op_merge_heads_backward(void *context, vitb200_tensor *attended,
                             const vitb200_tensor *merged, size_t batch,
                             size_t seq, size_t d_model, size_t heads) {
     CudaBackend *backend = self(context);
+    flush_pending(backend);
     if (!ours({attended->grad, merged->grad})) {
         return -1;
     }
@@ -574,6 +682,7 @@ int op_attention(void *context, const vitb200_tensor *query,
                  size_t batch, size_t heads, size_t seq, float scale,
                  vitb200_tensor *probabilities, vitb200_tensor *output) {
     CudaBackend *backend = self(context);
+    flush_pending(backend);
     if (!ours({query->data, key->data, value->data, probabilities->data,
                output->data}) ||
         query->cols > kMaxHeadDim || value->cols != query->cols ||
@@ -604,6 +713,7 @@ int op_attention_backward(void *context, const vitb200_tensor *query,
                           vitb200_tensor *query_grad, vitb200_tensor *key_grad,
                           vitb200_tensor *value_grad) {
     CudaBackend *backend = self(context);
+    flush_pending(backend);
     if (!ours({query->data, key->data, value->data, probabilities->data,
                output->data, output->grad, query_grad->grad, key_grad->grad,
                value_grad->grad}) ||
@@ -635,6 +745,7 @@ int op_attention_backward(void *context, const vitb200_tensor *query,
 
 int op_zero_gradient(void *context, vitb200_tensor *tensor) {
     CudaBackend *backend = self(context);
+    flush_pending(backend);
     if (!ours({tensor->grad})) {
         return -1;
     }
@@ -648,6 +759,7 @@ int op_zero_gradient(void *context, vitb200_tensor *tensor) {
 int op_zero_gradients(void *context, vitb200_tensor *const *tensors,
                       size_t count) {
     CudaBackend *backend = self(context);
+    flush_pending(backend);
     for (size_t i = 0; i < count; ++i) {
         if (!coherent_owns(tensors[i]->grad)) {
             return -1;
@@ -663,6 +775,7 @@ int op_extract_patches(void *context, const vitb200_tensor *images,
                        vitb200_tensor *patches, size_t channels, size_t height,
                        size_t width, size_t patch) {
     CudaBackend *backend = self(context);
+    flush_pending(backend);
     if (!ours({images->data, patches->data})) {
         return -1;
     }
@@ -681,6 +794,7 @@ int op_token_embedding(void *context, const vitb200_tensor *patch_tokens,
                        const vitb200_tensor *cls, const vitb200_tensor *pos,
                        vitb200_tensor *tokens, size_t batch) {
     CudaBackend *backend = self(context);
+    flush_pending(backend);
     if (!ours({patch_tokens->data, cls->data, pos->data, tokens->data})) {
         return -1;
     }
@@ -701,6 +815,7 @@ int op_token_embedding_backward(void *context, vitb200_tensor *patch_tokens,
                                 vitb200_tensor *cls, vitb200_tensor *pos,
                                 const vitb200_tensor *tokens, size_t batch) {
     CudaBackend *backend = self(context);
+    flush_pending(backend);
     if (!ours({patch_tokens->grad, cls->grad, pos->grad, tokens->grad})) {
         return -1;
     }
@@ -723,6 +838,7 @@ int op_token_embedding_backward(void *context, vitb200_tensor *patch_tokens,
 int op_gather_rows(void *context, const vitb200_tensor *source,
                    vitb200_tensor *destination, size_t row_stride) {
     CudaBackend *backend = self(context);
+    flush_pending(backend);
     if (!ours({source->data, destination->data})) {
         return -1;
     }
@@ -741,6 +857,7 @@ int op_gather_rows_backward(void *context, vitb200_tensor *source,
                             const vitb200_tensor *destination,
                             size_t row_stride) {
     CudaBackend *backend = self(context);
+    flush_pending(backend);
     if (!ours({source->grad, destination->grad})) {
         return -1;
     }
@@ -761,6 +878,7 @@ int op_softmax_cross_entropy(void *context, const vitb200_tensor *logits,
                              float label_smoothing, vitb200_tensor *loss,
                              vitb200_tensor *logits_grad) {
     CudaBackend *backend = self(context);
+    flush_pending(backend);
     if (!ours({logits->data, targets->data, loss->data, logits_grad->grad}) ||
         (class_weights && !coherent_owns(class_weights->data))) {
         return -1;
@@ -859,6 +977,7 @@ int build_slice_table(CudaBackend *backend,
 int op_clip_gradient_norm(void *context, vitb200_parameter *const *parameters,
                           size_t count, float max_norm) {
     CudaBackend *backend = self(context);
+    flush_pending(backend);
     SliceTable table;
     if (build_slice_table(backend, parameters, nullptr, count, 0.0f, 0.0f,
                           false, &table) != 0) {
@@ -880,6 +999,7 @@ int op_adamw_step(void *context, vitb200_parameter *parameter, float lr,
                   float beta1, float beta2, float epsilon, float weight_decay,
                   float correction1, float correction2) {
     CudaBackend *backend = self(context);
+    flush_pending(backend);
     if (!ours({parameter->value.data, parameter->value.grad, parameter->m,
                parameter->v})) {
         return -1;
@@ -904,6 +1024,7 @@ int op_adamw_step_parameters(void *context,
                              float beta1, float beta2, float epsilon,
                              float max_gradient_norm) {
     CudaBackend *backend = self(context);
+    flush_pending(backend);
     SliceTable table;
     if (build_slice_table(backend, parameters, weight_decays, count, beta1,
                           beta2, true, &table) != 0) {
@@ -1052,7 +1173,8 @@ extern "C" int cuda_backend_create(CudaBackend **backend) {
         cuda_backend_free(result);
         return -1;
     }
-    coherence_set_stream(result->stream, nullptr);
+    coherence_set_stream(result->stream, flush_hook);
+    g_flush_backend = result;
     *backend = result;
     return 0;
 }
@@ -1097,6 +1219,9 @@ extern "C" void cuda_backend_free(CudaBackend *backend) {
     // Tensors that outlive the backend are copied back on the legacy default
     // stream from here on.
     coherence_set_stream(nullptr, nullptr);
+    if (g_flush_backend == backend) {
+        g_flush_backend = nullptr;
+    }
     if (backend->stream) {
         cudaStreamDestroy(backend->stream);
     }
@@ -1130,7 +1255,8 @@ extern "C" int cuda_backend_enable_device_execution(CudaBackend *backend) {
     }
     check(cudaSetDevice(backend->device), "cudaSetDevice");
     coherence_install_fault_handler();
-    coherence_set_stream(backend->stream, nullptr);
+    coherence_set_stream(backend->stream, flush_hook);
+    g_flush_backend = backend;
     backend->table = make_table(backend);
     backend->set_table(&backend->table);
     backend->set_allocator(coherent_allocate, coherent_release, backend);

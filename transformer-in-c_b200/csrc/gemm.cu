@@ -113,6 +113,46 @@ int gemm_forward(const float *x, const float *w, float *y, int m, int k, int n,
     return run(g, precision, stream);
 }
 
+int gemm_forward_fused(const float *x, const float *w, float *y, int m, int k,
+                       int n, const GemmEpilogue &e, int precision,
+                       cudaStream_t stream) {
+    TcGemm g = {x, w, y, e.bias, m, n, k, k, n, n, false, true, false};
+    if (e.gelu_out) {
+        g.d2 = e.gelu_out;
+        g.ldd2 = n;
+    } else if (e.residual_out) {
+        g.d2 = e.residual_out;
+        g.ldd2 = n;
+        g.residual = e.residual;
+        g.ld_residual = n;
+    }
+    const int tensor = use_tensor_cores(g, precision);
+    if (tensor < 0) {
+        return -1;
+    }
+    if (tensor == 1 && launch_gemm_tc(g, stream) == 0) {
+        return 0;
+    }
+    if (tensor == 1 && precision == VITB200_PRECISION_TF32) {
+        return -1;
+    }
+    // Separate kernels, same results.
+    g.bias = nullptr;
+    g.d2 = nullptr;
+    g.residual = nullptr;
+    simt(g, stream);
+    const size_t count = size_t(m) * n;
+    if (e.bias) {
+        launch_bias_add(y, e.bias, y, m, n, stream);
+    }
+    if (e.gelu_out) {
+        launch_gelu(y, e.gelu_out, count, stream);
+    } else if (e.residual_out) {
+        launch_add(e.residual, y, e.residual_out, count, stream);
+    }
+    return 0;
+}
+
 int gemm_backward(const float *x, const float *w, const float *dy, float *dx,
                   float *dw, int m, int k, int n, int precision, bool dx_add,
                   cudaStream_t stream) {

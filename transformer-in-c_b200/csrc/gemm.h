@@ -9,11 +9,28 @@
 
 namespace vitb200 {
 
+// What may ride on the forward product's epilogue.  All pointers optional:
+//   bias           y += bias[col]                      (reference ops_bias_add)
+//   gelu_out       gelu_out = gelu(y)                  (ops_gelu on y)
+//   residual(+out) residual_out = residual + y         (ops_residual)
+// gelu_out and residual_out exclude each other.
+struct GemmEpilogue {
+    const float *bias = nullptr;
+    float *gelu_out = nullptr;
+    const float *residual = nullptr;
+    float *residual_out = nullptr;
+};
+
 // precision: one of the VITB200_PRECISION_* selectors.  Returns 0, or -1 when
 // the requested precision cannot serve the shape.
 int gemm_forward(const float *x, const float *w, float *y, int m, int k, int n,
                  int precision, cudaStream_t stream);
 // dx_add = false stores dX instead of adding to it (dX known to be zero).
+// Forward product with the epilogue above; falls back to separate kernels
+// when the tensor-core path does not take the shape.
+int gemm_forward_fused(const float *x, const float *w, float *y, int m, int k,
+                       int n, const GemmEpilogue &epilogue, int precision,
+                       cudaStream_t stream);
 int gemm_backward(const float *x, const float *w, const float *dy, float *dx,
                   float *dw, int m, int k, int n, int precision, bool dx_add,
                   cudaStream_t stream);

@@ -29,6 +29,7 @@
 // to the common teardown, which frees the tensor memory.
 #include "gemm_tc.h"
 #include "kernels.h"
+#include "device_util.cuh"
 
 #include <cuda.h>
 #include <cstdio>
@@ -45,7 +46,7 @@ constexpr int kBlockK = 32;                 // 128 bytes of FP32 per row
 constexpr int kMmaK = 8;                    // tf32 K per instruction
 constexpr int kOperandBytes = kTileM * kBlockK * 4;   // 16 KiB
 constexpr int kStageBytes = 2 * kOperandBytes;
-constexpr int kStages = 3;
+constexpr int kStages = 2;
 constexpr int kSmemBytes = kStages * kStageBytes + 1024;  // + alignment slack
 constexpr int kThreads = 192;
 constexpr int kTmemColumns = 128;
@@ -212,13 +213,20 @@ struct TcParams {
     int a_mn_major, b_mn_major;
     int reduce_add;           // 1: TMA reduce-add into D, 0: plain store
     const float *bias;        // nullable, length n
+    int second;               // 0, kSecondGelu or kSecondResidual
+    const float *residual;    // [m, n] with residual_pitch, for kSecondResidual
+    long long residual_pitch;
     int *status;              // device-visible word, 0 = ok
 };
+
+constexpr int kSecondGelu = 1;
+constexpr int kSecondResidual = 2;
 
 __global__ void __launch_bounds__(kThreads, 1)
 gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a,
                const __grid_constant__ CUtensorMap map_b,
-               const __grid_constant__ CUtensorMap map_d, const TcParams p) {
+               const __grid_constant__ CUtensorMap map_d,
+               const __grid_constant__ CUtensorMap map_d2, const TcParams p) {
     extern __shared__ uint8_t raw_smem[];
     __shared__ __align__(8) uint64_t full_bar[kStages];
     __shared__ __align__(8) uint64_t empty_bar[kStages];
@@ -350,63 +358,98 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a,
                 atomicExch(p.status, 3);
             }
             tcgen05_fence_after();
-            if (ok) {
+            // Pass 0 writes D = acc (+ bias).  Pass 1, when a second output
+            // is asked for, writes D2 = gelu(D) or D2 = D + residual through
+            // the same staging memory after the first store has drained it.
+            const int passes = p.second ? 2 : 1;
 #pragma unroll 1
-                for (int chunk = 0; chunk < kTileN / 32; ++chunk) {
-                    if (n0 + chunk * 32 >= p.n) {
-                        break;
-                    }
-                    uint32_t r[32];
-                    tcgen05_load_32(tmem_base + (uint32_t(quarter * 32) << 16) +
-                                        chunk * 32,
-                                    r);
-                    float *stage_row = reinterpret_cast<float *>(
-                        smem + chunk * kOperandBytes + row * 128);
-#pragma unroll
-                    for (int c = 0; c < 8; ++c) {
-                        float4 v;
-                        v.x = __uint_as_float(r[4 * c + 0]);
-                        v.y = __uint_as_float(r[4 * c + 1]);
-                        v.z = __uint_as_float(r[4 * c + 2]);
-                        v.w = __uint_as_float(r[4 * c + 3]);
-                        if (p.bias) {
-                            const int col = n0 + chunk * 32 + 4 * c;
-                            if (col + 3 < p.n) {
-                                const float4 b = __ldg(
-                                    reinterpret_cast<const float4 *>(p.bias + col));
-                                v.x += b.x; v.y += b.y; v.z += b.z; v.w += b.w;
-                            } else {
-                                if (col + 0 < p.n) v.x += __ldg(p.bias + col + 0);
-                                if (col + 1 < p.n) v.y += __ldg(p.bias + col + 1);
-                                if (col + 2 < p.n) v.z += __ldg(p.bias + col + 2);
-                            }
+            for (int pass = 0; pass < passes; ++pass) {
+                if (ok) {
+#pragma unroll 1
+                    for (int chunk = 0; chunk < kTileN / 32; ++chunk) {
+                        if (n0 + chunk * 32 >= p.n) {
+                            break;
                         }
-                        // 128-byte swizzle: 16-byte chunk c of row r lives at
-                        // chunk position c ^ (r % 8).
-                        *reinterpret_cast<float4 *>(
-                            stage_row + 4 * (c ^ (row & 7))) = v;
+                        uint32_t r[32];
+                        tcgen05_load_32(tmem_base +
+                                            (uint32_t(quarter * 32) << 16) +
+                                            chunk * 32,
+                                        r);
+                        float *stage_row = reinterpret_cast<float *>(
+                            smem + chunk * kOperandBytes + row * 128);
+                        const bool row_live = m0 + row < p.m;
+#pragma unroll
+                        for (int c = 0; c < 8; ++c) {
+                            float4 v;
+                            v.x = __uint_as_float(r[4 * c + 0]);
+                            v.y = __uint_as_float(r[4 * c + 1]);
+                            v.z = __uint_as_float(r[4 * c + 2]);
+                            v.w = __uint_as_float(r[4 * c + 3]);
+                            const int col = n0 + chunk * 32 + 4 * c;
+                            const bool full = col + 3 < p.n;
+                            if (p.bias) {
+                                if (full) {
+                                    const float4 b = __ldg(
+                                        reinterpret_cast<const float4 *>(p.bias + col));
+                                    v.x += b.x; v.y += b.y; v.z += b.z; v.w += b.w;
+                                } else {
+                                    if (col + 0 < p.n) v.x += __ldg(p.bias + col + 0);
+                                    if (col + 1 < p.n) v.y += __ldg(p.bias + col + 1);
+                                    if (col + 2 < p.n) v.z += __ldg(p.bias + col + 2);
+                                }
+                            }
+                            if (pass == 1) {
+                                if (p.second == kSecondGelu) {
+                                    v.x = gelu_value(v.x);
+                                    v.y = gelu_value(v.y);
+                                    v.z = gelu_value(v.z);
+                                    v.w = gelu_value(v.w);
+                                } else if (row_live) {
+                                    const float *res = p.residual +
+                                        size_t(m0 + row) * p.residual_pitch + col;
+                                    if (full) {
+                                        const float4 x = __ldcs(
+                                            reinterpret_cast<const float4 *>(res));
+                                        v.x += x.x; v.y += x.y; v.z += x.z; v.w += x.w;
+                                    } else {
+                                        if (col + 0 < p.n) v.x += res[0];
+                                        if (col + 1 < p.n) v.y += res[1];
+                                        if (col + 2 < p.n) v.z += res[2];
+                                    }
+                                }
+                            }
+                            // 128-byte swizzle: 16-byte chunk c of row r lives
+                            // at chunk position c ^ (r % 8).
+                            *reinterpret_cast<float4 *>(
+                                stage_row + 4 * (c ^ (row & 7))) = v;
+                        }
                     }
+                    // Make the generic-proxy writes visible to the TMA engine.
+                    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
                 }
-                // Make the generic-proxy writes visible to the TMA engine.
-                asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
-            }
-            tcgen05_fence_before();
-            asm volatile("bar.sync 1, 128;" ::: "memory");
-            if (ok && warp == 2 && lane == 0) {
-                for (int chunk = 0; chunk < kTileN / 32; ++chunk) {
-                    const int col = n0 + chunk * 32;
-                    if (col >= p.n) {
-                        break;
+                tcgen05_fence_before();
+                asm volatile("bar.sync 1, 128;" ::: "memory");
+                if (ok && warp == 2 && lane == 0) {
+                    const CUtensorMap *map = pass == 0 ? &map_d : &map_d2;
+                    for (int chunk = 0; chunk < kTileN / 32; ++chunk) {
+                        const int col = n0 + chunk * 32;
+                        if (col >= p.n) {
+                            break;
+                        }
+                        if (p.reduce_add) {
+                            tma_reduce_add_2d(smem + chunk * kOperandBytes, map,
+                                              col, m0);
+                        } else {
+                            tma_store_2d(smem + chunk * kOperandBytes, map, col,
+                                         m0);
+                        }
                     }
-                    if (p.reduce_add) {
-                        tma_reduce_add_2d(smem + chunk * kOperandBytes, &map_d,
-                                          col, m0);
-                    } else {
-                        tma_store_2d(smem + chunk * kOperandBytes, &map_d, col,
-                                     m0);
-                    }
+                    tma_store_commit_and_wait();
                 }
-                tma_store_commit_and_wait();
+                // The staging memory may be rewritten only after the store
+                // has read it.
+                asm volatile("bar.sync 1, 128;" ::: "memory");
+                tcgen05_fence_after();
             }
         }
     }
@@ -534,7 +577,10 @@ bool gemm_tc_supported(const TcGemm &g) {
     };
     return g.m >= 32 && g.n >= 32 && g.k >= 32 && g.lda % 4 == 0 &&
            g.ldb % 4 == 0 && g.ldd % 4 == 0 && aligned(g.a) && aligned(g.b) &&
-           aligned(g.d) && (!g.bias || aligned(g.bias)) && status_word() &&
+           aligned(g.d) && (!g.bias || aligned(g.bias)) &&
+           (!g.d2 || (aligned(g.d2) && g.ldd2 % 4 == 0 && !g.accumulate)) &&
+           (!g.residual || (aligned(g.residual) && g.ld_residual % 4 == 0)) &&
+           status_word() &&
            encode_tiled();
 }
 
@@ -564,7 +610,10 @@ int launch_gemm_tc(const TcGemm &g, cudaStream_t stream) {
         : tensor_map(g.b, g.k, g.n, g.ldb, 32, kTileN, chunks16, true, &map_b);
     const bool ok_d =
         tensor_map(g.d, g.n, g.m, g.ldd, 32, kTileM, chunks16, false, &map_d);
-    if (!ok_a || !ok_b || !ok_d) {
+    CUtensorMap map_d2 = map_d;
+    const bool ok_d2 = !g.d2 ||
+        tensor_map(g.d2, g.n, g.m, g.ldd2, 32, kTileM, chunks16, false, &map_d2);
+    if (!ok_a || !ok_b || !ok_d || !ok_d2) {
         return -1;
     }
     TcParams p;
@@ -591,12 +640,15 @@ int launch_gemm_tc(const TcGemm &g, cudaStream_t stream) {
     p.b_mn_major = g.b_mn_major ? 1 : 0;
     p.reduce_add = g.accumulate ? 1 : 0;
     p.bias = g.bias;
+    p.second = g.d2 ? (g.residual ? kSecondResidual : kSecondGelu) : 0;
+    p.residual = g.residual;
+    p.residual_pitch = g.ld_residual;
     int *device_status = nullptr;
     cudaHostGetDevicePointer(reinterpret_cast<void **>(&device_status),
                              status_word(), 0);
     p.status = device_status;
     gemm_tc_kernel<<<dim3(tiles, 1, splits), kThreads, kSmemBytes, stream>>>(
-        map_a, map_b, map_d, p);
+        map_a, map_b, map_d, map_d2, p);
     ++g_kernel_launches;
     return 0;
 }

@@ -19,6 +19,13 @@ struct TcGemm {
     int m, n, k;
     long long lda, ldb, ldd;
     bool a_mn_major, b_mn_major, accumulate;
+    // Optional second output of the same shape (not with accumulate):
+    //   residual == nullptr:  d2 = gelu(d)          (d = A*B + bias)
+    //   residual != nullptr:  d2 = d + residual
+    float *d2 = nullptr;
+    long long ldd2 = 0;
+    const float *residual = nullptr;
+    long long ld_residual = 0;
 };
 
 bool gemm_tc_supported(const TcGemm &gemm);
