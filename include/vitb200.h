@@ -136,6 +136,13 @@ int vitb200_profile_entry(CudaBackend *backend, size_t index, const char **name,
 
 int vitb200_k_gemm(const float *x, const float *w, float *y, size_t m,
                    size_t k, size_t n, int precision, void *stream);
+/* Forward product with what the host issues right after it folded into the
+ * epilogue: y = x w (+ bias), and optionally gelu_out = gelu(y) or
+ * residual_out = residual + y (not both).  Unused pointers are NULL. */
+int vitb200_k_gemm_fused(const float *x, const float *w, float *y,
+                         const float *bias, float *gelu_out,
+                         const float *residual, float *residual_out, size_t m,
+                         size_t k, size_t n, int precision, void *stream);
 int vitb200_k_gemm_backward(const float *x, const float *w, const float *dy,
                             float *dx, float *dw, size_t m, size_t k, size_t n,
                             int precision, void *stream);

@@ -10,18 +10,21 @@
 // transposed copy.  Nothing is converted or re-laid-out in global memory: TMA
 // rounds FP32 to TF32 while it fills the shared-memory stages.
 //
-// One CTA computes one 128 x 128 output tile over a slice of the reduction:
+// Persistent CTAs (one per SM) walk work items = (128 x 128 output tile,
+// slice of the reduction); three warp roles meet only through mbarriers:
 //
 //   warp 0      TMA producer: per 32-deep reduction block, one 128B-swizzled
 //               box (K-major) or four 32x32 boxes (MN-major) per operand into
-//               a ring of shared-memory stages, signalled through mbarriers
-//   warp 1      allocates 128 TMEM columns, issues four K=8 tcgen05.mma per
-//               block from one lane, releases stages with tcgen05.commit
-//   warps 2-5   epilogue: tcgen05.ld the accumulator (one TMEM lane quarter
-//               per warp), add the bias if asked, write a 128B-swizzled tile
-//               into the (now idle) stage memory and hand it to TMA, as a
-//               plain store or as an FP32 reduce-add (for "+=" outputs and for
-//               reductions split across CTAs)
+//               a 5- or 6-stage shared-memory ring
+//   warp 1      allocates 256 TMEM columns (two accumulators), issues four
+//               K=8 tcgen05.mma per block from one lane, releases stages with
+//               tcgen05.commit, and signals a finished accumulator
+//   warps 2-5   epilogue, overlapped with the next item's loads and MMAs:
+//               each warp tcgen05.ld's its 32 rows, adds the bias, optionally
+//               derives a second output (GELU, or + residual), stages 32x32
+//               blocks in its own 128B-swizzled buffers and issues its own TMA
+//               stores (plain, or FP32 reduce-add for "+=" outputs and for
+//               reductions split across CTAs); no block-wide barrier is used
 //
 // Partial tiles need no special code: TMA zero-fills out-of-range loads and
 // clips out-of-range stores.  Every wait on an mbarrier is bounded in time;
@@ -46,10 +49,12 @@ constexpr int kBlockK = 32;                 // 128 bytes of FP32 per row
 constexpr int kMmaK = 8;                    // tf32 K per instruction
 constexpr int kOperandBytes = kTileM * kBlockK * 4;   // 16 KiB
 constexpr int kStageBytes = 2 * kOperandBytes;
-constexpr int kStages = 2;
-constexpr int kSmemBytes = kStages * kStageBytes + 1024;  // + alignment slack
+// The load ring takes whatever shared memory the epilogue staging leaves:
+// 6 stages next to one staged output (2 buffers), 5 next to two.
+constexpr int kMaxStages = 6;
+constexpr int kSmemLimit = 227 * 1024 - 1024;   // leave room for static shared memory
 constexpr int kThreads = 192;
-constexpr int kTmemColumns = 128;
+constexpr int kTmemColumns = 256;                  // two 128-column accumulators
 constexpr unsigned long long kWaitLimitNs = 2000000000ull;  // 2 s
 
 // ---- PTX wrappers ----------------------------------------------------------
@@ -209,7 +214,9 @@ struct TcParams {
     int m, n;                 // output extents
     int k_blocks;             // ceil(reduction / 32)
     int k_blocks_per_split;
-    int n_tiles;
+    int splits;
+    int stages;               // depth of the load ring
+    int m_tiles, n_tiles;
     int a_mn_major, b_mn_major;
     int reduce_add;           // 1: TMA reduce-add into D, 0: plain store
     const float *bias;        // nullable, length n
@@ -222,34 +229,43 @@ struct TcParams {
 constexpr int kSecondGelu = 1;
 constexpr int kSecondResidual = 2;
 
+__device__ __forceinline__ void mbarrier_arrive(uint64_t *bar) {
+    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_address(bar))
+                 : "memory");
+}
+
+// Persistent kernel: each CTA walks work items (output tile x reduction
+// slice) item = blockIdx.x, blockIdx.x + gridDim.x, ...; the three roles run
+// the same sequence and meet only through mbarriers, so the loads and MMAs of
+// item i+1 overlap the epilogue of item i (two accumulator buffers in TMEM).
 __global__ void __launch_bounds__(kThreads, 1)
 gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a,
                const __grid_constant__ CUtensorMap map_b,
                const __grid_constant__ CUtensorMap map_d,
                const __grid_constant__ CUtensorMap map_d2, const TcParams p) {
     extern __shared__ uint8_t raw_smem[];
-    __shared__ __align__(8) uint64_t full_bar[kStages];
-    __shared__ __align__(8) uint64_t empty_bar[kStages];
-    __shared__ __align__(8) uint64_t accumulator_bar;
+    __shared__ __align__(8) uint64_t full_bar[kMaxStages];
+    __shared__ __align__(8) uint64_t empty_bar[kMaxStages];
+    __shared__ __align__(8) uint64_t tmem_full_bar[2];
+    __shared__ __align__(8) uint64_t tmem_empty_bar[2];
     __shared__ uint32_t tmem_base_slot;
 
     uint8_t *smem = reinterpret_cast<uint8_t *>(
         (reinterpret_cast<uintptr_t>(raw_smem) + 1023) & ~uintptr_t(1023));
+    const int kStages = p.stages;
+    uint8_t *staging = smem + kStages * kStageBytes;   // [output][buffer] 16 KiB
     const int warp = threadIdx.x >> 5;
     const int lane = threadIdx.x & 31;
-    const int tile = blockIdx.x;
-    const int m0 = (tile / p.n_tiles) * kTileM;
-    const int n0 = (tile % p.n_tiles) * kTileN;
-    const int kb_begin = blockIdx.z * p.k_blocks_per_split;
-    const int kb_end = min(p.k_blocks, kb_begin + p.k_blocks_per_split);
-    const int kb_count = kb_end - kb_begin;
 
     if (threadIdx.x == 0) {
         for (int s = 0; s < kStages; ++s) {
             mbarrier_init(&full_bar[s], 1);
             mbarrier_init(&empty_bar[s], 1);
         }
-        mbarrier_init(&accumulator_bar, 1);
+        for (int b = 0; b < 2; ++b) {
+            mbarrier_init(&tmem_full_bar[b], 1);
+            mbarrier_init(&tmem_empty_bar[b], 4);   // one arrival per epilogue warp
+        }
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
     if (warp == 1) {
@@ -265,14 +281,22 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a,
     __syncthreads();
     tcgen05_fence_after();
     const uint32_t tmem_base = tmem_base_slot;
+    const int tiles = p.m_tiles * p.n_tiles;
+    const int items = tiles * p.splits;
     bool ok = true;
 
-    if (kb_count > 0) {
-        if (warp == 0) {
-            if (lane == 0) {
-                for (int i = 0; i < kb_count && ok; ++i) {
-                    const int s = i % kStages;
-                    const uint32_t phase = (i / kStages) & 1;
+    if (warp == 0) {
+        if (lane == 0) {
+            int fill = 0;   // k-blocks loaded so far, across items
+            for (int item = blockIdx.x; item < items && ok; item += gridDim.x) {
+                const int tile = item % tiles;
+                const int m0 = (tile / p.n_tiles) * kTileM;
+                const int n0 = (tile % p.n_tiles) * kTileN;
+                const int kb_begin = (item / tiles) * p.k_blocks_per_split;
+                const int kb_end = min(p.k_blocks, kb_begin + p.k_blocks_per_split);
+                for (int kb = kb_begin; kb < kb_end; ++kb, ++fill) {
+                    const int s = fill % kStages;
+                    const uint32_t phase = (fill / kStages) & 1;
                     ok = mbarrier_wait(&empty_bar[s], phase ^ 1);
                     if (!ok) {
                         atomicExch(p.status, 1);
@@ -280,7 +304,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a,
                     }
                     uint8_t *a_tile = smem + s * kStageBytes;
                     uint8_t *b_tile = a_tile + kOperandBytes;
-                    const int k0 = (kb_begin + i) * kBlockK;
+                    const int k0 = kb * kBlockK;
                     mbarrier_expect_tx(&full_bar[s], kStageBytes);
                     if (p.a_mn_major) {
                         for (int j = 0; j < 4; ++j) {
@@ -300,31 +324,49 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a,
                     }
                 }
             }
-        } else if (warp == 1) {
-            if (lane == 0) {
-                // kind::tf32, FP32 accumulator, M = 128, N = 128.
-                const uint32_t idesc = (1u << 4) | (2u << 7) | (2u << 10) |
-                                       (uint32_t(p.a_mn_major) << 15) |
-                                       (uint32_t(p.b_mn_major) << 16) |
-                                       (uint32_t(kTileN >> 3) << 17) |
-                                       (uint32_t(kTileM >> 4) << 24);
-                // K-major: 8-row groups 1024 B apart, K steps of 32 B inside the
-                // swizzled row.  MN-major: 32-wide MN atoms one box (4096 B)
-                // apart, groups of four 128 B reduction rows 512 B apart, K
-                // steps of eight rows.
-                const uint32_t a_lead = p.a_mn_major ? 4096 : 16;
-                const uint32_t b_lead = p.b_mn_major ? 4096 : 16;
-                const uint32_t a_stride = p.a_mn_major ? 512 : 1024;
-                const uint32_t b_stride = p.b_mn_major ? 512 : 1024;
-                const uint32_t a_step = p.a_mn_major ? 1024 : kMmaK * 4;
-                const uint32_t b_step = p.b_mn_major ? 1024 : kMmaK * 4;
-                const uint32_t a_layout =
-                    p.a_mn_major ? kLayoutSwizzle128Base32 : kLayoutSwizzle128;
-                const uint32_t b_layout =
-                    p.b_mn_major ? kLayoutSwizzle128Base32 : kLayoutSwizzle128;
-                for (int i = 0; i < kb_count; ++i) {
-                    const int s = i % kStages;
-                    const uint32_t phase = (i / kStages) & 1;
+        }
+    } else if (warp == 1) {
+        if (lane == 0) {
+            // kind::tf32, FP32 accumulator, M = 128, N = 128.
+            const uint32_t idesc = (1u << 4) | (2u << 7) | (2u << 10) |
+                                   (uint32_t(p.a_mn_major) << 15) |
+                                   (uint32_t(p.b_mn_major) << 16) |
+                                   (uint32_t(kTileN >> 3) << 17) |
+                                   (uint32_t(kTileM >> 4) << 24);
+            // K-major: 8-row groups 1024 B apart, K steps of 32 B inside the
+            // swizzled row.  MN-major: 32-wide MN atoms one box (4096 B)
+            // apart, groups of four 128 B reduction rows 512 B apart, K
+            // steps of eight rows.
+            const uint32_t a_lead = p.a_mn_major ? 4096 : 16;
+            const uint32_t b_lead = p.b_mn_major ? 4096 : 16;
+            const uint32_t a_stride = p.a_mn_major ? 512 : 1024;
+            const uint32_t b_stride = p.b_mn_major ? 512 : 1024;
+            const uint32_t a_step = p.a_mn_major ? 1024 : kMmaK * 4;
+            const uint32_t b_step = p.b_mn_major ? 1024 : kMmaK * 4;
+            const uint32_t a_layout =
+                p.a_mn_major ? kLayoutSwizzle128Base32 : kLayoutSwizzle128;
+            const uint32_t b_layout =
+                p.b_mn_major ? kLayoutSwizzle128Base32 : kLayoutSwizzle128;
+            int drain = 0;   // k-blocks consumed so far, across items
+            int local = 0;   // items processed by this CTA
+            for (int item = blockIdx.x; item < items && ok;
+                 item += gridDim.x, ++local) {
+                const int tile_splits = item / tiles;
+                const int kb_begin = tile_splits * p.k_blocks_per_split;
+                const int kb_end = min(p.k_blocks, kb_begin + p.k_blocks_per_split);
+                const int buffer = local & 1;
+                const uint32_t buffer_phase = (local >> 1) & 1;
+                // The epilogue must have emptied this accumulator buffer.
+                ok = mbarrier_wait(&tmem_empty_bar[buffer], buffer_phase ^ 1);
+                if (!ok) {
+                    atomicExch(p.status, 4);
+                    break;
+                }
+                tcgen05_fence_after();
+                const uint32_t accumulator = tmem_base + buffer * kTileN;
+                for (int kb = kb_begin; kb < kb_end; ++kb, ++drain) {
+                    const int s = drain % kStages;
+                    const uint32_t phase = (drain / kStages) & 1;
                     ok = mbarrier_wait(&full_bar[s], phase);
                     if (!ok) {
                         atomicExch(p.status, 2);
@@ -339,118 +381,162 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a,
                             a_base + ks * a_step, a_lead, a_stride, a_layout);
                         const uint64_t db = operand_descriptor(
                             b_base + ks * b_step, b_lead, b_stride, b_layout);
-                        tcgen05_mma_tf32(tmem_base, da, db, idesc,
-                                         (i > 0 || ks > 0) ? 1u : 0u);
+                        tcgen05_mma_tf32(accumulator, da, db, idesc,
+                                         (kb > kb_begin || ks > 0) ? 1u : 0u);
                     }
                     tcgen05_commit(&empty_bar[s]);
                 }
                 if (ok) {
-                    tcgen05_commit(&accumulator_bar);
+                    tcgen05_commit(&tmem_full_bar[buffer]);
                 }
             }
-        } else {
-            // Epilogue warps 2..5 own TMEM lane quarters 2, 3, 0, 1.
-            const int quarter = warp & 3;
-            const int row = quarter * 32 + lane;
-            ok = mbarrier_wait(&accumulator_bar, 0);
+        }
+    } else {
+        // Epilogue warps 2..5 own TMEM lane quarters 2, 3, 0, 1, i.e. 32 rows
+        // of the tile each.  A warp stages its own 32 x 32 blocks (4 KiB, two
+        // buffers per output) and issues its own TMA stores, so the epilogue
+        // needs no block-wide barrier at all.
+        const int quarter = warp & 3;
+        const int outputs = p.second ? 2 : 1;
+        uint8_t *my_staging =
+            staging + quarter * (outputs * 2 * 4096);   // [output][buffer]
+        int local = 0;
+        int stored = 0;   // blocks handed to TMA so far (selects the buffer)
+        for (int item = blockIdx.x; item < items; item += gridDim.x, ++local) {
+            const int tile = item % tiles;
+            const int m0 = (tile / p.n_tiles) * kTileM + quarter * 32;
+            const int n0 = (tile % p.n_tiles) * kTileN;
+            const int buffer = local & 1;
+            const uint32_t buffer_phase = (local >> 1) & 1;
+            ok = mbarrier_wait(&tmem_full_bar[buffer], buffer_phase);
             ok = __all_sync(0xffffffffu, ok);   // keep the warp in step
             if (!ok) {
                 atomicExch(p.status, 3);
+                break;
             }
             tcgen05_fence_after();
-            // Pass 0 writes D = acc (+ bias).  Pass 1, when a second output
-            // is asked for, writes D2 = gelu(D) or D2 = D + residual through
-            // the same staging memory after the first store has drained it.
-            const int passes = p.second ? 2 : 1;
 #pragma unroll 1
-            for (int pass = 0; pass < passes; ++pass) {
-                if (ok) {
-#pragma unroll 1
-                    for (int chunk = 0; chunk < kTileN / 32; ++chunk) {
-                        if (n0 + chunk * 32 >= p.n) {
-                            break;
-                        }
-                        uint32_t r[32];
-                        tcgen05_load_32(tmem_base +
-                                            (uint32_t(quarter * 32) << 16) +
-                                            chunk * 32,
-                                        r);
-                        float *stage_row = reinterpret_cast<float *>(
-                            smem + chunk * kOperandBytes + row * 128);
-                        const bool row_live = m0 + row < p.m;
+            for (int chunk = 0; chunk < kTileN / 32; ++chunk) {
+                const int col0 = n0 + chunk * 32;
+                const bool chunk_live = col0 < p.n && m0 < p.m;
+                // Bias for these 32 columns, requested before the accumulator
+                // so the two latencies overlap.
+                float4 bias[8];
+                if (p.bias && chunk_live) {
 #pragma unroll
-                        for (int c = 0; c < 8; ++c) {
-                            float4 v;
-                            v.x = __uint_as_float(r[4 * c + 0]);
-                            v.y = __uint_as_float(r[4 * c + 1]);
-                            v.z = __uint_as_float(r[4 * c + 2]);
-                            v.w = __uint_as_float(r[4 * c + 3]);
-                            const int col = n0 + chunk * 32 + 4 * c;
-                            const bool full = col + 3 < p.n;
-                            if (p.bias) {
-                                if (full) {
-                                    const float4 b = __ldg(
-                                        reinterpret_cast<const float4 *>(p.bias + col));
-                                    v.x += b.x; v.y += b.y; v.z += b.z; v.w += b.w;
-                                } else {
-                                    if (col + 0 < p.n) v.x += __ldg(p.bias + col + 0);
-                                    if (col + 1 < p.n) v.y += __ldg(p.bias + col + 1);
-                                    if (col + 2 < p.n) v.z += __ldg(p.bias + col + 2);
-                                }
-                            }
-                            if (pass == 1) {
-                                if (p.second == kSecondGelu) {
-                                    v.x = gelu_value(v.x);
-                                    v.y = gelu_value(v.y);
-                                    v.z = gelu_value(v.z);
-                                    v.w = gelu_value(v.w);
-                                } else if (row_live) {
-                                    const float *res = p.residual +
-                                        size_t(m0 + row) * p.residual_pitch + col;
-                                    if (full) {
-                                        const float4 x = __ldcs(
-                                            reinterpret_cast<const float4 *>(res));
-                                        v.x += x.x; v.y += x.y; v.z += x.z; v.w += x.w;
-                                    } else {
-                                        if (col + 0 < p.n) v.x += res[0];
-                                        if (col + 1 < p.n) v.y += res[1];
-                                        if (col + 2 < p.n) v.z += res[2];
-                                    }
-                                }
-                            }
-                            // 128-byte swizzle: 16-byte chunk c of row r lives
-                            // at chunk position c ^ (r % 8).
-                            *reinterpret_cast<float4 *>(
-                                stage_row + 4 * (c ^ (row & 7))) = v;
-                        }
-                    }
-                    // Make the generic-proxy writes visible to the TMA engine.
-                    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
-                }
-                tcgen05_fence_before();
-                asm volatile("bar.sync 1, 128;" ::: "memory");
-                if (ok && warp == 2 && lane == 0) {
-                    const CUtensorMap *map = pass == 0 ? &map_d : &map_d2;
-                    for (int chunk = 0; chunk < kTileN / 32; ++chunk) {
-                        const int col = n0 + chunk * 32;
-                        if (col >= p.n) {
-                            break;
-                        }
-                        if (p.reduce_add) {
-                            tma_reduce_add_2d(smem + chunk * kOperandBytes, map,
-                                              col, m0);
+                    for (int c = 0; c < 8; ++c) {
+                        const int col = col0 + 4 * c;
+                        if (col + 3 < p.n) {
+                            bias[c] = __ldg(
+                                reinterpret_cast<const float4 *>(p.bias + col));
                         } else {
-                            tma_store_2d(smem + chunk * kOperandBytes, map, col,
-                                         m0);
+                            bias[c].x = col + 0 < p.n ? __ldg(p.bias + col + 0) : 0.f;
+                            bias[c].y = col + 1 < p.n ? __ldg(p.bias + col + 1) : 0.f;
+                            bias[c].z = col + 2 < p.n ? __ldg(p.bias + col + 2) : 0.f;
+                            bias[c].w = 0.f;
                         }
                     }
-                    tma_store_commit_and_wait();
                 }
-                // The staging memory may be rewritten only after the store
-                // has read it.
-                asm volatile("bar.sync 1, 128;" ::: "memory");
-                tcgen05_fence_after();
+                uint32_t r[32];
+                if (chunk_live) {
+                    tcgen05_load_32(tmem_base + (uint32_t(quarter * 32) << 16) +
+                                        buffer * kTileN + chunk * 32,
+                                    r);
+                }
+                if (chunk == kTileN / 32 - 1) {
+                    // Everything this warp needs is in registers: hand the
+                    // accumulator buffer back to the MMA warp.
+                    tcgen05_fence_before();
+                    __syncwarp();
+                    if (lane == 0) {
+                        mbarrier_arrive(&tmem_empty_bar[buffer]);
+                    }
+                }
+                if (!chunk_live) {
+                    continue;   // uniform across the warp
+                }
+                // The buffer about to be rewritten was last read by the store
+                // this warp issued two blocks ago.
+                if (lane == 0) {
+                    asm volatile("cp.async.bulk.wait_group.read 1;" ::: "memory");
+                }
+                __syncwarp();
+                const int slot = stored & 1;
+                ++stored;
+                float *first = reinterpret_cast<float *>(my_staging + slot * 4096);
+                float *second =
+                    reinterpret_cast<float *>(my_staging + (2 + slot) * 4096);
+#pragma unroll
+                for (int c = 0; c < 8; ++c) {
+                    float4 v;
+                    v.x = __uint_as_float(r[4 * c + 0]);
+                    v.y = __uint_as_float(r[4 * c + 1]);
+                    v.z = __uint_as_float(r[4 * c + 2]);
+                    v.w = __uint_as_float(r[4 * c + 3]);
+                    if (p.bias) {
+                        v.x += bias[c].x; v.y += bias[c].y;
+                        v.z += bias[c].z; v.w += bias[c].w;
+                    }
+                    // 128-byte swizzle: 16-byte chunk c of row r lives at
+                    // chunk position c ^ (r % 8).
+                    const int offset = lane * 32 + 4 * (c ^ (lane & 7));
+                    *reinterpret_cast<float4 *>(first + offset) = v;
+                    if (p.second == kSecondGelu) {
+                        v.x = gelu_value_fast(v.x);
+                        v.y = gelu_value_fast(v.y);
+                        v.z = gelu_value_fast(v.z);
+                        v.w = gelu_value_fast(v.w);
+                        *reinterpret_cast<float4 *>(second + offset) = v;
+                    }
+                }
+                if (p.second == kSecondResidual) {
+                    // D2 = D + residual.  In the accumulator layout a lane
+                    // owns a row, which would read the residual one row per
+                    // lane; instead the staged block is walked with eight
+                    // lanes per row, so every load covers four full 128-byte
+                    // row segments.
+                    __syncwarp();
+                    const int c = lane & 7;
+                    const int col = col0 + 4 * c;
+#pragma unroll
+                    for (int i = 0; i < 8; ++i) {
+                        const int row = (lane >> 3) + 4 * i;
+                        const int offset = row * 32 + 4 * (c ^ (row & 7));
+                        float4 v = *reinterpret_cast<const float4 *>(first + offset);
+                        if (m0 + row < p.m) {
+                            const float *res = p.residual +
+                                size_t(m0 + row) * p.residual_pitch + col;
+                            if (col + 3 < p.n) {
+                                const float4 x =
+                                    __ldcs(reinterpret_cast<const float4 *>(res));
+                                v.x += x.x; v.y += x.y; v.z += x.z; v.w += x.w;
+                            } else {
+                                if (col + 0 < p.n) v.x += res[0];
+                                if (col + 1 < p.n) v.y += res[1];
+                                if (col + 2 < p.n) v.z += res[2];
+                            }
+                        }
+                        *reinterpret_cast<float4 *>(second + offset) = v;
+                    }
+                }
+                // Make the generic-proxy writes visible to the TMA engine.
+                asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+                __syncwarp();
+                if (lane == 0) {
+                    if (p.reduce_add) {
+                        tma_reduce_add_2d(first, &map_d, col0, m0);
+                    } else {
+                        tma_store_2d(first, &map_d, col0, m0);
+                    }
+                    if (outputs == 2) {
+                        tma_store_2d(second, &map_d2, col0, m0);
+                    }
+                    asm volatile("cp.async.bulk.commit_group;" ::: "memory");
+                }
             }
+        }
+        if (lane == 0) {
+            asm volatile("cp.async.bulk.wait_group 0;" ::: "memory");
         }
     }
     tcgen05_fence_before();
@@ -592,7 +678,7 @@ int launch_gemm_tc(const TcGemm &g, cudaStream_t stream) {
     if (!configured) {
         if (cudaFuncSetAttribute(gemm_tc_kernel,
                                  cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                 kSmemBytes) != cudaSuccess) {
+                                 kSmemLimit) != cudaSuccess) {
             return -1;
         }
         configured = true;
@@ -609,10 +695,10 @@ int launch_gemm_tc(const TcGemm &g, cudaStream_t stream) {
         ? tensor_map(g.b, g.n, g.k, g.ldb, 32, 32, chunks32, true, &map_b)
         : tensor_map(g.b, g.k, g.n, g.ldb, 32, kTileN, chunks16, true, &map_b);
     const bool ok_d =
-        tensor_map(g.d, g.n, g.m, g.ldd, 32, kTileM, chunks16, false, &map_d);
+        tensor_map(g.d, g.n, g.m, g.ldd, 32, 32, chunks16, false, &map_d);
     CUtensorMap map_d2 = map_d;
     const bool ok_d2 = !g.d2 ||
-        tensor_map(g.d2, g.n, g.m, g.ldd2, 32, kTileM, chunks16, false, &map_d2);
+        tensor_map(g.d2, g.n, g.m, g.ldd2, 32, 32, chunks16, false, &map_d2);
     if (!ok_a || !ok_b || !ok_d || !ok_d2) {
         return -1;
     }
@@ -622,6 +708,7 @@ int launch_gemm_tc(const TcGemm &g, cudaStream_t stream) {
     p.k_blocks = (g.k + kBlockK - 1) / kBlockK;
     p.n_tiles = (g.n + kTileN - 1) / kTileN;
     const int m_tiles = (g.m + kTileM - 1) / kTileM;
+    p.m_tiles = m_tiles;
     const int tiles = m_tiles * p.n_tiles;
     int splits = 1;
     if (g.accumulate) {
@@ -647,7 +734,18 @@ int launch_gemm_tc(const TcGemm &g, cudaStream_t stream) {
     cudaHostGetDevicePointer(reinterpret_cast<void **>(&device_status),
                              status_word(), 0);
     p.status = device_status;
-    gemm_tc_kernel<<<dim3(tiles, 1, splits), kThreads, kSmemBytes, stream>>>(
+    p.splits = splits;
+    // One persistent CTA per SM (the shared-memory ring fills an SM), fewer
+    // when there is less work than SMs.
+    const long long items = (long long)tiles * splits;
+    const unsigned grid = unsigned(items < 148 ? items : 148);
+    const int staging_bytes = (g.d2 ? 4 : 2) * kOperandBytes;
+    p.stages = (kSmemLimit - 1024 - staging_bytes) / kStageBytes;
+    if (p.stages > kMaxStages) {
+        p.stages = kMaxStages;
+    }
+    const int smem_bytes = p.stages * kStageBytes + staging_bytes + 1024;
+    gemm_tc_kernel<<<grid, kThreads, smem_bytes, stream>>>(
         map_a, map_b, map_d, map_d2, p);
     ++g_kernel_launches;
     return 0;
