@@ -99,6 +99,35 @@ def test_gemm_tf32_tensor_cores(lib, m, k, n):
     close(host(tdw), dw0 + x.T @ dy, 2e-3)
 
 
+@pytest.mark.parametrize("precision", [FP32, TF32], ids=["fp32", "tf32"])
+@pytest.mark.parametrize("m,k,n", [(1600, 128, 384), (300, 64, 96), (1000, 512, 128)])
+@pytest.mark.parametrize("extra", ["bias", "bias+gelu", "bias+residual", "gelu"])
+def test_gemm_fused_epilogues(lib, m, k, n, extra, precision):
+    """y = x w + bias with gelu(y) or residual + y produced by the same launch
+    (what ops_gemm, ops_bias_add and ops_gelu / ops_residual compute in
+    sequence, reference src/vit.c:493-535)."""
+    rng = np.random.RandomState(m + k + n)
+    x, w, bias, res = rng.randn(m, k), rng.randn(k, n) / np.sqrt(k), rng.randn(n), rng.randn(m, n)
+    tx, tw, tb, tr = dev(x), dev(w), dev(bias), dev(res)
+    ty, ty2 = torch.empty(m, n, device="cuda"), torch.empty(m, n, device="cuda")
+    use_bias = "bias" in extra
+    assert lib.vitb200_k_gemm_fused(
+        ptr(tx), ptr(tw), ptr(ty), ptr(tb) if use_bias else None,
+        ptr(ty2) if "gelu" in extra else None,
+        ptr(tr) if "residual" in extra else None,
+        ptr(ty2) if "residual" in extra else None,
+        size(m), size(k), size(n), precision, None) == 0
+    torch.cuda.synchronize()
+    assert lib.vitb200_tensor_core_status() == 0
+    tolerance = 1e-5 if precision == FP32 else 2e-3
+    y = x @ w + (bias if use_bias else 0.0)
+    close(host(ty), y, tolerance)
+    if "gelu" in extra:
+        close(host(ty2), vo.gelu(y), tolerance)
+    if "residual" in extra:
+        close(host(ty2), y + res, tolerance)
+
+
 def test_gemm_tf32_declines_unaligned_shapes(lib):
     """Row pitches that are not multiples of 16 bytes cannot be described to
     TMA; an explicit TF32 request is refused rather than silently changed."""
