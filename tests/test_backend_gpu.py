@@ -295,3 +295,34 @@ def test_tensors_allocated_before_enable_fall_back_to_cpu(vit_host_module,
         np.testing.assert_array_equal(grad, expected_grads[name])
     backend.disable()
     cpu.close()
+
+
+def test_evaluation_and_prediction_match_cpu_reference(vit_host_module, host_lib,
+                                                       backend):
+    """The reference's inference entry points (vit_model_evaluate,
+    vit_model_predict_probabilities: 256-sample chunks plus a remainder, cache
+    allocated and freed inside the call) through the backend."""
+    vh = vit_host_module
+    config, samples = (1, 28, 28, 4, 32, 4, 2, 11), 300
+    images, labels = vh.synthetic_batch(samples, 28, 28, 11, 17)
+    backend.disable()
+    cpu = vh.VitHost(host_lib, config, 1)
+    cpu_accuracy, cpu_loss, cpu_rate = cpu.evaluate(images, labels)
+    cpu_probabilities = cpu.predict(images[:40])
+    backend.enable()
+    backend.set_gemm_precision(FP32)
+    launches = backend.kernel_launches()
+    gpu = vh.VitHost(host_lib, config, 1)
+    gpu_accuracy, gpu_loss, gpu_rate = gpu.evaluate(images, labels)
+    gpu_probabilities = gpu.predict(images[:40])
+    assert backend.kernel_launches() > launches
+    assert abs(gpu_loss - cpu_loss) <= 1e-4
+    assert abs(gpu_accuracy - cpu_accuracy) <= 1.0 / samples
+    np.testing.assert_allclose(gpu_probabilities, cpu_probabilities, rtol=0,
+                               atol=1e-5)
+    np.testing.assert_allclose(gpu_probabilities.sum(axis=1), 1.0, atol=1e-5)
+    assert gpu_rate > 0 and cpu_rate > 0
+    backend.set_gemm_precision(-1)
+    gpu.close()
+    cpu.close()
+    backend.disable()

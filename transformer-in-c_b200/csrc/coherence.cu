@@ -79,13 +79,35 @@ Region *find_containing(uintptr_t address) {
     return address < it->first + region.mapped ? &region : nullptr;
 }
 
+// Device buffers of released tensors, kept for reuse by size: the host's
+// evaluation entry points allocate and free a whole activation cache per call
+// (reference src/vit.c:1371-1375), and cudaMalloc / cudaFree would otherwise
+// dominate them.  Every kernel runs on one stream, so a recycled buffer cannot
+// be touched by work enqueued before its previous owner was released.
+std::multimap<size_t, float *> &buffer_pool() {
+    static std::multimap<size_t, float *> *pool =
+        new std::multimap<size_t, float *>();
+    return *pool;
+}
+size_t g_pooled_bytes = 0;
+constexpr size_t kPoolLimitBytes = size_t(8) << 30;
+
 void ensure_device_buffer(Region &region) {
-    if (!region.device) {
+    if (region.device) {
+        return;
+    }
+    auto &pool = buffer_pool();
+    auto found = pool.find(region.mapped);
+    if (found != pool.end()) {
+        region.device = found->second;
+        pool.erase(found);
+        g_pooled_bytes -= region.mapped;
+    } else {
         void *memory = nullptr;
         check(cudaMalloc(&memory, region.mapped), "cudaMalloc");
         region.device = static_cast<float *>(memory);
-        g_stats.device_bytes += region.mapped;
     }
+    g_stats.device_bytes += region.mapped;
 }
 
 void materialise_zero(Region &region, cudaStream_t stream) {
@@ -214,8 +236,13 @@ void coherent_release(void *context, void *memory) {
     Region region = it->second;
     regions.erase(it);
     if (region.device) {
-        // cudaFree waits for every kernel that may still use the buffer.
-        cudaFree(region.device);
+        if (g_pooled_bytes + region.mapped <= kPoolLimitBytes) {
+            buffer_pool().emplace(region.mapped, region.device);
+            g_pooled_bytes += region.mapped;
+        } else {
+            // cudaFree waits for every kernel that may still use the buffer.
+            cudaFree(region.device);
+        }
         g_stats.device_bytes -= region.mapped;
     }
     munmap(region.mirror, region.mapped);

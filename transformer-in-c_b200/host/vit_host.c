@@ -254,3 +254,27 @@ size_t vithost_block_tensor(VitHost *host, size_t layer, const char *name,
     }
     return 0;
 }
+
+/* Inference entry points of the reference, unchanged: chunked forward passes
+ * with the softmax / loss / argmax on the host (vit.c:1325-1403).  With a
+ * backend enabled the forward passes run on the device and the host reads
+ * the logits after each chunk's synchronise. */
+int vithost_evaluate(VitHost *host, const float *images, const size_t *labels,
+                     size_t sample_count, float *accuracy, float *average_loss,
+                     double *samples_per_second) {
+    ViTEvaluationMetrics metrics = {0};
+    const int result = vit_model_evaluate(&host->model, images, labels,
+                                          sample_count, &metrics);
+    if (result == 0) {
+        *accuracy = metrics.accuracy;
+        *average_loss = metrics.average_loss;
+        *samples_per_second = metrics.samples_per_second;
+    }
+    return result;
+}
+
+int vithost_predict(VitHost *host, const float *images, size_t sample_count,
+                    float *probabilities) {
+    return vit_model_predict_probabilities(&host->model, images, sample_count,
+                                           probabilities);
+}

@@ -60,6 +60,12 @@ def load_host_library(path):
         ctypes.c_void_p, _size_t, ctypes.c_char_p, ctypes.c_int,
         ctypes.POINTER(_float_p), ctypes.POINTER(_size_t),
         ctypes.POINTER(_size_t)]
+    lib.vithost_evaluate.restype = ctypes.c_int
+    lib.vithost_evaluate.argtypes = [
+        ctypes.c_void_p, _float_p, ctypes.POINTER(_size_t), _size_t, _float_p,
+        _float_p, ctypes.POINTER(ctypes.c_double)]
+    lib.vithost_predict.restype = ctypes.c_int
+    lib.vithost_predict.argtypes = [ctypes.c_void_p, _float_p, _size_t, _float_p]
     lib.ops_synchronize.restype = None
     return lib
 
@@ -313,6 +319,31 @@ class VitHost:
                                     logits.ctypes.data_as(_float_p)) != 0:
             raise RuntimeError("vit_model_forward failed")
         return logits
+
+    def evaluate(self, images, labels):
+        """vit_model_evaluate: (accuracy, average loss, samples per second)."""
+        images = np.ascontiguousarray(images, dtype=np.float32)
+        labels = np.ascontiguousarray(labels, dtype=np.uintp)
+        accuracy, loss = ctypes.c_float(), ctypes.c_float()
+        rate = ctypes.c_double()
+        if self.lib.vithost_evaluate(
+                self.handle, images.ctypes.data_as(_float_p),
+                labels.ctypes.data_as(ctypes.POINTER(_size_t)), len(labels),
+                ctypes.byref(accuracy), ctypes.byref(loss),
+                ctypes.byref(rate)) != 0:
+            raise RuntimeError("vit_model_evaluate failed")
+        return float(accuracy.value), float(loss.value), float(rate.value)
+
+    def predict(self, images):
+        """vit_model_predict_probabilities: [samples, classes]."""
+        images = np.ascontiguousarray(images, dtype=np.float32)
+        count = images.shape[0]
+        out = np.empty((count, self.config[7]), np.float32)
+        if self.lib.vithost_predict(self.handle,
+                                    images.ctypes.data_as(_float_p), count,
+                                    out.ctypes.data_as(_float_p)) != 0:
+            raise RuntimeError("vit_model_predict_probabilities failed")
+        return out
 
     def block_tensor(self, layer, name, grad=False):
         data = _float_p()
