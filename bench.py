@@ -311,7 +311,7 @@ def main():
         "share_of_device_time": top["ms"] / sum(e["ms"] for e in entries),
     }
     breakdown = {e["name"]: round(e["ms"] / args.steps, 4)
-                 for e in sorted(entries, key=lambda e: -e["ms"])[:8]}
+                 for e in sorted(entries, key=lambda e: -e["ms"])[:24]}
 
     line = {
         "metric": "train images/s", "value": value, "unit": "images/s",

@@ -67,6 +67,16 @@ void vitb200_memory_counters(size_t *live_allocations, size_t *mirror_bytes,
                              size_t *h2d_bytes, size_t *d2h_copies,
                              size_t *d2h_bytes, size_t *faults);
 
+/* Work the backend avoided: gradient zero fills that became "first writer
+ * stores" (or had to be issued after all because the zeros were read), and
+ * tensors that were defined but never computed because nobody read them
+ * before they were redefined (the attention probability matrix on the FP32
+ * short-sequence path), or computed on demand.  Any pointer may be NULL. */
+void vitb200_elision_counters(size_t *zero_fills_elided,
+                              size_t *zero_fills_materialised,
+                              size_t *lazy_defined, size_t *lazy_materialised,
+                              size_t *lazy_dropped);
+
 /* Makes a tensor buffer obtained through the backend allocator plainly
  * readable and writable by the host (copying it back from the device if
  * needed).  Required before passing it to read()/fread()/write()/fwrite(),

@@ -326,3 +326,47 @@ def test_evaluation_and_prediction_match_cpu_reference(vit_host_module, host_lib
     gpu.close()
     cpu.close()
     backend.disable()
+
+
+def test_unread_tensors_are_not_computed_but_reads_see_them(vit_host_module,
+                                                            host_lib, backend):
+    """The probability matrix of short-sequence attention is only defined, not
+    written, during training; a host read still returns the right values, and
+    the activation gradients that are zeroed every step are never filled."""
+    vh = vit_host_module
+    config, batch = (1, 28, 28, 4, 32, 4, 2, 11), 4
+    images, labels = vh.synthetic_batch(batch, 28, 28, 11, 3)
+    backend.disable()
+    cpu = vh.VitHost(host_lib, config, batch)
+    cpu.train_step(images, labels, LR, WD, None, 0.1)
+    backend.enable()
+    backend.set_gemm_precision(FP32)
+    gpu = vh.VitHost(host_lib, config, batch)
+    before = backend.elision_counters()
+    gpu.train_step(images, labels, LR, WD, None, 0.1)
+    gpu.train_step(images, labels, LR, WD, None, 0.1)
+    after = backend.elision_counters()
+    layers = config[6]
+    assert after["lazy_defined"] - before["lazy_defined"] == 2 * layers
+    assert after["lazy_materialised"] == before["lazy_materialised"]
+    assert after["lazy_dropped"] - before["lazy_dropped"] == layers  # step 1's
+    assert after["zero_fills_elided"] > before["zero_fills_elided"]
+    # A host read of P forces the computation, for that tensor only.  The
+    # second step started from the first step's weights, so compare with a CPU
+    # model after the same two steps.
+    cpu.train_step(images, labels, LR, WD, None, 0.1)
+    for layer in range(layers):
+        ours = gpu.block_tensor(layer, "probabilities")
+        theirs = cpu.block_tensor(layer, "probabilities")
+        np.testing.assert_allclose(ours, theirs, rtol=0, atol=2e-5)
+        np.testing.assert_allclose(ours.sum(axis=1), 1.0, atol=1e-5)
+    final = backend.elision_counters()
+    assert final["lazy_materialised"] - after["lazy_materialised"] == layers
+    # Training continues correctly after the read.
+    gpu_loss = gpu.train_step(images, labels, LR, WD, None, 0.1)
+    cpu_loss = cpu.train_step(images, labels, LR, WD, None, 0.1)
+    assert abs(gpu_loss - cpu_loss) <= 1e-3
+    backend.set_gemm_precision(-1)
+    gpu.close()
+    cpu.close()
+    backend.disable()

@@ -384,7 +384,7 @@ void launch_attention_forward(const float *q, const float *k, const float *v,
     }
     if (attention_small_supported(seq, head_dim) &&
         launch_attention_small_forward(q, k, v, probabilities, out, groups, seq,
-                                       head_dim, scale, stream)) {
+                                       head_dim, scale, true, true, stream)) {
         return;
     }
     const dim3 grid(static_cast<unsigned>(groups),
@@ -420,7 +420,7 @@ void launch_attention_backward(const float *q, const float *k, const float *v,
     if (attention_small_supported(seq, head_dim) &&
         launch_attention_small_backward(q, k, v, probabilities, out, dout, dq,
                                         dk, dv, groups, seq, head_dim, scale,
-                                        add_q, add_k, add_v, stream)) {
+                                        add_q, add_k, add_v, false, stream)) {
         return;
     }
     const size_t rows = groups * seq;

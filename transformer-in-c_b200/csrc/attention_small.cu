@@ -155,7 +155,7 @@ template <int HD>
 __global__ void attention_small_forward_kernel(
     const float *__restrict__ q, const float *__restrict__ k,
     const float *__restrict__ v, float *__restrict__ p, float *__restrict__ out,
-    int seq, float scale) {
+    int seq, float scale, bool write_p, bool write_o) {
     extern __shared__ __align__(16) float shared[];
     const int pitch = seq | 1;
     float *k_tile = shared;
@@ -193,10 +193,14 @@ __global__ void attention_small_forward_kernel(
             scores[j] = probability;
             axpy_tile<HD>(result, probability, v_tile + j * HD);
         }
-        store_row_pairs<HD>(out + base + row * HD, result, false);
+        if (write_o) {
+            store_row_pairs<HD>(out + base + row * HD, result, false);
+        }
     }
-    __syncthreads();
-    move_probabilities<true>(p + group * seq * seq, p_tile, seq, pitch);
+    if (write_p) {
+        __syncthreads();
+        move_probabilities<true>(p + group * seq * seq, p_tile, seq, pitch);
+    }
 }
 
 template <int HD>
@@ -205,7 +209,7 @@ __global__ void attention_small_backward_kernel(
     const float *__restrict__ v, const float *__restrict__ p,
     const float *__restrict__ out, const float *__restrict__ dout,
     float *__restrict__ dq, float *__restrict__ dk, float *__restrict__ dv,
-    int seq, float scale, bool add_q, bool add_k, bool add_v) {
+    int seq, float scale, bool add_q, bool add_k, bool add_v, bool recompute) {
     extern __shared__ __align__(16) float shared[];
     const int pitch = seq | 1;
     float *q_tile = shared;
@@ -219,8 +223,10 @@ __global__ void attention_small_backward_kernel(
     load_rows<HD>(k + base, k_tile, seq);
     load_rows<HD>(v + base, v_tile, seq);
     load_rows<HD>(dout + base, do_tile, seq);
-    move_probabilities<false>(const_cast<float *>(p) + group * seq * seq,
-                              p_tile, seq, pitch);
+    if (!recompute) {
+        move_probabilities<false>(const_cast<float *>(p) + group * seq * seq,
+                                  p_tile, seq, pitch);
+    }
     const int row = threadIdx.x;
     float row_dot = 0.0f;
     if (row < seq) {
@@ -234,6 +240,32 @@ __global__ void attention_small_backward_kernel(
         }
     }
     __syncthreads();
+    if (recompute) {
+        // The forward pass did not store P: rebuild this row of it from Q and
+        // K with the forward kernel's arithmetic (same order, same rounding).
+        if (row < seq) {
+            pair_t query[HD / 2];
+            load_row_pairs<HD>(query, q_tile + row * HD);
+            float *scores = p_tile + row * pitch;
+            float maximum = -FLT_MAX;
+            for (int j = 0; j < seq; ++j) {
+                const float dot = scale * dot_tile<HD>(query, k_tile + j * HD);
+                scores[j] = dot;
+                maximum = fmaxf(maximum, dot);
+            }
+            float denominator = 0.0f;
+            for (int j = 0; j < seq; ++j) {
+                const float e = softmax_exp(scores[j] - maximum);
+                scores[j] = e;
+                denominator += e;
+            }
+            const float inverse = 1.0f / denominator;
+            for (int j = 0; j < seq; ++j) {
+                scores[j] *= inverse;
+            }
+        }
+        __syncthreads();
+    }
     pair_t acc[HD / 2];
     // Columns: dV_j = sum_i P_ij dO_i.
     if (row < seq) {
@@ -300,8 +332,8 @@ bool attention_small_supported(size_t seq, size_t head_dim) {
 bool launch_attention_small_forward(const float *q, const float *k,
                                     const float *v, float *probabilities,
                                     float *out, size_t groups, size_t seq,
-                                    size_t head_dim, float scale,
-                                    cudaStream_t stream) {
+                                    size_t head_dim, float scale, bool write_p,
+                                    bool write_o, cudaStream_t stream) {
     const unsigned threads = unsigned((seq + 31) / 32 * 32);
     const size_t bytes = (2 * seq * head_dim + seq * (seq | 1)) * sizeof(float);
     bool launched = false;
@@ -309,7 +341,8 @@ bool launch_attention_small_forward(const float *q, const float *k,
     if (fit_shared(attention_small_forward_kernel<HD>, bytes)) {               \
         attention_small_forward_kernel<HD>                                     \
             <<<unsigned(groups), threads, bytes, stream>>>(                    \
-                q, k, v, probabilities, out, int(seq), scale);                 \
+                q, k, v, probabilities, out, int(seq), scale, write_p,         \
+                write_o);                                                      \
         launched = true;                                                       \
     }
     VITB200_DISPATCH_HD(head_dim, CALL)
@@ -324,7 +357,8 @@ bool launch_attention_small_backward(const float *q, const float *k,
                                      float *dq, float *dk, float *dv,
                                      size_t groups, size_t seq, size_t head_dim,
                                      float scale, bool add_q, bool add_k,
-                                     bool add_v, cudaStream_t stream) {
+                                     bool add_v, bool recompute,
+                                     cudaStream_t stream) {
     const unsigned threads = unsigned((seq + 31) / 32 * 32);
     const size_t bytes = (4 * seq * head_dim + seq * (seq | 1)) * sizeof(float);
     bool launched = false;
@@ -333,7 +367,7 @@ bool launch_attention_small_backward(const float *q, const float *k,
         attention_small_backward_kernel<HD>                                    \
             <<<unsigned(groups), threads, bytes, stream>>>(                    \
                 q, k, v, probabilities, out, dout, dq, dk, dv, int(seq),       \
-                scale, add_q, add_k, add_v);                                                      \
+                scale, add_q, add_k, add_v, recompute);                                                      \
         launched = true;                                                       \
     }
     VITB200_DISPATCH_HD(head_dim, CALL)

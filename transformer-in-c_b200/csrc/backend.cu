@@ -682,6 +682,34 @@ int op_merge_heads_backward(void *context, vitb200_tensor *attended,
 
 constexpr size_t kMaxHeadDim = 128;
 
+// Arguments of a pending probability matrix (see op_attention).
+struct ProbabilityDefinition {
+    size_t groups, seq, head_dim;
+    float scale;
+};
+
+// Produces P = softmax(scale Q K^T) for a definition that somebody finally
+// reads.  sources[0] = Q, sources[1] = K; the kernel's V input is irrelevant
+// when only P is written, K stands in for it.
+void materialise_probabilities(const void *arguments, float *output,
+                               float *const *sources, cudaStream_t stream) {
+    ProbabilityDefinition d;
+    memcpy(&d, arguments, sizeof(d));
+    launch_attention_small_forward(sources[0], sources[1], sources[1], output,
+                                   nullptr, d.groups, d.seq, d.head_dim,
+                                   d.scale, true, false, stream);
+}
+
+// Short sequences on the FP32 path: the probability matrix is half of the
+// forward pass's traffic and the backward pass can rebuild it from Q and K in
+// shared memory, so it is not written at all.  The host still owns a tensor
+// for it; that tensor is declared to be softmax(scale Q K^T) and is computed
+// only if somebody reads it.
+bool lazy_probabilities_apply(size_t seq, size_t head_dim) {
+    return attention_small_supported(seq, head_dim) &&
+           gemm_default_precision() != VITB200_PRECISION_TF32;
+}
+
 int op_attention(void *context, const vitb200_tensor *query,
                  const vitb200_tensor *key, const vitb200_tensor *value,
                  size_t batch, size_t heads, size_t seq, float scale,
@@ -694,15 +722,31 @@ int op_attention(void *context, const vitb200_tensor *query,
         !fits_int(seq) || !fits_int(batch * heads)) {
         return -1;
     }
+    const size_t groups = batch * heads;
     const float *q = view(backend, query->data, Access::Read);
     const float *k = view(backend, key->data, Access::Read);
     const float *v = view(backend, value->data, Access::Read);
-    float *p = view(backend, probabilities->data, Access::Overwrite);
     float *o = view(backend, output->data, Access::Overwrite);
+    if (lazy_probabilities_apply(seq, query->cols)) {
+        const ProbabilityDefinition definition = {groups, seq, query->cols, scale};
+        const void *sources[2] = {query->data, key->data};
+        if (coherent_define_lazy(probabilities->data, sources, 2,
+                                 materialise_probabilities, &definition,
+                                 sizeof(definition), backend->stream)) {
+            OpScope scope(backend, "multi_head_attention",
+                          16.0 * double(numel(query)),
+                          4.0 * double(numel(probabilities)) * double(query->cols));
+            launch_attention_small_forward(q, k, v, nullptr, o, groups, seq,
+                                           query->cols, scale, false, true,
+                                           backend->stream);
+            return 0;
+        }
+    }
+    float *p = view(backend, probabilities->data, Access::Overwrite);
     {
         OpScope scope(backend, "multi_head_attention", 4.0 * (4.0 * double(numel(query)) + double(numel(probabilities))),
                       4.0 * double(numel(probabilities)) * double(query->cols));
-        launch_attention_forward(q, k, v, p, o, batch * heads, seq, query->cols,
+        launch_attention_forward(q, k, v, p, o, groups, seq, query->cols,
                                  scale, VITB200_PRECISION_AUTO,
                                  backend->stream);
     }
@@ -731,7 +775,10 @@ int op_attention_backward(void *context, const vitb200_tensor *query,
     const float *q = view(backend, query->data, Access::Read);
     const float *k = view(backend, key->data, Access::Read);
     const float *v = view(backend, value->data, Access::Read);
-    const float *p = view(backend, probabilities->data, Access::Read);
+    const bool recompute = coherent_is_lazy(probabilities->data) &&
+                           lazy_probabilities_apply(seq, query->cols);
+    const float *p = recompute
+        ? nullptr : view(backend, probabilities->data, Access::Read);
     const float *o = view(backend, output->data, Access::Read);
     const float *go = view(backend, output->grad, Access::Read);
     bool add_q = true, add_k = true, add_v = true;
@@ -741,9 +788,17 @@ int op_attention_backward(void *context, const vitb200_tensor *query,
     {
         OpScope scope(backend, "multi_head_attention_backward", 4.0 * (11.0 * double(numel(query)) + double(numel(probabilities))),
                       8.0 * double(numel(probabilities)) * double(query->cols));
-        launch_attention_backward(q, k, v, p, o, go, dq, dk, dv, dots, groups, seq,
-                                  query->cols, scale, add_q, add_k, add_v,
-                                  VITB200_PRECISION_AUTO, backend->stream);
+        if (recompute) {
+            launch_attention_small_backward(q, k, v, nullptr, o, go, dq, dk, dv,
+                                            groups, seq, query->cols, scale,
+                                            add_q, add_k, add_v, true,
+                                            backend->stream);
+        } else {
+            launch_attention_backward(q, k, v, p, o, go, dq, dk, dv, dots,
+                                      groups, seq, query->cols, scale, add_q,
+                                      add_k, add_v, VITB200_PRECISION_AUTO,
+                                      backend->stream);
+        }
     }
     return 0;
 }
@@ -1300,6 +1355,19 @@ extern "C" void vitb200_memory_counters(size_t *live_allocations,
     if (d2h_copies) *d2h_copies = s.device_to_host_copies;
     if (d2h_bytes) *d2h_bytes = s.device_to_host_bytes;
     if (faults) *faults = s.faults_served;
+}
+
+extern "C" void vitb200_elision_counters(size_t *zero_fills_elided,
+                                         size_t *zero_fills_materialised,
+                                         size_t *lazy_defined,
+                                         size_t *lazy_materialised,
+                                         size_t *lazy_dropped) {
+    const CoherenceStats s = coherence_stats();
+    if (zero_fills_elided) *zero_fills_elided = s.zero_fills_elided;
+    if (zero_fills_materialised) *zero_fills_materialised = s.zero_fills_materialised;
+    if (lazy_defined) *lazy_defined = s.lazy_defined;
+    if (lazy_materialised) *lazy_materialised = s.lazy_materialised;
+    if (lazy_dropped) *lazy_dropped = s.lazy_dropped;
 }
 
 extern "C" int vitb200_make_host_coherent(const void *tensor_memory) {

@@ -17,7 +17,11 @@ namespace {
 
 enum class Owner { Host, Shared, Device };
 
+struct LazyDefinition;
+
 struct Region {
+    LazyDefinition *lazy = nullptr;    // this buffer's contents are defined lazily
+    LazyDefinition *feeds = nullptr;   // a lazy definition reads this buffer
     char *mirror = nullptr;
     size_t bytes = 0;         // size the host asked for
     size_t mapped = 0;        // page-rounded size of the mapping
@@ -110,6 +114,75 @@ void ensure_device_buffer(Region &region) {
     g_stats.device_bytes += region.mapped;
 }
 
+// A buffer whose contents are a known function of (at most two) other
+// buffers and have not been computed.  If a source is about to be overwritten
+// while the definition is still pending, the source keeps its old device
+// buffer alive here (`snapshot`) and continues with a fresh one.
+struct LazyDefinition {
+    LazyMaterialise function = nullptr;
+    unsigned char arguments[64] = {};
+    Region *output = nullptr;
+    int sources = 0;
+    Region *source[2] = {nullptr, nullptr};
+    float *snapshot[2] = {nullptr, nullptr};
+    size_t snapshot_bytes[2] = {0, 0};
+};
+
+void recycle(float *device, size_t bytes) {
+    if (g_pooled_bytes + bytes <= kPoolLimitBytes) {
+        buffer_pool().emplace(bytes, device);
+        g_pooled_bytes += bytes;
+    } else {
+        cudaFree(device);
+    }
+}
+
+// Forgets a definition without computing it (its output is being redefined).
+void drop_lazy(LazyDefinition *lazy) {
+    for (int i = 0; i < lazy->sources; ++i) {
+        if (lazy->source[i]) {
+            lazy->source[i]->feeds = nullptr;
+        }
+        if (lazy->snapshot[i]) {
+            recycle(lazy->snapshot[i], lazy->snapshot_bytes[i]);
+        }
+    }
+    if (lazy->output) {
+        lazy->output->lazy = nullptr;
+    }
+    delete lazy;
+    g_stats.lazy_dropped += 1;
+}
+
+// Computes a pending definition into its output buffer.
+void materialise_lazy(LazyDefinition *lazy, cudaStream_t stream) {
+    ensure_device_buffer(*lazy->output);
+    float *inputs[2] = {nullptr, nullptr};
+    for (int i = 0; i < lazy->sources; ++i) {
+        inputs[i] = lazy->snapshot[i] ? lazy->snapshot[i]
+                                      : lazy->source[i]->device;
+    }
+    lazy->function(lazy->arguments, lazy->output->device, inputs, stream);
+    g_stats.lazy_materialised += 1;
+    g_stats.lazy_dropped -= 1;   // drop_lazy below counts it again
+    drop_lazy(lazy);
+}
+
+// The source is about to change: give the pending reader the old buffer.
+void detach_source(Region &region) {
+    LazyDefinition *lazy = region.feeds;
+    for (int i = 0; i < lazy->sources; ++i) {
+        if (lazy->source[i] == &region) {
+            lazy->snapshot[i] = region.device;
+            lazy->snapshot_bytes[i] = region.mapped;
+            lazy->source[i] = nullptr;
+        }
+    }
+    region.feeds = nullptr;
+    g_stats.device_bytes -= region.mapped;
+    region.device = nullptr;
+}
+
 void materialise_zero(Region &region, cudaStream_t stream) {
     if (region.zero_pending) {
         check(cudaMemsetAsync(region.device, 0, region.bytes, stream),
@@ -122,10 +195,17 @@ void materialise_zero(Region &region, cudaStream_t stream) {
 // Brings the mirror up to date and hands ownership back to the host side.
 // `for_write` selects HOST (exclusive) over SHARED (both valid).
 void serve_host_access(Region &region, bool for_write) {
+    if (region.feeds && for_write) {
+        materialise_lazy(region.feeds, g_stream);
+    }
     if (region.owner == Owner::Device) {
         if (g_flush) {
             g_flush();
         }
+        if (region.lazy) {
+            materialise_lazy(region.lazy, g_stream);
+        }
+        ensure_device_buffer(region);
         materialise_zero(region, g_stream);
         check(cudaStreamSynchronize(g_stream), "cudaStreamSynchronize");
         protect(region, PROT_READ | PROT_WRITE);
@@ -233,16 +313,17 @@ void coherent_release(void *context, void *memory) {
     if (it == regions.end()) {
         return;
     }
+    if (it->second.lazy) {
+        drop_lazy(it->second.lazy);
+    }
+    if (it->second.feeds) {
+        // The pending reader inherits the buffer.
+        detach_source(it->second);
+    }
     Region region = it->second;
     regions.erase(it);
     if (region.device) {
-        if (g_pooled_bytes + region.mapped <= kPoolLimitBytes) {
-            buffer_pool().emplace(region.mapped, region.device);
-            g_pooled_bytes += region.mapped;
-        } else {
-            // cudaFree waits for every kernel that may still use the buffer.
-            cudaFree(region.device);
-        }
+        recycle(region.device, region.mapped);
         g_stats.device_bytes -= region.mapped;
     }
     munmap(region.mirror, region.mapped);
@@ -259,6 +340,20 @@ float *device_view(const void *host_pointer, Access access,
     Region *region = host_pointer ? find_base(host_pointer) : nullptr;
     if (!region) {
         return nullptr;
+    }
+    if (region->lazy) {
+        if (access == Access::Overwrite) {
+            drop_lazy(region->lazy);
+        } else {
+            materialise_lazy(region->lazy, stream);
+        }
+    }
+    if (region->feeds && access != Access::Read) {
+        if (access == Access::Overwrite && region->device) {
+            detach_source(*region);
+        } else {
+            materialise_lazy(region->feeds, stream);
+        }
     }
     ensure_device_buffer(*region);
     if (region->zero_pending) {
@@ -302,7 +397,11 @@ bool coherent_mark_zero(const void *host_pointer, cudaStream_t stream) {
     if (!region) {
         return false;
     }
-    ensure_device_buffer(*region);
+    if (region->lazy) {
+        drop_lazy(region->lazy);
+    }
+    // No device buffer is created here: a gradient that nobody writes in a
+    // step (the probability matrix's, the images') never needs one.
     if (region->owner != Owner::Device) {
         protect(*region, PROT_NONE);
         region->owner = Owner::Device;
@@ -312,6 +411,60 @@ bool coherent_mark_zero(const void *host_pointer, cudaStream_t stream) {
     }
     region->zero_pending = true;
     return true;
+}
+
+bool coherent_define_lazy(const void *output_host,
+                          const void *const *source_hosts, int sources,
+                          LazyMaterialise function, const void *arguments,
+                          size_t argument_bytes, cudaStream_t stream) {
+    Region *output = output_host ? find_base(output_host) : nullptr;
+    if (!output || sources < 0 || sources > 2 ||
+        argument_bytes > sizeof(LazyDefinition::arguments)) {
+        return false;
+    }
+    Region *inputs[2] = {nullptr, nullptr};
+    for (int i = 0; i < sources; ++i) {
+        inputs[i] = find_base(source_hosts[i]);
+        if (!inputs[i] || !inputs[i]->device || inputs[i] == output) {
+            return false;
+        }
+    }
+    if (output->lazy) {
+        drop_lazy(output->lazy);
+    }
+    if (output->feeds) {
+        materialise_lazy(output->feeds, stream);
+    }
+    for (int i = 0; i < sources; ++i) {
+        if (inputs[i]->feeds) {
+            materialise_lazy(inputs[i]->feeds, stream);
+        }
+    }
+    LazyDefinition *lazy = new LazyDefinition();
+    lazy->function = function;
+    memcpy(lazy->arguments, arguments, argument_bytes);
+    lazy->output = output;
+    lazy->sources = sources;
+    for (int i = 0; i < sources; ++i) {
+        lazy->source[i] = inputs[i];
+        inputs[i]->feeds = lazy;
+    }
+    output->lazy = lazy;
+    output->zero_pending = false;
+    if (output->owner != Owner::Device) {
+        protect(*output, PROT_NONE);
+        output->owner = Owner::Device;
+        if (output->mapped >= kDropPagesThreshold) {
+            madvise(output->mirror, output->mapped, MADV_DONTNEED);
+        }
+    }
+    g_stats.lazy_defined += 1;
+    return true;
+}
+
+bool coherent_is_lazy(const void *host_pointer) {
+    Region *region = host_pointer ? find_base(host_pointer) : nullptr;
+    return region && region->lazy != nullptr;
 }
 
 float *device_view_accumulate(const void *host_pointer, cudaStream_t stream,

@@ -36,6 +36,9 @@ struct CoherenceStats {
     size_t faults_served;
     size_t zero_fills_elided;
     size_t zero_fills_materialised;
+    size_t lazy_defined;
+    size_t lazy_materialised;
+    size_t lazy_dropped;
 };
 
 // Allocator pair installed through tensor_set_allocator
@@ -65,6 +68,21 @@ bool coherent_mark_zero(const void *host_pointer, cudaStream_t stream);
 // pending fill is dropped.
 float *device_view_accumulate(const void *host_pointer, cudaStream_t stream,
                               bool *was_zero);
+
+// Lazily defined buffers.  `output` is declared to hold function(sources)
+// without computing it.  The value is produced (by calling `function` on the
+// stream) the first time anybody, device op or host, reads the buffer, and is
+// never produced if the buffer is overwritten first.  Sources stay readable:
+// if one is about to be overwritten while the definition is pending, its old
+// device buffer is handed to the definition and the source continues in a
+// fresh one, so no copy is made either way.
+typedef void (*LazyMaterialise)(const void *arguments, float *output,
+                                float *const *sources, cudaStream_t stream);
+bool coherent_define_lazy(const void *output_host,
+                          const void *const *source_hosts, int sources,
+                          LazyMaterialise function, const void *arguments,
+                          size_t argument_bytes, cudaStream_t stream);
+bool coherent_is_lazy(const void *host_pointer);
 
 // Makes the mirror readable and writable by the host again (copying back if
 // the device holds the current contents).  Needed before handing a mirror to a

@@ -89,6 +89,10 @@ int run(const TcGemm &gemm, int precision, cudaStream_t stream) {
 
 }  // namespace
 
+int gemm_default_precision() {
+    return default_precision();
+}
+
 bool prefer_tensor_cores(int precision, double multiply_adds) {
     if (precision == VITB200_PRECISION_AUTO) {
         precision = default_precision();

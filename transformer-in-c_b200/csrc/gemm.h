@@ -39,6 +39,10 @@ int gemm_backward(const float *x, const float *w, const float *dy, float *dx,
 // op of `multiply_adds` should use TF32 under `precision`.
 bool prefer_tensor_cores(int precision, double multiply_adds);
 
+// The precision VITB200_PRECISION_AUTO currently resolves to (AUTO itself
+// when no override is active).
+int gemm_default_precision();
+
 // Overrides what VITB200_PRECISION_AUTO means (and the VITB200_GEMM
 // environment variable); -1 restores the default policy.
 void gemm_set_default_precision(int precision);

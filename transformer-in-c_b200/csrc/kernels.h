@@ -118,15 +118,17 @@ bool attention_small_supported(size_t seq, size_t head_dim);
 bool launch_attention_small_forward(const float *q, const float *k,
                                     const float *v, float *probabilities,
                                     float *out, size_t groups, size_t seq,
-                                    size_t head_dim, float scale,
-                                    cudaStream_t stream);
+                                    size_t head_dim, float scale, bool write_p,
+                                    bool write_o, cudaStream_t stream);
+// recompute = true: `probabilities` is not read; P is rebuilt from Q and K.
 bool launch_attention_small_backward(const float *q, const float *k,
                                      const float *v, const float *probabilities,
                                      const float *out, const float *dout,
                                      float *dq, float *dk, float *dv,
                                      size_t groups, size_t seq, size_t head_dim,
                                      float scale, bool add_q, bool add_k,
-                                     bool add_v, cudaStream_t stream);
+                                     bool add_v, bool recompute,
+                                     cudaStream_t stream);
 
 // ---- loss (loss.cu) -------------------------------------------------------
 // row_losses: scratch of `rows` floats.

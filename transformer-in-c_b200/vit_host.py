@@ -89,6 +89,8 @@ def load_backend_library():
     lib.vitb200_kernel_launches.restype = ctypes.c_ulonglong
     lib.vitb200_memory_counters.restype = None
     lib.vitb200_memory_counters.argtypes = [ctypes.POINTER(_size_t)] * 8
+    lib.vitb200_elision_counters.restype = None
+    lib.vitb200_elision_counters.argtypes = [ctypes.POINTER(_size_t)] * 5
     lib.vitb200_timer_begin.restype = ctypes.c_int
     lib.vitb200_timer_begin.argtypes = [ctypes.c_void_p]
     lib.vitb200_timer_end.restype = ctypes.c_float
@@ -187,6 +189,13 @@ class Backend:
 
     def tensor_core_status(self):
         return int(self.lib.vitb200_tensor_core_status())
+
+    def elision_counters(self):
+        values = [_size_t() for _ in range(5)]
+        self.lib.vitb200_elision_counters(*[ctypes.byref(v) for v in values])
+        names = ["zero_fills_elided", "zero_fills_materialised", "lazy_defined",
+                 "lazy_materialised", "lazy_dropped"]
+        return {n: int(v.value) for n, v in zip(names, values)}
 
     def device_busy_ms(self, reset=False):
         return float(self.lib.vitb200_device_busy_ms(self.handle, int(reset)))
