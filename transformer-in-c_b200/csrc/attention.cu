@@ -412,8 +412,9 @@ void launch_attention_backward(const float *q, const float *k, const float *v,
     if (attention_mma_supported(head_dim) &&
         (precision == VITB200_PRECISION_TF32 ||
          (!short_sequence && prefer_tensor_cores(precision, work))) &&
-        launch_attention_mma_backward(q, k, v, probabilities, out, dout, dq, dk,
-                                      dv, row_dots, groups, seq, head_dim,
+        launch_attention_mma_backward(q, k, v, probabilities, nullptr, out,
+                                      dout, dq, dk, dv, row_dots, groups, seq,
+                                      head_dim,
                                       scale, add_q, add_k, add_v, stream)) {
         return;
     }

@@ -262,7 +262,7 @@ attention_mma_forward_kernel(const float *__restrict__ q,
 #pragma unroll
         for (int h = 0; h < 2; ++h) {
             const int row = query0 + row0 + lane.g + 8 * h;
-            if (row < seq) {
+            if (row < seq && out != nullptr) {
                 *reinterpret_cast<float2 *>(out + base + size_t(row) * HD +
                                             nb * 8 + 2 * lane.t) =
                     make_float2(o[nb][2 * h], o[nb][2 * h + 1]);
@@ -310,21 +310,124 @@ __device__ __forceinline__ void store_rows(float *__restrict__ target,
     }
 }
 
+// Forward pass that never forms P in memory: one sweep over the keys with a
+// running row maximum and denominator, the output rescaled as the maximum
+// grows.  Saves the row log-sum-exp so the backward pass can rebuild any
+// probability as exp(scale s_ij - lse_i).
 template <int HD>
 __global__ void __launch_bounds__(kThreads)
-attention_mma_backward_query_kernel(const float *__restrict__ k,
+attention_mma_flash_forward_kernel(const float *__restrict__ q,
+                                   const float *__restrict__ k,
+                                   const float *__restrict__ v,
+                                   float *__restrict__ out,
+                                   float *__restrict__ lse, int seq,
+                                   float scale) {
+    constexpr int kPitch = HD + 4;
+    extern __shared__ __align__(16) float shared[];
+    float *q_tile = shared;
+    float *k_tile = q_tile + kRows * kPitch;
+    float *v_tile = k_tile + kRows * kPitch;
+    float *p_tile = v_tile + kRows * kPitch;     // [64][72], rows private to a warp
+    const Lane lane;
+    const int row0 = (threadIdx.x >> 5) * 16;
+    const size_t group = blockIdx.x;
+    const int query0 = blockIdx.y * kRows;
+    const size_t base = group * size_t(seq) * HD;
+
+    stage_rows<HD>(q + base, q_tile, query0, seq);
+    float maximum[2] = {-FLT_MAX, -FLT_MAX};
+    float denominator[2] = {0.0f, 0.0f};
+    float o[HD / 8][4];
+    clear<HD / 8>(o);
+    for (int key0 = 0; key0 < seq; key0 += kRows) {
+        __syncthreads();
+        stage_rows<HD>(k + base, k_tile, key0, seq);
+        stage_rows<HD>(v + base, v_tile, key0, seq);
+        __syncthreads();
+        float s[8][4];
+        clear<8>(s);
+        gemm_b_rows_n<8>(s, q_tile, kPitch, row0, k_tile, kPitch, 0, HD, lane);
+        float tile_max[2] = {-FLT_MAX, -FLT_MAX};
+#pragma unroll
+        for (int nb = 0; nb < 8; ++nb) {
+#pragma unroll
+            for (int e = 0; e < 4; ++e) {
+                const int key = key0 + nb * 8 + 2 * lane.t + (e & 1);
+                s[nb][e] = key < seq ? s[nb][e] * scale : -FLT_MAX;
+                tile_max[e >> 1] = fmaxf(tile_max[e >> 1], s[nb][e]);
+            }
+        }
+        float correction[2];
+#pragma unroll
+        for (int h = 0; h < 2; ++h) {
+            const float updated = fmaxf(maximum[h], quad_max(tile_max[h]));
+            correction[h] = __expf(maximum[h] - updated);
+            maximum[h] = updated;
+            float sum = 0.0f;
+#pragma unroll
+            for (int nb = 0; nb < 8; ++nb) {
+                s[nb][2 * h] = __expf(s[nb][2 * h] - updated);
+                s[nb][2 * h + 1] = __expf(s[nb][2 * h + 1] - updated);
+                sum += s[nb][2 * h] + s[nb][2 * h + 1];
+            }
+            denominator[h] = denominator[h] * correction[h] + quad_sum(sum);
+        }
+#pragma unroll
+        for (int nb = 0; nb < HD / 8; ++nb) {
+            o[nb][0] *= correction[0];
+            o[nb][1] *= correction[0];
+            o[nb][2] *= correction[1];
+            o[nb][3] *= correction[1];
+        }
+#pragma unroll
+        for (int nb = 0; nb < 8; ++nb) {
+#pragma unroll
+            for (int e = 0; e < 4; ++e) {
+                p_tile[(row0 + lane.g + 8 * (e >> 1)) * kScorePitch + nb * 8 +
+                       2 * lane.t + (e & 1)] = s[nb][e];
+            }
+        }
+        __syncwarp();
+        gemm_b_rows_k<HD / 8, false>(o, p_tile, kScorePitch, row0, v_tile,
+                                     kPitch, 0, kRows, lane);
+        __syncwarp();
+    }
+#pragma unroll
+    for (int h = 0; h < 2; ++h) {
+        const float inverse = 1.0f / denominator[h];
+#pragma unroll
+        for (int nb = 0; nb < HD / 8; ++nb) {
+            o[nb][2 * h] *= inverse;
+            o[nb][2 * h + 1] *= inverse;
+        }
+        const int row = query0 + row0 + lane.g + 8 * h;
+        if (lane.t == 0 && row < seq) {
+            lse[group * seq + row] = maximum[h] + __logf(denominator[h]);
+        }
+    }
+    store_rows<HD>(out + base, o, query0 + row0, seq, false, lane);
+}
+
+template <int HD, bool kRecompute>
+__global__ void __launch_bounds__(kThreads)
+attention_mma_backward_query_kernel(const float *__restrict__ q,
+                                    const float *__restrict__ k,
                                     const float *__restrict__ v,
                                     const float *__restrict__ p,
+                                    const float *__restrict__ lse,
                                     const float *__restrict__ dout,
                                     const float *__restrict__ row_dots,
                                     float *__restrict__ dq, int seq,
                                     float scale, bool add_q) {
+    // kRecompute: P is not read from memory but rebuilt per tile as
+    // exp(scale Q K^T - lse); `p` is unused then, `q` and `lse` otherwise.
     constexpr int kPitch = HD + 4;
     extern __shared__ __align__(16) float shared[];
     float *do_tile = shared;
     float *k_tile = do_tile + kRows * kPitch;
     float *v_tile = k_tile + kRows * kPitch;
     float *s_tile = v_tile + kRows * kPitch;     // P, then dS, [64][72]
+    float *q_tile = s_tile + kRows * kScorePitch;  // only with kRecompute
     const Lane lane;
     const int warp = threadIdx.x >> 5;
     const int row0 = warp * 16;
@@ -334,11 +437,17 @@ attention_mma_backward_query_kernel(const float *__restrict__ k,
     const float *p_group = p + group * size_t(seq) * seq;
 
     stage_rows<HD>(dout + base, do_tile, query0, seq);
-    float dot[2];
+    if (kRecompute) {
+        stage_rows<HD>(q + base, q_tile, query0, seq);
+    }
+    float dot[2], row_lse[2];
+    bool row_live[2];
 #pragma unroll
     for (int h = 0; h < 2; ++h) {
         const int row = query0 + row0 + lane.g + 8 * h;
-        dot[h] = row < seq ? row_dots[group * seq + row] : 0.0f;
+        row_live[h] = row < seq;
+        dot[h] = row_live[h] ? row_dots[group * seq + row] : 0.0f;
+        row_lse[h] = (kRecompute && row_live[h]) ? lse[group * seq + row] : 0.0f;
     }
     float acc[HD / 8][4];
     clear<HD / 8>(acc);
@@ -346,8 +455,26 @@ attention_mma_backward_query_kernel(const float *__restrict__ k,
         __syncthreads();
         stage_rows<HD>(k + base, k_tile, key0, seq);
         stage_rows<HD>(v + base, v_tile, key0, seq);
-        stage_probabilities(p_group, s_tile, query0, key0, seq);
+        if (!kRecompute) {
+            stage_probabilities(p_group, s_tile, query0, key0, seq);
+        }
         __syncthreads();
+        if (kRecompute) {
+            float s[8][4];
+            clear<8>(s);
+            gemm_b_rows_n<8>(s, q_tile, kPitch, row0, k_tile, kPitch, 0, HD, lane);
+#pragma unroll
+            for (int nb = 0; nb < 8; ++nb) {
+#pragma unroll
+                for (int e = 0; e < 4; ++e) {
+                    const int h = e >> 1;
+                    const int col = nb * 8 + 2 * lane.t + (e & 1);
+                    s_tile[(row0 + lane.g + 8 * h) * kScorePitch + col] =
+                        (row_live[h] && key0 + col < seq)
+                            ? __expf(s[nb][e] * scale - row_lse[h]) : 0.0f;
+                }
+            }
+        }
         float dp[8][4];
         clear<8>(dp);
         gemm_b_rows_n<8>(dp, do_tile, kPitch, row0, v_tile, kPitch, 0, HD, lane);
@@ -368,11 +495,13 @@ attention_mma_backward_query_kernel(const float *__restrict__ k,
     store_rows<HD>(dq + base, acc, query0 + row0, seq, add_q, lane);
 }
 
-template <int HD>
+template <int HD, bool kRecompute>
 __global__ void __launch_bounds__(kThreads)
 attention_mma_backward_key_kernel(const float *__restrict__ q,
+                                  const float *__restrict__ k,
                                   const float *__restrict__ v,
                                   const float *__restrict__ p,
+                                  const float *__restrict__ lse,
                                   const float *__restrict__ dout,
                                   const float *__restrict__ row_dots,
                                   float *__restrict__ dk, float *__restrict__ dv,
@@ -386,6 +515,8 @@ attention_mma_backward_key_kernel(const float *__restrict__ q,
     float *p_tile = do_tile + kRows * kPitch;    // [query][key], pitch 72
     float *s_tile = p_tile + kRows * kScorePitch;
     float *dots = s_tile + kRows * kScorePitch;  // [64]
+    float *lses = dots + kRows;                  // [64], only with kRecompute
+    float *k_own = lses + kRows;                 // [64][HD+4], only with kRecompute
     const Lane lane;
     const int warp = threadIdx.x >> 5;
     const int row0 = warp * 16;
@@ -395,6 +526,9 @@ attention_mma_backward_key_kernel(const float *__restrict__ q,
     const float *p_group = p + group * size_t(seq) * seq;
 
     stage_rows<HD>(v + base, v_own, key0, seq);
+    if (kRecompute) {
+        stage_rows<HD>(k + base, k_own, key0, seq);
+    }
     float acc_k[HD / 8][4], acc_v[HD / 8][4];
     clear<HD / 8>(acc_k);
     clear<HD / 8>(acc_v);
@@ -402,13 +536,37 @@ attention_mma_backward_key_kernel(const float *__restrict__ q,
         __syncthreads();
         stage_rows<HD>(q + base, q_tile, query0, seq);
         stage_rows<HD>(dout + base, do_tile, query0, seq);
-        stage_probabilities(p_group, p_tile, query0, key0, seq);
+        if (!kRecompute) {
+            stage_probabilities(p_group, p_tile, query0, key0, seq);
+        }
         if (threadIdx.x < kRows) {
-            dots[threadIdx.x] = query0 + threadIdx.x < seq
-                ? row_dots[group * seq + query0 + threadIdx.x]
-                : 0.0f;
+            const bool live = query0 + threadIdx.x < seq;
+            dots[threadIdx.x] =
+                live ? row_dots[group * seq + query0 + threadIdx.x] : 0.0f;
+            if (kRecompute) {
+                lses[threadIdx.x] =
+                    live ? lse[group * seq + query0 + threadIdx.x] : 0.0f;
+            }
         }
         __syncthreads();
+        if (kRecompute) {
+            // P for query rows row0..row0+15 against this block's 64 keys.
+            float s[8][4];
+            clear<8>(s);
+            gemm_b_rows_n<8>(s, q_tile, kPitch, row0, k_own, kPitch, 0, HD, lane);
+#pragma unroll
+            for (int nb = 0; nb < 8; ++nb) {
+#pragma unroll
+                for (int e = 0; e < 4; ++e) {
+                    const int r = row0 + lane.g + 8 * (e >> 1);
+                    const int c = nb * 8 + 2 * lane.t + (e & 1);
+                    p_tile[r * kScorePitch + c] =
+                        (query0 + r < seq && key0 + c < seq)
+                            ? __expf(s[nb][e] * scale - lses[r]) : 0.0f;
+                }
+            }
+            __syncwarp();
+        }
         // Score gradients of query rows row0..row0+15 against all 64 keys.
         float dp[8][4];
         clear<8>(dp);
@@ -684,21 +842,48 @@ bool launch_attention_mma_forward(const float *q, const float *k,
     return launched;
 }
 
+bool launch_attention_mma_flash_forward(const float *q, const float *k,
+                                        const float *v, float *out, float *lse,
+                                        size_t groups, size_t seq,
+                                        size_t head_dim, float scale,
+                                        cudaStream_t stream) {
+    const dim3 grid(unsigned(groups), unsigned((seq + kRows - 1) / kRows));
+    const size_t bytes =
+        (3 * kRows * (head_dim + 4) + kRows * kScorePitch) * sizeof(float);
+    bool launched = false;
+#define CALL(HD)                                                               \
+    if (allow(attention_mma_flash_forward_kernel<HD>, bytes)) {                \
+        attention_mma_flash_forward_kernel<HD>                                 \
+            <<<grid, kThreads, bytes, stream>>>(q, k, v, out, lse, int(seq),   \
+                                                scale);                        \
+        launched = true;                                                       \
+    }
+    VITB200_MMA_DISPATCH(head_dim, CALL)
+#undef CALL
+    g_kernel_launches += launched ? 1 : 0;
+    return launched;
+}
+
 bool launch_attention_mma_backward(const float *q, const float *k,
                                    const float *v, const float *probabilities,
-                                   const float *out, const float *dout,
-                                   float *dq, float *dk, float *dv,
-                                   float *row_dots, size_t groups, size_t seq,
-                                   size_t head_dim, float scale, bool add_q,
-                                   bool add_k, bool add_v,
+                                   const float *lse, const float *out,
+                                   const float *dout, float *dq, float *dk,
+                                   float *dv, float *row_dots, size_t groups,
+                                   size_t seq, size_t head_dim, float scale,
+                                   bool add_q, bool add_k, bool add_v,
                                    cudaStream_t stream) {
+    // lse != nullptr: probabilities are rebuilt from Q, K and the saved row
+    // log-sum-exp instead of being read.
+    const bool recompute = lse != nullptr;
     const dim3 grid(unsigned(groups), unsigned((seq + kRows - 1) / kRows));
     const size_t tile = kRows * (head_dim + 4);
-    const size_t query_bytes = (3 * tile + kRows * kScorePitch) * sizeof(float);
+    const size_t query_bytes =
+        ((recompute ? 4 : 3) * tile + kRows * kScorePitch) * sizeof(float);
     const size_t key_bytes =
-        (3 * tile + 2 * kRows * kScorePitch + kRows) * sizeof(float);
+        ((recompute ? 4 : 3) * tile + 2 * kRows * kScorePitch + 2 * kRows) *
+        sizeof(float);
     bool launched = false;
-    if (seq <= size_t(kRows) && head_dim <= 64) {
+    if (!recompute && seq <= size_t(kRows) && head_dim <= 64) {
         const size_t single =
             (4 * tile + 2 * kRows * kScorePitch) * sizeof(float);
 #define CALL(HD)                                                               \
@@ -714,24 +899,27 @@ bool launch_attention_mma_backward(const float *q, const float *k,
         g_kernel_launches += launched ? 1 : 0;
         return launched;
     }
-#define CALL(HD)                                                               \
-    if (allow(attention_mma_backward_query_kernel<HD>, query_bytes) &&         \
-        allow(attention_mma_backward_key_kernel<HD>, key_bytes)) {             \
+#define LAUNCH(HD, RECOMPUTE)                                                  \
+    if (allow(attention_mma_backward_query_kernel<HD, RECOMPUTE>, query_bytes) && \
+        allow(attention_mma_backward_key_kernel<HD, RECOMPUTE>, key_bytes)) {  \
         mma_row_dots_kernel<<<stream_grid(groups * seq * 32), kStreamThreads,  \
                               0, stream>>>(dout, out, row_dots, groups * seq,  \
                                            int(head_dim));                     \
-        attention_mma_backward_query_kernel<HD>                                \
+        attention_mma_backward_query_kernel<HD, RECOMPUTE>                     \
             <<<grid, kThreads, query_bytes, stream>>>(                         \
-                k, v, probabilities, dout, row_dots, dq, int(seq), scale,      \
-                add_q);                                                        \
-        attention_mma_backward_key_kernel<HD>                                  \
+                q, k, v, probabilities, lse, dout, row_dots, dq, int(seq),     \
+                scale, add_q);                                                 \
+        attention_mma_backward_key_kernel<HD, RECOMPUTE>                       \
             <<<grid, kThreads, key_bytes, stream>>>(                           \
-                q, v, probabilities, dout, row_dots, dk, dv, int(seq), scale,  \
-                add_k, add_v);                                                 \
+                q, k, v, probabilities, lse, dout, row_dots, dk, dv, int(seq), \
+                scale, add_k, add_v);                                          \
         launched = true;                                                       \
     }
+#define CALL(HD)                                                               \
+    if (recompute) { LAUNCH(HD, true) } else { LAUNCH(HD, false) }
     VITB200_MMA_DISPATCH(head_dim, CALL)
 #undef CALL
+#undef LAUNCH
     g_kernel_launches += launched ? 3 : 0;
     return launched;
 }

@@ -23,6 +23,7 @@
 #include <cstdlib>
 #include <cstring>
 #include <dlfcn.h>
+#include <unordered_map>
 #include <vector>
 
 // Host functions this backend calls into.  They live in the host program
@@ -103,6 +104,9 @@ struct CudaBackend {
     std::vector<cudaEvent_t> free_events;
     DataParallel *dp = nullptr;
     PendingGemm pending;
+    // Row log-sum-exp of flash attention, one buffer per probability tensor
+    // (keyed by the tensor's host address), kept from forward to backward.
+    std::unordered_map<const void *, Scratch> lse_buffers;
     unsigned long long fused_epilogues = 0;
     void (*set_table)(const vitb200_op_table *) = nullptr;
     void (*set_allocator)(vitb200_allocate_fn, vitb200_release_fn,
@@ -686,6 +690,7 @@ constexpr size_t kMaxHeadDim = 128;
 struct ProbabilityDefinition {
     size_t groups, seq, head_dim;
     float scale;
+    int tensor_cores;   // which forward kernel defines the values
 };
 
 // Produces P = softmax(scale Q K^T) for a definition that somebody finally
@@ -695,6 +700,12 @@ void materialise_probabilities(const void *arguments, float *output,
                                float *const *sources, cudaStream_t stream) {
     ProbabilityDefinition d;
     memcpy(&d, arguments, sizeof(d));
+    if (d.tensor_cores) {
+        launch_attention_mma_forward(sources[0], sources[1], sources[1], output,
+                                     nullptr, d.groups, d.seq, d.head_dim,
+                                     d.scale, stream);
+        return;
+    }
     launch_attention_small_forward(sources[0], sources[1], sources[1], output,
                                    nullptr, d.groups, d.seq, d.head_dim,
                                    d.scale, true, false, stream);
@@ -728,7 +739,8 @@ int op_attention(void *context, const vitb200_tensor *query,
     const float *v = view(backend, value->data, Access::Read);
     float *o = view(backend, output->data, Access::Overwrite);
     if (lazy_probabilities_apply(seq, query->cols)) {
-        const ProbabilityDefinition definition = {groups, seq, query->cols, scale};
+        const ProbabilityDefinition definition = {groups, seq, query->cols,
+                                                  scale, 0};
         const void *sources[2] = {query->data, key->data};
         if (coherent_define_lazy(probabilities->data, sources, 2,
                                  materialise_probabilities, &definition,
@@ -740,6 +752,31 @@ int op_attention(void *context, const vitb200_tensor *query,
                                            query->cols, scale, false, true,
                                            backend->stream);
             return 0;
+        }
+    }
+    // Long sequences on tensor cores: flash attention.  One sweep, P never
+    // written; the row log-sum-exp is kept for the backward pass and P itself
+    // stays a pending definition.
+    const double work = double(groups) * seq * seq * query->cols;
+    if (!attention_small_supported(seq, query->cols) &&
+        attention_mma_supported(query->cols) &&
+        prefer_tensor_cores(VITB200_PRECISION_AUTO, work)) {
+        const ProbabilityDefinition definition = {groups, seq, query->cols,
+                                                  scale, 1};
+        const void *sources[2] = {query->data, key->data};
+        Scratch &buffer = backend->lse_buffers[probabilities->data];
+        float *lse = scratch<float>(backend, buffer, groups * seq);
+        if (coherent_define_lazy(probabilities->data, sources, 2,
+                                 materialise_probabilities, &definition,
+                                 sizeof(definition), backend->stream)) {
+            OpScope scope(backend, "multi_head_attention",
+                          16.0 * double(numel(query)),
+                          4.0 * double(numel(probabilities)) * double(query->cols));
+            if (launch_attention_mma_flash_forward(q, k, v, o, lse, groups, seq,
+                                                   query->cols, scale,
+                                                   backend->stream)) {
+                return 0;
+            }
         }
     }
     float *p = view(backend, probabilities->data, Access::Overwrite);
@@ -775,9 +812,17 @@ int op_attention_backward(void *context, const vitb200_tensor *query,
     const float *q = view(backend, query->data, Access::Read);
     const float *k = view(backend, key->data, Access::Read);
     const float *v = view(backend, value->data, Access::Read);
-    const bool recompute = coherent_is_lazy(probabilities->data) &&
-                           lazy_probabilities_apply(seq, query->cols);
-    const float *p = recompute
+    const bool pending_p = coherent_is_lazy(probabilities->data);
+    const bool recompute = pending_p && lazy_probabilities_apply(seq, query->cols);
+    const float *lse = nullptr;
+    if (pending_p && !recompute) {
+        auto found = backend->lse_buffers.find(probabilities->data);
+        if (found != backend->lse_buffers.end() &&
+            found->second.bytes >= groups * seq * sizeof(float)) {
+            lse = static_cast<const float *>(found->second.memory);
+        }
+    }
+    const float *p = (recompute || lse)
         ? nullptr : view(backend, probabilities->data, Access::Read);
     const float *o = view(backend, output->data, Access::Read);
     const float *go = view(backend, output->grad, Access::Read);
@@ -793,6 +838,11 @@ int op_attention_backward(void *context, const vitb200_tensor *query,
                                             groups, seq, query->cols, scale,
                                             add_q, add_k, add_v, true,
                                             backend->stream);
+        } else if (lse) {
+            launch_attention_mma_backward(q, k, v, nullptr, lse, o, go, dq, dk,
+                                          dv, dots, groups, seq, query->cols,
+                                          scale, add_q, add_k, add_v,
+                                          backend->stream);
         } else {
             launch_attention_backward(q, k, v, p, o, go, dq, dk, dv, dots,
                                       groups, seq, query->cols, scale, add_q,
@@ -1249,6 +1299,10 @@ extern "C" void cuda_backend_free(CudaBackend *backend) {
     }
     dp_destroy(backend->dp);
     backend->dp = nullptr;
+    for (auto &entry : backend->lse_buffers) {
+        free_scratch(entry.second);
+    }
+    backend->lse_buffers.clear();
     free_scratch(backend->rows_scratch);
     free_scratch(backend->norm_partials);
     free_scratch(backend->clip_scale);

@@ -238,7 +238,7 @@ __device__ __forceinline__ void mbarrier_arrive(uint64_t *bar) {
 // slice) item = blockIdx.x, blockIdx.x + gridDim.x, ...; the three roles run
 // the same sequence and meet only through mbarriers, so the loads and MMAs of
 // item i+1 overlap the epilogue of item i (two accumulator buffers in TMEM).
-__global__ void __launch_bounds__(kThreads, 1)
+__global__ void __launch_bounds__(kThreads)
 gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a,
                const __grid_constant__ CUtensorMap map_b,
                const __grid_constant__ CUtensorMap map_d,
@@ -398,8 +398,10 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a,
         // needs no block-wide barrier at all.
         const int quarter = warp & 3;
         const int outputs = p.second ? 2 : 1;
-        uint8_t *my_staging =
-            staging + quarter * (outputs * 2 * 4096);   // [output][buffer]
+        // One staged output is double-buffered per warp; with two outputs each
+        // gets a single buffer, which keeps the CTA small enough for two per SM.
+        const int buffers = p.second ? 1 : 2;
+        uint8_t *my_staging = staging + quarter * (2 * 4096);   // [output|buffer]
         int local = 0;
         int stored = 0;   // blocks handed to TMA so far (selects the buffer)
         for (int item = blockIdx.x; item < items; item += gridDim.x, ++local) {
@@ -458,14 +460,17 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a,
                 // The buffer about to be rewritten was last read by the store
                 // this warp issued two blocks ago.
                 if (lane == 0) {
-                    asm volatile("cp.async.bulk.wait_group.read 1;" ::: "memory");
+                    if (buffers == 2) {
+                        asm volatile("cp.async.bulk.wait_group.read 1;" ::: "memory");
+                    } else {
+                        asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory");
+                    }
                 }
                 __syncwarp();
-                const int slot = stored & 1;
+                const int slot = buffers == 2 ? (stored & 1) : 0;
                 ++stored;
                 float *first = reinterpret_cast<float *>(my_staging + slot * 4096);
-                float *second =
-                    reinterpret_cast<float *>(my_staging + (2 + slot) * 4096);
+                float *second = reinterpret_cast<float *>(my_staging + 4096);
 #pragma unroll
                 for (int c = 0; c < 8; ++c) {
                     float4 v;
@@ -710,15 +715,44 @@ int launch_gemm_tc(const TcGemm &g, cudaStream_t stream) {
     const int m_tiles = (g.m + kTileM - 1) / kTileM;
     p.m_tiles = m_tiles;
     const int tiles = m_tiles * p.n_tiles;
+    // Two persistent CTAs per SM, each with a 2-stage load ring and 32 KiB of
+    // epilogue staging (97 KiB): they interleave their MMA issue and their
+    // epilogues, and measured faster than one CTA with a 4- to 6-stage ring
+    // at every size tried (449 against 346 TFLOP/s at [100864,512]x[512,2048]).
+    const int staging_bytes = 2 * kOperandBytes;
+    int ctas_per_sm = 2;
+    p.stages = 2;
+    static const int forced_stages =
+        getenv("VITB200_TC_STAGES") ? atoi(getenv("VITB200_TC_STAGES")) : 0;
+    static const int forced_ctas =
+        getenv("VITB200_TC_CTAS") ? atoi(getenv("VITB200_TC_CTAS")) : 0;
+    if (forced_stages > 0 && forced_stages <= kMaxStages) {
+        p.stages = forced_stages;
+    }
+    if (forced_ctas > 0) {
+        ctas_per_sm = forced_ctas;
+    }
+    const long long slots = 148LL * ctas_per_sm;
     int splits = 1;
     if (g.accumulate) {
-        // Long reductions onto few output tiles (weight gradients): spread the
-        // reduction over about two waves of CTAs, at least 8 blocks each.
-        const int wanted = (2 * 148 + tiles - 1) / tiles;
-        const int most = (p.k_blocks + 7) / 8;
-        splits = wanted < most ? wanted : most;
-        if (splits < 1) {
-            splits = 1;
+        // Long reductions onto few output tiles (weight gradients) are cut
+        // into slices.  With a persistent grid the slices should fill the CTA
+        // slots evenly: pick the slice count that minimises the k-blocks the
+        // busiest CTA walks, charging each item about eight k-blocks for its
+        // epilogue and reduce-add.
+        long long best_cost = -1;
+        for (int candidate = 1; candidate <= 512; ++candidate) {
+            const int per_slice = (p.k_blocks + candidate - 1) / candidate;
+            if (candidate > 1 && per_slice < 4) {
+                break;
+            }
+            const long long rounds =
+                ((long long)tiles * candidate + slots - 1) / slots;
+            const long long cost = rounds * (per_slice + 8);
+            if (best_cost < 0 || cost < best_cost) {
+                best_cost = cost;
+                splits = candidate;
+            }
         }
     }
     p.k_blocks_per_split = (p.k_blocks + splits - 1) / splits;
@@ -738,13 +772,8 @@ int launch_gemm_tc(const TcGemm &g, cudaStream_t stream) {
     // One persistent CTA per SM (the shared-memory ring fills an SM), fewer
     // when there is less work than SMs.
     const long long items = (long long)tiles * splits;
-    const unsigned grid = unsigned(items < 148 ? items : 148);
-    const int staging_bytes = (g.d2 ? 4 : 2) * kOperandBytes;
-    p.stages = (kSmemLimit - 1024 - staging_bytes) / kStageBytes;
-    if (p.stages > kMaxStages) {
-        p.stages = kMaxStages;
-    }
     const int smem_bytes = p.stages * kStageBytes + staging_bytes + 1024;
+    const unsigned grid = unsigned(items < slots ? items : slots);
     gemm_tc_kernel<<<grid, kThreads, smem_bytes, stream>>>(
         map_a, map_b, map_d, map_d2, p);
     ++g_kernel_launches;

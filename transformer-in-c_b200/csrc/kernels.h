@@ -103,13 +103,21 @@ bool launch_attention_mma_forward(const float *q, const float *k,
                                   float *out, size_t groups, size_t seq,
                                   size_t head_dim, float scale,
                                   cudaStream_t stream);
+// One sweep, no probability matrix: writes O and the row log-sum-exp.
+bool launch_attention_mma_flash_forward(const float *q, const float *k,
+                                        const float *v, float *out, float *lse,
+                                        size_t groups, size_t seq,
+                                        size_t head_dim, float scale,
+                                        cudaStream_t stream);
+// lse == nullptr: read `probabilities`; otherwise rebuild them from Q, K, lse.
 bool launch_attention_mma_backward(const float *q, const float *k,
                                    const float *v, const float *probabilities,
-                                   const float *out, const float *dout,
-                                   float *dq, float *dk, float *dv,
-                                   float *row_dots, size_t groups, size_t seq,
-                                   size_t head_dim, float scale, bool add_q,
-                                   bool add_k, bool add_v, cudaStream_t stream);
+                                   const float *lse, const float *out,
+                                   const float *dout, float *dq, float *dk,
+                                   float *dv, float *row_dots, size_t groups,
+                                   size_t seq, size_t head_dim, float scale,
+                                   bool add_q, bool add_k, bool add_v,
+                                   cudaStream_t stream);
 
 // Short sequences with the whole (sample, head) group in shared memory
 // (attention_small.cu).  The launchers return false when the shape is outside
