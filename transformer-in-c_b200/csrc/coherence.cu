@@ -28,6 +28,8 @@ struct Region {
     float *device = nullptr;  // created on first device use
     Owner owner = Owner::Host;
     bool zero_pending = false;  // device contents are an unmaterialised zero fill
+    unsigned uploads = 0;       // host-to-device copies so far
+    bool pinned = false;        // mirror registered with the driver
 };
 
 // Process-global on purpose: the host keeps the release function inside every
@@ -322,6 +324,9 @@ void coherent_release(void *context, void *memory) {
     }
     Region region = it->second;
     regions.erase(it);
+    if (region.pinned) {
+        cudaHostUnregister(region.mirror);
+    }
     if (region.device) {
         recycle(region.device, region.mapped);
         g_stats.device_bytes -= region.mapped;
@@ -370,6 +375,17 @@ float *device_view(const void *host_pointer, Access access,
         if (g_flush) {
             g_flush();
         }
+        // A mirror that is uploaded again and again (the image batch, the
+        // labels) is page-locked once, so its copies become plain DMA instead
+        // of going through the driver's staging buffer.
+        if (++region->uploads == 2 && !region->pinned) {
+            if (cudaHostRegister(region->mirror, region->mapped,
+                                 cudaHostRegisterDefault) == cudaSuccess) {
+                region->pinned = true;
+            } else {
+                cudaGetLastError();   // stay pageable; clear the error state
+            }
+        }
         check(cudaMemcpyAsync(region->device, region->mirror, region->bytes,
                               cudaMemcpyHostToDevice, stream),
               "cudaMemcpyAsync(host to device)");
@@ -384,7 +400,7 @@ float *device_view(const void *host_pointer, Access access,
     } else if (region->owner != Owner::Device) {
         protect(*region, PROT_NONE);
         region->owner = Owner::Device;
-        if (region->mapped >= kDropPagesThreshold) {
+        if (region->mapped >= kDropPagesThreshold && !region->pinned) {
             madvise(region->mirror, region->mapped, MADV_DONTNEED);
         }
     }
@@ -405,7 +421,7 @@ bool coherent_mark_zero(const void *host_pointer, cudaStream_t stream) {
     if (region->owner != Owner::Device) {
         protect(*region, PROT_NONE);
         region->owner = Owner::Device;
-        if (region->mapped >= kDropPagesThreshold) {
+        if (region->mapped >= kDropPagesThreshold && !region->pinned) {
             madvise(region->mirror, region->mapped, MADV_DONTNEED);
         }
     }
@@ -454,7 +470,7 @@ bool coherent_define_lazy(const void *output_host,
     if (output->owner != Owner::Device) {
         protect(*output, PROT_NONE);
         output->owner = Owner::Device;
-        if (output->mapped >= kDropPagesThreshold) {
+        if (output->mapped >= kDropPagesThreshold && !output->pinned) {
             madvise(output->mirror, output->mapped, MADV_DONTNEED);
         }
     }
