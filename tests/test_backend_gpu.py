@@ -347,9 +347,13 @@ def test_unread_tensors_are_not_computed_but_reads_see_them(vit_host_module,
     gpu.train_step(images, labels, LR, WD, None, 0.1)
     after = backend.elision_counters()
     layers = config[6]
-    assert after["lazy_defined"] - before["lazy_defined"] == 2 * layers
+    # Per block and step: P; the head-major Q, K, V and attention output
+    # (views of the projected / merged matrices); and the same five gradients
+    # less P's, which nobody produces.
+    per_block = 1 + 4 + 4
+    assert after["lazy_defined"] - before["lazy_defined"] == 2 * per_block * layers
     assert after["lazy_materialised"] == before["lazy_materialised"]
-    assert after["lazy_dropped"] - before["lazy_dropped"] == layers  # step 1's
+    assert after["lazy_dropped"] - before["lazy_dropped"] == per_block * layers  # step 1's
     assert after["zero_fills_elided"] > before["zero_fills_elided"]
     # A host read of P forces the computation, for that tensor only.  The
     # second step started from the first step's weights, so compare with a CPU
@@ -362,6 +366,20 @@ def test_unread_tensors_are_not_computed_but_reads_see_them(vit_host_module,
         np.testing.assert_allclose(ours.sum(axis=1), 1.0, atol=1e-5)
     final = backend.elision_counters()
     assert final["lazy_materialised"] - after["lazy_materialised"] == layers
+    # The head-major tensors that were never written read back correctly too,
+    # values and gradients.
+    for layer in range(layers):
+        for name in ("query", "key", "value", "attended"):
+            for grad in (False, True):
+                ours = gpu.block_tensor(layer, name, grad)
+                theirs = cpu.block_tensor(layer, name, grad)
+                scale = float(np.abs(theirs).max())
+                assert scale > 0
+                np.testing.assert_allclose(ours, theirs, rtol=0,
+                                           atol=2e-4 * scale + 1e-7,
+                                           err_msg=f"{name} grad={grad}")
+    reread = backend.elision_counters()
+    assert reread["lazy_materialised"] - final["lazy_materialised"] == 8 * layers
     # Training continues correctly after the read.
     gpu_loss = gpu.train_step(images, labels, LR, WD, None, 0.1)
     cpu_loss = cpu.train_step(images, labels, LR, WD, None, 0.1)

@@ -22,16 +22,26 @@
 namespace vitb200 {
 namespace {
 
-// Cooperative copy of a contiguous [rows, HD] block into shared memory.
+// Cooperative copy of a [rows, HD] block whose rows are `ld` floats apart into
+// a dense shared-memory tile.
 template <int HD>
 __device__ __forceinline__ void load_rows(const float *__restrict__ source,
-                                          float *tile, int rows) {
-    const int vectors = rows * HD / 4;
-    const float4 *from = reinterpret_cast<const float4 *>(source);
+                                          float *tile, int rows, int ld) {
+    constexpr int kPerRow = HD / 4;
+    const int vectors = rows * kPerRow;
     float4 *to = reinterpret_cast<float4 *>(tile);
     for (int i = threadIdx.x; i < vectors; i += blockDim.x) {
-        to[i] = __ldcs(from + i);
+        const int row = i / kPerRow, chunk = i % kPerRow;
+        to[i] = __ldcs(reinterpret_cast<const float4 *>(source + size_t(row) * ld) + chunk);
     }
+}
+
+// Offset of a group's first row under a layout (see HeadLayout).
+template <int HD>
+__device__ __forceinline__ size_t group_offset(size_t group, int seq,
+                                               HeadLayout layout) {
+    return (group / layout.heads) * size_t(seq) * layout.ld +
+           (group % layout.heads) * HD;
 }
 
 // Packed FP32 arithmetic: Blackwell issues two FP32 FMAs per instruction on
@@ -155,20 +165,21 @@ template <int HD>
 __global__ void attention_small_forward_kernel(
     const float *__restrict__ q, const float *__restrict__ k,
     const float *__restrict__ v, float *__restrict__ p, float *__restrict__ out,
-    int seq, float scale, bool write_p, bool write_o) {
+    int seq, float scale, bool write_p, bool write_o, HeadLayout in_layout,
+    HeadLayout out_layout) {
     extern __shared__ __align__(16) float shared[];
     const int pitch = seq | 1;
     float *k_tile = shared;
     float *v_tile = k_tile + seq * HD;
     float *p_tile = v_tile + seq * HD;
     const size_t group = blockIdx.x;
-    const size_t base = group * seq * HD;
-    load_rows<HD>(k + base, k_tile, seq);
-    load_rows<HD>(v + base, v_tile, seq);
+    const size_t base = group_offset<HD>(group, seq, in_layout);
+    load_rows<HD>(k + base, k_tile, seq, in_layout.ld);
+    load_rows<HD>(v + base, v_tile, seq, in_layout.ld);
     const int row = threadIdx.x;
     pair_t query[HD / 2];
     if (row < seq) {
-        load_row_pairs<HD>(query, q + base + row * HD);
+        load_row_pairs<HD>(query, q + base + size_t(row) * in_layout.ld);
     }
     __syncthreads();
     if (row < seq) {
@@ -194,7 +205,9 @@ __global__ void attention_small_forward_kernel(
             axpy_tile<HD>(result, probability, v_tile + j * HD);
         }
         if (write_o) {
-            store_row_pairs<HD>(out + base + row * HD, result, false);
+            store_row_pairs<HD>(out + group_offset<HD>(group, seq, out_layout) +
+                                    size_t(row) * out_layout.ld,
+                                result, false);
         }
     }
     if (write_p) {
@@ -209,7 +222,9 @@ __global__ void attention_small_backward_kernel(
     const float *__restrict__ v, const float *__restrict__ p,
     const float *__restrict__ out, const float *__restrict__ dout,
     float *__restrict__ dq, float *__restrict__ dk, float *__restrict__ dv,
-    int seq, float scale, bool add_q, bool add_k, bool add_v, bool recompute) {
+    int seq, float scale, bool add_q, bool add_k, bool add_v, bool recompute,
+    HeadLayout in_layout, HeadLayout out_layout, HeadLayout dout_layout,
+    HeadLayout grad_layout) {
     extern __shared__ __align__(16) float shared[];
     const int pitch = seq | 1;
     float *q_tile = shared;
@@ -218,11 +233,12 @@ __global__ void attention_small_backward_kernel(
     float *do_tile = v_tile + seq * HD;
     float *p_tile = do_tile + seq * HD;
     const size_t group = blockIdx.x;
-    const size_t base = group * seq * HD;
-    load_rows<HD>(q + base, q_tile, seq);
-    load_rows<HD>(k + base, k_tile, seq);
-    load_rows<HD>(v + base, v_tile, seq);
-    load_rows<HD>(dout + base, do_tile, seq);
+    const size_t base = group_offset<HD>(group, seq, in_layout);
+    load_rows<HD>(q + base, q_tile, seq, in_layout.ld);
+    load_rows<HD>(k + base, k_tile, seq, in_layout.ld);
+    load_rows<HD>(v + base, v_tile, seq, in_layout.ld);
+    load_rows<HD>(dout + group_offset<HD>(group, seq, dout_layout), do_tile,
+                  seq, dout_layout.ld);
     if (!recompute) {
         move_probabilities<false>(const_cast<float *>(p) + group * seq * seq,
                                   p_tile, seq, pitch);
@@ -230,12 +246,17 @@ __global__ void attention_small_backward_kernel(
     const int row = threadIdx.x;
     float row_dot = 0.0f;
     if (row < seq) {
+        const float *out_row = out + group_offset<HD>(group, seq, out_layout) +
+                               size_t(row) * out_layout.ld;
+        const float *dout_row = dout +
+                                group_offset<HD>(group, seq, dout_layout) +
+                                size_t(row) * dout_layout.ld;
 #pragma unroll
         for (int d = 0; d < HD; d += 4) {
             const float4 o =
-                __ldcs(reinterpret_cast<const float4 *>(out + base + row * HD + d));
+                __ldcs(reinterpret_cast<const float4 *>(out_row + d));
             const float4 g =
-                __ldcs(reinterpret_cast<const float4 *>(dout + base + row * HD + d));
+                __ldcs(reinterpret_cast<const float4 *>(dout_row + d));
             row_dot += (o.x * g.x + o.y * g.y) + (o.z * g.z + o.w * g.w);
         }
     }
@@ -267,13 +288,15 @@ __global__ void attention_small_backward_kernel(
         __syncthreads();
     }
     pair_t acc[HD / 2];
+    const size_t grad_row = group_offset<HD>(group, seq, grad_layout) +
+                            size_t(row) * grad_layout.ld;
     // Columns: dV_j = sum_i P_ij dO_i.
     if (row < seq) {
         clear_row<HD>(acc);
         for (int i = 0; i < seq; ++i) {
             axpy_tile<HD>(acc, p_tile[i * pitch + row], do_tile + i * HD);
         }
-        store_row_pairs<HD>(dv + base + row * HD, acc, add_v);
+        store_row_pairs<HD>(dv + grad_row, acc, add_v);
     }
     __syncthreads();
     // Rows: score gradients in place over P, then dQ_i.
@@ -288,7 +311,7 @@ __global__ void attention_small_backward_kernel(
             scores[j] = ds;
             axpy_tile<HD>(acc, ds, k_tile + j * HD);
         }
-        store_row_pairs<HD>(dq + base + row * HD, acc, add_q);
+        store_row_pairs<HD>(dq + grad_row, acc, add_q);
     }
     __syncthreads();
     // Columns: dK_j = sum_i dS_ij Q_i.
@@ -297,7 +320,7 @@ __global__ void attention_small_backward_kernel(
         for (int i = 0; i < seq; ++i) {
             axpy_tile<HD>(acc, p_tile[i * pitch + row], q_tile + i * HD);
         }
-        store_row_pairs<HD>(dk + base + row * HD, acc, add_k);
+        store_row_pairs<HD>(dk + grad_row, acc, add_k);
     }
 }
 
@@ -312,6 +335,11 @@ bool fit_shared(Kernel kernel, size_t bytes) {
                                     int(bytes)) == cudaSuccess;
     }
     return true;
+}
+
+// {0, x} stands for "stored group by group".
+HeadLayout resolve_layout(HeadLayout layout, size_t head_dim) {
+    return layout.ld ? layout : HeadLayout{int(head_dim), 1};
 }
 
 }  // namespace
@@ -333,7 +361,11 @@ bool launch_attention_small_forward(const float *q, const float *k,
                                     const float *v, float *probabilities,
                                     float *out, size_t groups, size_t seq,
                                     size_t head_dim, float scale, bool write_p,
-                                    bool write_o, cudaStream_t stream) {
+                                    bool write_o, cudaStream_t stream,
+                                    HeadLayout in_layout,
+                                    HeadLayout out_layout) {
+    in_layout = resolve_layout(in_layout, head_dim);
+    out_layout = resolve_layout(out_layout, head_dim);
     const unsigned threads = unsigned((seq + 31) / 32 * 32);
     const size_t bytes = (2 * seq * head_dim + seq * (seq | 1)) * sizeof(float);
     bool launched = false;
@@ -342,7 +374,7 @@ bool launch_attention_small_forward(const float *q, const float *k,
         attention_small_forward_kernel<HD>                                     \
             <<<unsigned(groups), threads, bytes, stream>>>(                    \
                 q, k, v, probabilities, out, int(seq), scale, write_p,         \
-                write_o);                                                      \
+                write_o, in_layout, out_layout);                               \
         launched = true;                                                       \
     }
     VITB200_DISPATCH_HD(head_dim, CALL)
@@ -358,7 +390,14 @@ bool launch_attention_small_backward(const float *q, const float *k,
                                      size_t groups, size_t seq, size_t head_dim,
                                      float scale, bool add_q, bool add_k,
                                      bool add_v, bool recompute,
-                                     cudaStream_t stream) {
+                                     cudaStream_t stream, HeadLayout in_layout,
+                                     HeadLayout out_layout,
+                                     HeadLayout dout_layout,
+                                     HeadLayout grad_layout) {
+    in_layout = resolve_layout(in_layout, head_dim);
+    out_layout = resolve_layout(out_layout, head_dim);
+    dout_layout = resolve_layout(dout_layout, head_dim);
+    grad_layout = resolve_layout(grad_layout, head_dim);
     const unsigned threads = unsigned((seq + 31) / 32 * 32);
     const size_t bytes = (4 * seq * head_dim + seq * (seq | 1)) * sizeof(float);
     bool launched = false;
@@ -367,7 +406,8 @@ bool launch_attention_small_backward(const float *q, const float *k,
         attention_small_backward_kernel<HD>                                    \
             <<<unsigned(groups), threads, bytes, stream>>>(                    \
                 q, k, v, probabilities, out, dout, dq, dk, dv, int(seq),       \
-                scale, add_q, add_k, add_v, recompute);                                                      \
+                scale, add_q, add_k, add_v, recompute, in_layout, out_layout,  \
+                dout_layout, grad_layout);                                     \
         launched = true;                                                       \
     }
     VITB200_DISPATCH_HD(head_dim, CALL)

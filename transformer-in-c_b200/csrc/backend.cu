@@ -73,6 +73,33 @@ struct PendingGemm {
     double bytes = 0.0, flops = 0.0;
 };
 
+// A short-sequence attention forward pass held back for one op: if the host
+// merges the heads next (reference src/vit.c:489-491) the kernel writes its
+// result in the merged layout and the head-major tensor becomes a pending
+// view of it.  Input pointers are resolved when the op is recorded.
+struct PendingAttention {
+    bool active = false;
+    const float *q = nullptr, *k = nullptr, *v = nullptr;
+    HeadLayout in_layout;
+    const void *output_host = nullptr;
+    size_t batch = 0, heads = 0, seq = 0, head_dim = 0;
+    float scale = 0.0f;
+    double bytes = 0.0, flops = 0.0;
+};
+
+// The matching backward pass, held back in case the host scatters the three
+// gradients into the projected gradient next (reference src/vit.c:618-626).
+struct PendingAttentionBackward {
+    bool active = false;
+    const float *q = nullptr, *k = nullptr, *v = nullptr, *out = nullptr,
+                *dout = nullptr;
+    HeadLayout in_layout, out_layout, dout_layout;
+    const void *dq_host = nullptr, *dk_host = nullptr, *dv_host = nullptr;
+    size_t batch = 0, heads = 0, seq = 0, head_dim = 0;
+    float scale = 0.0f;
+    double bytes = 0.0, flops = 0.0;
+};
+
 constexpr int kStagingSlots = 8;
 constexpr size_t kStagingBytes = 64 * 1024;
 
@@ -104,6 +131,9 @@ struct CudaBackend {
     std::vector<cudaEvent_t> free_events;
     DataParallel *dp = nullptr;
     PendingGemm pending;
+    PendingAttention pending_attention;
+    PendingAttentionBackward pending_attention_backward;
+    unsigned long long fused_head_layouts = 0;
     // Row log-sum-exp of flash attention, one buffer per probability tensor
     // (keyed by the tensor's host address), kept from forward to backward.
     std::unordered_map<const void *, Scratch> lse_buffers;
@@ -190,8 +220,14 @@ private:
     PendingOp pending_ = {};
 };
 
+void flush_attention(CudaBackend *backend);
+
 // Launches the held-back product, with whatever was attached to it.
 void flush_pending(CudaBackend *backend) {
+    if (backend->pending_attention.active ||
+        backend->pending_attention_backward.active) {
+        flush_attention(backend);
+    }
     PendingGemm &pending = backend->pending;
     if (!pending.active) {
         return;
@@ -302,6 +338,39 @@ float *accumulate_view(CudaBackend *backend, const void *pointer, bool *add) {
     float *device = device_view_accumulate(pointer, backend->stream, &was_zero);
     *add = !was_zero;
     return device;
+}
+
+// Held-back attention kernels, in their plain form: results go to the
+// head-major tensors the host named.
+void flush_attention(CudaBackend *backend) {
+    if (backend->pending_attention.active) {
+        const PendingAttention pending = backend->pending_attention;
+        backend->pending_attention.active = false;
+        float *o = view(backend, pending.output_host, Access::Overwrite);
+        OpScope scope(backend, "multi_head_attention", pending.bytes,
+                      pending.flops);
+        launch_attention_small_forward(
+            pending.q, pending.k, pending.v, nullptr, o,
+            pending.batch * pending.heads, pending.seq, pending.head_dim,
+            pending.scale, false, true, backend->stream, pending.in_layout);
+    }
+    if (backend->pending_attention_backward.active) {
+        const PendingAttentionBackward pending =
+            backend->pending_attention_backward;
+        backend->pending_attention_backward.active = false;
+        bool add_q = true, add_k = true, add_v = true;
+        float *dq = accumulate_view(backend, pending.dq_host, &add_q);
+        float *dk = accumulate_view(backend, pending.dk_host, &add_k);
+        float *dv = accumulate_view(backend, pending.dv_host, &add_v);
+        OpScope scope(backend, "multi_head_attention_backward", pending.bytes,
+                      pending.flops);
+        launch_attention_small_backward(
+            pending.q, pending.k, pending.v, nullptr, pending.out,
+            pending.dout, dq, dk, dv, pending.batch * pending.heads,
+            pending.seq, pending.head_dim, pending.scale, add_q, add_k, add_v,
+            true, backend->stream, pending.in_layout, pending.out_layout,
+            pending.dout_layout);
+    }
 }
 
 // ---------------------------------------------------------------- op slots
@@ -601,6 +670,95 @@ int op_gelu_backward(void *context, const vitb200_tensor *input,
     return 0;
 }
 
+constexpr size_t kMaxHeadDim = 128;
+
+// Short sequences on the FP32 path: the probability matrix is half of the
+// forward pass's traffic and the backward pass can rebuild it from Q and K in
+// shared memory, so it is not written at all.  The host still owns a tensor
+// for it; that tensor is declared to be softmax(scale Q K^T) and is computed
+// only if somebody reads it.  On the same path the head-major copies of the
+// projections and of their gradients are not made either (see HeadView).
+bool lazy_probabilities_apply(size_t seq, size_t head_dim) {
+    return attention_small_supported(seq, head_dim) &&
+           gemm_default_precision() != VITB200_PRECISION_TF32;
+}
+
+// Arguments of a pending head view: the output is columns
+// [col0, col0 + d_model) of a token-major [batch*seq, row_floats] matrix,
+// regrouped per head (what split_heads writes for one of Q, K, V, and what
+// merge_heads_backward writes).
+struct HeadView {
+    size_t batch, seq, d_model, heads, row_floats, col0;
+};
+
+void materialise_head_view(const void *arguments, float *output,
+                           float *const *sources, cudaStream_t stream) {
+    HeadView d;
+    memcpy(&d, arguments, sizeof(d));
+    launch_head_view(sources[0], output, d.batch, d.seq, d.d_model, d.heads,
+                     d.row_floats, d.col0, stream);
+}
+
+bool define_head_view(CudaBackend *backend, const void *output,
+                      const void *matrix, size_t batch, size_t seq,
+                      size_t d_model, size_t heads, size_t row_floats,
+                      size_t col0) {
+    const HeadView definition = {batch, seq, d_model, heads, row_floats, col0};
+    const void *sources[1] = {matrix};
+    return coherent_define_lazy(output, sources, 1, materialise_head_view,
+                                &definition, sizeof(definition),
+                                backend->stream);
+}
+
+// An attention operand: where its values can be read right now.
+struct HeadOperand {
+    const float *pointer = nullptr;
+    HeadLayout layout;
+    const void *matrix_host = nullptr;   // set when read through a head view
+    size_t col0 = 0;
+};
+
+// If `host` is a pending head view with the geometry the attention call
+// expects, points the operand at the matrix underneath; the view itself stays
+// pending.
+bool through_head_view(const void *host, size_t batch, size_t heads, size_t seq,
+                       size_t head_dim, HeadOperand *operand) {
+    HeadView d;
+    const float *matrix = nullptr;
+    const void *matrix_host = nullptr;
+    if (!coherent_lazy_source(host, materialise_head_view, &d, sizeof(d),
+                              &matrix, &matrix_host) ||
+        d.batch != batch || d.heads != heads || d.seq != seq ||
+        d.d_model != heads * head_dim || d.row_floats % 4 != 0 ||
+        d.col0 % 4 != 0 || !fits_int(d.row_floats)) {
+        return false;
+    }
+    operand->pointer = matrix + d.col0;
+    operand->layout.ld = int(d.row_floats);
+    operand->layout.heads = int(heads);
+    operand->matrix_host = matrix_host;
+    operand->col0 = d.col0;
+    return true;
+}
+
+// Operand for reading: through a pending head view when there is one,
+// otherwise the tensor itself (computing whatever defines it).
+HeadOperand read_operand(CudaBackend *backend, const void *host, size_t batch,
+                         size_t heads, size_t seq, size_t head_dim,
+                         bool allow_view) {
+    HeadOperand operand;
+    if (!allow_view ||
+        !through_head_view(host, batch, heads, seq, head_dim, &operand)) {
+        operand = HeadOperand();
+        operand.pointer = view(backend, host, Access::Read);
+    }
+    return operand;
+}
+
+bool same_layout(const HeadLayout &a, const HeadLayout &b) {
+    return a.ld == b.ld && a.heads == b.heads;
+}
+
 int op_split_heads(void *context, const vitb200_tensor *projected,
                    vitb200_tensor *query, vitb200_tensor *key,
                    vitb200_tensor *value, size_t batch, size_t seq,
@@ -611,6 +769,15 @@ int op_split_heads(void *context, const vitb200_tensor *projected,
         return -1;
     }
     const float *p = view(backend, projected->data, Access::Read);
+    if (heads > 0 && lazy_probabilities_apply(seq, d_model / heads) &&
+        define_head_view(backend, query->data, projected->data, batch, seq,
+                         d_model, heads, 3 * d_model, 0) &&
+        define_head_view(backend, key->data, projected->data, batch, seq,
+                         d_model, heads, 3 * d_model, d_model) &&
+        define_head_view(backend, value->data, projected->data, batch, seq,
+                         d_model, heads, 3 * d_model, 2 * d_model)) {
+        return 0;
+    }
     float *q = view(backend, query->data, Access::Overwrite);
     float *k = view(backend, key->data, Access::Overwrite);
     float *v = view(backend, value->data, Access::Overwrite);
@@ -628,10 +795,56 @@ int op_split_heads_backward(void *context, vitb200_tensor *projected,
                             const vitb200_tensor *value, size_t batch,
                             size_t seq, size_t d_model, size_t heads) {
     CudaBackend *backend = self(context);
-    flush_pending(backend);
     if (!ours({projected->grad, query->grad, key->grad, value->grad})) {
+        flush_pending(backend);
         return -1;
     }
+    // The attention backward pass that produces the three gradients is still
+    // held back and nothing else has been added to them or to the projected
+    // gradient: let it write the projected gradient directly and make the
+    // three tensors views of that.
+    PendingAttentionBackward &held = backend->pending_attention_backward;
+    if (held.active && held.dq_host == query->grad &&
+        held.dk_host == key->grad && held.dv_host == value->grad &&
+        held.batch == batch && held.heads == heads && held.seq == seq &&
+        held.head_dim * heads == d_model && fits_int(3 * d_model) &&
+        coherent_is_zero_pending(query->grad) &&
+        coherent_is_zero_pending(key->grad) &&
+        coherent_is_zero_pending(value->grad) &&
+        coherent_is_zero_pending(projected->grad)) {
+        const PendingAttentionBackward pending = held;
+        held.active = false;
+        flush_pending(backend);
+        float *p = view(backend, projected->grad, Access::Overwrite);
+        HeadLayout grad_layout;
+        grad_layout.ld = int(3 * d_model);
+        grad_layout.heads = int(heads);
+        {
+            OpScope scope(backend, "multi_head_attention_backward",
+                          pending.bytes, pending.flops);
+            launch_attention_small_backward(
+                pending.q, pending.k, pending.v, nullptr, pending.out,
+                pending.dout, p, p + d_model, p + 2 * d_model, batch * heads,
+                seq, pending.head_dim, pending.scale, false, false, false,
+                true, backend->stream, pending.in_layout, pending.out_layout,
+                pending.dout_layout, grad_layout);
+        }
+        const vitb200_tensor *parts[3] = {query, key, value};
+        for (size_t which = 0; which < 3; ++which) {
+            if (!define_head_view(backend, parts[which]->grad, projected->grad,
+                                  batch, seq, d_model, heads, 3 * d_model,
+                                  which * d_model)) {
+                float *part =
+                    view(backend, parts[which]->grad, Access::Overwrite);
+                launch_head_view(p, part, batch, seq, d_model, heads,
+                                 3 * d_model, which * d_model,
+                                 backend->stream);
+            }
+        }
+        backend->fused_head_layouts += 1;
+        return 0;
+    }
+    flush_pending(backend);
     bool add = true;
     float *p = accumulate_view(backend, projected->grad, &add);
     const float *q = view(backend, query->grad, Access::Read);
@@ -650,10 +863,39 @@ int op_merge_heads(void *context, const vitb200_tensor *attended,
                    vitb200_tensor *merged, size_t batch, size_t seq,
                    size_t d_model, size_t heads) {
     CudaBackend *backend = self(context);
-    flush_pending(backend);
     if (!ours({attended->data, merged->data})) {
+        flush_pending(backend);
         return -1;
     }
+    PendingAttention &held = backend->pending_attention;
+    if (held.active && held.output_host == attended->data &&
+        held.batch == batch && held.heads == heads && held.seq == seq &&
+        held.head_dim * heads == d_model && fits_int(d_model)) {
+        const PendingAttention pending = held;
+        held.active = false;
+        flush_pending(backend);
+        float *m = view(backend, merged->data, Access::Overwrite);
+        HeadLayout out_layout;
+        out_layout.ld = int(d_model);
+        out_layout.heads = int(heads);
+        {
+            OpScope scope(backend, "multi_head_attention", pending.bytes,
+                          pending.flops);
+            launch_attention_small_forward(
+                pending.q, pending.k, pending.v, nullptr, m, batch * heads, seq,
+                pending.head_dim, pending.scale, false, true, backend->stream,
+                pending.in_layout, out_layout);
+        }
+        if (!define_head_view(backend, attended->data, merged->data, batch, seq,
+                              d_model, heads, d_model, 0)) {
+            float *a = view(backend, attended->data, Access::Overwrite);
+            launch_head_view(m, a, batch, seq, d_model, heads, d_model, 0,
+                             backend->stream);
+        }
+        backend->fused_head_layouts += 1;
+        return 0;
+    }
+    flush_pending(backend);
     const float *a = view(backend, attended->data, Access::Read);
     float *m = view(backend, merged->data, Access::Overwrite);
     {
@@ -672,9 +914,18 @@ int op_merge_heads_backward(void *context, vitb200_tensor *attended,
     if (!ours({attended->grad, merged->grad})) {
         return -1;
     }
+    const float *m = view(backend, merged->grad, Access::Read);
+    // Nothing has been added to the head-major gradient yet: it simply is
+    // the merged gradient regrouped, which attention_backward can read in
+    // place.
+    if (heads > 0 && lazy_probabilities_apply(seq, d_model / heads) &&
+        coherent_is_zero_pending(attended->grad) &&
+        define_head_view(backend, attended->grad, merged->grad, batch, seq,
+                         d_model, heads, d_model, 0)) {
+        return 0;
+    }
     bool add = true;
     float *a = accumulate_view(backend, attended->grad, &add);
-    const float *m = view(backend, merged->grad, Access::Read);
     {
         OpScope scope(backend, "merge_heads_backward", 12.0 * double(numel(merged)),
                       0.0);
@@ -684,22 +935,35 @@ int op_merge_heads_backward(void *context, vitb200_tensor *attended,
     return 0;
 }
 
-constexpr size_t kMaxHeadDim = 128;
-
-// Arguments of a pending probability matrix (see op_attention).
+// Arguments of a pending probability matrix (see op_attention).  With one
+// source the queries and keys are read through head views of that matrix
+// (column offsets q_col0 / k_col0, row stride ld); with two sources they are
+// the head-major Q and K tensors.
 struct ProbabilityDefinition {
     size_t groups, seq, head_dim;
     float scale;
     int tensor_cores;   // which forward kernel defines the values
+    int ld, heads;
+    size_t q_col0, k_col0;
 };
 
 // Produces P = softmax(scale Q K^T) for a definition that somebody finally
-// reads.  sources[0] = Q, sources[1] = K; the kernel's V input is irrelevant
-// when only P is written, K stands in for it.
+// reads.  The kernel's V input is irrelevant when only P is written, K stands
+// in for it.
 void materialise_probabilities(const void *arguments, float *output,
                                float *const *sources, cudaStream_t stream) {
     ProbabilityDefinition d;
     memcpy(&d, arguments, sizeof(d));
+    if (d.ld) {
+        HeadLayout layout;
+        layout.ld = d.ld;
+        layout.heads = d.heads;
+        launch_attention_small_forward(
+            sources[0] + d.q_col0, sources[0] + d.k_col0, sources[0] + d.k_col0,
+            output, nullptr, d.groups, d.seq, d.head_dim, d.scale, true, false,
+            stream, layout);
+        return;
+    }
     if (d.tensor_cores) {
         launch_attention_mma_forward(sources[0], sources[1], sources[1], output,
                                      nullptr, d.groups, d.seq, d.head_dim,
@@ -709,16 +973,6 @@ void materialise_probabilities(const void *arguments, float *output,
     launch_attention_small_forward(sources[0], sources[1], sources[1], output,
                                    nullptr, d.groups, d.seq, d.head_dim,
                                    d.scale, true, false, stream);
-}
-
-// Short sequences on the FP32 path: the probability matrix is half of the
-// forward pass's traffic and the backward pass can rebuild it from Q and K in
-// shared memory, so it is not written at all.  The host still owns a tensor
-// for it; that tensor is declared to be softmax(scale Q K^T) and is computed
-// only if somebody reads it.
-bool lazy_probabilities_apply(size_t seq, size_t head_dim) {
-    return attention_small_supported(seq, head_dim) &&
-           gemm_default_precision() != VITB200_PRECISION_TF32;
 }
 
 int op_attention(void *context, const vitb200_tensor *query,
@@ -734,35 +988,70 @@ int op_attention(void *context, const vitb200_tensor *query,
         return -1;
     }
     const size_t groups = batch * heads;
+    const size_t head_dim = query->cols;
+    const double flops = 4.0 * double(numel(probabilities)) * double(head_dim);
+    if (lazy_probabilities_apply(seq, head_dim)) {
+        HeadOperand q, k, v;
+        const bool through =
+            through_head_view(query->data, batch, heads, seq, head_dim, &q) &&
+            through_head_view(key->data, batch, heads, seq, head_dim, &k) &&
+            through_head_view(value->data, batch, heads, seq, head_dim, &v) &&
+            q.matrix_host && q.matrix_host == k.matrix_host &&
+            same_layout(q.layout, k.layout) && same_layout(q.layout, v.layout);
+        bool defined = false;
+        if (through) {
+            const ProbabilityDefinition definition = {
+                groups, seq, head_dim, scale, 0, q.layout.ld, q.layout.heads,
+                q.col0, k.col0};
+            const void *sources[1] = {q.matrix_host};
+            defined = coherent_define_lazy(probabilities->data, sources, 1,
+                                           materialise_probabilities,
+                                           &definition, sizeof(definition),
+                                           backend->stream);
+        }
+        if (!defined) {
+            q = read_operand(backend, query->data, batch, heads, seq, head_dim, false);
+            k = read_operand(backend, key->data, batch, heads, seq, head_dim, false);
+            v = read_operand(backend, value->data, batch, heads, seq, head_dim, false);
+            const ProbabilityDefinition definition = {groups, seq, head_dim,
+                                                      scale, 0, 0, 1, 0, 0};
+            const void *sources[2] = {query->data, key->data};
+            defined = coherent_define_lazy(probabilities->data, sources, 2,
+                                           materialise_probabilities,
+                                           &definition, sizeof(definition),
+                                           backend->stream);
+        }
+        if (defined) {
+            PendingAttention &pending = backend->pending_attention;
+            pending.active = true;
+            pending.q = q.pointer;
+            pending.k = k.pointer;
+            pending.v = v.pointer;
+            pending.in_layout = q.layout;
+            pending.output_host = output->data;
+            pending.batch = batch;
+            pending.heads = heads;
+            pending.seq = seq;
+            pending.head_dim = head_dim;
+            pending.scale = scale;
+            pending.bytes = 16.0 * double(numel(query));
+            pending.flops = flops;
+            return 0;
+        }
+    }
     const float *q = view(backend, query->data, Access::Read);
     const float *k = view(backend, key->data, Access::Read);
     const float *v = view(backend, value->data, Access::Read);
     float *o = view(backend, output->data, Access::Overwrite);
-    if (lazy_probabilities_apply(seq, query->cols)) {
-        const ProbabilityDefinition definition = {groups, seq, query->cols,
-                                                  scale, 0};
-        const void *sources[2] = {query->data, key->data};
-        if (coherent_define_lazy(probabilities->data, sources, 2,
-                                 materialise_probabilities, &definition,
-                                 sizeof(definition), backend->stream)) {
-            OpScope scope(backend, "multi_head_attention",
-                          16.0 * double(numel(query)),
-                          4.0 * double(numel(probabilities)) * double(query->cols));
-            launch_attention_small_forward(q, k, v, nullptr, o, groups, seq,
-                                           query->cols, scale, false, true,
-                                           backend->stream);
-            return 0;
-        }
-    }
     // Long sequences on tensor cores: flash attention.  One sweep, P never
     // written; the row log-sum-exp is kept for the backward pass and P itself
     // stays a pending definition.
-    const double work = double(groups) * seq * seq * query->cols;
-    if (!attention_small_supported(seq, query->cols) &&
-        attention_mma_supported(query->cols) &&
+    const double work = double(groups) * seq * seq * head_dim;
+    if (!attention_small_supported(seq, head_dim) &&
+        attention_mma_supported(head_dim) &&
         prefer_tensor_cores(VITB200_PRECISION_AUTO, work)) {
-        const ProbabilityDefinition definition = {groups, seq, query->cols,
-                                                  scale, 1};
+        const ProbabilityDefinition definition = {groups, seq, head_dim,
+                                                  scale, 1, 0, 1, 0, 0};
         const void *sources[2] = {query->data, key->data};
         Scratch &buffer = backend->lse_buffers[probabilities->data];
         float *lse = scratch<float>(backend, buffer, groups * seq);
@@ -770,10 +1059,9 @@ int op_attention(void *context, const vitb200_tensor *query,
                                  materialise_probabilities, &definition,
                                  sizeof(definition), backend->stream)) {
             OpScope scope(backend, "multi_head_attention",
-                          16.0 * double(numel(query)),
-                          4.0 * double(numel(probabilities)) * double(query->cols));
+                          16.0 * double(numel(query)), flops);
             if (launch_attention_mma_flash_forward(q, k, v, o, lse, groups, seq,
-                                                   query->cols, scale,
+                                                   head_dim, scale,
                                                    backend->stream)) {
                 return 0;
             }
@@ -782,8 +1070,8 @@ int op_attention(void *context, const vitb200_tensor *query,
     float *p = view(backend, probabilities->data, Access::Overwrite);
     {
         OpScope scope(backend, "multi_head_attention", 4.0 * (4.0 * double(numel(query)) + double(numel(probabilities))),
-                      4.0 * double(numel(probabilities)) * double(query->cols));
-        launch_attention_forward(q, k, v, p, o, groups, seq, query->cols,
+                      flops);
+        launch_attention_forward(q, k, v, p, o, groups, seq, head_dim,
                                  scale, VITB200_PRECISION_AUTO,
                                  backend->stream);
     }
@@ -808,22 +1096,67 @@ int op_attention_backward(void *context, const vitb200_tensor *query,
         return -1;
     }
     const size_t groups = batch * heads;
+    const size_t head_dim = query->cols;
+    const bool pending_p = coherent_is_lazy(probabilities->data);
+    const bool recompute = pending_p && lazy_probabilities_apply(seq, head_dim);
+    const double bytes = 4.0 * (11.0 * double(numel(query)) +
+                                (recompute ? 0.0 : double(numel(probabilities))));
+    const double flops = 8.0 * double(numel(probabilities)) * double(head_dim);
+    if (recompute) {
+        // Short sequences: P is rebuilt in shared memory; every operand that
+        // is a pending head view is read in place.  The launch is held back
+        // for op_split_heads_backward.
+        HeadOperand q, k, v;
+        const bool through =
+            through_head_view(query->data, batch, heads, seq, head_dim, &q) &&
+            through_head_view(key->data, batch, heads, seq, head_dim, &k) &&
+            through_head_view(value->data, batch, heads, seq, head_dim, &v) &&
+            same_layout(q.layout, k.layout) && same_layout(q.layout, v.layout);
+        if (!through) {
+            q = read_operand(backend, query->data, batch, heads, seq, head_dim, false);
+            k = read_operand(backend, key->data, batch, heads, seq, head_dim, false);
+            v = read_operand(backend, value->data, batch, heads, seq, head_dim, false);
+        }
+        const HeadOperand o = read_operand(backend, output->data, batch, heads,
+                                           seq, head_dim, true);
+        const HeadOperand go = read_operand(backend, output->grad, batch, heads,
+                                            seq, head_dim, true);
+        PendingAttentionBackward &pending = backend->pending_attention_backward;
+        pending.active = true;
+        pending.q = q.pointer;
+        pending.k = k.pointer;
+        pending.v = v.pointer;
+        pending.out = o.pointer;
+        pending.dout = go.pointer;
+        pending.in_layout = q.layout;
+        pending.out_layout = o.layout;
+        pending.dout_layout = go.layout;
+        pending.dq_host = query_grad->grad;
+        pending.dk_host = key_grad->grad;
+        pending.dv_host = value_grad->grad;
+        pending.batch = batch;
+        pending.heads = heads;
+        pending.seq = seq;
+        pending.head_dim = head_dim;
+        pending.scale = scale;
+        pending.bytes = bytes;
+        pending.flops = flops;
+        return 0;
+    }
     float *dots = scratch<float>(backend, backend->rows_scratch, groups * seq);
     const float *q = view(backend, query->data, Access::Read);
     const float *k = view(backend, key->data, Access::Read);
     const float *v = view(backend, value->data, Access::Read);
-    const bool pending_p = coherent_is_lazy(probabilities->data);
-    const bool recompute = pending_p && lazy_probabilities_apply(seq, query->cols);
     const float *lse = nullptr;
-    if (pending_p && !recompute) {
+    if (pending_p) {
         auto found = backend->lse_buffers.find(probabilities->data);
         if (found != backend->lse_buffers.end() &&
             found->second.bytes >= groups * seq * sizeof(float)) {
             lse = static_cast<const float *>(found->second.memory);
         }
     }
-    const float *p = (recompute || lse)
-        ? nullptr : view(backend, probabilities->data, Access::Read);
+    const float *p =
+        lse ? nullptr : view(backend, probabilities->data, Access::Read);
     const float *o = view(backend, output->data, Access::Read);
     const float *go = view(backend, output->grad, Access::Read);
     bool add_q = true, add_k = true, add_v = true;
@@ -831,21 +1164,15 @@ int op_attention_backward(void *context, const vitb200_tensor *query,
     float *dk = accumulate_view(backend, key_grad->grad, &add_k);
     float *dv = accumulate_view(backend, value_grad->grad, &add_v);
     {
-        OpScope scope(backend, "multi_head_attention_backward", 4.0 * (11.0 * double(numel(query)) + double(numel(probabilities))),
-                      8.0 * double(numel(probabilities)) * double(query->cols));
-        if (recompute) {
-            launch_attention_small_backward(q, k, v, nullptr, o, go, dq, dk, dv,
-                                            groups, seq, query->cols, scale,
-                                            add_q, add_k, add_v, true,
-                                            backend->stream);
-        } else if (lse) {
+        OpScope scope(backend, "multi_head_attention_backward", bytes, flops);
+        if (lse) {
             launch_attention_mma_backward(q, k, v, nullptr, lse, o, go, dq, dk,
-                                          dv, dots, groups, seq, query->cols,
+                                          dv, dots, groups, seq, head_dim,
                                           scale, add_q, add_k, add_v,
                                           backend->stream);
         } else {
             launch_attention_backward(q, k, v, p, o, go, dq, dk, dv, dots,
-                                      groups, seq, query->cols, scale, add_q,
+                                      groups, seq, head_dim, scale, add_q,
                                       add_k, add_v, VITB200_PRECISION_AUTO,
                                       backend->stream);
         }

@@ -21,7 +21,7 @@ struct LazyDefinition;
 
 struct Region {
     LazyDefinition *lazy = nullptr;    // this buffer's contents are defined lazily
-    LazyDefinition *feeds = nullptr;   // a lazy definition reads this buffer
+    LazyDefinition *feeds = nullptr;   // first of the definitions reading this buffer
     char *mirror = nullptr;
     size_t bytes = 0;         // size the host asked for
     size_t mapped = 0;        // page-rounded size of the mapping
@@ -116,18 +116,28 @@ void ensure_device_buffer(Region &region) {
     g_stats.device_bytes += region.mapped;
 }
 
+// A device buffer that outlived its region's use of it because pending
+// definitions still read the old contents; shared by all of them.
+struct Snapshot {
+    float *device = nullptr;
+    size_t bytes = 0;
+    int references = 0;
+};
+
 // A buffer whose contents are a known function of (at most two) other
-// buffers and have not been computed.  If a source is about to be overwritten
-// while the definition is still pending, the source keeps its old device
-// buffer alive here (`snapshot`) and continues with a fresh one.
+// buffers and have not been computed.  All definitions reading one source are
+// chained from the source's `feeds` through `next_reader`.  If a source is
+// about to be overwritten while definitions are still pending, its old device
+// buffer moves into a Snapshot they share and the source continues with a
+// fresh buffer.
 struct LazyDefinition {
     LazyMaterialise function = nullptr;
     unsigned char arguments[64] = {};
     Region *output = nullptr;
     int sources = 0;
     Region *source[2] = {nullptr, nullptr};
-    float *snapshot[2] = {nullptr, nullptr};
-    size_t snapshot_bytes[2] = {0, 0};
+    Snapshot *snapshot[2] = {nullptr, nullptr};
+    LazyDefinition *next_reader[2] = {nullptr, nullptr};
 };
 
 void recycle(float *device, size_t bytes) {
@@ -139,14 +149,32 @@ void recycle(float *device, size_t bytes) {
     }
 }
 
+int reader_slot(const LazyDefinition *lazy, const Region *region) {
+    return lazy->source[0] == region ? 0 : 1;
+}
+
+void unlink_reader(LazyDefinition *lazy, int slot) {
+    Region *region = lazy->source[slot];
+    LazyDefinition **link = &region->feeds;
+    while (*link && *link != lazy) {
+        link = &(*link)->next_reader[reader_slot(*link, region)];
+    }
+    if (*link) {
+        *link = lazy->next_reader[slot];
+    }
+    lazy->source[slot] = nullptr;
+    lazy->next_reader[slot] = nullptr;
+}
+
 // Forgets a definition without computing it (its output is being redefined).
 void drop_lazy(LazyDefinition *lazy) {
     for (int i = 0; i < lazy->sources; ++i) {
         if (lazy->source[i]) {
-            lazy->source[i]->feeds = nullptr;
+            unlink_reader(lazy, i);
         }
-        if (lazy->snapshot[i]) {
-            recycle(lazy->snapshot[i], lazy->snapshot_bytes[i]);
+        if (lazy->snapshot[i] && --lazy->snapshot[i]->references == 0) {
+            recycle(lazy->snapshot[i]->device, lazy->snapshot[i]->bytes);
+            delete lazy->snapshot[i];
         }
     }
     if (lazy->output) {
@@ -156,13 +184,17 @@ void drop_lazy(LazyDefinition *lazy) {
     g_stats.lazy_dropped += 1;
 }
 
+const float *source_device(const LazyDefinition *lazy, int slot) {
+    return lazy->snapshot[slot] ? lazy->snapshot[slot]->device
+                                : lazy->source[slot]->device;
+}
+
 // Computes a pending definition into its output buffer.
 void materialise_lazy(LazyDefinition *lazy, cudaStream_t stream) {
     ensure_device_buffer(*lazy->output);
     float *inputs[2] = {nullptr, nullptr};
     for (int i = 0; i < lazy->sources; ++i) {
-        inputs[i] = lazy->snapshot[i] ? lazy->snapshot[i]
-                                      : lazy->source[i]->device;
+        inputs[i] = const_cast<float *>(source_device(lazy, i));
     }
     lazy->function(lazy->arguments, lazy->output->device, inputs, stream);
     g_stats.lazy_materialised += 1;
@@ -170,15 +202,28 @@ void materialise_lazy(LazyDefinition *lazy, cudaStream_t stream) {
     drop_lazy(lazy);
 }
 
-// The source is about to change: give the pending reader the old buffer.
+// Computes every definition that reads `region` (it is about to be modified
+// in place).
+void materialise_readers(Region &region, cudaStream_t stream) {
+    while (region.feeds) {
+        materialise_lazy(region.feeds, stream);
+    }
+}
+
+// The source is about to be replaced wholesale: the pending readers keep the
+// old buffer, the region goes on without one.
 void detach_source(Region &region) {
-    LazyDefinition *lazy = region.feeds;
-    for (int i = 0; i < lazy->sources; ++i) {
-        if (lazy->source[i] == &region) {
-            lazy->snapshot[i] = region.device;
-            lazy->snapshot_bytes[i] = region.mapped;
-            lazy->source[i] = nullptr;
-        }
+    Snapshot *snapshot = new Snapshot();
+    snapshot->device = region.device;
+    snapshot->bytes = region.mapped;
+    for (LazyDefinition *lazy = region.feeds; lazy;) {
+        const int slot = reader_slot(lazy, &region);
+        LazyDefinition *next = lazy->next_reader[slot];
+        lazy->snapshot[slot] = snapshot;
+        lazy->source[slot] = nullptr;
+        lazy->next_reader[slot] = nullptr;
+        snapshot->references += 1;
+        lazy = next;
     }
     region.feeds = nullptr;
     g_stats.device_bytes -= region.mapped;
@@ -198,7 +243,7 @@ void materialise_zero(Region &region, cudaStream_t stream) {
 // `for_write` selects HOST (exclusive) over SHARED (both valid).
 void serve_host_access(Region &region, bool for_write) {
     if (region.feeds && for_write) {
-        materialise_lazy(region.feeds, g_stream);
+        materialise_readers(region, g_stream);
     }
     if (region.owner == Owner::Device) {
         if (g_flush) {
@@ -357,7 +402,7 @@ float *device_view(const void *host_pointer, Access access,
         if (access == Access::Overwrite && region->device) {
             detach_source(*region);
         } else {
-            materialise_lazy(region->feeds, stream);
+            materialise_readers(*region, stream);
         }
     }
     ensure_device_buffer(*region);
@@ -416,6 +461,9 @@ bool coherent_mark_zero(const void *host_pointer, cudaStream_t stream) {
     if (region->lazy) {
         drop_lazy(region->lazy);
     }
+    if (region->feeds) {
+        detach_source(*region);   // pending readers keep the old contents
+    }
     // No device buffer is created here: a gradient that nobody writes in a
     // step (the probability matrix's, the images') never needs one.
     if (region->owner != Owner::Device) {
@@ -441,7 +489,10 @@ bool coherent_define_lazy(const void *output_host,
     Region *inputs[2] = {nullptr, nullptr};
     for (int i = 0; i < sources; ++i) {
         inputs[i] = find_base(source_hosts[i]);
-        if (!inputs[i] || !inputs[i]->device || inputs[i] == output) {
+        // A source must hold its current contents on the device.
+        if (!inputs[i] || inputs[i] == output || inputs[i]->lazy ||
+            !inputs[i]->device || inputs[i]->owner == Owner::Host ||
+            inputs[i]->zero_pending || (i == 1 && inputs[1] == inputs[0])) {
             return false;
         }
     }
@@ -449,11 +500,10 @@ bool coherent_define_lazy(const void *output_host,
         drop_lazy(output->lazy);
     }
     if (output->feeds) {
-        materialise_lazy(output->feeds, stream);
-    }
-    for (int i = 0; i < sources; ++i) {
-        if (inputs[i]->feeds) {
-            materialise_lazy(inputs[i]->feeds, stream);
+        if (output->device) {
+            detach_source(*output);
+        } else {
+            materialise_readers(*output, stream);
         }
     }
     LazyDefinition *lazy = new LazyDefinition();
@@ -463,6 +513,7 @@ bool coherent_define_lazy(const void *output_host,
     lazy->sources = sources;
     for (int i = 0; i < sources; ++i) {
         lazy->source[i] = inputs[i];
+        lazy->next_reader[i] = inputs[i]->feeds;
         inputs[i]->feeds = lazy;
     }
     output->lazy = lazy;
@@ -481,6 +532,27 @@ bool coherent_define_lazy(const void *output_host,
 bool coherent_is_lazy(const void *host_pointer) {
     Region *region = host_pointer ? find_base(host_pointer) : nullptr;
     return region && region->lazy != nullptr;
+}
+
+bool coherent_lazy_source(const void *output_host, LazyMaterialise function,
+                          void *arguments, size_t argument_bytes,
+                          const float **source, const void **source_host) {
+    Region *region = output_host ? find_base(output_host) : nullptr;
+    if (!region || !region->lazy || region->lazy->function != function ||
+        region->lazy->sources != 1 ||
+        argument_bytes > sizeof(LazyDefinition::arguments)) {
+        return false;
+    }
+    memcpy(arguments, region->lazy->arguments, argument_bytes);
+    *source = source_device(region->lazy, 0);
+    *source_host = region->lazy->source[0] ? region->lazy->source[0]->mirror
+                                           : nullptr;
+    return true;
+}
+
+bool coherent_is_zero_pending(const void *host_pointer) {
+    Region *region = host_pointer ? find_base(host_pointer) : nullptr;
+    return region && region->zero_pending && !region->lazy;
 }
 
 float *device_view_accumulate(const void *host_pointer, cudaStream_t stream,

@@ -73,9 +73,10 @@ float *device_view_accumulate(const void *host_pointer, cudaStream_t stream,
 // without computing it.  The value is produced (by calling `function` on the
 // stream) the first time anybody, device op or host, reads the buffer, and is
 // never produced if the buffer is overwritten first.  Sources stay readable:
-// if one is about to be overwritten while the definition is pending, its old
-// device buffer is handed to the definition and the source continues in a
-// fresh one, so no copy is made either way.
+// if one is about to be overwritten while definitions are pending, its old
+// device buffer is handed to them and the source continues in a fresh one, so
+// no copy is made either way.  Any number of definitions may read one source;
+// a source must itself hold computed values on the device.
 typedef void (*LazyMaterialise)(const void *arguments, float *output,
                                 float *const *sources, cudaStream_t stream);
 bool coherent_define_lazy(const void *output_host,
@@ -83,6 +84,18 @@ bool coherent_define_lazy(const void *output_host,
                           LazyMaterialise function, const void *arguments,
                           size_t argument_bytes, cudaStream_t stream);
 bool coherent_is_lazy(const void *host_pointer);
+// For an output pending under `function` with one source: copies the
+// definition's arguments out and returns the device pointer that currently
+// holds the source's values, so that a consumer can read through the
+// definition instead of having it computed.  The pointer is valid for work
+// enqueued on the stream before the next call into this layer.  *source_host
+// is the source's host address, or nullptr when the source has moved on and
+// the definition reads a kept copy of its old contents.
+bool coherent_lazy_source(const void *output_host, LazyMaterialise function,
+                          void *arguments, size_t argument_bytes,
+                          const float **source, const void **source_host);
+// True while the buffer is a pending zero fill (see coherent_mark_zero).
+bool coherent_is_zero_pending(const void *host_pointer);
 
 // Makes the mirror readable and writable by the host again (copying back if
 // the device holds the current contents).  Needed before handing a mirror to a

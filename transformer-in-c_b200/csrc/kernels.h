@@ -44,6 +44,11 @@ void launch_merge_heads(const float *attended, float *merged, size_t batch,
 void launch_merge_heads_backward(float *attended_grad, const float *merged_grad,
                                  size_t batch, size_t seq, size_t d_model,
                                  size_t heads, bool add, cudaStream_t stream);
+// view = columns [col0, col0 + d_model) of a [batch*seq, row_floats] matrix in
+// head-major order ([batch*heads*seq, d_model/heads]).
+void launch_head_view(const float *matrix, float *view, size_t batch, size_t seq,
+                      size_t d_model, size_t heads, size_t row_floats,
+                      size_t col0, cudaStream_t stream);
 void launch_extract_patches(const float *images, float *patches, size_t batch,
                             size_t channels, size_t height, size_t width,
                             size_t patch, cudaStream_t stream);
@@ -123,11 +128,22 @@ bool launch_attention_mma_backward(const float *q, const float *k,
 // (attention_small.cu).  The launchers return false when the shape is outside
 // what they cover; the tiled kernels above take over then.
 bool attention_small_supported(size_t seq, size_t head_dim);
+// Where the rows of a (sample, head) group live.  Row t of group g starts
+// (g / heads) * seq * ld + (g % heads) * head_dim + t * ld floats after the
+// base pointer: {ld, heads} addresses one head's columns inside a token-major
+// [batch*seq, ld] matrix (the base pointer already includes the first
+// column), and the default {0, 1} means "stored group by group".
+struct HeadLayout {
+    int ld = 0;
+    int heads = 1;
+};
 bool launch_attention_small_forward(const float *q, const float *k,
                                     const float *v, float *probabilities,
                                     float *out, size_t groups, size_t seq,
                                     size_t head_dim, float scale, bool write_p,
-                                    bool write_o, cudaStream_t stream);
+                                    bool write_o, cudaStream_t stream,
+                                    HeadLayout in_layout = HeadLayout(),
+                                    HeadLayout out_layout = HeadLayout());
 // recompute = true: `probabilities` is not read; P is rebuilt from Q and K.
 bool launch_attention_small_backward(const float *q, const float *k,
                                      const float *v, const float *probabilities,
@@ -136,7 +152,11 @@ bool launch_attention_small_backward(const float *q, const float *k,
                                      size_t groups, size_t seq, size_t head_dim,
                                      float scale, bool add_q, bool add_k,
                                      bool add_v, bool recompute,
-                                     cudaStream_t stream);
+                                     cudaStream_t stream,
+                                     HeadLayout in_layout = HeadLayout(),
+                                     HeadLayout out_layout = HeadLayout(),
+                                     HeadLayout dout_layout = HeadLayout(),
+                                     HeadLayout grad_layout = HeadLayout());
 
 // ---- loss (loss.cu) -------------------------------------------------------
 // row_losses: scratch of `rows` floats.

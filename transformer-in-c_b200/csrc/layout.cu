@@ -126,6 +126,24 @@ __global__ void merge_heads_backward_kernel(float *__restrict__ attended_grad,
     }
 }
 
+// One head-major tensor out of a token-major matrix: columns
+// [col0, col0 + d_model) of rows `row_floats` wide, regrouped per head.  This
+// is a third of split_heads and all of merge_heads_backward without the add.
+template <int V>
+__global__ void head_view_kernel(const float *__restrict__ matrix,
+                                 float *__restrict__ view, size_t batch,
+                                 size_t seq, size_t d_model, size_t heads,
+                                 size_t row_floats, size_t col0) {
+    using T = typename Vec<V>::type;
+    const size_t head_dim = d_model / heads;
+    const size_t total = batch * seq * d_model / V;
+    for (size_t i = global_thread(); i < total; i += grid_threads()) {
+        reinterpret_cast<T *>(view)[i] = reinterpret_cast<const T *>(
+            matrix)[token_major_index<V>(i, seq, heads, head_dim, row_floats,
+                                         col0)];
+    }
+}
+
 // patches[row, c*P*P + y*P + x] = image pixel (reference src/ops.c:379-392).
 template <int V>
 __global__ void extract_patches_kernel(const float *__restrict__ images,
@@ -236,6 +254,15 @@ __global__ void gather_rows_kernel(const float *__restrict__ strided,
         }                                                                      \
         ++g_kernel_launches;                                                   \
     } while (0)
+
+void launch_head_view(const float *matrix, float *view, size_t batch, size_t seq,
+                      size_t d_model, size_t heads, size_t row_floats,
+                      size_t col0, cudaStream_t stream) {
+    const bool vec = (d_model / heads) % 4 == 0 && row_floats % 4 == 0 &&
+                     col0 % 4 == 0;
+    VITB200_LAUNCH_V(vec, head_view_kernel, batch * seq * d_model, matrix, view,
+                     batch, seq, d_model, heads, row_floats, col0);
+}
 
 void launch_split_heads(const float *projected, float *q, float *k, float *v,
                         size_t batch, size_t seq, size_t d_model, size_t heads,
