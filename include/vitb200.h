@@ -170,6 +170,10 @@ int vitb200_k_layer_norm_backward(const float *x, const float *gamma,
 int vitb200_k_gelu(const float *in, float *out, size_t n, void *stream);
 int vitb200_k_gelu_backward(const float *x, const float *dy, float *dx,
                             size_t n, void *stream);
+/* probabilities may be NULL for seq <= 128 (FP32; head_dim 8, 16, 32, 64) or
+ * seq <= 64 (TF32; head_dim 16, 32): P then stays on chip in the forward pass
+ * and is rebuilt from Q and K in the backward pass (row_dots unused).  -1 if
+ * the shape has no such kernel. */
 int vitb200_k_attention(const float *q, const float *k, const float *v,
                         float *probabilities, float *out, size_t groups,
                         size_t seq, size_t head_dim, float scale, int precision,

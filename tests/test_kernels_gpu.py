@@ -229,6 +229,49 @@ def test_attention_forward_and_backward(lib, groups, seq, hd, precision):
     np.testing.assert_allclose(host(tp).sum(axis=1), 1.0, atol=1e-5)
 
 
+@pytest.mark.parametrize("precision", [FP32, TF32], ids=["fp32", "tf32"])
+@pytest.mark.parametrize("groups,seq,hd", [
+    (1, 1, 16), (3, 5, 16), (16, 50, 16), (5, 64, 16), (4, 17, 32),
+    (3, 50, 32), (2, 64, 32), (7, 33, 16), (300, 50, 16),
+])
+def test_attention_without_probability_matrix(lib, groups, seq, hd, precision):
+    """P = NULL: the whole-group kernels that never write P (FP32 SIMT, or
+    TF32 tensor cores with every intermediate tile in registers).  Same
+    tolerances as the kernels that do write it."""
+    forward_tol, backward_tol = (1e-5, 2e-5) if precision == FP32 else (2e-3, 2e-3)
+    rng = np.random.RandomState(groups * seq + hd + 1)
+    rows = groups * seq
+    q, k, v, dout = (rng.randn(rows, hd) for _ in range(4))
+    dq0, dk0, dv0 = (rng.randn(rows, hd) for _ in range(3))
+    scale = 1.0 / np.sqrt(hd)
+    tq, tk, tv, tdo = dev(q), dev(k), dev(v), dev(dout)
+    to = torch.empty(rows, hd, device="cuda")
+    tdq, tdk, tdv = dev(dq0), dev(dk0), dev(dv0)
+    assert lib.vitb200_k_attention(ptr(tq), ptr(tk), ptr(tv), None, ptr(to),
+                                   size(groups), size(seq), size(hd),
+                                   ctypes.c_float(scale), precision, None) == 0
+    assert lib.vitb200_k_attention_backward(
+        ptr(tq), ptr(tk), ptr(tv), None, ptr(to), ptr(tdo), ptr(tdq),
+        ptr(tdk), ptr(tdv), None, size(groups), size(seq), size(hd),
+        ctypes.c_float(scale), precision, None) == 0
+    p, o = vo.multi_head_attention(q, k, v, groups, seq, scale)
+    close(host(to), o, forward_tol)
+    dq, dk, dv = vo.multi_head_attention_backward(q, k, v, p, dout, groups,
+                                                  seq, scale)
+    close(host(tdq), dq0 + dq, backward_tol)
+    close(host(tdk), dk0 + dk, backward_tol)
+    close(host(tdv), dv0 + dv, backward_tol)
+
+
+def test_attention_without_probability_matrix_rejects_long_sequences(lib):
+    dummy = torch.zeros(1, device="cuda")
+    for precision, seq in ((FP32, 129), (TF32, 65)):
+        assert lib.vitb200_k_attention(ptr(dummy), ptr(dummy), ptr(dummy), None,
+                                       ptr(dummy), size(1), size(seq), size(16),
+                                       ctypes.c_float(1.0), precision,
+                                       None) == -1
+
+
 def test_attention_rejects_unsupported_head_dim(lib):
     dummy = torch.zeros(1, device="cuda")
     assert lib.vitb200_k_attention(ptr(dummy), ptr(dummy), ptr(dummy),

@@ -1,0 +1,568 @@
+// Tensor-core attention for sequences of at most 64 tokens: the whole
+// (sample, head) group is one 64 x 64 score tile, and everything between the
+// operand tiles and the results stays in registers.
+//
+// Same mathematics as the FP32 kernels (reference src/ops.c:1297-1355 forward,
+// :1381-1441 backward) on warp-level mma.sync m16n8k8 with TF32 operands
+// rounded to nearest and FP32 accumulation.  A block of two warps serves one
+// group; a warp owns 16-row tiles of the result.  The operand matrices
+// (K, V for the forward pass; Q, K, V, dO for the backward pass) are staged in
+// shared memory once, already rounded; no score, probability or gradient tile
+// ever goes to shared memory:
+//
+//  * The accumulator layout of one product is turned into the A operand of
+//    the next (P -> P V, dS -> dS K, P^T -> P^T dO, dS^T -> dS^T Q) without
+//    moving data between lanes.  A lane holds columns 2t and 2t+1 of every
+//    8-column accumulator tile; an A fragment wants columns t and t+4.  The
+//    sum over the contraction index does not care about its order, so the
+//    lane's two columns are declared to be "t" and "t+4" and the B operand's
+//    rows are fetched in the matching order (rows 8s+2t and 8s+2t+1).
+//  * The same freedom on the head dimension lets every fragment be fetched
+//    with 64- or 128-bit shared-memory loads: lane t owns HD/4 consecutive
+//    floats of a row and feeds them to the k-steps two at a time.
+//  * The backward pass needs P and dS transposed for dV and dK.  Instead of
+//    transposing through shared memory it recomputes the transposed tiles
+//    from swapped operands (S^T = K Q^T, dP^T = V dO^T) and normalises them
+//    with the per-row log-sum-exp and D = dO.O values of the first pass, the
+//    only data exchanged between the two warps (128 floats).
+//
+// Operands and results are addressed through HeadLayout, so the kernels read
+// Q, K, V straight out of the projected matrix and write into the merged /
+// projected-gradient matrices when the caller fuses the head regrouping.
+#include "kernels.h"
+#include "device_util.cuh"
+
+#include <cfloat>
+#include <cstdint>
+
+namespace vitb200 {
+namespace {
+
+constexpr int kTile = 64;       // rows of every staged operand tile
+constexpr int kWarps = 2;
+constexpr int kThreads = kWarps * 32;
+constexpr float kLog2e = 1.4426950408889634f;
+
+__device__ __forceinline__ float to_tf32(float x) {
+    uint32_t r;
+    asm("cvt.rna.tf32.f32 %0, %1;" : "=r"(r) : "f"(x));
+    return __uint_as_float(r);
+}
+
+__device__ __forceinline__ float exp2_fast(float x) {
+    float y;
+    asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+    return y;
+}
+
+__device__ __forceinline__ void mma_tf32(float (&c)[4], float a0, float a1,
+                                         float a2, float a3, float b0,
+                                         float b1) {
+    asm volatile(
+        "mma.sync.aligned.m16n8k8.row.col.f32.tf32.tf32.f32 "
+        "{%0, %1, %2, %3}, {%4, %5, %6, %7}, {%8, %9}, {%0, %1, %2, %3};"
+        : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+        : "r"(__float_as_uint(a0)), "r"(__float_as_uint(a1)),
+          "r"(__float_as_uint(a2)), "r"(__float_as_uint(a3)),
+          "r"(__float_as_uint(b0)), "r"(__float_as_uint(b1)));
+}
+
+__device__ __forceinline__ float quad_max(float v) {
+    v = fmaxf(v, __shfl_xor_sync(kFullMask, v, 1));
+    return fmaxf(v, __shfl_xor_sync(kFullMask, v, 2));
+}
+
+__device__ __forceinline__ float quad_sum(float v) {
+    v += __shfl_xor_sync(kFullMask, v, 1);
+    return v + __shfl_xor_sync(kFullMask, v, 2);
+}
+
+template <int HD>
+struct Shape {
+    static constexpr int kPitch = HD + 4;     // floats between tile rows
+    static constexpr int kRange = HD / 4;     // floats of a row one lane owns
+    static constexpr int kSteps = HD / 8;     // k-steps over the head dimension
+    static constexpr int kOut = HD / 8;       // 8-column tiles of an HD-wide result
+};
+
+// The lane's kRange consecutive floats of a row (16-byte aligned).
+template <int N>
+__device__ __forceinline__ void load_range(float (&x)[N], const float *source) {
+#pragma unroll
+    for (int i = 0; i < N; i += 4) {
+        const float4 v = *reinterpret_cast<const float4 *>(source + i);
+        x[i] = v.x; x[i + 1] = v.y; x[i + 2] = v.z; x[i + 3] = v.w;
+    }
+}
+
+template <int N>
+__device__ __forceinline__ void load_range_global(float (&x)[N],
+                                                  const float *source,
+                                                  bool rounded) {
+#pragma unroll
+    for (int i = 0; i < N; i += 4) {
+        const float4 v = __ldcs(reinterpret_cast<const float4 *>(source + i));
+        x[i] = rounded ? to_tf32(v.x) : v.x;
+        x[i + 1] = rounded ? to_tf32(v.y) : v.y;
+        x[i + 2] = rounded ? to_tf32(v.z) : v.z;
+        x[i + 3] = rounded ? to_tf32(v.w) : v.w;
+    }
+}
+
+// Staging of rows [0, 64) of a matrix whose rows are `ld` floats apart, in two
+// halves so that a block can put the loads of all its tiles in flight before
+// it waits for any of them: the groups are small, and with one load
+// outstanding per thread the kernel would be bound by memory latency.  Values
+// are stored rounded to TF32; rows past `seq` are zero.
+template <int HD>
+struct Staged {
+    float4 value[kTile * (HD / 4) / kThreads];
+};
+
+template <int HD>
+__device__ __forceinline__ void stage_load(Staged<HD> &staged,
+                                           const float *__restrict__ source,
+                                           int ld, int seq) {
+    constexpr int kVectors = HD / 4;
+#pragma unroll
+    for (int j = 0; j < kTile * kVectors / kThreads; ++j) {
+        const int i = threadIdx.x + j * kThreads;
+        const int r = i / kVectors;
+        const int c = (i % kVectors) * 4;
+        staged.value[j] = make_float4(0.f, 0.f, 0.f, 0.f);
+        if (r < seq) {
+            staged.value[j] = __ldcs(
+                reinterpret_cast<const float4 *>(source + size_t(r) * ld + c));
+        }
+    }
+}
+
+template <int HD>
+__device__ __forceinline__ void stage_store(const Staged<HD> &staged,
+                                            float *tile) {
+    constexpr int kVectors = HD / 4;
+#pragma unroll
+    for (int j = 0; j < kTile * kVectors / kThreads; ++j) {
+        const int i = threadIdx.x + j * kThreads;
+        const int r = i / kVectors;
+        const int c = (i % kVectors) * 4;
+        const float4 v = staged.value[j];
+        *reinterpret_cast<float4 *>(tile + r * Shape<HD>::kPitch + c) =
+            make_float4(to_tf32(v.x), to_tf32(v.y), to_tf32(v.z), to_tf32(v.w));
+    }
+}
+
+template <int HD>
+__device__ __forceinline__ size_t group_offset(size_t group, int seq,
+                                               HeadLayout layout) {
+    return (group / layout.heads) * size_t(seq) * layout.ld +
+           (group % layout.heads) * HD;
+}
+
+// c[16 x 64] += A B^T: A = rows (a0, a1) given as lane ranges, B = a staged
+// tile whose rows are the result's columns.
+template <int HD>
+__device__ __forceinline__ void product_rows(float (&c)[8][4],
+                                             const float (&a0)[HD / 4],
+                                             const float (&a1)[HD / 4],
+                                             const float *tile, int tiles,
+                                             int g, int t) {
+    using S = Shape<HD>;
+#pragma unroll
+    for (int n = 0; n < 8; ++n) {
+        if (n < tiles) {
+            float b[S::kRange];
+            load_range(b, tile + (n * 8 + g) * S::kPitch + t * S::kRange);
+#pragma unroll
+            for (int s = 0; s < S::kSteps; ++s) {
+                mma_tf32(c[n], a0[2 * s], a1[2 * s], a0[2 * s + 1],
+                         a1[2 * s + 1], b[2 * s], b[2 * s + 1]);
+            }
+        }
+    }
+}
+
+// o[16 x HD] += P B: P = an accumulator tile set reused as the A operand
+// (columns 2t, 2t+1 of tile s), B = a staged tile whose rows are the
+// contraction index.  Result element e of the lane's row range is
+// o[e % kOut][e / kOut] (row g) and o[e % kOut][2 + e / kOut] (row g + 8).
+template <int HD>
+__device__ __forceinline__ void product_columns(float (&o)[HD / 8][4],
+                                                const float (&p)[8][4],
+                                                const float *tile, int tiles,
+                                                int g, int t) {
+    using S = Shape<HD>;
+#pragma unroll
+    for (int s = 0; s < 8; ++s) {
+        if (s < tiles) {
+            float b0[S::kOut < 4 ? 4 : S::kOut], b1[S::kOut < 4 ? 4 : S::kOut];
+            const float *row = tile + (s * 8 + 2 * t) * S::kPitch + g * S::kOut;
+            if (S::kOut == 2) {
+                const float2 x = *reinterpret_cast<const float2 *>(row);
+                const float2 y = *reinterpret_cast<const float2 *>(row + S::kPitch);
+                b0[0] = x.x; b0[1] = x.y; b1[0] = y.x; b1[1] = y.y;
+            } else {
+#pragma unroll
+                for (int i = 0; i < S::kOut; i += 4) {
+                    const float4 x = *reinterpret_cast<const float4 *>(row + i);
+                    const float4 y = *reinterpret_cast<const float4 *>(row + S::kPitch + i);
+                    b0[i] = x.x; b0[i + 1] = x.y; b0[i + 2] = x.z; b0[i + 3] = x.w;
+                    b1[i] = y.x; b1[i + 1] = y.y; b1[i + 2] = y.z; b1[i + 3] = y.w;
+                }
+            }
+            const float a0 = to_tf32(p[s][0]), a1 = to_tf32(p[s][2]);
+            const float a2 = to_tf32(p[s][1]), a3 = to_tf32(p[s][3]);
+#pragma unroll
+            for (int u = 0; u < S::kOut; ++u) {
+                mma_tf32(o[u], a0, a1, a2, a3, b0[u], b1[u]);
+            }
+        }
+    }
+}
+
+// Writes (or adds) the lane's ranges of result rows r0 and r1.
+template <int HD>
+__device__ __forceinline__ void store_result(float *base, int ld, int r0, int r1,
+                                             int seq, int t,
+                                             const float (&o)[HD / 8][4],
+                                             bool add) {
+    using S = Shape<HD>;
+#pragma unroll
+    for (int half = 0; half < 2; ++half) {
+        const int row = half ? r1 : r0;
+        if (row < seq) {
+            float *target = base + size_t(row) * ld + t * S::kRange;
+#pragma unroll
+            for (int e = 0; e < S::kRange; e += 4) {
+                float4 v = add ? *reinterpret_cast<float4 *>(target + e)
+                               : make_float4(0.f, 0.f, 0.f, 0.f);
+                v.x += o[(e + 0) % S::kOut][2 * half + (e + 0) / S::kOut];
+                v.y += o[(e + 1) % S::kOut][2 * half + (e + 1) / S::kOut];
+                v.z += o[(e + 2) % S::kOut][2 * half + (e + 2) / S::kOut];
+                v.w += o[(e + 3) % S::kOut][2 * half + (e + 3) / S::kOut];
+                *reinterpret_cast<float4 *>(target + e) = v;
+            }
+        }
+    }
+}
+
+template <int N>
+__device__ __forceinline__ void clear(float (&c)[N][4]) {
+#pragma unroll
+    for (int n = 0; n < N; ++n) {
+        c[n][0] = c[n][1] = c[n][2] = c[n][3] = 0.0f;
+    }
+}
+
+// Row-wise softmax of a 16 x 64 accumulator tile set holding raw scores:
+// p = exp2(scale2 * s - lse2) with columns >= seq masked out.  Returns the two
+// rows' log-sum-exp (base 2, scaled scores).
+__device__ __forceinline__ void softmax_rows(float (&s)[8][4], int seq, int t,
+                                             float scale2, float &lse_a,
+                                             float &lse_b) {
+    float max_a = -FLT_MAX, max_b = -FLT_MAX;
+#pragma unroll
+    for (int n = 0; n < 8; ++n) {
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+            const int column = n * 8 + 2 * t + (e & 1);
+            s[n][e] = column < seq ? s[n][e] * scale2 : -FLT_MAX;
+        }
+        max_a = fmaxf(max_a, fmaxf(s[n][0], s[n][1]));
+        max_b = fmaxf(max_b, fmaxf(s[n][2], s[n][3]));
+    }
+    max_a = quad_max(max_a);
+    max_b = quad_max(max_b);
+    float sum_a = 0.0f, sum_b = 0.0f;
+#pragma unroll
+    for (int n = 0; n < 8; ++n) {
+        s[n][0] = exp2_fast(s[n][0] - max_a);
+        s[n][1] = exp2_fast(s[n][1] - max_a);
+        s[n][2] = exp2_fast(s[n][2] - max_b);
+        s[n][3] = exp2_fast(s[n][3] - max_b);
+        sum_a += s[n][0] + s[n][1];
+        sum_b += s[n][2] + s[n][3];
+    }
+    sum_a = quad_sum(sum_a);
+    sum_b = quad_sum(sum_b);
+    const float inverse_a = 1.0f / sum_a, inverse_b = 1.0f / sum_b;
+#pragma unroll
+    for (int n = 0; n < 8; ++n) {
+        s[n][0] *= inverse_a;
+        s[n][1] *= inverse_a;
+        s[n][2] *= inverse_b;
+        s[n][3] *= inverse_b;
+    }
+    lse_a = max_a + log2f(sum_a);
+    lse_b = max_b + log2f(sum_b);
+}
+
+template <int HD>
+__global__ void __launch_bounds__(kThreads)
+attention_warp_forward_kernel(const float *__restrict__ q,
+                              const float *__restrict__ k,
+                              const float *__restrict__ v,
+                              float *__restrict__ out, int seq, float scale,
+                              HeadLayout in_layout, HeadLayout out_layout) {
+    using S = Shape<HD>;
+    __shared__ __align__(16) float k_tile[kTile * S::kPitch];
+    __shared__ __align__(16) float v_tile[kTile * S::kPitch];
+    const size_t group = blockIdx.x;
+    const size_t in_base = group_offset<HD>(group, seq, in_layout);
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const int g = lane >> 2, t = lane & 3;
+    // All global loads of the block go out together: the K and V tiles and
+    // the query rows of this warp's (at most two) row tiles.  Rows past the
+    // end repeat the last row; their results are dropped.
+    float query[2][2][S::kRange];
+    {
+        Staged<HD> k_staged, v_staged;
+        stage_load<HD>(k_staged, k + in_base, in_layout.ld, seq);
+        stage_load<HD>(v_staged, v + in_base, in_layout.ld, seq);
+#pragma unroll
+        for (int pass = 0; pass < 2; ++pass) {
+            const int r0 = (warp + pass * kWarps) * 16 + g;
+            load_range_global(query[pass][0], q + in_base + size_t(min(r0, seq - 1)) * in_layout.ld + t * S::kRange, true);
+            load_range_global(query[pass][1], q + in_base + size_t(min(r0 + 8, seq - 1)) * in_layout.ld + t * S::kRange, true);
+        }
+        stage_store<HD>(k_staged, k_tile);
+        stage_store<HD>(v_staged, v_tile);
+    }
+    __syncthreads();
+    const int tiles = (seq + 7) / 8;
+    float *out_base = out + group_offset<HD>(group, seq, out_layout);
+#pragma unroll
+    for (int pass = 0; pass < 2; ++pass) {
+        const int m0 = (warp + pass * kWarps) * 16;
+        if (m0 >= seq) {
+            break;
+        }
+        const int r0 = m0 + g, r1 = r0 + 8;
+        const float (&a0)[S::kRange] = query[pass][0];
+        const float (&a1)[S::kRange] = query[pass][1];
+        float p[8][4];
+        clear(p);
+        product_rows<HD>(p, a0, a1, k_tile, tiles, g, t);
+        float lse_a, lse_b;
+        softmax_rows(p, seq, t, scale * kLog2e, lse_a, lse_b);
+        float o[S::kOut][4];
+        clear(o);
+        product_columns<HD>(o, p, v_tile, tiles, g, t);
+        store_result<HD>(out_base, out_layout.ld, r0, r1, seq, t, o, false);
+    }
+}
+
+// Backward.  Pass 1 (query tiles): P, D, dS row-wise, dQ.  Pass 2 (key tiles):
+// P^T and dS^T from swapped operands and pass 1's row statistics, dV and dK.
+template <int HD>
+__global__ void __launch_bounds__(kThreads)
+attention_warp_backward_kernel(
+    const float *__restrict__ q, const float *__restrict__ k,
+    const float *__restrict__ v, const float *__restrict__ out,
+    const float *__restrict__ dout, float *__restrict__ dq,
+    float *__restrict__ dk, float *__restrict__ dv, int seq, float scale,
+    bool add_q, bool add_k, bool add_v, HeadLayout in_layout,
+    HeadLayout out_layout, HeadLayout dout_layout, HeadLayout grad_layout) {
+    using S = Shape<HD>;
+    __shared__ __align__(16) float q_tile[kTile * S::kPitch];
+    __shared__ __align__(16) float k_tile[kTile * S::kPitch];
+    __shared__ __align__(16) float v_tile[kTile * S::kPitch];
+    __shared__ __align__(16) float g_tile[kTile * S::kPitch];
+    __shared__ __align__(8) float row_lse[kTile];
+    __shared__ __align__(8) float row_dot[kTile];
+    const size_t group = blockIdx.x;
+    const size_t in_base = group_offset<HD>(group, seq, in_layout);
+    const float *out_base = out + group_offset<HD>(group, seq, out_layout);
+    const float *dout_base = dout + group_offset<HD>(group, seq, dout_layout);
+    const size_t grad_base = group_offset<HD>(group, seq, grad_layout);
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const int g = lane >> 2, t = lane & 3;
+    // All global loads of the block go out together: the four operand tiles,
+    // and the O and dO rows behind D_i = dO_i . O_i (in full precision) for
+    // this warp's (at most two) row tiles.
+    float row_dots[2][2];
+    {
+        Staged<HD> staged[4];
+        stage_load<HD>(staged[0], q + in_base, in_layout.ld, seq);
+        stage_load<HD>(staged[1], k + in_base, in_layout.ld, seq);
+        stage_load<HD>(staged[2], v + in_base, in_layout.ld, seq);
+        stage_load<HD>(staged[3], dout_base, dout_layout.ld, seq);
+#pragma unroll
+        for (int pass = 0; pass < 2; ++pass) {
+#pragma unroll
+            for (int half = 0; half < 2; ++half) {
+                const int row = (warp + pass * kWarps) * 16 + g + 8 * half;
+                float o[S::kRange], d[S::kRange];
+                const int safe = min(row, seq - 1);
+                load_range_global(o, out_base + size_t(safe) * out_layout.ld + t * S::kRange, false);
+                load_range_global(d, dout_base + size_t(safe) * dout_layout.ld + t * S::kRange, false);
+                float dot = 0.0f;
+#pragma unroll
+                for (int e = 0; e < S::kRange; ++e) {
+                    dot = fmaf(o[e], d[e], dot);
+                }
+                row_dots[pass][half] = quad_sum(dot);
+            }
+        }
+        stage_store<HD>(staged[0], q_tile);
+        stage_store<HD>(staged[1], k_tile);
+        stage_store<HD>(staged[2], v_tile);
+        stage_store<HD>(staged[3], g_tile);
+    }
+    // Rows past the end: P^T must vanish there (lse = +inf) and D is unused.
+    for (int i = seq + threadIdx.x; i < kTile; i += kThreads) {
+        row_lse[i] = FLT_MAX;
+        row_dot[i] = 0.0f;
+    }
+    __syncthreads();
+    const int tiles = (seq + 7) / 8;
+    const float scale2 = scale * kLog2e;
+#pragma unroll
+    for (int pass = 0; pass < 2; ++pass) {
+        const int m0 = (warp + pass * kWarps) * 16;
+        if (m0 >= seq) {
+            break;
+        }
+        const int r0 = m0 + g, r1 = r0 + 8;
+        float a0[S::kRange], a1[S::kRange];
+        load_range(a0, q_tile + r0 * S::kPitch + t * S::kRange);
+        load_range(a1, q_tile + r1 * S::kPitch + t * S::kRange);
+        float p[8][4];
+        clear(p);
+        product_rows<HD>(p, a0, a1, k_tile, tiles, g, t);
+        float lse_a, lse_b;
+        softmax_rows(p, seq, t, scale2, lse_a, lse_b);
+        const float dot_a = row_dots[pass][0], dot_b = row_dots[pass][1];
+        if (t == 0) {
+            if (r0 < seq) {
+                row_lse[r0] = lse_a;
+                row_dot[r0] = dot_a;
+            }
+            if (r1 < seq) {
+                row_lse[r1] = lse_b;
+                row_dot[r1] = dot_b;
+            }
+        }
+        // dP = dO V^T, then dS = scale P (dP - D) in place over dP.
+        load_range(a0, g_tile + r0 * S::kPitch + t * S::kRange);
+        load_range(a1, g_tile + r1 * S::kPitch + t * S::kRange);
+        float ds[8][4];
+        clear(ds);
+        product_rows<HD>(ds, a0, a1, v_tile, tiles, g, t);
+#pragma unroll
+        for (int n = 0; n < 8; ++n) {
+            ds[n][0] = scale * p[n][0] * (ds[n][0] - dot_a);
+            ds[n][1] = scale * p[n][1] * (ds[n][1] - dot_a);
+            ds[n][2] = scale * p[n][2] * (ds[n][2] - dot_b);
+            ds[n][3] = scale * p[n][3] * (ds[n][3] - dot_b);
+        }
+        float result[S::kOut][4];
+        clear(result);
+        product_columns<HD>(result, ds, k_tile, tiles, g, t);
+        store_result<HD>(dq + grad_base, grad_layout.ld, r0, r1, seq, t, result,
+                         add_q);
+    }
+    __syncthreads();
+    for (int m0 = warp * 16; m0 < seq; m0 += kWarps * 16) {
+        const int r0 = m0 + g, r1 = r0 + 8;   // key rows
+        float a0[S::kRange], a1[S::kRange];
+        load_range(a0, k_tile + r0 * S::kPitch + t * S::kRange);
+        load_range(a1, k_tile + r1 * S::kPitch + t * S::kRange);
+        float p[8][4];
+        clear(p);
+        product_rows<HD>(p, a0, a1, q_tile, tiles, g, t);   // S^T
+        // Columns are queries here: normalise with their saved statistics.
+#pragma unroll
+        for (int n = 0; n < 8; ++n) {
+            const float2 lse = *reinterpret_cast<const float2 *>(row_lse + n * 8 + 2 * t);
+            p[n][0] = exp2_fast(p[n][0] * scale2 - lse.x);
+            p[n][1] = exp2_fast(p[n][1] * scale2 - lse.y);
+            p[n][2] = exp2_fast(p[n][2] * scale2 - lse.x);
+            p[n][3] = exp2_fast(p[n][3] * scale2 - lse.y);
+        }
+        float result[S::kOut][4];
+        clear(result);
+        product_columns<HD>(result, p, g_tile, tiles, g, t);   // dV = P^T dO
+        store_result<HD>(dv + grad_base, grad_layout.ld, r0, r1, seq, t, result,
+                         add_v);
+        load_range(a0, v_tile + r0 * S::kPitch + t * S::kRange);
+        load_range(a1, v_tile + r1 * S::kPitch + t * S::kRange);
+        float ds[8][4];
+        clear(ds);
+        product_rows<HD>(ds, a0, a1, g_tile, tiles, g, t);   // dP^T = V dO^T
+#pragma unroll
+        for (int n = 0; n < 8; ++n) {
+            const float2 dot = *reinterpret_cast<const float2 *>(row_dot + n * 8 + 2 * t);
+            ds[n][0] = scale * p[n][0] * (ds[n][0] - dot.x);
+            ds[n][1] = scale * p[n][1] * (ds[n][1] - dot.y);
+            ds[n][2] = scale * p[n][2] * (ds[n][2] - dot.x);
+            ds[n][3] = scale * p[n][3] * (ds[n][3] - dot.y);
+        }
+        clear(result);
+        product_columns<HD>(result, ds, q_tile, tiles, g, t);   // dK = dS^T Q
+        store_result<HD>(dk + grad_base, grad_layout.ld, r0, r1, seq, t, result,
+                         add_k);
+    }
+}
+
+HeadLayout resolve(HeadLayout layout, size_t head_dim) {
+    return layout.ld ? layout : HeadLayout{int(head_dim), 1};
+}
+
+}  // namespace
+
+bool attention_warp_supported(size_t seq, size_t head_dim) {
+    return seq >= 1 && seq <= size_t(kTile) && (head_dim == 16 || head_dim == 32);
+}
+
+bool launch_attention_warp_forward(const float *q, const float *k,
+                                   const float *v, float *out, size_t groups,
+                                   size_t seq, size_t head_dim, float scale,
+                                   cudaStream_t stream, HeadLayout in_layout,
+                                   HeadLayout out_layout) {
+    if (!attention_warp_supported(seq, head_dim)) {
+        return false;
+    }
+    in_layout = resolve(in_layout, head_dim);
+    out_layout = resolve(out_layout, head_dim);
+    if (head_dim == 16) {
+        attention_warp_forward_kernel<16><<<unsigned(groups), kThreads, 0, stream>>>(
+            q, k, v, out, int(seq), scale, in_layout, out_layout);
+    } else {
+        attention_warp_forward_kernel<32><<<unsigned(groups), kThreads, 0, stream>>>(
+            q, k, v, out, int(seq), scale, in_layout, out_layout);
+    }
+    ++g_kernel_launches;
+    return true;
+}
+
+bool launch_attention_warp_backward(const float *q, const float *k,
+                                    const float *v, const float *out,
+                                    const float *dout, float *dq, float *dk,
+                                    float *dv, size_t groups, size_t seq,
+                                    size_t head_dim, float scale, bool add_q,
+                                    bool add_k, bool add_v, cudaStream_t stream,
+                                    HeadLayout in_layout, HeadLayout out_layout,
+                                    HeadLayout dout_layout,
+                                    HeadLayout grad_layout) {
+    if (!attention_warp_supported(seq, head_dim)) {
+        return false;
+    }
+    in_layout = resolve(in_layout, head_dim);
+    out_layout = resolve(out_layout, head_dim);
+    dout_layout = resolve(dout_layout, head_dim);
+    grad_layout = resolve(grad_layout, head_dim);
+    if (head_dim == 16) {
+        attention_warp_backward_kernel<16><<<unsigned(groups), kThreads, 0, stream>>>(
+            q, k, v, out, dout, dq, dk, dv, int(seq), scale, add_q, add_k,
+            add_v, in_layout, out_layout, dout_layout, grad_layout);
+    } else {
+        attention_warp_backward_kernel<32><<<unsigned(groups), kThreads, 0, stream>>>(
+            q, k, v, out, dout, dq, dk, dv, int(seq), scale, add_q, add_k,
+            add_v, in_layout, out_layout, dout_layout, grad_layout);
+    }
+    ++g_kernel_launches;
+    return true;
+}
+
+}  // namespace vitb200

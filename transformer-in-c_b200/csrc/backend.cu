@@ -79,6 +79,7 @@ struct PendingGemm {
 // view of it.  Input pointers are resolved when the op is recorded.
 struct PendingAttention {
     bool active = false;
+    bool tensor_cores = false;
     const float *q = nullptr, *k = nullptr, *v = nullptr;
     HeadLayout in_layout;
     const void *output_host = nullptr;
@@ -91,6 +92,7 @@ struct PendingAttention {
 // gradients into the projected gradient next (reference src/vit.c:618-626).
 struct PendingAttentionBackward {
     bool active = false;
+    bool tensor_cores = false;
     const float *q = nullptr, *k = nullptr, *v = nullptr, *out = nullptr,
                 *dout = nullptr;
     HeadLayout in_layout, out_layout, dout_layout;
@@ -340,6 +342,48 @@ float *accumulate_view(CudaBackend *backend, const void *pointer, bool *add) {
     return device;
 }
 
+void run_attention(CudaBackend *backend, const PendingAttention &pending,
+                   float *out, HeadLayout out_layout) {
+    OpScope scope(backend, "multi_head_attention", pending.bytes,
+                  pending.flops);
+    const size_t groups = pending.batch * pending.heads;
+    if (pending.tensor_cores) {
+        launch_attention_warp_forward(pending.q, pending.k, pending.v, out,
+                                      groups, pending.seq, pending.head_dim,
+                                      pending.scale, backend->stream,
+                                      pending.in_layout, out_layout);
+    } else {
+        launch_attention_small_forward(pending.q, pending.k, pending.v, nullptr,
+                                       out, groups, pending.seq,
+                                       pending.head_dim, pending.scale, false,
+                                       true, backend->stream, pending.in_layout,
+                                       out_layout);
+    }
+}
+
+void run_attention_backward(CudaBackend *backend,
+                            const PendingAttentionBackward &pending, float *dq,
+                            float *dk, float *dv, bool add_q, bool add_k,
+                            bool add_v, HeadLayout grad_layout) {
+    OpScope scope(backend, "multi_head_attention_backward", pending.bytes,
+                  pending.flops);
+    const size_t groups = pending.batch * pending.heads;
+    if (pending.tensor_cores) {
+        launch_attention_warp_backward(
+            pending.q, pending.k, pending.v, pending.out, pending.dout, dq, dk,
+            dv, groups, pending.seq, pending.head_dim, pending.scale, add_q,
+            add_k, add_v, backend->stream, pending.in_layout,
+            pending.out_layout, pending.dout_layout, grad_layout);
+    } else {
+        launch_attention_small_backward(
+            pending.q, pending.k, pending.v, nullptr, pending.out,
+            pending.dout, dq, dk, dv, groups, pending.seq, pending.head_dim,
+            pending.scale, add_q, add_k, add_v, true, backend->stream,
+            pending.in_layout, pending.out_layout, pending.dout_layout,
+            grad_layout);
+    }
+}
+
 // Held-back attention kernels, in their plain form: results go to the
 // head-major tensors the host named.
 void flush_attention(CudaBackend *backend) {
@@ -347,12 +391,7 @@ void flush_attention(CudaBackend *backend) {
         const PendingAttention pending = backend->pending_attention;
         backend->pending_attention.active = false;
         float *o = view(backend, pending.output_host, Access::Overwrite);
-        OpScope scope(backend, "multi_head_attention", pending.bytes,
-                      pending.flops);
-        launch_attention_small_forward(
-            pending.q, pending.k, pending.v, nullptr, o,
-            pending.batch * pending.heads, pending.seq, pending.head_dim,
-            pending.scale, false, true, backend->stream, pending.in_layout);
+        run_attention(backend, pending, o, HeadLayout());
     }
     if (backend->pending_attention_backward.active) {
         const PendingAttentionBackward pending =
@@ -362,14 +401,8 @@ void flush_attention(CudaBackend *backend) {
         float *dq = accumulate_view(backend, pending.dq_host, &add_q);
         float *dk = accumulate_view(backend, pending.dk_host, &add_k);
         float *dv = accumulate_view(backend, pending.dv_host, &add_v);
-        OpScope scope(backend, "multi_head_attention_backward", pending.bytes,
-                      pending.flops);
-        launch_attention_small_backward(
-            pending.q, pending.k, pending.v, nullptr, pending.out,
-            pending.dout, dq, dk, dv, pending.batch * pending.heads,
-            pending.seq, pending.head_dim, pending.scale, add_q, add_k, add_v,
-            true, backend->stream, pending.in_layout, pending.out_layout,
-            pending.dout_layout);
+        run_attention_backward(backend, pending, dq, dk, dv, add_q, add_k,
+                               add_v, HeadLayout());
     }
 }
 
@@ -678,9 +711,23 @@ constexpr size_t kMaxHeadDim = 128;
 // for it; that tensor is declared to be softmax(scale Q K^T) and is computed
 // only if somebody reads it.  On the same path the head-major copies of the
 // projections and of their gradients are not made either (see HeadView).
-bool lazy_probabilities_apply(size_t seq, size_t head_dim) {
-    return attention_small_supported(seq, head_dim) &&
-           gemm_default_precision() != VITB200_PRECISION_TF32;
+//
+// Returns 0 when the path does not apply, 1 for the FP32 kernels and 2 for the
+// tensor-core kernels (TF32 operands), chosen like a matrix product's
+// precision: forced by the policy, otherwise by the amount of work.
+int short_attention_kind(size_t groups, size_t seq, size_t head_dim) {
+    const int policy = gemm_default_precision();
+    const double work = double(groups) * double(seq) * double(seq) * double(head_dim);
+    if (policy != VITB200_PRECISION_FP32 &&
+        attention_warp_supported(seq, head_dim) &&
+        prefer_tensor_cores(policy, work)) {
+        return 2;
+    }
+    if (policy != VITB200_PRECISION_TF32 &&
+        attention_small_supported(seq, head_dim)) {
+        return 1;
+    }
+    return 0;
 }
 
 // Arguments of a pending head view: the output is columns
@@ -769,7 +816,8 @@ int op_split_heads(void *context, const vitb200_tensor *projected,
         return -1;
     }
     const float *p = view(backend, projected->data, Access::Read);
-    if (heads > 0 && lazy_probabilities_apply(seq, d_model / heads) &&
+    if (heads > 0 &&
+        short_attention_kind(batch * heads, seq, d_model / heads) != 0 &&
         define_head_view(backend, query->data, projected->data, batch, seq,
                          d_model, heads, 3 * d_model, 0) &&
         define_head_view(backend, key->data, projected->data, batch, seq,
@@ -819,16 +867,9 @@ int op_split_heads_backward(void *context, vitb200_tensor *projected,
         HeadLayout grad_layout;
         grad_layout.ld = int(3 * d_model);
         grad_layout.heads = int(heads);
-        {
-            OpScope scope(backend, "multi_head_attention_backward",
-                          pending.bytes, pending.flops);
-            launch_attention_small_backward(
-                pending.q, pending.k, pending.v, nullptr, pending.out,
-                pending.dout, p, p + d_model, p + 2 * d_model, batch * heads,
-                seq, pending.head_dim, pending.scale, false, false, false,
-                true, backend->stream, pending.in_layout, pending.out_layout,
-                pending.dout_layout, grad_layout);
-        }
+        run_attention_backward(backend, pending, p, p + d_model,
+                               p + 2 * d_model, false, false, false,
+                               grad_layout);
         const vitb200_tensor *parts[3] = {query, key, value};
         for (size_t which = 0; which < 3; ++which) {
             if (!define_head_view(backend, parts[which]->grad, projected->grad,
@@ -878,14 +919,7 @@ int op_merge_heads(void *context, const vitb200_tensor *attended,
         HeadLayout out_layout;
         out_layout.ld = int(d_model);
         out_layout.heads = int(heads);
-        {
-            OpScope scope(backend, "multi_head_attention", pending.bytes,
-                          pending.flops);
-            launch_attention_small_forward(
-                pending.q, pending.k, pending.v, nullptr, m, batch * heads, seq,
-                pending.head_dim, pending.scale, false, true, backend->stream,
-                pending.in_layout, out_layout);
-        }
+        run_attention(backend, pending, m, out_layout);
         if (!define_head_view(backend, attended->data, merged->data, batch, seq,
                               d_model, heads, d_model, 0)) {
             float *a = view(backend, attended->data, Access::Overwrite);
@@ -918,7 +952,8 @@ int op_merge_heads_backward(void *context, vitb200_tensor *attended,
     // Nothing has been added to the head-major gradient yet: it simply is
     // the merged gradient regrouped, which attention_backward can read in
     // place.
-    if (heads > 0 && lazy_probabilities_apply(seq, d_model / heads) &&
+    if (heads > 0 &&
+        short_attention_kind(batch * heads, seq, d_model / heads) != 0 &&
         coherent_is_zero_pending(attended->grad) &&
         define_head_view(backend, attended->grad, merged->grad, batch, seq,
                          d_model, heads, d_model, 0)) {
@@ -990,7 +1025,8 @@ int op_attention(void *context, const vitb200_tensor *query,
     const size_t groups = batch * heads;
     const size_t head_dim = query->cols;
     const double flops = 4.0 * double(numel(probabilities)) * double(head_dim);
-    if (lazy_probabilities_apply(seq, head_dim)) {
+    const int kind = short_attention_kind(groups, seq, head_dim);
+    if (kind != 0) {
         HeadOperand q, k, v;
         const bool through =
             through_head_view(query->data, batch, heads, seq, head_dim, &q) &&
@@ -1024,6 +1060,7 @@ int op_attention(void *context, const vitb200_tensor *query,
         if (defined) {
             PendingAttention &pending = backend->pending_attention;
             pending.active = true;
+            pending.tensor_cores = kind == 2;
             pending.q = q.pointer;
             pending.k = k.pointer;
             pending.v = v.pointer;
@@ -1098,7 +1135,8 @@ int op_attention_backward(void *context, const vitb200_tensor *query,
     const size_t groups = batch * heads;
     const size_t head_dim = query->cols;
     const bool pending_p = coherent_is_lazy(probabilities->data);
-    const bool recompute = pending_p && lazy_probabilities_apply(seq, head_dim);
+    const int kind = short_attention_kind(groups, seq, head_dim);
+    const bool recompute = pending_p && kind != 0;
     const double bytes = 4.0 * (11.0 * double(numel(query)) +
                                 (recompute ? 0.0 : double(numel(probabilities))));
     const double flops = 8.0 * double(numel(probabilities)) * double(head_dim);
@@ -1123,6 +1161,7 @@ int op_attention_backward(void *context, const vitb200_tensor *query,
                                             seq, head_dim, true);
         PendingAttentionBackward &pending = backend->pending_attention_backward;
         pending.active = true;
+        pending.tensor_cores = kind == 2;
         pending.q = q.pointer;
         pending.k = k.pointer;
         pending.v = v.pointer;
@@ -1953,6 +1992,24 @@ extern "C" int vitb200_k_attention(const float *q, const float *k,
     if (head_dim > kMaxHeadDim || !fits_int(seq) || !fits_int(groups)) {
         return -1;
     }
+    if (!probabilities) {
+        // P is not wanted: the whole-group kernels that keep it on chip.
+        const double work = double(groups) * seq * seq * head_dim;
+        if (precision != VITB200_PRECISION_FP32 &&
+            attention_warp_supported(seq, head_dim) &&
+            prefer_tensor_cores(precision, work)) {
+            return launch_attention_warp_forward(q, k, v, out, groups, seq,
+                                                 head_dim, scale,
+                                                 as_stream(stream)) ? 0 : -1;
+        }
+        if (precision != VITB200_PRECISION_TF32 &&
+            attention_small_supported(seq, head_dim)) {
+            return launch_attention_small_forward(q, k, v, nullptr, out, groups,
+                                                  seq, head_dim, scale, false,
+                                                  true, as_stream(stream)) ? 0 : -1;
+        }
+        return -1;
+    }
     if (precision == VITB200_PRECISION_TF32 &&
         !attention_mma_supported(head_dim)) {
         return -1;
@@ -1968,6 +2025,24 @@ extern "C" int vitb200_k_attention_backward(
     float *row_dots, size_t groups, size_t seq, size_t head_dim, float scale,
     int precision, void *stream) {
     if (head_dim > kMaxHeadDim || !fits_int(seq) || !fits_int(groups)) {
+        return -1;
+    }
+    if (!probabilities) {
+        const double work = double(groups) * seq * seq * head_dim;
+        if (precision != VITB200_PRECISION_FP32 &&
+            attention_warp_supported(seq, head_dim) &&
+            prefer_tensor_cores(precision, work)) {
+            return launch_attention_warp_backward(
+                       q, k, v, out, dout, dq, dk, dv, groups, seq, head_dim,
+                       scale, true, true, true, as_stream(stream)) ? 0 : -1;
+        }
+        if (precision != VITB200_PRECISION_TF32 &&
+            attention_small_supported(seq, head_dim)) {
+            return launch_attention_small_backward(
+                       q, k, v, nullptr, out, dout, dq, dk, dv, groups, seq,
+                       head_dim, scale, true, true, true, true,
+                       as_stream(stream)) ? 0 : -1;
+        }
         return -1;
     }
     launch_attention_backward(q, k, v, probabilities, out, dout, dq, dk, dv,

@@ -144,6 +144,25 @@ bool launch_attention_small_forward(const float *q, const float *k,
                                     bool write_o, cudaStream_t stream,
                                     HeadLayout in_layout = HeadLayout(),
                                     HeadLayout out_layout = HeadLayout());
+// Tensor-core kernels for seq <= 64 and head_dim 16 or 32 (TF32 operands); P
+// is neither written nor read.
+bool attention_warp_supported(size_t seq, size_t head_dim);
+bool launch_attention_warp_forward(const float *q, const float *k,
+                                   const float *v, float *out, size_t groups,
+                                   size_t seq, size_t head_dim, float scale,
+                                   cudaStream_t stream,
+                                   HeadLayout in_layout = HeadLayout(),
+                                   HeadLayout out_layout = HeadLayout());
+bool launch_attention_warp_backward(const float *q, const float *k,
+                                    const float *v, const float *out,
+                                    const float *dout, float *dq, float *dk,
+                                    float *dv, size_t groups, size_t seq,
+                                    size_t head_dim, float scale, bool add_q,
+                                    bool add_k, bool add_v, cudaStream_t stream,
+                                    HeadLayout in_layout = HeadLayout(),
+                                    HeadLayout out_layout = HeadLayout(),
+                                    HeadLayout dout_layout = HeadLayout(),
+                                    HeadLayout grad_layout = HeadLayout());
 // recompute = true: `probabilities` is not read; P is rebuilt from Q and K.
 bool launch_attention_small_backward(const float *q, const float *k,
                                      const float *v, const float *probabilities,
