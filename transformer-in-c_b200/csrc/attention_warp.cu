@@ -161,16 +161,15 @@ __device__ __forceinline__ size_t group_offset(size_t group, int seq,
 
 // c[16 x 64] += A B^T: A = rows (a0, a1) given as lane ranges, B = a staged
 // tile whose rows are the result's columns.
-template <int HD>
+template <int HD, int TILES>
 __device__ __forceinline__ void product_rows(float (&c)[8][4],
                                              const float (&a0)[HD / 4],
                                              const float (&a1)[HD / 4],
-                                             const float *tile, int tiles,
-                                             int g, int t) {
+                                             const float *tile, int g, int t) {
     using S = Shape<HD>;
 #pragma unroll
-    for (int n = 0; n < 8; ++n) {
-        if (n < tiles) {
+    for (int n = 0; n < TILES; ++n) {
+        {
             float b[S::kRange];
             load_range(b, tile + (n * 8 + g) * S::kPitch + t * S::kRange);
 #pragma unroll
@@ -186,15 +185,15 @@ __device__ __forceinline__ void product_rows(float (&c)[8][4],
 // (columns 2t, 2t+1 of tile s), B = a staged tile whose rows are the
 // contraction index.  Result element e of the lane's row range is
 // o[e % kOut][e / kOut] (row g) and o[e % kOut][2 + e / kOut] (row g + 8).
-template <int HD>
+template <int HD, int TILES>
 __device__ __forceinline__ void product_columns(float (&o)[HD / 8][4],
                                                 const float (&p)[8][4],
-                                                const float *tile, int tiles,
-                                                int g, int t) {
+                                                const float *tile, int g,
+                                                int t) {
     using S = Shape<HD>;
 #pragma unroll
-    for (int s = 0; s < 8; ++s) {
-        if (s < tiles) {
+    for (int s = 0; s < TILES; ++s) {
+        {
             float b0[S::kOut < 4 ? 4 : S::kOut], b1[S::kOut < 4 ? 4 : S::kOut];
             const float *row = tile + (s * 8 + 2 * t) * S::kPitch + g * S::kOut;
             if (S::kOut == 2) {
@@ -257,12 +256,13 @@ __device__ __forceinline__ void clear(float (&c)[N][4]) {
 // Row-wise softmax of a 16 x 64 accumulator tile set holding raw scores:
 // p = exp2(scale2 * s - lse2) with columns >= seq masked out.  Returns the two
 // rows' log-sum-exp (base 2, scaled scores).
+template <int TILES>
 __device__ __forceinline__ void softmax_rows(float (&s)[8][4], int seq, int t,
                                              float scale2, float &lse_a,
                                              float &lse_b) {
     float max_a = -FLT_MAX, max_b = -FLT_MAX;
 #pragma unroll
-    for (int n = 0; n < 8; ++n) {
+    for (int n = 0; n < TILES; ++n) {
 #pragma unroll
         for (int e = 0; e < 4; ++e) {
             const int column = n * 8 + 2 * t + (e & 1);
@@ -275,7 +275,7 @@ __device__ __forceinline__ void softmax_rows(float (&s)[8][4], int seq, int t,
     max_b = quad_max(max_b);
     float sum_a = 0.0f, sum_b = 0.0f;
 #pragma unroll
-    for (int n = 0; n < 8; ++n) {
+    for (int n = 0; n < TILES; ++n) {
         s[n][0] = exp2_fast(s[n][0] - max_a);
         s[n][1] = exp2_fast(s[n][1] - max_a);
         s[n][2] = exp2_fast(s[n][2] - max_b);
@@ -287,7 +287,7 @@ __device__ __forceinline__ void softmax_rows(float (&s)[8][4], int seq, int t,
     sum_b = quad_sum(sum_b);
     const float inverse_a = 1.0f / sum_a, inverse_b = 1.0f / sum_b;
 #pragma unroll
-    for (int n = 0; n < 8; ++n) {
+    for (int n = 0; n < TILES; ++n) {
         s[n][0] *= inverse_a;
         s[n][1] *= inverse_a;
         s[n][2] *= inverse_b;
@@ -297,7 +297,7 @@ __device__ __forceinline__ void softmax_rows(float (&s)[8][4], int seq, int t,
     lse_b = max_b + log2f(sum_b);
 }
 
-template <int HD>
+template <int HD, int TILES>
 __global__ void __launch_bounds__(kThreads)
 attention_warp_forward_kernel(const float *__restrict__ q,
                               const float *__restrict__ k,
@@ -329,7 +329,6 @@ attention_warp_forward_kernel(const float *__restrict__ q,
         stage_store<HD>(v_staged, v_tile);
     }
     __syncthreads();
-    const int tiles = (seq + 7) / 8;
     float *out_base = out + group_offset<HD>(group, seq, out_layout);
 #pragma unroll
     for (int pass = 0; pass < 2; ++pass) {
@@ -342,19 +341,19 @@ attention_warp_forward_kernel(const float *__restrict__ q,
         const float (&a1)[S::kRange] = query[pass][1];
         float p[8][4];
         clear(p);
-        product_rows<HD>(p, a0, a1, k_tile, tiles, g, t);
+        product_rows<HD, TILES>(p, a0, a1, k_tile, g, t);
         float lse_a, lse_b;
-        softmax_rows(p, seq, t, scale * kLog2e, lse_a, lse_b);
+        softmax_rows<TILES>(p, seq, t, scale * kLog2e, lse_a, lse_b);
         float o[S::kOut][4];
         clear(o);
-        product_columns<HD>(o, p, v_tile, tiles, g, t);
+        product_columns<HD, TILES>(o, p, v_tile, g, t);
         store_result<HD>(out_base, out_layout.ld, r0, r1, seq, t, o, false);
     }
 }
 
 // Backward.  Pass 1 (query tiles): P, D, dS row-wise, dQ.  Pass 2 (key tiles):
 // P^T and dS^T from swapped operands and pass 1's row statistics, dV and dK.
-template <int HD>
+template <int HD, int TILES>
 __global__ void __launch_bounds__(kThreads)
 attention_warp_backward_kernel(
     const float *__restrict__ q, const float *__restrict__ k,
@@ -415,7 +414,6 @@ attention_warp_backward_kernel(
         row_dot[i] = 0.0f;
     }
     __syncthreads();
-    const int tiles = (seq + 7) / 8;
     const float scale2 = scale * kLog2e;
 #pragma unroll
     for (int pass = 0; pass < 2; ++pass) {
@@ -429,9 +427,9 @@ attention_warp_backward_kernel(
         load_range(a1, q_tile + r1 * S::kPitch + t * S::kRange);
         float p[8][4];
         clear(p);
-        product_rows<HD>(p, a0, a1, k_tile, tiles, g, t);
+        product_rows<HD, TILES>(p, a0, a1, k_tile, g, t);
         float lse_a, lse_b;
-        softmax_rows(p, seq, t, scale2, lse_a, lse_b);
+        softmax_rows<TILES>(p, seq, t, scale2, lse_a, lse_b);
         const float dot_a = row_dots[pass][0], dot_b = row_dots[pass][1];
         if (t == 0) {
             if (r0 < seq) {
@@ -448,9 +446,9 @@ attention_warp_backward_kernel(
         load_range(a1, g_tile + r1 * S::kPitch + t * S::kRange);
         float ds[8][4];
         clear(ds);
-        product_rows<HD>(ds, a0, a1, v_tile, tiles, g, t);
+        product_rows<HD, TILES>(ds, a0, a1, v_tile, g, t);
 #pragma unroll
-        for (int n = 0; n < 8; ++n) {
+        for (int n = 0; n < TILES; ++n) {
             ds[n][0] = scale * p[n][0] * (ds[n][0] - dot_a);
             ds[n][1] = scale * p[n][1] * (ds[n][1] - dot_a);
             ds[n][2] = scale * p[n][2] * (ds[n][2] - dot_b);
@@ -458,7 +456,7 @@ attention_warp_backward_kernel(
         }
         float result[S::kOut][4];
         clear(result);
-        product_columns<HD>(result, ds, k_tile, tiles, g, t);
+        product_columns<HD, TILES>(result, ds, k_tile, g, t);
         store_result<HD>(dq + grad_base, grad_layout.ld, r0, r1, seq, t, result,
                          add_q);
     }
@@ -470,10 +468,10 @@ attention_warp_backward_kernel(
         load_range(a1, k_tile + r1 * S::kPitch + t * S::kRange);
         float p[8][4];
         clear(p);
-        product_rows<HD>(p, a0, a1, q_tile, tiles, g, t);   // S^T
+        product_rows<HD, TILES>(p, a0, a1, q_tile, g, t);   // S^T
         // Columns are queries here: normalise with their saved statistics.
 #pragma unroll
-        for (int n = 0; n < 8; ++n) {
+        for (int n = 0; n < TILES; ++n) {
             const float2 lse = *reinterpret_cast<const float2 *>(row_lse + n * 8 + 2 * t);
             p[n][0] = exp2_fast(p[n][0] * scale2 - lse.x);
             p[n][1] = exp2_fast(p[n][1] * scale2 - lse.y);
@@ -482,16 +480,16 @@ attention_warp_backward_kernel(
         }
         float result[S::kOut][4];
         clear(result);
-        product_columns<HD>(result, p, g_tile, tiles, g, t);   // dV = P^T dO
+        product_columns<HD, TILES>(result, p, g_tile, g, t);   // dV = P^T dO
         store_result<HD>(dv + grad_base, grad_layout.ld, r0, r1, seq, t, result,
                          add_v);
         load_range(a0, v_tile + r0 * S::kPitch + t * S::kRange);
         load_range(a1, v_tile + r1 * S::kPitch + t * S::kRange);
         float ds[8][4];
         clear(ds);
-        product_rows<HD>(ds, a0, a1, g_tile, tiles, g, t);   // dP^T = V dO^T
+        product_rows<HD, TILES>(ds, a0, a1, g_tile, g, t);   // dP^T = V dO^T
 #pragma unroll
-        for (int n = 0; n < 8; ++n) {
+        for (int n = 0; n < TILES; ++n) {
             const float2 dot = *reinterpret_cast<const float2 *>(row_dot + n * 8 + 2 * t);
             ds[n][0] = scale * p[n][0] * (ds[n][0] - dot.x);
             ds[n][1] = scale * p[n][1] * (ds[n][1] - dot.y);
@@ -499,7 +497,7 @@ attention_warp_backward_kernel(
             ds[n][3] = scale * p[n][3] * (ds[n][3] - dot.y);
         }
         clear(result);
-        product_columns<HD>(result, ds, q_tile, tiles, g, t);   // dK = dS^T Q
+        product_columns<HD, TILES>(result, ds, q_tile, g, t);   // dK = dS^T Q
         store_result<HD>(dk + grad_base, grad_layout.ld, r0, r1, seq, t, result,
                          add_k);
     }
@@ -510,6 +508,23 @@ HeadLayout resolve(HeadLayout layout, size_t head_dim) {
 }
 
 }  // namespace
+
+// The number of 8-key tiles is a compile-time constant so that the fragment
+// loads of a product can all be scheduled ahead of its mma instructions: the
+// smallest of 4, 7 (covers the 50-token models) and 8 that holds the sequence.
+#define VITB200_WARP_DISPATCH(head_dim, seq, CALL)                             \
+    do {                                                                       \
+        const int tiles_ = int((seq + 7) / 8);                                 \
+        if (head_dim == 16) {                                                  \
+            if (tiles_ <= 4) { CALL(16, 4); }                                  \
+            else if (tiles_ <= 7) { CALL(16, 7); }                             \
+            else { CALL(16, 8); }                                              \
+        } else {                                                               \
+            if (tiles_ <= 4) { CALL(32, 4); }                                  \
+            else if (tiles_ <= 7) { CALL(32, 7); }                             \
+            else { CALL(32, 8); }                                              \
+        }                                                                      \
+    } while (0)
 
 bool attention_warp_supported(size_t seq, size_t head_dim) {
     return seq >= 1 && seq <= size_t(kTile) && (head_dim == 16 || head_dim == 32);
@@ -525,13 +540,12 @@ bool launch_attention_warp_forward(const float *q, const float *k,
     }
     in_layout = resolve(in_layout, head_dim);
     out_layout = resolve(out_layout, head_dim);
-    if (head_dim == 16) {
-        attention_warp_forward_kernel<16><<<unsigned(groups), kThreads, 0, stream>>>(
-            q, k, v, out, int(seq), scale, in_layout, out_layout);
-    } else {
-        attention_warp_forward_kernel<32><<<unsigned(groups), kThreads, 0, stream>>>(
-            q, k, v, out, int(seq), scale, in_layout, out_layout);
-    }
+#define FORWARD(HD, TILES)                                                     \
+    attention_warp_forward_kernel<HD, TILES>                                   \
+        <<<unsigned(groups), kThreads, 0, stream>>>(                           \
+            q, k, v, out, int(seq), scale, in_layout, out_layout)
+    VITB200_WARP_DISPATCH(head_dim, seq, FORWARD);
+#undef FORWARD
     ++g_kernel_launches;
     return true;
 }
@@ -552,15 +566,13 @@ bool launch_attention_warp_backward(const float *q, const float *k,
     out_layout = resolve(out_layout, head_dim);
     dout_layout = resolve(dout_layout, head_dim);
     grad_layout = resolve(grad_layout, head_dim);
-    if (head_dim == 16) {
-        attention_warp_backward_kernel<16><<<unsigned(groups), kThreads, 0, stream>>>(
-            q, k, v, out, dout, dq, dk, dv, int(seq), scale, add_q, add_k,
-            add_v, in_layout, out_layout, dout_layout, grad_layout);
-    } else {
-        attention_warp_backward_kernel<32><<<unsigned(groups), kThreads, 0, stream>>>(
-            q, k, v, out, dout, dq, dk, dv, int(seq), scale, add_q, add_k,
-            add_v, in_layout, out_layout, dout_layout, grad_layout);
-    }
+#define BACKWARD(HD, TILES)                                                    \
+    attention_warp_backward_kernel<HD, TILES>                                  \
+        <<<unsigned(groups), kThreads, 0, stream>>>(                           \
+            q, k, v, out, dout, dq, dk, dv, int(seq), scale, add_q, add_k,     \
+            add_v, in_layout, out_layout, dout_layout, grad_layout)
+    VITB200_WARP_DISPATCH(head_dim, seq, BACKWARD);
+#undef BACKWARD
     ++g_kernel_launches;
     return true;
 }

@@ -406,6 +406,15 @@ void flush_attention(CudaBackend *backend) {
     }
 }
 
+// destination += source where destination is a pending zero fill: make it an
+// alias of the source.  False when that is not the situation (or the source
+// cannot be aliased), in which case nothing has changed.
+bool alias_if_zero(CudaBackend *backend, const void *destination,
+                   const void *source) {
+    return coherent_is_zero_pending(destination) &&
+           coherent_define_alias(destination, source, backend->stream);
+}
+
 // ---------------------------------------------------------------- op slots
 
 int op_gemm(void *context, const vitb200_tensor *left,
@@ -520,6 +529,22 @@ int op_residual_backward(void *context, vitb200_tensor *left,
     }
     bool add_a = true, add_b = true;
     const float *g = view(backend, output->grad, Access::Read);
+    // A branch gradient that is still a pending zero fill simply becomes the
+    // output gradient: declare it an alias instead of copying.
+    const bool alias_a = alias_if_zero(backend, left->grad, output->grad);
+    const bool alias_b = alias_if_zero(backend, right->grad, output->grad);
+    if (alias_a && alias_b) {
+        return 0;
+    }
+    if (alias_a || alias_b) {
+        bool add = true;
+        float *rest = accumulate_view(backend, alias_a ? right->grad : left->grad,
+                                      &add);
+        OpScope scope(backend, "residual_backward", 12.0 * double(numel(output)),
+                      0.0);
+        launch_accumulate(rest, g, numel(output), add, backend->stream);
+        return 0;
+    }
     float *a = accumulate_view(backend, left->grad, &add_a);
     float *b = accumulate_view(backend, right->grad, &add_b);
     {
@@ -541,6 +566,9 @@ int op_accumulate_gradient(void *context, vitb200_tensor *destination,
     }
     bool add = true;
     const float *src = view(backend, source->grad, Access::Read);
+    if (alias_if_zero(backend, destination->grad, source->grad)) {
+        return 0;
+    }
     float *dst = accumulate_view(backend, destination->grad, &add);
     {
         OpScope scope(backend, "accumulate_gradient", 12.0 * double(numel(destination)),
@@ -638,15 +666,18 @@ int op_layer_norm_backward(void *context, const vitb200_tensor *input,
     const float *x = view(backend, input->data, Access::Read);
     const float *g = view(backend, gamma->data, Access::Read);
     const float *dy = view(backend, output->grad, Access::Read);
-    bool add_dx = true;
-    float *dx = accumulate_view(backend, input_grad->grad, &add_dx);
+    // dx = base + increment: base is dx itself, the source that dx is still
+    // an alias of, or absent when dx is a pending zero fill.
+    const float *base = nullptr;
+    float *dx = device_view_accumulate_based(input_grad->grad, backend->stream,
+                                             &base);
     float *dg = view(backend, gamma_grad->grad, Access::ReadWrite);
     float *db = view(backend, beta_grad->grad, Access::ReadWrite);
     {
         OpScope scope(backend, "layer_norm_backward", 16.0 * double(numel(input)),
                       0.0);
         launch_layer_norm_backward(x, g, epsilon, dy, dx, dg, db, input->rows,
-                                   input->cols, add_dx, backend->stream);
+                                   input->cols, base, backend->stream);
     }
     dp_gradient_produced(backend->dp, gamma_grad->grad, dg, numel(gamma_grad));
     dp_gradient_produced(backend->dp, beta_grad->grad, db, numel(beta_grad));
@@ -1968,7 +1999,7 @@ extern "C" int vitb200_k_layer_norm_backward(const float *x, const float *gamma,
                                              float *dbeta, size_t rows,
                                              size_t cols, void *stream) {
     launch_layer_norm_backward(x, gamma, epsilon, dy, dx, dgamma, dbeta, rows,
-                               cols, true, as_stream(stream));
+                               cols, dx, as_stream(stream));
     return 0;
 }
 

@@ -230,6 +230,20 @@ void detach_source(Region &region) {
     region.device = nullptr;
 }
 
+// Definition of an alias: the output is a plain copy of its source.
+void materialise_copy(const void *arguments, float *output,
+                      float *const *sources, cudaStream_t stream) {
+    size_t bytes = 0;
+    memcpy(&bytes, arguments, sizeof(bytes));
+    check(cudaMemcpyAsync(output, sources[0], bytes, cudaMemcpyDeviceToDevice,
+                          stream),
+          "cudaMemcpyAsync(device to device)");
+}
+
+bool is_alias(const Region &region) {
+    return region.lazy && region.lazy->function == materialise_copy;
+}
+
 void materialise_zero(Region &region, cudaStream_t stream) {
     if (region.zero_pending) {
         check(cudaMemsetAsync(region.device, 0, region.bytes, stream),
@@ -392,6 +406,11 @@ float *device_view(const void *host_pointer, Access access,
         return nullptr;
     }
     if (region->lazy) {
+        if (access == Access::Read && is_alias(*region)) {
+            // A reader of an alias is served from the source's buffer.
+            g_stats.alias_reads += 1;
+            return const_cast<float *>(source_device(region->lazy, 0));
+        }
         if (access == Access::Overwrite) {
             drop_lazy(region->lazy);
         } else {
@@ -527,6 +546,42 @@ bool coherent_define_lazy(const void *output_host,
     }
     g_stats.lazy_defined += 1;
     return true;
+}
+
+bool coherent_define_alias(const void *output_host, const void *source_host,
+                           cudaStream_t stream) {
+    Region *output = output_host ? find_base(output_host) : nullptr;
+    Region *source = source_host ? find_base(source_host) : nullptr;
+    if (!output || !source || output->bytes != source->bytes) {
+        return false;
+    }
+    const size_t bytes = source->bytes;
+    const void *sources[1] = {source_host};
+    return coherent_define_lazy(output_host, sources, 1, materialise_copy,
+                                &bytes, sizeof(bytes), stream);
+}
+
+float *device_view_accumulate_based(const void *host_pointer,
+                                    cudaStream_t stream, const float **base) {
+    Region *region = host_pointer ? find_base(host_pointer) : nullptr;
+    *base = nullptr;
+    if (!region) {
+        return nullptr;
+    }
+    if (is_alias(*region)) {
+        // The sum replaces the alias: read the source, write our own buffer.
+        // (If the source buffer is recycled into this very region the two
+        // pointers coincide and the update is in place, element by element.)
+        const float *source = source_device(region->lazy, 0);
+        drop_lazy(region->lazy);
+        float *own = device_view(host_pointer, Access::Overwrite, stream);
+        *base = source;
+        return own;
+    }
+    bool was_zero = false;
+    float *own = device_view_accumulate(host_pointer, stream, &was_zero);
+    *base = was_zero ? nullptr : own;
+    return own;
 }
 
 bool coherent_is_lazy(const void *host_pointer) {

@@ -39,6 +39,7 @@ struct CoherenceStats {
     size_t lazy_defined;
     size_t lazy_materialised;
     size_t lazy_dropped;
+    size_t alias_reads;
 };
 
 // Allocator pair installed through tensor_set_allocator
@@ -84,6 +85,17 @@ bool coherent_define_lazy(const void *output_host,
                           LazyMaterialise function, const void *arguments,
                           size_t argument_bytes, cudaStream_t stream);
 bool coherent_is_lazy(const void *host_pointer);
+// Declares `output` to be a copy of `source` (same size) without copying.
+// Readers (Access::Read) of the output are handed the source's buffer; the
+// copy is made only if the output is modified in place or read by the host.
+bool coherent_define_alias(const void *output_host, const void *source_host,
+                           cudaStream_t stream);
+// For an update output = output + increment written as a three-operand
+// kernel: returns the buffer to write and sets *base to the buffer holding the
+// current contents (the same pointer, an alias's source, or nullptr when the
+// contents are a pending zero fill).  Every element must be written.
+float *device_view_accumulate_based(const void *host_pointer,
+                                    cudaStream_t stream, const float **base);
 // For an output pending under `function` with one source: copies the
 // definition's arguments out and returns the device pointer that currently
 // holds the source's values, so that a consumer can read through the

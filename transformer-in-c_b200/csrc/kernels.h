@@ -81,7 +81,8 @@ void launch_layer_norm(const float *x, const float *gamma, const float *beta,
 void launch_layer_norm_backward(const float *x, const float *gamma,
                                 float epsilon, const float *dy, float *dx,
                                 float *dgamma, float *dbeta, size_t rows,
-                                size_t cols, bool add_dx, cudaStream_t stream);
+                                size_t cols, const float *base,
+                                cudaStream_t stream);
 
 // ---- attention (attention.cu) --------------------------------------------
 // q, k, v, out: [groups * seq, head_dim]; probabilities: [groups * seq, seq].

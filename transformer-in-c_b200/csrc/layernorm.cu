@@ -95,9 +95,9 @@ template <int NV>
 __global__ void __launch_bounds__(kWarpsPerBlock * 32)
 layer_norm_backward_kernel(const float *__restrict__ x,
                            const float *__restrict__ gamma, float epsilon,
-                           const float *__restrict__ dy, float *__restrict__ dx,
+                           const float *__restrict__ dy, float *dx,
                            float *__restrict__ dgamma, float *__restrict__ dbeta,
-                           size_t rows, size_t cols, bool add) {
+                           size_t rows, size_t cols, const float *base) {
     __shared__ float4 fold[kWarpsPerBlock][32];
     const int lane = threadIdx.x & 31;
     const int warp_in_block = threadIdx.x >> 5;
@@ -151,7 +151,9 @@ layer_norm_backward_kernel(const float *__restrict__ x,
             if (col < cols) {
                 float4 *target =
                     reinterpret_cast<float4 *>(dx + row * cols + col);
-                float4 d = add ? *target : make_float4(0.f, 0.f, 0.f, 0.f);
+                float4 d = base ? *reinterpret_cast<const float4 *>(
+                                      base + row * cols + col)
+                                : make_float4(0.f, 0.f, 0.f, 0.f);
                 d.x += inverse_std * (u[j].x - s1 - v[j].x * s2);
                 d.y += inverse_std * (u[j].y - s1 - v[j].y * s2);
                 d.z += inverse_std * (u[j].z - s1 - v[j].z * s2);
@@ -223,10 +225,10 @@ __global__ void __launch_bounds__(kWarpsPerBlock * 32)
 layer_norm_backward_generic_kernel(const float *__restrict__ x,
                                    const float *__restrict__ gamma,
                                    float epsilon, const float *__restrict__ dy,
-                                   float *__restrict__ dx,
+                                   float *dx,
                                    float *__restrict__ dgamma,
                                    float *__restrict__ dbeta, size_t rows,
-                                   size_t cols, bool add) {
+                                   size_t cols, const float *base) {
     const int lane = threadIdx.x & 31;
     const size_t warp = size_t(blockIdx.x) * kWarpsPerBlock + (threadIdx.x >> 5);
     const size_t warps = size_t(gridDim.x) * kWarpsPerBlock;
@@ -259,7 +261,7 @@ layer_norm_backward_generic_kernel(const float *__restrict__ x,
         for (size_t c = lane; c < cols; c += 32) {
             const float normalised = (values[c] - mean) * inverse_std;
             const float dxhat = upstream[c] * gamma[c];
-            dx[row * cols + c] = (add ? dx[row * cols + c] : 0.0f) +
+            dx[row * cols + c] = (base ? base[row * cols + c] : 0.0f) +
                                  inverse_std * (dxhat - s1 - normalised * s2);
         }
     }
@@ -302,25 +304,25 @@ void launch_layer_norm(const float *x, const float *gamma, const float *beta,
 void launch_layer_norm_backward(const float *x, const float *gamma,
                                 float epsilon, const float *dy, float *dx,
                                 float *dgamma, float *dbeta, size_t rows,
-                                size_t cols, bool add_dx, cudaStream_t stream) {
+                                size_t cols, const float *base, cudaStream_t stream) {
     const unsigned grid = row_grid(rows, 4);
     const unsigned block = kWarpsPerBlock * 32;
     const size_t slots = (cols + 127) / 128;
     if (cols % 4 != 0 || slots > 8) {
         layer_norm_backward_generic_kernel<<<grid, block, 0, stream>>>(
-            x, gamma, epsilon, dy, dx, dgamma, dbeta, rows, cols, add_dx);
+            x, gamma, epsilon, dy, dx, dgamma, dbeta, rows, cols, base);
     } else if (slots <= 1) {
         layer_norm_backward_kernel<1><<<grid, block, 0, stream>>>(
-            x, gamma, epsilon, dy, dx, dgamma, dbeta, rows, cols, add_dx);
+            x, gamma, epsilon, dy, dx, dgamma, dbeta, rows, cols, base);
     } else if (slots <= 2) {
         layer_norm_backward_kernel<2><<<grid, block, 0, stream>>>(
-            x, gamma, epsilon, dy, dx, dgamma, dbeta, rows, cols, add_dx);
+            x, gamma, epsilon, dy, dx, dgamma, dbeta, rows, cols, base);
     } else if (slots <= 4) {
         layer_norm_backward_kernel<4><<<grid, block, 0, stream>>>(
-            x, gamma, epsilon, dy, dx, dgamma, dbeta, rows, cols, add_dx);
+            x, gamma, epsilon, dy, dx, dgamma, dbeta, rows, cols, base);
     } else {
         layer_norm_backward_kernel<8><<<grid, block, 0, stream>>>(
-            x, gamma, epsilon, dy, dx, dgamma, dbeta, rows, cols, add_dx);
+            x, gamma, epsilon, dy, dx, dgamma, dbeta, rows, cols, base);
     }
     ++g_kernel_launches;
 }
