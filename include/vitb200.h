@@ -77,6 +77,15 @@ void vitb200_elision_counters(size_t *zero_fills_elided,
                               size_t *lazy_defined, size_t *lazy_materialised,
                               size_t *lazy_dropped);
 
+/* Ops the backend merged into a neighbour since it was created: bias / GELU
+ * ops carried by a product's epilogue, head split / merge ops absorbed by the
+ * attention kernels, and bias gradients taken from column sums that the
+ * producer of the matrix had already accumulated.  Any pointer may be NULL. */
+void vitb200_fusion_counters(const CudaBackend *backend,
+                             unsigned long long *epilogues,
+                             unsigned long long *head_layouts,
+                             unsigned long long *bias_gradients);
+
 /* Makes a tensor buffer obtained through the backend allocator plainly
  * readable and writable by the host (copying it back from the device if
  * needed).  Required before passing it to read()/fread()/write()/fwrite(),

@@ -343,10 +343,17 @@ def test_unread_tensors_are_not_computed_but_reads_see_them(vit_host_module,
     backend.set_gemm_precision(FP32)
     gpu = vh.VitHost(host_lib, config, batch)
     before = backend.elision_counters()
+    fused_before = backend.fusion_counters()
     gpu.train_step(images, labels, LR, WD, None, 0.1)
     gpu.train_step(images, labels, LR, WD, None, 0.1)
     after = backend.elision_counters()
+    fused = backend.fusion_counters()
     layers = config[6]
+    # Per block and step: merge_heads and split_heads_backward ride on the
+    # attention kernels, and three of the four bias gradients come from sums
+    # their matrix's producer made (layer_norm_backward twice, gelu_backward).
+    assert fused["head_layouts"] - fused_before["head_layouts"] == 2 * 2 * layers
+    assert fused["bias_gradients"] - fused_before["bias_gradients"] == 2 * 3 * layers
     # Per block and step: P; the head-major Q, K, V and attention output
     # (views of the projected / merged matrices); and the same five gradients
     # less P's, which nobody produces.

@@ -102,6 +102,22 @@ struct PendingAttentionBackward {
     double bytes = 0.0, flops = 0.0;
 };
 
+// Column sums of a gradient matrix that its producer computed on the way,
+// kept for the bias_add_backward the host issues next on the same values
+// (possibly through aliases of them).  Valid only while no other op has
+// launched anything and nothing has been uploaded since.
+struct ColumnSumMemo {
+    bool valid = false;
+    const float *data = nullptr;
+    size_t rows = 0, cols = 0;
+    unsigned long long epoch = 0;
+    size_t uploads = 0;
+    // Where the sums are: one row of `cols` floats in the zero-kept scratch
+    // (partial_rows == 0), or that many rows of partial sums.
+    const float *partials = nullptr;
+    size_t partial_rows = 0;
+};
+
 constexpr int kStagingSlots = 8;
 constexpr size_t kStagingBytes = 64 * 1024;
 
@@ -132,6 +148,13 @@ struct CudaBackend {
     std::vector<PendingOp> pending_ops;
     std::vector<cudaEvent_t> free_events;
     DataParallel *dp = nullptr;
+    // Ops that launched work so far (see ColumnSumMemo).
+    unsigned long long epoch = 0;
+    ColumnSumMemo column_memo;
+    Scratch column_sums;       // all zero whenever !column_sums_dirty
+    Scratch column_partials;
+    bool column_sums_dirty = false;
+    unsigned long long memo_hits = 0;
     PendingGemm pending;
     PendingAttention pending_attention;
     PendingAttentionBackward pending_attention_backward;
@@ -191,6 +214,7 @@ class OpScope {
 public:
     OpScope(CudaBackend *backend, const char *name, double bytes, double flops)
         : backend_(backend), name_(name) {
+        backend->epoch += 1;
         if (!backend->span_open) {
             check(cudaEventRecord(backend->span_begin, backend->stream),
                   "cudaEventRecord");
@@ -226,6 +250,9 @@ void flush_attention(CudaBackend *backend);
 
 // Launches the held-back product, with whatever was attached to it.
 void flush_pending(CudaBackend *backend) {
+    // Every op starts here: whatever it does may change the matrix a memo
+    // describes.  The few ops that provably do not put the memo back.
+    backend->column_memo.valid = false;
     if (backend->pending_attention.active ||
         backend->pending_attention_backward.active) {
         flush_attention(backend);
@@ -406,6 +433,47 @@ void flush_attention(CudaBackend *backend) {
     }
 }
 
+// A zeroed buffer of `cols` floats for a producer to add column sums into, or
+// nullptr if the width is not worth it.
+float *column_memo_begin(CudaBackend *backend, size_t cols) {
+    backend->column_memo.valid = false;
+    if (cols == 0 || cols > 16384) {
+        return nullptr;
+    }
+    const size_t before = backend->column_sums.bytes;
+    float *sums = scratch<float>(backend, backend->column_sums, cols);
+    if (backend->column_sums.bytes != before || backend->column_sums_dirty) {
+        check(cudaMemsetAsync(backend->column_sums.memory, 0,
+                              backend->column_sums.bytes, backend->stream),
+              "cudaMemsetAsync");
+    }
+    backend->column_sums_dirty = true;
+    return sums;
+}
+
+// Call after the producer's OpScope has closed.
+void column_memo_commit(CudaBackend *backend, const float *data, size_t rows,
+                        size_t cols, const float *partials = nullptr,
+                        size_t partial_rows = 0) {
+    ColumnSumMemo &memo = backend->column_memo;
+    memo.partials = partials;
+    memo.partial_rows = partial_rows;
+    memo.valid = true;
+    memo.data = data;
+    memo.rows = rows;
+    memo.cols = cols;
+    memo.epoch = backend->epoch;
+    memo.uploads = coherence_stats().host_to_device_copies;
+}
+
+bool column_memo_matches(CudaBackend *backend, const float *data, size_t rows,
+                         size_t cols) {
+    const ColumnSumMemo &memo = backend->column_memo;
+    return memo.valid && memo.data == data && memo.rows == rows &&
+           memo.cols == cols && memo.epoch == backend->epoch &&
+           memo.uploads == coherence_stats().host_to_device_copies;
+}
+
 // destination += source where destination is a pending zero fill: make it an
 // alias of the source.  False when that is not the situation (or the source
 // cannot be aliased), in which case nothing has changed.
@@ -521,6 +589,7 @@ int op_residual(void *context, const vitb200_tensor *left,
 int op_residual_backward(void *context, vitb200_tensor *left,
                          vitb200_tensor *right, const vitb200_tensor *output) {
     CudaBackend *backend = self(context);
+    const ColumnSumMemo memo = backend->column_memo;
     flush_pending(backend);
     // One pass updates both branches, which needs them to be distinct.
     if (!ours({left->grad, right->grad, output->grad}) ||
@@ -534,6 +603,7 @@ int op_residual_backward(void *context, vitb200_tensor *left,
     const bool alias_a = alias_if_zero(backend, left->grad, output->grad);
     const bool alias_b = alias_if_zero(backend, right->grad, output->grad);
     if (alias_a && alias_b) {
+        backend->column_memo = memo;   // nothing was written
         return 0;
     }
     if (alias_a || alias_b) {
@@ -559,6 +629,7 @@ int op_residual_backward(void *context, vitb200_tensor *left,
 int op_accumulate_gradient(void *context, vitb200_tensor *destination,
                            const vitb200_tensor *source) {
     CudaBackend *backend = self(context);
+    const ColumnSumMemo memo = backend->column_memo;
     flush_pending(backend);
     if (!ours({destination->grad, source->grad}) ||
         destination->grad == source->grad) {
@@ -567,6 +638,7 @@ int op_accumulate_gradient(void *context, vitb200_tensor *destination,
     bool add = true;
     const float *src = view(backend, source->grad, Access::Read);
     if (alias_if_zero(backend, destination->grad, source->grad)) {
+        backend->column_memo = memo;   // nothing was written
         return 0;
     }
     float *dst = accumulate_view(backend, destination->grad, &add);
@@ -612,11 +684,38 @@ int op_bias_add(void *context, const vitb200_tensor *input,
 int op_bias_add_backward(void *context, const vitb200_tensor *output,
                          vitb200_tensor *bias_grad) {
     CudaBackend *backend = self(context);
+    const ColumnSumMemo memo = backend->column_memo;
     flush_pending(backend);
+    backend->column_memo = memo;   // checked against the launch count below
     if (!ours({output->grad, bias_grad->grad})) {
         return -1;
     }
     const float *dy = view(backend, output->grad, Access::Read);
+    if (column_memo_matches(backend, dy, output->rows, output->cols)) {
+        // The kernel that produced these values summed their columns too.
+        const ColumnSumMemo used = backend->column_memo;
+        backend->column_memo.valid = false;
+        backend->memo_hits += 1;
+        float *db = nullptr;
+        if (used.partial_rows) {
+            db = view(backend, bias_grad->grad, Access::ReadWrite);
+            OpScope scope(backend, "bias_add_backward",
+                          4.0 * double(used.partial_rows * output->cols), 0.0);
+            launch_column_sums(used.partials, db, used.partial_rows,
+                               output->cols, output->cols, backend->stream);
+        } else {
+            backend->column_sums_dirty = false;
+            bool add = true;
+            db = accumulate_view(backend, bias_grad->grad, &add);
+            float *sums = static_cast<float *>(backend->column_sums.memory);
+            OpScope scope(backend, "bias_add_backward", 8.0 * double(output->cols),
+                          0.0);
+            launch_take_column_sums(db, sums, output->cols, add,
+                                    backend->stream);
+        }
+        dp_gradient_produced(backend->dp, bias_grad->grad, db, numel(bias_grad));
+        return 0;
+    }
     float *db = view(backend, bias_grad->grad, Access::ReadWrite);
     {
         OpScope scope(backend, "bias_add_backward", 4.0 * double(numel(output)),
@@ -673,11 +772,17 @@ int op_layer_norm_backward(void *context, const vitb200_tensor *input,
                                              &base);
     float *dg = view(backend, gamma_grad->grad, Access::ReadWrite);
     float *db = view(backend, beta_grad->grad, Access::ReadWrite);
+    // dx is what the two bias gradients of the preceding linear layers are
+    // the column sums of (reference src/vit.c:548-551, 567-571).
+    float *sums = column_memo_begin(backend, input->cols);
     {
         OpScope scope(backend, "layer_norm_backward", 16.0 * double(numel(input)),
                       0.0);
         launch_layer_norm_backward(x, g, epsilon, dy, dx, dg, db, input->rows,
-                                   input->cols, base, backend->stream);
+                                   input->cols, base, sums, backend->stream);
+    }
+    if (sums) {
+        column_memo_commit(backend, dx, input->rows, input->cols);
     }
     dp_gradient_produced(backend->dp, gamma_grad->grad, dg, numel(gamma_grad));
     dp_gradient_produced(backend->dp, beta_grad->grad, db, numel(beta_grad));
@@ -726,10 +831,26 @@ int op_gelu_backward(void *context, const vitb200_tensor *input,
     const float *dy = view(backend, output->grad, Access::Read);
     bool add = true;
     float *dx = accumulate_view(backend, input->grad, &add);
+    float *sums = nullptr;
+    size_t partial_rows = 0;
+    if (gelu_backward_sums_supported(input->cols)) {
+        partial_rows = gelu_backward_sums_blocks(input->rows, input->cols);
+        sums = scratch<float>(backend, backend->column_partials,
+                              partial_rows * input->cols);
+    }
     {
         OpScope scope(backend, "gelu_backward", 16.0 * double(numel(input)),
                       0.0);
-        launch_gelu_backward(x, dy, dx, numel(input), add, backend->stream);
+        if (sums) {
+            launch_gelu_backward_sums(x, dy, dx, sums, input->rows, input->cols,
+                                      add, backend->stream);
+        } else {
+            launch_gelu_backward(x, dy, dx, numel(input), add, backend->stream);
+        }
+    }
+    if (sums) {
+        column_memo_commit(backend, dx, input->rows, input->cols, sums,
+                           partial_rows);
     }
     return 0;
 }
@@ -1704,6 +1825,8 @@ extern "C" void cuda_backend_free(CudaBackend *backend) {
     free_scratch(backend->norm_partials);
     free_scratch(backend->clip_scale);
     free_scratch(backend->slice_table);
+    free_scratch(backend->column_sums);
+    free_scratch(backend->column_partials);
     for (int i = 0; i < kStagingSlots; ++i) {
         if (backend->staging[i]) {
             cudaFreeHost(backend->staging[i]);
@@ -1819,6 +1942,15 @@ extern "C" void vitb200_elision_counters(size_t *zero_fills_elided,
     if (lazy_defined) *lazy_defined = s.lazy_defined;
     if (lazy_materialised) *lazy_materialised = s.lazy_materialised;
     if (lazy_dropped) *lazy_dropped = s.lazy_dropped;
+}
+
+extern "C" void vitb200_fusion_counters(const CudaBackend *backend,
+                                        unsigned long long *epilogues,
+                                        unsigned long long *head_layouts,
+                                        unsigned long long *bias_gradients) {
+    if (epilogues) *epilogues = backend ? backend->fused_epilogues : 0;
+    if (head_layouts) *head_layouts = backend ? backend->fused_head_layouts : 0;
+    if (bias_gradients) *bias_gradients = backend ? backend->memo_hits : 0;
 }
 
 extern "C" int vitb200_make_host_coherent(const void *tensor_memory) {
@@ -1999,7 +2131,7 @@ extern "C" int vitb200_k_layer_norm_backward(const float *x, const float *gamma,
                                              float *dbeta, size_t rows,
                                              size_t cols, void *stream) {
     launch_layer_norm_backward(x, gamma, epsilon, dy, dx, dgamma, dbeta, rows,
-                               cols, dx, as_stream(stream));
+                               cols, dx, nullptr, as_stream(stream));
     return 0;
 }
 

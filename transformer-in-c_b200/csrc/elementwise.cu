@@ -132,6 +132,67 @@ __global__ void gelu_backward_kernel(const float *__restrict__ x,
     }
 }
 
+// The same with the column sums of the result accumulated on the way (they
+// are the bias gradient the host asks for next, reference src/vit.c:554-555).
+// A row is cols / 4 threads wide and that divides the block, so a thread keeps
+// its four columns for every row it visits and sums them in registers; the
+// block's threads that share columns are folded in shared memory, and the
+// block writes its sums as row blockIdx.x of `partials` ([gridDim.x, cols]);
+// atomics from a full wave of blocks onto so few addresses cost more than the
+// pass they save.
+__global__ void __launch_bounds__(kStreamThreads)
+gelu_backward_sums_kernel(const float *__restrict__ x,
+                          const float *__restrict__ dy, float *__restrict__ dx,
+                          float *__restrict__ partials, size_t rows,
+                          size_t cols, bool add) {
+    __shared__ float4 fold[kStreamThreads];
+    const unsigned row_threads = unsigned(cols / 4);
+    const unsigned rows_per_block = kStreamThreads / row_threads;
+    const unsigned column = threadIdx.x % row_threads;
+    const unsigned sub_row = threadIdx.x / row_threads;
+    float4 total = make_float4(0.f, 0.f, 0.f, 0.f);
+    for (size_t row = size_t(blockIdx.x) * rows_per_block + sub_row; row < rows;
+         row += size_t(gridDim.x) * rows_per_block) {
+        const size_t i = row * row_threads + column;
+        const float4 v = ld_stream(reinterpret_cast<const float4 *>(x) + i);
+        const float4 g = ld_stream(reinterpret_cast<const float4 *>(dy) + i);
+        float4 *target = reinterpret_cast<float4 *>(dx) + i;
+        float4 d = add ? *target : make_float4(0.f, 0.f, 0.f, 0.f);
+        d.x += g.x * gelu_slope(v.x);
+        d.y += g.y * gelu_slope(v.y);
+        d.z += g.z * gelu_slope(v.z);
+        d.w += g.w * gelu_slope(v.w);
+        *target = d;
+        total.x += d.x;
+        total.y += d.y;
+        total.z += d.z;
+        total.w += d.w;
+    }
+    fold[threadIdx.x] = total;
+    __syncthreads();
+    if (sub_row == 0) {
+        for (unsigned r = 1; r < rows_per_block; ++r) {
+            const float4 other = fold[r * row_threads + column];
+            total.x += other.x;
+            total.y += other.y;
+            total.z += other.z;
+            total.w += other.w;
+        }
+        reinterpret_cast<float4 *>(partials + size_t(blockIdx.x) * cols)[column] =
+            total;
+    }
+}
+
+// out (+)= sums, and the sums go back to zero for their next user.
+__global__ void take_column_sums_kernel(float *__restrict__ out,
+                                        float *__restrict__ sums, size_t cols,
+                                        bool add) {
+    for (size_t c = global_thread(); c < cols; c += grid_threads()) {
+        out[c] = (add ? out[c] : 0.0f) + sums[c];
+        sums[c] = 0.0f;
+    }
+}
+
 __global__ void scale_by_device_scalar_kernel(float *__restrict__ values,
                                               size_t n,
                                               const float *__restrict__ scale) {
@@ -196,6 +257,34 @@ void launch_gelu_backward(const float *x, const float *dy, float *dx, size_t n,
                           bool add, cudaStream_t stream) {
     gelu_backward_kernel<<<stream_grid(n / 4 + 1), kStreamThreads, 0, stream>>>(
         x, dy, dx, n, add);
+    ++g_kernel_launches;
+}
+
+bool gelu_backward_sums_supported(size_t cols) {
+    return cols >= 4 && cols % 4 == 0 && cols / 4 <= kStreamThreads &&
+           kStreamThreads % (cols / 4) == 0;
+}
+
+size_t gelu_backward_sums_blocks(size_t rows, size_t cols) {
+    const size_t rows_per_block = kStreamThreads / (cols / 4);
+    const size_t wanted = (rows + rows_per_block - 1) / rows_per_block;
+    const size_t limit = size_t(kSmCount) * kStreamBlocksPerSm;   // one wave
+    return wanted < limit ? wanted : limit;
+}
+
+void launch_gelu_backward_sums(const float *x, const float *dy, float *dx,
+                               float *partials, size_t rows, size_t cols,
+                               bool add, cudaStream_t stream) {
+    gelu_backward_sums_kernel<<<unsigned(gelu_backward_sums_blocks(rows, cols)),
+                                kStreamThreads, 0, stream>>>(
+        x, dy, dx, partials, rows, cols, add);
+    ++g_kernel_launches;
+}
+
+void launch_take_column_sums(float *out, float *sums, size_t cols, bool add,
+                             cudaStream_t stream) {
+    take_column_sums_kernel<<<stream_grid(cols), kStreamThreads, 0, stream>>>(
+        out, sums, cols, add);
     ++g_kernel_launches;
 }
 

@@ -10,12 +10,14 @@
 // transposed copy.  Nothing is converted or re-laid-out in global memory: TMA
 // rounds FP32 to TF32 while it fills the shared-memory stages.
 //
-// Persistent CTAs (one per SM) walk work items = (128 x 128 output tile,
-// slice of the reduction); three warp roles meet only through mbarriers:
+// Persistent CTAs (two per SM by default: with the short reductions of this
+// model, K = 128..512, two shallow pipelines hide the tile-to-tile bubbles
+// better than one deep one) walk work items = (128 x 128 output tile, slice
+// of the reduction); three warp roles meet only through mbarriers:
 //
 //   warp 0      TMA producer: per 32-deep reduction block, one 128B-swizzled
 //               box (K-major) or four 32x32 boxes (MN-major) per operand into
-//               a 5- or 6-stage shared-memory ring
+//               a shared-memory ring of 32 KB stages (2 stages by default)
 //   warp 1      allocates 256 TMEM columns (two accumulators), issues four
 //               K=8 tcgen05.mma per block from one lane, releases stages with
 //               tcgen05.commit, and signals a finished accumulator
@@ -49,8 +51,8 @@ constexpr int kBlockK = 32;                 // 128 bytes of FP32 per row
 constexpr int kMmaK = 8;                    // tf32 K per instruction
 constexpr int kOperandBytes = kTileM * kBlockK * 4;   // 16 KiB
 constexpr int kStageBytes = 2 * kOperandBytes;
-// The load ring takes whatever shared memory the epilogue staging leaves:
-// 6 stages next to one staged output (2 buffers), 5 next to two.
+// Upper bound on the load ring; the launch code picks the depth that fits
+// beside the epilogue staging for the chosen number of CTAs per SM.
 constexpr int kMaxStages = 6;
 constexpr int kSmemLimit = 227 * 1024 - 1024;   // leave room for static shared memory
 constexpr int kThreads = 192;

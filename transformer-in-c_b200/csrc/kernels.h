@@ -26,7 +26,19 @@ void launch_bias_add(const float *in, const float *bias, float *out,
                      size_t rows, size_t cols, cudaStream_t stream);
 void launch_gelu(const float *in, float *out, size_t n, cudaStream_t stream);
 void launch_gelu_backward(const float *x, const float *dy, float *dx, size_t n,
-                          bool add, cudaStream_t stream);   // dx (+)= dy*gelu'(x)
+                          bool add, cudaStream_t stream);
+// gelu_backward that also leaves partial column sums of dx ([rows, cols]) in
+// `partials`, one row of `cols` floats per block
+// (gelu_backward_sums_blocks(rows, cols) of them; their column sums are
+// dx's); only for widths gelu_backward_sums_supported accepts.
+bool gelu_backward_sums_supported(size_t cols);
+size_t gelu_backward_sums_blocks(size_t rows, size_t cols);
+void launch_gelu_backward_sums(const float *x, const float *dy, float *dx,
+                               float *partials, size_t rows, size_t cols,
+                               bool add, cudaStream_t stream);
+// out (+)= sums; sums = 0.
+void launch_take_column_sums(float *out, float *sums, size_t cols, bool add,
+                             cudaStream_t stream);   // dx (+)= dy*gelu'(x)
 void launch_scale_by_device_scalar(float *values, size_t n, const float *scale,
                                    cudaStream_t stream);
 
@@ -81,7 +93,7 @@ void launch_layer_norm(const float *x, const float *gamma, const float *beta,
 void launch_layer_norm_backward(const float *x, const float *gamma,
                                 float epsilon, const float *dy, float *dx,
                                 float *dgamma, float *dbeta, size_t rows,
-                                size_t cols, const float *base,
+                                size_t cols, const float *base, float *dx_sums,
                                 cudaStream_t stream);
 
 // ---- attention (attention.cu) --------------------------------------------

@@ -97,13 +97,14 @@ layer_norm_backward_kernel(const float *__restrict__ x,
                            const float *__restrict__ gamma, float epsilon,
                            const float *__restrict__ dy, float *dx,
                            float *__restrict__ dgamma, float *__restrict__ dbeta,
-                           size_t rows, size_t cols, const float *base) {
+                           size_t rows, size_t cols, const float *base,
+                           float *__restrict__ dx_sums) {
     __shared__ float4 fold[kWarpsPerBlock][32];
     const int lane = threadIdx.x & 31;
     const int warp_in_block = threadIdx.x >> 5;
     const size_t warp = size_t(blockIdx.x) * kWarpsPerBlock + warp_in_block;
     const size_t warps = size_t(gridDim.x) * kWarpsPerBlock;
-    float4 g[NV], sum_gamma[NV], sum_beta[NV];
+    float4 g[NV], sum_gamma[NV], sum_beta[NV], sum_dx[NV];
 #pragma unroll
     for (int j = 0; j < NV; ++j) {
         const size_t col = size_t(j) * 128 + lane * 4;
@@ -111,6 +112,7 @@ layer_norm_backward_kernel(const float *__restrict__ x,
                           : make_float4(0.f, 0.f, 0.f, 0.f);
         sum_gamma[j] = make_float4(0.f, 0.f, 0.f, 0.f);
         sum_beta[j] = make_float4(0.f, 0.f, 0.f, 0.f);
+        sum_dx[j] = make_float4(0.f, 0.f, 0.f, 0.f);
     }
     const float inverse_cols = 1.0f / float(cols);
     for (size_t row = warp; row < rows; row += warps) {
@@ -159,6 +161,10 @@ layer_norm_backward_kernel(const float *__restrict__ x,
                 d.z += inverse_std * (u[j].z - s1 - v[j].z * s2);
                 d.w += inverse_std * (u[j].w - s1 - v[j].w * s2);
                 *target = d;
+                sum_dx[j].x += d.x;
+                sum_dx[j].y += d.y;
+                sum_dx[j].z += d.z;
+                sum_dx[j].w += d.w;
             }
         }
     }
@@ -167,9 +173,10 @@ layer_norm_backward_kernel(const float *__restrict__ x,
     for (int j = 0; j < NV; ++j) {
         const size_t col = size_t(j) * 128 + lane * 4;
 #pragma unroll
-        for (int which = 0; which < 2; ++which) {
+        for (int which = 0; which < (dx_sums ? 3 : 2); ++which) {
             __syncthreads();
-            fold[warp_in_block][lane] = which == 0 ? sum_gamma[j] : sum_beta[j];
+            fold[warp_in_block][lane] =
+                which == 0 ? sum_gamma[j] : (which == 1 ? sum_beta[j] : sum_dx[j]);
             __syncthreads();
             if (warp_in_block == 0 && col < cols) {
                 float4 total = fold[0][lane];
@@ -181,7 +188,8 @@ layer_norm_backward_kernel(const float *__restrict__ x,
                     total.z += other.z;
                     total.w += other.w;
                 }
-                float *target = (which == 0 ? dgamma : dbeta) + col;
+                float *target =
+                    (which == 0 ? dgamma : (which == 1 ? dbeta : dx_sums)) + col;
                 atomicAdd(target + 0, total.x);
                 atomicAdd(target + 1, total.y);
                 atomicAdd(target + 2, total.z);
@@ -304,25 +312,29 @@ void launch_layer_norm(const float *x, const float *gamma, const float *beta,
 void launch_layer_norm_backward(const float *x, const float *gamma,
                                 float epsilon, const float *dy, float *dx,
                                 float *dgamma, float *dbeta, size_t rows,
-                                size_t cols, const float *base, cudaStream_t stream) {
+                                size_t cols, const float *base, float *dx_sums,
+                                cudaStream_t stream) {
     const unsigned grid = row_grid(rows, 4);
     const unsigned block = kWarpsPerBlock * 32;
     const size_t slots = (cols + 127) / 128;
     if (cols % 4 != 0 || slots > 8) {
         layer_norm_backward_generic_kernel<<<grid, block, 0, stream>>>(
             x, gamma, epsilon, dy, dx, dgamma, dbeta, rows, cols, base);
+        if (dx_sums) {
+            launch_column_sums(dx, dx_sums, rows, cols, cols, stream);
+        }
     } else if (slots <= 1) {
         layer_norm_backward_kernel<1><<<grid, block, 0, stream>>>(
-            x, gamma, epsilon, dy, dx, dgamma, dbeta, rows, cols, base);
+            x, gamma, epsilon, dy, dx, dgamma, dbeta, rows, cols, base, dx_sums);
     } else if (slots <= 2) {
         layer_norm_backward_kernel<2><<<grid, block, 0, stream>>>(
-            x, gamma, epsilon, dy, dx, dgamma, dbeta, rows, cols, base);
+            x, gamma, epsilon, dy, dx, dgamma, dbeta, rows, cols, base, dx_sums);
     } else if (slots <= 4) {
         layer_norm_backward_kernel<4><<<grid, block, 0, stream>>>(
-            x, gamma, epsilon, dy, dx, dgamma, dbeta, rows, cols, base);
+            x, gamma, epsilon, dy, dx, dgamma, dbeta, rows, cols, base, dx_sums);
     } else {
         layer_norm_backward_kernel<8><<<grid, block, 0, stream>>>(
-            x, gamma, epsilon, dy, dx, dgamma, dbeta, rows, cols, base);
+            x, gamma, epsilon, dy, dx, dgamma, dbeta, rows, cols, base, dx_sums);
     }
     ++g_kernel_launches;
 }

@@ -89,6 +89,9 @@ def load_backend_library():
     lib.vitb200_kernel_launches.restype = ctypes.c_ulonglong
     lib.vitb200_memory_counters.restype = None
     lib.vitb200_memory_counters.argtypes = [ctypes.POINTER(_size_t)] * 8
+    lib.vitb200_fusion_counters.restype = None
+    lib.vitb200_fusion_counters.argtypes = [ctypes.c_void_p] + \
+        [ctypes.POINTER(ctypes.c_ulonglong)] * 3
     lib.vitb200_elision_counters.restype = None
     lib.vitb200_elision_counters.argtypes = [ctypes.POINTER(_size_t)] * 5
     lib.vitb200_timer_begin.restype = ctypes.c_int
@@ -195,6 +198,13 @@ class Backend:
         self.lib.vitb200_elision_counters(*[ctypes.byref(v) for v in values])
         names = ["zero_fills_elided", "zero_fills_materialised", "lazy_defined",
                  "lazy_materialised", "lazy_dropped"]
+        return {n: int(v.value) for n, v in zip(names, values)}
+
+    def fusion_counters(self):
+        values = [ctypes.c_ulonglong() for _ in range(3)]
+        self.lib.vitb200_fusion_counters(self.handle,
+                                         *[ctypes.byref(v) for v in values])
+        names = ["epilogues", "head_layouts", "bias_gradients"]
         return {n: int(v.value) for n, v in zip(names, values)}
 
     def device_busy_ms(self, reset=False):
