@@ -56,6 +56,7 @@ constexpr int kStageBytes = 2 * kOperandBytes;
 constexpr int kMaxStages = 6;
 constexpr int kSmemLimit = 227 * 1024 - 1024;   // leave room for static shared memory
 constexpr int kThreads = 192;
+constexpr int kBarrierBytes = 256;   // 2 x kMaxStages + 4 mbarriers, TMEM slot
 constexpr int kTmemColumns = 256;                  // two 128-column accumulators
 constexpr unsigned long long kWaitLimitNs = 2000000000ull;  // 2 s
 
@@ -218,6 +219,7 @@ struct TcParams {
     int k_blocks_per_split;
     int splits;
     int stages;               // depth of the load ring
+    int staging_bytes;        // epilogue staging: 16 or 32 KiB
     int m_tiles, n_tiles;
     int a_mn_major, b_mn_major;
     int reduce_add;           // 1: TMA reduce-add into D, 0: plain store
@@ -245,19 +247,27 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a,
                const __grid_constant__ CUtensorMap map_b,
                const __grid_constant__ CUtensorMap map_d,
                const __grid_constant__ CUtensorMap map_d2, const TcParams p) {
-    extern __shared__ uint8_t raw_smem[];
-    __shared__ __align__(8) uint64_t full_bar[kMaxStages];
-    __shared__ __align__(8) uint64_t empty_bar[kMaxStages];
-    __shared__ __align__(8) uint64_t tmem_full_bar[2];
-    __shared__ __align__(8) uint64_t tmem_empty_bar[2];
-    __shared__ uint32_t tmem_base_slot;
-
-    uint8_t *smem = reinterpret_cast<uint8_t *>(
-        (reinterpret_cast<uintptr_t>(raw_smem) + 1023) & ~uintptr_t(1023));
+    // All shared memory is dynamic, so that it starts at the beginning of the
+    // CTA's window and the swizzled tiles get their 1024-byte alignment without
+    // padding (two CTAs with three stages each fill the SM to the last KiB):
+    //   [stages x 32 KiB operand tiles][epilogue staging][barriers]
+    extern __shared__ __align__(1024) uint8_t smem[];
     const int kStages = p.stages;
-    uint8_t *staging = smem + kStages * kStageBytes;   // [output][buffer] 16 KiB
+    uint8_t *staging = smem + kStages * kStageBytes;
+    uint64_t *full_bar = reinterpret_cast<uint64_t *>(staging + p.staging_bytes);
+    uint64_t *empty_bar = full_bar + kMaxStages;
+    uint64_t *tmem_full_bar = empty_bar + kMaxStages;
+    uint64_t *tmem_empty_bar = tmem_full_bar + 2;
+    uint32_t &tmem_base_slot = *reinterpret_cast<uint32_t *>(tmem_empty_bar + 2);
     const int warp = threadIdx.x >> 5;
     const int lane = threadIdx.x & 31;
+    if ((smem_address(smem) & 1023u) != 0) {
+        // Never expected; without the alignment the MMA would read garbage.
+        if (threadIdx.x == 0) {
+            atomicExch(p.status, 6);
+        }
+        return;
+    }
 
     if (threadIdx.x == 0) {
         for (int s = 0; s < kStages; ++s) {
@@ -400,10 +410,11 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a,
         // needs no block-wide barrier at all.
         const int quarter = warp & 3;
         const int outputs = p.second ? 2 : 1;
-        // One staged output is double-buffered per warp; with two outputs each
-        // gets a single buffer, which keeps the CTA small enough for two per SM.
-        const int buffers = p.second ? 1 : 2;
-        uint8_t *my_staging = staging + quarter * (2 * 4096);   // [output|buffer]
+        // Per warp: two 4 KiB blocks (one output double-buffered, or one buffer
+        // for each of two outputs), or a single block when the load ring was
+        // given the space instead.
+        const int buffers = p.second ? 1 : p.staging_bytes / (4 * 4096);
+        uint8_t *my_staging = staging + quarter * (p.staging_bytes / 4);
         int local = 0;
         int stored = 0;   // blocks handed to TMA so far (selects the buffer)
         for (int item = blockIdx.x; item < items; item += gridDim.x, ++local) {
@@ -721,9 +732,18 @@ int launch_gemm_tc(const TcGemm &g, cudaStream_t stream) {
     // epilogue staging (97 KiB): they interleave their MMA issue and their
     // epilogues, and measured faster than one CTA with a 4- to 6-stage ring
     // at every size tried (449 against 346 TFLOP/s at [100864,512]x[512,2048]).
-    const int staging_bytes = 2 * kOperandBytes;
+    // A single output can give up the second staging buffer of each epilogue
+    // warp for a third load stage: more bytes in flight, which is what the
+    // short-K, bandwidth-bound products of this model lack.
+    int staging_bytes = 2 * kOperandBytes;
     int ctas_per_sm = 2;
     p.stages = 2;
+    if (!g.d2) {
+        p.stages = 3;
+        staging_bytes = kOperandBytes;
+    }
+    static const int forced_staging =
+        getenv("VITB200_TC_STAGING") ? atoi(getenv("VITB200_TC_STAGING")) : 0;
     static const int forced_stages =
         getenv("VITB200_TC_STAGES") ? atoi(getenv("VITB200_TC_STAGES")) : 0;
     static const int forced_ctas =
@@ -734,6 +754,12 @@ int launch_gemm_tc(const TcGemm &g, cudaStream_t stream) {
     if (forced_ctas > 0) {
         ctas_per_sm = forced_ctas;
     }
+    if (forced_staging == 1 && !g.d2) {
+        staging_bytes = kOperandBytes;
+    } else if (forced_staging == 2 || (forced_stages > 0 && forced_staging == 0)) {
+        staging_bytes = 2 * kOperandBytes;
+    }
+    p.staging_bytes = staging_bytes;
     const long long slots = 148LL * ctas_per_sm;
     int splits = 1;
     if (g.accumulate) {
@@ -774,7 +800,7 @@ int launch_gemm_tc(const TcGemm &g, cudaStream_t stream) {
     // One persistent CTA per SM (the shared-memory ring fills an SM), fewer
     // when there is less work than SMs.
     const long long items = (long long)tiles * splits;
-    const int smem_bytes = p.stages * kStageBytes + staging_bytes + 1024;
+    const int smem_bytes = p.stages * kStageBytes + staging_bytes + kBarrierBytes;
     const unsigned grid = unsigned(items < slots ? items : slots);
     gemm_tc_kernel<<<grid, kThreads, smem_bytes, stream>>>(
         map_a, map_b, map_d, map_d2, p);
