@@ -674,12 +674,14 @@ int *status_word() {
 }  // namespace
 
 bool gemm_tc_supported(const TcGemm &g) {
-    // TMA needs 16-byte aligned bases and row pitches; tiny extents are left
-    // to the FP32 kernel.
+    // TMA needs 16-byte aligned bases and row pitches.  An extent may be
+    // smaller than the 32-wide box (the 16-pixel patches of the 28 x 28
+    // models): out-of-range elements load as zero and stores are clipped.
+    // Tiny extents are left to the FP32 kernel.
     auto aligned = [](const void *p) {
         return (reinterpret_cast<uintptr_t>(p) & 15) == 0;
     };
-    return g.m >= 32 && g.n >= 32 && g.k >= 32 && g.lda % 4 == 0 &&
+    return g.m >= 16 && g.n >= 16 && g.k >= 16 && g.lda % 4 == 0 &&
            g.ldb % 4 == 0 && g.ldd % 4 == 0 && aligned(g.a) && aligned(g.b) &&
            aligned(g.d) && (!g.bias || aligned(g.bias)) &&
            (!g.d2 || (aligned(g.d2) && g.ldd2 % 4 == 0 && !g.accumulate)) &&
