@@ -253,48 +253,49 @@ __device__ __forceinline__ void clear(float (&c)[N][4]) {
     }
 }
 
-// Row-wise softmax of a 16 x 64 accumulator tile set holding raw scores:
-// p = exp2(scale2 * s - lse2) with columns >= seq masked out.  Returns the two
-// rows' log-sum-exp (base 2, scaled scores).
+// Row-wise softmax of a 16 x 64 accumulator tile set holding raw scores, up
+// to the normalisation: s becomes exp2(scale2 * (s - max)) with columns >= seq
+// at zero; the caller applies 1 / sum where it is cheapest.  Also returns the
+// two rows' log-sum-exp (base 2, of the scaled scores).  scale2 > 0.
 template <int TILES>
 __device__ __forceinline__ void softmax_rows(float (&s)[8][4], int seq, int t,
-                                             float scale2, float &lse_a,
+                                             float scale2, float &inverse_a,
+                                             float &inverse_b, float &lse_a,
                                              float &lse_b) {
     float max_a = -FLT_MAX, max_b = -FLT_MAX;
 #pragma unroll
     for (int n = 0; n < TILES; ++n) {
+        if (n * 8 + 8 > seq) {   // only the tiles that reach past the end
 #pragma unroll
-        for (int e = 0; e < 4; ++e) {
-            const int column = n * 8 + 2 * t + (e & 1);
-            s[n][e] = column < seq ? s[n][e] * scale2 : -FLT_MAX;
+            for (int e = 0; e < 4; ++e) {
+                if (n * 8 + 2 * t + (e & 1) >= seq) {
+                    s[n][e] = -FLT_MAX;
+                }
+            }
         }
         max_a = fmaxf(max_a, fmaxf(s[n][0], s[n][1]));
         max_b = fmaxf(max_b, fmaxf(s[n][2], s[n][3]));
     }
     max_a = quad_max(max_a);
     max_b = quad_max(max_b);
+    const float shift_a = -max_a * scale2, shift_b = -max_b * scale2;
     float sum_a = 0.0f, sum_b = 0.0f;
 #pragma unroll
     for (int n = 0; n < TILES; ++n) {
-        s[n][0] = exp2_fast(s[n][0] - max_a);
-        s[n][1] = exp2_fast(s[n][1] - max_a);
-        s[n][2] = exp2_fast(s[n][2] - max_b);
-        s[n][3] = exp2_fast(s[n][3] - max_b);
+        // A masked entry is -FLT_MAX: the product overflows to -inf, exp2 -> 0.
+        s[n][0] = exp2_fast(fmaf(s[n][0], scale2, shift_a));
+        s[n][1] = exp2_fast(fmaf(s[n][1], scale2, shift_a));
+        s[n][2] = exp2_fast(fmaf(s[n][2], scale2, shift_b));
+        s[n][3] = exp2_fast(fmaf(s[n][3], scale2, shift_b));
         sum_a += s[n][0] + s[n][1];
         sum_b += s[n][2] + s[n][3];
     }
     sum_a = quad_sum(sum_a);
     sum_b = quad_sum(sum_b);
-    const float inverse_a = 1.0f / sum_a, inverse_b = 1.0f / sum_b;
-#pragma unroll
-    for (int n = 0; n < TILES; ++n) {
-        s[n][0] *= inverse_a;
-        s[n][1] *= inverse_a;
-        s[n][2] *= inverse_b;
-        s[n][3] *= inverse_b;
-    }
-    lse_a = max_a + log2f(sum_a);
-    lse_b = max_b + log2f(sum_b);
+    inverse_a = 1.0f / sum_a;
+    inverse_b = 1.0f / sum_b;
+    lse_a = max_a * scale2 + log2f(sum_a);
+    lse_b = max_b * scale2 + log2f(sum_b);
 }
 
 template <int HD, int TILES>
@@ -342,11 +343,21 @@ attention_warp_forward_kernel(const float *__restrict__ q,
         float p[8][4];
         clear(p);
         product_rows<HD, TILES>(p, a0, a1, k_tile, g, t);
-        float lse_a, lse_b;
-        softmax_rows<TILES>(p, seq, t, scale * kLog2e, lse_a, lse_b);
+        float inverse_a, inverse_b, lse_a, lse_b;
+        softmax_rows<TILES>(p, seq, t, scale * kLog2e, inverse_a, inverse_b,
+                            lse_a, lse_b);
         float o[S::kOut][4];
         clear(o);
         product_columns<HD, TILES>(o, p, v_tile, g, t);
+        // The probabilities were left unnormalised: scale the 16 x HD result
+        // instead of the 16 x 64 tile.
+#pragma unroll
+        for (int u = 0; u < S::kOut; ++u) {
+            o[u][0] *= inverse_a;
+            o[u][1] *= inverse_a;
+            o[u][2] *= inverse_b;
+            o[u][3] *= inverse_b;
+        }
         store_result<HD>(out_base, out_layout.ld, r0, r1, seq, t, o, false);
     }
 }
@@ -428,17 +439,18 @@ attention_warp_backward_kernel(
         float p[8][4];
         clear(p);
         product_rows<HD, TILES>(p, a0, a1, k_tile, g, t);
-        float lse_a, lse_b;
-        softmax_rows<TILES>(p, seq, t, scale2, lse_a, lse_b);
+        float inverse_a, inverse_b, lse_a, lse_b;
+        softmax_rows<TILES>(p, seq, t, scale2, inverse_a, inverse_b, lse_a,
+                            lse_b);
         const float dot_a = row_dots[pass][0], dot_b = row_dots[pass][1];
         if (t == 0) {
             if (r0 < seq) {
                 row_lse[r0] = lse_a;
-                row_dot[r0] = dot_a;
+                row_dot[r0] = -scale * dot_a;
             }
             if (r1 < seq) {
                 row_lse[r1] = lse_b;
-                row_dot[r1] = dot_b;
+                row_dot[r1] = -scale * dot_b;
             }
         }
         // dP = dO V^T, then dS = scale P (dP - D) in place over dP.
@@ -447,12 +459,15 @@ attention_warp_backward_kernel(
         float ds[8][4];
         clear(ds);
         product_rows<HD, TILES>(ds, a0, a1, v_tile, g, t);
+        // p holds exp2(.) without the 1 / sum: fold it into the row factor.
+        const float factor_a = scale * inverse_a, factor_b = scale * inverse_b;
+        const float offset_a = -dot_a * factor_a, offset_b = -dot_b * factor_b;
 #pragma unroll
         for (int n = 0; n < TILES; ++n) {
-            ds[n][0] = scale * p[n][0] * (ds[n][0] - dot_a);
-            ds[n][1] = scale * p[n][1] * (ds[n][1] - dot_a);
-            ds[n][2] = scale * p[n][2] * (ds[n][2] - dot_b);
-            ds[n][3] = scale * p[n][3] * (ds[n][3] - dot_b);
+            ds[n][0] = p[n][0] * fmaf(ds[n][0], factor_a, offset_a);
+            ds[n][1] = p[n][1] * fmaf(ds[n][1], factor_a, offset_a);
+            ds[n][2] = p[n][2] * fmaf(ds[n][2], factor_b, offset_b);
+            ds[n][3] = p[n][3] * fmaf(ds[n][3], factor_b, offset_b);
         }
         float result[S::kOut][4];
         clear(result);
@@ -490,11 +505,12 @@ attention_warp_backward_kernel(
         product_rows<HD, TILES>(ds, a0, a1, g_tile, g, t);   // dP^T = V dO^T
 #pragma unroll
         for (int n = 0; n < TILES; ++n) {
+            // row_dot holds -scale * D_i.
             const float2 dot = *reinterpret_cast<const float2 *>(row_dot + n * 8 + 2 * t);
-            ds[n][0] = scale * p[n][0] * (ds[n][0] - dot.x);
-            ds[n][1] = scale * p[n][1] * (ds[n][1] - dot.y);
-            ds[n][2] = scale * p[n][2] * (ds[n][2] - dot.x);
-            ds[n][3] = scale * p[n][3] * (ds[n][3] - dot.y);
+            ds[n][0] = p[n][0] * fmaf(ds[n][0], scale, dot.x);
+            ds[n][1] = p[n][1] * fmaf(ds[n][1], scale, dot.y);
+            ds[n][2] = p[n][2] * fmaf(ds[n][2], scale, dot.x);
+            ds[n][3] = p[n][3] * fmaf(ds[n][3], scale, dot.y);
         }
         clear(result);
         product_columns<HD, TILES>(result, ds, q_tile, g, t);   // dK = dS^T Q
