@@ -8,8 +8,9 @@ The reference sources are compiled where they lie (they are never copied into
 this repository) with the flags of the reference Makefile:2
 (-std=c99 -O2).  Outputs, all under oracle/_ref/ (git-ignored):
 
-  libvithost.so   ops.c vit.c autodiff.c arena.c  +  our flat ctypes-friendly
-                  entry points (transformer-in-c_b200/host/vit_host.c)
+  libvithost.so   ops.c vit.c autodiff.c arena.c augmentation.c  +  our flat
+                  ctypes-friendly entry points
+                  (transformer-in-c_b200/host/vit_host.c)
   test_device     the reference's CPU-vs-device acceptance test
                   (tests/test_device.c, -DENABLE_CUDA) linked against
                   libvitb200.so instead of the reference's cuda_backend.o
@@ -43,7 +44,8 @@ def build(reference_root="/root/reference"):
     flags = ["-std=c99", "-O2", "-fPIC", "-I" + include]
     core = [os.path.join(source, name) for name in CORE]
     run(["gcc", *flags, "-shared", "-o", os.path.join(OUT, "libvithost.so"),
-         *core, os.path.join(PACKAGE, "host", "vit_host.c"), "-lm"])
+         *core, os.path.join(source, "augmentation.c"),
+         os.path.join(PACKAGE, "host", "vit_host.c"), "-lm"])
     run(["gcc", *flags, "-o", os.path.join(OUT, "test_vision"),
          os.path.join(reference_root, "tests", "test_vision.c"), *core,
          *[os.path.join(source, name) for name in EXTRA], "-lm"])

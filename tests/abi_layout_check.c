@@ -3,6 +3,8 @@
 #include "ops.h"
 #include "tensor.h"
 #include "vitb200_host_abi.h"
+#include "augmentation.h"
+#include "vitb200_augmentation.h"
 
 #include <stddef.h>
 
@@ -42,6 +44,18 @@ SLOT(token_embedding); SLOT(token_embedding_backward); SLOT(gather_rows);
 SLOT(gather_rows_backward); SLOT(softmax_cross_entropy);
 SLOT(clip_gradient_norm); SLOT(adamw_step); SLOT(zero_gradients);
 SLOT(adamw_step_parameters); SLOT(synchronize);
+
+SAME_SIZE(DataAugmentation, vitb200_augmentation);
+#define AUGMENTATION_FIELD(f) \
+    SAME_FIELD(DataAugmentation, f, vitb200_augmentation, f)
+AUGMENTATION_FIELD(max_shift_pixels); AUGMENTATION_FIELD(max_rotation_degrees);
+AUGMENTATION_FIELD(max_scale_delta); AUGMENTATION_FIELD(max_brightness_delta);
+AUGMENTATION_FIELD(max_contrast_delta);
+AUGMENTATION_FIELD(noise_standard_deviation);
+AUGMENTATION_FIELD(erasing_probability);
+AUGMENTATION_FIELD(erasing_max_side_fraction);
+AUGMENTATION_FIELD(erasing_value); AUGMENTATION_FIELD(minimum_value);
+AUGMENTATION_FIELD(maximum_value);
 
 /* Assigning the host's function-pointer types to ours checks the signatures. */
 static void signatures(const OpsDeviceBackend *host, vitb200_op_table *ours) {

@@ -8,7 +8,9 @@ from conftest import PACKAGE, REPO
 
 
 def declared_functions():
-    text = open(os.path.join(REPO, "include", "vitb200.h")).read()
+    text = ""
+    for header in ("vitb200.h", "vitb200_augmentation.h"):
+        text += open(os.path.join(REPO, "include", header)).read()
     text = re.sub(r"/\*.*?\*/", "", text, flags=re.S)
     names = re.findall(r"\b((?:cuda_backend|vitb200)_\w+)\s*\(", text)
     return sorted(set(names))
@@ -20,6 +22,10 @@ def test_every_declared_symbol_is_exported():
     lib = ctypes.CDLL(library)
     names = declared_functions()
     assert len(names) >= 5 + 4 + 11
+    for name in ("vitb200_data_augmentation_apply",
+                 "vitb200_data_augmentation_translate",
+                 "vitb200_data_augmentation_enabled"):
+        assert name in names
     for name in ("cuda_backend_create", "cuda_backend_free",
                  "cuda_backend_available",
                  "cuda_backend_enable_device_execution",

@@ -15,7 +15,8 @@ import pytest
 from conftest import GOLDEN
 from oracle import vit_oracle as vo
 
-FIXTURES = sorted(glob.glob(os.path.join(GOLDEN, "*.npz")))
+FIXTURES = sorted(path for path in glob.glob(os.path.join(GOLDEN, "*.npz"))
+                  if os.path.basename(path) != "augmentation.npz")
 
 
 def load(path):

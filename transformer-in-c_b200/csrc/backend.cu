@@ -9,7 +9,9 @@
 // kernels index; it never declines half-way through.
 #include "../../include/vitb200.h"
 #include "../../include/vitb200_host_abi.h"
+#include "../../include/vitb200_augmentation.h"
 
+#include "augmentation.h"
 #include "coherence.h"
 #include "data_parallel.h"
 #include "gemm.h"
@@ -153,6 +155,12 @@ struct CudaBackend {
     ColumnSumMemo column_memo;
     Scratch column_sums;       // all zero whenever !column_sums_dirty
     Scratch column_partials;
+    // Batch augmentation: device staging for plain host buffers, the
+    // per-sample table (pinned host copy + device copy) and the plane means.
+    Scratch augment_source, augment_destination, augment_table, augment_means;
+    void *augment_host_table = nullptr;
+    size_t augment_host_bytes = 0;
+    cudaEvent_t augment_table_read = nullptr;
     bool column_sums_dirty = false;
     unsigned long long memo_hits = 0;
     PendingGemm pending;
@@ -1827,6 +1835,16 @@ extern "C" void cuda_backend_free(CudaBackend *backend) {
     free_scratch(backend->slice_table);
     free_scratch(backend->column_sums);
     free_scratch(backend->column_partials);
+    free_scratch(backend->augment_source);
+    free_scratch(backend->augment_destination);
+    free_scratch(backend->augment_table);
+    free_scratch(backend->augment_means);
+    if (backend->augment_host_table) {
+        cudaFreeHost(backend->augment_host_table);
+    }
+    if (backend->augment_table_read) {
+        cudaEventDestroy(backend->augment_table_read);
+    }
     for (int i = 0; i < kStagingSlots; ++i) {
         if (backend->staging[i]) {
             cudaFreeHost(backend->staging[i]);
@@ -1942,6 +1960,152 @@ extern "C" void vitb200_elision_counters(size_t *zero_fills_elided,
     if (lazy_defined) *lazy_defined = s.lazy_defined;
     if (lazy_materialised) *lazy_materialised = s.lazy_materialised;
     if (lazy_dropped) *lazy_dropped = s.lazy_dropped;
+}
+
+namespace {
+
+static_assert(sizeof(vitb200_augmentation) == sizeof(AugmentationSettings),
+              "public and internal augmentation settings must match");
+
+// Device view of an augmentation operand: tensor memory from our allocator is
+// used where it is, anything else goes through a staging buffer.
+const float *augment_input(CudaBackend *backend, const float *source,
+                           size_t count) {
+    if (coherent_owns(source)) {
+        return view(backend, source, Access::Read);
+    }
+    float *staged = scratch<float>(backend, backend->augment_source, count);
+    check(cudaMemcpyAsync(staged, source, count * sizeof(float),
+                          cudaMemcpyHostToDevice, backend->stream),
+          "cudaMemcpyAsync(host to device)");
+    return staged;
+}
+
+float *augment_output(CudaBackend *backend, float *destination, size_t count,
+                      bool *staged) {
+    *staged = !coherent_owns(destination);
+    if (!*staged) {
+        return view(backend, destination, Access::Overwrite);
+    }
+    return scratch<float>(backend, backend->augment_destination, count);
+}
+
+// Copies a staged result back and waits, so that a plain host buffer holds it
+// when the call returns.
+void augment_finish(CudaBackend *backend, float *destination,
+                    const float *device, size_t count, bool staged) {
+    if (staged) {
+        check(cudaMemcpyAsync(destination, device, count * sizeof(float),
+                              cudaMemcpyDeviceToHost, backend->stream),
+              "cudaMemcpyAsync(device to host)");
+        check(cudaStreamSynchronize(backend->stream), "cudaStreamSynchronize");
+    }
+}
+
+}  // namespace
+
+extern "C" int vitb200_data_augmentation_enabled(
+    const vitb200_augmentation *augmentation) {
+    return augmentation &&
+           augmentation_enabled(
+               *reinterpret_cast<const AugmentationSettings *>(augmentation));
+}
+
+extern "C" int vitb200_data_augmentation_apply(
+    CudaBackend *backend, const vitb200_augmentation *augmentation,
+    uint64_t *random_state, const float *source, float *destination,
+    size_t batch, size_t channels, size_t height, size_t width) {
+    const AugmentationSettings *settings =
+        reinterpret_cast<const AugmentationSettings *>(augmentation);
+    if (!cuda_backend_available(backend) ||
+        !augmentation_arguments_valid(settings, random_state, source,
+                                      destination, batch, channels, height,
+                                      width) ||
+        !fits_int(height * width) || !fits_int(channels)) {
+        return -1;
+    }
+    flush_pending(backend);
+    // The per-sample table is written on the host into pinned memory that the
+    // previous call's upload may still be reading.
+    const size_t table_bytes = batch * sizeof(AugmentationSample);
+    if (!backend->augment_table_read) {
+        check(cudaEventCreateWithFlags(&backend->augment_table_read,
+                                       cudaEventDisableTiming),
+              "cudaEventCreate");
+    } else {
+        check(cudaEventSynchronize(backend->augment_table_read),
+              "cudaEventSynchronize");
+    }
+    if (backend->augment_host_bytes < table_bytes) {
+        if (backend->augment_host_table) {
+            cudaFreeHost(backend->augment_host_table);
+        }
+        check(cudaHostAlloc(&backend->augment_host_table, table_bytes * 2,
+                            cudaHostAllocDefault),
+              "cudaHostAlloc");
+        backend->augment_host_bytes = table_bytes * 2;
+    }
+    AugmentationSample *host_table =
+        static_cast<AugmentationSample *>(backend->augment_host_table);
+    augmentation_plan(*settings, random_state, batch, channels, height, width,
+                      host_table);
+    const size_t count = batch * channels * height * width;
+    AugmentationSample *table = scratch<AugmentationSample>(
+        backend, backend->augment_table, batch);
+    float *means = scratch<float>(backend, backend->augment_means,
+                                  batch * channels);
+    check(cudaMemcpyAsync(table, host_table, table_bytes,
+                          cudaMemcpyHostToDevice, backend->stream),
+          "cudaMemcpyAsync(host to device)");
+    check(cudaEventRecord(backend->augment_table_read, backend->stream),
+          "cudaEventRecord");
+    const float *in = nullptr;
+    float *out = nullptr;
+    bool staged = false;
+    if (source == destination) {
+        // In place (only without a geometric transform, checked above).
+        if (coherent_owns(destination)) {
+            out = view(backend, destination, Access::ReadWrite);
+        } else {
+            out = const_cast<float *>(augment_input(backend, source, count));
+            staged = true;
+        }
+        in = out;
+    } else {
+        in = augment_input(backend, source, count);
+        out = augment_output(backend, destination, count, &staged);
+    }
+    {
+        OpScope scope(backend, "data_augmentation", 8.0 * double(count), 0.0);
+        launch_augmentation(*settings, table, in, out, means, batch, channels,
+                            height, width, backend->stream);
+    }
+    augment_finish(backend, destination, out, count, staged);
+    return 0;
+}
+
+extern "C" int vitb200_data_augmentation_translate(
+    CudaBackend *backend, const float *source, float *destination, size_t batch,
+    size_t channels, size_t height, size_t width, float shift_y,
+    float shift_x) {
+    // Checks of the reference, src/augmentation.c:235-238.
+    if (!cuda_backend_available(backend) || !source || !destination ||
+        source == destination || batch == 0 || channels == 0 || height == 0 ||
+        width == 0 || !fits_int(height * width) || !fits_int(channels)) {
+        return -1;
+    }
+    flush_pending(backend);
+    const size_t count = batch * channels * height * width;
+    const float *in = augment_input(backend, source, count);
+    bool staged = false;
+    float *out = augment_output(backend, destination, count, &staged);
+    {
+        OpScope scope(backend, "data_augmentation", 8.0 * double(count), 0.0);
+        launch_augmentation_translate(in, out, batch, channels, height, width,
+                                      shift_y, shift_x, backend->stream);
+    }
+    augment_finish(backend, destination, out, count, staged);
+    return 0;
 }
 
 extern "C" void vitb200_fusion_counters(const CudaBackend *backend,

@@ -25,6 +25,17 @@ _size_t = ctypes.c_size_t
 _float_p = ctypes.POINTER(ctypes.c_float)
 
 
+class Augmentation(ctypes.Structure):
+    """vitb200_augmentation: the reference's DataAugmentation, field for field
+    (include/augmentation.h:7-19)."""
+    _fields_ = [(name, ctypes.c_float) for name in (
+        "max_shift_pixels", "max_rotation_degrees", "max_scale_delta",
+        "max_brightness_delta", "max_contrast_delta",
+        "noise_standard_deviation", "erasing_probability",
+        "erasing_max_side_fraction", "erasing_value", "minimum_value",
+        "maximum_value")]
+
+
 def load_host_library(path):
     """Loads the host library so that its symbols are visible to the backend
     (RTLD_GLOBAL), and declares the flat entry points."""
@@ -89,6 +100,18 @@ def load_backend_library():
     lib.vitb200_kernel_launches.restype = ctypes.c_ulonglong
     lib.vitb200_memory_counters.restype = None
     lib.vitb200_memory_counters.argtypes = [ctypes.POINTER(_size_t)] * 8
+    lib.vitb200_data_augmentation_apply.restype = ctypes.c_int
+    lib.vitb200_data_augmentation_apply.argtypes = [
+        ctypes.c_void_p, ctypes.POINTER(Augmentation),
+        ctypes.POINTER(ctypes.c_uint64), _float_p, _float_p, _size_t, _size_t,
+        _size_t, _size_t]
+    lib.vitb200_data_augmentation_translate.restype = ctypes.c_int
+    lib.vitb200_data_augmentation_translate.argtypes = [
+        ctypes.c_void_p, _float_p, _float_p, _size_t, _size_t, _size_t, _size_t,
+        ctypes.c_float, ctypes.c_float]
+    lib.vitb200_data_augmentation_enabled.restype = ctypes.c_int
+    lib.vitb200_data_augmentation_enabled.argtypes = [
+        ctypes.POINTER(Augmentation)]
     lib.vitb200_fusion_counters.restype = None
     lib.vitb200_fusion_counters.argtypes = [ctypes.c_void_p] + \
         [ctypes.POINTER(ctypes.c_ulonglong)] * 3
@@ -199,6 +222,34 @@ class Backend:
         names = ["zero_fills_elided", "zero_fills_materialised", "lazy_defined",
                  "lazy_materialised", "lazy_dropped"]
         return {n: int(v.value) for n, v in zip(names, values)}
+
+    def augment(self, settings, state, source, destination=None):
+        """vitb200_data_augmentation_apply on host arrays.  `settings` maps the
+        reference's DataAugmentation field names to numbers; source is
+        [batch, channels, height, width] float32.  Returns
+        (status, destination, new_state); destination=source (the same array)
+        asks for in-place operation."""
+        config = Augmentation(**{k: float(v) for k, v in settings.items()})
+        source = np.ascontiguousarray(source, dtype=np.float32)
+        if destination is None:
+            destination = np.zeros_like(source)
+        rng = ctypes.c_uint64(state)
+        batch, channels, height, width = source.shape
+        status = self.lib.vitb200_data_augmentation_apply(
+            self.handle, ctypes.byref(config), ctypes.byref(rng),
+            source.ctypes.data_as(_float_p), destination.ctypes.data_as(_float_p),
+            batch, channels, height, width)
+        return int(status), destination, int(rng.value)
+
+    def translate(self, source, shift_y, shift_x):
+        source = np.ascontiguousarray(source, dtype=np.float32)
+        destination = np.zeros_like(source)
+        batch, channels, height, width = source.shape
+        status = self.lib.vitb200_data_augmentation_translate(
+            self.handle, source.ctypes.data_as(_float_p),
+            destination.ctypes.data_as(_float_p), batch, channels, height,
+            width, ctypes.c_float(shift_y), ctypes.c_float(shift_x))
+        return int(status), destination
 
     def fusion_counters(self):
         values = [ctypes.c_ulonglong() for _ in range(3)]
