@@ -137,6 +137,73 @@ def cpu_reference_rate(vh, host_lib, config, seconds_budget, max_batch=32):
     return batch * steps / elapsed, batch, steps
 
 
+# The trainer's augmentation settings (reference examples/organ_smnist.c:142-151)
+# for pixels in [0, 1].
+AUGMENTATION = {
+    "max_shift_pixels": 2.0, "max_rotation_degrees": 10.0,
+    "max_scale_delta": 0.1, "max_brightness_delta": 0.05,
+    "max_contrast_delta": 0.1, "noise_standard_deviation": 0.01,
+    "erasing_probability": 0.25, "erasing_max_side_fraction": 0.4,
+    "erasing_value": 0.5, "minimum_value": 0.0, "maximum_value": 1.0,
+}
+
+
+def augmentation_measurement(backend, host_lib, batch, channels, height, width,
+                             steps, with_cpu):
+    """The batch augmentation that precedes every training step in the
+    reference's trainer (examples/organ_smnist.c:594-612), on the device:
+    `e2e` with page-locked host buffers in and out (both copies inside the
+    timed calls), `value` from the kernels' own CUDA events; beside them the
+    reference's C code on one host core over a bounded sample."""
+    rng = np.random.RandomState(11)
+    pixels = (rng.randint(0, 256, size=(batch, channels, height, width))
+              .astype(np.float32) / np.float32(255.0))
+    keep_in, source = pinned_like(pixels)
+    keep_out, destination = pinned_like(np.zeros_like(pixels))
+    state = 1
+    for _ in range(3):
+        status, _, state = backend.augment(AUGMENTATION, state, source, destination)
+        assert status == 0
+    backend.profile(True)
+    start = time.perf_counter()
+    for _ in range(steps):
+        status, _, state = backend.augment(AUGMENTATION, state, source, destination)
+    elapsed = time.perf_counter() - start
+    kernel_ms = sum(e["ms"] for e in backend.profile_entries()
+                    if e["name"] == "data_augmentation")
+    backend.profile(False)
+    images = batch * steps
+    hbm_peak, _, peak_source = measured_peaks()
+    result = {
+        "metric": "augmented images/s", "unit": "images/s",
+        "settings": "reference trainer defaults",
+        "batch": batch, "image": [channels, height, width],
+        "value": images / (kernel_ms / 1e3),
+        "e2e": {"value": images / elapsed,
+                "h2d_bytes_per_step": int(pixels.nbytes) + batch * 48,
+                "d2h_bytes_per_step": int(pixels.nbytes)},
+        # One read and one write of every pixel.
+        "roofline": {"bound": "hbm", "achieved": 2 * pixels.nbytes * steps /
+                     (kernel_ms / 1e3) / 1e9, "peak": hbm_peak, "unit": "GB/s",
+                     "peak_source": peak_source},
+    }
+    result["roofline"]["frac"] = result["roofline"]["achieved"] / hbm_peak
+    if with_cpu:
+        golden = load_module("make_augmentation_golden", os.path.join(
+            REPO, "tests", "golden", "make_augmentation_golden.py"))
+        lib = golden.reference_library()
+        sample = pixels[:min(batch, 512)]
+        start = time.perf_counter()
+        golden.reference_apply(lib, AUGMENTATION, 1, sample)
+        cpu_seconds = time.perf_counter() - start
+        result["cpu_baseline"] = {
+            "value": len(sample) / cpu_seconds, "unit": "images/s", "cores": 1,
+            "kind": "reference",
+            "sample": f"reference data_augmentation_apply, {len(sample)} images, one call"}
+    del keep_in, keep_out
+    return result
+
+
 def run_reference(args, vh, config, batch, rank, world):
     """The reference's own CPU implementation of the step, timed on this
     machine's host cores.  The code is single-threaded on Linux
@@ -345,6 +412,10 @@ def main():
             "value": rate, "unit": "images/s", "cores": 1, "kind": "reference",
             "sample": f"reference CPU train step (single-threaded on Linux), "
                       f"batch {sample_batch}, {sample_steps} steps"}
+    if rank == 0 and world == 1:
+        line["augmentation"] = augmentation_measurement(
+            backend, host_lib, batch, config[0], config[1], config[2],
+            args.steps, with_cpu=not args.no_cpu_baseline)
     if world > 1:
         line["dp"] = backend.dp_counters()
     host.close()

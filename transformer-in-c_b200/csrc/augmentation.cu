@@ -11,8 +11,9 @@
 //
 //   affine kernel   one thread per output pixel: inverse-map, bilinear sample
 //                   with edge padding            (augmentation.c:36-90)
-//   mean kernel     one thread per image plane, summing in the reference's
-//                   order (a float sum is order-dependent)  (:118-122)
+//   mean kernel     one warp per image plane: coalesced loads, additions in
+//                   the reference's order by one lane (a float sum is
+//                   order-dependent)                         (:118-122)
 //   pixel kernel    contrast / brightness, Gaussian noise from the two draws
 //                   that belong to the pixel, clamp, erase  (:123-166, :215-226)
 //
@@ -130,17 +131,30 @@ __global__ void augmentation_affine_kernel(
     }
 }
 
-// augmentation.c:118-122: the plane mean, summed front to back.
+// augmentation.c:118-122: the plane mean, summed front to back.  A float sum
+// depends on its order, so the additions stay sequential (lane 0 does them),
+// but the loads are the warp's: 32 consecutive pixels at a time, handed to
+// lane 0 by shuffles that do not wait for the running sum.
 __global__ void augmentation_mean_kernel(const float *__restrict__ images,
                                          float *__restrict__ means,
                                          size_t planes, size_t plane_size) {
-    for (size_t p = global_thread(); p < planes; p += grid_threads()) {
+    const int lane = threadIdx.x & 31;
+    const size_t warp = global_thread() >> 5;
+    const size_t warps = grid_threads() >> 5;
+    for (size_t p = warp; p < planes; p += warps) {
         const float *plane = images + p * plane_size;
         float sum = 0.0f;
-        for (size_t i = 0; i < plane_size; ++i) {
-            sum = __fadd_rn(sum, plane[i]);
+        for (size_t base = 0; base < plane_size; base += 32) {
+            const size_t index = base + lane;
+            const float mine = index < plane_size ? plane[index] : 0.0f;
+            const int live = int(min(size_t(32), plane_size - base));
+            for (int l = 0; l < live; ++l) {
+                sum = __fadd_rn(sum, __shfl_sync(kFullMask, mine, l));
+            }
         }
-        means[p] = __fdiv_rn(sum, float(plane_size));
+        if (lane == 0) {
+            means[p] = __fdiv_rn(sum, float(plane_size));
+        }
     }
 }
 
@@ -289,9 +303,9 @@ void launch_augmentation(const AugmentationSettings &s,
     const bool clamps = s.minimum_value < s.maximum_value;
     const bool erasing = s.erasing_probability > 0.0f;
     if (jitter) {
-        augmentation_mean_kernel<<<stream_grid(batch * channels), kStreamThreads,
-                                   0, stream>>>(current, means, batch * channels,
-                                                height * width);
+        augmentation_mean_kernel<<<stream_grid(batch * channels * 32),
+                                   kStreamThreads, 0, stream>>>(
+            current, means, batch * channels, height * width);
         ++g_kernel_launches;
     }
     if (jitter || noise || clamps || erasing || current != destination) {
