@@ -15,6 +15,9 @@ this repository) with the flags of the reference Makefile:2
                   (tests/test_device.c, -DENABLE_CUDA) linked against
                   libvitb200.so instead of the reference's cuda_backend.o
   test_vision     the reference's CPU unit tests (oracle sanity)
+  checkpoint_roundtrip
+                  tests/checkpoint_roundtrip.c (ours) on the reference's
+                  vit_model_save / vit_model_load, linked like test_device
 
 Usage: python oracle/build_ref.py [reference_root]
 """
@@ -54,6 +57,10 @@ def build(reference_root="/root/reference"):
         run(["gcc", *flags, "-DENABLE_CUDA", "-o",
              os.path.join(OUT, "test_device"),
              os.path.join(reference_root, "tests", "test_device.c"), *core,
+             "-L" + PACKAGE, "-lvitb200",
+             "-Wl,-rpath,$ORIGIN/../../transformer-in-c_b200", "-lm"])
+        run(["gcc", *flags, "-o", os.path.join(OUT, "checkpoint_roundtrip"),
+             os.path.join(REPO, "tests", "checkpoint_roundtrip.c"), *core,
              "-L" + PACKAGE, "-lvitb200",
              "-Wl,-rpath,$ORIGIN/../../transformer-in-c_b200", "-lm"])
     return True

@@ -1,5 +1,7 @@
 #include "coherence.h"
 
+#include <atomic>
+
 #include <cerrno>
 #include <csignal>
 #include <cstdint>
@@ -83,6 +85,25 @@ Region *find_containing(uintptr_t address) {
     --it;
     Region &region = it->second;
     return address < it->first + region.mapped ? &region : nullptr;
+}
+
+// Lowest and highest mirror addresses ever handed out.  Read without the
+// single-thread assumption of the rest of this file: the stdio hooks are
+// entered from any thread that writes a log line, and must be able to tell
+// "not ours" without touching the registry.
+std::atomic<uintptr_t> g_lowest_mirror{~uintptr_t(0)};
+std::atomic<uintptr_t> g_highest_mirror{0};
+
+void note_mirror_range(const void *mirror, size_t bytes) {
+    const uintptr_t begin = reinterpret_cast<uintptr_t>(mirror);
+    uintptr_t seen = g_lowest_mirror.load(std::memory_order_relaxed);
+    while (begin < seen &&
+           !g_lowest_mirror.compare_exchange_weak(seen, begin)) {
+    }
+    seen = g_highest_mirror.load(std::memory_order_relaxed);
+    while (begin + bytes > seen &&
+           !g_highest_mirror.compare_exchange_weak(seen, begin + bytes)) {
+    }
 }
 
 // Device buffers of released tensors, kept for reuse by size: the host's
@@ -362,6 +383,7 @@ void *coherent_allocate(void *context, size_t bytes) {
     region.bytes = bytes;
     region.mapped = mapped;
     registry()[reinterpret_cast<uintptr_t>(mirror)] = region;
+    note_mirror_range(mirror, mapped);
     g_stats.live_allocations += 1;
     g_stats.mirror_bytes += mapped;
     return mirror;
@@ -632,6 +654,33 @@ int coherent_make_host_owned(const void *host_pointer) {
     }
     serve_host_access(*region, true);
     return 0;
+}
+
+int coherent_prepare_host_io(const void *pointer, size_t bytes,
+                             bool host_writes) {
+    const uintptr_t begin = reinterpret_cast<uintptr_t>(pointer);
+    if (!pointer || bytes == 0 ||
+        begin >= g_highest_mirror.load(std::memory_order_relaxed) ||
+        begin + bytes <= g_lowest_mirror.load(std::memory_order_relaxed)) {
+        return 0;
+    }
+    int touched = 0;
+    for (uintptr_t address = begin; address < begin + bytes;) {
+        Region *region = find_containing(address);
+        if (!region) {
+            // Not ours: step to the next mirror, if any starts inside the range.
+            auto next = registry().upper_bound(address);
+            if (next == registry().end() || next->first >= begin + bytes) {
+                break;
+            }
+            address = next->first;
+            continue;
+        }
+        serve_host_access(*region, host_writes);
+        touched += 1;
+        address = reinterpret_cast<uintptr_t>(region->mirror) + region->mapped;
+    }
+    return touched;
 }
 
 CoherenceStats coherence_stats() {

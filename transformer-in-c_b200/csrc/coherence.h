@@ -114,6 +114,14 @@ bool coherent_is_zero_pending(const void *host_pointer);
 // system call such as fread/fwrite, which reports EFAULT instead of faulting.
 int coherent_make_host_owned(const void *host_pointer);
 
+// Makes every mirror that overlaps [pointer, pointer + bytes) valid for a
+// host-side read (host_writes = false) or read-write access that cannot take
+// a page fault, i.e. a system call.  Returns the number of mirrors touched; 0
+// for memory we did not allocate (decided without looking at the registry, so
+// this may be called from any thread for foreign memory).
+int coherent_prepare_host_io(const void *pointer, size_t bytes,
+                             bool host_writes);
+
 // Called by the backend so the fault handler can drain work before copying.
 void coherence_set_stream(cudaStream_t stream, void (*flush)(void));
 void coherence_install_fault_handler();
