@@ -159,7 +159,8 @@ def test_gradients_and_training_match_cpu_reference(case, precision,
     cpu.close()
 
 
-FIXTURES = sorted(glob.glob(os.path.join(GOLDEN, "*.npz")))
+FIXTURES = sorted(path for path in glob.glob(os.path.join(GOLDEN, "*.npz"))
+                  if os.path.basename(path) != "augmentation.npz")
 
 
 @pytest.mark.parametrize("path", FIXTURES, ids=[os.path.basename(p) for p in FIXTURES])
@@ -354,6 +355,8 @@ def test_unread_tensors_are_not_computed_but_reads_see_them(vit_host_module,
     # their matrix's producer made (layer_norm_backward twice, gelu_backward).
     assert fused["head_layouts"] - fused_before["head_layouts"] == 2 * 2 * layers
     assert fused["bias_gradients"] - fused_before["bias_gradients"] == 2 * 3 * layers
+    # (The fourth, the QKV bias, also comes from its producer when the
+    # tensor-core attention kernels run; this test pins the FP32 policy.)
     # Per block and step: P; the head-major Q, K, V and attention output
     # (views of the projected / merged matrices); and the same five gradients
     # less P's, which nobody produces.

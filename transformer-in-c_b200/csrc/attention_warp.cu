@@ -245,6 +245,23 @@ __device__ __forceinline__ void store_result(float *base, int ld, int r0, int r1
     }
 }
 
+// Adds this lane's two rows of a 16 x HD result tile (rows past `seq`
+// excluded) to its running column sums, indexed like the lane's row range (see
+// store_result); the eight lanes that share the columns are combined once, at
+// the end of the kernel.
+template <int HD>
+__device__ __forceinline__ void add_column_sums(float (&sums)[HD / 4],
+                                                const float (&o)[HD / 8][4],
+                                                int r0, int r1, int seq) {
+    using S = Shape<HD>;
+    const float keep0 = r0 < seq ? 1.0f : 0.0f, keep1 = r1 < seq ? 1.0f : 0.0f;
+#pragma unroll
+    for (int e = 0; e < S::kRange; ++e) {
+        sums[e] += keep0 * o[e % S::kOut][e / S::kOut] +
+                   keep1 * o[e % S::kOut][2 + e / S::kOut];
+    }
+}
+
 template <int N>
 __device__ __forceinline__ void clear(float (&c)[N][4]) {
 #pragma unroll
@@ -372,7 +389,8 @@ attention_warp_backward_kernel(
     const float *__restrict__ dout, float *__restrict__ dq,
     float *__restrict__ dk, float *__restrict__ dv, int seq, float scale,
     bool add_q, bool add_k, bool add_v, HeadLayout in_layout,
-    HeadLayout out_layout, HeadLayout dout_layout, HeadLayout grad_layout) {
+    HeadLayout out_layout, HeadLayout dout_layout, HeadLayout grad_layout,
+    float *__restrict__ column_partials) {
     using S = Shape<HD>;
     __shared__ __align__(16) float q_tile[kTile * S::kPitch];
     __shared__ __align__(16) float k_tile[kTile * S::kPitch];
@@ -391,6 +409,7 @@ attention_warp_backward_kernel(
     // and the O and dO rows behind D_i = dO_i . O_i (in full precision) for
     // this warp's (at most two) row tiles.
     float row_dots[2][2];
+    float sums[3][S::kRange] = {};   // column sums of dQ, dK, dV (this warp's tiles)
     {
         Staged<HD> staged[4];
         stage_load<HD>(staged[0], q + in_base, in_layout.ld, seq);
@@ -474,6 +493,9 @@ attention_warp_backward_kernel(
         product_columns<HD, TILES>(result, ds, k_tile, g, t);
         store_result<HD>(dq + grad_base, grad_layout.ld, r0, r1, seq, t, result,
                          add_q);
+        if (column_partials) {
+            add_column_sums<HD>(sums[0], result, r0, r1, seq);
+        }
     }
     __syncthreads();
     for (int m0 = warp * 16; m0 < seq; m0 += kWarps * 16) {
@@ -498,6 +520,9 @@ attention_warp_backward_kernel(
         product_columns<HD, TILES>(result, p, g_tile, g, t);   // dV = P^T dO
         store_result<HD>(dv + grad_base, grad_layout.ld, r0, r1, seq, t, result,
                          add_v);
+        if (column_partials) {
+            add_column_sums<HD>(sums[2], result, r0, r1, seq);
+        }
         load_range(a0, v_tile + r0 * S::kPitch + t * S::kRange);
         load_range(a1, v_tile + r1 * S::kPitch + t * S::kRange);
         float ds[8][4];
@@ -516,6 +541,56 @@ attention_warp_backward_kernel(
         product_columns<HD, TILES>(result, ds, q_tile, g, t);   // dK = dS^T Q
         store_result<HD>(dk + grad_base, grad_layout.ld, r0, r1, seq, t, result,
                          add_k);
+        if (column_partials) {
+            add_column_sums<HD>(sums[1], result, r0, r1, seq);
+        }
+    }
+    if (column_partials) {
+        // Row `sample` of the partial matrix, in the column order of the
+        // projected gradient: [dQ | dK | dV] x heads x HD.  Warp 1 parks its
+        // sums in shared memory (the operand tiles are no longer needed),
+        // warp 0 adds its own and writes.
+#pragma unroll
+        for (int which = 0; which < 3; ++which) {
+#pragma unroll
+            for (int e = 0; e < S::kRange; ++e) {
+                float v = sums[which][e];
+                v += __shfl_xor_sync(kFullMask, v, 4);
+                v += __shfl_xor_sync(kFullMask, v, 8);
+                v += __shfl_xor_sync(kFullMask, v, 16);
+                sums[which][e] = v;
+            }
+        }
+        __syncthreads();
+        float *parked = q_tile;
+        if (warp == 1 && g == 0) {
+#pragma unroll
+            for (int which = 0; which < 3; ++which) {
+#pragma unroll
+                for (int e = 0; e < S::kRange; ++e) {
+                    parked[which * HD + t * S::kRange + e] = sums[which][e];
+                }
+            }
+        }
+        __syncthreads();
+        if (warp == 0 && g == 0) {
+            const int heads = grad_layout.heads;
+            const size_t d_model = size_t(heads) * HD;
+            float *row = column_partials + (group / heads) * 3 * d_model +
+                         (group % heads) * HD + t * S::kRange;
+#pragma unroll
+            for (int which = 0; which < 3; ++which) {
+#pragma unroll
+                for (int e = 0; e < S::kRange; e += 4) {
+                    float4 v;
+                    v.x = sums[which][e + 0] + parked[which * HD + t * S::kRange + e + 0];
+                    v.y = sums[which][e + 1] + parked[which * HD + t * S::kRange + e + 1];
+                    v.z = sums[which][e + 2] + parked[which * HD + t * S::kRange + e + 2];
+                    v.w = sums[which][e + 3] + parked[which * HD + t * S::kRange + e + 3];
+                    *reinterpret_cast<float4 *>(row + which * d_model + e) = v;
+                }
+            }
+        }
     }
 }
 
@@ -574,7 +649,8 @@ bool launch_attention_warp_backward(const float *q, const float *k,
                                     bool add_k, bool add_v, cudaStream_t stream,
                                     HeadLayout in_layout, HeadLayout out_layout,
                                     HeadLayout dout_layout,
-                                    HeadLayout grad_layout) {
+                                    HeadLayout grad_layout,
+                                    float *column_partials) {
     if (!attention_warp_supported(seq, head_dim)) {
         return false;
     }
@@ -586,7 +662,8 @@ bool launch_attention_warp_backward(const float *q, const float *k,
     attention_warp_backward_kernel<HD, TILES>                                  \
         <<<unsigned(groups), kThreads, 0, stream>>>(                           \
             q, k, v, out, dout, dq, dk, dv, int(seq), scale, add_q, add_k,     \
-            add_v, in_layout, out_layout, dout_layout, grad_layout)
+            add_v, in_layout, out_layout, dout_layout, grad_layout,            \
+            column_partials)
     VITB200_WARP_DISPATCH(head_dim, seq, BACKWARD);
 #undef BACKWARD
     ++g_kernel_launches;

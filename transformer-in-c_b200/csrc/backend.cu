@@ -399,7 +399,8 @@ void run_attention(CudaBackend *backend, const PendingAttention &pending,
 void run_attention_backward(CudaBackend *backend,
                             const PendingAttentionBackward &pending, float *dq,
                             float *dk, float *dv, bool add_q, bool add_k,
-                            bool add_v, HeadLayout grad_layout) {
+                            bool add_v, HeadLayout grad_layout,
+                            float *column_partials = nullptr) {
     OpScope scope(backend, "multi_head_attention_backward", pending.bytes,
                   pending.flops);
     const size_t groups = pending.batch * pending.heads;
@@ -408,7 +409,8 @@ void run_attention_backward(CudaBackend *backend,
             pending.q, pending.k, pending.v, pending.out, pending.dout, dq, dk,
             dv, groups, pending.seq, pending.head_dim, pending.scale, add_q,
             add_k, add_v, backend->stream, pending.in_layout,
-            pending.out_layout, pending.dout_layout, grad_layout);
+            pending.out_layout, pending.dout_layout, grad_layout,
+            column_partials);
     } else {
         launch_attention_small_backward(
             pending.q, pending.k, pending.v, nullptr, pending.out,
@@ -1027,9 +1029,17 @@ int op_split_heads_backward(void *context, vitb200_tensor *projected,
         HeadLayout grad_layout;
         grad_layout.ld = int(3 * d_model);
         grad_layout.heads = int(heads);
+        // The tensor-core kernel also leaves per-sample column sums of what it
+        // writes: the QKV bias gradient the host asks for next
+        // (reference src/vit.c:588-591) then sums [batch, 3d] instead of
+        // [batch * seq, 3d].
+        float *partials = pending.tensor_cores
+            ? scratch<float>(backend, backend->column_partials,
+                             batch * 3 * d_model)
+            : nullptr;
         run_attention_backward(backend, pending, p, p + d_model,
                                p + 2 * d_model, false, false, false,
-                               grad_layout);
+                               grad_layout, partials);
         const vitb200_tensor *parts[3] = {query, key, value};
         for (size_t which = 0; which < 3; ++which) {
             if (!define_head_view(backend, parts[which]->grad, projected->grad,
@@ -1043,6 +1053,10 @@ int op_split_heads_backward(void *context, vitb200_tensor *projected,
             }
         }
         backend->fused_head_layouts += 1;
+        if (partials) {
+            column_memo_commit(backend, p, batch * seq, 3 * d_model, partials,
+                               batch);
+        }
         return 0;
     }
     flush_pending(backend);

@@ -158,7 +158,10 @@ bool launch_attention_small_forward(const float *q, const float *k,
                                     HeadLayout in_layout = HeadLayout(),
                                     HeadLayout out_layout = HeadLayout());
 // Tensor-core kernels for seq <= 64 and head_dim 16 or 32 (TF32 operands); P
-// is neither written nor read.
+// is neither written nor read.  With grad_layout = {3 * d_model, heads} (dq, dk,
+// dv pointing at the three column blocks of the projected gradient),
+// column_partials ([groups / heads, 3 * d_model]) receives per-sample column
+// sums of that gradient: summed over its rows they are the bias gradient.
 bool attention_warp_supported(size_t seq, size_t head_dim);
 bool launch_attention_warp_forward(const float *q, const float *k,
                                    const float *v, float *out, size_t groups,
@@ -175,7 +178,8 @@ bool launch_attention_warp_backward(const float *q, const float *k,
                                     HeadLayout in_layout = HeadLayout(),
                                     HeadLayout out_layout = HeadLayout(),
                                     HeadLayout dout_layout = HeadLayout(),
-                                    HeadLayout grad_layout = HeadLayout());
+                                    HeadLayout grad_layout = HeadLayout(),
+                                    float *column_partials = nullptr);
 // recompute = true: `probabilities` is not read; P is rebuilt from Q and K.
 bool launch_attention_small_backward(const float *q, const float *k,
                                      const float *v, const float *probabilities,

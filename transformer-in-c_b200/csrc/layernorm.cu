@@ -54,11 +54,20 @@ __device__ __forceinline__ void row_statistics(const float4 (&v)[NV],
     inverse_std = 1.0f / sqrtf(variance + epsilon);
 }
 
+// Rows a warp has in flight at a time: with one, a warp's loads (512 B per
+// 128 columns) wait behind its own shuffle reductions and the SM cannot keep
+// enough bytes outstanding to reach the memory rate.
+template <int NV>
+struct RowsInFlight {
+    static constexpr int value = NV <= 2 ? 2 : 1;
+};
+
 template <int NV>
 __global__ void __launch_bounds__(kWarpsPerBlock * 32)
 layer_norm_kernel(const float *__restrict__ x, const float *__restrict__ gamma,
                   const float *__restrict__ beta, float epsilon,
                   float *__restrict__ y, size_t rows, size_t cols) {
+    constexpr int R = RowsInFlight<NV>::value;
     const int lane = threadIdx.x & 31;
     const size_t warp = size_t(blockIdx.x) * kWarpsPerBlock + (threadIdx.x >> 5);
     const size_t warps = size_t(gridDim.x) * kWarpsPerBlock;
@@ -71,21 +80,34 @@ layer_norm_kernel(const float *__restrict__ x, const float *__restrict__ gamma,
             b[j] = __ldg(reinterpret_cast<const float4 *>(beta + col));
         }
     }
-    for (size_t row = warp; row < rows; row += warps) {
-        float4 v[NV];
-        load_row<NV>(x + row * cols, cols, lane, v);
-        float mean, inverse_std;
-        row_statistics<NV>(v, cols, lane, epsilon, mean, inverse_std);
+    for (size_t first = warp; first < rows; first += warps * R) {
+        float4 v[R][NV];
 #pragma unroll
-        for (int j = 0; j < NV; ++j) {
-            const size_t col = size_t(j) * 128 + lane * 4;
-            if (col < cols) {
-                float4 out;
-                out.x = (v[j].x - mean) * inverse_std * g[j].x + b[j].x;
-                out.y = (v[j].y - mean) * inverse_std * g[j].y + b[j].y;
-                out.z = (v[j].z - mean) * inverse_std * g[j].z + b[j].z;
-                out.w = (v[j].w - mean) * inverse_std * g[j].w + b[j].w;
-                *reinterpret_cast<float4 *>(y + row * cols + col) = out;
+        for (int r = 0; r < R; ++r) {
+            const size_t row = first + r * warps;
+            if (row < rows) {
+                load_row<NV>(x + row * cols, cols, lane, v[r]);
+            }
+        }
+#pragma unroll
+        for (int r = 0; r < R; ++r) {
+            const size_t row = first + r * warps;
+            if (row >= rows) {
+                break;
+            }
+            float mean, inverse_std;
+            row_statistics<NV>(v[r], cols, lane, epsilon, mean, inverse_std);
+#pragma unroll
+            for (int j = 0; j < NV; ++j) {
+                const size_t col = size_t(j) * 128 + lane * 4;
+                if (col < cols) {
+                    float4 out;
+                    out.x = (v[r][j].x - mean) * inverse_std * g[j].x + b[j].x;
+                    out.y = (v[r][j].y - mean) * inverse_std * g[j].y + b[j].y;
+                    out.z = (v[r][j].z - mean) * inverse_std * g[j].z + b[j].z;
+                    out.w = (v[r][j].w - mean) * inverse_std * g[j].w + b[j].w;
+                    *reinterpret_cast<float4 *>(y + row * cols + col) = out;
+                }
             }
         }
     }
@@ -115,56 +137,72 @@ layer_norm_backward_kernel(const float *__restrict__ x,
         sum_dx[j] = make_float4(0.f, 0.f, 0.f, 0.f);
     }
     const float inverse_cols = 1.0f / float(cols);
-    for (size_t row = warp; row < rows; row += warps) {
-        float4 v[NV], u[NV];
-        load_row<NV>(x + row * cols, cols, lane, v);
-        load_row<NV>(dy + row * cols, cols, lane, u);
-        float mean, inverse_std;
-        row_statistics<NV>(v, cols, lane, epsilon, mean, inverse_std);
-        float s1 = 0.0f, s2 = 0.0f;
+    constexpr int R = RowsInFlight<NV>::value;
+    for (size_t first = warp; first < rows; first += warps * R) {
+        float4 vs[R][NV], us[R][NV], bases[R][NV];
 #pragma unroll
-        for (int j = 0; j < NV; ++j) {
-            // Out-of-range slots hold x = 0 and dy = 0, so they add nothing.
-            v[j].x = (v[j].x - mean) * inverse_std;
-            v[j].y = (v[j].y - mean) * inverse_std;
-            v[j].z = (v[j].z - mean) * inverse_std;
-            v[j].w = (v[j].w - mean) * inverse_std;
-            sum_gamma[j].x += u[j].x * v[j].x;
-            sum_gamma[j].y += u[j].y * v[j].y;
-            sum_gamma[j].z += u[j].z * v[j].z;
-            sum_gamma[j].w += u[j].w * v[j].w;
-            sum_beta[j].x += u[j].x;
-            sum_beta[j].y += u[j].y;
-            sum_beta[j].z += u[j].z;
-            sum_beta[j].w += u[j].w;
-            u[j].x *= g[j].x;
-            u[j].y *= g[j].y;
-            u[j].z *= g[j].z;
-            u[j].w *= g[j].w;
-            s1 += (u[j].x + u[j].y) + (u[j].z + u[j].w);
-            s2 += (u[j].x * v[j].x + u[j].y * v[j].y) +
-                  (u[j].z * v[j].z + u[j].w * v[j].w);
+        for (int r = 0; r < R; ++r) {
+            const size_t row = first + r * warps;
+            if (row < rows) {
+                load_row<NV>(x + row * cols, cols, lane, vs[r]);
+                load_row<NV>(dy + row * cols, cols, lane, us[r]);
+                if (base) {
+                    load_row<NV>(base + row * cols, cols, lane, bases[r]);
+                }
+            }
         }
-        s1 = warp_sum(s1) * inverse_cols;
-        s2 = warp_sum(s2) * inverse_cols;
 #pragma unroll
-        for (int j = 0; j < NV; ++j) {
-            const size_t col = size_t(j) * 128 + lane * 4;
-            if (col < cols) {
-                float4 *target =
-                    reinterpret_cast<float4 *>(dx + row * cols + col);
-                float4 d = base ? *reinterpret_cast<const float4 *>(
-                                      base + row * cols + col)
-                                : make_float4(0.f, 0.f, 0.f, 0.f);
-                d.x += inverse_std * (u[j].x - s1 - v[j].x * s2);
-                d.y += inverse_std * (u[j].y - s1 - v[j].y * s2);
-                d.z += inverse_std * (u[j].z - s1 - v[j].z * s2);
-                d.w += inverse_std * (u[j].w - s1 - v[j].w * s2);
-                *target = d;
-                sum_dx[j].x += d.x;
-                sum_dx[j].y += d.y;
-                sum_dx[j].z += d.z;
-                sum_dx[j].w += d.w;
+        for (int r = 0; r < R; ++r) {
+            const size_t row = first + r * warps;
+            if (row >= rows) {
+                break;
+            }
+            float4 (&v)[NV] = vs[r];
+            float4 (&u)[NV] = us[r];
+            float mean, inverse_std;
+            row_statistics<NV>(v, cols, lane, epsilon, mean, inverse_std);
+            float s1 = 0.0f, s2 = 0.0f;
+#pragma unroll
+            for (int j = 0; j < NV; ++j) {
+                // Out-of-range slots hold x = 0 and dy = 0, so they add nothing.
+                v[j].x = (v[j].x - mean) * inverse_std;
+                v[j].y = (v[j].y - mean) * inverse_std;
+                v[j].z = (v[j].z - mean) * inverse_std;
+                v[j].w = (v[j].w - mean) * inverse_std;
+                sum_gamma[j].x += u[j].x * v[j].x;
+                sum_gamma[j].y += u[j].y * v[j].y;
+                sum_gamma[j].z += u[j].z * v[j].z;
+                sum_gamma[j].w += u[j].w * v[j].w;
+                sum_beta[j].x += u[j].x;
+                sum_beta[j].y += u[j].y;
+                sum_beta[j].z += u[j].z;
+                sum_beta[j].w += u[j].w;
+                u[j].x *= g[j].x;
+                u[j].y *= g[j].y;
+                u[j].z *= g[j].z;
+                u[j].w *= g[j].w;
+                s1 += (u[j].x + u[j].y) + (u[j].z + u[j].w);
+                s2 += (u[j].x * v[j].x + u[j].y * v[j].y) +
+                      (u[j].z * v[j].z + u[j].w * v[j].w);
+            }
+            s1 = warp_sum(s1) * inverse_cols;
+            s2 = warp_sum(s2) * inverse_cols;
+#pragma unroll
+            for (int j = 0; j < NV; ++j) {
+                const size_t col = size_t(j) * 128 + lane * 4;
+                if (col < cols) {
+                    float4 d = base ? bases[r][j]
+                                    : make_float4(0.f, 0.f, 0.f, 0.f);
+                    d.x += inverse_std * (u[j].x - s1 - v[j].x * s2);
+                    d.y += inverse_std * (u[j].y - s1 - v[j].y * s2);
+                    d.z += inverse_std * (u[j].z - s1 - v[j].z * s2);
+                    d.w += inverse_std * (u[j].w - s1 - v[j].w * s2);
+                    *reinterpret_cast<float4 *>(dx + row * cols + col) = d;
+                    sum_dx[j].x += d.x;
+                    sum_dx[j].y += d.y;
+                    sum_dx[j].z += d.z;
+                    sum_dx[j].w += d.w;
+                }
             }
         }
     }
