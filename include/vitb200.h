@@ -187,6 +187,22 @@ int vitb200_k_attention(const float *q, const float *k, const float *v,
                         float *probabilities, float *out, size_t groups,
                         size_t seq, size_t head_dim, float scale, int precision,
                         void *stream);
+/* Flash attention on tensor cores (TF32 operands) for any sequence length and
+ * head_dim 16, 32 or 64: P is never materialised.  The forward pass leaves
+ * each row's log-sum-exp in `lse` (groups*seq floats, an opaque input of the
+ * backward pass); row_dots is scratch of the same size.  The backward pass
+ * adds into dq, dk, dv.  -1 if head_dim has no such kernel. */
+int vitb200_k_attention_stream(const float *q, const float *k, const float *v,
+                               float *out, float *lse, size_t groups,
+                               size_t seq, size_t head_dim, float scale,
+                               void *stream);
+int vitb200_k_attention_stream_backward(const float *q, const float *k,
+                                        const float *v, const float *out,
+                                        const float *dout, const float *lse,
+                                        float *dq, float *dk, float *dv,
+                                        float *row_dots, size_t groups,
+                                        size_t seq, size_t head_dim, float scale,
+                                        void *stream);
 /* row_dots: scratch, groups*seq floats. */
 int vitb200_k_attention_backward(const float *q, const float *k, const float *v,
                                  const float *probabilities, const float *out,

@@ -264,6 +264,53 @@ def test_attention_without_probability_matrix(lib, groups, seq, hd, precision):
     close(host(tdv), dv0 + dv, backward_tol)
 
 
+@pytest.mark.parametrize("groups,seq,hd", [
+    (2, 197, 32), (3, 197, 64), (1, 1025, 64), (2, 64, 16), (2, 65, 16),
+    (4, 50, 32), (1, 1, 16), (2, 130, 64), (5, 300, 16),
+])
+def test_streaming_attention(lib, groups, seq, hd):
+    """Flash attention with every tile in registers (TF32): forward, saved
+    log-sum-exp, and the two backward kernels, against the float64 oracle."""
+    rng = np.random.RandomState(groups * seq + hd + 2)
+    rows = groups * seq
+    q, k, v, dout = (rng.randn(rows, hd) for _ in range(4))
+    dq0, dk0, dv0 = (rng.randn(rows, hd) for _ in range(3))
+    scale = 1.0 / np.sqrt(hd)
+    tq, tk, tv, tdo = dev(q), dev(k), dev(v), dev(dout)
+    to = torch.empty(rows, hd, device="cuda")
+    lse = torch.empty(rows, device="cuda")
+    dots = torch.empty(rows, device="cuda")
+    tdq, tdk, tdv = dev(dq0), dev(dk0), dev(dv0)
+    assert lib.vitb200_k_attention_stream(
+        ptr(tq), ptr(tk), ptr(tv), ptr(to), ptr(lse), size(groups), size(seq),
+        size(hd), ctypes.c_float(scale), None) == 0
+    assert lib.vitb200_k_attention_stream_backward(
+        ptr(tq), ptr(tk), ptr(tv), ptr(to), ptr(tdo), ptr(lse), ptr(tdq),
+        ptr(tdk), ptr(tdv), ptr(dots), size(groups), size(seq), size(hd),
+        ctypes.c_float(scale), None) == 0
+    p, o = vo.multi_head_attention(q, k, v, groups, seq, scale)
+    close(host(to), o, 2e-3)
+    # Row log-sum-exp of the scaled scores, in base 2.
+    scores = np.einsum("gid,gjd->gij", q.reshape(groups, seq, hd),
+                       k.reshape(groups, seq, hd)) * scale
+    expected_lse = (np.log(np.exp(scores - scores.max(-1, keepdims=True)).sum(-1))
+                    + scores.max(-1)) / np.log(2.0)
+    np.testing.assert_allclose(host(lse).reshape(groups, seq), expected_lse,
+                               rtol=0, atol=5e-3)
+    dq, dk, dv = vo.multi_head_attention_backward(q, k, v, p, dout, groups,
+                                                  seq, scale)
+    close(host(tdq), dq0 + dq, 2e-3)
+    close(host(tdk), dk0 + dk, 2e-3)
+    close(host(tdv), dv0 + dv, 2e-3)
+
+
+def test_streaming_attention_rejects_other_head_dims(lib):
+    dummy = torch.zeros(1, device="cuda")
+    assert lib.vitb200_k_attention_stream(
+        ptr(dummy), ptr(dummy), ptr(dummy), ptr(dummy), ptr(dummy), size(1),
+        size(1), size(8), ctypes.c_float(1.0), None) == -1
+
+
 def test_attention_without_probability_matrix_rejects_long_sequences(lib):
     dummy = torch.zeros(1, device="cuda")
     for precision, seq in ((FP32, 129), (TF32, 65)):

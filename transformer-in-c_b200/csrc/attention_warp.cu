@@ -114,19 +114,19 @@ __device__ __forceinline__ void load_range_global(float (&x)[N],
 // it waits for any of them: the groups are small, and with one load
 // outstanding per thread the kernel would be bound by memory latency.  Values
 // are stored rounded to TF32; rows past `seq` are zero.
-template <int HD>
+template <int HD, int THREADS = kThreads>
 struct Staged {
-    float4 value[kTile * (HD / 4) / kThreads];
+    float4 value[kTile * (HD / 4) / THREADS];
 };
 
-template <int HD>
-__device__ __forceinline__ void stage_load(Staged<HD> &staged,
+template <int HD, int THREADS = kThreads>
+__device__ __forceinline__ void stage_load(Staged<HD, THREADS> &staged,
                                            const float *__restrict__ source,
                                            int ld, int seq) {
     constexpr int kVectors = HD / 4;
 #pragma unroll
-    for (int j = 0; j < kTile * kVectors / kThreads; ++j) {
-        const int i = threadIdx.x + j * kThreads;
+    for (int j = 0; j < kTile * kVectors / THREADS; ++j) {
+        const int i = threadIdx.x + j * THREADS;
         const int r = i / kVectors;
         const int c = (i % kVectors) * 4;
         staged.value[j] = make_float4(0.f, 0.f, 0.f, 0.f);
@@ -137,13 +137,13 @@ __device__ __forceinline__ void stage_load(Staged<HD> &staged,
     }
 }
 
-template <int HD>
-__device__ __forceinline__ void stage_store(const Staged<HD> &staged,
+template <int HD, int THREADS = kThreads>
+__device__ __forceinline__ void stage_store(const Staged<HD, THREADS> &staged,
                                             float *tile) {
     constexpr int kVectors = HD / 4;
 #pragma unroll
-    for (int j = 0; j < kTile * kVectors / kThreads; ++j) {
-        const int i = threadIdx.x + j * kThreads;
+    for (int j = 0; j < kTile * kVectors / THREADS; ++j) {
+        const int i = threadIdx.x + j * THREADS;
         const int r = i / kVectors;
         const int c = (i % kVectors) * 4;
         const float4 v = staged.value[j];
@@ -594,6 +594,304 @@ attention_warp_backward_kernel(
     }
 }
 
+// ---------------------------------------------------------------------------
+// Any sequence length: the same register-resident products, streamed over
+// 64-row tiles of the other axis (flash attention).  A block of four warps owns
+// 64 rows (a warp 16); the tiles it sweeps are staged in shared memory by all
+// four warps.  The forward pass keeps a running maximum and denominator per
+// row and saves the row's log-sum-exp (base 2, of the scaled scores); the two
+// backward kernels rebuild P tiles from it.
+//
+//   forward        per query tile: for key tiles: S, online softmax, O += P V
+//   backward rows  per query tile: D = dO.O (saved, pre-multiplied by -scale);
+//                  for key tiles: P, dP = dO V^T, dS, dQ += dS K
+//   backward cols  per key tile: for query tiles: P^T = f(K Q^T, lse),
+//                  dV += P^T dO, dP^T = V dO^T, dS^T, dK += dS^T Q
+constexpr int kStreamWarps = 4;
+constexpr int kStreamBlock = kStreamWarps * 32;
+
+// Masks the columns of a 16 x 64 score tile set that lie at or past `limit`
+// (columns are counted from the tile's first key).
+__device__ __forceinline__ void mask_columns(float (&s)[8][4], int limit, int t) {
+#pragma unroll
+    for (int n = 0; n < 8; ++n) {
+        if (n * 8 + 8 > limit) {
+#pragma unroll
+            for (int e = 0; e < 4; ++e) {
+                if (n * 8 + 2 * t + (e & 1) >= limit) {
+                    s[n][e] = -FLT_MAX;
+                }
+            }
+        }
+    }
+}
+
+template <int HD>
+__global__ void __launch_bounds__(kStreamBlock)
+attention_stream_forward_kernel(const float *__restrict__ q,
+                                const float *__restrict__ k,
+                                const float *__restrict__ v,
+                                float *__restrict__ out,
+                                float *__restrict__ lse, int seq, float scale,
+                                HeadLayout in_layout, HeadLayout out_layout) {
+    using S = Shape<HD>;
+    __shared__ __align__(16) float k_tile[kTile * S::kPitch];
+    __shared__ __align__(16) float v_tile[kTile * S::kPitch];
+    const size_t group = blockIdx.x;
+    const size_t base = group_offset<HD>(group, seq, in_layout);
+    const int ld = in_layout.ld;
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const int g = lane >> 2, t = lane & 3;
+    const int r0 = blockIdx.y * kTile + warp * 16 + g, r1 = r0 + 8;
+    const float scale2 = scale * kLog2e;
+    float a0[S::kRange], a1[S::kRange];
+    load_range_global(a0, q + base + size_t(min(r0, seq - 1)) * ld + t * S::kRange, true);
+    load_range_global(a1, q + base + size_t(min(r1, seq - 1)) * ld + t * S::kRange, true);
+    float max_a = -FLT_MAX, max_b = -FLT_MAX;   // running maxima of raw scores
+    float sum_a = 0.0f, sum_b = 0.0f;           // this lane's share of the denominators
+    float o[S::kOut][4];
+    clear(o);
+    for (int k0 = 0; k0 < seq; k0 += kTile) {
+        __syncthreads();   // the previous tiles have been consumed
+        {
+            Staged<HD, kStreamBlock> k_staged, v_staged;
+            stage_load<HD, kStreamBlock>(k_staged, k + base + size_t(k0) * ld, ld, seq - k0);
+            stage_load<HD, kStreamBlock>(v_staged, v + base + size_t(k0) * ld, ld, seq - k0);
+            stage_store<HD, kStreamBlock>(k_staged, k_tile);
+            stage_store<HD, kStreamBlock>(v_staged, v_tile);
+        }
+        __syncthreads();
+        float p[8][4];
+        clear(p);
+        product_rows<HD, 8>(p, a0, a1, k_tile, g, t);
+        if (k0 + kTile > seq) {
+            mask_columns(p, seq - k0, t);
+        }
+        float tile_a = -FLT_MAX, tile_b = -FLT_MAX;
+#pragma unroll
+        for (int n = 0; n < 8; ++n) {
+            tile_a = fmaxf(tile_a, fmaxf(p[n][0], p[n][1]));
+            tile_b = fmaxf(tile_b, fmaxf(p[n][2], p[n][3]));
+        }
+        const float new_a = fmaxf(max_a, quad_max(tile_a));
+        const float new_b = fmaxf(max_b, quad_max(tile_b));
+        // Rescale what has been accumulated under the old maximum (the first
+        // tile multiplies zeros by exp2(-inf) = 0).
+        const float alpha_a = exp2_fast((max_a - new_a) * scale2);
+        const float alpha_b = exp2_fast((max_b - new_b) * scale2);
+        const float shift_a = -new_a * scale2, shift_b = -new_b * scale2;
+        max_a = new_a;
+        max_b = new_b;
+        float part_a = 0.0f, part_b = 0.0f;
+#pragma unroll
+        for (int n = 0; n < 8; ++n) {
+            p[n][0] = exp2_fast(fmaf(p[n][0], scale2, shift_a));
+            p[n][1] = exp2_fast(fmaf(p[n][1], scale2, shift_a));
+            p[n][2] = exp2_fast(fmaf(p[n][2], scale2, shift_b));
+            p[n][3] = exp2_fast(fmaf(p[n][3], scale2, shift_b));
+            part_a += p[n][0] + p[n][1];
+            part_b += p[n][2] + p[n][3];
+        }
+        sum_a = fmaf(sum_a, alpha_a, part_a);
+        sum_b = fmaf(sum_b, alpha_b, part_b);
+#pragma unroll
+        for (int u = 0; u < S::kOut; ++u) {
+            o[u][0] *= alpha_a;
+            o[u][1] *= alpha_a;
+            o[u][2] *= alpha_b;
+            o[u][3] *= alpha_b;
+        }
+        product_columns<HD, 8>(o, p, v_tile, g, t);
+    }
+    sum_a = quad_sum(sum_a);
+    sum_b = quad_sum(sum_b);
+    const float inverse_a = 1.0f / sum_a, inverse_b = 1.0f / sum_b;
+#pragma unroll
+    for (int u = 0; u < S::kOut; ++u) {
+        o[u][0] *= inverse_a;
+        o[u][1] *= inverse_a;
+        o[u][2] *= inverse_b;
+        o[u][3] *= inverse_b;
+    }
+    store_result<HD>(out + group_offset<HD>(group, seq, out_layout),
+                     out_layout.ld, r0, r1, seq, t, o, false);
+    if (t == 0) {
+        if (r0 < seq) {
+            lse[group * seq + r0] = max_a * scale2 + log2f(sum_a);
+        }
+        if (r1 < seq) {
+            lse[group * seq + r1] = max_b * scale2 + log2f(sum_b);
+        }
+    }
+}
+
+// dQ, and D_i = dO_i . O_i saved as -scale * D_i for the column kernel.
+template <int HD>
+__global__ void __launch_bounds__(kStreamBlock)
+attention_stream_backward_rows_kernel(
+    const float *__restrict__ q, const float *__restrict__ k,
+    const float *__restrict__ v, const float *__restrict__ out,
+    const float *__restrict__ dout, const float *__restrict__ lse,
+    float *__restrict__ dq, float *__restrict__ row_dots, int seq, float scale,
+    bool add_q, HeadLayout in_layout, HeadLayout out_layout,
+    HeadLayout dout_layout, HeadLayout grad_layout) {
+    using S = Shape<HD>;
+    __shared__ __align__(16) float k_tile[kTile * S::kPitch];
+    __shared__ __align__(16) float v_tile[kTile * S::kPitch];
+    const size_t group = blockIdx.x;
+    const size_t base = group_offset<HD>(group, seq, in_layout);
+    const int ld = in_layout.ld;
+    const float *out_base = out + group_offset<HD>(group, seq, out_layout);
+    const float *dout_base = dout + group_offset<HD>(group, seq, dout_layout);
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const int g = lane >> 2, t = lane & 3;
+    const int r0 = blockIdx.y * kTile + warp * 16 + g, r1 = r0 + 8;
+    const int safe0 = min(r0, seq - 1), safe1 = min(r1, seq - 1);
+    const float scale2 = scale * kLog2e;
+    float qa[S::kRange], qb[S::kRange], ga[S::kRange], gb[S::kRange];
+    float offset_a, offset_b;   // -scale * D
+    {
+        float oa[S::kRange], ob[S::kRange];
+        load_range_global(qa, q + base + size_t(safe0) * ld + t * S::kRange, true);
+        load_range_global(qb, q + base + size_t(safe1) * ld + t * S::kRange, true);
+        load_range_global(ga, dout_base + size_t(safe0) * dout_layout.ld + t * S::kRange, false);
+        load_range_global(gb, dout_base + size_t(safe1) * dout_layout.ld + t * S::kRange, false);
+        load_range_global(oa, out_base + size_t(safe0) * out_layout.ld + t * S::kRange, false);
+        load_range_global(ob, out_base + size_t(safe1) * out_layout.ld + t * S::kRange, false);
+        float dot_a = 0.0f, dot_b = 0.0f;
+#pragma unroll
+        for (int e = 0; e < S::kRange; ++e) {
+            dot_a = fmaf(oa[e], ga[e], dot_a);
+            dot_b = fmaf(ob[e], gb[e], dot_b);
+            ga[e] = to_tf32(ga[e]);
+            gb[e] = to_tf32(gb[e]);
+        }
+        offset_a = -scale * quad_sum(dot_a);
+        offset_b = -scale * quad_sum(dot_b);
+        if (t == 0) {
+            if (r0 < seq) {
+                row_dots[group * seq + r0] = offset_a;
+            }
+            if (r1 < seq) {
+                row_dots[group * seq + r1] = offset_b;
+            }
+        }
+    }
+    const float lse_a = lse[group * seq + safe0], lse_b = lse[group * seq + safe1];
+    float result[S::kOut][4];
+    clear(result);
+    for (int k0 = 0; k0 < seq; k0 += kTile) {
+        __syncthreads();
+        {
+            Staged<HD, kStreamBlock> k_staged, v_staged;
+            stage_load<HD, kStreamBlock>(k_staged, k + base + size_t(k0) * ld, ld, seq - k0);
+            stage_load<HD, kStreamBlock>(v_staged, v + base + size_t(k0) * ld, ld, seq - k0);
+            stage_store<HD, kStreamBlock>(k_staged, k_tile);
+            stage_store<HD, kStreamBlock>(v_staged, v_tile);
+        }
+        __syncthreads();
+        float p[8][4];
+        clear(p);
+        product_rows<HD, 8>(p, qa, qb, k_tile, g, t);
+        if (k0 + kTile > seq) {
+            mask_columns(p, seq - k0, t);   // -FLT_MAX: exp2 gives 0 below
+        }
+        float ds[8][4];
+        clear(ds);
+        product_rows<HD, 8>(ds, ga, gb, v_tile, g, t);
+#pragma unroll
+        for (int n = 0; n < 8; ++n) {
+            ds[n][0] = exp2_fast(fmaf(p[n][0], scale2, -lse_a)) * fmaf(ds[n][0], scale, offset_a);
+            ds[n][1] = exp2_fast(fmaf(p[n][1], scale2, -lse_a)) * fmaf(ds[n][1], scale, offset_a);
+            ds[n][2] = exp2_fast(fmaf(p[n][2], scale2, -lse_b)) * fmaf(ds[n][2], scale, offset_b);
+            ds[n][3] = exp2_fast(fmaf(p[n][3], scale2, -lse_b)) * fmaf(ds[n][3], scale, offset_b);
+        }
+        product_columns<HD, 8>(result, ds, k_tile, g, t);
+    }
+    store_result<HD>(dq + group_offset<HD>(group, seq, grad_layout),
+                     grad_layout.ld, r0, r1, seq, t, result, add_q);
+}
+
+// dK and dV for a tile of keys, sweeping the queries.
+template <int HD>
+__global__ void __launch_bounds__(kStreamBlock)
+attention_stream_backward_columns_kernel(
+    const float *__restrict__ q, const float *__restrict__ k,
+    const float *__restrict__ v, const float *__restrict__ dout,
+    const float *__restrict__ lse, const float *__restrict__ row_dots,
+    float *__restrict__ dk, float *__restrict__ dv, int seq, float scale,
+    bool add_k, bool add_v, HeadLayout in_layout, HeadLayout dout_layout,
+    HeadLayout grad_layout) {
+    using S = Shape<HD>;
+    __shared__ __align__(16) float q_tile[kTile * S::kPitch];
+    __shared__ __align__(16) float g_tile[kTile * S::kPitch];
+    __shared__ __align__(8) float tile_lse[kTile];
+    __shared__ __align__(8) float tile_dot[kTile];
+    const size_t group = blockIdx.x;
+    const size_t base = group_offset<HD>(group, seq, in_layout);
+    const int ld = in_layout.ld;
+    const float *dout_base = dout + group_offset<HD>(group, seq, dout_layout);
+    const size_t grad_base = group_offset<HD>(group, seq, grad_layout);
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const int g = lane >> 2, t = lane & 3;
+    const int r0 = blockIdx.y * kTile + warp * 16 + g, r1 = r0 + 8;   // keys
+    const int safe0 = min(r0, seq - 1), safe1 = min(r1, seq - 1);
+    const float scale2 = scale * kLog2e;
+    float ka[S::kRange], kb[S::kRange], va[S::kRange], vb[S::kRange];
+    load_range_global(ka, k + base + size_t(safe0) * ld + t * S::kRange, true);
+    load_range_global(kb, k + base + size_t(safe1) * ld + t * S::kRange, true);
+    load_range_global(va, v + base + size_t(safe0) * ld + t * S::kRange, true);
+    load_range_global(vb, v + base + size_t(safe1) * ld + t * S::kRange, true);
+    float dk_acc[S::kOut][4], dv_acc[S::kOut][4];
+    clear(dk_acc);
+    clear(dv_acc);
+    for (int q0 = 0; q0 < seq; q0 += kTile) {
+        __syncthreads();
+        {
+            Staged<HD, kStreamBlock> q_staged, g_staged;
+            stage_load<HD, kStreamBlock>(q_staged, q + base + size_t(q0) * ld, ld, seq - q0);
+            stage_load<HD, kStreamBlock>(g_staged, dout_base + size_t(q0) * dout_layout.ld,
+                                         dout_layout.ld, seq - q0);
+            if (threadIdx.x < kTile) {
+                // Queries past the end: an infinite log-sum-exp makes their
+                // column of P^T vanish.
+                const int row = q0 + threadIdx.x;
+                tile_lse[threadIdx.x] = row < seq ? lse[group * seq + row] : FLT_MAX;
+                tile_dot[threadIdx.x] = row < seq ? row_dots[group * seq + row] : 0.0f;
+            }
+            stage_store<HD, kStreamBlock>(q_staged, q_tile);
+            stage_store<HD, kStreamBlock>(g_staged, g_tile);
+        }
+        __syncthreads();
+        float p[8][4];
+        clear(p);
+        product_rows<HD, 8>(p, ka, kb, q_tile, g, t);   // S^T
+#pragma unroll
+        for (int n = 0; n < 8; ++n) {
+            const float2 l = *reinterpret_cast<const float2 *>(tile_lse + n * 8 + 2 * t);
+            p[n][0] = exp2_fast(fmaf(p[n][0], scale2, -l.x));
+            p[n][1] = exp2_fast(fmaf(p[n][1], scale2, -l.y));
+            p[n][2] = exp2_fast(fmaf(p[n][2], scale2, -l.x));
+            p[n][3] = exp2_fast(fmaf(p[n][3], scale2, -l.y));
+        }
+        product_columns<HD, 8>(dv_acc, p, g_tile, g, t);   // dV += P^T dO
+        float ds[8][4];
+        clear(ds);
+        product_rows<HD, 8>(ds, va, vb, g_tile, g, t);   // dP^T = V dO^T
+#pragma unroll
+        for (int n = 0; n < 8; ++n) {
+            const float2 d = *reinterpret_cast<const float2 *>(tile_dot + n * 8 + 2 * t);
+            ds[n][0] = p[n][0] * fmaf(ds[n][0], scale, d.x);
+            ds[n][1] = p[n][1] * fmaf(ds[n][1], scale, d.y);
+            ds[n][2] = p[n][2] * fmaf(ds[n][2], scale, d.x);
+            ds[n][3] = p[n][3] * fmaf(ds[n][3], scale, d.y);
+        }
+        product_columns<HD, 8>(dk_acc, ds, q_tile, g, t);   // dK += dS^T Q
+    }
+    store_result<HD>(dv + grad_base, grad_layout.ld, r0, r1, seq, t, dv_acc, add_v);
+    store_result<HD>(dk + grad_base, grad_layout.ld, r0, r1, seq, t, dk_acc, add_k);
+}
+
 HeadLayout resolve(HeadLayout layout, size_t head_dim) {
     return layout.ld ? layout : HeadLayout{int(head_dim), 1};
 }
@@ -667,6 +965,72 @@ bool launch_attention_warp_backward(const float *q, const float *k,
     VITB200_WARP_DISPATCH(head_dim, seq, BACKWARD);
 #undef BACKWARD
     ++g_kernel_launches;
+    return true;
+}
+
+bool attention_stream_supported(size_t head_dim) {
+    return head_dim == 16 || head_dim == 32 || head_dim == 64;
+}
+
+#define VITB200_STREAM_DISPATCH(head_dim, CALL)                                \
+    do {                                                                       \
+        if (head_dim == 16) { CALL(16); }                                      \
+        else if (head_dim == 32) { CALL(32); }                                 \
+        else { CALL(64); }                                                     \
+    } while (0)
+
+bool launch_attention_stream_forward(const float *q, const float *k,
+                                     const float *v, float *out, float *lse,
+                                     size_t groups, size_t seq, size_t head_dim,
+                                     float scale, cudaStream_t stream,
+                                     HeadLayout in_layout,
+                                     HeadLayout out_layout) {
+    if (!attention_stream_supported(head_dim) || seq == 0) {
+        return false;
+    }
+    in_layout = resolve(in_layout, head_dim);
+    out_layout = resolve(out_layout, head_dim);
+    const dim3 grid(unsigned(groups), unsigned((seq + kTile - 1) / kTile));
+#define FORWARD(HD)                                                            \
+    attention_stream_forward_kernel<HD><<<grid, kStreamBlock, 0, stream>>>(    \
+        q, k, v, out, lse, int(seq), scale, in_layout, out_layout)
+    VITB200_STREAM_DISPATCH(head_dim, FORWARD);
+#undef FORWARD
+    ++g_kernel_launches;
+    return true;
+}
+
+bool launch_attention_stream_backward(const float *q, const float *k,
+                                      const float *v, const float *out,
+                                      const float *dout, const float *lse,
+                                      float *dq, float *dk, float *dv,
+                                      float *row_dots, size_t groups, size_t seq,
+                                      size_t head_dim, float scale, bool add_q,
+                                      bool add_k, bool add_v,
+                                      cudaStream_t stream, HeadLayout in_layout,
+                                      HeadLayout out_layout,
+                                      HeadLayout dout_layout,
+                                      HeadLayout grad_layout) {
+    if (!attention_stream_supported(head_dim) || seq == 0) {
+        return false;
+    }
+    in_layout = resolve(in_layout, head_dim);
+    out_layout = resolve(out_layout, head_dim);
+    dout_layout = resolve(dout_layout, head_dim);
+    grad_layout = resolve(grad_layout, head_dim);
+    const dim3 grid(unsigned(groups), unsigned((seq + kTile - 1) / kTile));
+#define BACKWARD(HD)                                                           \
+    attention_stream_backward_rows_kernel<HD>                                  \
+        <<<grid, kStreamBlock, 0, stream>>>(                                   \
+            q, k, v, out, dout, lse, dq, row_dots, int(seq), scale, add_q,     \
+            in_layout, out_layout, dout_layout, grad_layout);                  \
+    attention_stream_backward_columns_kernel<HD>                               \
+        <<<grid, kStreamBlock, 0, stream>>>(                                   \
+            q, k, v, dout, lse, row_dots, dk, dv, int(seq), scale, add_k,      \
+            add_v, in_layout, dout_layout, grad_layout)
+    VITB200_STREAM_DISPATCH(head_dim, BACKWARD);
+#undef BACKWARD
+    g_kernel_launches += 2;
     return true;
 }
 

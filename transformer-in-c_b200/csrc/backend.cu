@@ -170,6 +170,7 @@ struct CudaBackend {
     // Row log-sum-exp of flash attention, one buffer per probability tensor
     // (keyed by the tensor's host address), kept from forward to backward.
     std::unordered_map<const void *, Scratch> lse_buffers;
+    std::unordered_map<const void *, bool> lse_streamed;
     unsigned long long fused_epilogues = 0;
     void (*set_table)(const vitb200_op_table *) = nullptr;
     void (*set_allocator)(vitb200_allocate_fn, vitb200_release_fn,
@@ -1271,6 +1272,16 @@ int op_attention(void *context, const vitb200_tensor *query,
                                  sizeof(definition), backend->stream)) {
             OpScope scope(backend, "multi_head_attention",
                           16.0 * double(numel(query)), flops);
+            // The register-resident streaming kernels where they exist
+            // (head_dim 16, 32, 64); the two families keep different
+            // log-sum-exp conventions, remembered per tensor.
+            if (launch_attention_stream_forward(q, k, v, o, lse, groups, seq,
+                                                head_dim, scale,
+                                                backend->stream)) {
+                backend->lse_streamed[probabilities->data] = true;
+                return 0;
+            }
+            backend->lse_streamed[probabilities->data] = false;
             if (launch_attention_mma_flash_forward(q, k, v, o, lse, groups, seq,
                                                    head_dim, scale,
                                                    backend->stream)) {
@@ -1378,7 +1389,12 @@ int op_attention_backward(void *context, const vitb200_tensor *query,
     float *dv = accumulate_view(backend, value_grad->grad, &add_v);
     {
         OpScope scope(backend, "multi_head_attention_backward", bytes, flops);
-        if (lse) {
+        if (lse && backend->lse_streamed[probabilities->data]) {
+            launch_attention_stream_backward(q, k, v, o, go, lse, dq, dk, dv,
+                                             dots, groups, seq, head_dim, scale,
+                                             add_q, add_k, add_v,
+                                             backend->stream);
+        } else if (lse) {
             launch_attention_mma_backward(q, k, v, nullptr, lse, o, go, dq, dk,
                                           dv, dots, groups, seq, head_dim,
                                           scale, add_q, add_k, add_v,
@@ -2358,6 +2374,34 @@ extern "C" int vitb200_k_attention(const float *q, const float *k,
     launch_attention_forward(q, k, v, probabilities, out, groups, seq, head_dim,
                              scale, precision, as_stream(stream));
     return 0;
+}
+
+extern "C" int vitb200_k_attention_stream(const float *q, const float *k,
+                                          const float *v, float *out,
+                                          float *lse, size_t groups, size_t seq,
+                                          size_t head_dim, float scale,
+                                          void *stream) {
+    if (!fits_int(seq) || !fits_int(groups)) {
+        return -1;
+    }
+    return launch_attention_stream_forward(q, k, v, out, lse, groups, seq,
+                                           head_dim, scale, as_stream(stream))
+        ? 0 : -1;
+}
+
+extern "C" int vitb200_k_attention_stream_backward(
+    const float *q, const float *k, const float *v, const float *out,
+    const float *dout, const float *lse, float *dq, float *dk, float *dv,
+    float *row_dots, size_t groups, size_t seq, size_t head_dim, float scale,
+    void *stream) {
+    if (!fits_int(seq) || !fits_int(groups)) {
+        return -1;
+    }
+    return launch_attention_stream_backward(q, k, v, out, dout, lse, dq, dk, dv,
+                                            row_dots, groups, seq, head_dim,
+                                            scale, true, true, true,
+                                            as_stream(stream))
+        ? 0 : -1;
 }
 
 extern "C" int vitb200_k_attention_backward(

@@ -180,6 +180,29 @@ bool launch_attention_warp_backward(const float *q, const float *k,
                                     HeadLayout dout_layout = HeadLayout(),
                                     HeadLayout grad_layout = HeadLayout(),
                                     float *column_partials = nullptr);
+// The same register-resident products streamed over 64-row tiles, for any
+// sequence length and head_dim 16, 32 or 64.  The forward pass saves each
+// row's log-sum-exp (base 2, of the scaled scores; groups * seq floats) for
+// the backward pass, which also wants groups * seq floats of scratch.
+bool attention_stream_supported(size_t head_dim);
+bool launch_attention_stream_forward(const float *q, const float *k,
+                                     const float *v, float *out, float *lse,
+                                     size_t groups, size_t seq, size_t head_dim,
+                                     float scale, cudaStream_t stream,
+                                     HeadLayout in_layout = HeadLayout(),
+                                     HeadLayout out_layout = HeadLayout());
+bool launch_attention_stream_backward(const float *q, const float *k,
+                                      const float *v, const float *out,
+                                      const float *dout, const float *lse,
+                                      float *dq, float *dk, float *dv,
+                                      float *row_dots, size_t groups, size_t seq,
+                                      size_t head_dim, float scale, bool add_q,
+                                      bool add_k, bool add_v,
+                                      cudaStream_t stream,
+                                      HeadLayout in_layout = HeadLayout(),
+                                      HeadLayout out_layout = HeadLayout(),
+                                      HeadLayout dout_layout = HeadLayout(),
+                                      HeadLayout grad_layout = HeadLayout());
 // recompute = true: `probabilities` is not read; P is rebuilt from Q and K.
 bool launch_attention_small_backward(const float *q, const float *k,
                                      const float *v, const float *probabilities,
