@@ -161,15 +161,18 @@ __device__ __forceinline__ size_t group_offset(size_t group, int seq,
 
 // c[16 x 64] += A B^T: A = rows (a0, a1) given as lane ranges, B = a staged
 // tile whose rows are the result's columns.
-template <int HD, int TILES>
+// `live` (< TILES) restricts the work to the first `live` 8-row groups of the
+// tile when kPartial is set (the last tile of a streamed axis).
+template <int HD, int TILES, bool kPartial = false>
 __device__ __forceinline__ void product_rows(float (&c)[8][4],
                                              const float (&a0)[HD / 4],
                                              const float (&a1)[HD / 4],
-                                             const float *tile, int g, int t) {
+                                             const float *tile, int g, int t,
+                                             int live = TILES) {
     using S = Shape<HD>;
 #pragma unroll
     for (int n = 0; n < TILES; ++n) {
-        {
+        if (!kPartial || n < live) {
             float b[S::kRange];
             load_range(b, tile + (n * 8 + g) * S::kPitch + t * S::kRange);
 #pragma unroll
@@ -185,15 +188,15 @@ __device__ __forceinline__ void product_rows(float (&c)[8][4],
 // (columns 2t, 2t+1 of tile s), B = a staged tile whose rows are the
 // contraction index.  Result element e of the lane's row range is
 // o[e % kOut][e / kOut] (row g) and o[e % kOut][2 + e / kOut] (row g + 8).
-template <int HD, int TILES>
+template <int HD, int TILES, bool kPartial = false>
 __device__ __forceinline__ void product_columns(float (&o)[HD / 8][4],
                                                 const float (&p)[8][4],
                                                 const float *tile, int g,
-                                                int t) {
+                                                int t, int live = TILES) {
     using S = Shape<HD>;
 #pragma unroll
     for (int s = 0; s < TILES; ++s) {
-        {
+        if (!kPartial || s < live) {
             float b0[S::kOut < 4 ? 4 : S::kOut], b1[S::kOut < 4 ? 4 : S::kOut];
             const float *row = tile + (s * 8 + 2 * t) * S::kPitch + g * S::kOut;
             if (S::kOut == 2) {
@@ -637,12 +640,17 @@ attention_stream_forward_kernel(const float *__restrict__ q,
     using S = Shape<HD>;
     __shared__ __align__(16) float k_tile[kTile * S::kPitch];
     __shared__ __align__(16) float v_tile[kTile * S::kPitch];
-    const size_t group = blockIdx.x;
+    // Blocks of one group are neighbours in launch order, so that the K / V
+    // tiles they all sweep stay in L2.
+    const int row_tiles = (seq + kTile - 1) / kTile;
+    const size_t group = blockIdx.x / row_tiles;
+    const int row_tile = blockIdx.x % row_tiles;
     const size_t base = group_offset<HD>(group, seq, in_layout);
     const int ld = in_layout.ld;
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     const int g = lane >> 2, t = lane & 3;
-    const int r0 = blockIdx.y * kTile + warp * 16 + g, r1 = r0 + 8;
+    const int r0 = row_tile * kTile + warp * 16 + g, r1 = r0 + 8;
+    const bool live_warp = row_tile * kTile + warp * 16 < seq;   // else: staging only
     const float scale2 = scale * kLog2e;
     float a0[S::kRange], a1[S::kRange];
     load_range_global(a0, q + base + size_t(min(r0, seq - 1)) * ld + t * S::kRange, true);
@@ -661,9 +669,17 @@ attention_stream_forward_kernel(const float *__restrict__ q,
             stage_store<HD, kStreamBlock>(v_staged, v_tile);
         }
         __syncthreads();
+        if (!live_warp) {
+            continue;
+        }
+        const int live = (min(kTile, seq - k0) + 7) / 8;   // 8-key groups in this tile
         float p[8][4];
         clear(p);
-        product_rows<HD, 8>(p, a0, a1, k_tile, g, t);
+        if (live == 8) {
+            product_rows<HD, 8>(p, a0, a1, k_tile, g, t);
+        } else {
+            product_rows<HD, 8, true>(p, a0, a1, k_tile, g, t, live);
+        }
         if (k0 + kTile > seq) {
             mask_columns(p, seq - k0, t);
         }
@@ -701,7 +717,14 @@ attention_stream_forward_kernel(const float *__restrict__ q,
             o[u][2] *= alpha_b;
             o[u][3] *= alpha_b;
         }
-        product_columns<HD, 8>(o, p, v_tile, g, t);
+        if (live == 8) {
+            product_columns<HD, 8>(o, p, v_tile, g, t);
+        } else {
+            product_columns<HD, 8, true>(o, p, v_tile, g, t, live);
+        }
+    }
+    if (!live_warp) {
+        return;
     }
     sum_a = quad_sum(sum_a);
     sum_b = quad_sum(sum_b);
@@ -738,14 +761,17 @@ attention_stream_backward_rows_kernel(
     using S = Shape<HD>;
     __shared__ __align__(16) float k_tile[kTile * S::kPitch];
     __shared__ __align__(16) float v_tile[kTile * S::kPitch];
-    const size_t group = blockIdx.x;
+    const int row_tiles = (seq + kTile - 1) / kTile;
+    const size_t group = blockIdx.x / row_tiles;
+    const int row_tile = blockIdx.x % row_tiles;
     const size_t base = group_offset<HD>(group, seq, in_layout);
     const int ld = in_layout.ld;
     const float *out_base = out + group_offset<HD>(group, seq, out_layout);
     const float *dout_base = dout + group_offset<HD>(group, seq, dout_layout);
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     const int g = lane >> 2, t = lane & 3;
-    const int r0 = blockIdx.y * kTile + warp * 16 + g, r1 = r0 + 8;
+    const int r0 = row_tile * kTile + warp * 16 + g, r1 = r0 + 8;
+    const bool live_warp = row_tile * kTile + warp * 16 < seq;
     const int safe0 = min(r0, seq - 1), safe1 = min(r1, seq - 1);
     const float scale2 = scale * kLog2e;
     float qa[S::kRange], qb[S::kRange], ga[S::kRange], gb[S::kRange];
@@ -790,15 +816,24 @@ attention_stream_backward_rows_kernel(
             stage_store<HD, kStreamBlock>(v_staged, v_tile);
         }
         __syncthreads();
+        if (!live_warp) {
+            continue;
+        }
+        const int live = (min(kTile, seq - k0) + 7) / 8;
         float p[8][4];
+        float ds[8][4];
         clear(p);
-        product_rows<HD, 8>(p, qa, qb, k_tile, g, t);
+        clear(ds);
+        if (live == 8) {
+            product_rows<HD, 8>(p, qa, qb, k_tile, g, t);
+            product_rows<HD, 8>(ds, ga, gb, v_tile, g, t);
+        } else {
+            product_rows<HD, 8, true>(p, qa, qb, k_tile, g, t, live);
+            product_rows<HD, 8, true>(ds, ga, gb, v_tile, g, t, live);
+        }
         if (k0 + kTile > seq) {
             mask_columns(p, seq - k0, t);   // -FLT_MAX: exp2 gives 0 below
         }
-        float ds[8][4];
-        clear(ds);
-        product_rows<HD, 8>(ds, ga, gb, v_tile, g, t);
 #pragma unroll
         for (int n = 0; n < 8; ++n) {
             ds[n][0] = exp2_fast(fmaf(p[n][0], scale2, -lse_a)) * fmaf(ds[n][0], scale, offset_a);
@@ -806,7 +841,14 @@ attention_stream_backward_rows_kernel(
             ds[n][2] = exp2_fast(fmaf(p[n][2], scale2, -lse_b)) * fmaf(ds[n][2], scale, offset_b);
             ds[n][3] = exp2_fast(fmaf(p[n][3], scale2, -lse_b)) * fmaf(ds[n][3], scale, offset_b);
         }
-        product_columns<HD, 8>(result, ds, k_tile, g, t);
+        if (live == 8) {
+            product_columns<HD, 8>(result, ds, k_tile, g, t);
+        } else {
+            product_columns<HD, 8, true>(result, ds, k_tile, g, t, live);
+        }
+    }
+    if (!live_warp) {
+        return;
     }
     store_result<HD>(dq + group_offset<HD>(group, seq, grad_layout),
                      grad_layout.ld, r0, r1, seq, t, result, add_q);
@@ -827,14 +869,17 @@ attention_stream_backward_columns_kernel(
     __shared__ __align__(16) float g_tile[kTile * S::kPitch];
     __shared__ __align__(8) float tile_lse[kTile];
     __shared__ __align__(8) float tile_dot[kTile];
-    const size_t group = blockIdx.x;
+    const int row_tiles = (seq + kTile - 1) / kTile;
+    const size_t group = blockIdx.x / row_tiles;
+    const int row_tile = blockIdx.x % row_tiles;
     const size_t base = group_offset<HD>(group, seq, in_layout);
     const int ld = in_layout.ld;
     const float *dout_base = dout + group_offset<HD>(group, seq, dout_layout);
     const size_t grad_base = group_offset<HD>(group, seq, grad_layout);
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     const int g = lane >> 2, t = lane & 3;
-    const int r0 = blockIdx.y * kTile + warp * 16 + g, r1 = r0 + 8;   // keys
+    const int r0 = row_tile * kTile + warp * 16 + g, r1 = r0 + 8;   // keys
+    const bool live_warp = row_tile * kTile + warp * 16 < seq;
     const int safe0 = min(r0, seq - 1), safe1 = min(r1, seq - 1);
     const float scale2 = scale * kLog2e;
     float ka[S::kRange], kb[S::kRange], va[S::kRange], vb[S::kRange];
@@ -863,9 +908,17 @@ attention_stream_backward_columns_kernel(
             stage_store<HD, kStreamBlock>(g_staged, g_tile);
         }
         __syncthreads();
+        if (!live_warp) {
+            continue;
+        }
+        const int live = (min(kTile, seq - q0) + 7) / 8;   // 8-query groups
         float p[8][4];
         clear(p);
-        product_rows<HD, 8>(p, ka, kb, q_tile, g, t);   // S^T
+        if (live == 8) {
+            product_rows<HD, 8>(p, ka, kb, q_tile, g, t);   // S^T
+        } else {
+            product_rows<HD, 8, true>(p, ka, kb, q_tile, g, t, live);
+        }
 #pragma unroll
         for (int n = 0; n < 8; ++n) {
             const float2 l = *reinterpret_cast<const float2 *>(tile_lse + n * 8 + 2 * t);
@@ -874,10 +927,15 @@ attention_stream_backward_columns_kernel(
             p[n][2] = exp2_fast(fmaf(p[n][2], scale2, -l.x));
             p[n][3] = exp2_fast(fmaf(p[n][3], scale2, -l.y));
         }
-        product_columns<HD, 8>(dv_acc, p, g_tile, g, t);   // dV += P^T dO
         float ds[8][4];
         clear(ds);
-        product_rows<HD, 8>(ds, va, vb, g_tile, g, t);   // dP^T = V dO^T
+        if (live == 8) {
+            product_columns<HD, 8>(dv_acc, p, g_tile, g, t);   // dV += P^T dO
+            product_rows<HD, 8>(ds, va, vb, g_tile, g, t);     // dP^T = V dO^T
+        } else {
+            product_columns<HD, 8, true>(dv_acc, p, g_tile, g, t, live);
+            product_rows<HD, 8, true>(ds, va, vb, g_tile, g, t, live);
+        }
 #pragma unroll
         for (int n = 0; n < 8; ++n) {
             const float2 d = *reinterpret_cast<const float2 *>(tile_dot + n * 8 + 2 * t);
@@ -886,7 +944,14 @@ attention_stream_backward_columns_kernel(
             ds[n][2] = p[n][2] * fmaf(ds[n][2], scale, d.x);
             ds[n][3] = p[n][3] * fmaf(ds[n][3], scale, d.y);
         }
-        product_columns<HD, 8>(dk_acc, ds, q_tile, g, t);   // dK += dS^T Q
+        if (live == 8) {
+            product_columns<HD, 8>(dk_acc, ds, q_tile, g, t);   // dK += dS^T Q
+        } else {
+            product_columns<HD, 8, true>(dk_acc, ds, q_tile, g, t, live);
+        }
+    }
+    if (!live_warp) {
+        return;
     }
     store_result<HD>(dv + grad_base, grad_layout.ld, r0, r1, seq, t, dv_acc, add_v);
     store_result<HD>(dk + grad_base, grad_layout.ld, r0, r1, seq, t, dk_acc, add_k);
@@ -990,7 +1055,7 @@ bool launch_attention_stream_forward(const float *q, const float *k,
     }
     in_layout = resolve(in_layout, head_dim);
     out_layout = resolve(out_layout, head_dim);
-    const dim3 grid(unsigned(groups), unsigned((seq + kTile - 1) / kTile));
+    const unsigned grid = unsigned(groups * ((seq + kTile - 1) / kTile));
 #define FORWARD(HD)                                                            \
     attention_stream_forward_kernel<HD><<<grid, kStreamBlock, 0, stream>>>(    \
         q, k, v, out, lse, int(seq), scale, in_layout, out_layout)
@@ -1018,7 +1083,7 @@ bool launch_attention_stream_backward(const float *q, const float *k,
     out_layout = resolve(out_layout, head_dim);
     dout_layout = resolve(dout_layout, head_dim);
     grad_layout = resolve(grad_layout, head_dim);
-    const dim3 grid(unsigned(groups), unsigned((seq + kTile - 1) / kTile));
+    const unsigned grid = unsigned(groups * ((seq + kTile - 1) / kTile));
 #define BACKWARD(HD)                                                           \
     attention_stream_backward_rows_kernel<HD>                                  \
         <<<grid, kStreamBlock, 0, stream>>>(                                   \

@@ -81,7 +81,8 @@ struct PendingGemm {
 // view of it.  Input pointers are resolved when the op is recorded.
 struct PendingAttention {
     bool active = false;
-    bool tensor_cores = false;
+    int kind = 0;            // see attention_kind()
+    float *lse = nullptr;    // kind 3: where the rows' log-sum-exp goes
     const float *q = nullptr, *k = nullptr, *v = nullptr;
     HeadLayout in_layout;
     const void *output_host = nullptr;
@@ -94,7 +95,8 @@ struct PendingAttention {
 // gradients into the projected gradient next (reference src/vit.c:618-626).
 struct PendingAttentionBackward {
     bool active = false;
-    bool tensor_cores = false;
+    int kind = 0;
+    const float *lse = nullptr;   // kind 3
     const float *q = nullptr, *k = nullptr, *v = nullptr, *out = nullptr,
                 *dout = nullptr;
     HeadLayout in_layout, out_layout, dout_layout;
@@ -383,7 +385,13 @@ void run_attention(CudaBackend *backend, const PendingAttention &pending,
     OpScope scope(backend, "multi_head_attention", pending.bytes,
                   pending.flops);
     const size_t groups = pending.batch * pending.heads;
-    if (pending.tensor_cores) {
+    if (pending.kind == 3) {
+        launch_attention_stream_forward(pending.q, pending.k, pending.v, out,
+                                        pending.lse, groups, pending.seq,
+                                        pending.head_dim, pending.scale,
+                                        backend->stream, pending.in_layout,
+                                        out_layout);
+    } else if (pending.kind == 2) {
         launch_attention_warp_forward(pending.q, pending.k, pending.v, out,
                                       groups, pending.seq, pending.head_dim,
                                       pending.scale, backend->stream,
@@ -405,7 +413,16 @@ void run_attention_backward(CudaBackend *backend,
     OpScope scope(backend, "multi_head_attention_backward", pending.bytes,
                   pending.flops);
     const size_t groups = pending.batch * pending.heads;
-    if (pending.tensor_cores) {
+    if (pending.kind == 3) {
+        float *dots = scratch<float>(backend, backend->rows_scratch,
+                                     groups * pending.seq);
+        launch_attention_stream_backward(
+            pending.q, pending.k, pending.v, pending.out, pending.dout,
+            pending.lse, dq, dk, dv, dots, groups, pending.seq,
+            pending.head_dim, pending.scale, add_q, add_k, add_v,
+            backend->stream, pending.in_layout, pending.out_layout,
+            pending.dout_layout, grad_layout);
+    } else if (pending.kind == 2) {
         launch_attention_warp_backward(
             pending.q, pending.k, pending.v, pending.out, pending.dout, dq, dk,
             dv, groups, pending.seq, pending.head_dim, pending.scale, add_q,
@@ -875,16 +892,21 @@ constexpr size_t kMaxHeadDim = 128;
 // only if somebody reads it.  On the same path the head-major copies of the
 // projections and of their gradients are not made either (see HeadView).
 //
-// Returns 0 when the path does not apply, 1 for the FP32 kernels and 2 for the
-// tensor-core kernels (TF32 operands), chosen like a matrix product's
-// precision: forced by the policy, otherwise by the amount of work.
+// Returns 0 when the path does not apply, 1 for the FP32 whole-group kernels
+// (seq <= 128), 2 for the tensor-core whole-group kernels (seq <= 64) and 3
+// for the tensor-core streaming kernels (any length); tensor cores (TF32
+// operands) are chosen like a matrix product's precision: forced by the
+// policy, otherwise by the amount of work.
 int short_attention_kind(size_t groups, size_t seq, size_t head_dim) {
     const int policy = gemm_default_precision();
     const double work = double(groups) * double(seq) * double(seq) * double(head_dim);
-    if (policy != VITB200_PRECISION_FP32 &&
-        attention_warp_supported(seq, head_dim) &&
-        prefer_tensor_cores(policy, work)) {
-        return 2;
+    if (policy != VITB200_PRECISION_FP32 && prefer_tensor_cores(policy, work)) {
+        if (attention_warp_supported(seq, head_dim)) {
+            return 2;
+        }
+        if (attention_stream_supported(head_dim)) {
+            return 3;
+        }
     }
     if (policy != VITB200_PRECISION_TF32 &&
         attention_small_supported(seq, head_dim)) {
@@ -1034,7 +1056,7 @@ int op_split_heads_backward(void *context, vitb200_tensor *projected,
         // writes: the QKV bias gradient the host asks for next
         // (reference src/vit.c:588-591) then sums [batch, 3d] instead of
         // [batch * seq, 3d].
-        float *partials = pending.tensor_cores
+        float *partials = pending.kind == 2
             ? scratch<float>(backend, backend->column_partials,
                              batch * 3 * d_model)
             : nullptr;
@@ -1164,6 +1186,28 @@ void materialise_probabilities(const void *arguments, float *output,
                                float *const *sources, cudaStream_t stream) {
     ProbabilityDefinition d;
     memcpy(&d, arguments, sizeof(d));
+    if (d.ld && !attention_small_supported(d.seq, d.head_dim)) {
+        // Long sequences read through head views: regroup Q and K into
+        // temporary head-major buffers for the kernel that writes P.  Only a
+        // host that asks for P ever gets here, so the allocation is made (and
+        // released) on the spot.
+        const size_t elements = d.groups * d.seq * d.head_dim;
+        const size_t batch = d.groups / size_t(d.heads);
+        const size_t d_model = size_t(d.heads) * d.head_dim;
+        float *regrouped = nullptr;
+        check(cudaMalloc(&regrouped, 2 * elements * sizeof(float)), "cudaMalloc");
+        launch_head_view(sources[0], regrouped, batch, d.seq, d_model, d.heads,
+                         size_t(d.ld), d.q_col0, stream);
+        launch_head_view(sources[0], regrouped + elements, batch, d.seq, d_model,
+                         d.heads, size_t(d.ld), d.k_col0, stream);
+        launch_attention_mma_forward(regrouped, regrouped + elements,
+                                     regrouped + elements, output, nullptr,
+                                     d.groups, d.seq, d.head_dim, d.scale,
+                                     stream);
+        check(cudaStreamSynchronize(stream), "cudaStreamSynchronize");
+        check(cudaFree(regrouped), "cudaFree");
+        return;
+    }
     if (d.ld) {
         HeadLayout layout;
         layout.ld = d.ld;
@@ -1224,8 +1268,9 @@ int op_attention(void *context, const vitb200_tensor *query,
             q = read_operand(backend, query->data, batch, heads, seq, head_dim, false);
             k = read_operand(backend, key->data, batch, heads, seq, head_dim, false);
             v = read_operand(backend, value->data, batch, heads, seq, head_dim, false);
-            const ProbabilityDefinition definition = {groups, seq, head_dim,
-                                                      scale, 0, 0, 1, 0, 0};
+            const ProbabilityDefinition definition = {
+                groups, seq, head_dim, scale,
+                attention_small_supported(seq, head_dim) ? 0 : 1, 0, 1, 0, 0};
             const void *sources[2] = {query->data, key->data};
             defined = coherent_define_lazy(probabilities->data, sources, 2,
                                            materialise_probabilities,
@@ -1235,7 +1280,14 @@ int op_attention(void *context, const vitb200_tensor *query,
         if (defined) {
             PendingAttention &pending = backend->pending_attention;
             pending.active = true;
-            pending.tensor_cores = kind == 2;
+            pending.kind = kind;
+            pending.lse = nullptr;
+            if (kind == 3) {
+                pending.lse = scratch<float>(
+                    backend, backend->lse_buffers[probabilities->data],
+                    groups * seq);
+                backend->lse_streamed[probabilities->data] = true;
+            }
             pending.q = q.pointer;
             pending.k = k.pointer;
             pending.v = v.pointer;
@@ -1321,7 +1373,20 @@ int op_attention_backward(void *context, const vitb200_tensor *query,
     const size_t head_dim = query->cols;
     const bool pending_p = coherent_is_lazy(probabilities->data);
     const int kind = short_attention_kind(groups, seq, head_dim);
-    const bool recompute = pending_p && kind != 0;
+    // The streaming kernels rebuild P from the log-sum-exp their own forward
+    // pass saved.
+    const float *streamed_lse = nullptr;
+    if (pending_p && kind == 3) {
+        auto found = backend->lse_buffers.find(probabilities->data);
+        auto streamed = backend->lse_streamed.find(probabilities->data);
+        if (found != backend->lse_buffers.end() &&
+            found->second.bytes >= groups * seq * sizeof(float) &&
+            streamed != backend->lse_streamed.end() && streamed->second) {
+            streamed_lse = static_cast<const float *>(found->second.memory);
+        }
+    }
+    const bool recompute =
+        pending_p && kind != 0 && (kind != 3 || streamed_lse != nullptr);
     const double bytes = 4.0 * (11.0 * double(numel(query)) +
                                 (recompute ? 0.0 : double(numel(probabilities))));
     const double flops = 8.0 * double(numel(probabilities)) * double(head_dim);
@@ -1346,7 +1411,8 @@ int op_attention_backward(void *context, const vitb200_tensor *query,
                                             seq, head_dim, true);
         PendingAttentionBackward &pending = backend->pending_attention_backward;
         pending.active = true;
-        pending.tensor_cores = kind == 2;
+        pending.kind = kind;
+        pending.lse = streamed_lse;
         pending.q = q.pointer;
         pending.k = k.pointer;
         pending.v = v.pointer;
