@@ -122,6 +122,17 @@ struct ColumnSumMemo {
     size_t partial_rows = 0;
 };
 
+// A residual add held back for one op: the layer norm that the host applies
+// to the sum next (reference src/vit.c:520-523, and the next block's first
+// layer norm after :534) computes the sum itself.
+struct PendingResidual {
+    bool active = false;
+    const float *a = nullptr, *b = nullptr;
+    float *sum = nullptr;
+    const void *sum_host = nullptr;
+    size_t count = 0;
+};
+
 constexpr int kStagingSlots = 8;
 constexpr size_t kStagingBytes = 64 * 1024;
 
@@ -168,6 +179,8 @@ struct CudaBackend {
     PendingGemm pending;
     PendingAttention pending_attention;
     PendingAttentionBackward pending_attention_backward;
+    PendingResidual pending_residual;
+    unsigned long long fused_residuals = 0;
     unsigned long long fused_head_layouts = 0;
     // Row log-sum-exp of flash attention, one buffer per probability tensor
     // (keyed by the tensor's host address), kept from forward to backward.
@@ -267,6 +280,12 @@ void flush_pending(CudaBackend *backend) {
     if (backend->pending_attention.active ||
         backend->pending_attention_backward.active) {
         flush_attention(backend);
+    }
+    if (backend->pending_residual.active) {
+        const PendingResidual held = backend->pending_residual;
+        backend->pending_residual.active = false;
+        OpScope scope(backend, "residual", 12.0 * double(held.count), 0.0);
+        launch_add(held.a, held.b, held.sum, held.count, backend->stream);
     }
     PendingGemm &pending = backend->pending;
     if (!pending.active) {
@@ -606,11 +625,15 @@ int op_residual(void *context, const vitb200_tensor *left,
     const float *a = view(backend, left->data, Access::Read);
     const float *b = view(backend, right->data, Access::Read);
     float *out = view(backend, output->data, Access::Overwrite);
-    {
-        OpScope scope(backend, "residual", 12.0 * double(numel(output)),
-                      0.0);
-        launch_add(a, b, out, numel(output), backend->stream);
-    }
+    // Not launched yet: a layer norm of the sum usually follows and adds the
+    // two itself.  (The output is device-owned, so a host access flushes.)
+    PendingResidual &held = backend->pending_residual;
+    held.active = true;
+    held.a = a;
+    held.b = b;
+    held.sum = out;
+    held.sum_host = output->data;
+    held.count = numel(output);
     return 0;
 }
 
@@ -759,15 +782,32 @@ int op_layer_norm(void *context, const vitb200_tensor *input,
                   const vitb200_tensor *gamma, const vitb200_tensor *beta,
                   float epsilon, vitb200_tensor *output) {
     CudaBackend *backend = self(context);
+    // The residual add that produced the input may still be held back.
+    PendingResidual held = backend->pending_residual;
+    const bool fuse = held.active && held.sum_host == input->data &&
+                      held.count == numel(input) &&
+                      layer_norm_takes_addend(input->cols) &&
+                      ours({input->data, gamma->data, beta->data, output->data}) &&
+                      input->data != output->data;
+    if (fuse) {
+        backend->pending_residual.active = false;
+    }
     flush_pending(backend);
     if (!ours({input->data, gamma->data, beta->data, output->data}) ||
         input->data == output->data) {
         return -1;
     }
-    const float *x = view(backend, input->data, Access::Read);
     const float *g = view(backend, gamma->data, Access::Read);
     const float *b = view(backend, beta->data, Access::Read);
     float *y = view(backend, output->data, Access::Overwrite);
+    if (fuse) {
+        backend->fused_residuals += 1;
+        OpScope scope(backend, "layer_norm", 20.0 * double(numel(input)), 0.0);
+        launch_layer_norm(held.a, g, b, epsilon, y, input->rows, input->cols,
+                          backend->stream, held.b, held.sum);
+        return 0;
+    }
+    const float *x = view(backend, input->data, Access::Read);
     {
         OpScope scope(backend, "layer_norm", 8.0 * double(numel(input)),
                       0.0);

@@ -86,9 +86,13 @@ void launch_column_sums(const float *in, float *out, size_t rows, size_t cols,
                         size_t ld, cudaStream_t stream);
 
 // ---- layer norm (layernorm.cu) -------------------------------------------
+// With `addend` (only for widths layer_norm_takes_addend accepts) the input
+// is x + addend, which is also written to `sum`.
+bool layer_norm_takes_addend(size_t cols);
 void launch_layer_norm(const float *x, const float *gamma, const float *beta,
                        float epsilon, float *y, size_t rows, size_t cols,
-                       cudaStream_t stream);
+                       cudaStream_t stream, const float *addend = nullptr,
+                       float *sum = nullptr);
 // dx += ...; dgamma += ...; dbeta += ...   (all accumulate)
 void launch_layer_norm_backward(const float *x, const float *gamma,
                                 float epsilon, const float *dy, float *dx,

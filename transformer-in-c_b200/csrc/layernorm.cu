@@ -66,7 +66,10 @@ template <int NV>
 __global__ void __launch_bounds__(kWarpsPerBlock * 32)
 layer_norm_kernel(const float *__restrict__ x, const float *__restrict__ gamma,
                   const float *__restrict__ beta, float epsilon,
-                  float *__restrict__ y, size_t rows, size_t cols) {
+                  float *__restrict__ y, size_t rows, size_t cols,
+                  const float *__restrict__ addend, float *__restrict__ sum) {
+    // With `addend`: the input is x + addend (the residual add the host issued
+    // just before, reference src/vit.c:520-523), which is also stored to `sum`.
     constexpr int R = RowsInFlight<NV>::value;
     const int lane = threadIdx.x & 31;
     const size_t warp = size_t(blockIdx.x) * kWarpsPerBlock + (threadIdx.x >> 5);
@@ -81,12 +84,15 @@ layer_norm_kernel(const float *__restrict__ x, const float *__restrict__ gamma,
         }
     }
     for (size_t first = warp; first < rows; first += warps * R) {
-        float4 v[R][NV];
+        float4 v[R][NV], w[R][NV];
 #pragma unroll
         for (int r = 0; r < R; ++r) {
             const size_t row = first + r * warps;
             if (row < rows) {
                 load_row<NV>(x + row * cols, cols, lane, v[r]);
+                if (addend) {
+                    load_row<NV>(addend + row * cols, cols, lane, w[r]);
+                }
             }
         }
 #pragma unroll
@@ -94,6 +100,19 @@ layer_norm_kernel(const float *__restrict__ x, const float *__restrict__ gamma,
             const size_t row = first + r * warps;
             if (row >= rows) {
                 break;
+            }
+            if (addend) {
+#pragma unroll
+                for (int j = 0; j < NV; ++j) {
+                    v[r][j].x += w[r][j].x;
+                    v[r][j].y += w[r][j].y;
+                    v[r][j].z += w[r][j].z;
+                    v[r][j].w += w[r][j].w;
+                    const size_t col = size_t(j) * 128 + lane * 4;
+                    if (col < cols) {
+                        *reinterpret_cast<float4 *>(sum + row * cols + col) = v[r][j];
+                    }
+                }
             }
             float mean, inverse_std;
             row_statistics<NV>(v[r], cols, lane, epsilon, mean, inverse_std);
@@ -321,9 +340,13 @@ unsigned row_grid(size_t rows, unsigned blocks_per_sm) {
 
 }  // namespace
 
+bool layer_norm_takes_addend(size_t cols) {
+    return cols % 4 == 0 && (cols + 127) / 128 <= 8;
+}
+
 void launch_layer_norm(const float *x, const float *gamma, const float *beta,
                        float epsilon, float *y, size_t rows, size_t cols,
-                       cudaStream_t stream) {
+                       cudaStream_t stream, const float *addend, float *sum) {
     const unsigned grid = row_grid(rows, 8);
     const unsigned block = kWarpsPerBlock * 32;
     const size_t slots = (cols + 127) / 128;
@@ -333,16 +356,16 @@ void launch_layer_norm(const float *x, const float *gamma, const float *beta,
                                                               cols);
     } else if (slots <= 1) {
         layer_norm_kernel<1><<<grid, block, 0, stream>>>(x, gamma, beta, epsilon,
-                                                         y, rows, cols);
+                                                         y, rows, cols, addend, sum);
     } else if (slots <= 2) {
         layer_norm_kernel<2><<<grid, block, 0, stream>>>(x, gamma, beta, epsilon,
-                                                         y, rows, cols);
+                                                         y, rows, cols, addend, sum);
     } else if (slots <= 4) {
         layer_norm_kernel<4><<<grid, block, 0, stream>>>(x, gamma, beta, epsilon,
-                                                         y, rows, cols);
+                                                         y, rows, cols, addend, sum);
     } else {
         layer_norm_kernel<8><<<grid, block, 0, stream>>>(x, gamma, beta, epsilon,
-                                                         y, rows, cols);
+                                                         y, rows, cols, addend, sum);
     }
     ++g_kernel_launches;
 }
