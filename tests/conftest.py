@@ -26,7 +26,7 @@ def load_module(name, path):
 
 
 def pytest_configure(config):
-    config.addinivalue_line("markers", "gpu: needs a B200 (run under gpurun)")
+    config.addinivalue_line("markers", "gpu: needs a B200")
 
 
 @pytest.fixture(scope="session")
