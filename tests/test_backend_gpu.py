@@ -194,6 +194,53 @@ def test_matches_committed_reference_fixtures(path, vit_host_module, host_lib,
     backend.disable()
 
 
+@pytest.mark.parametrize("config,small,copies,bias_from_producer", [
+    ((1, 28, 28, 4, 128, 8, 4, 11), 32, 64, 4),    # cfg 2: batch 2048
+    ((1, 28, 28, 2, 256, 8, 6, 11), 4, 128, 3),    # cfg 3: batch 512, S = 197
+], ids=["cfg2", "cfg3"])
+def test_bench_size_batch_is_the_small_batch_replicated(config, small, copies,
+                                                        bias_from_producer,
+                                                        vit_host_module,
+                                                        host_lib, backend):
+    """The bench workloads at full size (cfg 2: M = 102 400 token rows, 16 384
+    attention groups; cfg 3: 100 864 rows of 197-token sequences; every
+    large-shape kernel and fusion) checked through a size-independent
+    property: a batch made of copies of a small batch has the same mean loss
+    and the same mean gradients as the small batch, which the float64 oracle
+    can afford.  Shipped precision policy."""
+    vh = vit_host_module
+    images, labels = vh.synthetic_batch(small, 28, 28, 11, 4321)
+    backend.enable()
+    backend.set_gemm_precision(0)
+    gpu = vh.VitHost(host_lib, config, small * copies)
+    init = gpu.parameters(0)
+    fused_before = backend.fusion_counters()
+    loss = gpu.gradients(np.tile(images, (copies, 1)), np.tile(labels, copies),
+                         None, 0.1)
+    grads = gpu.parameters(1)
+    fused = backend.fusion_counters()
+    loss64, grads64, _ = vo.loss_and_gradients(
+        {k: v.astype(np.float64) for k, v in init.items()}, config,
+        images.astype(np.float64), labels.astype(np.int64), None, 0.1)
+    assert abs(loss - float(loss64)) <= 5e-4
+    for name in grads:
+        ours = drop_key_bias(name, grads[name], config[4])
+        theirs = drop_key_bias(name, grads64[name], config[4])
+        assert max_relative(ours, theirs) <= 2e-3, name
+    # At this size everything that can ride on a neighbour does: per block the
+    # attention kernels absorb merge_heads and split_heads_backward, and the
+    # bias gradients come from their producers' column sums (all four with
+    # the whole-group attention kernels, three with the streaming ones).
+    layers = config[6]
+    assert fused["head_layouts"] - fused_before["head_layouts"] == 2 * layers
+    assert (fused["bias_gradients"] - fused_before["bias_gradients"] ==
+            bias_from_producer * layers)
+    assert backend.tensor_core_status() == 0
+    backend.set_gemm_precision(-1)
+    gpu.close()
+    backend.disable()
+
+
 @pytest.mark.parametrize("precision", [FP32, 0], ids=["fp32", "default"])
 def test_vit_c_full_batch_against_oracle(precision, vit_host_module, host_lib,
                                          backend):
