@@ -361,6 +361,23 @@ void free_scratch(Scratch &buffer) {
     buffer = Scratch{};
 }
 
+// A tensor is gone: forget the log-sum-exp buffer kept for it, if any (the
+// host's evaluation entry points create and free a cache per call).
+void release_hook(const void *host_pointer) {
+    CudaBackend *backend = g_flush_backend;
+    if (!backend) {
+        return;
+    }
+    auto found = backend->lse_buffers.find(host_pointer);
+    if (found != backend->lse_buffers.end()) {
+        // The buffer may still be read by enqueued work.
+        cudaStreamSynchronize(backend->stream);
+        free_scratch(found->second);
+        backend->lse_buffers.erase(found);
+    }
+    backend->lse_streamed.erase(host_pointer);
+}
+
 size_t numel(const vitb200_tensor *tensor) {
     size_t count = 1;
     for (size_t i = 0; i < tensor->ndim; ++i) {
@@ -1946,6 +1963,7 @@ extern "C" int cuda_backend_create(CudaBackend **backend) {
         return -1;
     }
     coherence_set_stream(result->stream, flush_hook);
+    coherence_set_release_hook(release_hook);
     g_flush_backend = result;
     *backend = result;
     return 0;
@@ -2007,6 +2025,7 @@ extern "C" void cuda_backend_free(CudaBackend *backend) {
     // Tensors that outlive the backend are copied back on the legacy default
     // stream from here on.
     coherence_set_stream(nullptr, nullptr);
+    coherence_set_release_hook(nullptr);
     if (g_flush_backend == backend) {
         g_flush_backend = nullptr;
     }
@@ -2044,6 +2063,7 @@ extern "C" int cuda_backend_enable_device_execution(CudaBackend *backend) {
     check(cudaSetDevice(backend->device), "cudaSetDevice");
     coherence_install_fault_handler();
     coherence_set_stream(backend->stream, flush_hook);
+    coherence_set_release_hook(release_hook);
     g_flush_backend = backend;
     backend->table = make_table(backend);
     backend->set_table(&backend->table);

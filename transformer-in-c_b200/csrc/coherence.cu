@@ -366,6 +366,12 @@ void coherence_set_stream(cudaStream_t stream, void (*flush)(void)) {
     g_flush = flush;
 }
 
+void (*g_released)(const void *) = nullptr;
+
+void coherence_set_release_hook(void (*released)(const void *)) {
+    g_released = released;
+}
+
 void *coherent_allocate(void *context, size_t bytes) {
     (void)context;
     if (bytes == 0) {
@@ -405,6 +411,9 @@ void coherent_release(void *context, void *memory) {
     }
     Region region = it->second;
     regions.erase(it);
+    if (g_released) {
+        g_released(memory);
+    }
     if (region.pinned) {
         cudaHostUnregister(region.mirror);
     }

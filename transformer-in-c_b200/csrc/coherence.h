@@ -124,6 +124,9 @@ int coherent_prepare_host_io(const void *pointer, size_t bytes,
 
 // Called by the backend so the fault handler can drain work before copying.
 void coherence_set_stream(cudaStream_t stream, void (*flush)(void));
+// Called with the host address of every allocation that is released, so that
+// the backend can drop what it keeps per tensor.
+void coherence_set_release_hook(void (*released)(const void *));
 void coherence_install_fault_handler();
 CoherenceStats coherence_stats();
 

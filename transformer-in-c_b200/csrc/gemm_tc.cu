@@ -46,18 +46,18 @@ namespace vitb200 {
 namespace {
 
 constexpr int kTileM = 128;
-constexpr int kTileN = 128;
+constexpr int kTileN = 128;                 // narrow tiles; the wide variant is 256
 constexpr int kBlockK = 32;                 // 128 bytes of FP32 per row
 constexpr int kMmaK = 8;                    // tf32 K per instruction
 constexpr int kOperandBytes = kTileM * kBlockK * 4;   // 16 KiB
-constexpr int kStageBytes = 2 * kOperandBytes;
+constexpr int kStageBytes = 2 * kOperandBytes;        // narrow tiles
 // Upper bound on the load ring; the launch code picks the depth that fits
 // beside the epilogue staging for the chosen number of CTAs per SM.
 constexpr int kMaxStages = 6;
 constexpr int kSmemLimit = 227 * 1024 - 1024;   // leave room for static shared memory
 constexpr int kThreads = 192;
 constexpr int kBarrierBytes = 256;   // 2 x kMaxStages + 4 mbarriers, TMEM slot
-constexpr int kTmemColumns = 256;                  // two 128-column accumulators
+constexpr int kTmemColumns = 256;                  // two 128-column accumulators (narrow tiles)
 constexpr unsigned long long kWaitLimitNs = 2000000000ull;  // 2 s
 
 // ---- PTX wrappers ----------------------------------------------------------
@@ -242,6 +242,14 @@ __device__ __forceinline__ void mbarrier_arrive(uint64_t *bar) {
 // slice) item = blockIdx.x, blockIdx.x + gridDim.x, ...; the three roles run
 // the same sequence and meet only through mbarriers, so the loads and MMAs of
 // item i+1 overlap the epilogue of item i (two accumulator buffers in TMEM).
+//
+// TILE_N = 128: two CTAs per SM share the 512 TMEM columns (2 x 128 each).
+// TILE_N = 256: one CTA per SM with all 512 columns; an MMA instruction then
+// covers twice the columns for the same A bytes, which is what the
+// compute-bound shapes (K >= 256) need from shared memory.  The launch code
+// guarantees one CTA per SM for it through the shared-memory request, so the
+// two allocations can never wait for each other.
+template <int TILE_N>
 __global__ void __launch_bounds__(kThreads)
 gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a,
                const __grid_constant__ CUtensorMap map_b,
@@ -252,6 +260,8 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a,
     // padding (two CTAs with three stages each fill the SM to the last KiB):
     //   [stages x 32 KiB operand tiles][epilogue staging][barriers]
     extern __shared__ __align__(1024) uint8_t smem[];
+    constexpr int kStageBytes = kOperandBytes + TILE_N * kBlockK * 4;
+    constexpr int kTmemColumns = 2 * TILE_N;
     const int kStages = p.stages;
     uint8_t *staging = smem + kStages * kStageBytes;
     uint64_t *full_bar = reinterpret_cast<uint64_t *>(staging + p.staging_bytes);
@@ -303,7 +313,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a,
             for (int item = blockIdx.x; item < items && ok; item += gridDim.x) {
                 const int tile = item % tiles;
                 const int m0 = (tile / p.n_tiles) * kTileM;
-                const int n0 = (tile % p.n_tiles) * kTileN;
+                const int n0 = (tile % p.n_tiles) * TILE_N;
                 const int kb_begin = (item / tiles) * p.k_blocks_per_split;
                 const int kb_end = min(p.k_blocks, kb_begin + p.k_blocks_per_split);
                 for (int kb = kb_begin; kb < kb_end; ++kb, ++fill) {
@@ -327,7 +337,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a,
                         tma_load_2d(a_tile, &map_a, k0, m0, &full_bar[s]);
                     }
                     if (p.b_mn_major) {
-                        for (int j = 0; j < 4; ++j) {
+                        for (int j = 0; j < TILE_N / 32; ++j) {
                             tma_load_2d(b_tile + j * 4096, &map_b, n0 + 32 * j, k0,
                                         &full_bar[s]);
                         }
@@ -343,7 +353,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a,
             const uint32_t idesc = (1u << 4) | (2u << 7) | (2u << 10) |
                                    (uint32_t(p.a_mn_major) << 15) |
                                    (uint32_t(p.b_mn_major) << 16) |
-                                   (uint32_t(kTileN >> 3) << 17) |
+                                   (uint32_t(TILE_N >> 3) << 17) |
                                    (uint32_t(kTileM >> 4) << 24);
             // K-major: 8-row groups 1024 B apart, K steps of 32 B inside the
             // swizzled row.  MN-major: 32-wide MN atoms one box (4096 B)
@@ -375,7 +385,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a,
                     break;
                 }
                 tcgen05_fence_after();
-                const uint32_t accumulator = tmem_base + buffer * kTileN;
+                const uint32_t accumulator = tmem_base + buffer * TILE_N;
                 for (int kb = kb_begin; kb < kb_end; ++kb, ++drain) {
                     const int s = drain % kStages;
                     const uint32_t phase = (drain / kStages) & 1;
@@ -420,7 +430,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a,
         for (int item = blockIdx.x; item < items; item += gridDim.x, ++local) {
             const int tile = item % tiles;
             const int m0 = (tile / p.n_tiles) * kTileM + quarter * 32;
-            const int n0 = (tile % p.n_tiles) * kTileN;
+            const int n0 = (tile % p.n_tiles) * TILE_N;
             const int buffer = local & 1;
             const uint32_t buffer_phase = (local >> 1) & 1;
             ok = mbarrier_wait(&tmem_full_bar[buffer], buffer_phase);
@@ -431,7 +441,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a,
             }
             tcgen05_fence_after();
 #pragma unroll 1
-            for (int chunk = 0; chunk < kTileN / 32; ++chunk) {
+            for (int chunk = 0; chunk < TILE_N / 32; ++chunk) {
                 const int col0 = n0 + chunk * 32;
                 const bool chunk_live = col0 < p.n && m0 < p.m;
                 // Bias for these 32 columns, requested before the accumulator
@@ -455,10 +465,10 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a,
                 uint32_t r[32];
                 if (chunk_live) {
                     tcgen05_load_32(tmem_base + (uint32_t(quarter * 32) << 16) +
-                                        buffer * kTileN + chunk * 32,
+                                        buffer * TILE_N + chunk * 32,
                                     r);
                 }
-                if (chunk == kTileN / 32 - 1) {
+                if (chunk == TILE_N / 32 - 1) {
                     // Everything this warp needs is in registers: hand the
                     // accumulator buffer back to the MMA warp.
                     tcgen05_fence_before();
@@ -696,13 +706,27 @@ int launch_gemm_tc(const TcGemm &g, cudaStream_t stream) {
     }
     static bool configured = false;
     if (!configured) {
-        if (cudaFuncSetAttribute(gemm_tc_kernel,
+        if (cudaFuncSetAttribute(gemm_tc_kernel<128>,
+                                 cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                 kSmemLimit) != cudaSuccess ||
+            cudaFuncSetAttribute(gemm_tc_kernel<256>,
                                  cudaFuncAttributeMaxDynamicSharedMemorySize,
                                  kSmemLimit) != cudaSuccess) {
             return -1;
         }
         configured = true;
     }
+    // Wide tiles where the product is compute-bound and divides evenly:
+    // deep reductions, one output, a multiple of 256 columns.
+    static const int forced_tile =
+        getenv("VITB200_TC_TILE_N") ? atoi(getenv("VITB200_TC_TILE_N")) : 0;
+    bool wide = !g.d2 && g.k >= 256 && g.n % 256 == 0;
+    if (forced_tile == 128 || g.d2) {
+        wide = false;
+    } else if (forced_tile == 256) {
+        wide = g.n >= 256;
+    }
+    const int tile_n = wide ? 256 : kTileN;
     CUtensorMap map_a, map_b, map_d;
     // K-major operand: rows = output index, inner = reduction index.
     // MN-major operand: rows = reduction index, inner = output index.
@@ -713,7 +737,7 @@ int launch_gemm_tc(const TcGemm &g, cudaStream_t stream) {
         : tensor_map(g.a, g.k, g.m, g.lda, 32, kTileM, chunks16, true, &map_a);
     const bool ok_b = g.b_mn_major
         ? tensor_map(g.b, g.n, g.k, g.ldb, 32, 32, chunks32, true, &map_b)
-        : tensor_map(g.b, g.k, g.n, g.ldb, 32, kTileN, chunks16, true, &map_b);
+        : tensor_map(g.b, g.k, g.n, g.ldb, 32, tile_n, chunks16, true, &map_b);
     const bool ok_d =
         tensor_map(g.d, g.n, g.m, g.ldd, 32, 32, chunks16, false, &map_d);
     CUtensorMap map_d2 = map_d;
@@ -726,7 +750,7 @@ int launch_gemm_tc(const TcGemm &g, cudaStream_t stream) {
     p.m = g.m;
     p.n = g.n;
     p.k_blocks = (g.k + kBlockK - 1) / kBlockK;
-    p.n_tiles = (g.n + kTileN - 1) / kTileN;
+    p.n_tiles = (g.n + tile_n - 1) / tile_n;
     const int m_tiles = (g.m + kTileM - 1) / kTileM;
     p.m_tiles = m_tiles;
     const int tiles = m_tiles * p.n_tiles;
@@ -755,6 +779,13 @@ int launch_gemm_tc(const TcGemm &g, cudaStream_t stream) {
     }
     if (forced_ctas > 0) {
         ctas_per_sm = forced_ctas;
+    }
+    if (wide) {
+        // One CTA per SM (it owns all of tensor memory): four 48 KiB stages
+        // and double-buffered staging, 224 KiB.
+        ctas_per_sm = 1;
+        p.stages = 4;
+        staging_bytes = 2 * kOperandBytes;
     }
     if (forced_staging == 1 && !g.d2) {
         staging_bytes = kOperandBytes;
@@ -802,10 +833,16 @@ int launch_gemm_tc(const TcGemm &g, cudaStream_t stream) {
     // One persistent CTA per SM (the shared-memory ring fills an SM), fewer
     // when there is less work than SMs.
     const long long items = (long long)tiles * splits;
-    const int smem_bytes = p.stages * kStageBytes + staging_bytes + kBarrierBytes;
+    const int stage_bytes = kOperandBytes + tile_n * kBlockK * 4;
+    const int smem_bytes = p.stages * stage_bytes + staging_bytes + kBarrierBytes;
     const unsigned grid = unsigned(items < slots ? items : slots);
-    gemm_tc_kernel<<<grid, kThreads, smem_bytes, stream>>>(
-        map_a, map_b, map_d, map_d2, p);
+    if (wide) {
+        gemm_tc_kernel<256><<<grid, kThreads, smem_bytes, stream>>>(
+            map_a, map_b, map_d, map_d2, p);
+    } else {
+        gemm_tc_kernel<128><<<grid, kThreads, smem_bytes, stream>>>(
+            map_a, map_b, map_d, map_d2, p);
+    }
     ++g_kernel_launches;
     return 0;
 }
