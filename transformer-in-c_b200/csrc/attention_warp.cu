@@ -630,8 +630,7 @@ __device__ __forceinline__ void mask_columns(float (&s)[8][4], int limit, int t)
 }
 
 template <int HD>
-__global__ void __launch_bounds__(kStreamBlock)
-attention_stream_forward_kernel(const float *__restrict__ q,
+__device__ __forceinline__ void attention_stream_forward_body(const float *__restrict__ q,
                                 const float *__restrict__ k,
                                 const float *__restrict__ v,
                                 float *__restrict__ out,
@@ -748,10 +747,33 @@ attention_stream_forward_kernel(const float *__restrict__ q,
     }
 }
 
-// dQ, and D_i = dO_i . O_i saved as -scale * D_i for the column kernel.
+// Thin entry points: the occupancy target (four blocks per SM, 128 registers)
+// pays for head dimensions up to 32 and costs spills at 64.
 template <int HD>
 __global__ void __launch_bounds__(kStreamBlock)
-attention_stream_backward_rows_kernel(
+attention_stream_forward_kernel(const float *__restrict__ q,
+                                const float *__restrict__ k,
+                                const float *__restrict__ v,
+                                float *__restrict__ out,
+                                float *__restrict__ lse, int seq, float scale,
+                                HeadLayout in_layout, HeadLayout out_layout) {
+    attention_stream_forward_body<HD>(q, k, v, out, lse, seq, scale, in_layout, out_layout);
+}
+
+template <int HD>
+__global__ void __launch_bounds__(kStreamBlock, 4)
+attention_stream_forward_dense_kernel(const float *__restrict__ q,
+                                const float *__restrict__ k,
+                                const float *__restrict__ v,
+                                float *__restrict__ out,
+                                float *__restrict__ lse, int seq, float scale,
+                                HeadLayout in_layout, HeadLayout out_layout) {
+    attention_stream_forward_body<HD>(q, k, v, out, lse, seq, scale, in_layout, out_layout);
+}
+
+// dQ, and D_i = dO_i . O_i saved as -scale * D_i for the column kernel.
+template <int HD>
+__device__ __forceinline__ void attention_stream_backward_rows_body(
     const float *__restrict__ q, const float *__restrict__ k,
     const float *__restrict__ v, const float *__restrict__ out,
     const float *__restrict__ dout, const float *__restrict__ lse,
@@ -854,10 +876,35 @@ attention_stream_backward_rows_kernel(
                      grad_layout.ld, r0, r1, seq, t, result, add_q);
 }
 
-// dK and dV for a tile of keys, sweeping the queries.
+// Thin entry points: the occupancy target (four blocks per SM, 128 registers)
+// pays for head dimensions up to 32 and costs spills at 64.
 template <int HD>
 __global__ void __launch_bounds__(kStreamBlock)
-attention_stream_backward_columns_kernel(
+attention_stream_backward_rows_kernel(
+    const float *__restrict__ q, const float *__restrict__ k,
+    const float *__restrict__ v, const float *__restrict__ out,
+    const float *__restrict__ dout, const float *__restrict__ lse,
+    float *__restrict__ dq, float *__restrict__ row_dots, int seq, float scale,
+    bool add_q, HeadLayout in_layout, HeadLayout out_layout,
+    HeadLayout dout_layout, HeadLayout grad_layout) {
+    attention_stream_backward_rows_body<HD>(q, k, v, out, dout, lse, dq, row_dots, seq, scale, add_q, in_layout, out_layout, dout_layout, grad_layout);
+}
+
+template <int HD>
+__global__ void __launch_bounds__(kStreamBlock, 4)
+attention_stream_backward_rows_dense_kernel(
+    const float *__restrict__ q, const float *__restrict__ k,
+    const float *__restrict__ v, const float *__restrict__ out,
+    const float *__restrict__ dout, const float *__restrict__ lse,
+    float *__restrict__ dq, float *__restrict__ row_dots, int seq, float scale,
+    bool add_q, HeadLayout in_layout, HeadLayout out_layout,
+    HeadLayout dout_layout, HeadLayout grad_layout) {
+    attention_stream_backward_rows_body<HD>(q, k, v, out, dout, lse, dq, row_dots, seq, scale, add_q, in_layout, out_layout, dout_layout, grad_layout);
+}
+
+// dK and dV for a tile of keys, sweeping the queries.
+template <int HD>
+__device__ __forceinline__ void attention_stream_backward_columns_body(
     const float *__restrict__ q, const float *__restrict__ k,
     const float *__restrict__ v, const float *__restrict__ dout,
     const float *__restrict__ lse, const float *__restrict__ row_dots,
@@ -957,6 +1004,32 @@ attention_stream_backward_columns_kernel(
     store_result<HD>(dk + grad_base, grad_layout.ld, r0, r1, seq, t, dk_acc, add_k);
 }
 
+// Thin entry points: the occupancy target (four blocks per SM, 128 registers)
+// pays for head dimensions up to 32 and costs spills at 64.
+template <int HD>
+__global__ void __launch_bounds__(kStreamBlock)
+attention_stream_backward_columns_kernel(
+    const float *__restrict__ q, const float *__restrict__ k,
+    const float *__restrict__ v, const float *__restrict__ dout,
+    const float *__restrict__ lse, const float *__restrict__ row_dots,
+    float *__restrict__ dk, float *__restrict__ dv, int seq, float scale,
+    bool add_k, bool add_v, HeadLayout in_layout, HeadLayout dout_layout,
+    HeadLayout grad_layout) {
+    attention_stream_backward_columns_body<HD>(q, k, v, dout, lse, row_dots, dk, dv, seq, scale, add_k, add_v, in_layout, dout_layout, grad_layout);
+}
+
+template <int HD>
+__global__ void __launch_bounds__(kStreamBlock, 4)
+attention_stream_backward_columns_dense_kernel(
+    const float *__restrict__ q, const float *__restrict__ k,
+    const float *__restrict__ v, const float *__restrict__ dout,
+    const float *__restrict__ lse, const float *__restrict__ row_dots,
+    float *__restrict__ dk, float *__restrict__ dv, int seq, float scale,
+    bool add_k, bool add_v, HeadLayout in_layout, HeadLayout dout_layout,
+    HeadLayout grad_layout) {
+    attention_stream_backward_columns_body<HD>(q, k, v, dout, lse, row_dots, dk, dv, seq, scale, add_k, add_v, in_layout, dout_layout, grad_layout);
+}
+
 HeadLayout resolve(HeadLayout layout, size_t head_dim) {
     return layout.ld ? layout : HeadLayout{int(head_dim), 1};
 }
@@ -1039,9 +1112,9 @@ bool attention_stream_supported(size_t head_dim) {
 
 #define VITB200_STREAM_DISPATCH(head_dim, CALL)                                \
     do {                                                                       \
-        if (head_dim == 16) { CALL(16); }                                      \
-        else if (head_dim == 32) { CALL(32); }                                 \
-        else { CALL(64); }                                                     \
+        if (head_dim == 16) { CALL(16, _dense_kernel); }                       \
+        else if (head_dim == 32) { CALL(32, _dense_kernel); }                  \
+        else { CALL(64, _kernel); }                                            \
     } while (0)
 
 bool launch_attention_stream_forward(const float *q, const float *k,
@@ -1056,8 +1129,8 @@ bool launch_attention_stream_forward(const float *q, const float *k,
     in_layout = resolve(in_layout, head_dim);
     out_layout = resolve(out_layout, head_dim);
     const unsigned grid = unsigned(groups * ((seq + kTile - 1) / kTile));
-#define FORWARD(HD)                                                            \
-    attention_stream_forward_kernel<HD><<<grid, kStreamBlock, 0, stream>>>(    \
+#define FORWARD(HD, KIND)                                                      \
+    attention_stream_forward##KIND<HD><<<grid, kStreamBlock, 0, stream>>>(     \
         q, k, v, out, lse, int(seq), scale, in_layout, out_layout)
     VITB200_STREAM_DISPATCH(head_dim, FORWARD);
 #undef FORWARD
@@ -1084,12 +1157,12 @@ bool launch_attention_stream_backward(const float *q, const float *k,
     dout_layout = resolve(dout_layout, head_dim);
     grad_layout = resolve(grad_layout, head_dim);
     const unsigned grid = unsigned(groups * ((seq + kTile - 1) / kTile));
-#define BACKWARD(HD)                                                           \
-    attention_stream_backward_rows_kernel<HD>                                  \
+#define BACKWARD(HD, KIND)                                                     \
+    attention_stream_backward_rows##KIND<HD>                                   \
         <<<grid, kStreamBlock, 0, stream>>>(                                   \
             q, k, v, out, dout, lse, dq, row_dots, int(seq), scale, add_q,     \
             in_layout, out_layout, dout_layout, grad_layout);                  \
-    attention_stream_backward_columns_kernel<HD>                               \
+    attention_stream_backward_columns##KIND<HD>                                \
         <<<grid, kStreamBlock, 0, stream>>>(                                   \
             q, k, v, dout, lse, row_dots, dk, dv, int(seq), scale, add_k,      \
             add_v, in_layout, dout_layout, grad_layout)
