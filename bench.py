@@ -204,6 +204,28 @@ def augmentation_measurement(backend, host_lib, batch, channels, height, width,
     return result
 
 
+def reference_cuda_rate(config, batch, warmup=2, steps=5):
+    """Secondary baseline: the reference's own CUDA backend (src/cuda_backend.cu,
+    cuBLAS FP32 SGEMM + managed memory + its SIMT kernels) compiled unmodified
+    for sm_100a by oracle/build_ref.py, on the same GPU and workload, in a
+    process of its own.  None when that binary is not present or fails."""
+    binary = os.path.join(REPO, "oracle", "_ref", "reference_cuda_step")
+    if not os.path.exists(binary):
+        return None
+    command = [binary, *[str(v) for v in config], str(batch), str(warmup), str(steps)]
+    try:
+        done = subprocess.run(command, capture_output=True, text=True, timeout=240)
+        if done.returncode != 0:
+            return None
+        result = json.loads(done.stdout.strip().splitlines()[-1])
+    except (subprocess.TimeoutExpired, ValueError, IndexError):
+        return None
+    return {"value": result["images_per_second"], "unit": "images/s",
+            "ms_per_step": result["ms_per_step"], "batch": batch, "steps": steps,
+            "kind": "reference src/cuda_backend.cu built for sm_100a (cuBLAS FP32, "
+                    "managed memory), wall clock around the same train calls"}
+
+
 def run_reference(args, vh, config, batch, rank, world):
     """The reference's own CPU implementation of the step, timed on this
     machine's host cores.  The code is single-threaded on Linux
@@ -412,6 +434,10 @@ def main():
             "value": rate, "unit": "images/s", "cores": 1, "kind": "reference",
             "sample": f"reference CPU train step (single-threaded on Linux), "
                       f"batch {sample_batch}, {sample_steps} steps"}
+    if rank == 0 and world == 1 and not args.no_cpu_baseline:
+        secondary = reference_cuda_rate(config, batch)
+        if secondary:
+            line["reference_cuda"] = secondary
     if rank == 0 and world == 1:
         line["augmentation"] = augmentation_measurement(
             backend, host_lib, batch, config[0], config[1], config[2],

@@ -19,6 +19,11 @@ this repository) with the flags of the reference Makefile:2
                   tests/checkpoint_roundtrip.c (ours) on the reference's
                   vit_model_save / vit_model_load, linked like test_device
 
+  reference_cuda_step
+                  oracle/reference_cuda_step.c (ours, a timing driver) with the
+                  reference's own src/cuda_backend.cu compiled for sm_100a and
+                  cuBLAS: the secondary GPU baseline of bench.py
+
 Usage: python oracle/build_ref.py [reference_root]
 """
 import os
@@ -63,6 +68,20 @@ def build(reference_root="/root/reference"):
              os.path.join(REPO, "tests", "checkpoint_roundtrip.c"), *core,
              "-L" + PACKAGE, "-lvitb200",
              "-Wl,-rpath,$ORIGIN/../../transformer-in-c_b200", "-lm"])
+    # The reference's CUDA backend, unmodified, for the same GPU.
+    cuda_home = os.environ.get("CUDA_HOME", "/usr/local/cuda")
+    nvcc = os.path.join(cuda_home, "bin", "nvcc")
+    if os.path.exists(nvcc):
+        backend_object = os.path.join(OUT, "reference_cuda_backend.o")
+        run([nvcc, "-O2", "-std=c++17", "-gencode",
+             "arch=compute_100a,code=sm_100a", "-I" + include, "-c",
+             os.path.join(source, "cuda_backend.cu"), "-o", backend_object])
+        run(["gcc", *flags, "-DENABLE_CUDA", "-o",
+             os.path.join(OUT, "reference_cuda_step"),
+             os.path.join(REPO, "oracle", "reference_cuda_step.c"), *core,
+             backend_object, "-L" + os.path.join(cuda_home, "lib64"),
+             "-Wl,-rpath," + os.path.join(cuda_home, "lib64"),
+             "-lcublas", "-lcudart", "-lstdc++", "-lm"])
     return True
 
 
