@@ -142,11 +142,6 @@ __device__ __forceinline__ void tma_reduce_add_2d(const void *smem,
         : "memory");
 }
 
-__device__ __forceinline__ void tma_store_commit_and_wait() {
-    asm volatile("cp.async.bulk.commit_group;" ::: "memory");
-    asm volatile("cp.async.bulk.wait_group 0;" ::: "memory");
-}
-
 __device__ __forceinline__ void tcgen05_fence_before() {
     asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
 }
