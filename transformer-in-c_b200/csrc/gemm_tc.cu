@@ -50,14 +50,12 @@ constexpr int kTileN = 128;                 // narrow tiles; the wide variant is
 constexpr int kBlockK = 32;                 // 128 bytes of FP32 per row
 constexpr int kMmaK = 8;                    // tf32 K per instruction
 constexpr int kOperandBytes = kTileM * kBlockK * 4;   // 16 KiB
-constexpr int kStageBytes = 2 * kOperandBytes;        // narrow tiles
 // Upper bound on the load ring; the launch code picks the depth that fits
 // beside the epilogue staging for the chosen number of CTAs per SM.
 constexpr int kMaxStages = 6;
 constexpr int kSmemLimit = 227 * 1024 - 1024;   // leave room for static shared memory
 constexpr int kThreads = 192;
 constexpr int kBarrierBytes = 256;   // 2 x kMaxStages + 4 mbarriers, TMEM slot
-constexpr int kTmemColumns = 256;                  // two 128-column accumulators (narrow tiles)
 constexpr unsigned long long kWaitLimitNs = 2000000000ull;  // 2 s
 
 // ---- PTX wrappers ----------------------------------------------------------
