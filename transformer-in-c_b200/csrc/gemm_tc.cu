@@ -486,7 +486,11 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a,
                 const int slot = buffers == 2 ? (stored & 1) : 0;
                 ++stored;
                 float *first = reinterpret_cast<float *>(my_staging + slot * 4096);
-                float *second = reinterpret_cast<float *>(my_staging + 4096);
+                // With 16 KiB of staging both outputs of a warp go through the
+                // same 4 KiB block, one after the other.
+                const bool shared_block = outputs == 2 && p.staging_bytes == kOperandBytes;
+                float *second = shared_block
+                    ? first : reinterpret_cast<float *>(my_staging + 4096);
 #pragma unroll
                 for (int c = 0; c < 8; ++c) {
                     float4 v;
@@ -502,7 +506,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a,
                     // chunk position c ^ (r % 8).
                     const int offset = lane * 32 + 4 * (c ^ (lane & 7));
                     *reinterpret_cast<float4 *>(first + offset) = v;
-                    if (p.second == kSecondGelu) {
+                    if (p.second == kSecondGelu && !shared_block) {
                         v.x = gelu_value_fast(v.x);
                         v.y = gelu_value_fast(v.y);
                         v.z = gelu_value_fast(v.z);
@@ -543,7 +547,40 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a,
                 // Make the generic-proxy writes visible to the TMA engine.
                 asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
                 __syncwarp();
-                if (lane == 0) {
+                if (shared_block && p.second == kSecondGelu) {
+                    // First output out, wait until the copy engine has read
+                    // the block, then the second output through the same block.
+                    if (lane == 0) {
+                        tma_store_2d(first, &map_d, col0, m0);
+                        asm volatile("cp.async.bulk.commit_group;" ::: "memory");
+                        asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory");
+                    }
+                    __syncwarp();
+#pragma unroll
+                    for (int c = 0; c < 8; ++c) {
+                        float4 v;
+                        v.x = __uint_as_float(r[4 * c + 0]);
+                        v.y = __uint_as_float(r[4 * c + 1]);
+                        v.z = __uint_as_float(r[4 * c + 2]);
+                        v.w = __uint_as_float(r[4 * c + 3]);
+                        if (p.bias) {
+                            v.x += bias[c].x; v.y += bias[c].y;
+                            v.z += bias[c].z; v.w += bias[c].w;
+                        }
+                        v.x = gelu_value_fast(v.x);
+                        v.y = gelu_value_fast(v.y);
+                        v.z = gelu_value_fast(v.z);
+                        v.w = gelu_value_fast(v.w);
+                        const int offset = lane * 32 + 4 * (c ^ (lane & 7));
+                        *reinterpret_cast<float4 *>(second + offset) = v;
+                    }
+                    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+                    __syncwarp();
+                    if (lane == 0) {
+                        tma_store_2d(second, &map_d2, col0, m0);
+                        asm volatile("cp.async.bulk.commit_group;" ::: "memory");
+                    }
+                } else if (lane == 0) {
                     if (p.reduce_add) {
                         tma_reduce_add_2d(first, &map_d, col0, m0);
                     } else {
@@ -757,7 +794,8 @@ int launch_gemm_tc(const TcGemm &g, cudaStream_t stream) {
     int staging_bytes = 2 * kOperandBytes;
     int ctas_per_sm = 2;
     p.stages = 2;
-    if (!g.d2) {
+    if (!g.d2 || !g.residual) {
+        // (Also the GELU pair: its two outputs share each warp's block.)
         p.stages = 3;
         staging_bytes = kOperandBytes;
     }
@@ -780,7 +818,7 @@ int launch_gemm_tc(const TcGemm &g, cudaStream_t stream) {
         p.stages = 4;
         staging_bytes = 2 * kOperandBytes;
     }
-    if (forced_staging == 1 && !g.d2) {
+    if (forced_staging == 1 && !(g.d2 && g.residual)) {
         staging_bytes = kOperandBytes;
     } else if (forced_staging == 2 || (forced_stages > 0 && forced_staging == 0)) {
         staging_bytes = 2 * kOperandBytes;
