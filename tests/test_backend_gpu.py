@@ -452,3 +452,35 @@ def test_unread_tensors_are_not_computed_but_reads_see_them(vit_host_module,
     gpu.close()
     cpu.close()
     backend.disable()
+
+
+def test_device_memory_is_steady_over_many_steps(vit_host_module, host_lib, backend):
+    """Pooled buffers, snapshots of overwritten sources and per-tensor scratch
+    must reach a steady state: after a few steps, further training steps and
+    evaluation calls (which create and free a whole activation cache each)
+    allocate nothing more on the device."""
+    import torch
+    vh = vit_host_module
+    config, batch = (1, 28, 28, 4, 64, 4, 2, 11), 64
+    images, labels = vh.synthetic_batch(batch, 28, 28, 11, 9)
+    backend.enable()
+    backend.set_gemm_precision(0)
+    gpu = vh.VitHost(host_lib, config, batch)
+    for _ in range(4):
+        gpu.train_step(images, labels, LR, WD, None, 0.1)
+        gpu.evaluate(images, labels)
+    torch.cuda.synchronize()
+    free_before, _ = torch.cuda.mem_get_info()
+    counters_before = backend.memory_counters()
+    for _ in range(25):
+        gpu.train_step(images, labels, LR, WD, None, 0.1)
+        gpu.evaluate(images, labels)
+    torch.cuda.synchronize()
+    free_after, _ = torch.cuda.mem_get_info()
+    counters_after = backend.memory_counters()
+    assert free_after >= free_before - (1 << 20), (free_before, free_after)
+    assert counters_after["live_allocations"] == counters_before["live_allocations"]
+    assert counters_after["device_bytes"] <= counters_before["device_bytes"]
+    gpu.close()
+    backend.set_gemm_precision(-1)
+    backend.disable()
