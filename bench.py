@@ -387,10 +387,9 @@ def main():
     kernel_name = top["name"]
     if top["name"] in ("gemm", "gemm_backward"):
         # Both ops are launches of one kernel (one per forward product, two per
-        # gradient pair): judge it as a whole.
+        # gradient pair, each timed as one entry): judge it as a whole.
         parts = [e for e in entries if e["name"] in ("gemm", "gemm_backward")]
-        kernel_launches = sum(e["calls"] * (2 if e["name"] == "gemm_backward" else 1)
-                              for e in parts)
+        kernel_launches = sum(e["calls"] for e in parts)
         top = {"name": "gemm_tc_kernel", "ms": sum(e["ms"] for e in parts),
                "bytes": sum(e["bytes"] for e in parts),
                "flops": sum(e["flops"] for e in parts), "calls": kernel_launches}

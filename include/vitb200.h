@@ -165,6 +165,21 @@ int vitb200_k_gemm_fused(const float *x, const float *w, float *y,
 int vitb200_k_gemm_backward(const float *x, const float *w, const float *dy,
                             float *dx, float *dw, size_t m, size_t k, size_t n,
                             int precision, void *stream);
+/* The input half of vitb200_k_gemm_backward followed by
+ * vitb200_k_gelu_backward, for a layer whose input was gelu(gelu_input), as
+ * one tensor-core kernel:
+ *   d_gelu_input[m,k] = (dy[m,n] w[k,n]^T) * gelu'(gelu_input[m,k])
+ * (stored, not added; the gradient of the layer's input itself is not
+ * written).  column_partials, optional, receives
+ * VITB200_GEMM_PARTIAL_ROWS rows of k floats whose column-wise sum is the
+ * column sum of d_gelu_input (the bias gradient of the layer before the
+ * GELU).  Returns -1, with nothing done, when the precision selector or the
+ * shape keeps the product off the tensor cores. */
+#define VITB200_GEMM_PARTIAL_ROWS 296
+int vitb200_k_gemm_backward_gelu(const float *w, const float *dy,
+                                 const float *gelu_input, float *d_gelu_input,
+                                 float *column_partials, size_t m, size_t k,
+                                 size_t n, int precision, void *stream);
 int vitb200_k_bias_add(const float *in, const float *bias, float *out,
                        size_t rows, size_t cols, void *stream);
 int vitb200_k_column_sums(const float *in, float *out, size_t rows,

@@ -454,6 +454,62 @@ def test_unread_tensors_are_not_computed_but_reads_see_them(vit_host_module,
     backend.disable()
 
 
+def test_gelu_backward_rides_on_the_product_before_it(vit_host_module, host_lib,
+                                                      backend):
+    """With tensor-core products, the gradient of the GELU output is never
+    stored: the product that would write it applies the GELU's slope in its
+    epilogue (reference src/vit.c:552-554 as one kernel).  The gradient before
+    the GELU, the bias gradient taken from the kernel's column sums, a host
+    read of the skipped gradient and the following steps all agree with the
+    CPU path."""
+    vh = vit_host_module
+    config, batch = (1, 28, 28, 4, 64, 4, 2, 11), 16
+    layers = config[6]
+    images, labels = vh.synthetic_batch(batch, 28, 28, 11, 5)
+    backend.disable()
+    cpu = vh.VitHost(host_lib, config, batch)
+    backend.enable()
+    backend.set_gemm_precision(TF32)
+    gpu = vh.VitHost(host_lib, config, batch)
+    # (The first step uploads the parameters as they are first used, which
+    # launches held-back products early; the counts below are a later step's.)
+    gpu.train_step(images, labels, LR, WD, None, 0.1)
+    cpu.train_step(images, labels, LR, WD, None, 0.1)
+    for step in range(2):
+        before = backend.elision_counters()
+        fused_before = backend.fusion_counters()
+        gpu_loss = gpu.train_step(images, labels, LR, WD, None, 0.1)
+        cpu_loss = cpu.train_step(images, labels, LR, WD, None, 0.1)
+        after = backend.elision_counters()
+        fused = backend.fusion_counters()
+        assert abs(gpu_loss - cpu_loss) <= 5e-3
+        # Forward: the bias of the patch embedding, of the classifier and of
+        # each block's four products, and the GELU; backward: the GELU's slope
+        # on each block's second MLP product.
+        assert fused["epilogues"] - fused_before["epilogues"] == 2 + (5 + 1) * layers
+        assert fused["bias_gradients"] - fused_before["bias_gradients"] == 4 * layers
+        assert after["lazy_materialised"] == before["lazy_materialised"]
+    for layer in range(layers):
+        for name in ("hidden", "activated"):
+            ours = gpu.block_tensor(layer, name, True)
+            theirs = cpu.block_tensor(layer, name, True)
+            scale = float(np.abs(theirs).max())
+            assert scale > 0
+            np.testing.assert_allclose(ours, theirs, rtol=0, atol=1e-2 * scale,
+                                       err_msg=name)
+    reread = backend.elision_counters()
+    # Only the skipped gradient had to be computed for the read.
+    assert reread["lazy_materialised"] - after["lazy_materialised"] == layers
+    gpu_loss = gpu.train_step(images, labels, LR, WD, None, 0.1)
+    cpu_loss = cpu.train_step(images, labels, LR, WD, None, 0.1)
+    assert abs(gpu_loss - cpu_loss) <= 5e-3
+    assert backend.tensor_core_status() == 0
+    backend.set_gemm_precision(-1)
+    gpu.close()
+    cpu.close()
+    backend.disable()
+
+
 def test_device_memory_is_steady_over_many_steps(vit_host_module, host_lib, backend):
     """Pooled buffers, snapshots of overwritten sources and per-tensor scratch
     must reach a steady state: after a few steps, further training steps and

@@ -130,6 +130,52 @@ def test_gemm_fused_epilogues(lib, m, k, n, extra, precision):
         close(host(ty2), y + res, tolerance)
 
 
+@pytest.mark.parametrize("m,k,n", [
+    (1600, 512, 128), (300, 96, 64), (130, 48, 32), (4096, 2048, 512),
+    (25600, 512, 128), (129, 132, 36),
+])
+@pytest.mark.parametrize("with_sums", [False, True], ids=["plain", "sums"])
+def test_gemm_backward_through_gelu(lib, m, k, n, with_sums):
+    """d(hidden) = (dY W^T) * gelu'(hidden) in one kernel, the reference's
+    gemm_backward input half followed by gelu_backward (src/vit.c:552-554),
+    with the per-CTA column sums the bias gradient is taken from.  TF32
+    operands: 2e-3 of the largest entry; the column sums add up to m values
+    each, so they get the same relative bound against their own scale."""
+    rng = np.random.RandomState(m + k + n)
+    w = rng.randn(k, n) / np.sqrt(n)
+    dy = rng.randn(m, n)
+    hidden = rng.randn(m, k) * 1.5
+    tw, tdy, th = dev(w), dev(dy), dev(hidden)
+    tdh = torch.full((m, k), 7.0, device="cuda")   # stored, not accumulated
+    rows = 296
+    tsums = torch.full((rows, k), 3.0, device="cuda") if with_sums else None
+    assert lib.vitb200_k_gemm_backward_gelu(
+        ptr(tw), ptr(tdy), ptr(th), ptr(tdh), ptr(tsums) if with_sums else None,
+        size(m), size(k), size(n), TF32, None) == 0
+    torch.cuda.synchronize()
+    assert lib.vitb200_tensor_core_status() == 0
+    expected = vo.gelu_backward(hidden, dy @ w.T)
+    close(host(tdh), expected, 2e-3)
+    if with_sums:
+        sums = host(tsums).astype(np.float64).sum(axis=0)
+        # Exactly the column sums of what the kernel stored (up to FP32
+        # summation order), and close to the reference's.
+        stored = host(tdh).astype(np.float64).sum(axis=0)
+        assert np.abs(sums - stored).max() <= 1e-4 * max(np.abs(stored).max(), 1.0)
+        close(sums, expected.sum(axis=0), 5e-3)
+
+
+def test_gemm_backward_through_gelu_declines_fp32(lib):
+    """The fused kernel exists on the tensor-core path only; an FP32 request
+    is refused with nothing written."""
+    t = torch.zeros(64 * 64, device="cuda")
+    out = torch.full((64 * 64,), 5.0, device="cuda")
+    assert lib.vitb200_k_gemm_backward_gelu(
+        ptr(t), ptr(t), ptr(t), ptr(out), None, size(64), size(64), size(64),
+        FP32, None) == -1
+    assert float(host(out).min()) == 5.0
+
+
 def test_gemm_tf32_declines_unaligned_shapes(lib):
     """Row pitches that are not multiples of 16 bytes cannot be described to
     TMA; an explicit TF32 request is refused rather than silently changed."""

@@ -133,6 +133,21 @@ struct PendingResidual {
     size_t count = 0;
 };
 
+// The input half of a product's backward pass, dX = dY W^T, held back while
+// dX is still a pending zero fill: when the next op is the GELU backward pass
+// that consumes dX (reference src/vit.c:552-554), the two run as one kernel
+// and dX itself is never stored.
+struct PendingInputGradient {
+    bool active = false;
+    const void *dx_host = nullptr, *w_host = nullptr, *dy_host = nullptr;
+    int m = 0, k = 0, n = 0;
+};
+
+// Arguments of a gradient that was skipped that way, should somebody read it.
+struct InputGradientShape {
+    int m, k, n;
+};
+
 constexpr int kStagingSlots = 8;
 constexpr size_t kStagingBytes = 64 * 1024;
 
@@ -180,6 +195,7 @@ struct CudaBackend {
     PendingAttention pending_attention;
     PendingAttentionBackward pending_attention_backward;
     PendingResidual pending_residual;
+    PendingInputGradient pending_input_gradient;
     unsigned long long fused_residuals = 0;
     unsigned long long fused_head_layouts = 0;
     // Row log-sum-exp of flash attention, one buffer per probability tensor
@@ -272,6 +288,8 @@ private:
 
 void flush_attention(CudaBackend *backend);
 
+void flush_input_gradient(CudaBackend *backend);
+
 // Launches the held-back product, with whatever was attached to it.
 void flush_pending(CudaBackend *backend) {
     // Every op starts here: whatever it does may change the matrix a memo
@@ -286,6 +304,9 @@ void flush_pending(CudaBackend *backend) {
         backend->pending_residual.active = false;
         OpScope scope(backend, "residual", 12.0 * double(held.count), 0.0);
         launch_add(held.a, held.b, held.sum, held.count, backend->stream);
+    }
+    if (backend->pending_input_gradient.active) {
+        flush_input_gradient(backend);
     }
     PendingGemm &pending = backend->pending;
     if (!pending.active) {
@@ -415,6 +436,24 @@ float *accumulate_view(CudaBackend *backend, const void *pointer, bool *add) {
     *add = !was_zero;
     return device;
 }
+
+// dX = dY W^T on its own: the op after the product's backward pass was not
+// the GELU backward pass the product was held back for.
+void flush_input_gradient(CudaBackend *backend) {
+    const PendingInputGradient held = backend->pending_input_gradient;
+    backend->pending_input_gradient.active = false;
+    const float *w = view(backend, held.w_host, Access::Read);
+    const float *dy = view(backend, held.dy_host, Access::Read);
+    bool add = true;
+    float *dx = accumulate_view(backend, held.dx_host, &add);
+    OpScope scope(backend, "gemm_backward",
+                  4.0 * (double(held.m) * held.n + double(held.k) * held.n +
+                         (add ? 2.0 : 1.0) * double(held.m) * held.k),
+                  2.0 * double(held.m) * held.k * held.n);
+    gemm_backward_input(w, dy, dx, held.m, held.k, held.n,
+                        VITB200_PRECISION_AUTO, add, backend->stream);
+}
+
 
 void run_attention(CudaBackend *backend, const PendingAttention &pending,
                    float *out, HeadLayout out_layout) {
@@ -593,15 +632,49 @@ int op_gemm_backward(void *context, vitb200_tensor *left, vitb200_tensor *right,
     const float *x = view(backend, left->data, Access::Read);
     const float *w = view(backend, right->data, Access::Read);
     const float *dy = view(backend, output->grad, Access::Read);
+    float *dw = view(backend, right->grad, Access::ReadWrite);
+    const int m = int(left->rows), k = int(left->cols), n = int(right->cols);
+    const double weight_bytes = 4.0 * (double(m) * k + double(m) * n +
+                                       2.0 * double(k) * n);
+    const double half_flops = 2.0 * double(m) * k * n;
+    // The input gradient waits for one op when it would be the first thing
+    // written into a zeroed buffer by a tensor-core product: a GELU backward
+    // pass that follows takes it over (see op_gelu_backward).
+    static const bool hold_back = getenv("VITB200_NO_GELU_BACKWARD_FUSION") == nullptr;
+    if (hold_back && coherent_is_zero_pending(left->grad) &&
+        prefer_tensor_cores(VITB200_PRECISION_AUTO, double(m) * k * n) &&
+        k % 4 == 0 && n % 4 == 0) {
+        {
+            OpScope scope(backend, "gemm_backward", weight_bytes, half_flops);
+            gemm_backward_weights(x, dy, dw, m, k, n, VITB200_PRECISION_AUTO,
+                                  backend->stream);
+        }
+        PendingInputGradient &held = backend->pending_input_gradient;
+        held.active = true;
+        held.dx_host = left->grad;
+        held.w_host = right->data;
+        held.dy_host = output->grad;
+        held.m = m;
+        held.k = k;
+        held.n = n;
+        dp_gradient_produced(backend->dp, right->grad, dw, numel(right));
+        return 0;
+    }
     bool dx_add = true;
     float *dx = accumulate_view(backend, left->grad, &dx_add);
-    float *dw = view(backend, right->grad, Access::ReadWrite);
+    // One scope per launch, here and where the input half is held back.
     {
-        OpScope scope(backend, "gemm_backward", 4.0 * (double(output->rows) * output->cols + 3.0 * double(right->rows) * right->cols + 3.0 * double(left->rows) * left->cols),
-                      4.0 * double(left->rows) * left->cols * right->cols);
-        gemm_backward(x, w, dy, dx, dw, int(left->rows), int(left->cols),
-                      int(right->cols), VITB200_PRECISION_AUTO, dx_add,
-                      backend->stream);
+        OpScope scope(backend, "gemm_backward",
+                      4.0 * (double(m) * n + double(k) * n +
+                             (dx_add ? 2.0 : 1.0) * double(m) * k),
+                      half_flops);
+        gemm_backward_input(w, dy, dx, m, k, n, VITB200_PRECISION_AUTO, dx_add,
+                            backend->stream);
+    }
+    {
+        OpScope scope(backend, "gemm_backward", weight_bytes, half_flops);
+        gemm_backward_weights(x, dy, dw, m, k, n, VITB200_PRECISION_AUTO,
+                              backend->stream);
     }
     dp_gradient_produced(backend->dp, right->grad, dw, numel(right));
     return 0;
@@ -905,9 +978,82 @@ int op_gelu(void *context, const vitb200_tensor *input,
     return 0;
 }
 
+// A gradient skipped by the fused product + GELU backward kernel, computed
+// after all because somebody reads it: dX = dY W^T.
+void materialise_input_gradient(const void *arguments, float *output,
+                                float *const *sources, cudaStream_t stream) {
+    InputGradientShape shape;
+    memcpy(&shape, arguments, sizeof(shape));
+    gemm_backward_input(sources[1], sources[0], output, shape.m, shape.k,
+                        shape.n, VITB200_PRECISION_AUTO, false, stream);
+}
+
+// gelu_backward right after the gemm_backward that would have produced its
+// incoming gradient: one kernel computes d(hidden) = (dY W^T) * gelu'(hidden)
+// and the column sums the bias gradient needs; the gradient in between is
+// declared (dY W^T, should anybody read it) but not stored.  Returns false,
+// with the held-back product still pending, when the situation is another.
+bool gelu_backward_through_product(CudaBackend *backend,
+                                   const vitb200_tensor *input,
+                                   const vitb200_tensor *output) {
+    const PendingInputGradient held = backend->pending_input_gradient;
+    if (!held.active || output->grad != held.dx_host ||
+        input->rows != size_t(held.m) || input->cols != size_t(held.k) ||
+        !coherent_is_zero_pending(input->grad) ||
+        !coherent_is_zero_pending(held.dx_host)) {
+        return false;
+    }
+    // The skipped gradient is defined in terms of dY and W, which must be
+    // plain device-resident buffers (dY is usually an alias: use its source).
+    const void *sources[2] = {coherent_alias_root(held.dy_host), held.w_host};
+    if (!sources[0] || sources[0] == sources[1]) {
+        return false;
+    }
+    const float *w = view(backend, held.w_host, Access::Read);
+    const float *dy = view(backend, held.dy_host, Access::Read);
+    const float *h = view(backend, input->data, Access::Read);
+    if (!gemm_backward_input_gelu_supported(w, dy, h, nullptr, held.m, held.k,
+                                            held.n, VITB200_PRECISION_AUTO)) {
+        return false;
+    }
+    const InputGradientShape shape = {held.m, held.k, held.n};
+    if (!coherent_define_lazy(held.dx_host, sources, 2,
+                              materialise_input_gradient, &shape, sizeof(shape),
+                              backend->stream)) {
+        return false;
+    }
+    backend->pending_input_gradient.active = false;
+    flush_pending(backend);
+    bool add = true;
+    float *dh = accumulate_view(backend, input->grad, &add);   // add == false
+    float *sums = scratch<float>(backend, backend->column_partials,
+                                 size_t(kGemmPartialRows) * input->cols);
+    {
+        OpScope scope(backend, "gemm_backward",
+                      4.0 * (double(held.m) * held.n + double(held.k) * held.n +
+                             2.0 * double(held.m) * held.k),
+                      2.0 * double(held.m) * held.k * held.n);
+        if (gemm_backward_input_gelu(w, dy, h, dh, sums, held.m, held.k, held.n,
+                                     VITB200_PRECISION_AUTO,
+                                     backend->stream) != 0) {
+            fprintf(stderr, "vitb200: fused product + GELU backward failed to launch\n");
+            abort();
+        }
+    }
+    backend->fused_epilogues += 1;
+    column_memo_commit(backend, dh, input->rows, input->cols, sums,
+                       kGemmPartialRows);
+    return true;
+}
+
 int op_gelu_backward(void *context, const vitb200_tensor *input,
                      const vitb200_tensor *output) {
     CudaBackend *backend = self(context);
+    if (backend->pending_input_gradient.active &&
+        ours({input->data, input->grad, output->grad}) &&
+        gelu_backward_through_product(backend, input, output)) {
+        return 0;
+    }
     flush_pending(backend);
     if (!ours({input->data, input->grad, output->grad})) {
         return -1;
@@ -2120,6 +2266,8 @@ extern "C" void vitb200_elision_counters(size_t *zero_fills_elided,
 
 namespace {
 
+static_assert(VITB200_GEMM_PARTIAL_ROWS == kGemmPartialRows,
+              "the public header states the partial row count");
 static_assert(sizeof(vitb200_augmentation) == sizeof(AugmentationSettings),
               "public and internal augmentation settings must match");
 
@@ -2422,6 +2570,20 @@ extern "C" int vitb200_k_gemm_backward(const float *x, const float *w,
     }
     return gemm_backward(x, w, dy, dx, dw, int(m), int(k), int(n), precision,
                          true, as_stream(stream));
+}
+
+extern "C" int vitb200_k_gemm_backward_gelu(const float *w, const float *dy,
+                                            const float *gelu_input,
+                                            float *d_gelu_input,
+                                            float *column_partials, size_t m,
+                                            size_t k, size_t n, int precision,
+                                            void *stream) {
+    if (!fits_int(m) || !fits_int(k) || !fits_int(n)) {
+        return -1;
+    }
+    return gemm_backward_input_gelu(w, dy, gelu_input, d_gelu_input,
+                                    column_partials, int(m), int(k), int(n),
+                                    precision, as_stream(stream));
 }
 
 extern "C" int vitb200_k_bias_add(const float *in, const float *bias,

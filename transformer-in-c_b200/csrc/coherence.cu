@@ -231,6 +231,17 @@ void materialise_readers(Region &region, cudaStream_t stream) {
     }
 }
 
+// True when copying `region` costs much less memory traffic than computing the
+// definitions that read it.
+bool copy_beats_readers(const Region &region) {
+    size_t readers = 0;
+    for (const LazyDefinition *lazy = region.feeds; lazy;
+         lazy = lazy->next_reader[reader_slot(lazy, &region)]) {
+        readers += lazy->output ? lazy->output->bytes : 0;
+    }
+    return readers / 8 >= region.bytes;
+}
+
 // The source is about to be replaced wholesale: the pending readers keep the
 // old buffer, the region goes on without one.
 void detach_source(Region &region) {
@@ -451,6 +462,18 @@ float *device_view(const void *host_pointer, Access access,
     if (region->feeds && access != Access::Read) {
         if (access == Access::Overwrite && region->device) {
             detach_source(*region);
+        } else if (region->device && region->owner != Owner::Host &&
+                   copy_beats_readers(*region)) {
+            // An in-place update of a small source with large definitions
+            // pending on it (a weight matrix under the optimizer): the
+            // readers keep the old buffer, the update runs on a copy.
+            float *old = region->device;
+            detach_source(*region);
+            ensure_device_buffer(*region);
+            check(cudaMemcpyAsync(region->device, old, region->bytes,
+                                  cudaMemcpyDeviceToDevice, stream),
+                  "cudaMemcpyAsync(device to device)");
+            g_stats.sources_copied += 1;
         } else {
             materialise_readers(*region, stream);
         }
@@ -634,6 +657,14 @@ bool coherent_lazy_source(const void *output_host, LazyMaterialise function,
     *source_host = region->lazy->source[0] ? region->lazy->source[0]->mirror
                                            : nullptr;
     return true;
+}
+
+const void *coherent_alias_root(const void *host_pointer) {
+    Region *region = host_pointer ? find_base(host_pointer) : nullptr;
+    if (!region || !is_alias(*region)) {
+        return host_pointer;
+    }
+    return region->lazy->source[0] ? region->lazy->source[0]->mirror : nullptr;
 }
 
 bool coherent_is_zero_pending(const void *host_pointer) {

@@ -40,6 +40,7 @@ struct CoherenceStats {
     size_t lazy_materialised;
     size_t lazy_dropped;
     size_t alias_reads;
+    size_t sources_copied;   // in-place updates moved to a copy (readers pending)
 };
 
 // Allocator pair installed through tensor_set_allocator
@@ -106,6 +107,10 @@ float *device_view_accumulate_based(const void *host_pointer,
 bool coherent_lazy_source(const void *output_host, LazyMaterialise function,
                           void *arguments, size_t argument_bytes,
                           const float **source, const void **source_host);
+// The buffer whose values `host_pointer` currently stands for: itself, or the
+// source when it is an alias.  nullptr for an alias whose source has moved on
+// (the alias then reads a kept copy that has no address of its own).
+const void *coherent_alias_root(const void *host_pointer);
 // True while the buffer is a pending zero fill (see coherent_mark_zero).
 bool coherent_is_zero_pending(const void *host_pointer);
 

@@ -157,17 +157,52 @@ int gemm_forward_fused(const float *x, const float *w, float *y, int m, int k,
     return 0;
 }
 
-int gemm_backward(const float *x, const float *w, const float *dy, float *dx,
-                  float *dw, int m, int k, int n, int precision, bool dx_add,
-                  cudaStream_t stream) {
+int gemm_backward_input(const float *w, const float *dy, float *dx, int m,
+                        int k, int n, int precision, bool dx_add,
+                        cudaStream_t stream) {
     // dX[m,k] += dY[m,n] W^T: both operands have the reduction (n) contiguous.
     TcGemm gx = {dy, w, dx, nullptr, m, k, n, n, n, k, false, false, dx_add};
-    if (run(gx, precision, stream) != 0) {
-        return -1;
-    }
+    return run(gx, precision, stream);
+}
+
+int gemm_backward_weights(const float *x, const float *dy, float *dw, int m,
+                          int k, int n, int precision, cudaStream_t stream) {
     // dW[k,n] += X^T dY: both operands have their output index contiguous.
     TcGemm gw = {x, dy, dw, nullptr, k, n, m, k, n, n, true, true, true};
     return run(gw, precision, stream);
+}
+
+int gemm_backward(const float *x, const float *w, const float *dy, float *dx,
+                  float *dw, int m, int k, int n, int precision, bool dx_add,
+                  cudaStream_t stream) {
+    if (gemm_backward_input(w, dy, dx, m, k, n, precision, dx_add, stream) != 0) {
+        return -1;
+    }
+    return gemm_backward_weights(x, dy, dw, m, k, n, precision, stream);
+}
+
+bool gemm_backward_input_gelu_supported(const float *w, const float *dy,
+                                        const float *gelu_input,
+                                        float *d_gelu_input, int m, int k,
+                                        int n, int precision) {
+    TcGemm g = {dy, w, d_gelu_input, nullptr, m, k, n, n, n, k, false, false, false};
+    g.gelu_input = gelu_input;
+    g.ld_gelu_input = k;
+    return use_tensor_cores(g, precision) == 1;
+}
+
+int gemm_backward_input_gelu(const float *w, const float *dy,
+                             const float *gelu_input, float *d_gelu_input,
+                             float *column_partials, int m, int k, int n,
+                             int precision, cudaStream_t stream) {
+    TcGemm g = {dy, w, d_gelu_input, nullptr, m, k, n, n, n, k, false, false, false};
+    g.gelu_input = gelu_input;
+    g.ld_gelu_input = k;
+    g.column_partials = column_partials;
+    if (use_tensor_cores(g, precision) != 1) {
+        return -1;
+    }
+    return launch_gemm_tc(g, stream);
 }
 
 }  // namespace vitb200

@@ -34,6 +34,28 @@ int gemm_forward_fused(const float *x, const float *w, float *y, int m, int k,
 int gemm_backward(const float *x, const float *w, const float *dy, float *dx,
                   float *dw, int m, int k, int n, int precision, bool dx_add,
                   cudaStream_t stream);
+// Its two halves.
+int gemm_backward_input(const float *w, const float *dy, float *dx, int m,
+                        int k, int n, int precision, bool dx_add,
+                        cudaStream_t stream);
+int gemm_backward_weights(const float *x, const float *dy, float *dw, int m,
+                          int k, int n, int precision, cudaStream_t stream);
+// The input half followed by a GELU's backward pass, in one kernel:
+//   d_gelu_input[m,k] = (dY[m,n] W^T) * gelu'(gelu_input[m,k])
+// for a layer whose input X = gelu(gelu_input) (reference src/ops.c:107-165
+// then 965-1000, with the intermediate dX never stored).  column_partials,
+// optional, receives kGemmPartialRows rows of k partial column sums of the
+// result.  Tensor-core path only: -1, with nothing done, when the shape or the
+// precision policy does not put the product there (`..._supported` tells in
+// advance).
+bool gemm_backward_input_gelu_supported(const float *w, const float *dy,
+                                        const float *gelu_input,
+                                        float *d_gelu_input, int m, int k,
+                                        int n, int precision);
+int gemm_backward_input_gelu(const float *w, const float *dy,
+                             const float *gelu_input, float *d_gelu_input,
+                             float *column_partials, int m, int k, int n,
+                             int precision, cudaStream_t stream);
 
 // The same policy for other tensor-core capable ops (attention): true when an
 // op of `multiply_adds` should use TF32 under `precision`.

@@ -217,14 +217,19 @@ struct TcParams {
     int a_mn_major, b_mn_major;
     int reduce_add;           // 1: TMA reduce-add into D, 0: plain store
     const float *bias;        // nullable, length n
-    int second;               // 0, kSecondGelu or kSecondResidual
     const float *residual;    // [m, n] with residual_pitch, for kSecondResidual
     long long residual_pitch;
+    float *column_partials;   // kGeluSlope: [gridDim.x][n] column sums of D, or null
     int *status;              // device-visible word, 0 = ok
 };
 
-constexpr int kSecondGelu = 1;
-constexpr int kSecondResidual = 2;
+constexpr int kSecondGelu = 1;       // D = A*B + bias, D2 = gelu(D)
+constexpr int kSecondResidual = 2;   // D = A*B + bias, D2 = D + residual
+// D = (A*B) * gelu'(H): the backward pass through a GELU folded into the
+// product that computes the GELU output's gradient.  H is read through
+// map_d2 (one 32 x 32 block per accumulator block, by TMA into the block the
+// result is then staged in); there is one output.
+constexpr int kGeluSlope = 3;
 
 __device__ __forceinline__ void mbarrier_arrive(uint64_t *bar) {
     asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_address(bar))
@@ -242,7 +247,9 @@ __device__ __forceinline__ void mbarrier_arrive(uint64_t *bar) {
 // compute-bound shapes (K >= 256) need from shared memory.  The launch code
 // guarantees one CTA per SM for it through the shared-memory request, so the
 // two allocations can never wait for each other.
-template <int TILE_N>
+// SECOND is the epilogue variant (0 or a kSecond... / kGeluSlope constant): a
+// compile-time choice, so that no variant pays for another's registers.
+template <int TILE_N, int SECOND>
 __global__ void __launch_bounds__(kThreads)
 gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a,
                const __grid_constant__ CUtensorMap map_b,
@@ -262,6 +269,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a,
     uint64_t *tmem_full_bar = empty_bar + kMaxStages;
     uint64_t *tmem_empty_bar = tmem_full_bar + 2;
     uint32_t &tmem_base_slot = *reinterpret_cast<uint32_t *>(tmem_empty_bar + 2);
+    uint64_t *operand_bar = tmem_empty_bar + 3;   // two per epilogue warp
     const int warp = threadIdx.x >> 5;
     const int lane = threadIdx.x & 31;
     if ((smem_address(smem) & 1023u) != 0) {
@@ -280,6 +288,9 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a,
         for (int b = 0; b < 2; ++b) {
             mbarrier_init(&tmem_full_bar[b], 1);
             mbarrier_init(&tmem_empty_bar[b], 4);   // one arrival per epilogue warp
+        }
+        for (int w = 0; w < 8; ++w) {
+            mbarrier_init(&operand_bar[w], 1);
         }
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
@@ -406,17 +417,141 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a,
                 }
             }
         }
+    } else if constexpr (SECOND == kGeluSlope) {
+        // Epilogue of D = (A*B) * gelu'(H).  Each warp walks its 32 x 32
+        // blocks in order (tile after tile, four column chunks per tile) as a
+        // two-deep pipeline over its two staging blocks: while block j is
+        // multiplied and stored, the copy engine already fetches the H values
+        // of block j+1 into the other staging block, so the latency of that
+        // read stays off the critical path.
+        const int quarter = warp & 3;
+        uint8_t *my_staging = staging + quarter * (p.staging_bytes / 4);
+        uint64_t *my_bar = operand_bar + 2 * quarter;
+        uint32_t phases = 0;   // bit b: parity of the next completion of my_bar[b]
+        int issued = 0;        // H blocks requested so far
+        int consumed = 0;      // H blocks used so far
+        // Requests the H block of (item, chunk) when that block exists.
+        auto request = [&](int item, int chunk) {
+            const int tile = item % tiles;
+            const int m0 = (tile / p.n_tiles) * kTileM + quarter * 32;
+            const int col0 = (tile % p.n_tiles) * TILE_N + chunk * 32;
+            if (col0 >= p.n || m0 >= p.m) {
+                return;
+            }
+            if (lane == 0) {
+                // The block was last read by the store issued for the block
+                // before the current one.
+                asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory");
+                asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+                const int b = issued & 1;
+                mbarrier_expect_tx(&my_bar[b], 4096);
+                tma_load_2d(my_staging + b * 4096, &map_d2, col0, m0, &my_bar[b]);
+            }
+            ++issued;
+        };
+        if (int(blockIdx.x) < items) {
+            request(blockIdx.x, 0);
+        }
+        int local = 0;
+        for (int item = blockIdx.x; item < items && ok; item += gridDim.x, ++local) {
+            const int tile = item % tiles;
+            const int m0 = (tile / p.n_tiles) * kTileM + quarter * 32;
+            const int n0 = (tile % p.n_tiles) * TILE_N;
+            const int buffer = local & 1;
+            const uint32_t buffer_phase = (local >> 1) & 1;
+            ok = mbarrier_wait(&tmem_full_bar[buffer], buffer_phase);
+            ok = __all_sync(0xffffffffu, ok);   // keep the warp in step
+            if (!ok) {
+                atomicExch(p.status, 3);
+                break;
+            }
+            tcgen05_fence_after();
+#pragma unroll 1
+            for (int chunk = 0; chunk < TILE_N / 32; ++chunk) {
+                const int col0 = n0 + chunk * 32;
+                const bool chunk_live = col0 < p.n && m0 < p.m;
+                uint32_t r[32];
+                if (chunk_live) {
+                    tcgen05_load_32(tmem_base + (uint32_t(quarter * 32) << 16) +
+                                        buffer * TILE_N + chunk * 32,
+                                    r);
+                }
+                if (chunk == TILE_N / 32 - 1) {
+                    tcgen05_fence_before();
+                    __syncwarp();
+                    if (lane == 0) {
+                        mbarrier_arrive(&tmem_empty_bar[buffer]);
+                    }
+                }
+                // The block after this one, possibly the next tile's first.
+                if (chunk + 1 < TILE_N / 32) {
+                    request(item, chunk + 1);
+                } else if (item + int(gridDim.x) < items) {
+                    request(item + gridDim.x, 0);
+                }
+                if (!chunk_live) {
+                    continue;   // uniform across the warp
+                }
+                const int b = consumed & 1;
+                ++consumed;
+                ok = mbarrier_wait(&my_bar[b], (phases >> b) & 1u);
+                ok = __all_sync(0xffffffffu, ok);
+                if (!ok) {
+                    atomicExch(p.status, 7);
+                    break;
+                }
+                phases ^= 1u << b;
+                float *block = reinterpret_cast<float *>(my_staging + b * 4096);
+#pragma unroll
+                for (int c = 0; c < 8; ++c) {
+                    // 128-byte swizzle: 16-byte chunk c of row r lives at
+                    // chunk position c ^ (r % 8).
+                    const int offset = lane * 32 + 4 * (c ^ (lane & 7));
+                    float4 h = *reinterpret_cast<const float4 *>(block + offset);
+                    h.x = __uint_as_float(r[4 * c + 0]) * gelu_slope_fast(h.x);
+                    h.y = __uint_as_float(r[4 * c + 1]) * gelu_slope_fast(h.y);
+                    h.z = __uint_as_float(r[4 * c + 2]) * gelu_slope_fast(h.z);
+                    h.w = __uint_as_float(r[4 * c + 3]) * gelu_slope_fast(h.w);
+                    *reinterpret_cast<float4 *>(block + offset) = h;
+                }
+                if (p.column_partials) {
+                    // Column sums of the block (rows past the matrix are
+                    // zero: their accumulators are), lane = column.
+                    __syncwarp();
+                    float sum = 0.0f;
+#pragma unroll
+                    for (int row = 0; row < 32; ++row) {
+                        sum += block[row * 32 + 4 * ((lane >> 2) ^ (row & 7)) +
+                                     (lane & 3)];
+                    }
+                    if (col0 + lane < p.n) {
+                        atomicAdd(p.column_partials + size_t(blockIdx.x) * p.n +
+                                      col0 + lane,
+                                  sum);
+                    }
+                }
+                asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+                __syncwarp();
+                if (lane == 0) {
+                    tma_store_2d(block, &map_d, col0, m0);
+                    asm volatile("cp.async.bulk.commit_group;" ::: "memory");
+                }
+            }
+        }
+        if (lane == 0) {
+            asm volatile("cp.async.bulk.wait_group 0;" ::: "memory");
+        }
     } else {
         // Epilogue warps 2..5 own TMEM lane quarters 2, 3, 0, 1, i.e. 32 rows
         // of the tile each.  A warp stages its own 32 x 32 blocks (4 KiB, two
         // buffers per output) and issues its own TMA stores, so the epilogue
         // needs no block-wide barrier at all.
         const int quarter = warp & 3;
-        const int outputs = p.second ? 2 : 1;
+        const int outputs = SECOND ? 2 : 1;
         // Per warp: two 4 KiB blocks (one output double-buffered, or one buffer
         // for each of two outputs), or a single block when the load ring was
         // given the space instead.
-        const int buffers = p.second ? 1 : p.staging_bytes / (4 * 4096);
+        const int buffers = outputs == 2 ? 1 : p.staging_bytes / (4 * 4096);
         uint8_t *my_staging = staging + quarter * (p.staging_bytes / 4);
         int local = 0;
         int stored = 0;   // blocks handed to TMA so far (selects the buffer)
@@ -473,6 +608,17 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a,
                 if (!chunk_live) {
                     continue;   // uniform across the warp
                 }
+                if (p.bias) {
+                    // Folded into the accumulator registers once, so the bias
+                    // registers are free again before the stores.
+#pragma unroll
+                    for (int c = 0; c < 8; ++c) {
+                        r[4 * c + 0] = __float_as_uint(__uint_as_float(r[4 * c + 0]) + bias[c].x);
+                        r[4 * c + 1] = __float_as_uint(__uint_as_float(r[4 * c + 1]) + bias[c].y);
+                        r[4 * c + 2] = __float_as_uint(__uint_as_float(r[4 * c + 2]) + bias[c].z);
+                        r[4 * c + 3] = __float_as_uint(__uint_as_float(r[4 * c + 3]) + bias[c].w);
+                    }
+                }
                 // The buffer about to be rewritten was last read by the store
                 // this warp issued two blocks ago.
                 if (lane == 0) {
@@ -491,6 +637,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a,
                 const bool shared_block = outputs == 2 && p.staging_bytes == kOperandBytes;
                 float *second = shared_block
                     ? first : reinterpret_cast<float *>(my_staging + 4096);
+                {
 #pragma unroll
                 for (int c = 0; c < 8; ++c) {
                     float4 v;
@@ -498,15 +645,11 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a,
                     v.y = __uint_as_float(r[4 * c + 1]);
                     v.z = __uint_as_float(r[4 * c + 2]);
                     v.w = __uint_as_float(r[4 * c + 3]);
-                    if (p.bias) {
-                        v.x += bias[c].x; v.y += bias[c].y;
-                        v.z += bias[c].z; v.w += bias[c].w;
-                    }
                     // 128-byte swizzle: 16-byte chunk c of row r lives at
                     // chunk position c ^ (r % 8).
                     const int offset = lane * 32 + 4 * (c ^ (lane & 7));
                     *reinterpret_cast<float4 *>(first + offset) = v;
-                    if (p.second == kSecondGelu && !shared_block) {
+                    if (SECOND == kSecondGelu && !shared_block) {
                         v.x = gelu_value_fast(v.x);
                         v.y = gelu_value_fast(v.y);
                         v.z = gelu_value_fast(v.z);
@@ -514,7 +657,8 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a,
                         *reinterpret_cast<float4 *>(second + offset) = v;
                     }
                 }
-                if (p.second == kSecondResidual) {
+                }
+                if (SECOND == kSecondResidual) {
                     // D2 = D + residual.  In the accumulator layout a lane
                     // owns a row, which would read the residual one row per
                     // lane; instead the staged block is walked with eight
@@ -547,7 +691,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a,
                 // Make the generic-proxy writes visible to the TMA engine.
                 asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
                 __syncwarp();
-                if (shared_block && p.second == kSecondGelu) {
+                if (shared_block && SECOND == kSecondGelu) {
                     // First output out, wait until the copy engine has read
                     // the block, then the second output through the same block.
                     if (lane == 0) {
@@ -563,10 +707,6 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a,
                         v.y = __uint_as_float(r[4 * c + 1]);
                         v.z = __uint_as_float(r[4 * c + 2]);
                         v.w = __uint_as_float(r[4 * c + 3]);
-                        if (p.bias) {
-                            v.x += bias[c].x; v.y += bias[c].y;
-                            v.z += bias[c].z; v.w += bias[c].w;
-                        }
                         v.x = gelu_value_fast(v.x);
                         v.y = gelu_value_fast(v.y);
                         v.z = gelu_value_fast(v.z);
@@ -726,6 +866,10 @@ bool gemm_tc_supported(const TcGemm &g) {
            aligned(g.d) && (!g.bias || aligned(g.bias)) &&
            (!g.d2 || (aligned(g.d2) && g.ldd2 % 4 == 0 && !g.accumulate)) &&
            (!g.residual || (aligned(g.residual) && g.ld_residual % 4 == 0)) &&
+           (!g.gelu_input ||
+            (aligned(g.gelu_input) && g.ld_gelu_input % 4 == 0 && !g.accumulate &&
+             !g.bias && !g.d2)) &&
+           (!g.column_partials || g.gelu_input) &&
            status_word() &&
            encode_tiled();
 }
@@ -736,13 +880,18 @@ int launch_gemm_tc(const TcGemm &g, cudaStream_t stream) {
     }
     static bool configured = false;
     if (!configured) {
-        if (cudaFuncSetAttribute(gemm_tc_kernel<128>,
-                                 cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                 kSmemLimit) != cudaSuccess ||
-            cudaFuncSetAttribute(gemm_tc_kernel<256>,
-                                 cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                 kSmemLimit) != cudaSuccess) {
-            return -1;
+        const void *kernels[] = {
+            reinterpret_cast<const void *>(gemm_tc_kernel<128, 0>),
+            reinterpret_cast<const void *>(gemm_tc_kernel<128, kSecondGelu>),
+            reinterpret_cast<const void *>(gemm_tc_kernel<128, kSecondResidual>),
+            reinterpret_cast<const void *>(gemm_tc_kernel<128, kGeluSlope>),
+            reinterpret_cast<const void *>(gemm_tc_kernel<256, 0>)};
+        for (const void *kernel : kernels) {
+            if (cudaFuncSetAttribute(kernel,
+                                     cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                     kSmemLimit) != cudaSuccess) {
+                return -1;
+            }
         }
         configured = true;
     }
@@ -750,8 +899,8 @@ int launch_gemm_tc(const TcGemm &g, cudaStream_t stream) {
     // deep reductions, one output, a multiple of 256 columns.
     static const int forced_tile =
         getenv("VITB200_TC_TILE_N") ? atoi(getenv("VITB200_TC_TILE_N")) : 0;
-    bool wide = !g.d2 && g.k >= 256 && g.n % 256 == 0;
-    if (forced_tile == 128 || g.d2) {
+    bool wide = !g.d2 && !g.gelu_input && g.k >= 256 && g.n % 256 == 0;
+    if (forced_tile == 128 || g.d2 || g.gelu_input) {
         wide = false;
     } else if (forced_tile == 256) {
         wide = g.n >= 256;
@@ -776,6 +925,11 @@ int launch_gemm_tc(const TcGemm &g, cudaStream_t stream) {
     if (!ok_a || !ok_b || !ok_d || !ok_d2) {
         return -1;
     }
+    if (g.gelu_input &&
+        !tensor_map(g.gelu_input, g.n, g.m, g.ld_gelu_input, 32, 32, chunks16,
+                    false, &map_d2)) {
+        return -1;
+    }
     TcParams p;
     p.m = g.m;
     p.n = g.n;
@@ -794,7 +948,7 @@ int launch_gemm_tc(const TcGemm &g, cudaStream_t stream) {
     int staging_bytes = 2 * kOperandBytes;
     int ctas_per_sm = 2;
     p.stages = 2;
-    if (!g.d2 || !g.residual) {
+    if ((!g.d2 || !g.residual) && !g.gelu_input) {
         // (Also the GELU pair: its two outputs share each warp's block.)
         p.stages = 3;
         staging_bytes = kOperandBytes;
@@ -822,6 +976,12 @@ int launch_gemm_tc(const TcGemm &g, cudaStream_t stream) {
         staging_bytes = kOperandBytes;
     } else if (forced_staging == 2 || (forced_stages > 0 && forced_staging == 0)) {
         staging_bytes = 2 * kOperandBytes;
+    }
+    if (g.gelu_input) {
+        staging_bytes = 2 * kOperandBytes;   // its epilogue pipeline needs both blocks
+        if (p.stages > 2 && ctas_per_sm > 1) {
+            p.stages = 2;
+        }
     }
     p.staging_bytes = staging_bytes;
     const long long slots = 148LL * ctas_per_sm;
@@ -853,7 +1013,9 @@ int launch_gemm_tc(const TcGemm &g, cudaStream_t stream) {
     p.b_mn_major = g.b_mn_major ? 1 : 0;
     p.reduce_add = g.accumulate ? 1 : 0;
     p.bias = g.bias;
-    p.second = g.d2 ? (g.residual ? kSecondResidual : kSecondGelu) : 0;
+    const int second = g.d2 ? (g.residual ? kSecondResidual : kSecondGelu)
+                            : (g.gelu_input ? kGeluSlope : 0);
+    p.column_partials = g.column_partials;
     p.residual = g.residual;
     p.residual_pitch = g.ld_residual;
     int *device_status = nullptr;
@@ -867,11 +1029,31 @@ int launch_gemm_tc(const TcGemm &g, cudaStream_t stream) {
     const int stage_bytes = kOperandBytes + tile_n * kBlockK * 4;
     const int smem_bytes = p.stages * stage_bytes + staging_bytes + kBarrierBytes;
     const unsigned grid = unsigned(items < slots ? items : slots);
+    if (g.column_partials && grid > unsigned(kGemmPartialRows)) {
+        return -1;
+    }
+    if (g.column_partials) {
+        static_assert(kGemmPartialRows == 148 * 2, "one row per CTA slot");
+        if (cudaMemsetAsync(g.column_partials, 0,
+                            size_t(kGemmPartialRows) * g.n * sizeof(float),
+                            stream) != cudaSuccess) {
+            return -1;
+        }
+    }
     if (wide) {
-        gemm_tc_kernel<256><<<grid, kThreads, smem_bytes, stream>>>(
+        gemm_tc_kernel<256, 0><<<grid, kThreads, smem_bytes, stream>>>(
+            map_a, map_b, map_d, map_d2, p);
+    } else if (second == kSecondGelu) {
+        gemm_tc_kernel<128, kSecondGelu><<<grid, kThreads, smem_bytes, stream>>>(
+            map_a, map_b, map_d, map_d2, p);
+    } else if (second == kSecondResidual) {
+        gemm_tc_kernel<128, kSecondResidual><<<grid, kThreads, smem_bytes, stream>>>(
+            map_a, map_b, map_d, map_d2, p);
+    } else if (second == kGeluSlope) {
+        gemm_tc_kernel<128, kGeluSlope><<<grid, kThreads, smem_bytes, stream>>>(
             map_a, map_b, map_d, map_d2, p);
     } else {
-        gemm_tc_kernel<128><<<grid, kThreads, smem_bytes, stream>>>(
+        gemm_tc_kernel<128, 0><<<grid, kThreads, smem_bytes, stream>>>(
             map_a, map_b, map_d, map_d2, p);
     }
     ++g_kernel_launches;

@@ -26,7 +26,17 @@ struct TcGemm {
     long long ldd2 = 0;
     const float *residual = nullptr;
     long long ld_residual = 0;
+    // Optional (not with accumulate, bias or d2): d = (A*B) * gelu'(gelu_input)
+    // element by element, gelu_input of the output's shape.  With
+    // column_partials, [kGemmPartialRows][n] floats, the kernel also leaves
+    // per-CTA column sums of d there (the launcher clears them first).
+    const float *gelu_input = nullptr;
+    long long ld_gelu_input = 0;
+    float *column_partials = nullptr;
 };
+
+// Upper bound of the persistent grid: two CTAs on each of 148 SMs.
+constexpr int kGemmPartialRows = 296;
 
 bool gemm_tc_supported(const TcGemm &gemm);
 int launch_gemm_tc(const TcGemm &gemm, cudaStream_t stream);
