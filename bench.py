@@ -403,13 +403,13 @@ def main():
     else:
         achieved, peak, unit = top["bytes"] / seconds / 1e9, hbm_peak, "GB/s"
     # dram__bytes_read + dram__bytes_write over the 51 gemm_tc_kernel launches
-    # of one step, from an ncu capture at batch 1024 (4.247 GB: 3.425 read,
-    # 0.822 written before the launches ended) scaled to batch 2048 by the rows
+    # of one step, from an ncu capture at batch 1024 (4.727 GB: 3.844 read,
+    # 0.883 written before the launches ended) scaled to batch 2048 by the rows
     # processed; see profiles/gemm_tc_kernel_vit_c_batch1024.md.
     traffic = None
     if (top["name"] == "gemm_tc_kernel" and args.workload == "cfg2" and
             batch == 2048 and not tensor_bound):
-        traffic = 2 * 4.247e9 / 51
+        traffic = 2 * 4.727e9 / 51
     roofline = {
         "bound": "tensor" if tensor_bound else "hbm", "kernel": kernel_name,
         "achieved": achieved, "peak": peak, "unit": unit,
