@@ -116,6 +116,18 @@ void vitb200_dp_counters(CudaBackend *backend,
                          unsigned long long *late_tensors,
                          unsigned long long *bytes);
 
+/* Gradient accumulation (no counterpart in the reference, whose train call
+ * steps the optimiser after every batch).  Tells the backend that the next
+ * ops_adamw_step_parameters calls consume gradients summed over
+ * `micro_batches` forward/backward passes (the host zeroes the parameter
+ * gradients once, runs the passes, then calls the optimiser once): the factor
+ * 1 / micro_batches is folded into the clip scale, like 1 / world, so the norm
+ * that is clipped and the update are those of the mean gradient.  With data
+ * parallelism each gradient's all-reduce starts when the last micro-batch's
+ * op has added to it.  1 restores plain steps.  0 on success, -1 on a bad
+ * argument. */
+int vitb200_set_gradient_accumulation(CudaBackend *backend, int micro_batches);
+
 /* Operand precision of the dense products issued through the op table:
  * VITB200_PRECISION_AUTO (default: TF32 tensor cores for products of at least
  * 16 Mi multiply-adds whose layout TMA can describe, FP32 FMA otherwise),

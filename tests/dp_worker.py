@@ -1,8 +1,9 @@
 """One rank of a data-parallel run (started by tests/test_dp_gpu.py).
 
-argv: rank world directory steps.  Rank r trains on its contiguous shard of a
-fixed global batch with the backend on GPU r; the NCCL id travels through a
-file in `directory`.  Writes the final parameters and per-step losses to
+argv: rank world directory steps [micro_batches].  Rank r trains on its
+contiguous shard of a fixed global batch with the backend on GPU r, in
+`micro_batches` passes per optimiser step when given (gradient accumulation);
+the NCCL id travels through a file in `directory`.  Writes the final parameters and per-step losses to
 directory/rank<r>.npz.  world = 1 is the single-GPU yardstick on the whole batch.
 """
 import os
@@ -21,6 +22,7 @@ GLOBAL_BATCH = 8
 def main():
     rank, world, directory, steps = (int(sys.argv[1]), int(sys.argv[2]),
                                      sys.argv[3], int(sys.argv[4]))
+    micro_batches = int(sys.argv[5]) if len(sys.argv) > 5 else 1
     os.environ["VITB200_DEVICE"] = str(rank)
     os.environ.setdefault("NCCL_NVLS_ENABLE", "0")
     vh = load_module("vitb200_vit_host", os.path.join(PACKAGE, "vit_host.py"))
@@ -44,9 +46,18 @@ def main():
     shard = GLOBAL_BATCH // world
     images = images[rank * shard:(rank + 1) * shard]
     labels = labels[rank * shard:(rank + 1) * shard]
-    model = vh.VitHost(host_lib, CONFIG, shard)
-    losses = [model.train_step(images, labels, 1e-3, 0.05, None, 0.1)
-              for _ in range(steps)]
+    if micro_batches > 1:
+        backend.set_gradient_accumulation(micro_batches)
+        model = vh.VitHost(host_lib, CONFIG, shard // micro_batches)
+        images = np.ascontiguousarray(images)
+        labels = np.ascontiguousarray(labels)
+        losses = [model.train_step_accumulated(images, labels, micro_batches,
+                                               1e-3, 0.05, None, 0.1)
+                  for _ in range(steps)]
+    else:
+        model = vh.VitHost(host_lib, CONFIG, shard)
+        losses = [model.train_step(images, labels, 1e-3, 0.05, None, 0.1)
+                  for _ in range(steps)]
     out = {"losses": np.array(losses)}
     for name, value in model.parameters(0).items():
         out["w/" + name] = value

@@ -17,10 +17,10 @@ WORKER = os.path.join(REPO, "tests", "dp_worker.py")
 STEPS = 5
 
 
-def run_world(world, directory):
+def run_world(world, directory, micro_batches=1):
     os.makedirs(directory, exist_ok=True)
     children = [subprocess.Popen([sys.executable, WORKER, str(rank), str(world),
-                                  directory, str(STEPS)])
+                                  directory, str(STEPS), str(micro_batches)])
                 for rank in range(world)]
     for child in children:
         assert child.wait(timeout=300) == 0
@@ -49,3 +49,28 @@ def test_two_ranks_match_one_gpu_on_the_same_global_batch(tmp_path):
     # from the third step on gradients are exchanged while backward still runs
     assert int(ranks[0]["overlapped"]) > 0
     assert int(ranks[0]["late"]) >= 2 * len(names)
+
+
+@pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs two GPUs")
+def test_two_ranks_accumulating_two_micro_batches_match_one_gpu(tmp_path):
+    """Global batch 8 = 2 ranks x 2 micro-batches x 2 images: each gradient is
+    exchanged once per optimiser step, after the second micro-batch has added
+    to it, and 1 / (world x micro-batches) turns the sum into the mean."""
+    single = run_world(1, str(tmp_path / "single"))[0]
+    ranks = run_world(2, str(tmp_path / "pair"), micro_batches=2)
+    names = [k for k in single.files if k.startswith("w/")]
+    for name in names:
+        np.testing.assert_array_equal(ranks[0][name], ranks[1][name])
+        keep = np.ones(single[name].shape[-1], bool)
+        if name.endswith("query_key_value_bias"):
+            keep[32:64] = False
+        np.testing.assert_allclose(ranks[0][name][..., keep],
+                                   single[name][..., keep], rtol=0, atol=2e-4,
+                                   err_msg=name)
+    np.testing.assert_allclose(
+        (ranks[0]["losses"] + ranks[1]["losses"]) / 2, single["losses"],
+        rtol=0, atol=1e-4)
+    # exactly one exchange per parameter and optimiser step (not one per
+    # micro-batch), overlapped with backward once the schedule is known
+    assert int(ranks[0]["overlapped"]) > 0
+    assert int(ranks[0]["overlapped"]) + int(ranks[0]["late"]) == STEPS * len(names)

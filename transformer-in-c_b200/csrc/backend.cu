@@ -178,6 +178,8 @@ struct CudaBackend {
     std::vector<PendingOp> pending_ops;
     std::vector<cudaEvent_t> free_events;
     DataParallel *dp = nullptr;
+    // 1 / (micro-batches whose gradients one optimiser step consumes).
+    float accumulation_inverse = 1.0f;
     // Ops that launched work so far (see ColumnSumMemo).
     unsigned long long epoch = 0;
     ColumnSumMemo column_memo;
@@ -1982,6 +1984,8 @@ int op_adamw_step_parameters(void *context,
                                             device_grads.data(), counts.data(),
                                             count);
     }
+    // Gradient accumulation: the gradients are sums over micro-batches as well.
+    inverse_world *= backend->accumulation_inverse;
     const bool needs_scale = max_gradient_norm > 0.0f || inverse_world != 1.0f;
     const float *scale = nullptr;
     float *partials = nullptr, *scale_out = nullptr;
@@ -2473,6 +2477,19 @@ extern "C" void vitb200_dp_counters(CudaBackend *backend,
                                     unsigned long long *bytes) {
     dp_counters(backend ? backend->dp : nullptr, all_reduce_calls,
                 overlapped_tensors, late_tensors, bytes);
+}
+
+extern "C" int vitb200_set_gradient_accumulation(CudaBackend *backend,
+                                                 int micro_batches) {
+    if (!cuda_backend_available(backend) || micro_batches < 1) {
+        return -1;
+    }
+    const float inverse = 1.0f / float(micro_batches);
+    if (inverse != backend->accumulation_inverse) {
+        backend->accumulation_inverse = inverse;
+        dp_forget_schedule(backend->dp);
+    }
+    return 0;
 }
 
 extern "C" void vitb200_set_gemm_precision(int precision) {

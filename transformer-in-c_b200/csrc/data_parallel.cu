@@ -81,7 +81,8 @@ struct Gradient {
     float *device = nullptr;
     size_t count = 0;
     int producers_this_step = 0;
-    bool overlap = false;   // exactly one producer per step: safe to reduce early
+    int expected_producers = 0;  // producers seen in the previous step
+    bool overlap = false;   // the producer count is known: safe to reduce early
     bool reduced = false;
 };
 
@@ -217,7 +218,8 @@ void dp_gradient_produced(DataParallel *dp, const void *host_grad,
     }
     Gradient &gradient = found->second;
     gradient.producers_this_step += 1;
-    if (gradient.overlap && !gradient.reduced && gradient.count == count) {
+    if (gradient.overlap && !gradient.reduced && gradient.count == count &&
+        gradient.producers_this_step == gradient.expected_producers) {
         gradient.device = device_grad;
         gradient.reduced = true;
         dp->overlapped += 1;
@@ -234,8 +236,9 @@ float dp_before_optimizer(DataParallel *dp, const void *const *host_grads,
     dp->optimizer_calls += 1;
     for (size_t i = 0; i < parameters; ++i) {
         Gradient &gradient = dp->gradients[host_grads[i]];
-        if (gradient.reduced && gradient.producers_this_step > 1) {
-            // A second op added to a gradient after it had been exchanged: the
+        if (gradient.reduced &&
+            gradient.producers_this_step > gradient.expected_producers) {
+            // Another op added to a gradient after it had been exchanged: the
             // sum on the wire is incomplete.  This model never does it; refuse
             // to continue rather than train on wrong gradients.
             fprintf(stderr,
@@ -247,10 +250,14 @@ float dp_before_optimizer(DataParallel *dp, const void *const *host_grads,
             dp->late += 1;
             enqueue(dp, device_grads[i], counts[i]);
         }
-        // From the second observed step on, gradients with exactly one
-        // producer are exchanged as soon as that producer has been enqueued.
-        gradient.overlap =
-            dp->optimizer_calls >= 2 && gradient.producers_this_step == 1;
+        // Once two steps in a row have written a gradient the same number of
+        // times (one op per micro-batch), it is exchanged as soon as the last
+        // of those ops has been enqueued.
+        gradient.overlap = dp->optimizer_calls >= 2 &&
+                           gradient.producers_this_step >= 1 &&
+                           gradient.producers_this_step ==
+                               gradient.expected_producers;
+        gradient.expected_producers = gradient.producers_this_step;
         gradient.device = device_grads[i];
         gradient.count = counts[i];
         gradient.producers_this_step = 0;
@@ -261,6 +268,17 @@ float dp_before_optimizer(DataParallel *dp, const void *const *host_grads,
     check_cuda(cudaStreamWaitEvent(dp->compute, dp->exchanged, 0),
                "cudaStreamWaitEvent");
     return 1.0f / float(dp->world);
+}
+
+void dp_forget_schedule(DataParallel *dp) {
+    if (!dp) {
+        return;
+    }
+    dp->optimizer_calls = 0;
+    for (auto &entry : dp->gradients) {
+        entry.second.overlap = false;
+        entry.second.expected_producers = 0;
+    }
 }
 
 void dp_counters(const DataParallel *dp, unsigned long long *all_reduce_calls,

@@ -4,9 +4,10 @@
 //
 // The host program is unaware of it.  It keeps calling the op table; the
 // backend learns which gradient buffers belong to parameters from the
-// optimiser call (`adamw_step_parameters` lists them), and from the second step
-// on it starts reducing a gradient as soon as the single op that produces it
-// has been enqueued:
+// optimiser call (`adamw_step_parameters` lists them) and counts the ops that
+// write each one between two optimiser calls (one per micro-batch); once that
+// count has repeated it starts reducing a gradient as soon as the last op that
+// adds to it has been enqueued:
 //
 //   compute stream   ... dW GEMM | record event ........ | wait comm | clip + AdamW
 //   comm stream                  | wait event, all-reduce bucket ... |
@@ -47,6 +48,11 @@ void dp_gradient_produced(DataParallel *dp, const void *host_grad,
 float dp_before_optimizer(DataParallel *dp, const void *const *host_grads,
                           float *const *device_grads, const size_t *counts,
                           size_t parameters);
+
+// Forgets how many ops write each gradient per step; the next two steps are
+// exchanged at the optimiser call while the counts are learnt again.  To be
+// called when the number of micro-batches per optimiser step changes.
+void dp_forget_schedule(DataParallel *dp);
 
 // Counters for tests and the bench line.
 void dp_counters(const DataParallel *dp, unsigned long long *all_reduce_calls,

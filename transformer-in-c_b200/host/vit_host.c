@@ -203,6 +203,86 @@ int vithost_train_step(VitHost *host, const float *images,
         weight_decay, class_weights, label_smoothing, loss);
 }
 
+/* One optimiser step over `micro_batches` consecutive batches of host->batch
+ * images each (gradient accumulation), composed from the reference's public
+ * pieces in the order of vit_model_train_batch_smoothed (vit.c:1094-1121): the
+ * parameter gradients are zeroed once, every micro-batch runs zero-cache /
+ * upload / forward / loss / backward and adds into them, and one
+ * ops_adamw_step_parameters call with the reference's constants (vit.c:1085,
+ * 1102) follows.  Each micro-batch loss is a mean over its rows
+ * (ops.c:1067-1070), so the accumulated gradient is `micro_batches` times the
+ * gradient of the mean loss over all images: with `scale_on_host` the
+ * gradients are divided on the host before the optimiser (CPU models);
+ * without it the device backend must have been told the count
+ * (vitb200_set_gradient_accumulation), which folds the factor into its clip
+ * scale.  *loss receives the mean of the micro-batch losses. */
+int vithost_train_step_accumulated(VitHost *host, const float *images,
+                                   const size_t *labels, size_t micro_batches,
+                                   float learning_rate, float weight_decay,
+                                   const float *class_weights,
+                                   float label_smoothing, int scale_on_host,
+                                   float *loss) {
+    if (!host || !images || !labels || !loss || micro_batches == 0) {
+        return -1;
+    }
+    ViTModelCache *cache = &host->cache;
+    const ViTConfig *config = &host->model.config;
+    const size_t image_floats =
+        config->channels * config->height * config->width;
+    double loss_sum = 0.0;
+    vit_model_zero_grad(&host->model);
+    for (size_t micro = 0; micro < micro_batches; ++micro) {
+        const float *batch_images = images + micro * host->batch * image_floats;
+        const int result = zero_cache_gradients(cache) ||
+            ops_upload_labels(&cache->targets, labels + micro * host->batch) ||
+            (class_weights &&
+             ops_upload_values(&cache->class_weights, class_weights)) ||
+            vit_model_forward(&host->model, batch_images, host->batch, cache) ||
+            ops_softmax_cross_entropy_tensor(
+                &cache->logits, &cache->targets,
+                class_weights ? &cache->class_weights : NULL, label_smoothing,
+                &cache->loss, &cache->logits) ||
+            vit_model_backward(&host->model, batch_images, cache, NULL);
+        if (result != 0) {
+            ops_synchronize();
+            return result;
+        }
+        if (micro + 1 < micro_batches) {
+            /* The next micro-batch overwrites the loss tensor. */
+            ops_synchronize();
+            loss_sum += cache->loss.data[0];
+        }
+    }
+    if (scale_on_host && micro_batches > 1) {
+        ops_synchronize();
+        const float inverse = 1.0f / (float)micro_batches;
+        for (size_t p = 0; p < host->parameter_count; ++p) {
+            Tensor *value = &host->parameters[p]->value;
+            const size_t count = tensor_numel(value);
+            for (size_t i = 0; i < count; ++i) {
+                value->grad[i] *= inverse;
+            }
+        }
+    }
+    float *decays = malloc(host->parameter_count * sizeof(*decays));
+    if (!decays) {
+        return -1;
+    }
+    for (size_t p = 0; p < host->parameter_count; ++p) {
+        decays[p] = host->weight_decay_mask[p] * weight_decay;
+    }
+    const int result = ops_adamw_step_parameters(
+        host->parameters, decays, host->parameter_count, learning_rate, 0.9f,
+        0.999f, 1e-8f, 1.0f);
+    free(decays);
+    ops_synchronize();
+    if (result == 0) {
+        loss_sum += cache->loss.data[0];
+        *loss = (float)(loss_sum / (double)micro_batches);
+    }
+    return result;
+}
+
 /* Forward only; copies the [batch, classes] logits out. */
 int vithost_forward(VitHost *host, const float *images, float *logits) {
     const int result =

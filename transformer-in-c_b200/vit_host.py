@@ -62,6 +62,11 @@ def load_host_library(path):
     lib.vithost_train_step.argtypes = [
         ctypes.c_void_p, _float_p, ctypes.POINTER(_size_t), ctypes.c_float,
         ctypes.c_float, _float_p, ctypes.c_float, _float_p]
+    lib.vithost_train_step_accumulated.restype = ctypes.c_int
+    lib.vithost_train_step_accumulated.argtypes = [
+        ctypes.c_void_p, _float_p, ctypes.POINTER(_size_t), _size_t,
+        ctypes.c_float, ctypes.c_float, _float_p, ctypes.c_float, ctypes.c_int,
+        _float_p]
     lib.vithost_forward.restype = ctypes.c_int
     lib.vithost_forward.argtypes = [ctypes.c_void_p, _float_p, _float_p]
     lib.vithost_set_parameter.restype = ctypes.c_int
@@ -131,6 +136,9 @@ def load_backend_library():
     lib.vitb200_dp_counters.restype = None
     lib.vitb200_dp_counters.argtypes = [ctypes.c_void_p] + \
         [ctypes.POINTER(ctypes.c_ulonglong)] * 4
+    lib.vitb200_set_gradient_accumulation.restype = ctypes.c_int
+    lib.vitb200_set_gradient_accumulation.argtypes = [ctypes.c_void_p,
+                                                      ctypes.c_int]
     lib.vitb200_set_gemm_precision.restype = None
     lib.vitb200_set_gemm_precision.argtypes = [ctypes.c_int]
     lib.vitb200_tensor_core_status.restype = ctypes.c_int
@@ -208,6 +216,13 @@ class Backend:
                                      *[ctypes.byref(v) for v in values])
         names = ["all_reduce_calls", "overlapped_tensors", "late_tensors", "bytes"]
         return {n: int(v.value) for n, v in zip(names, values)}
+
+    def set_gradient_accumulation(self, micro_batches):
+        """The following optimiser steps consume gradients summed over this
+        many forward/backward passes (VitHost.train_step_accumulated)."""
+        if self.lib.vitb200_set_gradient_accumulation(
+                self.handle, int(micro_batches)) != 0:
+            raise ValueError("vitb200_set_gradient_accumulation failed")
 
     def set_gemm_precision(self, precision):
         """0 auto, 1 FP32 FMA, 2 TF32 tensor cores, -1 start-up default."""
@@ -379,6 +394,24 @@ class VitHost:
             label_smoothing, ctypes.byref(loss))
         if status != 0:
             raise RuntimeError("vit_model_train_batch_smoothed failed")
+        return float(loss.value)
+
+    def train_step_accumulated(self, images, labels, micro_batches, lr,
+                               weight_decay, weights=None, label_smoothing=0.0,
+                               scale_on_host=False):
+        """One optimiser step over `micro_batches` x batch images (contiguous
+        float32 / uintp arrays).  On a device model the backend must have been
+        told the count (Backend.set_gradient_accumulation); a CPU model passes
+        scale_on_host=True instead."""
+        loss = ctypes.c_float()
+        status = self.lib.vithost_train_step_accumulated(
+            self.handle, images.ctypes.data_as(_float_p),
+            labels.ctypes.data_as(ctypes.POINTER(_size_t)), int(micro_batches),
+            lr, weight_decay,
+            weights.ctypes.data_as(_float_p) if weights is not None else None,
+            label_smoothing, int(scale_on_host), ctypes.byref(loss))
+        if status != 0:
+            raise RuntimeError("vithost_train_step_accumulated failed")
         return float(loss.value)
 
     def forward(self, images):
