@@ -7,7 +7,10 @@ One step = one call of the reference's vit_model_train_batch_smoothed on one
 synthetic batch.  The host side is the reference's unmodified C code
 (oracle/_ref/libvithost.so, built from the reference sources); with the B200
 backend enabled every op it dispatches runs as one of this repository's CUDA
-kernels.  Prints ONE JSON line (rank 0).
+kernels.  Prints ONE JSON line (rank 0).  Workloads quoted on a fixed global
+batch (cfg5: 4096 images per optimiser step whatever the GPU count) run each
+rank's share as micro-batches with gradient accumulation, one optimiser call
+and one gradient exchange per step ("scaling": "strong").
 
 Timed quantities
   e2e    wall clock over K steps called with HOST buffers: per step the host
@@ -44,6 +47,10 @@ WORKLOADS = {
     "cfg4": ((1, 64, 64, 2, 384, 6, 12, 11), 64),
     "cfg5": ((1, 28, 28, 2, 512, 8, 12, 11), 512),
 }
+# Workloads quoted on a fixed GLOBAL batch: every rank takes global / world
+# images per optimiser step, in micro-batches of the size above (gradient
+# accumulation), so the total work is the same at every GPU count.
+GLOBAL_BATCH = {"cfg5": 4096}
 LR, WD, SMOOTHING = 1e-3, 0.05, 0.1
 TENSOR_OPS = {"gemm", "gemm_backward", "multi_head_attention",
               "multi_head_attention_backward"}
@@ -297,6 +304,9 @@ def main():
     parser.add_argument("--batch", type=int, default=0,
                         help="override the workload's batch (per GPU)")
     parser.add_argument("--no-cpu-baseline", action="store_true")
+    parser.add_argument("--global-batch", type=int, default=-1,
+                        help="images per optimiser step over all GPUs; 0 = one "
+                             "micro-batch per GPU, -1 = the workload's own")
     args = parser.parse_args()
     args.warmup = max(args.warmup, 3) if args.impl == "ours" else args.warmup
 
@@ -306,6 +316,14 @@ def main():
     config, batch = WORKLOADS[args.workload]
     if args.batch:
         batch = args.batch
+    global_batch = (GLOBAL_BATCH.get(args.workload, 0) if args.global_batch < 0
+                    else args.global_batch)
+    micro_batches = 1
+    if global_batch:
+        if global_batch % (world * batch):
+            parser.error(f"global batch {global_batch} is not a multiple of "
+                         f"{world} GPUs x micro-batch {batch}")
+        micro_batches = global_batch // (world * batch)
 
     vh = load_module("vitb200_vit_host", os.path.join(PACKAGE, "vit_host.py"))
     if args.impl == "reference":
@@ -330,9 +348,10 @@ def main():
         dist.broadcast_object_list(holder, src=0)
         backend.dp_init(rank, world, holder[0])
     backend.enable()
+    backend.set_gradient_accumulation(micro_batches)
     host = vh.VitHost(host_lib, config, batch)
-    images, labels = vh.synthetic_batch(batch, config[1], config[2], config[7],
-                                        1234 + rank)
+    images, labels = vh.synthetic_batch(batch * micro_batches, config[1],
+                                        config[2], config[7], 1234 + rank)
     keep_images, images = pinned_like(images)
     keep_labels, labels = pinned_like(labels.astype(np.int64))
     labels = labels.view(np.uintp)
@@ -343,6 +362,9 @@ def main():
         torch.cuda.synchronize()
 
     def step():
+        if micro_batches > 1:
+            return host.train_step_accumulated(images, labels, micro_batches,
+                                               LR, WD, None, SMOOTHING)
         return host.train_step_raw(images, labels, LR, WD, None, SMOOTHING)
 
     for _ in range(args.warmup):
@@ -378,7 +400,7 @@ def main():
     if world > 1:
         dist.all_reduce(busy, op=dist.ReduceOp.MAX)
     busy_ms, e2e_seconds = float(busy[0]), float(busy[1])
-    images_per_step = batch * world
+    images_per_step = batch * micro_batches * world
     value = images_per_step * args.steps / (busy_ms / 1e3)
     e2e_value = images_per_step * args.steps / e2e_seconds
 
@@ -395,8 +417,11 @@ def main():
                "flops": sum(e["flops"] for e in parts), "calls": kernel_launches}
         kernel_name = "gemm_tc_kernel (ops gemm + gemm_backward)"
     seconds = top["ms"] / 1e3
+    # The contractions take TF32 operands, whose dense rate is half the BF16
+    # rate MEASURED_PEAKS.json holds: that half decides which roof is nearer;
+    # `peak` stays the measured BF16 figure and `frac_of_tf32_peak` is added.
     tensor_bound = (top["name"] in TENSOR_OPS | {"gemm_tc_kernel"} and
-                    top["flops"] / (tensor_peak * 1e12) >
+                    top["flops"] / (0.5 * tensor_peak * 1e12) >
                     top["bytes"] / (hbm_peak * 1e9))
     if tensor_bound:
         achieved, peak, unit = top["flops"] / seconds / 1e12, tensor_peak, "TFLOP/s"
@@ -419,17 +444,34 @@ def main():
         "launch_ms": top["ms"] / top["calls"],
         "share_of_device_time": top["ms"] / sum(e["ms"] for e in entries),
     }
+    if tensor_bound:
+        roofline["frac_of_tf32_peak"] = achieved / (0.5 * tensor_peak)
     breakdown = {e["name"]: round(e["ms"] / args.steps, 4)
                  for e in sorted(entries, key=lambda e: -e["ms"])[:24]}
+    # Every op against the roofline that bounds it: algorithmic bytes (and
+    # flops for the contractions) over the CUDA-event time of its launches.
+    by_op = {}
+    for e in sorted(entries, key=lambda e: -e["ms"])[:16]:
+        if e["ms"] <= 0.0:
+            continue
+        op = {"ms_per_step": round(e["ms"] / args.steps, 4),
+              "launches_per_step": round(e["calls"] / args.steps, 1),
+              "GB/s": round(e["bytes"] / e["ms"] / 1e6, 1),
+              "frac_hbm": round(e["bytes"] / e["ms"] / 1e6 / hbm_peak, 3)}
+        if e["flops"] > 0.0:
+            op["TFLOP/s"] = round(e["flops"] / e["ms"] / 1e9, 1)
+        by_op[e["name"]] = op
 
     line = {
         "metric": "train images/s", "value": value, "unit": "images/s",
         "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
         "ms_per_step": busy_ms / args.steps, "higher_is_better": True,
-        "scaling": "weak", "vs_baseline": None, "dtype": "f32",
-        "data": "synthetic",
+        "scaling": "strong" if global_batch else "weak", "vs_baseline": None,
+        "dtype": "f32", "data": "synthetic",
         "config": {"workload": args.workload, "vit": list(config),
-                   "batch_per_gpu": batch, "global_batch": images_per_step,
+                   "batch_per_gpu": batch * micro_batches,
+                   "micro_batch": batch, "micro_batches_per_step": micro_batches,
+                   "global_batch": images_per_step,
                    "parallelism": f"dp{world}" + (
                        " (batch sharded by sample, NCCL all-reduce of gradients "
                        "overlapped with backward)" if world > 1 else ""),
@@ -443,6 +485,7 @@ def main():
         "gpu_launches": launches,
         "roofline": roofline,
         "ms_per_step_by_op": breakdown,
+        "roofline_by_op": by_op,
         "loss": loss,
     }
     if rank == 0 and not args.no_cpu_baseline and world == 1:
