@@ -894,7 +894,10 @@ int op_layer_norm(void *context, const vitb200_tensor *input,
     float *y = view(backend, output->data, Access::Overwrite);
     if (fuse) {
         backend->fused_residuals += 1;
-        OpScope scope(backend, "layer_norm", 20.0 * double(numel(input)), 0.0);
+        // Two reads (the addends), two writes (their sum, the normalised
+        // rows): what the fused pass has to move, not the 12 + 8 B/elt of the
+        // two ops it stands for.
+        OpScope scope(backend, "layer_norm", 16.0 * double(numel(input)), 0.0);
         launch_layer_norm(held.a, g, b, epsilon, y, input->rows, input->cols,
                           backend->stream, held.b, held.sum);
         return 0;
