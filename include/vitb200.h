@@ -124,8 +124,10 @@ void vitb200_dp_counters(CudaBackend *backend,
  * 1 / micro_batches is folded into the clip scale, like 1 / world, so the norm
  * that is clipped and the update are those of the mean gradient.  With data
  * parallelism each gradient's all-reduce starts when the last micro-batch's
- * op has added to it.  1 restores plain steps.  0 on success, -1 on a bad
- * argument. */
+ * op has added to it (after a change of the count the exchange takes two
+ * steps to learn the new schedule and runs at the optimiser call meanwhile).
+ * To be called between optimiser steps, not between the micro-batches of one.
+ * 1 restores plain steps.  0 on success, -1 on a bad argument. */
 int vitb200_set_gradient_accumulation(CudaBackend *backend, int micro_batches);
 
 /* Operand precision of the dense products issued through the op table:

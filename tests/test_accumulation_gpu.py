@@ -13,7 +13,7 @@ LR, WD, SMOOTHING = 1e-3, 0.05, 0.1
 CASES = [
     # config, micro-batches, batch per micro-batch
     ((1, 28, 28, 4, 32, 4, 2, 11), 3, 4),
-    ((1, 28, 28, 2, 64, 2, 1, 11), 2, 2),   # 197 tokens: streaming attention
+    ((1, 28, 28, 2, 64, 2, 1, 11), 2, 2),   # 197 tokens: the long-sequence attention path
 ]
 
 
