@@ -88,19 +88,21 @@ layer_norm_kernel(const float *__restrict__ x, const float *__restrict__ gamma,
 #pragma unroll
         for (int r = 0; r < R; ++r) {
             const size_t row = first + r * warps;
-            if (row < rows) {
-                load_row<NV>(x + row * cols, cols, lane, v[r]);
-                if (addend) {
-                    load_row<NV>(addend + row * cols, cols, lane, w[r]);
-                }
+            // cols = 0 makes load_row fill with zeros without touching memory.
+            const size_t width = row < rows ? cols : 0;
+            const size_t offset = row < rows ? row * cols : 0;
+            load_row<NV>(x + offset, width, lane, v[r]);
+            if (addend) {
+                load_row<NV>(addend + offset, width, lane, w[r]);
             }
         }
+        // Rows past the end are computed on zeros and never stored, so that
+        // the rows in flight form one straight-line region whose shuffle
+        // reductions the scheduler can interleave.
 #pragma unroll
         for (int r = 0; r < R; ++r) {
             const size_t row = first + r * warps;
-            if (row >= rows) {
-                break;
-            }
+            const bool live = row < rows;
             if (addend) {
 #pragma unroll
                 for (int j = 0; j < NV; ++j) {
@@ -109,7 +111,7 @@ layer_norm_kernel(const float *__restrict__ x, const float *__restrict__ gamma,
                     v[r][j].z += w[r][j].z;
                     v[r][j].w += w[r][j].w;
                     const size_t col = size_t(j) * 128 + lane * 4;
-                    if (col < cols) {
+                    if (live && col < cols) {
                         *reinterpret_cast<float4 *>(sum + row * cols + col) = v[r][j];
                     }
                 }
@@ -119,7 +121,7 @@ layer_norm_kernel(const float *__restrict__ x, const float *__restrict__ gamma,
 #pragma unroll
             for (int j = 0; j < NV; ++j) {
                 const size_t col = size_t(j) * 128 + lane * 4;
-                if (col < cols) {
+                if (live && col < cols) {
                     float4 out;
                     out.x = (v[r][j].x - mean) * inverse_std * g[j].x + b[j].x;
                     out.y = (v[r][j].y - mean) * inverse_std * g[j].y + b[j].y;
@@ -162,20 +164,23 @@ layer_norm_backward_kernel(const float *__restrict__ x,
 #pragma unroll
         for (int r = 0; r < R; ++r) {
             const size_t row = first + r * warps;
-            if (row < rows) {
-                load_row<NV>(x + row * cols, cols, lane, vs[r]);
-                load_row<NV>(dy + row * cols, cols, lane, us[r]);
-                if (base) {
-                    load_row<NV>(base + row * cols, cols, lane, bases[r]);
-                }
+            // cols = 0 makes load_row fill with zeros without touching memory.
+            const size_t width = row < rows ? cols : 0;
+            const size_t offset = row < rows ? row * cols : 0;
+            load_row<NV>(x + offset, width, lane, vs[r]);
+            load_row<NV>(dy + offset, width, lane, us[r]);
+            if (base) {
+                load_row<NV>(base + offset, width, lane, bases[r]);
             }
         }
+        // Rows past the end are computed on zeros (they add nothing to the
+        // column sums) and never stored, so that the rows in flight form one
+        // straight-line region whose shuffle reductions the scheduler can
+        // interleave.
 #pragma unroll
         for (int r = 0; r < R; ++r) {
             const size_t row = first + r * warps;
-            if (row >= rows) {
-                break;
-            }
+            const bool live = row < rows;
             float4 (&v)[NV] = vs[r];
             float4 (&u)[NV] = us[r];
             float mean, inverse_std;
@@ -209,7 +214,7 @@ layer_norm_backward_kernel(const float *__restrict__ x,
 #pragma unroll
             for (int j = 0; j < NV; ++j) {
                 const size_t col = size_t(j) * 128 + lane * 4;
-                if (col < cols) {
+                if (live && col < cols) {
                     float4 d = base ? bases[r][j]
                                     : make_float4(0.f, 0.f, 0.f, 0.f);
                     d.x += inverse_std * (u[j].x - s1 - v[j].x * s2);
