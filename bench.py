@@ -211,6 +211,50 @@ def augmentation_measurement(backend, host_lib, batch, channels, height, width,
     return result
 
 
+def dataset_measurement(vh, backend, batch, height, width, steps):
+    """Batches out of a device-resident dataset (include/vitb200_dataset.h):
+    gather by the shuffled order, integer -> [0, 1] -> normalised float, the
+    work the reference's trainer does on the host once per dataset and per
+    epoch (examples/organ_smnist.c:75-139).  `value` from the kernel's own CUDA
+    events, `e2e` with a page-locked host destination (copy inside the call);
+    algorithmic bytes: one stored byte read and one float written per pixel."""
+    rng = np.random.RandomState(5)
+    samples = 8 * batch
+    pixels = rng.randint(0, 256, size=(samples, height, width)).astype(np.uint16)
+    labels = rng.randint(0, 11, size=samples).astype(np.uintp)
+    dataset = vh.Dataset(backend, pixels=pixels, labels=labels)
+    mean, inverse = dataset.statistics()
+    dataset.shuffle(1)
+    keep, destination = pinned_like(np.zeros((batch, height * width), np.float32))
+    for index in range(3):
+        dataset.batch(index * batch, batch, mean, inverse, destination)
+    backend.profile(True)
+    start = time.perf_counter()
+    for index in range(steps):
+        status, _, _ = dataset.batch((index % 8) * batch, batch, mean, inverse,
+                                     destination)
+        assert status == 0
+    elapsed = time.perf_counter() - start
+    kernel_ms = sum(e["ms"] for e in backend.profile_entries()
+                    if e["name"] == "dataset_batch")
+    backend.profile(False)
+    dataset.close()
+    del keep
+    hbm_peak, _, peak_source = measured_peaks()
+    moved = 5.0 * batch * height * width * steps
+    result = {
+        "metric": "dataset batch images/s", "unit": "images/s", "batch": batch,
+        "samples": samples, "storage": "uint8",
+        "value": batch * steps / (kernel_ms / 1e3),
+        "e2e": {"value": batch * steps / elapsed, "h2d_bytes_per_step": 0,
+                "d2h_bytes_per_step": 4 * batch * height * width},
+        "roofline": {"bound": "hbm", "achieved": moved / (kernel_ms / 1e3) / 1e9,
+                     "peak": hbm_peak, "unit": "GB/s", "peak_source": peak_source},
+    }
+    result["roofline"]["frac"] = result["roofline"]["achieved"] / hbm_peak
+    return result
+
+
 def reference_cuda_rate(config, batch, warmup=2, steps=5):
     """Secondary baseline: the reference's own CUDA backend (src/cuda_backend.cu,
     cuBLAS FP32 SGEMM + managed memory + its SIMT kernels) compiled unmodified
@@ -505,6 +549,9 @@ def main():
         line["augmentation"] = augmentation_measurement(
             backend, host_lib, batch, config[0], config[1], config[2],
             args.steps, with_cpu=not args.no_cpu_baseline)
+    if rank == 0 and world == 1:
+        line["dataset"] = dataset_measurement(vh, backend, batch, config[1],
+                                              config[2], args.steps)
     if world > 1:
         line["dp"] = backend.dp_counters()
     host.close()

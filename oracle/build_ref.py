@@ -19,6 +19,12 @@ this repository) with the flags of the reference Makefile:2
                   tests/checkpoint_roundtrip.c (ours) on the reference's
                   vit_model_save / vit_model_load, linked like test_device
 
+  libtrainer_pieces.so
+                  tests/trainer_pieces.c (ours) around the reference's trainer
+                  source and loader: shuffle, pixel statistics, normalisation
+                  and vision_dataset_load_pgm_csv, the checker of the
+                  device-resident dataset
+
   reference_cuda_step
                   oracle/reference_cuda_step.c (ours, a timing driver) with the
                   reference's own src/cuda_backend.cu compiled for sm_100a and
@@ -57,6 +63,11 @@ def build(reference_root="/root/reference"):
     run(["gcc", *flags, "-o", os.path.join(OUT, "test_vision"),
          os.path.join(reference_root, "tests", "test_vision.c"), *core,
          *[os.path.join(source, name) for name in EXTRA], "-lm"])
+    run(["gcc", *flags, "-w", "-shared", "-I" + os.path.join(reference_root, "examples"),
+         "-o", os.path.join(OUT, "libtrainer_pieces.so"),
+         os.path.join(REPO, "tests", "trainer_pieces.c"), *core,
+         os.path.join(source, "dataset.c"),
+         os.path.join(source, "augmentation.c"), "-lm"])
     library = os.path.join(PACKAGE, "libvitb200.so")
     if os.path.exists(library):
         run(["gcc", *flags, "-DENABLE_CUDA", "-o",

@@ -10,10 +10,12 @@
 #include "../../include/vitb200.h"
 #include "../../include/vitb200_host_abi.h"
 #include "../../include/vitb200_augmentation.h"
+#include "../../include/vitb200_dataset.h"
 
 #include "augmentation.h"
 #include "coherence.h"
 #include "data_parallel.h"
+#include "dataset.h"
 #include "gemm.h"
 #include "gemm_tc.h"
 #include "kernels.h"
@@ -2417,6 +2419,274 @@ extern "C" int vitb200_data_augmentation_translate(
     }
     augment_finish(backend, destination, out, count, staged);
     return 0;
+}
+
+// ------------------------------------------------------------ dataset
+
+// Samples on the device as 8- or 16-bit integers, the order table next to
+// them; labels and the order's master copy stay on the host, where the
+// shuffle draws and the label upload happen.
+struct vitb200_dataset {
+    CudaBackend *backend = nullptr;
+    size_t samples = 0, height = 0, width = 0;
+    bool wide = false;
+    void *pixels = nullptr;
+    uint16_t *max_values = nullptr;
+    uint32_t *order = nullptr;
+    bool order_on_device = false;   // false: identity, or a shuffle not yet uploaded
+    bool shuffled = false;
+    std::vector<uint32_t> host_order;
+    std::vector<size_t> labels;
+    float mean = 0.0f, inverse_std = 1.0f;
+    Scratch staging;
+};
+
+namespace {
+
+int dataset_create(CudaBackend *backend, ParsedDataset &parsed,
+                   vitb200_dataset **out) {
+    vitb200_dataset *dataset = new vitb200_dataset();
+    dataset->backend = backend;
+    dataset->samples = parsed.samples();
+    dataset->height = parsed.height;
+    dataset->width = parsed.width;
+    dataset_statistics(parsed, &dataset->mean, &dataset->inverse_std);
+    for (uint16_t max_value : parsed.max_values) {
+        dataset->wide = dataset->wide || max_value >= 256;
+    }
+    // A binary file may hold bytes above its own maximum; they still fit.
+    const size_t count = parsed.pixels.size();
+    check(cudaSetDevice(backend->device), "cudaSetDevice");
+    if (dataset->wide) {
+        check(cudaMalloc(&dataset->pixels, count * sizeof(uint16_t)), "cudaMalloc");
+        check(cudaMemcpy(dataset->pixels, parsed.pixels.data(),
+                         count * sizeof(uint16_t), cudaMemcpyHostToDevice),
+              "cudaMemcpy");
+    } else {
+        std::vector<uint8_t> narrow(count);
+        for (size_t i = 0; i < count; ++i) {
+            narrow[i] = uint8_t(parsed.pixels[i]);
+        }
+        check(cudaMalloc(&dataset->pixels, count ? count : 1), "cudaMalloc");
+        check(cudaMemcpy(dataset->pixels, narrow.data(), count,
+                         cudaMemcpyHostToDevice),
+              "cudaMemcpy");
+    }
+    check(cudaMalloc(&dataset->max_values, dataset->samples * sizeof(uint16_t)),
+          "cudaMalloc");
+    check(cudaMemcpy(dataset->max_values, parsed.max_values.data(),
+                     dataset->samples * sizeof(uint16_t), cudaMemcpyHostToDevice),
+          "cudaMemcpy");
+    check(cudaMalloc(&dataset->order, dataset->samples * sizeof(uint32_t)),
+          "cudaMalloc");
+    dataset->host_order.resize(dataset->samples);
+    for (size_t i = 0; i < dataset->samples; ++i) {
+        dataset->host_order[i] = uint32_t(i);
+    }
+    dataset->labels.swap(parsed.labels);
+    *out = dataset;
+    return 0;
+}
+
+}  // namespace
+
+extern "C" int vitb200_dataset_load_pgm_csv(CudaBackend *backend,
+                                            const char *manifest_path,
+                                            vitb200_dataset **dataset) {
+    if (dataset) {
+        *dataset = nullptr;
+    }
+    ParsedDataset parsed;
+    if (!dataset || !cuda_backend_available(backend) ||
+        dataset_parse_pgm_csv(manifest_path, &parsed) != 0 ||
+        parsed.samples() > UINT_MAX) {
+        return -1;
+    }
+    return dataset_create(backend, parsed, dataset);
+}
+
+extern "C" int vitb200_dataset_from_integers(
+    CudaBackend *backend, const unsigned short *pixels,
+    const unsigned short *max_values, const size_t *labels, size_t sample_count,
+    size_t height, size_t width, vitb200_dataset **dataset) {
+    if (dataset) {
+        *dataset = nullptr;
+    }
+    if (!dataset || !cuda_backend_available(backend) || !pixels || !labels ||
+        sample_count == 0 || height == 0 || width == 0 ||
+        sample_count > UINT_MAX) {
+        return -1;
+    }
+    ParsedDataset parsed;
+    parsed.height = height;
+    parsed.width = width;
+    parsed.pixels.assign(pixels, pixels + sample_count * height * width);
+    parsed.labels.assign(labels, labels + sample_count);
+    parsed.max_values.assign(sample_count, uint16_t(255));
+    for (size_t i = 0; max_values && i < sample_count; ++i) {
+        if (max_values[i] == 0) {
+            return -1;
+        }
+        parsed.max_values[i] = max_values[i];
+    }
+    return dataset_create(backend, parsed, dataset);
+}
+
+extern "C" void vitb200_dataset_free(vitb200_dataset *dataset) {
+    if (!dataset) {
+        return;
+    }
+    cudaStreamSynchronize(dataset->backend->stream);
+    cudaFree(dataset->pixels);
+    cudaFree(dataset->max_values);
+    cudaFree(dataset->order);
+    free_scratch(dataset->staging);
+    delete dataset;
+}
+
+extern "C" size_t vitb200_dataset_sample_count(const vitb200_dataset *dataset) {
+    return dataset ? dataset->samples : 0;
+}
+
+extern "C" size_t vitb200_dataset_height(const vitb200_dataset *dataset) {
+    return dataset ? dataset->height : 0;
+}
+
+extern "C" size_t vitb200_dataset_width(const vitb200_dataset *dataset) {
+    return dataset ? dataset->width : 0;
+}
+
+extern "C" size_t vitb200_dataset_channels(const vitb200_dataset *dataset) {
+    return dataset ? 1 : 0;
+}
+
+extern "C" int vitb200_dataset_statistics(const vitb200_dataset *dataset,
+                                          float *mean,
+                                          float *inverse_standard_deviation) {
+    if (!dataset || !mean || !inverse_standard_deviation) {
+        return -1;
+    }
+    *mean = dataset->mean;
+    *inverse_standard_deviation = dataset->inverse_std;
+    return 0;
+}
+
+extern "C" int vitb200_dataset_shuffle(vitb200_dataset *dataset,
+                                       unsigned long *state) {
+    if (!dataset || !state) {
+        return -1;
+    }
+    dataset_shuffle(dataset->host_order, state);
+    dataset->shuffled = true;
+    dataset->order_on_device = false;
+    return 0;
+}
+
+extern "C" int vitb200_dataset_batch(vitb200_dataset *dataset, size_t offset,
+                                     size_t batch, float mean,
+                                     float inverse_standard_deviation,
+                                     float *images, size_t *labels) {
+    if (!dataset || !images || batch == 0 || offset > dataset->samples ||
+        batch > dataset->samples - offset ||
+        !cuda_backend_available(dataset->backend)) {
+        return -1;
+    }
+    CudaBackend *backend = dataset->backend;
+    flush_pending(backend);
+    if (dataset->shuffled && !dataset->order_on_device) {
+        // Pageable source: the copy is staged before the call returns, and it
+        // is ordered behind the batches that still read the old table.
+        check(cudaMemcpyAsync(dataset->order, dataset->host_order.data(),
+                              dataset->samples * sizeof(uint32_t),
+                              cudaMemcpyHostToDevice, backend->stream),
+              "cudaMemcpyAsync(host to device)");
+        dataset->order_on_device = true;
+    }
+    const size_t image_size = dataset->height * dataset->width;
+    const size_t count = batch * image_size;
+    const bool staged = !coherent_owns(images);
+    float *out = staged ? scratch<float>(backend, dataset->staging, count)
+                        : view(backend, images, Access::Overwrite);
+    {
+        OpScope scope(backend, "dataset_batch",
+                      double(count) * (4.0 + (dataset->wide ? 2.0 : 1.0)), 0.0);
+        launch_dataset_batch(dataset->pixels, dataset->wide, dataset->max_values,
+                             dataset->shuffled ? dataset->order : nullptr,
+                             offset, batch, image_size, mean,
+                             inverse_standard_deviation, out, backend->stream);
+    }
+    if (staged) {
+        check(cudaMemcpyAsync(images, out, count * sizeof(float),
+                              cudaMemcpyDeviceToHost, backend->stream),
+              "cudaMemcpyAsync(device to host)");
+        check(cudaStreamSynchronize(backend->stream), "cudaStreamSynchronize");
+    }
+    for (size_t i = 0; labels && i < batch; ++i) {
+        labels[i] = dataset->labels[dataset->host_order[offset + i]];
+    }
+    return 0;
+}
+
+extern "C" int vitb200_dataset_parse_pgm_csv(
+    const char *manifest_path, unsigned short **pixels,
+    unsigned short **max_values, size_t **labels, size_t *sample_count,
+    size_t *height, size_t *width) {
+    ParsedDataset parsed;
+    if (!pixels || !max_values || !labels || !sample_count || !height ||
+        !width || dataset_parse_pgm_csv(manifest_path, &parsed) != 0) {
+        return -1;
+    }
+    *pixels = static_cast<unsigned short *>(
+        malloc(parsed.pixels.size() * sizeof(unsigned short)));
+    *max_values = static_cast<unsigned short *>(
+        malloc(parsed.samples() * sizeof(unsigned short)));
+    *labels = static_cast<size_t *>(malloc(parsed.samples() * sizeof(size_t)));
+    if (!*pixels || !*max_values || !*labels) {
+        free(*pixels);
+        free(*max_values);
+        free(*labels);
+        return -1;
+    }
+    memcpy(*pixels, parsed.pixels.data(),
+           parsed.pixels.size() * sizeof(unsigned short));
+    memcpy(*max_values, parsed.max_values.data(),
+           parsed.samples() * sizeof(unsigned short));
+    memcpy(*labels, parsed.labels.data(), parsed.samples() * sizeof(size_t));
+    *sample_count = parsed.samples();
+    *height = parsed.height;
+    *width = parsed.width;
+    return 0;
+}
+
+extern "C" int vitb200_dataset_pixel_statistics(
+    const unsigned short *pixels, const unsigned short *max_values,
+    size_t sample_count, size_t image_size, float *mean,
+    float *inverse_standard_deviation) {
+    if (!pixels || !mean || !inverse_standard_deviation || sample_count == 0 ||
+        image_size == 0) {
+        return -1;
+    }
+    ParsedDataset parsed;
+    parsed.height = image_size;
+    parsed.width = 1;
+    parsed.pixels.assign(pixels, pixels + sample_count * image_size);
+    parsed.labels.assign(sample_count, 0);
+    parsed.max_values.assign(sample_count, uint16_t(255));
+    for (size_t i = 0; max_values && i < sample_count; ++i) {
+        parsed.max_values[i] = max_values[i];
+    }
+    dataset_statistics(parsed, mean, inverse_standard_deviation);
+    return 0;
+}
+
+extern "C" void vitb200_dataset_shuffle_order(unsigned int *order, size_t count,
+                                              unsigned long *state) {
+    if (!order || !state) {
+        return;
+    }
+    std::vector<uint32_t> table(order, order + count);
+    dataset_shuffle(table, state);
+    memcpy(order, table.data(), count * sizeof(uint32_t));
 }
 
 extern "C" void vitb200_fusion_counters(const CudaBackend *backend,

@@ -294,6 +294,13 @@ int vithost_forward(VitHost *host, const float *images, float *logits) {
     return result;
 }
 
+/* The cache's image tensor ([batch, channels * height * width], vit.c:837-879):
+ * memory from the tensor allocator, so with a backend enabled a device-side
+ * producer (augmentation, dataset batches) can fill it where it lives. */
+float *vithost_images_tensor(VitHost *host) {
+    return host->cache.images.data;
+}
+
 /* Overwrites one parameter's values (host write; the next device op picks the
  * new contents up). */
 int vithost_set_parameter(VitHost *host, size_t index, const float *values) {

@@ -82,6 +82,8 @@ def load_host_library(path):
         _float_p, ctypes.POINTER(ctypes.c_double)]
     lib.vithost_predict.restype = ctypes.c_int
     lib.vithost_predict.argtypes = [ctypes.c_void_p, _float_p, _size_t, _float_p]
+    lib.vithost_images_tensor.restype = ctypes.c_void_p
+    lib.vithost_images_tensor.argtypes = [ctypes.c_void_p]
     lib.ops_synchronize.restype = None
     return lib
 
@@ -139,6 +141,40 @@ def load_backend_library():
     lib.vitb200_set_gradient_accumulation.restype = ctypes.c_int
     lib.vitb200_set_gradient_accumulation.argtypes = [ctypes.c_void_p,
                                                       ctypes.c_int]
+    _ushort_p = ctypes.POINTER(ctypes.c_ushort)
+    lib.vitb200_dataset_load_pgm_csv.restype = ctypes.c_int
+    lib.vitb200_dataset_load_pgm_csv.argtypes = [
+        ctypes.c_void_p, ctypes.c_char_p, ctypes.POINTER(ctypes.c_void_p)]
+    lib.vitb200_dataset_from_integers.restype = ctypes.c_int
+    lib.vitb200_dataset_from_integers.argtypes = [
+        ctypes.c_void_p, _ushort_p, _ushort_p, ctypes.POINTER(_size_t), _size_t,
+        _size_t, _size_t, ctypes.POINTER(ctypes.c_void_p)]
+    lib.vitb200_dataset_free.restype = None
+    lib.vitb200_dataset_free.argtypes = [ctypes.c_void_p]
+    for name in ("sample_count", "height", "width", "channels"):
+        getter = getattr(lib, "vitb200_dataset_" + name)
+        getter.restype = _size_t
+        getter.argtypes = [ctypes.c_void_p]
+    lib.vitb200_dataset_statistics.restype = ctypes.c_int
+    lib.vitb200_dataset_statistics.argtypes = [ctypes.c_void_p, _float_p, _float_p]
+    lib.vitb200_dataset_shuffle.restype = ctypes.c_int
+    lib.vitb200_dataset_shuffle.argtypes = [ctypes.c_void_p,
+                                            ctypes.POINTER(ctypes.c_ulong)]
+    lib.vitb200_dataset_batch.restype = ctypes.c_int
+    lib.vitb200_dataset_batch.argtypes = [
+        ctypes.c_void_p, _size_t, _size_t, ctypes.c_float, ctypes.c_float,
+        ctypes.c_void_p, ctypes.POINTER(_size_t)]
+    lib.vitb200_dataset_parse_pgm_csv.restype = ctypes.c_int
+    lib.vitb200_dataset_parse_pgm_csv.argtypes = [
+        ctypes.c_char_p, ctypes.POINTER(_ushort_p), ctypes.POINTER(_ushort_p),
+        ctypes.POINTER(ctypes.POINTER(_size_t)), ctypes.POINTER(_size_t),
+        ctypes.POINTER(_size_t), ctypes.POINTER(_size_t)]
+    lib.vitb200_dataset_pixel_statistics.restype = ctypes.c_int
+    lib.vitb200_dataset_pixel_statistics.argtypes = [
+        _ushort_p, _ushort_p, _size_t, _size_t, _float_p, _float_p]
+    lib.vitb200_dataset_shuffle_order.restype = None
+    lib.vitb200_dataset_shuffle_order.argtypes = [
+        ctypes.POINTER(ctypes.c_uint), _size_t, ctypes.POINTER(ctypes.c_ulong)]
     lib.vitb200_set_gemm_precision.restype = None
     lib.vitb200_set_gemm_precision.argtypes = [ctypes.c_int]
     lib.vitb200_tensor_core_status.restype = ctypes.c_int
@@ -301,6 +337,96 @@ class Backend:
         return float(self.lib.vitb200_timer_end(self.handle))
 
 
+def parse_pgm_csv(lib, manifest_path):
+    """vitb200_dataset_parse_pgm_csv (no device): (status, pixels
+    [samples, height, width] uint16, max_values, labels)."""
+    pixels = ctypes.POINTER(ctypes.c_ushort)()
+    maxima = ctypes.POINTER(ctypes.c_ushort)()
+    labels = ctypes.POINTER(_size_t)()
+    count, height, width = _size_t(), _size_t(), _size_t()
+    status = lib.vitb200_dataset_parse_pgm_csv(
+        os.fsencode(manifest_path), ctypes.byref(pixels), ctypes.byref(maxima),
+        ctypes.byref(labels), ctypes.byref(count), ctypes.byref(height),
+        ctypes.byref(width))
+    if status != 0:
+        return status, None, None, None
+    n, h, w = int(count.value), int(height.value), int(width.value)
+    out = (np.ctypeslib.as_array(pixels, shape=(n, h, w)).copy(),
+           np.ctypeslib.as_array(maxima, shape=(n,)).copy(),
+           np.ctypeslib.as_array(labels, shape=(n,)).copy())
+    libc = ctypes.CDLL(None)
+    libc.free.argtypes = [ctypes.c_void_p]
+    for pointer in (pixels, maxima, labels):
+        libc.free(ctypes.cast(pointer, ctypes.c_void_p))
+    return 0, out[0], out[1], out[2]
+
+
+class Dataset:
+    """A vitb200_dataset: samples resident on the backend's device
+    (include/vitb200_dataset.h)."""
+
+    def __init__(self, backend, manifest_path=None, pixels=None, max_values=None,
+                 labels=None):
+        self.backend = backend
+        self.lib = backend.lib
+        handle = ctypes.c_void_p()
+        if manifest_path is not None:
+            status = self.lib.vitb200_dataset_load_pgm_csv(
+                backend.handle, os.fsencode(manifest_path), ctypes.byref(handle))
+        else:
+            pixels = np.ascontiguousarray(pixels, dtype=np.uint16)
+            labels = np.ascontiguousarray(labels, dtype=np.uintp)
+            maxima = None
+            if max_values is not None:
+                maxima = np.ascontiguousarray(max_values, dtype=np.uint16)
+            ushort_p = ctypes.POINTER(ctypes.c_ushort)
+            status = self.lib.vitb200_dataset_from_integers(
+                backend.handle, pixels.ctypes.data_as(ushort_p),
+                maxima.ctypes.data_as(ushort_p) if maxima is not None else None,
+                labels.ctypes.data_as(ctypes.POINTER(_size_t)), pixels.shape[0],
+                pixels.shape[1], pixels.shape[2], ctypes.byref(handle))
+        if status != 0 or not handle:
+            raise RuntimeError("the dataset could not be loaded")
+        self.handle = handle
+        self.samples = int(self.lib.vitb200_dataset_sample_count(handle))
+        self.height = int(self.lib.vitb200_dataset_height(handle))
+        self.width = int(self.lib.vitb200_dataset_width(handle))
+
+    def close(self):
+        if self.handle:
+            self.lib.vitb200_dataset_free(self.handle)
+            self.handle = None
+
+    def statistics(self):
+        mean, inverse = ctypes.c_float(), ctypes.c_float()
+        self.lib.vitb200_dataset_statistics(self.handle, ctypes.byref(mean),
+                                            ctypes.byref(inverse))
+        return float(mean.value), float(inverse.value)
+
+    def shuffle(self, state):
+        """Returns the generator state after the shuffle's draws."""
+        value = ctypes.c_ulong(state)
+        if self.lib.vitb200_dataset_shuffle(self.handle, ctypes.byref(value)) != 0:
+            raise RuntimeError("vitb200_dataset_shuffle failed")
+        return int(value.value)
+
+    def batch(self, offset, batch, mean, inverse_std, destination=None):
+        """(status, images, labels).  `destination`: None (a new host array), a
+        float32 host array, or an integer address of tensor memory."""
+        labels = np.empty(batch, np.uintp)
+        if isinstance(destination, int):
+            target, images = ctypes.c_void_p(destination), None
+        else:
+            images = destination if destination is not None else np.empty(
+                (batch, self.height * self.width), np.float32)
+            target = ctypes.c_void_p(images.ctypes.data)
+        status = self.lib.vitb200_dataset_batch(
+            self.handle, offset, batch, ctypes.c_float(mean),
+            ctypes.c_float(inverse_std), target,
+            labels.ctypes.data_as(ctypes.POINTER(_size_t)))
+        return int(status), images, labels
+
+
 class VitHost:
     """A model plus its activation cache, created through the reference's
     vit_model_init_seeded / vit_model_cache_init.  Tensors land on the device
@@ -413,6 +539,20 @@ class VitHost:
         if status != 0:
             raise RuntimeError("vithost_train_step_accumulated failed")
         return float(loss.value)
+
+    def images_tensor(self):
+        """Host address of the cache's image tensor (tensor memory)."""
+        return int(self.lib.vithost_images_tensor(self.handle))
+
+    def forward_from_address(self, address):
+        """vit_model_forward with the images read from `address` (for example
+        images_tensor() after a device-side producer has filled it)."""
+        logits = np.empty((self.batch, self.config[7]), np.float32)
+        if self.lib.vithost_forward(self.handle,
+                                    ctypes.cast(ctypes.c_void_p(address), _float_p),
+                                    logits.ctypes.data_as(_float_p)) != 0:
+            raise RuntimeError("vit_model_forward failed")
+        return logits
 
     def forward(self, images):
         images = np.ascontiguousarray(images, dtype=np.float32)
