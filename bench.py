@@ -211,7 +211,7 @@ def augmentation_measurement(backend, host_lib, batch, channels, height, width,
     return result
 
 
-def dataset_measurement(vh, backend, batch, height, width, steps):
+def dataset_measurement(vh, backend, batch, height, width, steps, with_cpu):
     """Batches out of a device-resident dataset (include/vitb200_dataset.h):
     gather by the shuffled order, integer -> [0, 1] -> normalised float, the
     work the reference's trainer does on the host once per dataset and per
@@ -252,6 +252,18 @@ def dataset_measurement(vh, backend, batch, height, width, steps):
                      "peak": hbm_peak, "unit": "GB/s", "peak_source": peak_source},
     }
     result["roofline"]["frac"] = result["roofline"]["achieved"] / hbm_peak
+    if with_cpu:
+        import dataset_reference
+        timed = dataset_reference.time_reference(samples, height, width)
+        if timed:
+            result["cpu_baseline"] = {
+                "value": samples / timed["shuffle_seconds"], "unit": "images/s",
+                "cores": 1, "kind": "reference",
+                "sample": f"reference trainer shuffle_dataset over {samples} "
+                          f"images in memory (its batches are slices of the "
+                          f"shuffled array), mean of 3; its one-off "
+                          f"normalize_dataset took "
+                          f"{1e3 * timed['normalise_seconds']:.1f} ms"}
     return result
 
 
@@ -550,8 +562,9 @@ def main():
             backend, host_lib, batch, config[0], config[1], config[2],
             args.steps, with_cpu=not args.no_cpu_baseline)
     if rank == 0 and world == 1:
-        line["dataset"] = dataset_measurement(vh, backend, batch, config[1],
-                                              config[2], args.steps)
+        line["dataset"] = dataset_measurement(
+            vh, backend, batch, config[1], config[2], args.steps,
+            with_cpu=not args.no_cpu_baseline)
     if world > 1:
         line["dp"] = backend.dp_counters()
     host.close()

@@ -84,6 +84,47 @@ def run(manifest, directory, shuffles=0, state=1):
     return dict(np.load(output))
 
 
+def _time_child(samples, height, width):
+    """Seconds the reference's trainer spends per epoch on a dataset that is
+    already in memory: shuffle_dataset (images moved by memcpy); and once per
+    run: normalize_dataset."""
+    import json
+    import time
+    lib = ctypes.CDLL(LIBRARY)
+    rng = np.random.RandomState(1)
+    images = rng.rand(samples, height * width).astype(np.float32)
+    labels = rng.randint(0, 11, size=samples).astype(np.uintp)
+    dataset = VisionDataset(
+        images.ctypes.data_as(ctypes.POINTER(ctypes.c_float)),
+        labels.ctypes.data_as(ctypes.POINTER(ctypes.c_size_t)), samples, height,
+        width, 1)
+    lib.trainer_normalize.argtypes = [ctypes.c_void_p, ctypes.c_float,
+                                      ctypes.c_float]
+    start = time.perf_counter()
+    lib.trainer_normalize(ctypes.byref(dataset), 0.5, 2.0)
+    normalise = time.perf_counter() - start
+    state = ctypes.c_ulong(1)
+    lib.trainer_shuffle(ctypes.byref(dataset), ctypes.byref(state))
+    start = time.perf_counter()
+    for _ in range(3):
+        lib.trainer_shuffle(ctypes.byref(dataset), ctypes.byref(state))
+    shuffle = (time.perf_counter() - start) / 3
+    print(json.dumps({"shuffle_seconds": shuffle, "normalise_seconds": normalise}))
+
+
+def time_reference(samples, height, width):
+    """Runs _time_child in a process of its own; None if the library is absent."""
+    import json
+    if not available():
+        return None
+    done = subprocess.run([sys.executable, os.path.abspath(__file__), "time",
+                           str(samples), str(height), str(width)],
+                          capture_output=True, text=True, timeout=300)
+    if done.returncode != 0:
+        return None
+    return json.loads(done.stdout.strip().splitlines()[-1])
+
+
 def write_pgm(path, pixels, max_value, binary, comment=False):
     """One PGM file: P5 (binary; two bytes per sample, most significant first,
     when max_value >= 256) or P2 (decimal text)."""
@@ -128,4 +169,7 @@ def write_dataset(directory, samples, height, width, seed, wide=False):
 
 
 if __name__ == "__main__":
-    _child(sys.argv[1], sys.argv[2], int(sys.argv[3]), int(sys.argv[4]))
+    if sys.argv[1] == "time":
+        _time_child(int(sys.argv[2]), int(sys.argv[3]), int(sys.argv[4]))
+    else:
+        _child(sys.argv[1], sys.argv[2], int(sys.argv[3]), int(sys.argv[4]))
