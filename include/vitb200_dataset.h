@@ -45,7 +45,8 @@ int vitb200_dataset_from_integers(CudaBackend *backend,
                                   size_t height, size_t width,
                                   vitb200_dataset **dataset);
 
-/* vision_dataset_free (include/dataset.h:25).  NULL-safe. */
+/* vision_dataset_free (include/dataset.h:25).  NULL-safe.  A dataset uses its
+ * backend's stream: free it before cuda_backend_free. */
 void vitb200_dataset_free(vitb200_dataset *dataset);
 
 /* The fields of the reference's VisionDataset. */
