@@ -79,11 +79,32 @@ __device__ __forceinline__ float quad_sum(float v) {
 
 template <int HD>
 struct Shape {
-    static constexpr int kPitch = HD + 4;     // floats between tile rows
+    // Floats a staged tile row takes: four floats of padding keep the fragment
+    // loads of the wider heads apart; head dimension 16 uses a swizzle
+    // instead (tile_index).
+    static constexpr int kPitch = HD == 16 ? 16 : HD + 4;
     static constexpr int kRange = HD / 4;     // floats of a row one lane owns
     static constexpr int kSteps = HD / 8;     // k-steps over the head dimension
     static constexpr int kOut = HD / 8;       // 8-column tiles of an HD-wide result
 };
+
+// Where element (row, col) of a staged tile lives.  Head dimension 16: rows of
+// 64 bytes, no padding; each pair of rows fills the 32 banks once, the second
+// pair of every four rows is stored in swapped order and rows 4..7 of every
+// eight swap their 32-byte halves.  With that both access patterns of the
+// products are free of bank conflicts: the 128-bit loads of product_rows
+// (eight lanes = two consecutive rows) and the 64-bit loads of
+// product_columns (sixteen lanes = four rows two apart, a 32-byte quarter of
+// each), which padding alone cannot give at this width.
+template <int HD>
+__device__ __forceinline__ int tile_index(int row, int col) {
+    if (HD == 16) {
+        const int slot = (row & ~1) | ((row ^ (row >> 1)) & 1);
+        const int chunk = (col >> 2) ^ ((row >> 1) & 2);
+        return slot * 16 + (chunk << 2) + (col & 3);
+    }
+    return row * Shape<HD>::kPitch + col;
+}
 
 // The lane's kRange consecutive floats of a row (16-byte aligned).
 template <int N>
@@ -147,7 +168,7 @@ __device__ __forceinline__ void stage_store(const Staged<HD, THREADS> &staged,
         const int r = i / kVectors;
         const int c = (i % kVectors) * 4;
         const float4 v = staged.value[j];
-        *reinterpret_cast<float4 *>(tile + r * Shape<HD>::kPitch + c) =
+        *reinterpret_cast<float4 *>(tile + tile_index<HD>(r, c)) =
             make_float4(to_tf32(v.x), to_tf32(v.y), to_tf32(v.z), to_tf32(v.w));
     }
 }
@@ -170,11 +191,14 @@ __device__ __forceinline__ void product_rows(float (&c)[8][4],
                                              const float *tile, int g, int t,
                                              int live = TILES) {
     using S = Shape<HD>;
+    // Both layouts repeat every eight rows, so the lane's position within a
+    // group of eight is computed once and the groups are immediate offsets.
+    const float *lane_rows = tile + tile_index<HD>(g, t * S::kRange);
 #pragma unroll
     for (int n = 0; n < TILES; ++n) {
         if (!kPartial || n < live) {
             float b[S::kRange];
-            load_range(b, tile + (n * 8 + g) * S::kPitch + t * S::kRange);
+            load_range(b, lane_rows + n * 8 * S::kPitch);
 #pragma unroll
             for (int s = 0; s < S::kSteps; ++s) {
                 mma_tf32(c[n], a0[2 * s], a1[2 * s], a0[2 * s + 1],
@@ -194,20 +218,23 @@ __device__ __forceinline__ void product_columns(float (&o)[HD / 8][4],
                                                 const float *tile, int g,
                                                 int t, int live = TILES) {
     using S = Shape<HD>;
+    const float *lane_row = tile + tile_index<HD>(2 * t, g * S::kOut);
+    const float *lane_next = tile + tile_index<HD>(2 * t + 1, g * S::kOut);
 #pragma unroll
     for (int s = 0; s < TILES; ++s) {
         if (!kPartial || s < live) {
             float b0[S::kOut < 4 ? 4 : S::kOut], b1[S::kOut < 4 ? 4 : S::kOut];
-            const float *row = tile + (s * 8 + 2 * t) * S::kPitch + g * S::kOut;
+            const float *row = lane_row + s * 8 * S::kPitch;
+            const float *next = lane_next + s * 8 * S::kPitch;
             if (S::kOut == 2) {
                 const float2 x = *reinterpret_cast<const float2 *>(row);
-                const float2 y = *reinterpret_cast<const float2 *>(row + S::kPitch);
+                const float2 y = *reinterpret_cast<const float2 *>(next);
                 b0[0] = x.x; b0[1] = x.y; b1[0] = y.x; b1[1] = y.y;
             } else {
 #pragma unroll
                 for (int i = 0; i < S::kOut; i += 4) {
                     const float4 x = *reinterpret_cast<const float4 *>(row + i);
-                    const float4 y = *reinterpret_cast<const float4 *>(row + S::kPitch + i);
+                    const float4 y = *reinterpret_cast<const float4 *>(next + i);
                     b0[i] = x.x; b0[i + 1] = x.y; b0[i + 2] = x.z; b0[i + 3] = x.w;
                     b1[i] = y.x; b1[i + 1] = y.y; b1[i + 2] = y.z; b1[i + 3] = y.w;
                 }
@@ -460,8 +487,8 @@ attention_warp_backward_kernel(
         }
         const int r0 = m0 + g, r1 = r0 + 8;
         float a0[S::kRange], a1[S::kRange];
-        load_range(a0, q_tile + r0 * S::kPitch + t * S::kRange);
-        load_range(a1, q_tile + r1 * S::kPitch + t * S::kRange);
+        load_range(a0, q_tile + tile_index<HD>(r0, t * S::kRange));
+        load_range(a1, q_tile + tile_index<HD>(r1, t * S::kRange));
         float p[8][4];
         clear(p);
         product_rows<HD, TILES>(p, a0, a1, k_tile, g, t);
@@ -480,8 +507,8 @@ attention_warp_backward_kernel(
             }
         }
         // dP = dO V^T, then dS = scale P (dP - D) in place over dP.
-        load_range(a0, g_tile + r0 * S::kPitch + t * S::kRange);
-        load_range(a1, g_tile + r1 * S::kPitch + t * S::kRange);
+        load_range(a0, g_tile + tile_index<HD>(r0, t * S::kRange));
+        load_range(a1, g_tile + tile_index<HD>(r1, t * S::kRange));
         float ds[8][4];
         clear(ds);
         product_rows<HD, TILES>(ds, a0, a1, v_tile, g, t);
@@ -508,8 +535,8 @@ attention_warp_backward_kernel(
     for (int m0 = warp * 16; m0 < seq; m0 += kWarps * 16) {
         const int r0 = m0 + g, r1 = r0 + 8;   // key rows
         float a0[S::kRange], a1[S::kRange];
-        load_range(a0, k_tile + r0 * S::kPitch + t * S::kRange);
-        load_range(a1, k_tile + r1 * S::kPitch + t * S::kRange);
+        load_range(a0, k_tile + tile_index<HD>(r0, t * S::kRange));
+        load_range(a1, k_tile + tile_index<HD>(r1, t * S::kRange));
         float p[8][4];
         clear(p);
         product_rows<HD, TILES>(p, a0, a1, q_tile, g, t);   // S^T
@@ -530,8 +557,8 @@ attention_warp_backward_kernel(
         if (column_partials) {
             add_column_sums<HD>(sums[2], result, r0, r1, seq);
         }
-        load_range(a0, v_tile + r0 * S::kPitch + t * S::kRange);
-        load_range(a1, v_tile + r1 * S::kPitch + t * S::kRange);
+        load_range(a0, v_tile + tile_index<HD>(r0, t * S::kRange));
+        load_range(a1, v_tile + tile_index<HD>(r1, t * S::kRange));
         float ds[8][4];
         clear(ds);
         product_rows<HD, TILES>(ds, a0, a1, g_tile, g, t);   // dP^T = V dO^T
