@@ -411,10 +411,10 @@ attention_warp_forward_kernel(const float *__restrict__ q,
 
 // Backward.  Pass 1 (query tiles): P, D, dS row-wise, dQ.  Pass 2 (key tiles):
 // P^T and dS^T from swapped operands and pass 1's row statistics, dV and dK.
-// Register caps: 112 keeps nine blocks of head dimension 16 resident per SM
-// (the compiler would take 122 and leave eight) without spilling; the kernel
-// is bound by instruction issue with two warps per block, so warps in flight
-// pay.  168 is what the 32-wide instantiations use anyway.
+// Register caps: at head dimension 16 the compiler would take 126 registers;
+// 112 costs no spill and leaves room next to the eight resident blocks (four
+// warps per scheduler either way).  168 is what the 32-wide instantiations use
+// anyway.
 template <int HD, int TILES>
 __global__ void __launch_bounds__(kThreads) __maxnreg__(HD == 16 ? 112 : 168)
 attention_warp_backward_kernel(
