@@ -80,9 +80,9 @@ __device__ __forceinline__ float quad_sum(float v) {
 template <int HD>
 struct Shape {
     // Floats a staged tile row takes: four floats of padding keep the fragment
-    // loads of the wider heads apart; head dimension 16 uses a swizzle
-    // instead (tile_index).
-    static constexpr int kPitch = HD == 16 ? 16 : HD + 4;
+    // loads of head dimension 32 apart; 16 and 64 use a swizzle instead
+    // (tile_index).
+    static constexpr int kPitch = HD == 16 ? 16 : (HD == 64 ? 64 : HD + 4);
     static constexpr int kRange = HD / 4;     // floats of a row one lane owns
     static constexpr int kSteps = HD / 8;     // k-steps over the head dimension
     static constexpr int kOut = HD / 8;       // 8-column tiles of an HD-wide result
@@ -103,7 +103,48 @@ __device__ __forceinline__ int tile_index(int row, int col) {
         const int chunk = (col >> 2) ^ ((row >> 1) & 2);
         return slot * 16 + (chunk << 2) + (col & 3);
     }
+    if (HD == 64) {
+        // Rows of 256 bytes (sixteen 16-byte chunks, two passes over the
+        // banks), the chunk index XORed with a row-dependent value out of
+        // {0, 1, 4, 5}: bit 2 separates the two consecutive rows that one
+        // 128-bit load of product_rows touches (its lanes read four adjacent
+        // chunks each, see lane_column), bits 0 and 2 spread the four rows two
+        // apart of one load of product_columns (two chunks each) over the
+        // eight bank groups.  With a padded pitch either pattern is left with
+        // a two-way conflict.
+        const int twist = ((row >> 1) & 1) | ((((row >> 2) ^ row) & 1) << 2);
+        return row * 64 + ((((col >> 2) ^ twist)) << 2) + (col & 3);
+    }
     return row * Shape<HD>::kPitch + col;
+}
+
+// Column of element e of the head-dimension slice lane t contracts over (the
+// A rows and B rows of product_rows).  Any split of the columns over the four
+// lanes works as long as both operands use the same one: consecutive quarters
+// in general; at head dimension 64 the lane takes every fourth 16-byte chunk,
+// so that the four lanes of a row read adjacent chunks of shared memory.
+template <int HD>
+__device__ __forceinline__ int lane_column(int t, int e) {
+    if (HD == 64) {
+        return (e >> 2) * 16 + t * 4 + (e & 3);
+    }
+    return t * Shape<HD>::kRange + e;
+}
+
+// The lane's slice of a row in global memory (row points at column 0).
+template <int HD>
+__device__ __forceinline__ void load_lane_global(float (&x)[HD / 4],
+                                                 const float *row, int t,
+                                                 bool rounded) {
+#pragma unroll
+    for (int i = 0; i < HD / 4; i += 4) {
+        const float4 v = __ldcs(
+            reinterpret_cast<const float4 *>(row + lane_column<HD>(t, i)));
+        x[i] = rounded ? to_tf32(v.x) : v.x;
+        x[i + 1] = rounded ? to_tf32(v.y) : v.y;
+        x[i + 2] = rounded ? to_tf32(v.z) : v.z;
+        x[i + 3] = rounded ? to_tf32(v.w) : v.w;
+    }
 }
 
 // The lane's kRange consecutive floats of a row (16-byte aligned).
@@ -193,12 +234,22 @@ __device__ __forceinline__ void product_rows(float (&c)[8][4],
     using S = Shape<HD>;
     // Both layouts repeat every eight rows, so the lane's position within a
     // group of eight is computed once and the groups are immediate offsets.
-    const float *lane_rows = tile + tile_index<HD>(g, t * S::kRange);
+    int lane_chunks[S::kRange / 4];
+#pragma unroll
+    for (int i = 0; i < S::kRange / 4; ++i) {
+        lane_chunks[i] = tile_index<HD>(g, lane_column<HD>(t, 4 * i));
+    }
 #pragma unroll
     for (int n = 0; n < TILES; ++n) {
         if (!kPartial || n < live) {
             float b[S::kRange];
-            load_range(b, lane_rows + n * 8 * S::kPitch);
+#pragma unroll
+            for (int i = 0; i < S::kRange / 4; ++i) {
+                const float4 v = *reinterpret_cast<const float4 *>(
+                    tile + n * 8 * S::kPitch + lane_chunks[i]);
+                b[4 * i] = v.x; b[4 * i + 1] = v.y;
+                b[4 * i + 2] = v.z; b[4 * i + 3] = v.w;
+            }
 #pragma unroll
             for (int s = 0; s < S::kSteps; ++s) {
                 mma_tf32(c[n], a0[2 * s], a1[2 * s], a0[2 * s + 1],
@@ -218,23 +269,29 @@ __device__ __forceinline__ void product_columns(float (&o)[HD / 8][4],
                                                 const float *tile, int g,
                                                 int t, int live = TILES) {
     using S = Shape<HD>;
-    const float *lane_row = tile + tile_index<HD>(2 * t, g * S::kOut);
-    const float *lane_next = tile + tile_index<HD>(2 * t + 1, g * S::kOut);
+    // The lane's 16-byte chunks of rows 2t and 2t + 1 (a swizzled layout does
+    // not keep consecutive chunks next to each other).
+    constexpr int kChunks = S::kOut < 4 ? 1 : S::kOut / 4;
+    int lane_row[kChunks], lane_next[kChunks];
+#pragma unroll
+    for (int i = 0; i < kChunks; ++i) {
+        lane_row[i] = tile_index<HD>(2 * t, g * S::kOut + 4 * i);
+        lane_next[i] = tile_index<HD>(2 * t + 1, g * S::kOut + 4 * i);
+    }
 #pragma unroll
     for (int s = 0; s < TILES; ++s) {
         if (!kPartial || s < live) {
             float b0[S::kOut < 4 ? 4 : S::kOut], b1[S::kOut < 4 ? 4 : S::kOut];
-            const float *row = lane_row + s * 8 * S::kPitch;
-            const float *next = lane_next + s * 8 * S::kPitch;
+            const float *group = tile + s * 8 * S::kPitch;
             if (S::kOut == 2) {
-                const float2 x = *reinterpret_cast<const float2 *>(row);
-                const float2 y = *reinterpret_cast<const float2 *>(next);
+                const float2 x = *reinterpret_cast<const float2 *>(group + lane_row[0]);
+                const float2 y = *reinterpret_cast<const float2 *>(group + lane_next[0]);
                 b0[0] = x.x; b0[1] = x.y; b1[0] = y.x; b1[1] = y.y;
             } else {
 #pragma unroll
                 for (int i = 0; i < S::kOut; i += 4) {
-                    const float4 x = *reinterpret_cast<const float4 *>(row + i);
-                    const float4 y = *reinterpret_cast<const float4 *>(next + i);
+                    const float4 x = *reinterpret_cast<const float4 *>(group + lane_row[i / 4]);
+                    const float4 y = *reinterpret_cast<const float4 *>(group + lane_next[i / 4]);
                     b0[i] = x.x; b0[i + 1] = x.y; b0[i + 2] = x.z; b0[i + 3] = x.w;
                     b1[i] = y.x; b1[i + 1] = y.y; b1[i + 2] = y.z; b1[i + 3] = y.w;
                 }
@@ -683,8 +740,8 @@ __device__ __forceinline__ void attention_stream_forward_body(const float *__res
     const bool live_warp = row_tile * kTile + warp * 16 < seq;   // else: staging only
     const float scale2 = scale * kLog2e;
     float a0[S::kRange], a1[S::kRange];
-    load_range_global(a0, q + base + size_t(min(r0, seq - 1)) * ld + t * S::kRange, true);
-    load_range_global(a1, q + base + size_t(min(r1, seq - 1)) * ld + t * S::kRange, true);
+    load_lane_global<HD>(a0, q + base + size_t(min(r0, seq - 1)) * ld, t, true);
+    load_lane_global<HD>(a1, q + base + size_t(min(r1, seq - 1)) * ld, t, true);
     float max_a = -FLT_MAX, max_b = -FLT_MAX;   // running maxima of raw scores
     float sum_a = 0.0f, sum_b = 0.0f;           // this lane's share of the denominators
     float o[S::kOut][4];
@@ -831,12 +888,12 @@ __device__ __forceinline__ void attention_stream_backward_rows_body(
     float offset_a, offset_b;   // -scale * D
     {
         float oa[S::kRange], ob[S::kRange];
-        load_range_global(qa, q + base + size_t(safe0) * ld + t * S::kRange, true);
-        load_range_global(qb, q + base + size_t(safe1) * ld + t * S::kRange, true);
-        load_range_global(ga, dout_base + size_t(safe0) * dout_layout.ld + t * S::kRange, false);
-        load_range_global(gb, dout_base + size_t(safe1) * dout_layout.ld + t * S::kRange, false);
-        load_range_global(oa, out_base + size_t(safe0) * out_layout.ld + t * S::kRange, false);
-        load_range_global(ob, out_base + size_t(safe1) * out_layout.ld + t * S::kRange, false);
+        load_lane_global<HD>(qa, q + base + size_t(safe0) * ld, t, true);
+        load_lane_global<HD>(qb, q + base + size_t(safe1) * ld, t, true);
+        load_lane_global<HD>(ga, dout_base + size_t(safe0) * dout_layout.ld, t, false);
+        load_lane_global<HD>(gb, dout_base + size_t(safe1) * dout_layout.ld, t, false);
+        load_lane_global<HD>(oa, out_base + size_t(safe0) * out_layout.ld, t, false);
+        load_lane_global<HD>(ob, out_base + size_t(safe1) * out_layout.ld, t, false);
         float dot_a = 0.0f, dot_b = 0.0f;
 #pragma unroll
         for (int e = 0; e < S::kRange; ++e) {
@@ -961,10 +1018,10 @@ __device__ __forceinline__ void attention_stream_backward_columns_body(
     const int safe0 = min(r0, seq - 1), safe1 = min(r1, seq - 1);
     const float scale2 = scale * kLog2e;
     float ka[S::kRange], kb[S::kRange], va[S::kRange], vb[S::kRange];
-    load_range_global(ka, k + base + size_t(safe0) * ld + t * S::kRange, true);
-    load_range_global(kb, k + base + size_t(safe1) * ld + t * S::kRange, true);
-    load_range_global(va, v + base + size_t(safe0) * ld + t * S::kRange, true);
-    load_range_global(vb, v + base + size_t(safe1) * ld + t * S::kRange, true);
+    load_lane_global<HD>(ka, k + base + size_t(safe0) * ld, t, true);
+    load_lane_global<HD>(kb, k + base + size_t(safe1) * ld, t, true);
+    load_lane_global<HD>(va, v + base + size_t(safe0) * ld, t, true);
+    load_lane_global<HD>(vb, v + base + size_t(safe1) * ld, t, true);
     float dk_acc[S::kOut][4], dv_acc[S::kOut][4];
     clear(dk_acc);
     clear(dv_acc);
