@@ -239,6 +239,14 @@ int vitb200_k_attention_backward(const float *q, const float *k, const float *v,
                                  float *dv, float *row_dots, size_t groups,
                                  size_t seq, size_t head_dim, float scale,
                                  int precision, void *stream);
+/* Shared-memory layout of the staged 64-row operand tiles of the tensor-core
+ * attention kernels (head dimensions 16, 32, 64), computed on the host by the
+ * code the kernels use: the float offset of element (row, col), and column e of
+ * the head-dimension slice lane t (0..3) of a quad contracts over.  No device
+ * needed; for checking that the layout is a bijection and that the kernels'
+ * fragment loads meet no bank conflict.  -1 for arguments out of range. */
+int vitb200_attention_tile_index(int head_dim, int row, int col);
+int vitb200_attention_lane_column(int head_dim, int t, int e);
 /* row_losses: scratch, rows floats. */
 int vitb200_k_softmax_cross_entropy(const float *logits, const float *targets,
                                     const float *class_weights,

@@ -97,7 +97,7 @@ struct Shape {
 // product_columns (sixteen lanes = four rows two apart, a 32-byte quarter of
 // each), which padding alone cannot give at this width.
 template <int HD>
-__device__ __forceinline__ int tile_index(int row, int col) {
+__host__ __device__ __forceinline__ int tile_index(int row, int col) {
     if (HD == 16) {
         const int slot = (row & ~1) | ((row ^ (row >> 1)) & 1);
         const int chunk = (col >> 2) ^ ((row >> 1) & 2);
@@ -124,7 +124,7 @@ __device__ __forceinline__ int tile_index(int row, int col) {
 // in general; at head dimension 64 the lane takes every fourth 16-byte chunk,
 // so that the four lanes of a row read adjacent chunks of shared memory.
 template <int HD>
-__device__ __forceinline__ int lane_column(int t, int e) {
+__host__ __device__ __forceinline__ int lane_column(int t, int e) {
     if (HD == 64) {
         return (e >> 2) * 16 + t * 4 + (e & 3);
     }
@@ -1140,6 +1140,24 @@ HeadLayout resolve(HeadLayout layout, size_t head_dim) {
             else { CALL(32, 8); }                                              \
         }                                                                      \
     } while (0)
+
+int attention_tile_index(int head_dim, int row, int col) {
+    switch (head_dim) {
+        case 16: return tile_index<16>(row, col);
+        case 32: return tile_index<32>(row, col);
+        case 64: return tile_index<64>(row, col);
+        default: return -1;
+    }
+}
+
+int attention_lane_column(int head_dim, int t, int e) {
+    switch (head_dim) {
+        case 16: return lane_column<16>(t, e);
+        case 32: return lane_column<32>(t, e);
+        case 64: return lane_column<64>(t, e);
+        default: return -1;
+    }
+}
 
 bool attention_warp_supported(size_t seq, size_t head_dim) {
     return seq >= 1 && seq <= size_t(kTile) && (head_dim == 16 || head_dim == 32);

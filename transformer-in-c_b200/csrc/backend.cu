@@ -3024,6 +3024,16 @@ extern "C" int vitb200_k_softmax_cross_entropy(
     return 0;
 }
 
+extern "C" int vitb200_attention_tile_index(int head_dim, int row, int col) {
+    return row < 0 || row >= 64 || col < 0 || col >= head_dim
+        ? -1 : attention_tile_index(head_dim, row, col);
+}
+
+extern "C" int vitb200_attention_lane_column(int head_dim, int t, int e) {
+    return t < 0 || t >= 4 || e < 0 || e >= head_dim / 4
+        ? -1 : attention_lane_column(head_dim, t, e);
+}
+
 extern "C" int vitb200_k_softmax_cross_entropy_static(
     const float *logits, const float *targets, const float *class_weights,
     float label_smoothing, float *loss, float *logits_grad, size_t rows,

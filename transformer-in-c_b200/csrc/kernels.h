@@ -167,6 +167,12 @@ bool launch_attention_small_forward(const float *q, const float *k,
 // column_partials ([groups / heads, 3 * d_model]) receives per-sample column
 // sums of that gradient: summed over its rows they are the bias gradient.
 bool attention_warp_supported(size_t seq, size_t head_dim);
+// Host copies of the shared-memory layout of the tensor-core attention
+// kernels' staged tiles, for checking it without a device: the float offset of
+// element (row, col) of a 64-row tile, and column e of the head-dimension
+// slice that lane t of a quad contracts over.  -1 for other head dimensions.
+int attention_tile_index(int head_dim, int row, int col);
+int attention_lane_column(int head_dim, int t, int e);
 bool launch_attention_warp_forward(const float *q, const float *k,
                                    const float *v, float *out, size_t groups,
                                    size_t seq, size_t head_dim, float scale,
