@@ -232,6 +232,31 @@ int vitb200_k_attention_stream_backward(const float *q, const float *k,
                                         float *row_dots, size_t groups,
                                         size_t seq, size_t head_dim, float scale,
                                         void *stream);
+/* The same flash attention on the tcgen05 tensor cores (128-row tiles, scores
+ * and P in tensor memory, operands fetched by TMA; TF32 operands, FP32
+ * accumulation and softmax), head_dim 32 or 64, any sequence length.  Replaces
+ * attention_forward_flash / attention_backward_flash_{queries,keys} of the
+ * reference backend (src/cuda_backend.cu:532-723; host loops src/ops.c:1297-1355,
+ * 1381-1441).  `lse` and `row_dots` as above; the two families' `lse` rows are
+ * interchangeable.  ld = 0: head-major tensors.  ld != 0: each operand is a block of
+ * heads * head_dim columns of a token-major matrix with rows `ld` floats apart
+ * (q, k, v: in_ld; out and dout: out_ld; dq, dk, dv: grad_ld), the pointer
+ * naming the block's first column, groups = samples * heads.  The backward
+ * pass adds into dq, dk, dv when `accumulate` is non-zero and overwrites them
+ * otherwise.  -1: shape, alignment (16 bytes, ld a multiple of 4) or layout
+ * not covered; nothing was launched. */
+int vitb200_k_attention_tc(const float *q, const float *k, const float *v,
+                           float *out, float *lse, size_t groups, size_t seq,
+                           size_t head_dim, float scale, size_t in_ld,
+                           size_t out_ld, size_t heads, void *stream);
+int vitb200_k_attention_tc_backward(const float *q, const float *k,
+                                    const float *v, const float *out,
+                                    const float *dout, const float *lse,
+                                    float *dq, float *dk, float *dv,
+                                    float *row_dots, size_t groups, size_t seq,
+                                    size_t head_dim, float scale, int accumulate,
+                                    size_t in_ld, size_t out_ld, size_t grad_ld,
+                                    size_t heads, void *stream);
 /* row_dots: scratch, groups*seq floats. */
 int vitb200_k_attention_backward(const float *q, const float *k, const float *v,
                                  const float *probabilities, const float *out,

@@ -1,0 +1,1127 @@
+// Flash attention on the tcgen05 tensor cores (sm_100a), forward and backward,
+// for long sequences and head dimensions 32 and 64.  Semantics: reference
+// src/ops.c:1297-1355 (forward: P = softmax(scale Q K^T), O = P V per
+// (sample, head) group, no mask) and src/ops.c:1381-1441 (backward); P is
+// never stored, the forward pass keeps each row's log-sum-exp instead.
+//
+// All three kernels are one template.  A CTA owns a tile of 128 rows of one
+// group (queries, or keys in the key/value-gradient kernel) whose operands
+// stay resident in shared memory, and walks the other index in tiles of N
+// columns.  For every column tile
+//
+//   1. "SS" products (both operands in shared memory, K-major, TF32) put a
+//      128 x N block of scores into tensor memory:
+//        forward            S  = Q K^T
+//        query gradient     S  = Q K^T,   dP  = dO V^T
+//        key/value gradient S^T = K Q^T,  dP^T = V dO^T
+//   2. a group of four transform warps (one tensor-memory lane = one row per
+//      thread) rewrites the block in place:
+//        forward            P  = exp2(scale2 S - m)  (running maximum m, lazily
+//                           raised; row sums kept in registers)
+//        query gradient     dS = P o (dP - D) scale, P rebuilt from the saved
+//                           log-sum-exp, D = rowsum(dO o O)
+//        key/value gradient P^T and dS^T likewise, D and the log-sum-exp of the
+//                           tile's queries read from a small shared table
+//   3. "TS" products take that block straight from tensor memory as their A
+//      operand (it never visits shared memory) and a token-major tile as B:
+//        forward            O  += P V
+//        query gradient     dQ += dS K
+//        key/value gradient dV += P^T dO,  dK += dS^T Q
+//
+// Column tiles alternate between two tensor-memory buffers, each with its own
+// transform group, so the tensor pipe works on tile j+1 while tile j is being
+// transformed.  In the forward pass each buffer keeps its own running maximum,
+// row sum and output accumulator (a split over the keys inside the CTA); the
+// two halves are merged at the end.
+//
+// Warp roles: warp 0 issues TMA loads (3-D tensor maps [sample][token][column]
+// over the token-major projection matrix or the head-major tensors, so rows
+// past the end of a group read as zero and stores are clipped), warp 1 issues
+// the MMAs and owns the tensor-memory allocation, warps 2-9 are the two
+// transform groups and store the results (32 x 32 blocks staged in shared
+// memory, TMA store or reduce-add).  Roles meet only through mbarriers; every
+// wait is bounded in time, records a code in the library's status word when
+// it gives up and lets the kernel run to its normal end.
+#include "device_util.cuh"
+#include "gemm_tc.h"
+#include "kernels.h"
+#include "tcgen05.cuh"
+
+#include <algorithm>
+#include <climits>
+#include <cmath>
+#include <cstring>
+#include <unordered_map>
+
+namespace vitb200 {
+namespace {
+
+using namespace tc;
+
+constexpr int kTileRows = 128;
+constexpr int kAttnThreads = 320;   // TMA warp, MMA warp, two groups of four
+constexpr int kTmemColumns = 512;
+constexpr int kBarrierBytes = 256;
+constexpr int kMinSmemBytes = 116 * 1024;   // one CTA per SM: it owns all of tensor memory
+
+constexpr int kForward = 0;
+constexpr int kGradQuery = 1;
+constexpr int kGradKeyValue = 2;
+
+// kCols: columns per tile; kResident: operands that stay for the whole row
+// tile; kProducts: SS products per tile; kUpdates: TS products per tile;
+// kAccumulators: 128 x head_dim accumulators per work item (there are two
+// sets, so that one item's results are read while the next item's grow);
+// kStagingBytes: shared memory the results leave through (4 KiB per storing
+// warp); kTableBytes: the transform warps' exchange table.
+template <int MODE> struct Traits;
+template <> struct Traits<kForward> {
+    static constexpr int kCols = 128, kResident = 1, kProducts = 1, kUpdates = 1,
+                         kAccumulators = 2, kStagingBytes = 32768,
+                         kTableBytes = 4096;
+};
+template <> struct Traits<kGradQuery> {
+    static constexpr int kCols = 96, kResident = 2, kProducts = 2, kUpdates = 1,
+                         kAccumulators = 1, kStagingBytes = 16384, kTableBytes = 0;
+};
+template <> struct Traits<kGradKeyValue> {
+    static constexpr int kCols = 64, kResident = 2, kProducts = 2, kUpdates = 2,
+                         kAccumulators = 2, kStagingBytes = 32768,
+                         kTableBytes = 2048;
+};
+
+struct AttnMaps {
+    CUtensorMap resident[2];   // 128-row boxes, K-major
+    CUtensorMap ss[2];         // N-row boxes, K-major
+    CUtensorMap ts[2];         // 32 x 32 boxes, 32-byte-atom swizzle
+    CUtensorMap out[2];        // 32 x 32 boxes, plain FP32
+};
+
+struct AttnParams {
+    int seq;
+    int heads;      // groups per sample (1 when the tensors are head-major)
+    int row_tiles;  // ceil(seq / 128)
+    int items;      // groups * row_tiles
+    float scale;    // 1 / sqrt(head_dim)
+    float scale2;   // scale * log2(e)
+    float *lse;               // [groups * seq]: written forward, read backward
+    const float *row_dots;    // [groups * seq]: rowsum(dO o O), backward
+    int add0, add1;           // outputs accumulate
+    int *status;
+};
+
+enum Barrier {
+    kResidentFull = 0,
+    kResidentEmpty = 1,
+    kSsFull = 2,     // two each from here on
+    kSsEmpty = 4,
+    kTsFull = 6,
+    kTsEmpty = 8,
+    kScoresFull = 10,
+    kBlockReady = 12,
+    kUpdateDone = 14,
+    kAllDone = 16,
+    kAccEmpty = 18,
+    kBarriers = 20,
+};
+
+// True in exactly one lane of a converged warp.
+__device__ __forceinline__ bool elect_one() {
+    uint32_t elected;
+    asm volatile(
+        "{\n\t"
+        ".reg .pred p;\n\t"
+        "elect.sync _|p, 0xffffffff;\n\t"
+        "selp.u32 %0, 1, 0, p;\n\t"
+        "}"
+        : "=r"(elected));
+    return elected != 0;
+}
+
+__device__ __forceinline__ void group_barrier(int id, int threads) {
+    asm volatile("bar.sync %0, %1;" ::"r"(id), "r"(threads) : "memory");
+}
+
+// Persistent: CTA c works on items c, c + gridDim.x, ... (item = one 128-row
+// tile of one group; the row tiles of a group are neighbours, so CTAs that run
+// side by side share the group's other operand in L2).  Column tiles are
+// numbered through all of a CTA's items; tile g uses load stage, tensor-memory
+// buffer and transform group g % 2, and the SS products of tile g + 2 are
+// issued right after the TS products of tile g, across item boundaries, so
+// the next item's first scores are computed while this item's results are
+// merged and stored.
+template <int HD, int MODE>
+__global__ void __launch_bounds__(kAttnThreads, 1)
+attention_tc_kernel(const __grid_constant__ AttnMaps maps, const AttnParams p) {
+    using T = Traits<MODE>;
+    constexpr int N = T::kCols;
+    constexpr int kBlocks = HD / 32;   // 32-float column blocks of the head dimension
+    constexpr int kResidentBytes = kTileRows * HD * 4;
+    constexpr int kOperandBytes = N * HD * 4;
+    constexpr int kResidentTotal = T::kResident * kResidentBytes;
+    constexpr int kSsStage = T::kProducts * kOperandBytes;
+    constexpr int kTsStage = T::kUpdates * kOperandBytes;
+    constexpr int kBufferColumns = T::kProducts * N;
+    constexpr int kAccumulatorBase = 2 * kBufferColumns;
+    constexpr int kSetColumns = T::kAccumulators * HD;
+    static_assert(kAccumulatorBase + 2 * kSetColumns <= kTmemColumns, "tensor memory");
+    static_assert(N % 32 == 0 && HD % 32 == 0, "tile shapes");
+
+    extern __shared__ __align__(1024) uint8_t smem[];
+    uint8_t *resident = smem;
+    uint8_t *ss_ring = resident + kResidentTotal;
+    uint8_t *ts_ring = ss_ring + 2 * kSsStage;
+    uint8_t *staging_base = ts_ring + 2 * kTsStage;
+    uint8_t *tail = staging_base + T::kStagingBytes;
+    uint64_t *bars = reinterpret_cast<uint64_t *>(tail);
+    uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(bars + kBarriers);
+    volatile int *failed = reinterpret_cast<volatile int *>(tmem_slot + 1);
+    float *table = reinterpret_cast<float *>(tail + kBarrierBytes);
+
+    const int warp = threadIdx.x >> 5;
+    const int lane = threadIdx.x & 31;
+    const int tiles = (p.seq + N - 1) / N;
+    const int my_items = (p.items - int(blockIdx.x) + int(gridDim.x) - 1) / int(gridDim.x);
+
+    if ((smem_address(smem) & 1023u) != 0) {
+        if (threadIdx.x == 0) {
+            atomicExch(p.status, 16);
+        }
+        return;
+    }
+    if (threadIdx.x == 0) {
+        for (int b = 0; b < kBarriers; ++b) {
+            const int count = (b == kBlockReady || b == kBlockReady + 1) ? 4
+                : (b == kAccEmpty || b == kAccEmpty + 1) ? 8 : 1;
+            mbarrier_init(&bars[b], count);
+        }
+        *failed = 0;
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    if (warp == 1) {
+        tmem_allocate(tmem_slot, kTmemColumns);
+    }
+    tcgen05_fence_before();
+    __syncthreads();
+    tcgen05_fence_after();
+    const uint32_t tmem_base_any = *tmem_slot;
+    const uint32_t tmem_base = tmem_base_any;
+
+    // A wait that has run out marks the CTA as failed; from then on nobody
+    // waits any more and every role runs its loops to their normal end, so no
+    // barrier is left with a missing participant.
+    auto wait = [&](int barrier, uint32_t parity, int code) {
+        if (*failed) {
+            return;
+        }
+        if (!mbarrier_wait(&bars[barrier], parity)) {
+            *failed = 1;
+            atomicExch(p.status, code);
+        }
+    };
+    // Where the it-th item of this CTA lives.
+    struct Item {
+        int group, m0, sample, col0;
+    };
+    auto item_at = [&](int it) {
+        const int index = int(blockIdx.x) + it * int(gridDim.x);
+        Item item;
+        item.group = index / p.row_tiles;
+        item.m0 = (index - item.group * p.row_tiles) * kTileRows;
+        item.sample = item.group / p.heads;
+        item.col0 = (item.group - item.sample * p.heads) * HD;
+        return item;
+    };
+
+    if (warp == 0) {
+        if (lane == 0) {
+            int fill = 0;   // column tiles loaded so far
+            for (int it = 0; it < my_items; ++it) {
+                const Item item = item_at(it);
+                wait(kResidentEmpty, (it & 1) ^ 1, 17);
+                mbarrier_expect_tx(&bars[kResidentFull], kResidentTotal);
+#pragma unroll
+                for (int r = 0; r < T::kResident; ++r) {
+#pragma unroll
+                    for (int kb = 0; kb < kBlocks; ++kb) {
+                        tma_load_3d(resident + r * kResidentBytes + kb * (kTileRows * 128),
+                                    &maps.resident[r], item.col0 + 32 * kb, item.m0,
+                                    item.sample, &bars[kResidentFull]);
+                    }
+                }
+                for (int j = 0; j < tiles; ++j, ++fill) {
+                    const int s = fill & 1;
+                    const uint32_t phase = (fill >> 1) & 1;
+                    const int n0 = j * N;
+                    wait(kSsEmpty + s, phase ^ 1, 18);
+                    mbarrier_expect_tx(&bars[kSsFull + s], kSsStage);
+#pragma unroll
+                    for (int product = 0; product < T::kProducts; ++product) {
+#pragma unroll
+                        for (int kb = 0; kb < kBlocks; ++kb) {
+                            tma_load_3d(ss_ring + s * kSsStage + product * kOperandBytes +
+                                            kb * (N * 128),
+                                        &maps.ss[product], item.col0 + 32 * kb, n0,
+                                        item.sample, &bars[kSsFull + s]);
+                        }
+                    }
+                    wait(kTsEmpty + s, phase ^ 1, 19);
+                    mbarrier_expect_tx(&bars[kTsFull + s], kTsStage);
+#pragma unroll
+                    for (int update = 0; update < T::kUpdates; ++update) {
+#pragma unroll
+                        for (int kk = 0; kk < N / 32; ++kk) {
+#pragma unroll
+                            for (int a = 0; a < kBlocks; ++a) {
+                                tma_load_3d(ts_ring + s * kTsStage + update * kOperandBytes +
+                                                (kk * kBlocks + a) * 4096,
+                                            &maps.ts[update], item.col0 + 32 * a,
+                                            n0 + 32 * kk, item.sample, &bars[kTsFull + s]);
+                            }
+                        }
+                    }
+                }
+            }
+        }
+    } else if (warp == 1) {
+        {
+            // One elected lane issues every MMA, but the whole warp runs the
+            // control flow: values every lane computes alike live in uniform
+            // registers, which is where tcgen05.mma takes its operands from
+            // (inside a one-lane branch each operand would be moved there
+            // instruction by instruction).  The descriptors are built once
+            // (high word constant, low word = address field + leading offset)
+            // and stepped by adding compile-time constants to the low word.
+            const bool leader = elect_one();
+            const uint32_t tmem_base = __shfl_sync(kFullMask, tmem_base_any, 0);
+            const uint32_t update_instruction = tf32_instruction(kTileRows, HD, 0, 1);
+            const uint32_t full_instruction = tf32_instruction(kTileRows, N, 0, 0);
+            // K-major: 8-row groups 1024 bytes apart (stride), K steps of 32
+            // bytes inside the 128-byte swizzled row, one 32-float block of
+            // the head dimension after the other.
+            constexpr uint32_t kHighKMajor = (1024u >> 4) | (1u << 14) |
+                                             (kLayoutSwizzle128 << 29);
+            // Output index contiguous, 32-byte-atom swizzle: boxes of one
+            // 32-row reduction block 4096 bytes apart (leading offset),
+            // groups of four rows 512 bytes apart, K steps of eight rows.
+            constexpr uint32_t kHighBox32 = (512u >> 4) | (1u << 14) |
+                                            (kLayoutSwizzle128Base32 << 29);
+            auto descriptor = [](uint32_t low, uint32_t high) {
+                return (uint64_t(high) << 32) | low;
+            };
+            auto low_word = [](uint32_t address, uint32_t leading_bytes) {
+                return ((address >> 4) & 0x3fffu) | ((leading_bytes >> 4) << 16);
+            };
+            const uint32_t resident_low = low_word(smem_address(resident), 16);
+            const uint32_t ss_low = low_word(smem_address(ss_ring), 16);
+            const uint32_t ts_low = low_word(smem_address(ts_ring), 4096);
+            const int total = my_items * tiles;
+            // SS products of column tile g into buffer g % 2.
+            int scores_it = 0, scores_j = 0;
+            auto scores = [&](int g) {
+                const int s = g & 1;
+                if (scores_j == 0) {
+                    wait(kResidentFull, scores_it & 1, 20);
+                }
+                wait(kSsFull + s, (g >> 1) & 1, 21);
+                tcgen05_fence_after();
+                const int valid = p.seq - scores_j * N;
+                const uint32_t instruction = valid >= N
+                    ? full_instruction
+                    : tf32_instruction(kTileRows, (valid + 15) & ~15, 0, 0);
+#pragma unroll
+                for (int product = 0; product < T::kProducts; ++product) {
+                    const uint32_t d = tmem_base + s * kBufferColumns + product * N;
+                    const uint32_t a_low = resident_low + ((product * kResidentBytes) >> 4);
+                    const uint32_t b_low =
+                        ss_low + ((s * kSsStage + product * kOperandBytes) >> 4);
+#pragma unroll
+                    for (int ks = 0; ks < HD / 8; ++ks) {
+                        constexpr int kRowBlock = kTileRows * 128, kColBlock = N * 128;
+                        if (leader) tcgen05_mma_tf32(
+                            d,
+                            descriptor(a_low + (((ks / 4) * kRowBlock + (ks % 4) * 32) >> 4),
+                                       kHighKMajor),
+                            descriptor(b_low + (((ks / 4) * kColBlock + (ks % 4) * 32) >> 4),
+                                       kHighKMajor),
+                            instruction, ks > 0 ? 1u : 0u);
+                    }
+                }
+                if (leader) {
+                    tcgen05_commit(&bars[kSsEmpty + s]);
+                    tcgen05_commit(&bars[kScoresFull + s]);
+                }
+                if (++scores_j == tiles) {
+                    // The item's resident operands have been read for the
+                    // last time once these products retire.
+                    if (leader) {
+                        tcgen05_commit(&bars[kResidentEmpty]);
+                    }
+                    scores_j = 0;
+                    ++scores_it;
+                }
+            };
+            // TS products of column tile g: A = the transformed block in
+            // tensor memory (eight columns per K step), B = 32 x 32 boxes.
+            int update_it = 0, update_j = 0;
+            auto update = [&](int g) {
+                const int s = g & 1;
+                const uint32_t phase = (g >> 1) & 1;
+                const int set = update_it & 1;
+                wait(kBlockReady + s, phase, 22);
+                wait(kTsFull + s, phase, 23);
+                if (update_j == 0) {
+                    // The transform warps must have read this accumulator
+                    // set's previous contents (two items ago).
+                    wait(kAccEmpty + set, ((update_it >> 1) & 1) ^ 1, 24);
+                }
+                tcgen05_fence_after();
+                const int valid = min(N, p.seq - update_j * N);
+                const int steps = (valid + 7) >> 3;
+#pragma unroll
+                for (int u = 0; u < T::kUpdates; ++u) {
+                    const int accumulator = MODE == kForward ? s : u;
+                    const bool first = MODE == kForward ? update_j < 2 : update_j == 0;
+                    const uint32_t d = tmem_base + kAccumulatorBase + set * kSetColumns +
+                                       accumulator * HD;
+                    const uint32_t a = tmem_base + s * kBufferColumns + u * N;
+                    const uint32_t b_low = ts_low + ((s * kTsStage + u * kOperandBytes) >> 4);
+                    if (leader) {
+                        tcgen05_mma_tf32_tmem_a(d, a, descriptor(b_low, kHighBox32),
+                                                update_instruction, first ? 0u : 1u);
+                    }
+#pragma unroll
+                    for (int ks = 1; ks < N / 8; ++ks) {
+                        if (leader && ks < steps) {
+                            tcgen05_mma_tf32_tmem_a(
+                                d, a + 8 * ks,
+                                descriptor(b_low + (((ks / 4) * (kBlocks * 4096) +
+                                                     (ks % 4) * 1024) >> 4),
+                                           kHighBox32),
+                                update_instruction, 1u);
+                        }
+                    }
+                }
+                if (leader) {
+                    tcgen05_commit(&bars[kTsEmpty + s]);
+                    tcgen05_commit(&bars[kUpdateDone + s]);
+                }
+                if (++update_j == tiles) {
+                    if (leader) {
+                        tcgen05_commit(&bars[kAllDone + set]);
+                    }
+                    update_j = 0;
+                    ++update_it;
+                }
+            };
+            if (total > 0) {
+                scores(0);
+            }
+            if (total > 1) {
+                scores(1);
+            }
+            for (int g = 0; g < total; ++g) {
+                update(g);
+                if (g + 2 < total) {
+                    scores(g + 2);
+                }
+            }
+        }
+    } else {
+        const int wg = (warp - 2) >> 2;       // transform group = buffer
+        const int quarter = warp & 3;         // tensor-memory lanes this warp may touch
+        const int row = quarter * 32 + lane;  // row of the tile this thread owns
+        const uint32_t lane_base = tmem_base + (uint32_t(quarter * 32) << 16);
+        const uint32_t block_address = lane_base + wg * kBufferColumns;
+        float *staging = reinterpret_cast<float *>(
+            staging_base + ((T::kStagingBytes == 32768 ? wg * 4 : 0) + quarter) * 4096);
+        bool staged = false;   // this warp has a store in flight from `staging`
+        int visit = 0;         // column tiles this group has transformed so far
+
+        // Stages r[] (this lane's 32 values of a 32 x 32 block) in the
+        // 128-byte swizzle the store map expects and hands it to the copy
+        // engine.  Rows past the end of the group are clipped by the map.
+        auto store_block = [&](uint32_t (&r)[32], const CUtensorMap *map, const Item &item,
+                               int column, bool add) {
+            if (staged) {
+                if (lane == 0) {
+                    asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory");
+                }
+                __syncwarp();
+            }
+            staged = true;
+#pragma unroll
+            for (int c = 0; c < 8; ++c) {
+                float4 v;
+                v.x = __uint_as_float(r[4 * c + 0]);
+                v.y = __uint_as_float(r[4 * c + 1]);
+                v.z = __uint_as_float(r[4 * c + 2]);
+                v.w = __uint_as_float(r[4 * c + 3]);
+                *reinterpret_cast<float4 *>(staging + lane * 32 + 4 * (c ^ (lane & 7))) = v;
+            }
+            asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+            __syncwarp();
+            if (lane == 0 && item.m0 + quarter * 32 < p.seq) {
+                if (add) {
+                    tma_reduce_add_3d(staging, map, item.col0 + column,
+                                      item.m0 + quarter * 32, item.sample);
+                } else {
+                    tma_store_3d(staging, map, item.col0 + column,
+                                 item.m0 + quarter * 32, item.sample);
+                }
+                asm volatile("cp.async.bulk.commit_group;" ::: "memory");
+            }
+        };
+        auto publish_block = [&]() {
+            tcgen05_wait_store();
+            tcgen05_fence_before();
+            __syncwarp();
+            if (lane == 0) {
+                mbarrier_arrive(&bars[kBlockReady + wg]);
+            }
+        };
+        // The accumulators of item `it` are complete / have been read.
+        auto await_results = [&](int it) {
+            wait(kAllDone + (it & 1), (it >> 1) & 1, 27);
+            tcgen05_fence_after();
+        };
+        auto release_results = [&](int it) {
+            tcgen05_fence_before();
+            __syncwarp();
+            if (lane == 0) {
+                mbarrier_arrive(&bars[kAccEmpty + (it & 1)]);
+            }
+        };
+
+        if constexpr (MODE == kForward) {
+            for (int it = 0; it < my_items; ++it) {
+                const Item item = item_at(it);
+                const int first_tile = it * tiles;
+                const uint32_t set_address =
+                    lane_base + kAccumulatorBase + (it & 1) * kSetColumns;
+                const uint32_t output = set_address + wg * HD;
+                // Online softmax over this group's share of the key tiles.
+                // The reference maximum is raised only when a tile exceeds it
+                // by more than 2^8, so the output accumulator is rescaled
+                // rarely.
+                float reference = -INFINITY;   // in units of scale2 * score
+                float sum = 0.0f;
+                bool seen = false;
+                for (int j = (first_tile & 1) ^ wg; j < tiles; j += 2, ++visit) {
+                    wait(kScoresFull + wg, visit & 1, 25);
+                    tcgen05_fence_after();
+                    const int valid = min(N, p.seq - j * N);
+                    if (valid == N) {
+                        // Full tile: the row's 128 scores in two halves, once
+                        // for the maximum and once for the exponentials.
+                        float top[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
+#pragma unroll 1
+                        for (int half = 0; half < 2; ++half) {
+                            uint32_t r[64];
+                            tcgen05_load_64(block_address + 64 * half, r);
+#pragma unroll
+                            for (int e = 0; e < 64; ++e) {
+                                top[e & 3] = fmaxf(top[e & 3], __uint_as_float(r[e]));
+                            }
+                        }
+                        const float tile_max =
+                            fmaxf(fmaxf(top[0], top[1]), fmaxf(top[2], top[3])) * p.scale2;
+                        const bool raise = tile_max > reference + 8.0f;
+                        float factor = 1.0f;
+                        if (raise) {
+                            factor = exp2_approx(reference - tile_max);   // 0 the first time
+                            reference = tile_max;
+                            sum *= factor;
+                        }
+                        if (seen && __any_sync(kFullMask, raise)) {
+                            wait(kUpdateDone + wg, (visit - 1) & 1, 26);
+                            tcgen05_fence_after();
+#pragma unroll
+                            for (int c = 0; c < kBlocks; ++c) {
+                                uint32_t o[32];
+                                tcgen05_load_32(output + 32 * c, o);
+#pragma unroll
+                                for (int e = 0; e < 32; ++e) {
+                                    o[e] = __float_as_uint(__uint_as_float(o[e]) * factor);
+                                }
+                                tcgen05_store_32(output + 32 * c, o);
+                            }
+                        }
+                        const float shift = -reference;
+                        float part[4] = {0.0f, 0.0f, 0.0f, 0.0f};
+#pragma unroll 1
+                        for (int half = 0; half < 2; ++half) {
+                            uint32_t r[64];
+                            tcgen05_load_64(block_address + 64 * half, r);
+#pragma unroll
+                            for (int e = 0; e < 64; ++e) {
+                                r[e] = round_tf32(exp2_approx(
+                                    fmaf(__uint_as_float(r[e]), p.scale2, shift)));
+                                part[e & 3] += __uint_as_float(r[e]);
+                            }
+                            tcgen05_store_64(block_address + 64 * half, r);
+                        }
+                        sum += (part[0] + part[1]) + (part[2] + part[3]);
+                    } else {
+                        // Partial last tile: 32 columns at a time, columns
+                        // past the end of the group masked out.
+                        const int chunks = (valid + 31) >> 5;
+                        float tile_max = -INFINITY;
+#pragma unroll 1
+                        for (int c = 0; c < chunks; ++c) {
+                            uint32_t r[32];
+                            tcgen05_load_32(block_address + 32 * c, r);
+                            const int live = valid - 32 * c;
+#pragma unroll
+                            for (int e = 0; e < 32; ++e) {
+                                if (e < live) {
+                                    tile_max = fmaxf(tile_max, __uint_as_float(r[e]));
+                                }
+                            }
+                        }
+                        tile_max *= p.scale2;
+                        const bool raise = tile_max > reference + 8.0f;
+                        float factor = 1.0f;
+                        if (raise) {
+                            factor = exp2_approx(reference - tile_max);
+                            reference = tile_max;
+                            sum *= factor;
+                        }
+                        if (seen && __any_sync(kFullMask, raise)) {
+                            wait(kUpdateDone + wg, (visit - 1) & 1, 26);
+                            tcgen05_fence_after();
+#pragma unroll
+                            for (int c = 0; c < kBlocks; ++c) {
+                                uint32_t o[32];
+                                tcgen05_load_32(output + 32 * c, o);
+#pragma unroll
+                                for (int e = 0; e < 32; ++e) {
+                                    o[e] = __float_as_uint(__uint_as_float(o[e]) * factor);
+                                }
+                                tcgen05_store_32(output + 32 * c, o);
+                            }
+                        }
+                        const float shift = -reference;
+#pragma unroll 1
+                        for (int c = 0; c < chunks; ++c) {
+                            uint32_t r[32];
+                            tcgen05_load_32(block_address + 32 * c, r);
+                            const int live = valid - 32 * c;
+#pragma unroll
+                            for (int e = 0; e < 32; ++e) {
+                                float value = exp2_approx(
+                                    fmaf(__uint_as_float(r[e]), p.scale2, shift));
+                                if (e >= live) {
+                                    value = 0.0f;
+                                }
+                                r[e] = round_tf32(value);
+                                sum += __uint_as_float(r[e]);
+                            }
+                            tcgen05_store_32(block_address + 32 * c, r);
+                        }
+                    }
+                    publish_block();
+                    seen = true;
+                }
+                // Merge the two groups' halves: O = (w0 O0 + w1 O1) / (w0 l0 +
+                // w1 l1) with w = 2^(m - max(m0, m1)); a group that saw no tile
+                // has l = 0 and its accumulator is not read.
+                float *stats = table + (it & 1) * 512;
+                stats[wg * kTileRows + row] = reference;
+                stats[256 + wg * kTileRows + row] = sum;
+                group_barrier(1, 256);
+                const float m_a = stats[row], m_b = stats[kTileRows + row];
+                const float l_a = stats[256 + row], l_b = stats[256 + kTileRows + row];
+                const float top = fmaxf(m_a, m_b);
+                const float w_a = l_a > 0.0f ? exp2_approx(m_a - top) : 0.0f;
+                const float w_b = l_b > 0.0f ? exp2_approx(m_b - top) : 0.0f;
+                const float total = l_a * w_a + l_b * w_b;
+                const float inverse = 1.0f / total;
+                if (wg == 0 && p.lse && item.m0 + row < p.seq) {
+                    p.lse[size_t(item.group) * p.seq + item.m0 + row] = top + log2f(total);
+                }
+                const bool use_a = tiles > 1 || (first_tile & 1) == 0;
+                const bool use_b = tiles > 1 || (first_tile & 1) == 1;
+                await_results(it);
+                uint32_t r[32];
+                const int block = wg;   // group 0: columns 0..31, group 1: 32..63
+                if (block < kBlocks) {
+                    uint32_t other[32];
+                    if (use_a) {
+                        tcgen05_load_32(set_address + 32 * block, r);
+                    }
+                    if (use_b) {
+                        tcgen05_load_32(set_address + HD + 32 * block, other);
+                    }
+#pragma unroll
+                    for (int e = 0; e < 32; ++e) {
+                        const float a = use_a ? __uint_as_float(r[e]) * w_a : 0.0f;
+                        const float b = use_b ? __uint_as_float(other[e]) * w_b : 0.0f;
+                        r[e] = __float_as_uint((a + b) * inverse);
+                    }
+                }
+                release_results(it);
+                if (block < kBlocks) {
+                    store_block(r, &maps.out[0], item, 32 * block, false);
+                }
+            }
+        } else if constexpr (MODE == kGradQuery) {
+            for (int it = 0; it < my_items; ++it) {
+                const Item item = item_at(it);
+                const int first_tile = it * tiles;
+                const size_t group_row0 = size_t(item.group) * p.seq;
+                const int q = item.m0 + row;
+                const float row_lse = q < p.seq ? p.lse[group_row0 + q] : 0.0f;
+                const float row_dot = q < p.seq ? p.row_dots[group_row0 + q] : 0.0f;
+                for (int j = (first_tile & 1) ^ wg; j < tiles; j += 2, ++visit) {
+                    wait(kScoresFull + wg, visit & 1, 25);
+                    tcgen05_fence_after();
+                    const int valid = min(N, p.seq - j * N);
+                    const int chunks = (valid + 31) >> 5;
+#pragma unroll 1
+                    for (int c = 0; c < chunks; ++c) {
+                        uint32_t s[32], g[32];
+                        tcgen05_load_32_pair(block_address + 32 * c,
+                                             block_address + N + 32 * c, s, g);
+#pragma unroll
+                        for (int e = 0; e < 32; ++e) {
+                            const float probability = exp2_approx(
+                                fmaf(__uint_as_float(s[e]), p.scale2, -row_lse));
+                            s[e] = round_tf32(
+                                probability *
+                                ((__uint_as_float(g[e]) - row_dot) * p.scale));
+                        }
+                        tcgen05_store_32(block_address + 32 * c, s);
+                    }
+                    publish_block();
+                }
+                await_results(it);
+                if (wg == 0) {
+                    // One group stores; the other goes on to the next item.
+                    const uint32_t set_address =
+                        lane_base + kAccumulatorBase + (it & 1) * kSetColumns;
+                    uint32_t r[kBlocks][32];
+#pragma unroll
+                    for (int block = 0; block < kBlocks; ++block) {
+                        tcgen05_load_32(set_address + 32 * block, r[block]);
+                    }
+                    release_results(it);
+#pragma unroll
+                    for (int block = 0; block < kBlocks; ++block) {
+                        store_block(r[block], &maps.out[0], item, 32 * block, p.add0 != 0);
+                    }
+                } else {
+                    release_results(it);
+                }
+            }
+        } else {
+            static_assert(MODE != kGradKeyValue || N == 64, "table size");
+            // Rows are keys, columns the queries of tile j: their log-sum-exp
+            // and D come from a table in shared memory, fetched one visit
+            // ahead by this group's 128 threads (64 of each).
+            float2 *pairs = reinterpret_cast<float2 *>(table) + wg * 2 * N;
+            const int t = int(threadIdx.x) - 64 - wg * 128;
+            // The tile this group transforms after (it, j); false at the end.
+            auto advance = [&](int &it, int &j) {
+                j += 2;
+                while (j >= tiles) {
+                    if (++it >= my_items) {
+                        return false;
+                    }
+                    j = ((it * tiles) & 1) ^ wg;
+                }
+                return true;
+            };
+            auto fetch = [&](int it, int j) {
+                const Item item = item_at(it);
+                const int q = j * N + (t & (N - 1));
+                if (q >= p.seq) {
+                    return 0.0f;
+                }
+                return (t < N ? p.lse : p.row_dots)[size_t(item.group) * p.seq + q];
+            };
+            auto put = [&](int buffer, float value) {
+                float *pair = reinterpret_cast<float *>(pairs + buffer * N + (t & (N - 1)));
+                pair[t < N ? 0 : 1] = value;
+            };
+            int ahead_it = 0, ahead_j = wg - 2;
+            bool ahead = my_items > 0 && advance(ahead_it, ahead_j);
+            if (ahead) {
+                put(0, fetch(ahead_it, ahead_j));
+                ahead = advance(ahead_it, ahead_j);
+            }
+            for (int it = 0; it < my_items; ++it) {
+                const Item item = item_at(it);
+                const int first_tile = it * tiles;
+                for (int j = (first_tile & 1) ^ wg; j < tiles; j += 2, ++visit) {
+                    const float next = ahead ? fetch(ahead_it, ahead_j) : 0.0f;
+                    group_barrier(2 + wg, 128);
+                    wait(kScoresFull + wg, visit & 1, 25);
+                    tcgen05_fence_after();
+                    const float2 *columns = pairs + (visit & 1) * N;
+                    const int valid = min(N, p.seq - j * N);
+                    const int chunks = (valid + 31) >> 5;
+#pragma unroll 1
+                    for (int c = 0; c < chunks; ++c) {
+                        uint32_t s[32], g[32];
+                        tcgen05_load_32_pair(block_address + 32 * c,
+                                             block_address + N + 32 * c, s, g);
+#pragma unroll
+                        for (int e = 0; e < 32; e += 2) {
+                            const float4 two =
+                                *reinterpret_cast<const float4 *>(columns + 32 * c + e);
+                            const float p0 = exp2_approx(
+                                fmaf(__uint_as_float(s[e]), p.scale2, -two.x));
+                            const float p1 = exp2_approx(
+                                fmaf(__uint_as_float(s[e + 1]), p.scale2, -two.z));
+                            g[e] = round_tf32(
+                                p0 * ((__uint_as_float(g[e]) - two.y) * p.scale));
+                            g[e + 1] = round_tf32(
+                                p1 * ((__uint_as_float(g[e + 1]) - two.w) * p.scale));
+                            s[e] = round_tf32(p0);
+                            s[e + 1] = round_tf32(p1);
+                        }
+                        tcgen05_store_32(block_address + 32 * c, s);
+                        tcgen05_store_32(block_address + N + 32 * c, g);
+                    }
+                    publish_block();
+                    if (ahead) {
+                        put((visit + 1) & 1, next);
+                        ahead = advance(ahead_it, ahead_j);
+                    }
+                }
+                // Group 0 stores dV, group 1 stores dK.
+                await_results(it);
+                const uint32_t mine =
+                    lane_base + kAccumulatorBase + (it & 1) * kSetColumns + wg * HD;
+                uint32_t r[kBlocks][32];
+#pragma unroll
+                for (int block = 0; block < kBlocks; ++block) {
+                    tcgen05_load_32(mine + 32 * block, r[block]);
+                }
+                release_results(it);
+#pragma unroll
+                for (int block = 0; block < kBlocks; ++block) {
+                    store_block(r[block], &maps.out[wg], item, 32 * block,
+                                (wg ? p.add1 : p.add0) != 0);
+                }
+            }
+        }
+        if (lane == 0) {
+            asm volatile("cp.async.bulk.wait_group 0;" ::: "memory");
+        }
+    }
+    tcgen05_fence_before();
+    __syncthreads();
+    if (warp == 1) {
+        __syncwarp();
+        tcgen05_fence_after();
+        tmem_free(tmem_base, kTmemColumns);
+    }
+}
+
+// dots[g * seq + t] = sum_c dO[g, t, c] * O[g, t, c]; one warp per row.
+template <int HD>
+__global__ void __launch_bounds__(256)
+attention_row_dots_kernel(const float *__restrict__ out, const float *__restrict__ dout,
+                          float *__restrict__ dots, size_t rows, int seq,
+                          HeadLayout out_layout, HeadLayout dout_layout) {
+    const int lane = threadIdx.x & 31;
+    const size_t warps = grid_threads() >> 5;
+    for (size_t r = global_thread() >> 5; r < rows; r += warps) {
+        const size_t group = r / size_t(seq), t = r % size_t(seq);
+        const size_t o_at =
+            (group / out_layout.heads) * seq * size_t(out_layout.ld) +
+            (group % out_layout.heads) * HD + t * size_t(out_layout.ld);
+        const size_t d_at =
+            (group / dout_layout.heads) * seq * size_t(dout_layout.ld) +
+            (group % dout_layout.heads) * HD + t * size_t(dout_layout.ld);
+        float sum = 0.0f;
+#pragma unroll
+        for (int c = 0; c < HD / 32; ++c) {
+            sum += out[o_at + 32 * c + lane] * dout[d_at + 32 * c + lane];
+        }
+        sum = warp_sum(sum);
+        if (lane == 0) {
+            dots[r] = sum;
+        }
+    }
+}
+
+// ---- host side -------------------------------------------------------------
+
+using EncodeTiled = CUresult (*)(CUtensorMap *, CUtensorMapDataType, cuuint32_t,
+                                 void *, const cuuint64_t *, const cuuint64_t *,
+                                 const cuuint32_t *, const cuuint32_t *,
+                                 CUtensorMapInterleave, CUtensorMapSwizzle,
+                                 CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+EncodeTiled encode_tiled() {
+    static EncodeTiled function = []() -> EncodeTiled {
+        void *entry = nullptr;
+        cudaDriverEntryPointQueryResult result;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &entry,
+                                    cudaEnableDefault, &result) != cudaSuccess ||
+            result != cudaDriverEntryPointSuccess) {
+            return nullptr;
+        }
+        return reinterpret_cast<EncodeTiled>(entry);
+    }();
+    return function;
+}
+
+struct MapKey {
+    const void *base;
+    int ld, heads, seq, samples, head_dim, box_rows, kind;
+    bool operator==(const MapKey &o) const {
+        return base == o.base && ld == o.ld && heads == o.heads && seq == o.seq &&
+               samples == o.samples && head_dim == o.head_dim &&
+               box_rows == o.box_rows && kind == o.kind;
+    }
+};
+
+struct MapKeyHash {
+    size_t operator()(const MapKey &k) const {
+        size_t h = reinterpret_cast<size_t>(k.base);
+        for (int v : {k.ld, k.heads, k.seq, k.samples, k.head_dim, k.box_rows, k.kind}) {
+            h = h * 1000003u ^ size_t(v);
+        }
+        return h;
+    }
+};
+
+constexpr int kMapKMajor = 0;   // TF32, 128-byte swizzle, 32 x box_rows
+constexpr int kMapBox32 = 1;    // TF32, 32-byte-atom swizzle, 32 x 32
+constexpr int kMapStore = 2;    // FP32, 128-byte swizzle, 32 x 32
+
+// [samples][seq][heads * head_dim] view of a tensor whose rows are `ld` floats
+// apart: the token-major projection matrix (heads > 1, base = first column of
+// Q, K or V) or a head-major tensor (heads = 1, ld = head_dim, one "sample"
+// per group).  Rows past `seq` read as zero and are not written.
+bool group_map(const float *base, HeadLayout layout, size_t groups, size_t seq,
+               int head_dim, int box_rows, int kind, CUtensorMap *out) {
+    static std::unordered_map<MapKey, CUtensorMap, MapKeyHash> cache;
+    const int samples = int(groups / size_t(layout.heads));
+    const MapKey key{base, layout.ld, layout.heads, int(seq), samples, head_dim,
+                     box_rows, kind};
+    auto found = cache.find(key);
+    if (found != cache.end()) {
+        *out = found->second;
+        return true;
+    }
+    EncodeTiled encode = encode_tiled();
+    if (!encode) {
+        return false;
+    }
+    const cuuint64_t dims[3] = {cuuint64_t(layout.heads) * head_dim, seq,
+                                cuuint64_t(samples)};
+    const cuuint64_t strides[2] = {cuuint64_t(layout.ld) * sizeof(float),
+                                   cuuint64_t(seq) * layout.ld * sizeof(float)};
+    const cuuint32_t box[3] = {32, cuuint32_t(box_rows), 1};
+    const cuuint32_t element_strides[3] = {1, 1, 1};
+    const CUresult status = encode(
+        out,
+        kind == kMapStore ? CU_TENSOR_MAP_DATA_TYPE_FLOAT32
+                          : CU_TENSOR_MAP_DATA_TYPE_TFLOAT32,
+        3, const_cast<float *>(base), dims, strides, box, element_strides,
+        CU_TENSOR_MAP_INTERLEAVE_NONE,
+        kind == kMapBox32 ? CU_TENSOR_MAP_SWIZZLE_128B_ATOM_32B
+                          : CU_TENSOR_MAP_SWIZZLE_128B,
+        CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (status != CUDA_SUCCESS) {
+        return false;
+    }
+    if (cache.size() > 4096) {
+        cache.clear();
+    }
+    cache.emplace(key, *out);
+    return true;
+}
+
+HeadLayout resolved(HeadLayout layout, size_t head_dim) {
+    if (layout.ld == 0) {
+        layout.ld = int(head_dim);
+        layout.heads = 1;
+    }
+    return layout;
+}
+
+bool operand_ok(const void *pointer, HeadLayout layout, size_t groups) {
+    return (reinterpret_cast<uintptr_t>(pointer) & 15) == 0 && layout.ld % 4 == 0 &&
+           layout.heads >= 1 && groups % size_t(layout.heads) == 0;
+}
+
+template <int HD, int MODE>
+constexpr int smem_bytes() {
+    using T = Traits<MODE>;
+    const int bytes = T::kResident * kTileRows * HD * 4 +
+                      2 * (T::kProducts + T::kUpdates) * T::kCols * HD * 4 +
+                      T::kStagingBytes + kBarrierBytes + T::kTableBytes;
+    return bytes < kMinSmemBytes ? kMinSmemBytes : bytes;
+}
+
+int sm_count() {
+    static const int count = []() {
+        int device = 0, value = 0;
+        if (cudaGetDevice(&device) != cudaSuccess ||
+            cudaDeviceGetAttribute(&value, cudaDevAttrMultiProcessorCount, device) !=
+                cudaSuccess ||
+            value <= 0) {
+            return int(kSmCount);
+        }
+        return value;
+    }();
+    return count;
+}
+
+template <int HD, int MODE>
+bool launch(const AttnMaps &maps, AttnParams params, size_t groups,
+            cudaStream_t stream) {
+    static bool configured = false;
+    constexpr int bytes = smem_bytes<HD, MODE>();
+    static_assert(bytes <= 227 * 1024, "shared memory");
+    if (!configured) {
+        if (cudaFuncSetAttribute(attention_tc_kernel<HD, MODE>,
+                                 cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                 bytes) != cudaSuccess) {
+            return false;
+        }
+        configured = true;
+    }
+    const size_t items = groups * size_t(params.row_tiles);
+    if (items > size_t(INT_MAX)) {
+        return false;
+    }
+    params.items = int(items);
+    // One persistent CTA per SM (it owns the SM's tensor memory).
+    const unsigned grid = unsigned(std::min<size_t>(items, size_t(sm_count())));
+    attention_tc_kernel<HD, MODE><<<grid, kAttnThreads, bytes, stream>>>(maps, params);
+    ++g_kernel_launches;
+    return true;
+}
+
+AttnParams base_params(size_t seq, int heads, float scale) {
+    AttnParams params;
+    memset(&params, 0, sizeof(params));
+    params.seq = int(seq);
+    params.heads = heads;
+    params.row_tiles = int((seq + kTileRows - 1) / kTileRows);
+    params.scale = scale;
+    params.scale2 = scale * 1.4426950408889634f;
+    params.status = tc_status_device_pointer();
+    return params;
+}
+
+}  // namespace
+
+bool attention_tc_supported(size_t seq, size_t head_dim) {
+    return (head_dim == 32 || head_dim == 64) && seq >= 1 && seq <= (1u << 20);
+}
+
+bool launch_attention_tc_forward(const float *q, const float *k, const float *v,
+                                 float *out, float *lse, size_t groups, size_t seq,
+                                 size_t head_dim, float scale, cudaStream_t stream,
+                                 HeadLayout in_layout, HeadLayout out_layout) {
+    if (!attention_tc_supported(seq, head_dim) || groups == 0) {
+        return false;
+    }
+    in_layout = resolved(in_layout, head_dim);
+    out_layout = resolved(out_layout, head_dim);
+    if (!operand_ok(q, in_layout, groups) || !operand_ok(k, in_layout, groups) ||
+        !operand_ok(v, in_layout, groups) || !operand_ok(out, out_layout, groups)) {
+        return false;
+    }
+    const int hd = int(head_dim);
+    AttnMaps maps;
+    memset(&maps, 0, sizeof(maps));
+    constexpr int N = Traits<kForward>::kCols;
+    if (!group_map(q, in_layout, groups, seq, hd, kTileRows, kMapKMajor, &maps.resident[0]) ||
+        !group_map(k, in_layout, groups, seq, hd, N, kMapKMajor, &maps.ss[0]) ||
+        !group_map(v, in_layout, groups, seq, hd, 32, kMapBox32, &maps.ts[0]) ||
+        !group_map(out, out_layout, groups, seq, hd, 32, kMapStore, &maps.out[0])) {
+        return false;
+    }
+    AttnParams params = base_params(seq, in_layout.heads, scale);
+    if (!params.status || out_layout.heads != in_layout.heads) {
+        return false;
+    }
+    params.lse = lse;
+    return hd == 32 ? launch<32, kForward>(maps, params, groups, stream)
+                    : launch<64, kForward>(maps, params, groups, stream);
+}
+
+bool launch_attention_tc_backward(const float *q, const float *k, const float *v,
+                                  const float *out, const float *dout,
+                                  const float *lse, float *dq, float *dk, float *dv,
+                                  float *row_dots, size_t groups, size_t seq,
+                                  size_t head_dim, float scale, bool add_q,
+                                  bool add_k, bool add_v, cudaStream_t stream,
+                                  HeadLayout in_layout, HeadLayout out_layout,
+                                  HeadLayout dout_layout, HeadLayout grad_layout) {
+    if (!attention_tc_supported(seq, head_dim) || groups == 0) {
+        return false;
+    }
+    in_layout = resolved(in_layout, head_dim);
+    out_layout = resolved(out_layout, head_dim);
+    dout_layout = resolved(dout_layout, head_dim);
+    grad_layout = resolved(grad_layout, head_dim);
+    if (!operand_ok(q, in_layout, groups) || !operand_ok(k, in_layout, groups) ||
+        !operand_ok(v, in_layout, groups) || !operand_ok(dout, dout_layout, groups) ||
+        !operand_ok(dq, grad_layout, groups) || !operand_ok(dk, grad_layout, groups) ||
+        !operand_ok(dv, grad_layout, groups) || out_layout.heads < 1 ||
+        groups % size_t(out_layout.heads) != 0 ||
+        in_layout.heads != dout_layout.heads || in_layout.heads != grad_layout.heads) {
+        return false;
+    }
+    const int hd = int(head_dim);
+    AttnMaps query_maps, key_maps;
+    memset(&query_maps, 0, sizeof(query_maps));
+    memset(&key_maps, 0, sizeof(key_maps));
+    constexpr int NQ = Traits<kGradQuery>::kCols;
+    constexpr int NK = Traits<kGradKeyValue>::kCols;
+    if (!group_map(q, in_layout, groups, seq, hd, kTileRows, kMapKMajor, &query_maps.resident[0]) ||
+        !group_map(dout, dout_layout, groups, seq, hd, kTileRows, kMapKMajor, &query_maps.resident[1]) ||
+        !group_map(k, in_layout, groups, seq, hd, NQ, kMapKMajor, &query_maps.ss[0]) ||
+        !group_map(v, in_layout, groups, seq, hd, NQ, kMapKMajor, &query_maps.ss[1]) ||
+        !group_map(k, in_layout, groups, seq, hd, 32, kMapBox32, &query_maps.ts[0]) ||
+        !group_map(dq, grad_layout, groups, seq, hd, 32, kMapStore, &query_maps.out[0]) ||
+        !group_map(k, in_layout, groups, seq, hd, kTileRows, kMapKMajor, &key_maps.resident[0]) ||
+        !group_map(v, in_layout, groups, seq, hd, kTileRows, kMapKMajor, &key_maps.resident[1]) ||
+        !group_map(q, in_layout, groups, seq, hd, NK, kMapKMajor, &key_maps.ss[0]) ||
+        !group_map(dout, dout_layout, groups, seq, hd, NK, kMapKMajor, &key_maps.ss[1]) ||
+        !group_map(dout, dout_layout, groups, seq, hd, 32, kMapBox32, &key_maps.ts[0]) ||
+        !group_map(q, in_layout, groups, seq, hd, 32, kMapBox32, &key_maps.ts[1]) ||
+        !group_map(dv, grad_layout, groups, seq, hd, 32, kMapStore, &key_maps.out[0]) ||
+        !group_map(dk, grad_layout, groups, seq, hd, 32, kMapStore, &key_maps.out[1])) {
+        return false;
+    }
+    AttnParams params = base_params(seq, in_layout.heads, scale);
+    if (!params.status) {
+        return false;
+    }
+    params.lse = const_cast<float *>(lse);
+    params.row_dots = row_dots;
+    const size_t rows = groups * seq;
+    const unsigned dots_grid = unsigned(std::min<size_t>((rows + 7) / 8, 148 * 8));
+    if (hd == 32) {
+        attention_row_dots_kernel<32><<<dots_grid, 256, 0, stream>>>(
+            out, dout, row_dots, rows, int(seq), out_layout, dout_layout);
+    } else {
+        attention_row_dots_kernel<64><<<dots_grid, 256, 0, stream>>>(
+            out, dout, row_dots, rows, int(seq), out_layout, dout_layout);
+    }
+    ++g_kernel_launches;
+    AttnParams query_params = params;
+    query_params.add0 = add_q ? 1 : 0;
+    AttnParams key_params = params;
+    key_params.add0 = add_v ? 1 : 0;
+    key_params.add1 = add_k ? 1 : 0;
+    if (hd == 32) {
+        return launch<32, kGradQuery>(query_maps, query_params, groups, stream) &&
+               launch<32, kGradKeyValue>(key_maps, key_params, groups, stream);
+    }
+    return launch<64, kGradQuery>(query_maps, query_params, groups, stream) &&
+           launch<64, kGradKeyValue>(key_maps, key_params, groups, stream);
+}
+
+}  // namespace vitb200

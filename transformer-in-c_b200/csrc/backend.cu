@@ -2982,6 +2982,55 @@ extern "C" int vitb200_k_attention_stream_backward(
         ? 0 : -1;
 }
 
+// ld == 0: head-major tensors ([groups*seq, head_dim]).  Otherwise every
+// operand is a block of `heads * head_dim` columns inside a token-major matrix
+// whose rows are `ld` floats apart (the pointers name the first column), as
+// the Q, K, V blocks of the projection and the merged attention output are.
+static HeadLayout abi_layout(size_t ld, size_t heads) {
+    HeadLayout layout;
+    if (ld != 0) {
+        layout.ld = int(ld);
+        layout.heads = int(heads);
+    }
+    return layout;
+}
+
+extern "C" int vitb200_k_attention_tc(const float *q, const float *k,
+                                      const float *v, float *out, float *lse,
+                                      size_t groups, size_t seq, size_t head_dim,
+                                      float scale, size_t in_ld, size_t out_ld,
+                                      size_t heads, void *stream) {
+    if (!fits_int(seq) || !fits_int(groups) || !fits_int(heads) ||
+        in_ld > size_t(INT_MAX) || out_ld > size_t(INT_MAX)) {
+        return -1;
+    }
+    return launch_attention_tc_forward(q, k, v, out, lse, groups, seq, head_dim,
+                                       scale, as_stream(stream),
+                                       abi_layout(in_ld, heads),
+                                       abi_layout(out_ld, heads))
+        ? 0 : -1;
+}
+
+extern "C" int vitb200_k_attention_tc_backward(
+    const float *q, const float *k, const float *v, const float *out,
+    const float *dout, const float *lse, float *dq, float *dk, float *dv,
+    float *row_dots, size_t groups, size_t seq, size_t head_dim, float scale,
+    int accumulate, size_t in_ld, size_t out_ld, size_t grad_ld, size_t heads,
+    void *stream) {
+    if (!fits_int(seq) || !fits_int(groups) || !fits_int(heads) ||
+        in_ld > size_t(INT_MAX) || out_ld > size_t(INT_MAX) ||
+        grad_ld > size_t(INT_MAX)) {
+        return -1;
+    }
+    const bool add = accumulate != 0;
+    return launch_attention_tc_backward(
+               q, k, v, out, dout, lse, dq, dk, dv, row_dots, groups, seq,
+               head_dim, scale, add, add, add, as_stream(stream),
+               abi_layout(in_ld, heads), abi_layout(out_ld, heads),
+               abi_layout(out_ld, heads), abi_layout(grad_ld, heads))
+        ? 0 : -1;
+}
+
 extern "C" int vitb200_k_attention_backward(
     const float *q, const float *k, const float *v, const float *probabilities,
     const float *out, const float *dout, float *dq, float *dk, float *dv,

@@ -35,6 +35,7 @@
 #include "gemm_tc.h"
 #include "kernels.h"
 #include "device_util.cuh"
+#include "tcgen05.cuh"
 
 #include <cuda.h>
 #include <cstdio>
@@ -56,155 +57,8 @@ constexpr int kMaxStages = 6;
 constexpr int kSmemLimit = 227 * 1024 - 1024;   // leave room for static shared memory
 constexpr int kThreads = 192;
 constexpr int kBarrierBytes = 256;   // 2 x kMaxStages + 4 mbarriers, TMEM slot
-constexpr unsigned long long kWaitLimitNs = 2000000000ull;  // 2 s
 
-// ---- PTX wrappers ----------------------------------------------------------
-
-__device__ __forceinline__ uint32_t smem_address(const void *pointer) {
-    return static_cast<uint32_t>(__cvta_generic_to_shared(pointer));
-}
-
-__device__ __forceinline__ unsigned long long global_timer_ns() {
-    unsigned long long t;
-    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
-    return t;
-}
-
-__device__ __forceinline__ void mbarrier_init(uint64_t *bar, uint32_t count) {
-    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_address(bar)),
-                 "r"(count));
-}
-
-__device__ __forceinline__ void mbarrier_expect_tx(uint64_t *bar, uint32_t bytes) {
-    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(
-                     smem_address(bar)),
-                 "r"(bytes)
-                 : "memory");
-}
-
-__device__ __forceinline__ bool mbarrier_try_wait(uint64_t *bar, uint32_t parity) {
-    uint32_t done;
-    asm volatile(
-        "{\n\t"
-        ".reg .pred p;\n\t"
-        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
-        "selp.u32 %0, 1, 0, p;\n\t"
-        "}"
-        : "=r"(done)
-        : "r"(smem_address(bar)), "r"(parity)
-        : "memory");
-    return done != 0;
-}
-
-// Returns false if the phase did not complete within kWaitLimitNs.
-__device__ __forceinline__ bool mbarrier_wait(uint64_t *bar, uint32_t parity) {
-    if (mbarrier_try_wait(bar, parity)) {
-        return true;
-    }
-    const unsigned long long start = global_timer_ns();
-    while (!mbarrier_try_wait(bar, parity)) {
-        if (global_timer_ns() - start > kWaitLimitNs) {
-            return false;
-        }
-    }
-    return true;
-}
-
-__device__ __forceinline__ void tma_load_2d(void *smem, const CUtensorMap *map,
-                                            int x, int y, uint64_t *bar) {
-    asm volatile(
-        "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes"
-        " [%0], [%1, {%2, %3}], [%4];" ::"r"(smem_address(smem)),
-        "l"(reinterpret_cast<uint64_t>(map)), "r"(x), "r"(y),
-        "r"(smem_address(bar))
-        : "memory");
-}
-
-__device__ __forceinline__ void tma_store_2d(const void *smem,
-                                             const CUtensorMap *map, int x,
-                                             int y) {
-    asm volatile(
-        "cp.async.bulk.tensor.2d.global.shared::cta.bulk_group [%0, {%2, %3}], [%1];" ::
-            "l"(reinterpret_cast<uint64_t>(map)),
-        "r"(smem_address(smem)), "r"(x), "r"(y)
-        : "memory");
-}
-
-__device__ __forceinline__ void tma_reduce_add_2d(const void *smem,
-                                                  const CUtensorMap *map, int x,
-                                                  int y) {
-    asm volatile(
-        "cp.reduce.async.bulk.tensor.2d.global.shared::cta.add.bulk_group"
-        " [%0, {%2, %3}], [%1];" ::"l"(reinterpret_cast<uint64_t>(map)),
-        "r"(smem_address(smem)), "r"(x), "r"(y)
-        : "memory");
-}
-
-__device__ __forceinline__ void tcgen05_fence_before() {
-    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
-}
-
-__device__ __forceinline__ void tcgen05_fence_after() {
-    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-}
-
-__device__ __forceinline__ void tcgen05_commit(uint64_t *bar) {
-    asm volatile(
-        "tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::
-            "r"(smem_address(bar))
-        : "memory");
-}
-
-__device__ __forceinline__ void tcgen05_mma_tf32(uint32_t tmem_d, uint64_t desc_a,
-                                                 uint64_t desc_b, uint32_t idesc,
-                                                 uint32_t accumulate) {
-    asm volatile(
-        "{\n\t"
-        ".reg .pred p;\n\t"
-        "setp.ne.b32 p, %4, 0;\n\t"
-        "tcgen05.mma.cta_group::1.kind::tf32 [%0], %1, %2, %3, p;\n\t"
-        "}" ::"r"(tmem_d),
-        "l"(desc_a), "l"(desc_b), "r"(idesc), "r"(accumulate)
-        : "memory");
-}
-
-__device__ __forceinline__ void tcgen05_load_32(uint32_t tmem_address,
-                                                uint32_t (&r)[32]) {
-    asm volatile(
-        "tcgen05.ld.sync.aligned.32x32b.x32.b32"
-        "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15,"
-        " %16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29,"
-        " %30, %31}, [%32];"
-        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]),
-          "=r"(r[6]), "=r"(r[7]), "=r"(r[8]), "=r"(r[9]), "=r"(r[10]),
-          "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]),
-          "=r"(r[16]), "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]),
-          "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]), "=r"(r[25]),
-          "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]),
-          "=r"(r[31])
-        : "r"(tmem_address));
-    asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
-}
-
-// Shared-memory operand descriptor with the Blackwell version field.  Offsets
-// are in bytes; the hardware fields drop the low four bits.  Layout types:
-// 2 = 128-byte swizzle of 16-byte chunks (K-major operands), 1 = 128-byte
-// swizzle of 32-byte chunks, the only layout tcgen05 accepts for 32-bit
-// operands whose output index is the contiguous one.
-constexpr uint32_t kLayoutSwizzle128 = 2;
-constexpr uint32_t kLayoutSwizzle128Base32 = 1;
-__device__ __forceinline__ uint64_t operand_descriptor(uint32_t smem_byte_address,
-                                                       uint32_t leading_bytes,
-                                                       uint32_t stride_bytes,
-                                                       uint32_t layout_type) {
-    uint64_t desc = 0;
-    desc |= uint64_t((smem_byte_address >> 4) & 0x3fff);
-    desc |= uint64_t((leading_bytes >> 4) & 0x3fff) << 16;
-    desc |= uint64_t((stride_bytes >> 4) & 0x3fff) << 32;
-    desc |= uint64_t(1) << 46;   // descriptor version
-    desc |= uint64_t(layout_type) << 61;
-    return desc;
-}
+using namespace tc;
 
 struct TcParams {
     int m, n;                 // output extents
@@ -230,11 +84,6 @@ constexpr int kSecondResidual = 2;   // D = A*B + bias, D2 = D + residual
 // map_d2 (one 32 x 32 block per accumulator block, by TMA into the block the
 // result is then staged in); there is one output.
 constexpr int kGeluSlope = 3;
-
-__device__ __forceinline__ void mbarrier_arrive(uint64_t *bar) {
-    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_address(bar))
-                 : "memory");
-}
 
 // Persistent kernel: each CTA walks work items (output tile x reduction
 // slice) item = blockIdx.x, blockIdx.x + gridDim.x, ...; the three roles run
@@ -1063,6 +912,16 @@ int launch_gemm_tc(const TcGemm &g, cudaStream_t stream) {
 int gemm_tc_status() {
     int *word = status_word();
     return word ? *word : 0;
+}
+
+int *tc_status_device_pointer() {
+    int *word = status_word();
+    int *device = nullptr;
+    if (!word || cudaHostGetDevicePointer(reinterpret_cast<void **>(&device),
+                                          word, 0) != cudaSuccess) {
+        return nullptr;
+    }
+    return device;
 }
 
 }  // namespace vitb200

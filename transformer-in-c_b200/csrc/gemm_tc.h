@@ -42,5 +42,9 @@ bool gemm_tc_supported(const TcGemm &gemm);
 int launch_gemm_tc(const TcGemm &gemm, cudaStream_t stream);
 // 0, or the code of the first bounded wait that expired inside the kernel.
 int gemm_tc_status();
+// Device address of that status word, shared by every kernel of the library
+// that waits on an mbarrier (codes 1..15: matrix product, 16..: attention);
+// nullptr when it could not be mapped.
+int *tc_status_device_pointer();
 
 }  // namespace vitb200

@@ -213,6 +213,29 @@ bool launch_attention_stream_backward(const float *q, const float *k,
                                       HeadLayout out_layout = HeadLayout(),
                                       HeadLayout dout_layout = HeadLayout(),
                                       HeadLayout grad_layout = HeadLayout());
+// The same computation on the tcgen05 tensor cores (attention_tc.cu): 128-row
+// tiles, scores in tensor memory, operands by TMA; head_dim 32 or 64, any
+// sequence length (meant for seq >= 128).  Same log-sum-exp convention as the
+// streaming kernels, so either backward pass accepts either forward pass's
+// rows.  False = shape, alignment or layout not covered (nothing launched).
+bool attention_tc_supported(size_t seq, size_t head_dim);
+bool launch_attention_tc_forward(const float *q, const float *k, const float *v,
+                                 float *out, float *lse, size_t groups,
+                                 size_t seq, size_t head_dim, float scale,
+                                 cudaStream_t stream,
+                                 HeadLayout in_layout = HeadLayout(),
+                                 HeadLayout out_layout = HeadLayout());
+bool launch_attention_tc_backward(const float *q, const float *k, const float *v,
+                                  const float *out, const float *dout,
+                                  const float *lse, float *dq, float *dk,
+                                  float *dv, float *row_dots, size_t groups,
+                                  size_t seq, size_t head_dim, float scale,
+                                  bool add_q, bool add_k, bool add_v,
+                                  cudaStream_t stream,
+                                  HeadLayout in_layout = HeadLayout(),
+                                  HeadLayout out_layout = HeadLayout(),
+                                  HeadLayout dout_layout = HeadLayout(),
+                                  HeadLayout grad_layout = HeadLayout());
 // recompute = true: `probabilities` is not read; P is rebuilt from Q and K.
 bool launch_attention_small_backward(const float *q, const float *k,
                                      const float *v, const float *probabilities,
