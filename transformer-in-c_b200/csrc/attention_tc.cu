@@ -211,7 +211,7 @@ attention_tc_kernel(const __grid_constant__ AttnMaps maps, const AttnParams p) {
     // waits any more and every role runs its loops to their normal end, so no
     // barrier is left with a missing participant.
     auto wait = [&](int barrier, uint32_t parity, int code) {
-        if (*failed) {
+        if (mbarrier_try_wait(&bars[barrier], parity) || *failed) {
             return;
         }
         if (!mbarrier_wait(&bars[barrier], parity)) {
@@ -493,142 +493,33 @@ attention_tc_kernel(const __grid_constant__ AttnMaps maps, const AttnParams p) {
             }
         };
 
+        // The tensor cores drop the low 13 mantissa bits of an FP32 word in
+        // tensor memory.  Values written there are scaled by 1 + 2^-11 first
+        // (folded into an exponent or a factor that is applied anyway), which
+        // turns that truncation into rounding to nearest on average at no
+        // cost per element.
+        constexpr float kRoundUp = 1.00048828125f;            // 1 + 2^-11
+        constexpr float kRoundUpLog2 = 0.000704269011247f;    // log2(1 + 2^-11)
+
+        // Results of item `it` are merged / stored one tile into item it + 1
+        // (see the loops below): by then the next scores this group needs
+        // have been turned into work for the tensor pipe, so the stores and
+        // the wait for the item's last products stay off the critical path.
         if constexpr (MODE == kForward) {
-            for (int it = 0; it < my_items; ++it) {
+            float reference = -INFINITY;   // running maximum, in units of scale2 * score
+            float sum = 0.0f;              // row sum of P (times 1 + 2^-11)
+            float done_reference = 0.0f, done_sum = 0.0f;   // of the item awaiting its merge
+            // Merge the two groups' halves: O = (w0 O0 + w1 O1) / (w0 l0 +
+            // w1 l1) with w = 2^(m - max(m0, m1)); a group that saw no tile
+            // has l = 0 and its accumulator is not read.
+            auto finish = [&](int it) {
                 const Item item = item_at(it);
                 const int first_tile = it * tiles;
                 const uint32_t set_address =
                     lane_base + kAccumulatorBase + (it & 1) * kSetColumns;
-                const uint32_t output = set_address + wg * HD;
-                // Online softmax over this group's share of the key tiles.
-                // The reference maximum is raised only when a tile exceeds it
-                // by more than 2^8, so the output accumulator is rescaled
-                // rarely.
-                float reference = -INFINITY;   // in units of scale2 * score
-                float sum = 0.0f;
-                bool seen = false;
-                for (int j = (first_tile & 1) ^ wg; j < tiles; j += 2, ++visit) {
-                    wait(kScoresFull + wg, visit & 1, 25);
-                    tcgen05_fence_after();
-                    const int valid = min(N, p.seq - j * N);
-                    if (valid == N) {
-                        // Full tile: the row's 128 scores in two halves, once
-                        // for the maximum and once for the exponentials.
-                        float top[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
-#pragma unroll 1
-                        for (int half = 0; half < 2; ++half) {
-                            uint32_t r[64];
-                            tcgen05_load_64(block_address + 64 * half, r);
-#pragma unroll
-                            for (int e = 0; e < 64; ++e) {
-                                top[e & 3] = fmaxf(top[e & 3], __uint_as_float(r[e]));
-                            }
-                        }
-                        const float tile_max =
-                            fmaxf(fmaxf(top[0], top[1]), fmaxf(top[2], top[3])) * p.scale2;
-                        const bool raise = tile_max > reference + 8.0f;
-                        float factor = 1.0f;
-                        if (raise) {
-                            factor = exp2_approx(reference - tile_max);   // 0 the first time
-                            reference = tile_max;
-                            sum *= factor;
-                        }
-                        if (seen && __any_sync(kFullMask, raise)) {
-                            wait(kUpdateDone + wg, (visit - 1) & 1, 26);
-                            tcgen05_fence_after();
-#pragma unroll
-                            for (int c = 0; c < kBlocks; ++c) {
-                                uint32_t o[32];
-                                tcgen05_load_32(output + 32 * c, o);
-#pragma unroll
-                                for (int e = 0; e < 32; ++e) {
-                                    o[e] = __float_as_uint(__uint_as_float(o[e]) * factor);
-                                }
-                                tcgen05_store_32(output + 32 * c, o);
-                            }
-                        }
-                        const float shift = -reference;
-                        float part[4] = {0.0f, 0.0f, 0.0f, 0.0f};
-#pragma unroll 1
-                        for (int half = 0; half < 2; ++half) {
-                            uint32_t r[64];
-                            tcgen05_load_64(block_address + 64 * half, r);
-#pragma unroll
-                            for (int e = 0; e < 64; ++e) {
-                                r[e] = round_tf32(exp2_approx(
-                                    fmaf(__uint_as_float(r[e]), p.scale2, shift)));
-                                part[e & 3] += __uint_as_float(r[e]);
-                            }
-                            tcgen05_store_64(block_address + 64 * half, r);
-                        }
-                        sum += (part[0] + part[1]) + (part[2] + part[3]);
-                    } else {
-                        // Partial last tile: 32 columns at a time, columns
-                        // past the end of the group masked out.
-                        const int chunks = (valid + 31) >> 5;
-                        float tile_max = -INFINITY;
-#pragma unroll 1
-                        for (int c = 0; c < chunks; ++c) {
-                            uint32_t r[32];
-                            tcgen05_load_32(block_address + 32 * c, r);
-                            const int live = valid - 32 * c;
-#pragma unroll
-                            for (int e = 0; e < 32; ++e) {
-                                if (e < live) {
-                                    tile_max = fmaxf(tile_max, __uint_as_float(r[e]));
-                                }
-                            }
-                        }
-                        tile_max *= p.scale2;
-                        const bool raise = tile_max > reference + 8.0f;
-                        float factor = 1.0f;
-                        if (raise) {
-                            factor = exp2_approx(reference - tile_max);
-                            reference = tile_max;
-                            sum *= factor;
-                        }
-                        if (seen && __any_sync(kFullMask, raise)) {
-                            wait(kUpdateDone + wg, (visit - 1) & 1, 26);
-                            tcgen05_fence_after();
-#pragma unroll
-                            for (int c = 0; c < kBlocks; ++c) {
-                                uint32_t o[32];
-                                tcgen05_load_32(output + 32 * c, o);
-#pragma unroll
-                                for (int e = 0; e < 32; ++e) {
-                                    o[e] = __float_as_uint(__uint_as_float(o[e]) * factor);
-                                }
-                                tcgen05_store_32(output + 32 * c, o);
-                            }
-                        }
-                        const float shift = -reference;
-#pragma unroll 1
-                        for (int c = 0; c < chunks; ++c) {
-                            uint32_t r[32];
-                            tcgen05_load_32(block_address + 32 * c, r);
-                            const int live = valid - 32 * c;
-#pragma unroll
-                            for (int e = 0; e < 32; ++e) {
-                                float value = exp2_approx(
-                                    fmaf(__uint_as_float(r[e]), p.scale2, shift));
-                                if (e >= live) {
-                                    value = 0.0f;
-                                }
-                                r[e] = round_tf32(value);
-                                sum += __uint_as_float(r[e]);
-                            }
-                            tcgen05_store_32(block_address + 32 * c, r);
-                        }
-                    }
-                    publish_block();
-                    seen = true;
-                }
-                // Merge the two groups' halves: O = (w0 O0 + w1 O1) / (w0 l0 +
-                // w1 l1) with w = 2^(m - max(m0, m1)); a group that saw no tile
-                // has l = 0 and its accumulator is not read.
                 float *stats = table + (it & 1) * 512;
-                stats[wg * kTileRows + row] = reference;
-                stats[256 + wg * kTileRows + row] = sum;
+                stats[wg * kTileRows + row] = done_reference;
+                stats[256 + wg * kTileRows + row] = done_sum;
                 group_barrier(1, 256);
                 const float m_a = stats[row], m_b = stats[kTileRows + row];
                 const float l_a = stats[256 + row], l_b = stats[256 + kTileRows + row];
@@ -636,9 +527,10 @@ attention_tc_kernel(const __grid_constant__ AttnMaps maps, const AttnParams p) {
                 const float w_a = l_a > 0.0f ? exp2_approx(m_a - top) : 0.0f;
                 const float w_b = l_b > 0.0f ? exp2_approx(m_b - top) : 0.0f;
                 const float total = l_a * w_a + l_b * w_b;
-                const float inverse = 1.0f / total;
+                const float inverse = kRoundUp / total;
                 if (wg == 0 && p.lse && item.m0 + row < p.seq) {
-                    p.lse[size_t(item.group) * p.seq + item.m0 + row] = top + log2f(total);
+                    p.lse[size_t(item.group) * p.seq + item.m0 + row] =
+                        top + log2f(total) - kRoundUpLog2;
                 }
                 const bool use_a = tiles > 1 || (first_tile & 1) == 0;
                 const bool use_b = tiles > 1 || (first_tile & 1) == 1;
@@ -664,40 +556,141 @@ attention_tc_kernel(const __grid_constant__ AttnMaps maps, const AttnParams p) {
                 if (block < kBlocks) {
                     store_block(r, &maps.out[0], item, 32 * block, false);
                 }
-            }
-        } else if constexpr (MODE == kGradQuery) {
-            for (int it = 0; it < my_items; ++it) {
-                const Item item = item_at(it);
-                const int first_tile = it * tiles;
-                const size_t group_row0 = size_t(item.group) * p.seq;
-                const int q = item.m0 + row;
-                const float row_lse = q < p.seq ? p.lse[group_row0 + q] : 0.0f;
-                const float row_dot = q < p.seq ? p.row_dots[group_row0 + q] : 0.0f;
-                for (int j = (first_tile & 1) ^ wg; j < tiles; j += 2, ++visit) {
+            };
+            // One loop body for "transform the group's next tile" and "finish
+            // the previous item" (after the first tile of the next item, or
+            // at once when this group has no tile there).
+            int it = 0, j = wg;
+            bool seen = false, owed = false;
+            while (it < my_items || owed) {
+                const bool tile = it < my_items && j < tiles;
+                if (tile) {
+                    // Online softmax over this group's share of the key
+                    // tiles.  The reference maximum is raised only when a tile
+                    // exceeds it by more than 2^8, so the output accumulator
+                    // is rescaled rarely.
+                    const uint32_t output =
+                        lane_base + kAccumulatorBase + (it & 1) * kSetColumns + wg * HD;
                     wait(kScoresFull + wg, visit & 1, 25);
                     tcgen05_fence_after();
                     const int valid = min(N, p.seq - j * N);
-                    const int chunks = (valid + 31) >> 5;
+                    // Columns are handled 64 at a time (32 in the ragged last
+                    // block), once for the maximum and once for the
+                    // exponentials; columns past the end of the group count
+                    // as -inf / 0.
+                    float top[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
+                    if (valid == N) {
 #pragma unroll 1
-                    for (int c = 0; c < chunks; ++c) {
-                        uint32_t s[32], g[32];
-                        tcgen05_load_32_pair(block_address + 32 * c,
-                                             block_address + N + 32 * c, s, g);
+                        for (int half = 0; half < 2; ++half) {
+                            uint32_t r[64];
+                            tcgen05_load_64(block_address + 64 * half, r);
 #pragma unroll
-                        for (int e = 0; e < 32; ++e) {
-                            const float probability = exp2_approx(
-                                fmaf(__uint_as_float(s[e]), p.scale2, -row_lse));
-                            s[e] = round_tf32(
-                                probability *
-                                ((__uint_as_float(g[e]) - row_dot) * p.scale));
+                            for (int e = 0; e < 64; ++e) {
+                                top[e & 3] = fmaxf(top[e & 3], __uint_as_float(r[e]));
+                            }
                         }
-                        tcgen05_store_32(block_address + 32 * c, s);
+                    } else {
+#pragma unroll 1
+                        for (int c = 0; 32 * c < valid; ++c) {
+                            uint32_t r[32];
+                            tcgen05_load_32(block_address + 32 * c, r);
+                            const int live = valid - 32 * c;
+#pragma unroll
+                            for (int e = 0; e < 32; ++e) {
+                                if (e < live) {
+                                    top[e & 3] = fmaxf(top[e & 3], __uint_as_float(r[e]));
+                                }
+                            }
+                        }
                     }
+                    const float tile_max =
+                        fmaxf(fmaxf(top[0], top[1]), fmaxf(top[2], top[3])) * p.scale2;
+                    const bool raise = tile_max > reference + 8.0f;
+                    float factor = 1.0f;
+                    if (raise) {
+                        factor = exp2_approx(reference - tile_max);   // 0 the first time
+                        reference = tile_max;
+                        sum *= factor;
+                    }
+                    if (seen && __any_sync(kFullMask, raise)) {
+                        wait(kUpdateDone + wg, (visit - 1) & 1, 26);
+                        tcgen05_fence_after();
+#pragma unroll
+                        for (int c = 0; c < kBlocks; ++c) {
+                            uint32_t o[32];
+                            tcgen05_load_32(output + 32 * c, o);
+#pragma unroll
+                            for (int e = 0; e < 32; ++e) {
+                                o[e] = __float_as_uint(__uint_as_float(o[e]) * factor);
+                            }
+                            tcgen05_store_32(output + 32 * c, o);
+                        }
+                    }
+                    const float shift = kRoundUpLog2 - reference;
+                    float part[4] = {0.0f, 0.0f, 0.0f, 0.0f};
+                    if (valid == N) {
+#pragma unroll 1
+                        for (int half = 0; half < 2; ++half) {
+                            uint32_t r[64];
+                            tcgen05_load_64(block_address + 64 * half, r);
+#pragma unroll
+                            for (int e = 0; e < 64; ++e) {
+                                const float value =
+                                    exp2_approx(fmaf(__uint_as_float(r[e]), p.scale2, shift));
+                                part[e & 3] += value;
+                                r[e] = __float_as_uint(value);
+                            }
+                            tcgen05_store_64(block_address + 64 * half, r);
+                        }
+                    } else {
+#pragma unroll 1
+                        for (int c = 0; 32 * c < valid; ++c) {
+                            uint32_t r[32];
+                            tcgen05_load_32(block_address + 32 * c, r);
+                            const int live = valid - 32 * c;
+#pragma unroll
+                            for (int e = 0; e < 32; ++e) {
+                                float value =
+                                    exp2_approx(fmaf(__uint_as_float(r[e]), p.scale2, shift));
+                                if (e >= live) {
+                                    value = 0.0f;
+                                }
+                                part[e & 3] += value;
+                                r[e] = __float_as_uint(value);
+                            }
+                            tcgen05_store_32(block_address + 32 * c, r);
+                        }
+                    }
+                    sum += (part[0] + part[1]) + (part[2] + part[3]);
                     publish_block();
+                    seen = true;
+                    j += 2;
+                    ++visit;
                 }
+                if (owed) {
+                    finish(it - 1);
+                    owed = false;
+                }
+                if (!tile) {
+                    if (it >= my_items) {
+                        break;
+                    }
+                    done_reference = reference;
+                    done_sum = sum;
+                    reference = -INFINITY;
+                    sum = 0.0f;
+                    seen = false;
+                    ++it;
+                    j = ((it * tiles) & 1) ^ wg;
+                    owed = true;
+                }
+            }
+        } else if constexpr (MODE == kGradQuery) {
+            auto finish = [&](int it) {
+                const Item item = item_at(it);
                 await_results(it);
                 if (wg == 0) {
-                    // One group stores; the other goes on to the next item.
+                    // One group stores; the other goes on with its tiles.
                     const uint32_t set_address =
                         lane_base + kAccumulatorBase + (it & 1) * kSetColumns;
                     uint32_t r[kBlocks][32];
@@ -713,12 +706,64 @@ attention_tc_kernel(const __grid_constant__ AttnMaps maps, const AttnParams p) {
                 } else {
                     release_results(it);
                 }
+            };
+            const float factor = p.scale * kRoundUp;
+            int it = 0, j = wg;
+            bool owed = false, fresh = true;
+            float row_lse = 0.0f, row_dot = 0.0f;
+            while (it < my_items || owed) {
+                const bool tile = it < my_items && j < tiles;
+                if (tile) {
+                    if (fresh) {
+                        const Item item = item_at(it);
+                        const int q = item.m0 + row;
+                        const size_t at = size_t(item.group) * p.seq + q;
+                        row_lse = q < p.seq ? p.lse[at] : 0.0f;
+                        row_dot = q < p.seq ? p.row_dots[at] : 0.0f;
+                        fresh = false;
+                    }
+                    wait(kScoresFull + wg, visit & 1, 25);
+                    tcgen05_fence_after();
+                    const int valid = min(N, p.seq - j * N);
+                    const int chunks = (valid + 31) >> 5;
+#pragma unroll 1
+                    for (int c = 0; c < chunks; ++c) {
+                        uint32_t s[32], g[32];
+                        tcgen05_load_32_pair(block_address + 32 * c,
+                                             block_address + N + 32 * c, s, g);
+#pragma unroll
+                        for (int e = 0; e < 32; ++e) {
+                            const float probability = exp2_approx(
+                                fmaf(__uint_as_float(s[e]), p.scale2, -row_lse));
+                            s[e] = __float_as_uint(
+                                probability * ((__uint_as_float(g[e]) - row_dot) * factor));
+                        }
+                        tcgen05_store_32(block_address + 32 * c, s);
+                    }
+                    publish_block();
+                    j += 2;
+                    ++visit;
+                }
+                if (owed) {
+                    finish(it - 1);
+                    owed = false;
+                }
+                if (!tile) {
+                    if (it >= my_items) {
+                        break;
+                    }
+                    ++it;
+                    j = ((it * tiles) & 1) ^ wg;
+                    owed = true;
+                    fresh = true;
+                }
             }
         } else {
             static_assert(MODE != kGradKeyValue || N == 64, "table size");
             // Rows are keys, columns the queries of tile j: their log-sum-exp
-            // and D come from a table in shared memory, fetched one visit
-            // ahead by this group's 128 threads (64 of each).
+            // (less log2(1 + 2^-11)) and D come from a table in shared
+            // memory, fetched one visit ahead by this group's 128 threads (64
+            // of each).
             float2 *pairs = reinterpret_cast<float2 *>(table) + wg * 2 * N;
             const int t = int(threadIdx.x) - 64 - wg * 128;
             // The tile this group transforms after (it, j); false at the end.
@@ -738,11 +783,30 @@ attention_tc_kernel(const __grid_constant__ AttnMaps maps, const AttnParams p) {
                 if (q >= p.seq) {
                     return 0.0f;
                 }
-                return (t < N ? p.lse : p.row_dots)[size_t(item.group) * p.seq + q];
+                const size_t at = size_t(item.group) * p.seq + q;
+                return t < N ? p.lse[at] - kRoundUpLog2 : p.row_dots[at];
             };
             auto put = [&](int buffer, float value) {
                 float *pair = reinterpret_cast<float *>(pairs + buffer * N + (t & (N - 1)));
                 pair[t < N ? 0 : 1] = value;
+            };
+            // Group 0 stores dV, group 1 stores dK.
+            auto finish = [&](int it) {
+                const Item item = item_at(it);
+                await_results(it);
+                const uint32_t mine =
+                    lane_base + kAccumulatorBase + (it & 1) * kSetColumns + wg * HD;
+                uint32_t r[kBlocks][32];
+#pragma unroll
+                for (int block = 0; block < kBlocks; ++block) {
+                    tcgen05_load_32(mine + 32 * block, r[block]);
+                }
+                release_results(it);
+#pragma unroll
+                for (int block = 0; block < kBlocks; ++block) {
+                    store_block(r[block], &maps.out[wg], item, 32 * block,
+                                (wg ? p.add1 : p.add0) != 0);
+                }
             };
             int ahead_it = 0, ahead_j = wg - 2;
             bool ahead = my_items > 0 && advance(ahead_it, ahead_j);
@@ -750,10 +814,11 @@ attention_tc_kernel(const __grid_constant__ AttnMaps maps, const AttnParams p) {
                 put(0, fetch(ahead_it, ahead_j));
                 ahead = advance(ahead_it, ahead_j);
             }
-            for (int it = 0; it < my_items; ++it) {
-                const Item item = item_at(it);
-                const int first_tile = it * tiles;
-                for (int j = (first_tile & 1) ^ wg; j < tiles; j += 2, ++visit) {
+            int it = 0, j = wg;
+            bool owed = false;
+            while (it < my_items || owed) {
+                const bool tile = it < my_items && j < tiles;
+                if (tile) {
                     const float next = ahead ? fetch(ahead_it, ahead_j) : 0.0f;
                     group_barrier(2 + wg, 128);
                     wait(kScoresFull + wg, visit & 1, 25);
@@ -774,12 +839,12 @@ attention_tc_kernel(const __grid_constant__ AttnMaps maps, const AttnParams p) {
                                 fmaf(__uint_as_float(s[e]), p.scale2, -two.x));
                             const float p1 = exp2_approx(
                                 fmaf(__uint_as_float(s[e + 1]), p.scale2, -two.z));
-                            g[e] = round_tf32(
+                            g[e] = __float_as_uint(
                                 p0 * ((__uint_as_float(g[e]) - two.y) * p.scale));
-                            g[e + 1] = round_tf32(
+                            g[e + 1] = __float_as_uint(
                                 p1 * ((__uint_as_float(g[e + 1]) - two.w) * p.scale));
-                            s[e] = round_tf32(p0);
-                            s[e + 1] = round_tf32(p1);
+                            s[e] = __float_as_uint(p0);
+                            s[e + 1] = __float_as_uint(p1);
                         }
                         tcgen05_store_32(block_address + 32 * c, s);
                         tcgen05_store_32(block_address + N + 32 * c, g);
@@ -789,21 +854,20 @@ attention_tc_kernel(const __grid_constant__ AttnMaps maps, const AttnParams p) {
                         put((visit + 1) & 1, next);
                         ahead = advance(ahead_it, ahead_j);
                     }
+                    j += 2;
+                    ++visit;
                 }
-                // Group 0 stores dV, group 1 stores dK.
-                await_results(it);
-                const uint32_t mine =
-                    lane_base + kAccumulatorBase + (it & 1) * kSetColumns + wg * HD;
-                uint32_t r[kBlocks][32];
-#pragma unroll
-                for (int block = 0; block < kBlocks; ++block) {
-                    tcgen05_load_32(mine + 32 * block, r[block]);
+                if (owed) {
+                    finish(it - 1);
+                    owed = false;
                 }
-                release_results(it);
-#pragma unroll
-                for (int block = 0; block < kBlocks; ++block) {
-                    store_block(r[block], &maps.out[wg], item, 32 * block,
-                                (wg ? p.add1 : p.add0) != 0);
+                if (!tile) {
+                    if (it >= my_items) {
+                        break;
+                    }
+                    ++it;
+                    j = ((it * tiles) & 1) ^ wg;
+                    owed = true;
                 }
             }
         }
