@@ -5,12 +5,18 @@
 
 One step = one call of the reference's vit_model_train_batch_smoothed on one
 synthetic batch.  The host side is the reference's unmodified C code
-(oracle/_ref/libvithost.so, built from the reference sources); with the B200
-backend enabled every op it dispatches runs as one of this repository's CUDA
-kernels.  Prints ONE JSON line (rank 0).  Workloads quoted on a fixed global
-batch (cfg5: 4096 images per optimiser step whatever the GPU count) run each
-rank's share as micro-batches with gradient accumulation, one optimiser call
-and one gradient exchange per step ("scaling": "strong").
+(transformer-in-c_b200/host/libvithost.so, built from the reference sources);
+with the B200 backend enabled every op it dispatches runs as one of this
+repository's CUDA kernels.  Prints ONE JSON line (rank 0).  Workloads quoted on
+a fixed global batch (cfg5: 4096 images per optimiser step whatever the GPU
+count) run each rank's share as micro-batches with gradient accumulation, one
+optimiser call and one gradient exchange per step ("scaling": "strong").
+
+The headline numbers of the line are the workload named by --workload (cfg2,
+the configuration the metric is quoted on).  Unless --no-cfg5 is given the
+line also carries a "cfg5" object: the data-parallel configuration (d 512, 12
+layers, global batch 4096) measured the same way at the same GPU count, so a
+run at 1, 2, 4 and 8 GPUs yields its strong-scaling curve.
 
 Timed quantities
   e2e    wall clock over K steps called with HOST buffers: per step the host
@@ -35,9 +41,26 @@ import time
 
 import numpy as np
 
+import importlib.util
+
 REPO = os.path.dirname(os.path.abspath(__file__))
-sys.path.insert(0, os.path.join(REPO, "tests"))
-from conftest import HOST_LIBRARY, PACKAGE, load_module  # noqa: E402
+PACKAGE = os.path.join(REPO, "transformer-in-c_b200")
+# The reference's unmodified host code, compiled twice by oracle/build_ref.py:
+# the copy that drives the backend in the timed steps, and the copy that only
+# runs the CPU loops (the cpu_baseline legs and --impl reference).
+HOST_LIBRARY = os.path.join(PACKAGE, "host", "libvithost.so")
+CPU_LIBRARY = os.path.join(REPO, "oracle", "_ref", "libvithost.so")
+
+
+def load_module(name, path):
+    if name in sys.modules:
+        return sys.modules[name]
+    spec = importlib.util.spec_from_file_location(name, path)
+    module = importlib.util.module_from_spec(spec)
+    sys.modules[name] = module
+    spec.loader.exec_module(module)
+    return module
+
 
 # (channels, height, width, patch, d_model, heads, layers, classes), batch
 WORKLOADS = {
@@ -64,6 +87,56 @@ def measured_peaks():
                 float(peaks.get("bf16_tflops_sustained", peaks["bf16_tflops"])),
                 "measured")
     return 6650.0, 1400.0, "fallback"
+
+
+def measure_tf32_peak(seconds=2.0):
+    """Dense TF32 rate of this GPU, measured here because no recorded peak
+    exists for it: a cuBLAS FP32 matmul with TF32 allowed, 8192^3, as a burst
+    (20 products) and sustained over `seconds`.  The library call only
+    supplies the denominator of the contractions' roofline fractions."""
+    import torch
+    previous = torch.backends.cuda.matmul.allow_tf32
+    torch.backends.cuda.matmul.allow_tf32 = True
+    n = 8192
+    a = torch.randn(n, n, device="cuda")
+    b = torch.randn(n, n, device="cuda")
+    c = torch.empty(n, n, device="cuda")
+
+    def timed(count):
+        begin = torch.cuda.Event(enable_timing=True)
+        end = torch.cuda.Event(enable_timing=True)
+        begin.record()
+        for _ in range(count):
+            torch.matmul(a, b, out=c)
+        end.record()
+        torch.cuda.synchronize()
+        return begin.elapsed_time(end) / 1e3
+
+    timed(3)
+    burst_seconds = timed(20)
+    burst = 2.0 * n ** 3 * 20 / burst_seconds / 1e12
+    count = max(20, int(seconds / (burst_seconds / 20)))
+    sustained = 2.0 * n ** 3 * count / timed(count) / 1e12
+    torch.backends.cuda.matmul.allow_tf32 = previous
+    del a, b, c
+    torch.cuda.empty_cache()
+    return {"burst_tflops": burst, "sustained_tflops": sustained,
+            "how": f"torch.matmul fp32 8192^3 with TF32 allowed: 20 products, "
+                   f"then {count} products"}
+
+
+def recorded_traffic(kernel, workload, batch):
+    """dram__bytes_read + dram__bytes_write per launch of `kernel` from the ncu
+    capture summarised under profiles/ (the JSON beside the summary names the
+    capture's workload, batch and source commit), scaled to this batch by the
+    rows processed; None when no capture of this kernel and workload exists."""
+    path = os.path.join(REPO, "profiles", "dram_traffic.json")
+    if not os.path.exists(path):
+        return None
+    for entry in json.load(open(path)).get("captures", []):
+        if entry["kernel"] == kernel and entry["workload"] == workload:
+            return entry["bytes_per_launch"] * batch / entry["batch"]
+    return None
 
 
 class ClockSampler:
@@ -253,7 +326,8 @@ def dataset_measurement(vh, backend, batch, height, width, steps, with_cpu):
     }
     result["roofline"]["frac"] = result["roofline"]["achieved"] / hbm_peak
     if with_cpu:
-        import dataset_reference
+        dataset_reference = load_module("dataset_reference", os.path.join(
+            REPO, "tests", "dataset_reference.py"))
         timed = dataset_reference.time_reference(samples, height, width)
         if timed:
             result["cpu_baseline"] = {
@@ -289,6 +363,24 @@ def reference_cuda_rate(config, batch, warmup=2, steps=5):
                     "managed memory), wall clock around the same train calls"}
 
 
+def reference_replica(args):
+    """One replica of the reference arm: a model of its own on its own sample,
+    `--warmup` untimed and `--steps` timed CPU train steps; prints the time."""
+    vh = load_module("vitb200_vit_host", os.path.join(PACKAGE, "vit_host.py"))
+    config, _ = WORKLOADS[args.workload]
+    lib = vh.load_host_library(CPU_LIBRARY, visible_to_backend=False)
+    host = vh.VitHost(lib, config, args.batch)
+    images, labels = vh.synthetic_batch(args.batch, config[1], config[2], config[7],
+                                        100 + args.replica)
+    for _ in range(args.warmup):
+        host.train_step(images, labels, LR, WD, None, SMOOTHING)
+    start = time.perf_counter()
+    for _ in range(args.steps):
+        host.train_step(images, labels, LR, WD, None, SMOOTHING)
+    print(json.dumps(time.perf_counter() - start), flush=True)
+    host.close()
+
+
 def run_reference(args, vh, config, batch, rank, world):
     """The reference's own CPU implementation of the step, timed on this
     machine's host cores.  The code is single-threaded on Linux
@@ -296,8 +388,8 @@ def run_reference(args, vh, config, batch, rank, world):
     replicas, each stepping its own model on its own sample."""
     if rank != 0:
         return None
-    host_lib = vh.load_host_library(HOST_LIBRARY)
-    probe = vh.VitHost(host_lib, config, 1)
+    cpu_lib = vh.load_host_library(CPU_LIBRARY, visible_to_backend=False)
+    probe = vh.VitHost(cpu_lib, config, 1)
     images, labels = vh.synthetic_batch(1, config[1], config[2], config[7], 77)
     start = time.perf_counter()
     probe.train_step(images, labels, LR, WD, None, SMOOTHING)
@@ -307,24 +399,11 @@ def run_reference(args, vh, config, batch, rank, world):
     budget = 150.0
     sample = int(max(1, min(batch, 32, budget / (total_steps * per_image))))
     replicas = max(1, min(os.cpu_count() or 1, 64))
-    code = (
-        "import sys, time, json; sys.path.insert(0, %r); "
-        "from conftest import HOST_LIBRARY, PACKAGE, load_module; import os; "
-        "vh = load_module('vitb200_vit_host', os.path.join(PACKAGE, 'vit_host.py')); "
-        "lib = vh.load_host_library(HOST_LIBRARY); "
-        "cfg = %r; b = %d; "
-        "h = vh.VitHost(lib, cfg, b); "
-        "x, y = vh.synthetic_batch(b, cfg[1], cfg[2], cfg[7], 100 + int(sys.argv[1])); "
-        "[h.train_step(x, y, %r, %r, None, %r) for _ in range(%d)]; "
-        "t = time.perf_counter(); "
-        "[h.train_step(x, y, %r, %r, None, %r) for _ in range(%d)]; "
-        "print(json.dumps(time.perf_counter() - t))"
-    ) % (os.path.join(REPO, "tests"), tuple(config), sample, LR, WD, SMOOTHING,
-         args.warmup, LR, WD, SMOOTHING, args.steps)
-    start = time.perf_counter()
-    children = [subprocess.Popen([sys.executable, "-c", code, str(i)],
-                                 stdout=subprocess.PIPE, text=True)
-                for i in range(replicas)]
+    children = [subprocess.Popen(
+        [sys.executable, os.path.abspath(__file__), "--impl", "reference-replica",
+         "--workload", args.workload, "--batch", str(sample), "--replica", str(i),
+         "--steps", str(args.steps), "--warmup", str(args.warmup)],
+        stdout=subprocess.PIPE, text=True) for i in range(replicas)]
     times = [float(json.loads(child.communicate()[0].strip().splitlines()[-1]))
              for child in children]
     elapsed = max(times)
@@ -337,6 +416,7 @@ def run_reference(args, vh, config, batch, rank, world):
         "dtype": "f32", "data": "synthetic",
         "config": {"workload": args.workload, "vit": list(config),
                    "batch_per_gpu": batch, "global_batch": batch,
+                   "timed_batch_per_replica": sample, "replicas": replicas,
                    "parallelism": "dp1"},
         "cpu_baseline": {
             "value": value, "unit": "images/s", "cores": replicas,
@@ -350,60 +430,13 @@ def run_reference(args, vh, config, batch, rank, world):
     return line
 
 
-def main():
-    parser = argparse.ArgumentParser()
-    parser.add_argument("--gpus", type=int, default=1)
-    parser.add_argument("--steps", type=int, default=20)
-    parser.add_argument("--warmup", type=int, default=3)
-    parser.add_argument("--impl", default="ours", choices=["ours", "reference"])
-    parser.add_argument("--workload", default="cfg2", choices=sorted(WORKLOADS))
-    parser.add_argument("--batch", type=int, default=0,
-                        help="override the workload's batch (per GPU)")
-    parser.add_argument("--no-cpu-baseline", action="store_true")
-    parser.add_argument("--global-batch", type=int, default=-1,
-                        help="images per optimiser step over all GPUs; 0 = one "
-                             "micro-batch per GPU, -1 = the workload's own")
-    args = parser.parse_args()
-    args.warmup = max(args.warmup, 3) if args.impl == "ours" else args.warmup
-
-    rank = int(os.environ.get("RANK", "0"))
-    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
-    world = int(os.environ.get("WORLD_SIZE", "1"))
-    config, batch = WORKLOADS[args.workload]
-    if args.batch:
-        batch = args.batch
-    global_batch = (GLOBAL_BATCH.get(args.workload, 0) if args.global_batch < 0
-                    else args.global_batch)
-    micro_batches = 1
-    if global_batch:
-        if global_batch % (world * batch):
-            parser.error(f"global batch {global_batch} is not a multiple of "
-                         f"{world} GPUs x micro-batch {batch}")
-        micro_batches = global_batch // (world * batch)
-
-    vh = load_module("vitb200_vit_host", os.path.join(PACKAGE, "vit_host.py"))
-    if args.impl == "reference":
-        line = run_reference(args, vh, config, batch, rank, world)
-        if line is not None:
-            print(json.dumps(line), flush=True)
-        return
-
+def measure(vh, backend, host_lib, workload, config, batch, micro_batches, steps,
+            warmup, rank, local_rank, world, tf32_peak):
+    """`warmup` untimed and 2 x `steps` timed optimiser steps of one workload
+    (one pass for the end-to-end rate, one for device time and the per-op
+    table); returns the fields of a bench line."""
     import torch
     import torch.distributed as dist
-    if world > 1:
-        dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
-    torch.cuda.set_device(local_rank)
-    os.environ["VITB200_DEVICE"] = str(local_rank)
-
-    host_lib = vh.load_host_library(HOST_LIBRARY)
-    backend = vh.Backend()          # raises without the library or a B200
-    if world > 1:
-        # One NCCL communicator of our own for the gradient exchange; its id
-        # travels through torch.distributed.
-        holder = [backend.dp_unique_id() if rank == 0 else None]
-        dist.broadcast_object_list(holder, src=0)
-        backend.dp_init(rank, world, holder[0])
-    backend.enable()
     backend.set_gradient_accumulation(micro_batches)
     host = vh.VitHost(host_lib, config, batch)
     images, labels = vh.synthetic_batch(batch * micro_batches, config[1],
@@ -423,46 +456,57 @@ def main():
                                                LR, WD, None, SMOOTHING)
         return host.train_step_raw(images, labels, LR, WD, None, SMOOTHING)
 
-    for _ in range(args.warmup):
+    declined = backend.declined_ops()
+    for _ in range(warmup):
         step()
 
     # ---- e2e: host buffers in, loss out, wall clock ----------------------
     barrier()
     counters = backend.memory_counters()
     start = time.perf_counter()
-    for _ in range(args.steps):
+    for _ in range(steps):
         loss = step()
     barrier()
     e2e_seconds = time.perf_counter() - start
     moved = backend.memory_counters()
-    h2d_per_step = (moved["h2d_bytes"] - counters["h2d_bytes"]) / args.steps
-    d2h_per_step = (moved["d2h_bytes"] - counters["d2h_bytes"]) / args.steps
+    h2d_per_step = (moved["h2d_bytes"] - counters["h2d_bytes"]) / steps
+    d2h_per_step = (moved["d2h_bytes"] - counters["d2h_bytes"]) / steps
 
     # ---- value + per-op roofline: device-busy time over K steps ----------
     barrier()
     backend.device_busy_ms(reset=True)
     backend.profile(True)
     launches = backend.kernel_launches()
+    paths = backend.kernel_paths()
     with ClockSampler(local_rank) as clocks:
-        for _ in range(args.steps):
+        for _ in range(steps):
             loss = step()
         busy_ms = backend.device_busy_ms(reset=True)
     barrier()
     launches = backend.kernel_launches() - launches
+    paths = {k: v - paths[k] for k, v in backend.kernel_paths().items()}
     entries = backend.profile_entries()
     backend.profile(False)
+    declined = backend.declined_ops() - declined
 
     busy = torch.tensor([busy_ms, e2e_seconds], dtype=torch.float64, device="cuda")
     if world > 1:
         dist.all_reduce(busy, op=dist.ReduceOp.MAX)
     busy_ms, e2e_seconds = float(busy[0]), float(busy[1])
     images_per_step = batch * micro_batches * world
-    value = images_per_step * args.steps / (busy_ms / 1e3)
-    e2e_value = images_per_step * args.steps / e2e_seconds
+    value = images_per_step * steps / (busy_ms / 1e3)
+    e2e_value = images_per_step * steps / e2e_seconds
 
-    hbm_peak, tensor_peak, peak_source = measured_peaks()
+    hbm_peak, bf16_peak, peak_source = measured_peaks()
+    # The contractions take TF32 operands: their roof is the TF32 rate
+    # measured on this GPU by this run (sustained figure: the kernels are
+    # timed inside a long step).
+    tensor_peak = tf32_peak["sustained_tflops"] if tf32_peak else 0.44 * bf16_peak
+    tensor_source = ("TF32 matmul measured by this run" if tf32_peak
+                     else "0.44 x recorded BF16 rate (TF32 not measured at this GPU count)")
     top = max(entries, key=lambda e: e["ms"])
     kernel_name = top["name"]
+    traffic_kernel = None
     if top["name"] in ("gemm", "gemm_backward"):
         # Both ops are launches of one kernel (one per forward product, two per
         # gradient pair, each timed as one entry): judge it as a whole.
@@ -472,37 +516,31 @@ def main():
                "bytes": sum(e["bytes"] for e in parts),
                "flops": sum(e["flops"] for e in parts), "calls": kernel_launches}
         kernel_name = "gemm_tc_kernel (ops gemm + gemm_backward)"
+        traffic_kernel = "gemm_tc_kernel"
     seconds = top["ms"] / 1e3
-    # The contractions take TF32 operands, whose dense rate is half the BF16
-    # rate MEASURED_PEAKS.json holds: that half decides which roof is nearer;
-    # `peak` stays the measured BF16 figure and `frac_of_tf32_peak` is added.
     tensor_bound = (top["name"] in TENSOR_OPS | {"gemm_tc_kernel"} and
-                    top["flops"] / (0.5 * tensor_peak * 1e12) >
+                    top["flops"] / (tensor_peak * 1e12) >
                     top["bytes"] / (hbm_peak * 1e9))
     if tensor_bound:
         achieved, peak, unit = top["flops"] / seconds / 1e12, tensor_peak, "TFLOP/s"
     else:
         achieved, peak, unit = top["bytes"] / seconds / 1e9, hbm_peak, "GB/s"
-    # dram__bytes_read + dram__bytes_write over the 51 gemm_tc_kernel launches
-    # of one step, from an ncu capture at batch 1024 (4.727 GB: 3.844 read,
-    # 0.883 written before the launches ended) scaled to batch 2048 by the rows
-    # processed; see profiles/gemm_tc_kernel_vit_c_batch1024.md.
-    traffic = None
-    if (top["name"] == "gemm_tc_kernel" and args.workload == "cfg2" and
-            batch == 2048 and not tensor_bound):
-        traffic = 2 * 4.727e9 / 51
+    traffic = (recorded_traffic(traffic_kernel, workload, batch)
+               if traffic_kernel and not tensor_bound else None)
     roofline = {
         "bound": "tensor" if tensor_bound else "hbm", "kernel": kernel_name,
         "achieved": achieved, "peak": peak, "unit": unit,
-        "frac": achieved / peak, "peak_source": peak_source, "traffic": traffic,
+        "frac": achieved / peak,
+        "peak_source": tensor_source if tensor_bound else peak_source,
+        "traffic": traffic,
         "algorithmic_per_launch": (top["flops"] if tensor_bound else top["bytes"]) /
                                   max(top["calls"], 1),
         "launch_ms": top["ms"] / top["calls"],
         "share_of_device_time": top["ms"] / sum(e["ms"] for e in entries),
     }
     if tensor_bound:
-        roofline["frac_of_tf32_peak"] = achieved / (0.5 * tensor_peak)
-    breakdown = {e["name"]: round(e["ms"] / args.steps, 4)
+        roofline["frac_of_recorded_bf16_rate"] = achieved / bf16_peak
+    breakdown = {e["name"]: round(e["ms"] / steps, 4)
                  for e in sorted(entries, key=lambda e: -e["ms"])[:24]}
     # Every op against the roofline that bounds it: algorithmic bytes (and
     # flops for the contractions) over the CUDA-event time of its launches.
@@ -510,24 +548,29 @@ def main():
     for e in sorted(entries, key=lambda e: -e["ms"])[:16]:
         if e["ms"] <= 0.0:
             continue
-        op = {"ms_per_step": round(e["ms"] / args.steps, 4),
-              "launches_per_step": round(e["calls"] / args.steps, 1),
+        op = {"ms_per_step": round(e["ms"] / steps, 4),
+              "launches_per_step": round(e["calls"] / steps, 1),
               "GB/s": round(e["bytes"] / e["ms"] / 1e6, 1),
               "frac_hbm": round(e["bytes"] / e["ms"] / 1e6 / hbm_peak, 3)}
         if e["flops"] > 0.0:
             op["TFLOP/s"] = round(e["flops"] / e["ms"] / 1e9, 1)
+            op["frac_tf32"] = round(e["flops"] / e["ms"] / 1e9 / tensor_peak, 3)
         by_op[e["name"]] = op
 
-    line = {
+    result = {
         "metric": "train images/s", "value": value, "unit": "images/s",
-        "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
-        "ms_per_step": busy_ms / args.steps, "higher_is_better": True,
-        "scaling": "strong" if global_batch else "weak", "vs_baseline": None,
-        "dtype": "f32", "data": "synthetic",
-        "config": {"workload": args.workload, "vit": list(config),
+        "n_gpus": world, "steps": steps, "warmup": warmup,
+        "ms_per_step": busy_ms / steps, "higher_is_better": True,
+        "scaling": "strong" if micro_batches > 1 or workload in GLOBAL_BATCH
+                   else "weak",
+        "vs_baseline": None,
+        "dtype": "tf32", "data": "synthetic",
+        "config": {"workload": workload, "vit": list(config),
                    "batch_per_gpu": batch * micro_batches,
                    "micro_batch": batch, "micro_batches_per_step": micro_batches,
                    "global_batch": images_per_step,
+                   "precision": "TF32 operands on the tensor cores, FP32 storage, "
+                                "accumulation, softmax, normalisation and optimiser",
                    "parallelism": f"dp{world}" + (
                        " (batch sharded by sample, NCCL all-reduce of gradients "
                        "overlapped with backward)" if world > 1 else ""),
@@ -537,18 +580,105 @@ def main():
         "e2e": {"value": e2e_value, "unit": "images/s",
                 "h2d_bytes_per_step": h2d_per_step,
                 "d2h_bytes_per_step": d2h_per_step,
-                "ms_per_step": 1e3 * e2e_seconds / args.steps},
+                "ms_per_step": 1e3 * e2e_seconds / steps},
         "gpu_launches": launches,
+        "declined_ops": declined,
+        "kernel_paths": paths,
         "roofline": roofline,
         "ms_per_step_by_op": breakdown,
         "roofline_by_op": by_op,
         "loss": loss,
     }
+    if world > 1:
+        result["dp"] = backend.dp_counters()
+    host.close()
+    del keep_images, keep_labels
+    return result
+
+
+def main():
+    parser = argparse.ArgumentParser()
+    parser.add_argument("--gpus", type=int, default=1)
+    parser.add_argument("--steps", type=int, default=20)
+    parser.add_argument("--warmup", type=int, default=3)
+    parser.add_argument("--impl", default="ours",
+                        choices=["ours", "reference", "reference-replica"])
+    parser.add_argument("--workload", default="cfg2", choices=sorted(WORKLOADS))
+    parser.add_argument("--batch", type=int, default=0,
+                        help="override the workload's batch (per GPU)")
+    parser.add_argument("--no-cpu-baseline", action="store_true")
+    parser.add_argument("--no-cfg5", action="store_true",
+                        help="leave out the data-parallel configuration's object")
+    parser.add_argument("--cfg5-steps", type=int, default=3)
+    parser.add_argument("--replica", type=int, default=0, help=argparse.SUPPRESS)
+    parser.add_argument("--global-batch", type=int, default=-1,
+                        help="images per optimiser step over all GPUs; 0 = one "
+                             "micro-batch per GPU, -1 = the workload's own")
+    args = parser.parse_args()
+    if args.impl == "reference-replica":
+        reference_replica(args)
+        return
+    args.warmup = max(args.warmup, 3) if args.impl == "ours" else args.warmup
+
+    rank = int(os.environ.get("RANK", "0"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    if world != args.gpus and rank == 0:
+        print(f"bench.py: --gpus {args.gpus} but the launcher started {world} "
+              f"rank(s); measuring {world}", file=sys.stderr)
+    config, batch = WORKLOADS[args.workload]
+    if args.batch:
+        batch = args.batch
+
+    def micro_batch_count(workload, micro_batch):
+        total = (GLOBAL_BATCH.get(workload, 0) if args.global_batch < 0
+                 else args.global_batch)
+        if not total:
+            return 1
+        if total % (world * micro_batch):
+            parser.error(f"global batch {total} is not a multiple of "
+                         f"{world} GPUs x micro-batch {micro_batch}")
+        return total // (world * micro_batch)
+
+    micro_batches = micro_batch_count(args.workload, batch)
+
+    vh = load_module("vitb200_vit_host", os.path.join(PACKAGE, "vit_host.py"))
+    if args.impl == "reference":
+        line = run_reference(args, vh, config, batch, rank, world)
+        if line is not None:
+            print(json.dumps(line), flush=True)
+        return
+
+    import torch
+    import torch.distributed as dist
+    if world > 1:
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
+    torch.cuda.set_device(local_rank)
+    os.environ["VITB200_DEVICE"] = str(local_rank)
+
+    # The TF32 roof, before the backend holds any memory.  With several ranks
+    # only a single-GPU run measures it (the ranks would share the power and
+    # the result would not be a per-GPU peak).
+    tf32_peak = measure_tf32_peak() if world == 1 else None
+
+    host_lib = vh.load_host_library(HOST_LIBRARY)
+    backend = vh.Backend()          # raises without the library or a B200
+    if world > 1:
+        # One NCCL communicator of our own for the gradient exchange; its id
+        # travels through torch.distributed.
+        holder = [backend.dp_unique_id() if rank == 0 else None]
+        dist.broadcast_object_list(holder, src=0)
+        backend.dp_init(rank, world, holder[0])
+    backend.enable()
+    line = measure(vh, backend, host_lib, args.workload, config, batch,
+                   micro_batches, args.steps, args.warmup, rank, local_rank,
+                   world, tf32_peak)
+    if tf32_peak:
+        line["tf32_peak"] = tf32_peak
     if rank == 0 and not args.no_cpu_baseline and world == 1:
-        backend.disable()
+        cpu_lib = vh.load_host_library(CPU_LIBRARY, visible_to_backend=False)
         rate, sample_batch, sample_steps = cpu_reference_rate(
-            vh, host_lib, config, seconds_budget=12.0)
-        backend.enable()
+            vh, cpu_lib, config, seconds_budget=12.0)
         line["cpu_baseline"] = {
             "value": rate, "unit": "images/s", "cores": 1, "kind": "reference",
             "sample": f"reference CPU train step (single-threaded on Linux), "
@@ -565,9 +695,15 @@ def main():
         line["dataset"] = dataset_measurement(
             vh, backend, batch, config[1], config[2], args.steps,
             with_cpu=not args.no_cpu_baseline)
-    if world > 1:
-        line["dp"] = backend.dp_counters()
-    host.close()
+    if not args.no_cfg5 and args.workload != "cfg5":
+        # The data-parallel configuration at this GPU count: the same global
+        # batch of 4096 whatever the count, micro-batches of 512.
+        cfg5_config, cfg5_batch = WORKLOADS["cfg5"]
+        torch.cuda.empty_cache()
+        line["cfg5"] = measure(
+            vh, backend, host_lib, "cfg5", cfg5_config, cfg5_batch,
+            micro_batch_count("cfg5", cfg5_batch), args.cfg5_steps, 2, rank,
+            local_rank, world, tf32_peak)
     backend.disable()
     backend.dp_shutdown()
     backend.close()

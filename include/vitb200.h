@@ -86,6 +86,23 @@ void vitb200_fusion_counters(const CudaBackend *backend,
                              unsigned long long *head_layouts,
                              unsigned long long *bias_gradients);
 
+/* Op-table calls this backend declined since it was created (a slot returned
+ * non-zero, so the host synchronised and ran its own CPU loop for that op:
+ * reference src/ops.c:61-64).  Zero for any step that ran on the device. */
+unsigned long long vitb200_declined_ops(const CudaBackend *backend);
+
+/* Which kernels served the contractions: matrix products launched on the
+ * tcgen05 tensor cores (and how many of those with the 128 x 256 tile) or on
+ * the FP32 FMA kernel since the library was loaded, and long-sequence
+ * attention passes served by the tcgen05 kernels or by the streaming
+ * mma.sync kernels since the backend was created.  Any pointer may be NULL. */
+void vitb200_kernel_path_counters(const CudaBackend *backend,
+                                  unsigned long long *tensor_core_products,
+                                  unsigned long long *wide_tile_products,
+                                  unsigned long long *fma_products,
+                                  unsigned long long *tensor_core_attention,
+                                  unsigned long long *streaming_attention);
+
 /* Makes a tensor buffer obtained through the backend allocator plainly
  * readable and writable by the host (copying it back from the device if
  * needed).  Required before passing it to read()/fread()/write()/fwrite(),
@@ -115,6 +132,11 @@ void vitb200_dp_counters(CudaBackend *backend,
                          unsigned long long *overlapped_tensors,
                          unsigned long long *late_tensors,
                          unsigned long long *bytes);
+/* Contiguous ranges of the gradient arena all-reduced so far: from the third
+ * optimiser step on the gradients live in one allocation, ordered as the
+ * backward pass completes them, and leave in a few ranges of at least 4 MiB
+ * (counted here and in all_reduce_calls) instead of one call per tensor. */
+unsigned long long vitb200_dp_flat_ranges(CudaBackend *backend);
 
 /* Gradient accumulation (no counterpart in the reference, whose train call
  * steps the optimiser after every batch).  Tells the backend that the next

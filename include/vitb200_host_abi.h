@@ -30,6 +30,12 @@ extern "C" {
 typedef void *(*vitb200_allocate_fn)(void *context, size_t bytes);
 typedef void (*vitb200_release_fn)(void *context, void *memory);
 
+/* A translation unit that has the host's own headers may define
+ * VITB200_HOST_TYPES_ARE_THE_HOSTS after `typedef Tensor vitb200_tensor;
+ * typedef Parameter vitb200_parameter;`: the op table below is then declared
+ * over the host's types, which lets a compiler compare every slot's signature
+ * with the host's (tests/abi_signature_check.c). */
+#ifndef VITB200_HOST_TYPES_ARE_THE_HOSTS
 typedef struct vitb200_tensor {
     float *data;                               /* values, row-major          */
     float *grad;                               /* same shape as data         */
@@ -51,6 +57,7 @@ typedef struct vitb200_parameter {
     float *v;                                  /* == second_moment.data      */
     size_t step;                               /* incremented by the host    */
 } vitb200_parameter;
+#endif
 
 typedef struct vitb200_op_table {
     void *context;

@@ -10,7 +10,17 @@ this repository) with the flags of the reference Makefile:2
 
   libvithost.so   ops.c vit.c autodiff.c arena.c augmentation.c  +  our flat
                   ctypes-friendly entry points
-                  (transformer-in-c_b200/host/vit_host.c)
+                  (transformer-in-c_b200/host/vit_host.c): the CHECKER.  No
+                  backend is ever installed into this copy; it is loaded
+                  with local symbol scope and only runs the CPU loops.
+
+The same sources are compiled a second time into
+transformer-in-c_b200/host/libvithost.so: the CALLER, the unmodified host
+program that drives the backend through the op table (what the reference's
+own binaries are once they link the backend).  Both copies are linked with
+-Bsymbolic, so each keeps its own op table and allocator hook when both are
+loaded into one process and results of one can be checked against the other.
+
   test_device     the reference's CPU-vs-device acceptance test
                   (tests/test_device.c, -DENABLE_CUDA) linked against
                   libvitb200.so instead of the reference's cuda_backend.o
@@ -30,6 +40,10 @@ this repository) with the flags of the reference Makefile:2
                   reference's own src/cuda_backend.cu compiled for sm_100a and
                   cuBLAS: the secondary GPU baseline of bench.py
 
+The reference tree is looked for at the path given as argument, else in
+$VITB200_REFERENCE_ROOT, else in a directory named `reference` next to this
+repository.
+
 Usage: python oracle/build_ref.py [reference_root]
 """
 import os
@@ -47,9 +61,15 @@ def run(command):
     subprocess.run(command, check=True)
 
 
-def build(reference_root="/root/reference"):
+def default_reference_root():
+    return os.environ.get("VITB200_REFERENCE_ROOT") or \
+        os.path.join(os.path.dirname(REPO), "reference")
+
+
+def build(reference_root=None):
     """Returns True when the outputs were (re)built, False when the reference
     tree is not present (the GPU box: prebuilt files are used as they are)."""
+    reference_root = reference_root or default_reference_root()
     source = os.path.join(reference_root, "src")
     include = os.path.join(reference_root, "include")
     if not os.path.isdir(source):
@@ -57,9 +77,11 @@ def build(reference_root="/root/reference"):
     os.makedirs(OUT, exist_ok=True)
     flags = ["-std=c99", "-O2", "-fPIC", "-I" + include]
     core = [os.path.join(source, name) for name in CORE]
-    run(["gcc", *flags, "-shared", "-o", os.path.join(OUT, "libvithost.so"),
-         *core, os.path.join(source, "augmentation.c"),
-         os.path.join(PACKAGE, "host", "vit_host.c"), "-lm"])
+    for library in (os.path.join(OUT, "libvithost.so"),
+                    os.path.join(PACKAGE, "host", "libvithost.so")):
+        run(["gcc", *flags, "-shared", "-Wl,-Bsymbolic", "-o", library, *core,
+             os.path.join(source, "augmentation.c"),
+             os.path.join(PACKAGE, "host", "vit_host.c"), "-lm"])
     run(["gcc", *flags, "-o", os.path.join(OUT, "test_vision"),
          os.path.join(reference_root, "tests", "test_vision.c"), *core,
          *[os.path.join(source, name) for name in EXTRA], "-lm"])

@@ -6,7 +6,11 @@ import pytest
 
 REPO = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
 PACKAGE = os.path.join(REPO, "transformer-in-c_b200")
-HOST_LIBRARY = os.path.join(REPO, "oracle", "_ref", "libvithost.so")
+# The reference's unmodified host code, compiled twice (oracle/build_ref.py):
+# the copy that drives the backend, and the copy that only ever runs the CPU
+# loops and serves as the checker.
+HOST_LIBRARY = os.path.join(PACKAGE, "host", "libvithost.so")
+CHECKER_LIBRARY = os.path.join(REPO, "oracle", "_ref", "libvithost.so")
 GOLDEN = os.path.join(REPO, "tests", "golden")
 
 if REPO not in sys.path:
@@ -37,8 +41,18 @@ def vit_host_module():
 @pytest.fixture(scope="session")
 def host_lib(vit_host_module):
     if not os.path.exists(HOST_LIBRARY):
-        pytest.skip("oracle/_ref/libvithost.so not built (needs the reference tree)")
+        pytest.skip("host/libvithost.so not built (needs the reference tree)")
     return vit_host_module.load_host_library(HOST_LIBRARY)
+
+
+@pytest.fixture(scope="session")
+def checker_lib(vit_host_module):
+    """The reference's CPU path in a library of its own: no backend is ever
+    installed into it, whatever the state of the one the tests drive."""
+    if not os.path.exists(CHECKER_LIBRARY):
+        pytest.skip("oracle/_ref/libvithost.so not built (needs the reference tree)")
+    return vit_host_module.load_host_library(CHECKER_LIBRARY,
+                                             visible_to_backend=False)
 
 
 @pytest.fixture(scope="session")

@@ -64,6 +64,7 @@ def main():
     counters = backend.dp_counters()
     out["overlapped"] = counters["overlapped_tensors"]
     out["late"] = counters["late_tensors"]
+    out["flat_ranges"] = counters["flat_ranges"]
     np.savez(os.path.join(directory, f"rank{rank}.npz"), **out)
     model.close()
     backend.disable()

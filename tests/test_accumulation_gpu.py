@@ -26,14 +26,14 @@ def keep_mask(name, array, d_model):
 
 @pytest.mark.parametrize("config,micro_batches,batch", CASES)
 def test_accumulated_device_steps_match_the_cpu_full_batch(
-        config, micro_batches, batch, vit_host_module, host_lib, backend):
+        config, micro_batches, batch, vit_host_module, host_lib, checker_lib, backend):
     vh = vit_host_module
     total = micro_batches * batch
     steps = 3
     images, labels = vh.synthetic_batch(total, config[1], config[2], config[7], 9)
 
     backend.disable()
-    cpu = vh.VitHost(host_lib, config, total)
+    cpu = vh.VitHost(checker_lib, config, total)
     cpu_losses = [cpu.train_step(images, labels, LR, WD, None, SMOOTHING)
                   for _ in range(steps)]
 
@@ -59,7 +59,7 @@ def test_accumulated_device_steps_match_the_cpu_full_batch(
     plain_gpu = gpu.train_step(images[:batch], labels[:batch], LR, WD, None,
                                SMOOTHING)
     backend.disable()
-    small = vh.VitHost(host_lib, config, batch)
+    small = vh.VitHost(checker_lib, config, batch)
     small.set_parameters(expected)
     # Same weights, fresh moments: only the loss of the step is comparable.
     plain_cpu = small.train_step(images[:batch], labels[:batch], LR, WD, None,

@@ -83,7 +83,7 @@ def test_reference_acceptance_binary_passes():
 @pytest.mark.parametrize("precision", [FP32, TF32], ids=["fp32", "tf32"])
 @pytest.mark.parametrize("case", sorted(CASES))
 def test_gradients_and_training_match_cpu_reference(case, precision,
-                                                    vit_host_module, host_lib,
+                                                    vit_host_module, host_lib, checker_lib,
                                                     backend):
     vh = vit_host_module
     backend.set_gemm_precision(precision)
@@ -94,16 +94,20 @@ def test_gradients_and_training_match_cpu_reference(case, precision,
     d_model = config[4]
 
     backend.disable()
-    cpu = vh.VitHost(host_lib, config, batch)
+    cpu = vh.VitHost(checker_lib, config, batch)
     cpu_loss = cpu.gradients(images, labels, weights, smoothing)
     cpu_grads = cpu.parameters(1)
 
     backend.enable()
     launches_before = backend.kernel_launches()
+    declined_before = backend.declined_ops()
     gpu = vh.VitHost(host_lib, config, batch)
     gpu_loss = gpu.gradients(images, labels, weights, smoothing)
     gpu_grads = gpu.parameters(1)
     assert backend.kernel_launches() > launches_before, "no kernel was launched"
+    # Every op of the step ran in its device slot: none fell back to the
+    # host's own loop.
+    assert backend.declined_ops() == declined_before
     assert backend.memory_counters()["device_bytes"] > 0
 
     assert abs(cpu_loss - gpu_loss) <= loss_tol
@@ -128,6 +132,7 @@ def test_gradients_and_training_match_cpu_reference(case, precision,
     gpu_after = gpu.parameters(0)
     gpu_m, gpu_v = gpu.parameters(2), gpu.parameters(3)
     assert gpu.steps() == [steps] * gpu.count
+    assert backend.declined_ops() == declined_before
     backend.disable()
     cpu_losses = [cpu.train_step(images, labels, LR, WD, weights, smoothing)
                   for _ in range(steps)]
@@ -173,6 +178,7 @@ def test_matches_committed_reference_fixtures(path, vit_host_module, host_lib,
     labels = data["labels"].astype(np.uintp)
     backend.enable()
     backend.set_gemm_precision(FP32)
+    declined_before = backend.declined_ops()
     gpu = vit_host_module.VitHost(host_lib, config, int(data["batch"]))
     loss = gpu.gradients(data["images"], labels, weights, smoothing)
     assert abs(loss - float(data["loss"])) <= 1e-4
@@ -189,6 +195,7 @@ def test_matches_committed_reference_fixtures(path, vit_host_module, host_lib,
             drop_key_bias(name, value, config[4]),
             drop_key_bias(name, data["after/" + name], config[4]),
             rtol=0, atol=2e-4, err_msg=name)
+    assert backend.declined_ops() == declined_before
     backend.set_gemm_precision(-1)
     gpu.close()
     backend.disable()
@@ -215,10 +222,21 @@ def test_bench_size_batch_is_the_small_batch_replicated(config, small, copies,
     gpu = vh.VitHost(host_lib, config, small * copies)
     init = gpu.parameters(0)
     fused_before = backend.fusion_counters()
+    declined_before = backend.declined_ops()
+    paths_before = backend.kernel_paths()
     loss = gpu.gradients(np.tile(images, (copies, 1)), np.tile(labels, copies),
                          None, 0.1)
     grads = gpu.parameters(1)
     fused = backend.fusion_counters()
+    paths = backend.kernel_paths()
+    assert backend.declined_ops() == declined_before
+    assert paths["tensor_core_products"] > paths_before["tensor_core_products"]
+    if config[4] // config[5] >= 32:
+        # 197-token sequences with 32-wide heads: the tcgen05 attention
+        # kernels, forward and backward in every block.
+        assert (paths["tensor_core_attention"] -
+                paths_before["tensor_core_attention"] == 2 * config[6])
+        assert paths["streaming_attention"] == paths_before["streaming_attention"]
     loss64, grads64, _ = vo.loss_and_gradients(
         {k: v.astype(np.float64) for k, v in init.items()}, config,
         images.astype(np.float64), labels.astype(np.int64), None, 0.1)
@@ -255,6 +273,7 @@ def test_vit_c_full_batch_against_oracle(precision, vit_host_module, host_lib,
         grad_tol = 2e-3  # the bound stated for TF32 products
     backend.enable()
     backend.set_gemm_precision(precision)
+    declined_before = backend.declined_ops()
     gpu = vh.VitHost(host_lib, config, batch)
     init = gpu.parameters(0)
     loss = gpu.gradients(images, labels, None, 0.1)
@@ -283,9 +302,141 @@ def test_vit_c_full_batch_against_oracle(precision, vit_host_module, host_lib,
             assert np.abs(ours - theirs).max() <= 2.02 * LR, name
             assert (np.linalg.norm(ours - theirs) <=
                     0.25 * np.linalg.norm(theirs - start) + 1e-7), name
+    assert backend.declined_ops() == declined_before
     assert backend.tensor_core_status() == 0
     backend.set_gemm_precision(-1)
     gpu.close()
+    backend.disable()
+
+
+LONG_SEQUENCE_CASES = {
+    # name: (config, batch): two blocks of the 64 x 64-pixel model (1025
+    # tokens, d 384, head dimension 64) and of the data-parallel model (197
+    # tokens, d 512, head dimension 64).
+    "cfg4_dims": ((1, 64, 64, 2, 384, 6, 2, 11), 2),
+    "cfg5_dims": ((1, 28, 28, 2, 512, 8, 2, 11), 2),
+}
+
+
+@pytest.mark.parametrize("case", sorted(LONG_SEQUENCE_CASES))
+def test_long_sequence_models_against_oracle(case, vit_host_module, host_lib,
+                                             backend):
+    """Whole models at the dimensions of the two largest configurations
+    (reference tests/test_device.c:83-139 is the pattern: loss, every
+    gradient, then a training step) under the shipped precision policy,
+    against the float64 oracle: 2e-3 per parameter, the bound stated for TF32
+    products.  These are the shapes that reach the tcgen05 attention kernels
+    through the op table (token-major operands, the saved log-sum-exp rows
+    keyed by tensor), the 128 x 256 product tile (K >= 256, N a multiple of
+    256) and the wide LayerNorm rows; the counters prove that those kernels
+    were the ones that ran and that no op fell back to the host."""
+    vh = vit_host_module
+    config, batch = LONG_SEQUENCE_CASES[case]
+    layers, d_model = config[6], config[4]
+    images, labels = vh.synthetic_batch(batch, config[1], config[2], config[7], 77)
+    backend.enable()
+    backend.set_gemm_precision(0)
+    declined_before = backend.declined_ops()
+    paths_before = backend.kernel_paths()
+    gpu = vh.VitHost(host_lib, config, batch)
+    init = gpu.parameters(0)
+    loss = gpu.gradients(images, labels, None, 0.1)
+    grads = gpu.parameters(1)
+    paths = backend.kernel_paths()
+    assert backend.declined_ops() == declined_before
+    assert (paths["tensor_core_attention"] - paths_before["tensor_core_attention"]
+            == 2 * layers)
+    assert paths["streaming_attention"] == paths_before["streaming_attention"]
+    assert paths["wide_tile_products"] > paths_before["wide_tile_products"]
+    trainer = vo.Trainer({k: v.astype(np.float64) for k, v in init.items()}, config)
+    loss64, grads64, _ = vo.loss_and_gradients(
+        trainer.params, config, images.astype(np.float64),
+        labels.astype(np.int64), None, 0.1)
+    assert abs(loss - float(loss64)) <= 5e-4
+    for name in grads:
+        ours = drop_key_bias(name, grads[name], d_model)
+        theirs = drop_key_bias(name, grads64[name], d_model)
+        assert max_relative(ours, theirs) <= 2e-3, name
+    gpu_loss = gpu.train_step(images, labels, LR, WD, None, 0.1)
+    ref_loss = trainer.train_batch(images.astype(np.float64),
+                                   labels.astype(np.int64), LR, WD, None, 0.1)
+    assert abs(gpu_loss - float(ref_loss)) <= 5e-4
+    for name, value in gpu.parameters(0).items():
+        ours = drop_key_bias(name, value, d_model)
+        theirs = drop_key_bias(name, trainer.params[name], d_model)
+        start = drop_key_bias(name, init[name], d_model)
+        assert np.abs(ours - theirs).max() <= 2.02 * LR, name
+        assert (np.linalg.norm(ours - theirs) <=
+                0.25 * np.linalg.norm(theirs - start) + 1e-7), name
+    assert backend.declined_ops() == declined_before
+    assert backend.tensor_core_status() == 0
+    backend.set_gemm_precision(-1)
+    gpu.close()
+    backend.disable()
+
+
+def test_single_parameter_optimiser_and_clipping_slots(vit_host_module, host_lib,
+                                                       checker_lib, backend):
+    """ops_adamw_step (reference src/ops.c:1102-1121; its own test,
+    tests/test_vision.c:616-624, expects a decayed value and step == 1) and
+    ops_clip_gradient_norm (src/ops.c:588-617) through their device slots,
+    against the same calls on the CPU library."""
+    import ctypes
+    floats = ctypes.POINTER(ctypes.c_float)
+
+    def adamw(lib, values, gradient, steps):
+        rows, cols = values.shape
+        out = [np.zeros_like(values) for _ in range(3)]
+        step = ctypes.c_size_t()
+        lib.vithost_adamw_single.restype = ctypes.c_int
+        lib.vithost_adamw_single.argtypes = [floats, floats] + \
+            [ctypes.c_size_t] * 3 + [ctypes.c_float] * 5 + [floats] * 3 + \
+            [ctypes.POINTER(ctypes.c_size_t)]
+        status = lib.vithost_adamw_single(
+            values.ctypes.data_as(floats), gradient.ctypes.data_as(floats), rows,
+            cols, steps, 0.01, 0.9, 0.999, 1e-8, 0.01,
+            *[o.ctypes.data_as(floats) for o in out], ctypes.byref(step))
+        assert status == 0
+        return out, int(step.value)
+
+    def clip(lib, gradients, max_norm):
+        copies = [g.copy() for g in gradients]
+        pointers = (floats * len(copies))(*[c.ctypes.data_as(floats) for c in copies])
+        counts = (ctypes.c_size_t * len(copies))(*[c.size for c in copies])
+        lib.vithost_clip_gradients.restype = ctypes.c_int
+        lib.vithost_clip_gradients.argtypes = [
+            ctypes.POINTER(floats), ctypes.POINTER(ctypes.c_size_t),
+            ctypes.c_size_t, ctypes.c_float]
+        assert lib.vithost_clip_gradients(pointers, counts, len(copies),
+                                          max_norm) == 0
+        return copies
+
+    rng = np.random.RandomState(5)
+    backend.enable()
+    declined_before = backend.declined_ops()
+    launches_before = backend.kernel_launches()
+    # The reference's own known answer: one step on value 1, gradient 1.
+    one = np.ones((1, 1), np.float32)
+    (value, m, v), step = adamw(host_lib, one, one, 1)
+    assert step == 1 and value[0, 0] < 1.0
+    assert abs(value[0, 0] - (1.0 - 0.01 * (1.0 + 0.01 * 1.0))) <= 1e-6
+    assert abs(m[0, 0] - 0.1) <= 1e-7 and abs(v[0, 0] - 0.001) <= 1e-7
+    for shape, steps in (((3, 5), 1), ((257, 130), 4), ((1, 70001), 2)):
+        values = rng.randn(*shape).astype(np.float32)
+        gradient = rng.randn(*shape).astype(np.float32)
+        ours, our_step = adamw(host_lib, values, gradient, steps)
+        theirs, their_step = adamw(checker_lib, values, gradient, steps)
+        assert our_step == their_step == steps
+        for a, b, tolerance in zip(ours, theirs, (1e-6, 1e-6, 1e-7)):
+            np.testing.assert_allclose(a, b, rtol=1e-5, atol=tolerance)
+    gradients = [rng.randn(n).astype(np.float32) for n in (7, 4096, 100001)]
+    for max_norm in (1.0, 1e6):   # clipped, and left alone
+        ours = clip(host_lib, gradients, max_norm)
+        theirs = clip(checker_lib, gradients, max_norm)
+        for a, b in zip(ours, theirs):
+            np.testing.assert_allclose(a, b, rtol=1e-5, atol=1e-8)
+    assert backend.kernel_launches() > launches_before
+    assert backend.declined_ops() == declined_before
     backend.disable()
 
 
@@ -331,21 +482,23 @@ def test_tensors_allocated_before_enable_fall_back_to_cpu(vit_host_module,
     config, batch = (1, 28, 28, 7, 16, 2, 1, 11), 2
     images, labels = vh.synthetic_batch(batch, 28, 28, 11, 9)
     backend.disable()
-    cpu = vh.VitHost(host_lib, config, batch)
+    cpu = vh.VitHost(host_lib, config, batch)   # the driving library, on purpose
     expected = cpu.gradients(images, labels, None, 0.1)
     expected_grads = cpu.parameters(1)
     backend.enable()
     launches = backend.kernel_launches()
+    declined = backend.declined_ops()
     again = cpu.gradients(images, labels, None, 0.1)
     assert again == expected
     assert backend.kernel_launches() == launches
+    assert backend.declined_ops() > declined
     for name, grad in cpu.parameters(1).items():
         np.testing.assert_array_equal(grad, expected_grads[name])
     backend.disable()
     cpu.close()
 
 
-def test_evaluation_and_prediction_match_cpu_reference(vit_host_module, host_lib,
+def test_evaluation_and_prediction_match_cpu_reference(vit_host_module, host_lib, checker_lib,
                                                        backend):
     """The reference's inference entry points (vit_model_evaluate,
     vit_model_predict_probabilities: 256-sample chunks plus a remainder, cache
@@ -354,7 +507,7 @@ def test_evaluation_and_prediction_match_cpu_reference(vit_host_module, host_lib
     config, samples = (1, 28, 28, 4, 32, 4, 2, 11), 300
     images, labels = vh.synthetic_batch(samples, 28, 28, 11, 17)
     backend.disable()
-    cpu = vh.VitHost(host_lib, config, 1)
+    cpu = vh.VitHost(checker_lib, config, 1)
     cpu_accuracy, cpu_loss, cpu_rate = cpu.evaluate(images, labels)
     cpu_probabilities = cpu.predict(images[:40])
     backend.enable()
@@ -377,7 +530,7 @@ def test_evaluation_and_prediction_match_cpu_reference(vit_host_module, host_lib
 
 
 def test_unread_tensors_are_not_computed_but_reads_see_them(vit_host_module,
-                                                            host_lib, backend):
+                                                            host_lib, checker_lib, backend):
     """The probability matrix of short-sequence attention is only defined, not
     written, during training; a host read still returns the right values, and
     the activation gradients that are zeroed every step are never filled."""
@@ -385,7 +538,7 @@ def test_unread_tensors_are_not_computed_but_reads_see_them(vit_host_module,
     config, batch = (1, 28, 28, 4, 32, 4, 2, 11), 4
     images, labels = vh.synthetic_batch(batch, 28, 28, 11, 3)
     backend.disable()
-    cpu = vh.VitHost(host_lib, config, batch)
+    cpu = vh.VitHost(checker_lib, config, batch)
     cpu.train_step(images, labels, LR, WD, None, 0.1)
     backend.enable()
     backend.set_gemm_precision(FP32)
@@ -454,7 +607,7 @@ def test_unread_tensors_are_not_computed_but_reads_see_them(vit_host_module,
     backend.disable()
 
 
-def test_gelu_backward_rides_on_the_product_before_it(vit_host_module, host_lib,
+def test_gelu_backward_rides_on_the_product_before_it(vit_host_module, host_lib, checker_lib,
                                                       backend):
     """With tensor-core products, the gradient of the GELU output is never
     stored: the product that would write it applies the GELU's slope in its
@@ -467,7 +620,7 @@ def test_gelu_backward_rides_on_the_product_before_it(vit_host_module, host_lib,
     layers = config[6]
     images, labels = vh.synthetic_batch(batch, 28, 28, 11, 5)
     backend.disable()
-    cpu = vh.VitHost(host_lib, config, batch)
+    cpu = vh.VitHost(checker_lib, config, batch)
     backend.enable()
     backend.set_gemm_precision(TF32)
     gpu = vh.VitHost(host_lib, config, batch)

@@ -5,6 +5,7 @@ into the clip scale, every rank must end with the weights a single GPU gets
 import os
 import subprocess
 import sys
+import time
 
 import numpy as np
 import pytest
@@ -22,8 +23,27 @@ def run_world(world, directory, micro_batches=1):
     children = [subprocess.Popen([sys.executable, WORKER, str(rank), str(world),
                                   directory, str(STEPS), str(micro_batches)])
                 for rank in range(world)]
-    for child in children:
-        assert child.wait(timeout=300) == 0
+    # All ranks are watched together: the first one that fails (or the
+    # deadline) ends the others at once, so that no rank is left behind
+    # blocked in a collective on a shared GPU after the test has gone.
+    deadline = time.monotonic() + 300
+    try:
+        running = list(children)
+        while running:
+            for child in list(running):
+                status = child.poll()
+                if status is None:
+                    continue
+                assert status == 0, f"a rank exited with status {status}"
+                running.remove(child)
+            assert time.monotonic() < deadline, "ranks did not finish in 300 s"
+            time.sleep(0.05)
+    finally:
+        for child in children:
+            if child.poll() is None:
+                child.kill()
+        for child in children:
+            child.wait()
     return [np.load(os.path.join(directory, f"rank{rank}.npz"))
             for rank in range(world)]
 
@@ -49,6 +69,8 @@ def test_two_ranks_match_one_gpu_on_the_same_global_batch(tmp_path):
     # from the third step on gradients are exchanged while backward still runs
     assert int(ranks[0]["overlapped"]) > 0
     assert int(ranks[0]["late"]) >= 2 * len(names)
+    # and leave as a few contiguous ranges of one arena, not tensor by tensor
+    assert 0 < int(ranks[0]["flat_ranges"]) <= 3 * (STEPS - 2)
 
 
 @pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs two GPUs")

@@ -69,25 +69,28 @@ constexpr int kGradQuery = 1;
 constexpr int kGradKeyValue = 2;
 
 // kCols: columns per tile; kResident: operands that stay for the whole row
-// tile; kProducts: SS products per tile; kUpdates: TS products per tile;
+// tile; kResidentStages: buffers for them (two where shared memory allows, so
+// the next item's are fetched while this item's are still in use);
+// kProducts: SS products per tile; kUpdates: TS products per tile;
 // kAccumulators: 128 x head_dim accumulators per work item (there are two
 // sets, so that one item's results are read while the next item's grow);
 // kStagingBytes: shared memory the results leave through (4 KiB per storing
 // warp); kTableBytes: the transform warps' exchange table.
 template <int MODE> struct Traits;
 template <> struct Traits<kForward> {
-    static constexpr int kCols = 128, kResident = 1, kProducts = 1, kUpdates = 1,
-                         kAccumulators = 2, kStagingBytes = 32768,
-                         kTableBytes = 4096;
+    static constexpr int kCols = 128, kResident = 1, kResidentStages = 2,
+                         kProducts = 1, kUpdates = 1, kAccumulators = 2,
+                         kStagingBytes = 32768, kTableBytes = 2048;
 };
 template <> struct Traits<kGradQuery> {
-    static constexpr int kCols = 96, kResident = 2, kProducts = 2, kUpdates = 1,
-                         kAccumulators = 1, kStagingBytes = 16384, kTableBytes = 0;
+    static constexpr int kCols = 96, kResident = 2, kResidentStages = 1,
+                         kProducts = 2, kUpdates = 1, kAccumulators = 1,
+                         kStagingBytes = 16384, kTableBytes = 0;
 };
 template <> struct Traits<kGradKeyValue> {
-    static constexpr int kCols = 64, kResident = 2, kProducts = 2, kUpdates = 2,
-                         kAccumulators = 2, kStagingBytes = 32768,
-                         kTableBytes = 2048;
+    static constexpr int kCols = 64, kResident = 2, kResidentStages = 1,
+                         kProducts = 2, kUpdates = 2, kAccumulators = 2,
+                         kStagingBytes = 32768, kTableBytes = 2048;
 };
 
 struct AttnMaps {
@@ -110,19 +113,19 @@ struct AttnParams {
     int *status;
 };
 
-enum Barrier {
+enum Barrier {   // two of each
     kResidentFull = 0,
-    kResidentEmpty = 1,
-    kSsFull = 2,     // two each from here on
-    kSsEmpty = 4,
-    kTsFull = 6,
-    kTsEmpty = 8,
-    kScoresFull = 10,
-    kBlockReady = 12,
-    kUpdateDone = 14,
-    kAllDone = 16,
-    kAccEmpty = 18,
-    kBarriers = 20,
+    kResidentEmpty = 2,
+    kSsFull = 4,
+    kSsEmpty = 6,
+    kTsFull = 8,
+    kTsEmpty = 10,
+    kScoresFull = 12,
+    kBlockReady = 14,
+    kUpdateDone = 16,
+    kAllDone = 18,
+    kAccEmpty = 20,
+    kBarriers = 22,
 };
 
 // True in exactly one lane of a converged warp.
@@ -169,7 +172,7 @@ attention_tc_kernel(const __grid_constant__ AttnMaps maps, const AttnParams p) {
 
     extern __shared__ __align__(1024) uint8_t smem[];
     uint8_t *resident = smem;
-    uint8_t *ss_ring = resident + kResidentTotal;
+    uint8_t *ss_ring = resident + T::kResidentStages * kResidentTotal;
     uint8_t *ts_ring = ss_ring + 2 * kSsStage;
     uint8_t *staging_base = ts_ring + 2 * kTsStage;
     uint8_t *tail = staging_base + T::kStagingBytes;
@@ -238,15 +241,18 @@ attention_tc_kernel(const __grid_constant__ AttnMaps maps, const AttnParams p) {
             int fill = 0;   // column tiles loaded so far
             for (int it = 0; it < my_items; ++it) {
                 const Item item = item_at(it);
-                wait(kResidentEmpty, (it & 1) ^ 1, 17);
-                mbarrier_expect_tx(&bars[kResidentFull], kResidentTotal);
+                const int stage = it % T::kResidentStages;
+                const uint32_t round = it / T::kResidentStages;
+                wait(kResidentEmpty + stage, (round & 1) ^ 1, 17);
+                mbarrier_expect_tx(&bars[kResidentFull + stage], kResidentTotal);
 #pragma unroll
                 for (int r = 0; r < T::kResident; ++r) {
 #pragma unroll
                     for (int kb = 0; kb < kBlocks; ++kb) {
-                        tma_load_3d(resident + r * kResidentBytes + kb * (kTileRows * 128),
+                        tma_load_3d(resident + stage * kResidentTotal + r * kResidentBytes +
+                                        kb * (kTileRows * 128),
                                     &maps.resident[r], item.col0 + 32 * kb, item.m0,
-                                    item.sample, &bars[kResidentFull]);
+                                    item.sample, &bars[kResidentFull + stage]);
                     }
                 }
                 for (int j = 0; j < tiles; ++j, ++fill) {
@@ -320,8 +326,9 @@ attention_tc_kernel(const __grid_constant__ AttnMaps maps, const AttnParams p) {
             int scores_it = 0, scores_j = 0;
             auto scores = [&](int g) {
                 const int s = g & 1;
+                const int stage = scores_it % T::kResidentStages;
                 if (scores_j == 0) {
-                    wait(kResidentFull, scores_it & 1, 20);
+                    wait(kResidentFull + stage, (scores_it / T::kResidentStages) & 1, 20);
                 }
                 wait(kSsFull + s, (g >> 1) & 1, 21);
                 tcgen05_fence_after();
@@ -332,7 +339,8 @@ attention_tc_kernel(const __grid_constant__ AttnMaps maps, const AttnParams p) {
 #pragma unroll
                 for (int product = 0; product < T::kProducts; ++product) {
                     const uint32_t d = tmem_base + s * kBufferColumns + product * N;
-                    const uint32_t a_low = resident_low + ((product * kResidentBytes) >> 4);
+                    const uint32_t a_low =
+                        resident_low + ((stage * kResidentTotal + product * kResidentBytes) >> 4);
                     const uint32_t b_low =
                         ss_low + ((s * kSsStage + product * kOperandBytes) >> 4);
 #pragma unroll
@@ -355,7 +363,7 @@ attention_tc_kernel(const __grid_constant__ AttnMaps maps, const AttnParams p) {
                     // The item's resident operands have been read for the
                     // last time once these products retire.
                     if (leader) {
-                        tcgen05_commit(&bars[kResidentEmpty]);
+                        tcgen05_commit(&bars[kResidentEmpty + stage]);
                     }
                     scores_j = 0;
                     ++scores_it;
@@ -517,12 +525,13 @@ attention_tc_kernel(const __grid_constant__ AttnMaps maps, const AttnParams p) {
                 const int first_tile = it * tiles;
                 const uint32_t set_address =
                     lane_base + kAccumulatorBase + (it & 1) * kSetColumns;
-                float *stats = table + (it & 1) * 512;
+                float *stats = table;
                 stats[wg * kTileRows + row] = done_reference;
                 stats[256 + wg * kTileRows + row] = done_sum;
                 group_barrier(1, 256);
                 const float m_a = stats[row], m_b = stats[kTileRows + row];
                 const float l_a = stats[256 + row], l_b = stats[256 + kTileRows + row];
+                group_barrier(1, 256);   // the table may be rewritten from here on
                 const float top = fmaxf(m_a, m_b);
                 const float w_a = l_a > 0.0f ? exp2_approx(m_a - top) : 0.0f;
                 const float w_b = l_b > 0.0f ? exp2_approx(m_b - top) : 0.0f;
@@ -1018,7 +1027,7 @@ bool operand_ok(const void *pointer, HeadLayout layout, size_t groups) {
 template <int HD, int MODE>
 constexpr int smem_bytes() {
     using T = Traits<MODE>;
-    const int bytes = T::kResident * kTileRows * HD * 4 +
+    const int bytes = T::kResidentStages * T::kResident * kTileRows * HD * 4 +
                       2 * (T::kProducts + T::kUpdates) * T::kCols * HD * 4 +
                       T::kStagingBytes + kBarrierBytes + T::kTableBytes;
     return bytes < kMinSmemBytes ? kMinSmemBytes : bytes;

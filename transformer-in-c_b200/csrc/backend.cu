@@ -207,6 +207,11 @@ struct CudaBackend {
     std::unordered_map<const void *, Scratch> lse_buffers;
     std::unordered_map<const void *, bool> lse_streamed;
     unsigned long long fused_epilogues = 0;
+    // Op slots that returned non-zero (the host then runs its CPU loop), and
+    // which attention family served the long sequences.
+    unsigned long long declined_ops = 0;
+    unsigned long long tc_attention_launches = 0;
+    unsigned long long streaming_attention_launches = 0;
     void (*set_table)(const vitb200_op_table *) = nullptr;
     void (*set_allocator)(vitb200_allocate_fn, vitb200_release_fn,
                           void *) = nullptr;
@@ -386,13 +391,25 @@ void free_scratch(Scratch &buffer) {
     buffer = Scratch{};
 }
 
-// A tensor is gone: forget the log-sum-exp buffer kept for it, if any (the
-// host's evaluation entry points create and free a cache per call).
+void flush_pending(CudaBackend *backend);
+
+// A tensor is about to go (its region still exists).  Ops that were recorded
+// but held back keep raw pointers into tensors, so they are launched now,
+// while every buffer they name is still there; then the log-sum-exp buffer
+// kept for the tensor, if any, is forgotten (the host's evaluation entry
+// points create and free a cache per call).
 void release_hook(const void *host_pointer) {
     CudaBackend *backend = g_flush_backend;
     if (!backend) {
         return;
     }
+    if (backend->pending.active || backend->pending_attention.active ||
+        backend->pending_attention_backward.active ||
+        backend->pending_residual.active ||
+        backend->pending_input_gradient.active) {
+        flush_pending(backend);
+    }
+    dp_tensor_released(backend->dp, host_pointer);
     auto found = backend->lse_buffers.find(host_pointer);
     if (found != backend->lse_buffers.end()) {
         // The buffer may still be read by enqueued work.
@@ -459,17 +476,75 @@ void flush_input_gradient(CudaBackend *backend) {
 }
 
 
+// Long sequences: the tcgen05 kernels where they apply (head_dim 32 or 64, at
+// least a tile's worth of rows; VITB200_ATTENTION=stream switches them off),
+// otherwise the register-resident streaming kernels.  Both keep the same
+// log-sum-exp rows.
+bool tc_attention_wanted(size_t seq, size_t head_dim) {
+    static const bool disabled = []() {
+        const char *choice = getenv("VITB200_ATTENTION");
+        return choice && strcmp(choice, "stream") == 0;
+    }();
+    return !disabled && seq >= 96 && attention_tc_supported(seq, head_dim);
+}
+
+bool long_attention_forward(CudaBackend *backend, const float *q, const float *k,
+                            const float *v, float *out, float *lse, size_t groups,
+                            size_t seq, size_t head_dim, float scale,
+                            HeadLayout in_layout = HeadLayout(),
+                            HeadLayout out_layout = HeadLayout()) {
+    if (tc_attention_wanted(seq, head_dim) &&
+        launch_attention_tc_forward(q, k, v, out, lse, groups, seq, head_dim, scale,
+                                    backend->stream, in_layout, out_layout)) {
+        backend->tc_attention_launches += 1;
+        return true;
+    }
+    if (launch_attention_stream_forward(q, k, v, out, lse, groups, seq, head_dim,
+                                        scale, backend->stream, in_layout,
+                                        out_layout)) {
+        backend->streaming_attention_launches += 1;
+        return true;
+    }
+    return false;
+}
+
+bool long_attention_backward(CudaBackend *backend, const float *q, const float *k,
+                             const float *v, const float *out, const float *dout,
+                             const float *lse, float *dq, float *dk, float *dv,
+                             float *row_dots, size_t groups, size_t seq,
+                             size_t head_dim, float scale, bool add_q, bool add_k,
+                             bool add_v, HeadLayout in_layout = HeadLayout(),
+                             HeadLayout out_layout = HeadLayout(),
+                             HeadLayout dout_layout = HeadLayout(),
+                             HeadLayout grad_layout = HeadLayout()) {
+    if (tc_attention_wanted(seq, head_dim) &&
+        launch_attention_tc_backward(q, k, v, out, dout, lse, dq, dk, dv, row_dots,
+                                     groups, seq, head_dim, scale, add_q, add_k,
+                                     add_v, backend->stream, in_layout, out_layout,
+                                     dout_layout, grad_layout)) {
+        backend->tc_attention_launches += 1;
+        return true;
+    }
+    if (launch_attention_stream_backward(q, k, v, out, dout, lse, dq, dk, dv,
+                                         row_dots, groups, seq, head_dim, scale,
+                                         add_q, add_k, add_v, backend->stream,
+                                         in_layout, out_layout, dout_layout,
+                                         grad_layout)) {
+        backend->streaming_attention_launches += 1;
+        return true;
+    }
+    return false;
+}
+
 void run_attention(CudaBackend *backend, const PendingAttention &pending,
                    float *out, HeadLayout out_layout) {
     OpScope scope(backend, "multi_head_attention", pending.bytes,
                   pending.flops);
     const size_t groups = pending.batch * pending.heads;
     if (pending.kind == 3) {
-        launch_attention_stream_forward(pending.q, pending.k, pending.v, out,
-                                        pending.lse, groups, pending.seq,
-                                        pending.head_dim, pending.scale,
-                                        backend->stream, pending.in_layout,
-                                        out_layout);
+        long_attention_forward(backend, pending.q, pending.k, pending.v, out,
+                               pending.lse, groups, pending.seq, pending.head_dim,
+                               pending.scale, pending.in_layout, out_layout);
     } else if (pending.kind == 2) {
         launch_attention_warp_forward(pending.q, pending.k, pending.v, out,
                                       groups, pending.seq, pending.head_dim,
@@ -495,12 +570,12 @@ void run_attention_backward(CudaBackend *backend,
     if (pending.kind == 3) {
         float *dots = scratch<float>(backend, backend->rows_scratch,
                                      groups * pending.seq);
-        launch_attention_stream_backward(
-            pending.q, pending.k, pending.v, pending.out, pending.dout,
+        long_attention_backward(
+            backend, pending.q, pending.k, pending.v, pending.out, pending.dout,
             pending.lse, dq, dk, dv, dots, groups, pending.seq,
             pending.head_dim, pending.scale, add_q, add_k, add_v,
-            backend->stream, pending.in_layout, pending.out_layout,
-            pending.dout_layout, grad_layout);
+            pending.in_layout, pending.out_layout, pending.dout_layout,
+            grad_layout);
     } else if (pending.kind == 2) {
         launch_attention_warp_backward(
             pending.q, pending.k, pending.v, pending.out, pending.dout, dq, dk,
@@ -525,7 +600,9 @@ void flush_attention(CudaBackend *backend) {
         const PendingAttention pending = backend->pending_attention;
         backend->pending_attention.active = false;
         float *o = view(backend, pending.output_host, Access::Overwrite);
-        run_attention(backend, pending, o, HeadLayout());
+        if (o) {
+            run_attention(backend, pending, o, HeadLayout());
+        }
     }
     if (backend->pending_attention_backward.active) {
         const PendingAttentionBackward pending =
@@ -535,8 +612,10 @@ void flush_attention(CudaBackend *backend) {
         float *dq = accumulate_view(backend, pending.dq_host, &add_q);
         float *dk = accumulate_view(backend, pending.dk_host, &add_k);
         float *dv = accumulate_view(backend, pending.dv_host, &add_v);
-        run_attention_backward(backend, pending, dq, dk, dv, add_q, add_k,
-                               add_v, HeadLayout());
+        if (dq && dk && dv) {
+            run_attention_backward(backend, pending, dq, dk, dv, add_q, add_k,
+                                   add_v, HeadLayout());
+        }
     }
 }
 
@@ -1537,9 +1616,8 @@ int op_attention(void *context, const vitb200_tensor *query,
             // The register-resident streaming kernels where they exist
             // (head_dim 16, 32, 64); the two families keep different
             // log-sum-exp conventions, remembered per tensor.
-            if (launch_attention_stream_forward(q, k, v, o, lse, groups, seq,
-                                                head_dim, scale,
-                                                backend->stream)) {
+            if (long_attention_forward(backend, q, k, v, o, lse, groups, seq,
+                                       head_dim, scale)) {
                 backend->lse_streamed[probabilities->data] = true;
                 return 0;
             }
@@ -1666,10 +1744,9 @@ int op_attention_backward(void *context, const vitb200_tensor *query,
     {
         OpScope scope(backend, "multi_head_attention_backward", bytes, flops);
         if (lse && backend->lse_streamed[probabilities->data]) {
-            launch_attention_stream_backward(q, k, v, o, go, lse, dq, dk, dv,
-                                             dots, groups, seq, head_dim, scale,
-                                             add_q, add_k, add_v,
-                                             backend->stream);
+            long_attention_backward(backend, q, k, v, o, go, lse, dq, dk, dv,
+                                    dots, groups, seq, head_dim, scale, add_q,
+                                    add_k, add_v);
         } else if (lse) {
             launch_attention_mma_backward(q, k, v, nullptr, lse, o, go, dq, dk,
                                           dv, dots, groups, seq, head_dim,
@@ -1967,13 +2044,16 @@ int op_adamw_step_parameters(void *context,
                              float max_gradient_norm) {
     CudaBackend *backend = self(context);
     flush_pending(backend);
-    SliceTable table;
-    if (build_slice_table(backend, parameters, weight_decays, count, beta1,
-                          beta2, true, &table) != 0) {
-        return -1;
+    for (size_t i = 0; i < count; ++i) {
+        if (!ours({parameters[i]->value.data, parameters[i]->value.grad,
+                   parameters[i]->m, parameters[i]->v})) {
+            return -1;
+        }
     }
     // Data parallel: finish the gradient exchange first; the summed gradients
-    // are turned into their mean by the scale the update multiplies by.
+    // are turned into their mean by the scale the update multiplies by.  (The
+    // exchange may move the gradients' device buffers, so it comes before the
+    // table of pointers the kernels work from.)
     float inverse_world = 1.0f;
     if (backend->dp && dp_world(backend->dp) > 1) {
         std::vector<const void *> host_grads(count);
@@ -1988,6 +2068,11 @@ int op_adamw_step_parameters(void *context,
         inverse_world = dp_before_optimizer(backend->dp, host_grads.data(),
                                             device_grads.data(), counts.data(),
                                             count);
+    }
+    SliceTable table;
+    if (build_slice_table(backend, parameters, weight_decays, count, beta1,
+                          beta2, true, &table) != 0) {
+        return -1;
     }
     // Gradient accumulation: the gradients are sums over micro-batches as well.
     inverse_world *= backend->accumulation_inverse;
@@ -2016,37 +2101,55 @@ void op_synchronize(void *context) {
     settle_timers(self(context));
 }
 
+// Every op slot goes through this wrapper, which counts the calls the slot
+// declined (non-zero return: the host synchronises and runs its own CPU loop,
+// reference src/ops.c:61-64).  A training or evaluation step that is meant to
+// run on the device must leave the count unchanged.
+template <auto Slot>
+struct Counted;
+template <typename... Arguments, int (*Slot)(void *, Arguments...)>
+struct Counted<Slot> {
+    static int call(void *context, Arguments... arguments) {
+        const int status = Slot(context, arguments...);
+        if (status != 0) {
+            self(context)->declined_ops += 1;
+        }
+        return status;
+    }
+};
+#define COUNTED(slot) Counted<slot>::call
+
 vitb200_op_table make_table(CudaBackend *backend) {
     vitb200_op_table table = {};
     table.context = backend;
-    table.gemm = op_gemm;
-    table.gemm_backward = op_gemm_backward;
-    table.residual = op_residual;
-    table.residual_backward = op_residual_backward;
-    table.accumulate_gradient = op_accumulate_gradient;
-    table.bias_add = op_bias_add;
-    table.bias_add_backward = op_bias_add_backward;
-    table.layer_norm = op_layer_norm;
-    table.layer_norm_backward = op_layer_norm_backward;
-    table.gelu = op_gelu;
-    table.gelu_backward = op_gelu_backward;
-    table.split_heads = op_split_heads;
-    table.split_heads_backward = op_split_heads_backward;
-    table.merge_heads = op_merge_heads;
-    table.merge_heads_backward = op_merge_heads_backward;
-    table.multi_head_attention = op_attention;
-    table.multi_head_attention_backward = op_attention_backward;
-    table.zero_gradient = op_zero_gradient;
-    table.extract_patches = op_extract_patches;
-    table.token_embedding = op_token_embedding;
-    table.token_embedding_backward = op_token_embedding_backward;
-    table.gather_rows = op_gather_rows;
-    table.gather_rows_backward = op_gather_rows_backward;
-    table.softmax_cross_entropy = op_softmax_cross_entropy;
-    table.clip_gradient_norm = op_clip_gradient_norm;
-    table.adamw_step = op_adamw_step;
-    table.zero_gradients = op_zero_gradients;
-    table.adamw_step_parameters = op_adamw_step_parameters;
+    table.gemm = COUNTED(op_gemm);
+    table.gemm_backward = COUNTED(op_gemm_backward);
+    table.residual = COUNTED(op_residual);
+    table.residual_backward = COUNTED(op_residual_backward);
+    table.accumulate_gradient = COUNTED(op_accumulate_gradient);
+    table.bias_add = COUNTED(op_bias_add);
+    table.bias_add_backward = COUNTED(op_bias_add_backward);
+    table.layer_norm = COUNTED(op_layer_norm);
+    table.layer_norm_backward = COUNTED(op_layer_norm_backward);
+    table.gelu = COUNTED(op_gelu);
+    table.gelu_backward = COUNTED(op_gelu_backward);
+    table.split_heads = COUNTED(op_split_heads);
+    table.split_heads_backward = COUNTED(op_split_heads_backward);
+    table.merge_heads = COUNTED(op_merge_heads);
+    table.merge_heads_backward = COUNTED(op_merge_heads_backward);
+    table.multi_head_attention = COUNTED(op_attention);
+    table.multi_head_attention_backward = COUNTED(op_attention_backward);
+    table.zero_gradient = COUNTED(op_zero_gradient);
+    table.extract_patches = COUNTED(op_extract_patches);
+    table.token_embedding = COUNTED(op_token_embedding);
+    table.token_embedding_backward = COUNTED(op_token_embedding_backward);
+    table.gather_rows = COUNTED(op_gather_rows);
+    table.gather_rows_backward = COUNTED(op_gather_rows_backward);
+    table.softmax_cross_entropy = COUNTED(op_softmax_cross_entropy);
+    table.clip_gradient_norm = COUNTED(op_clip_gradient_norm);
+    table.adamw_step = COUNTED(op_adamw_step);
+    table.zero_gradients = COUNTED(op_zero_gradients);
+    table.adamw_step_parameters = COUNTED(op_adamw_step_parameters);
     table.synchronize = op_synchronize;
     return table;
 }
@@ -2698,6 +2801,28 @@ extern "C" void vitb200_fusion_counters(const CudaBackend *backend,
     if (bias_gradients) *bias_gradients = backend ? backend->memo_hits : 0;
 }
 
+extern "C" unsigned long long vitb200_declined_ops(const CudaBackend *backend) {
+    return backend ? backend->declined_ops : 0;
+}
+
+extern "C" void vitb200_kernel_path_counters(
+    const CudaBackend *backend, unsigned long long *tensor_core_products,
+    unsigned long long *wide_tile_products, unsigned long long *fma_products,
+    unsigned long long *tensor_core_attention,
+    unsigned long long *streaming_attention) {
+    unsigned long long tc = 0, wide = 0, fma = 0;
+    gemm_path_counters(&tc, &wide, &fma);
+    if (tensor_core_products) *tensor_core_products = tc;
+    if (wide_tile_products) *wide_tile_products = wide;
+    if (fma_products) *fma_products = fma;
+    if (tensor_core_attention) {
+        *tensor_core_attention = backend ? backend->tc_attention_launches : 0;
+    }
+    if (streaming_attention) {
+        *streaming_attention = backend ? backend->streaming_attention_launches : 0;
+    }
+}
+
 extern "C" int vitb200_make_host_coherent(const void *tensor_memory) {
     return coherent_make_host_owned(tensor_memory);
 }
@@ -2750,6 +2875,10 @@ extern "C" void vitb200_dp_counters(CudaBackend *backend,
                                     unsigned long long *bytes) {
     dp_counters(backend ? backend->dp : nullptr, all_reduce_calls,
                 overlapped_tensors, late_tensors, bytes);
+}
+
+extern "C" unsigned long long vitb200_dp_flat_ranges(CudaBackend *backend) {
+    return dp_flat_ranges(backend ? backend->dp : nullptr);
 }
 
 extern "C" int vitb200_set_gradient_accumulation(CudaBackend *backend,

@@ -9,6 +9,7 @@
 #include <cstdlib>
 #include <cstring>
 #include <map>
+#include <vector>
 
 #include <sys/mman.h>
 #include <ucontext.h>
@@ -161,7 +162,30 @@ struct LazyDefinition {
     LazyDefinition *next_reader[2] = {nullptr, nullptr};
 };
 
+// Device memory owned by somebody else (the gradient-exchange arena) that
+// buffers may be placed in: never pooled, never freed here.
+struct ExternalRange {
+    uintptr_t begin, end;
+};
+std::vector<ExternalRange> &external_ranges() {
+    static std::vector<ExternalRange> *ranges = new std::vector<ExternalRange>();
+    return *ranges;
+}
+
+bool is_external(const void *device) {
+    const uintptr_t address = reinterpret_cast<uintptr_t>(device);
+    for (const ExternalRange &range : external_ranges()) {
+        if (address >= range.begin && address < range.end) {
+            return true;
+        }
+    }
+    return false;
+}
+
 void recycle(float *device, size_t bytes) {
+    if (is_external(device)) {
+        return;
+    }
     if (g_pooled_bytes + bytes <= kPoolLimitBytes) {
         buffer_pool().emplace(bytes, device);
         g_pooled_bytes += bytes;
@@ -408,6 +432,11 @@ void *coherent_allocate(void *context, size_t bytes) {
 
 void coherent_release(void *context, void *memory) {
     (void)context;
+    if (g_released && memory) {
+        // While the region still exists: work that was recorded against it
+        // but not launched yet has to go out (or be dropped) first.
+        g_released(memory);
+    }
     auto &regions = registry();
     auto it = regions.find(reinterpret_cast<uintptr_t>(memory));
     if (it == regions.end()) {
@@ -422,9 +451,6 @@ void coherent_release(void *context, void *memory) {
     }
     Region region = it->second;
     regions.erase(it);
-    if (g_released) {
-        g_released(memory);
-    }
     if (region.pinned) {
         cudaHostUnregister(region.mirror);
     }
@@ -435,6 +461,63 @@ void coherent_release(void *context, void *memory) {
     munmap(region.mirror, region.mapped);
     g_stats.live_allocations -= 1;
     g_stats.mirror_bytes -= region.mapped;
+}
+
+void coherent_external_range(const void *base, size_t bytes, bool add) {
+    auto &ranges = external_ranges();
+    const uintptr_t begin = reinterpret_cast<uintptr_t>(base);
+    if (add) {
+        ranges.push_back(ExternalRange{begin, begin + bytes});
+        return;
+    }
+    for (size_t i = 0; i < ranges.size(); ++i) {
+        if (ranges[i].begin == begin) {
+            ranges.erase(ranges.begin() + long(i));
+            return;
+        }
+    }
+}
+
+size_t coherent_device_bytes(const void *host_pointer) {
+    const Region *region = host_pointer ? find_base(host_pointer) : nullptr;
+    return region ? region->mapped : 0;
+}
+
+bool coherent_place_device_buffer(const void *host_pointer, float *device,
+                                  cudaStream_t stream) {
+    Region *region = host_pointer ? find_base(host_pointer) : nullptr;
+    if (!region || region->lazy || region->feeds) {
+        return false;
+    }
+    if (region->device == device && device) {
+        return true;
+    }
+    float *old = region->device;
+    if (!device) {
+        if (!old || !is_external(old)) {
+            return true;   // already in memory of its own (or nowhere yet)
+        }
+        region->device = nullptr;
+        g_stats.device_bytes -= region->mapped;
+        ensure_device_buffer(*region);
+        device = region->device;
+    } else {
+        if (!old) {
+            g_stats.device_bytes += region->mapped;
+        }
+        region->device = device;
+    }
+    if (old) {
+        // Whatever the old buffer holds that is current moves along; a
+        // pending zero fill or host-owned contents need no copy.
+        if (region->owner != Owner::Host && !region->zero_pending) {
+            check(cudaMemcpyAsync(device, old, region->bytes,
+                                  cudaMemcpyDeviceToDevice, stream),
+                  "cudaMemcpyAsync(device to device)");
+        }
+        recycle(old, region->mapped);
+    }
+    return true;
 }
 
 bool coherent_owns(const void *host_pointer) {

@@ -127,6 +127,22 @@ int coherent_make_host_owned(const void *host_pointer);
 int coherent_prepare_host_io(const void *pointer, size_t bytes,
                              bool host_writes);
 
+// Device memory owned by the caller in which buffers may be placed
+// (coherent_place_device_buffer): this layer never pools or frees it.
+// add = false withdraws a range registered earlier (by its base address).
+void coherent_external_range(const void *base, size_t bytes, bool add);
+// Bytes a device buffer for this mirror occupies (the page-rounded size of the
+// allocation); 0 for memory we did not allocate.
+size_t coherent_device_bytes(const void *host_pointer);
+// Moves a mirror's device buffer to `device` (inside a registered external
+// range, coherent_device_bytes() large), carrying current device contents
+// along on `stream`; the old buffer is recycled.  device = nullptr moves a
+// buffer that lives in external memory back into memory of this layer's own.
+// False (nothing changed) for memory we did not allocate and for buffers that
+// are lazily defined or read by pending definitions.
+bool coherent_place_device_buffer(const void *host_pointer, float *device,
+                                  cudaStream_t stream);
+
 // Called by the backend so the fault handler can drain work before copying.
 void coherence_set_stream(cudaStream_t stream, void (*flush)(void));
 // Called with the host address of every allocation that is released, so that

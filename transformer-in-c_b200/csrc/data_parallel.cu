@@ -1,4 +1,5 @@
 #include "data_parallel.h"
+#include "coherence.h"
 
 #include <cstdio>
 #include <cstdlib>
@@ -83,7 +84,9 @@ struct Gradient {
     int producers_this_step = 0;
     int expected_producers = 0;  // producers seen in the previous step
     bool overlap = false;   // the producer count is known: safe to reduce early
-    bool reduced = false;
+    bool reduced = false;   // handed to NCCL, or complete inside the arena, this step
+    size_t offset = 0;      // arena mode: position inside the arena, in floats
+    size_t slot = 0;        // arena mode: floats reserved (a multiple of a page)
 };
 
 struct Pending {
@@ -91,9 +94,10 @@ struct Pending {
     size_t count;
 };
 
-// Buckets are flushed once they hold this much, so the exchange starts while
-// the backward pass is still running but launch overheads stay amortised.
-constexpr size_t kBucketBytes = size_t(2) << 20;
+// Ranges are handed to NCCL once they hold this much, so the exchange starts
+// while the backward pass is still running but launch overheads stay
+// amortised; the last range goes out as soon as the last gradient is complete.
+constexpr size_t kBucketBytes = size_t(4) << 20;
 
 }  // namespace
 
@@ -113,17 +117,37 @@ struct DataParallel {
     unsigned long long overlapped = 0;
     unsigned long long late = 0;
     unsigned long long bytes = 0;
+    // Flat exchange.  Step 2 records the order in which the gradients become
+    // complete; at its optimiser call their device buffers move, in that
+    // order, into one allocation (the arena), and from then on contiguous
+    // ranges of it are all-reduced as their last gradient becomes complete:
+    // a handful of NCCL calls per step instead of one per tensor.
+    std::vector<const void *> completion_order;   // being recorded this step
+    std::vector<const void *> arena_order;
+    float *arena = nullptr;
+    size_t arena_floats = 0;
+    bool arena_failed = false;   // do not try again
+    size_t complete_prefix = 0;  // gradients of arena_order complete this step
+    size_t complete_floats = 0;  // arena floats they cover
+    size_t sent_floats = 0;      // arena floats handed to NCCL this step
+    unsigned long long arena_ranges = 0;
 };
 
 namespace {
+
+constexpr size_t kPageFloats = 1024;
+
+void wait_for_compute(DataParallel *dp) {
+    check_cuda(cudaEventRecord(dp->produced, dp->compute), "cudaEventRecord");
+    check_cuda(cudaStreamWaitEvent(dp->exchange, dp->produced, 0),
+               "cudaStreamWaitEvent");
+}
 
 void flush(DataParallel *dp) {
     if (dp->pending.empty()) {
         return;
     }
-    check_cuda(cudaEventRecord(dp->produced, dp->compute), "cudaEventRecord");
-    check_cuda(cudaStreamWaitEvent(dp->exchange, dp->produced, 0),
-               "cudaStreamWaitEvent");
+    wait_for_compute(dp);
     check_nccl(nccl().group_start(), "ncclGroupStart");
     for (const Pending &item : dp->pending) {
         check_nccl(nccl().all_reduce(item.device, item.device, item.count,
@@ -143,6 +167,88 @@ void enqueue(DataParallel *dp, float *device, size_t count) {
     dp->pending_bytes += count * sizeof(float);
     if (dp->pending_bytes >= kBucketBytes) {
         flush(dp);
+    }
+}
+
+// All-reduces arena floats [sent, upto) in one call.
+void send_range(DataParallel *dp, size_t upto) {
+    if (upto <= dp->sent_floats) {
+        return;
+    }
+    wait_for_compute(dp);
+    float *range = dp->arena + dp->sent_floats;
+    const size_t count = upto - dp->sent_floats;
+    check_nccl(nccl().all_reduce(range, range, count, kNcclFloat32, kNcclSum,
+                                 dp->comm, dp->exchange),
+               "ncclAllReduce");
+    dp->all_reduce_calls += 1;
+    dp->arena_ranges += 1;
+    dp->bytes += count * sizeof(float);
+    dp->sent_floats = upto;
+}
+
+// Gives every gradient its own device buffer back and frees the arena.
+void drop_arena(DataParallel *dp) {
+    if (!dp->arena) {
+        return;
+    }
+    for (const void *host : dp->arena_order) {
+        // False for tensors that are gone already: nothing to move.
+        coherent_place_device_buffer(host, nullptr, dp->compute);
+    }
+    check_cuda(cudaStreamSynchronize(dp->compute), "cudaStreamSynchronize");
+    check_cuda(cudaStreamSynchronize(dp->exchange), "cudaStreamSynchronize");
+    coherent_external_range(dp->arena, dp->arena_floats * sizeof(float), false);
+    cudaFree(dp->arena);
+    dp->arena = nullptr;
+    dp->arena_floats = 0;
+    dp->arena_order.clear();
+}
+
+// Step 2's optimiser call: the completion order is known for every
+// parameter exactly once -> move the gradients into one allocation.
+void build_arena(DataParallel *dp, const void *const *host_grads, size_t parameters) {
+    if (dp->arena || dp->arena_failed ||
+        dp->completion_order.size() != parameters) {
+        return;
+    }
+    size_t total = 0;
+    for (const void *host : dp->completion_order) {
+        auto found = dp->gradients.find(host);
+        const size_t bytes = coherent_device_bytes(host);
+        if (found == dp->gradients.end() || found->second.slot != 0 || bytes == 0) {
+            for (auto &entry : dp->gradients) {
+                entry.second.slot = 0;
+            }
+            return;   // not a permutation of the parameter list
+        }
+        found->second.slot =
+            (bytes / sizeof(float) + kPageFloats - 1) / kPageFloats * kPageFloats;
+        found->second.offset = total;
+        total += found->second.slot;
+    }
+    (void)host_grads;
+    void *memory = nullptr;
+    if (cudaMalloc(&memory, total * sizeof(float)) != cudaSuccess) {
+        cudaGetLastError();
+        dp->arena_failed = true;
+        return;
+    }
+    dp->arena = static_cast<float *>(memory);
+    dp->arena_floats = total;
+    check_cuda(cudaMemsetAsync(dp->arena, 0, total * sizeof(float), dp->compute),
+               "cudaMemsetAsync");
+    coherent_external_range(dp->arena, total * sizeof(float), true);
+    dp->arena_order = dp->completion_order;
+    for (const void *host : dp->arena_order) {
+        Gradient &gradient = dp->gradients[host];
+        if (!coherent_place_device_buffer(host, dp->arena + gradient.offset,
+                                          dp->compute)) {
+            drop_arena(dp);
+            dp->arena_failed = true;
+            return;
+        }
+        gradient.device = dp->arena + gradient.offset;
     }
 }
 
@@ -178,6 +284,8 @@ DataParallel *dp_create(int rank, int world, const void *id128,
         dp_destroy(dp);
         return nullptr;
     }
+    const char *flat = getenv("VITB200_DP_FLAT");
+    dp->arena_failed = flat && atoi(flat) == 0;   // per-tensor exchange only
     return dp;
 }
 
@@ -187,6 +295,9 @@ void dp_destroy(DataParallel *dp) {
     }
     if (dp->exchange) {
         cudaStreamSynchronize(dp->exchange);
+    }
+    if (dp->compute && dp->exchange) {
+        drop_arena(dp);
     }
     if (dp->comm) {
         nccl().comm_destroy(dp->comm);
@@ -218,13 +329,43 @@ void dp_gradient_produced(DataParallel *dp, const void *host_grad,
     }
     Gradient &gradient = found->second;
     gradient.producers_this_step += 1;
-    if (gradient.overlap && !gradient.reduced && gradient.count == count &&
-        gradient.producers_this_step == gradient.expected_producers) {
-        gradient.device = device_grad;
+    const bool complete = gradient.expected_producers > 0 &&
+                          gradient.producers_this_step == gradient.expected_producers;
+    if (complete && !dp->arena) {
+        dp->completion_order.push_back(host_grad);
+    }
+    if (!complete || !gradient.overlap || gradient.reduced ||
+        gradient.count != count) {
+        return;
+    }
+    if (dp->arena) {
+        if (device_grad != dp->arena + gradient.offset) {
+            // The buffer has left the arena (it should not): the optimiser
+            // call notices and falls back to the per-tensor exchange.
+            return;
+        }
         gradient.reduced = true;
         dp->overlapped += 1;
-        enqueue(dp, device_grad, count);
+        // Extend the prefix of complete gradients; ranges go out whole.
+        while (dp->complete_prefix < dp->arena_order.size()) {
+            const Gradient &next = dp->gradients[dp->arena_order[dp->complete_prefix]];
+            if (!next.reduced) {
+                break;
+            }
+            dp->complete_floats = next.offset + next.slot;
+            dp->complete_prefix += 1;
+        }
+        const bool everything = dp->complete_prefix == dp->arena_order.size();
+        if (everything || (dp->complete_floats - dp->sent_floats) * sizeof(float) >=
+                              kBucketBytes) {
+            send_range(dp, dp->complete_floats);
+        }
+        return;
     }
+    gradient.device = device_grad;
+    gradient.reduced = true;
+    dp->overlapped += 1;
+    enqueue(dp, device_grad, count);
 }
 
 float dp_before_optimizer(DataParallel *dp, const void *const *host_grads,
@@ -234,6 +375,26 @@ float dp_before_optimizer(DataParallel *dp, const void *const *host_grads,
         return 1.0f;
     }
     dp->optimizer_calls += 1;
+    // The arena serves exactly the parameter list it was built for, with
+    // every buffer still inside it.
+    if (dp->arena) {
+        bool intact = parameters == dp->arena_order.size();
+        for (size_t i = 0; intact && i < parameters; ++i) {
+            auto found = dp->gradients.find(host_grads[i]);
+            intact = found != dp->gradients.end() && found->second.slot != 0 &&
+                     device_grads[i] == dp->arena + found->second.offset;
+        }
+        if (!intact) {
+            if (dp->sent_floats != 0) {
+                fprintf(stderr, "vitb200: the parameter list changed after part of "
+                                "its gradients had been exchanged\n");
+                abort();
+            }
+            drop_arena(dp);
+            dp->gradients.clear();
+            dp->optimizer_calls = 1;
+        }
+    }
     for (size_t i = 0; i < parameters; ++i) {
         Gradient &gradient = dp->gradients[host_grads[i]];
         if (gradient.reduced &&
@@ -248,7 +409,9 @@ float dp_before_optimizer(DataParallel *dp, const void *const *host_grads,
         }
         if (!gradient.reduced) {
             dp->late += 1;
-            enqueue(dp, device_grads[i], counts[i]);
+            if (!dp->arena) {
+                enqueue(dp, device_grads[i], counts[i]);
+            }
         }
         // Once two steps in a row have written a gradient the same number of
         // times (one op per micro-batch), it is exchanged as soon as the last
@@ -258,15 +421,28 @@ float dp_before_optimizer(DataParallel *dp, const void *const *host_grads,
                            gradient.producers_this_step ==
                                gradient.expected_producers;
         gradient.expected_producers = gradient.producers_this_step;
-        gradient.device = device_grads[i];
+        if (!dp->arena) {
+            gradient.device = device_grads[i];
+        }
         gradient.count = counts[i];
         gradient.producers_this_step = 0;
         gradient.reduced = false;
     }
-    flush(dp);
+    if (dp->arena) {
+        send_range(dp, dp->arena_floats);   // whatever has not gone out yet
+        dp->complete_prefix = 0;
+        dp->complete_floats = 0;
+        dp->sent_floats = 0;
+    } else {
+        flush(dp);
+    }
     check_cuda(cudaEventRecord(dp->exchanged, dp->exchange), "cudaEventRecord");
     check_cuda(cudaStreamWaitEvent(dp->compute, dp->exchanged, 0),
                "cudaStreamWaitEvent");
+    if (!dp->arena && dp->optimizer_calls >= 2) {
+        build_arena(dp, host_grads, parameters);
+    }
+    dp->completion_order.clear();
     return 1.0f / float(dp->world);
 }
 
@@ -281,6 +457,20 @@ void dp_forget_schedule(DataParallel *dp) {
     }
 }
 
+void dp_tensor_released(DataParallel *dp, const void *host_pointer) {
+    if (!dp || dp->gradients.find(host_pointer) == dp->gradients.end()) {
+        return;
+    }
+    // A parameter is going away: this model's schedule and arena are over.
+    drop_arena(dp);
+    dp->gradients.clear();
+    dp->completion_order.clear();
+    dp->optimizer_calls = 0;
+    dp->complete_prefix = 0;
+    dp->complete_floats = 0;
+    dp->sent_floats = 0;
+}
+
 void dp_counters(const DataParallel *dp, unsigned long long *all_reduce_calls,
                  unsigned long long *overlapped_tensors,
                  unsigned long long *late_tensors, unsigned long long *bytes) {
@@ -288,6 +478,10 @@ void dp_counters(const DataParallel *dp, unsigned long long *all_reduce_calls,
     if (overlapped_tensors) *overlapped_tensors = dp ? dp->overlapped : 0;
     if (late_tensors) *late_tensors = dp ? dp->late : 0;
     if (bytes) *bytes = dp ? dp->bytes : 0;
+}
+
+unsigned long long dp_flat_ranges(const DataParallel *dp) {
+    return dp ? dp->arena_ranges : 0;
 }
 
 }  // namespace vitb200

@@ -14,6 +14,15 @@
 //
 // Gradients are summed; the 1/world factor is folded into the clip scale the
 // optimiser kernel already multiplies by, so no extra pass touches them.
+//
+// The first optimiser call learns the parameter list, the second the order in
+// which the gradients become complete; their device buffers then move, in
+// that order, into one allocation, and from the third step on contiguous
+// ranges of it (at least 4 MiB, the last one whatever is left) are
+// all-reduced as soon as their last gradient is complete: a handful of NCCL
+// calls per step, the final one issued when the last weight gradient of the
+// backward pass has been enqueued.  VITB200_DP_FLAT=0 keeps the per-tensor
+// exchange of the first two steps for good.
 // NCCL is loaded with dlopen when data parallelism is switched on, so single
 // GPU users need no NCCL at all.
 #pragma once
@@ -54,9 +63,17 @@ float dp_before_optimizer(DataParallel *dp, const void *const *host_grads,
 // called when the number of micro-batches per optimiser step changes.
 void dp_forget_schedule(DataParallel *dp);
 
+// A tensor is about to be released: if it is one of the known parameter
+// gradients, the schedule (and the arena the gradients were moved into) is
+// dropped and learnt again from the next optimiser call on.
+void dp_tensor_released(DataParallel *dp, const void *host_pointer);
+
 // Counters for tests and the bench line.
 void dp_counters(const DataParallel *dp, unsigned long long *all_reduce_calls,
                  unsigned long long *overlapped_tensors,
                  unsigned long long *late_tensors, unsigned long long *bytes);
+
+// Contiguous ranges all-reduced out of the gradient arena so far.
+unsigned long long dp_flat_ranges(const DataParallel *dp);
 
 }  // namespace vitb200

@@ -106,6 +106,15 @@ bool prefer_tensor_cores(int precision, double multiply_adds) {
     return multiply_adds >= kTensorCoreMinimumWork;
 }
 
+extern unsigned long long g_fma_products;
+
+void gemm_path_counters(unsigned long long *tensor_core,
+                        unsigned long long *wide_tile, unsigned long long *fma) {
+    *tensor_core = g_tc_products;
+    *wide_tile = g_tc_wide_products;
+    *fma = g_fma_products;
+}
+
 void gemm_set_default_precision(int precision) {
     g_forced_precision = precision;
 }

@@ -68,5 +68,9 @@ int gemm_default_precision();
 // Overrides what VITB200_PRECISION_AUTO means (and the VITB200_GEMM
 // environment variable); -1 restores the default policy.
 void gemm_set_default_precision(int precision);
+// Products launched since the library was loaded: on the tensor cores, of
+// those with the 128 x 256 tile, and on the FP32 FMA kernel.
+void gemm_path_counters(unsigned long long *tensor_core,
+                        unsigned long long *wide_tile, unsigned long long *fma);
 
 }  // namespace vitb200

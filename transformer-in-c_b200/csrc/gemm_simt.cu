@@ -117,7 +117,10 @@ gemm_simt_kernel(GemmOperands op, int k_per_split) {
 
 }  // namespace
 
+unsigned long long g_fma_products = 0;
+
 void launch_gemm_simt(const GemmOperands &operands, cudaStream_t stream) {
+    ++g_fma_products;
     const unsigned grid_x = (operands.m + kTileM - 1) / kTileM;
     const unsigned grid_y = (operands.n + kTileN - 1) / kTileN;
     unsigned splits = 1;

@@ -906,8 +906,14 @@ int launch_gemm_tc(const TcGemm &g, cudaStream_t stream) {
             map_a, map_b, map_d, map_d2, p);
     }
     ++g_kernel_launches;
+    ++g_tc_products;
+    if (wide) {
+        ++g_tc_wide_products;
+    }
     return 0;
 }
+
+unsigned long long g_tc_products = 0, g_tc_wide_products = 0;
 
 int gemm_tc_status() {
     int *word = status_word();

@@ -42,6 +42,9 @@ bool gemm_tc_supported(const TcGemm &gemm);
 int launch_gemm_tc(const TcGemm &gemm, cudaStream_t stream);
 // 0, or the code of the first bounded wait that expired inside the kernel.
 int gemm_tc_status();
+// Products launched on the tensor cores since the library was loaded, and
+// how many of them used the 128 x 256 tile.
+extern unsigned long long g_tc_products, g_tc_wide_products;
 // Device address of that status word, shared by every kernel of the library
 // that waits on an mbarrier (codes 1..15: matrix product, 16..: attention);
 // nullptr when it could not be mapped.

@@ -365,3 +365,71 @@ int vithost_predict(VitHost *host, const float *images, size_t sample_count,
     return vit_model_predict_probabilities(&host->model, images, sample_count,
                                            probabilities);
 }
+
+/* The reference's single-parameter optimiser entry point (ops.c:1102-1121,
+ * used by its own tests, tests/test_vision.c:616-624) on a parameter created
+ * here: `steps` calls of ops_adamw_step on a [rows, cols] parameter whose
+ * value and gradient start from the given arrays (the gradient is restored
+ * before every call: the update zeroes it).  Returns the value, both moments
+ * and the step counter.  With a backend enabled the parameter lives in
+ * backend memory and the update runs in the adamw_step slot. */
+int vithost_adamw_single(const float *values, const float *gradient, size_t rows,
+                         size_t cols, size_t steps, float learning_rate,
+                         float beta1, float beta2, float epsilon,
+                         float weight_decay, float *value_out, float *m_out,
+                         float *v_out, size_t *step_out) {
+    Parameter parameter;
+    memset(&parameter, 0, sizeof(parameter));
+    if (parameter_init(&parameter, rows, cols) != 0) {
+        return -1;
+    }
+    const size_t count = rows * cols;
+    int status = 0;
+    ops_synchronize();
+    memcpy(parameter.value.data, values, count * sizeof(float));
+    for (size_t step = 0; step < steps && status == 0; ++step) {
+        ops_synchronize();
+        memcpy(parameter.value.grad, gradient, count * sizeof(float));
+        status = ops_adamw_step(&parameter, learning_rate, beta1, beta2, epsilon,
+                                weight_decay);
+    }
+    ops_synchronize();
+    memcpy(value_out, parameter.value.data, count * sizeof(float));
+    memcpy(m_out, parameter.m, count * sizeof(float));
+    memcpy(v_out, parameter.v, count * sizeof(float));
+    *step_out = parameter.step;
+    parameter_free(&parameter);
+    return status;
+}
+
+/* ops_clip_gradient_norm (ops.c:588-617) over freshly created parameters
+ * whose gradients are the given arrays (one array of `counts[i]` floats
+ * each); the clipped gradients are copied back. */
+int vithost_clip_gradients(float *const *gradients, const size_t *counts,
+                           size_t tensors, float max_norm) {
+    Parameter *storage = calloc(tensors, sizeof(*storage));
+    Parameter **list = calloc(tensors, sizeof(*list));
+    int status = storage && list ? 0 : -1;
+    size_t made = 0;
+    for (; status == 0 && made < tensors; ++made) {
+        status = parameter_init(&storage[made], 1, counts[made]);
+        list[made] = &storage[made];
+    }
+    if (status == 0) {
+        ops_synchronize();
+        for (size_t i = 0; i < tensors; ++i) {
+            memcpy(storage[i].value.grad, gradients[i], counts[i] * sizeof(float));
+        }
+        status = ops_clip_gradient_norm(list, tensors, max_norm);
+        ops_synchronize();
+        for (size_t i = 0; i < tensors; ++i) {
+            memcpy(gradients[i], storage[i].value.grad, counts[i] * sizeof(float));
+        }
+    }
+    for (size_t i = 0; i < made; ++i) {
+        parameter_free(&storage[i]);
+    }
+    free(storage);
+    free(list);
+    return status;
+}

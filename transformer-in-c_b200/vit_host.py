@@ -36,10 +36,14 @@ class Augmentation(ctypes.Structure):
         "maximum_value")]
 
 
-def load_host_library(path):
-    """Loads the host library so that its symbols are visible to the backend
-    (RTLD_GLOBAL), and declares the flat entry points."""
-    lib = ctypes.CDLL(path, mode=ctypes.RTLD_GLOBAL)
+def load_host_library(path, visible_to_backend=True):
+    """Loads a host library and declares the flat entry points.  The copy that
+    drives the backend is loaded with RTLD_GLOBAL, so that the backend finds
+    its ops_set_device_backend / tensor_set_allocator; a copy that serves as
+    the CPU checker is loaded with local scope (visible_to_backend=False) and
+    never gets a backend installed."""
+    lib = ctypes.CDLL(path, mode=ctypes.RTLD_GLOBAL if visible_to_backend
+                      else ctypes.RTLD_LOCAL)
     lib.vithost_create.restype = ctypes.c_void_p
     lib.vithost_create.argtypes = [_size_t] * 9 + [ctypes.c_uint64]
     lib.vithost_destroy.argtypes = [ctypes.c_void_p]
@@ -251,7 +255,11 @@ class Backend:
         self.lib.vitb200_dp_counters(self.handle,
                                      *[ctypes.byref(v) for v in values])
         names = ["all_reduce_calls", "overlapped_tensors", "late_tensors", "bytes"]
-        return {n: int(v.value) for n, v in zip(names, values)}
+        counters = {n: int(v.value) for n, v in zip(names, values)}
+        self.lib.vitb200_dp_flat_ranges.restype = ctypes.c_ulonglong
+        self.lib.vitb200_dp_flat_ranges.argtypes = [ctypes.c_void_p]
+        counters["flat_ranges"] = int(self.lib.vitb200_dp_flat_ranges(self.handle))
+        return counters
 
     def set_gradient_accumulation(self, micro_batches):
         """The following optimiser steps consume gradients summed over this
@@ -307,6 +315,23 @@ class Backend:
         self.lib.vitb200_fusion_counters(self.handle,
                                          *[ctypes.byref(v) for v in values])
         names = ["epilogues", "head_layouts", "bias_gradients"]
+        return {n: int(v.value) for n, v in zip(names, values)}
+
+    def declined_ops(self):
+        """Op-table calls the backend declined (the host ran its CPU loop)."""
+        self.lib.vitb200_declined_ops.restype = ctypes.c_ulonglong
+        self.lib.vitb200_declined_ops.argtypes = [ctypes.c_void_p]
+        return int(self.lib.vitb200_declined_ops(self.handle))
+
+    def kernel_paths(self):
+        values = [ctypes.c_ulonglong() for _ in range(5)]
+        self.lib.vitb200_kernel_path_counters.restype = None
+        self.lib.vitb200_kernel_path_counters.argtypes = \
+            [ctypes.c_void_p] + [ctypes.POINTER(ctypes.c_ulonglong)] * 5
+        self.lib.vitb200_kernel_path_counters(
+            self.handle, *[ctypes.byref(v) for v in values])
+        names = ["tensor_core_products", "wide_tile_products", "fma_products",
+                 "tensor_core_attention", "streaming_attention"]
         return {n: int(v.value) for n, v in zip(names, values)}
 
     def device_busy_ms(self, reset=False):
