@@ -186,12 +186,28 @@ void recycle(float *device, size_t bytes) {
     if (is_external(device)) {
         return;
     }
-    if (g_pooled_bytes + bytes <= kPoolLimitBytes) {
-        buffer_pool().emplace(bytes, device);
-        g_pooled_bytes += bytes;
-    } else {
+    if (bytes > kPoolLimitBytes) {
         cudaFree(device);
+        return;
     }
+    // Over the limit the pool gives up buffers of other sizes first: what is
+    // being released now is what the running workload allocates and will ask
+    // for again, while the rest may be left over from a model that is gone.
+    auto &pool = buffer_pool();
+    while (g_pooled_bytes + bytes > kPoolLimitBytes && !pool.empty()) {
+        auto victim = pool.begin();
+        if (victim->first == bytes) {
+            victim = pool.upper_bound(bytes);
+            if (victim == pool.end()) {
+                victim = pool.begin();
+            }
+        }
+        cudaFree(victim->second);
+        g_pooled_bytes -= victim->first;
+        pool.erase(victim);
+    }
+    pool.emplace(bytes, device);
+    g_pooled_bytes += bytes;
 }
 
 int reader_slot(const LazyDefinition *lazy, const Region *region) {
