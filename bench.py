@@ -464,10 +464,13 @@ def measure(vh, backend, host_lib, workload, config, batch, micro_batches, steps
     barrier()
     counters = backend.memory_counters()
     start = time.perf_counter()
+    step_ends = []
     for _ in range(steps):
         loss = step()
+        step_ends.append(time.perf_counter())
     barrier()
     e2e_seconds = time.perf_counter() - start
+    step_ms = [round(1e3 * (b - a), 3) for a, b in zip([start] + step_ends, step_ends)]
     moved = backend.memory_counters()
     h2d_per_step = (moved["h2d_bytes"] - counters["h2d_bytes"]) / steps
     d2h_per_step = (moved["d2h_bytes"] - counters["d2h_bytes"]) / steps
@@ -580,7 +583,8 @@ def measure(vh, backend, host_lib, workload, config, batch, micro_batches, steps
         "e2e": {"value": e2e_value, "unit": "images/s",
                 "h2d_bytes_per_step": h2d_per_step,
                 "d2h_bytes_per_step": d2h_per_step,
-                "ms_per_step": 1e3 * e2e_seconds / steps},
+                "ms_per_step": 1e3 * e2e_seconds / steps,
+                "ms_of_each_step_on_rank0": step_ms},
         "gpu_launches": launches,
         "declined_ops": declined,
         "kernel_paths": paths,
@@ -702,7 +706,7 @@ def main():
         torch.cuda.empty_cache()
         line["cfg5"] = measure(
             vh, backend, host_lib, "cfg5", cfg5_config, cfg5_batch,
-            micro_batch_count("cfg5", cfg5_batch), args.cfg5_steps, 2, rank,
+            micro_batch_count("cfg5", cfg5_batch), args.cfg5_steps, 3, rank,
             local_rank, world, tf32_peak)
     backend.disable()
     backend.dp_shutdown()
