@@ -103,6 +103,34 @@ void vitb200_kernel_path_counters(const CudaBackend *backend,
                                   unsigned long long *tensor_core_attention,
                                   unsigned long long *streaming_attention);
 
+/* Checkpoints straight from and into device memory, in the host's own file
+ * format ("CVITCKP" version 1: reference src/vit.c:1123-1215 writes it,
+ * :1217-1268 reads it), so files are interchangeable with vit_model_save /
+ * vit_model_load.  `config` is the host's ViTConfig as raw bytes (it is stored
+ * verbatim, and on load it must equal the stored one byte for byte, as in the
+ * reference's reader); `parameters` lists the model's parameters in the
+ * reference's order (src/vit.c:1144-1172: patch projection and bias, class
+ * token, positions, then per block the four matrices with their biases and
+ * the four normalisation vectors, then final gamma, beta, head and its bias).
+ * Values and both Adam moments go device -> page-locked staging -> file (and
+ * back) without touching the tensors' host mirrors or their ownership; step
+ * counters are host fields.  Loading leaves the tensors device-owned.
+ * 0 = success, -1 = failure (I/O error, wrong magic / version /
+ * configuration / element count).  vitb200_checkpoint_counters reports, for
+ * the last save, the bytes that came from device buffers and from host
+ * memory that held the current values. */
+struct vitb200_parameter;   /* include/vitb200_host_abi.h; the host's Parameter */
+int vitb200_checkpoint_save(CudaBackend *backend, const char *path,
+                            const void *config, size_t config_bytes,
+                            struct vitb200_parameter *const *parameters,
+                            size_t count);
+int vitb200_checkpoint_load(CudaBackend *backend, const char *path,
+                            const void *config, size_t config_bytes,
+                            struct vitb200_parameter *const *parameters,
+                            size_t count);
+void vitb200_checkpoint_counters(size_t *bytes_from_device,
+                                 size_t *bytes_from_host_memory);
+
 /* Makes a tensor buffer obtained through the backend allocator plainly
  * readable and writable by the host (copying it back from the device if
  * needed).  Required before passing it to read()/fread()/write()/fwrite(),
@@ -137,6 +165,15 @@ void vitb200_dp_counters(CudaBackend *backend,
  * backward pass completes them, and leave in a few ranges of at least 4 MiB
  * (counted here and in all_reduce_calls) instead of one call per tensor. */
 unsigned long long vitb200_dp_flat_ranges(CudaBackend *backend);
+/* 0 while the exchange is healthy.  Every synchronise asks NCCL for
+ * asynchronous errors (a peer that died, a transport failure); on the first
+ * one the communicator is aborted, so this rank's stream drains instead of
+ * waiting for the peer, the code is kept and returned here, and the optimiser
+ * slot declines from then on (the host must stop training: its gradients are
+ * incomplete).  What can be known on the host before a launch -- a rank that
+ * never joined, left or stalled -- is the caller's to check first; see
+ * ExchangeGroup in transformer-in-c_b200/vit_host.py and INTEGRATION.md. */
+int vitb200_dp_status(CudaBackend *backend);
 
 /* Gradient accumulation (no counterpart in the reference, whose train call
  * steps the optimiser after every batch).  Tells the backend that the next

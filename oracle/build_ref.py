@@ -97,7 +97,8 @@ def build(reference_root=None):
              os.path.join(reference_root, "tests", "test_device.c"), *core,
              "-L" + PACKAGE, "-lvitb200",
              "-Wl,-rpath,$ORIGIN/../../transformer-in-c_b200", "-lm"])
-        run(["gcc", *flags, "-o", os.path.join(OUT, "checkpoint_roundtrip"),
+        run(["gcc", *flags, "-I" + os.path.join(REPO, "include"), "-o",
+             os.path.join(OUT, "checkpoint_roundtrip"),
              os.path.join(REPO, "tests", "checkpoint_roundtrip.c"), *core,
              "-L" + PACKAGE, "-lvitb200",
              "-Wl,-rpath,$ORIGIN/../../transformer-in-c_b200", "-lm"])

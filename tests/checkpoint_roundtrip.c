@@ -13,9 +13,17 @@
  *     and two device models with the same contents must produce the same
  *     loss on the next step;
  *  4. load a checkpoint into a device model whose parameters currently live
- *     on the device (fread into protected pages).
+ *     on the device (fread into protected pages);
+ *  5. the direct path (vitb200_checkpoint_save / _load: device buffers ->
+ *     page-locked staging -> file and back): its file must be byte-identical
+ *     to the one the reference's writer produces for the same model, every
+ *     byte of it must have come straight from device buffers, the reference's
+ *     reader must accept it into a CPU model, and a device model loaded from
+ *     the reference's file through the direct reader must hold the same
+ *     contents and give the same loss on the next step.
  */
 #include "cuda_backend.h"
+#include "vitb200.h"
 #include "ops.h"
 #include "tensor.h"
 #include "vit.h"
@@ -68,6 +76,23 @@ static size_t collect(ViTModel *model, Parameter **list) {
     list[n++] = &model->classification_head.projection;
     list[n++] = &model->classification_head.bias;
     return n;
+}
+
+static int same_file(const char *a, const char *b) {
+    FILE *fa = fopen(a, "rb"), *fb = fopen(b, "rb");
+    int same = fa && fb;
+    size_t bytes = 0;
+    while (same) {
+        const int ca = fgetc(fa), cb = fgetc(fb);
+        same = ca == cb;
+        if (ca == EOF || cb == EOF) {
+            break;
+        }
+        ++bytes;
+    }
+    if (fa) fclose(fa);
+    if (fb) fclose(fb);
+    return same && bytes > 1000;
 }
 
 static int same_parameters(ViTModel *a, ViTModel *b) {
@@ -158,6 +183,57 @@ int main(int argc, char **argv) {
                                          0.1f, &loss_second) == 0);
     CHECK(loss_first == loss_second);
     CHECK(vit_model_save(&second, path) == 0);
+    ops_synchronize();
+
+    /* 5. The direct path.  One more step first, so that values and moments
+     * are device-owned when the file is written. */
+    char direct_path[1024];
+    snprintf(direct_path, sizeof(direct_path), "%s.direct", path);
+    CHECK(vit_model_train_batch_smoothed(&second, images, labels, BATCH,
+                                         &second_cache, 1e-3f, 0.05f, NULL,
+                                         0.1f, &loss_second) == 0);
+    Parameter *list[8 + 12 * 4];
+    const size_t listed = collect(&second, list);
+    CHECK(vitb200_checkpoint_save(backend, direct_path, &second.config,
+                                  sizeof(second.config),
+                                  (struct vitb200_parameter *const *)list,
+                                  listed) == 0);
+    size_t from_device = 0, from_host = 0, parameter_bytes = 0;
+    vitb200_checkpoint_counters(&from_device, &from_host);
+    for (size_t i = 0; i < listed; ++i) {
+        parameter_bytes += 3 * tensor_numel(&list[i]->value) * sizeof(float);
+    }
+    CHECK(from_device == parameter_bytes && from_host == 0);
+    CHECK(vit_model_save(&second, path) == 0);   /* the reference's writer */
+    CHECK(same_file(path, direct_path));
+    /* The reference's file through the direct reader into the other device
+     * model: same contents, same next loss. */
+    const size_t first_listed = collect(&first, list);
+    CHECK(vitb200_checkpoint_load(backend, path, &first.config,
+                                  sizeof(first.config),
+                                  (struct vitb200_parameter *const *)list,
+                                  first_listed) == 0);
+    CHECK(same_parameters(&first, &second));
+    CHECK(vit_model_train_batch_smoothed(&first, images, labels, BATCH,
+                                         &first_cache, 1e-3f, 0.05f, NULL, 0.1f,
+                                         &loss_first) == 0);
+    CHECK(vit_model_train_batch_smoothed(&second, images, labels, BATCH,
+                                         &second_cache, 1e-3f, 0.05f, NULL,
+                                         0.1f, &loss_second) == 0);
+    CHECK(loss_first == loss_second);
+    /* A file of the wrong configuration is refused. */
+    ViTConfig other = second.config;
+    other.layers += 1;
+    CHECK(vitb200_checkpoint_load(backend, path, &other, sizeof(other),
+                                  (struct vitb200_parameter *const *)list,
+                                  first_listed) == -1);
+    /* The direct writer's file of the current state, for the CPU model below. */
+    const size_t second_listed = collect(&second, list);
+    CHECK(vitb200_checkpoint_save(backend, path, &second.config,
+                                  sizeof(second.config),
+                                  (struct vitb200_parameter *const *)list,
+                                  second_listed) == 0);
+    remove(direct_path);
     ops_synchronize();
     cuda_backend_disable_device_execution(backend);
 

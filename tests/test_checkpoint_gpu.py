@@ -1,6 +1,9 @@
-"""The reference's checkpoint writer and reader (vit_model_save / vit_model_load,
-src/vit.c:1203-1259) on device-resident models: tests/checkpoint_roundtrip.c,
-built by oracle/build_ref.py against the reference's sources and libvitb200.so."""
+"""Checkpoints of device-resident models: the reference's own writer and reader
+(vit_model_save / vit_model_load, src/vit.c:1203-1259) working on tensor memory
+whose contents live on the device, and the direct device <-> file path
+(vitb200_checkpoint_save / _load), whose files must be byte-identical to the
+reference's.  The program is tests/checkpoint_roundtrip.c, built by
+oracle/build_ref.py against the reference's sources and libvitb200.so."""
 import os
 import subprocess
 

@@ -13,6 +13,7 @@
 #include "../../include/vitb200_dataset.h"
 
 #include "augmentation.h"
+#include "checkpoint.h"
 #include "coherence.h"
 #include "data_parallel.h"
 #include "dataset.h"
@@ -343,6 +344,18 @@ void settle_timers(CudaBackend *backend) {
     if (backend->span_open) {
         check(cudaEventRecord(backend->span_end, backend->stream),
               "cudaEventRecord");
+    }
+    if (backend->dp && dp_world(backend->dp) > 1) {
+        // With an exchange in flight the wait also watches the communicator:
+        // a failed peer shows up as an asynchronous NCCL error, and aborting
+        // the communicator then lets this stream drain.
+        unsigned spins = 0;
+        while (cudaStreamQuery(backend->stream) == cudaErrorNotReady) {
+            if ((++spins & 1023u) == 0 && dp_poll(backend->dp) != 0) {
+                break;
+            }
+        }
+        cudaGetLastError();
     }
     check(cudaStreamSynchronize(backend->stream), "cudaStreamSynchronize");
     if (const int code = gemm_tc_status()) {
@@ -2055,6 +2068,9 @@ int op_adamw_step_parameters(void *context,
     // exchange may move the gradients' device buffers, so it comes before the
     // table of pointers the kernels work from.)
     float inverse_world = 1.0f;
+    if (backend->dp && dp_status(backend->dp) != 0) {
+        return -1;   // the exchange has failed: nothing sensible to apply
+    }
     if (backend->dp && dp_world(backend->dp) > 1) {
         std::vector<const void *> host_grads(count);
         std::vector<float *> device_grads(count);
@@ -2823,6 +2839,40 @@ extern "C" void vitb200_kernel_path_counters(
     }
 }
 
+static CheckpointCounters g_last_checkpoint = {};
+
+extern "C" int vitb200_checkpoint_save(CudaBackend *backend, const char *path,
+                                       const void *config, size_t config_bytes,
+                                       vitb200_parameter *const *parameters,
+                                       size_t count) {
+    if (!cuda_backend_available(backend)) {
+        return -1;
+    }
+    flush_pending(backend);
+    g_last_checkpoint = CheckpointCounters{};
+    return checkpoint_save(path, config, config_bytes, parameters, count,
+                           backend->stream, &g_last_checkpoint);
+}
+
+extern "C" int vitb200_checkpoint_load(CudaBackend *backend, const char *path,
+                                       const void *config, size_t config_bytes,
+                                       vitb200_parameter *const *parameters,
+                                       size_t count) {
+    if (!cuda_backend_available(backend)) {
+        return -1;
+    }
+    flush_pending(backend);
+    settle_timers(backend);
+    return checkpoint_load(path, config, config_bytes, parameters, count,
+                           backend->stream);
+}
+
+extern "C" void vitb200_checkpoint_counters(size_t *bytes_from_device,
+                                            size_t *bytes_from_host_memory) {
+    if (bytes_from_device) *bytes_from_device = g_last_checkpoint.from_device;
+    if (bytes_from_host_memory) *bytes_from_host_memory = g_last_checkpoint.from_mirrors;
+}
+
 extern "C" int vitb200_make_host_coherent(const void *tensor_memory) {
     return coherent_make_host_owned(tensor_memory);
 }
@@ -2875,6 +2925,10 @@ extern "C" void vitb200_dp_counters(CudaBackend *backend,
                                     unsigned long long *bytes) {
     dp_counters(backend ? backend->dp : nullptr, all_reduce_calls,
                 overlapped_tensors, late_tensors, bytes);
+}
+
+extern "C" int vitb200_dp_status(CudaBackend *backend) {
+    return dp_status(backend ? backend->dp : nullptr);
 }
 
 extern "C" unsigned long long vitb200_dp_flat_ranges(CudaBackend *backend) {

@@ -536,6 +536,23 @@ bool coherent_place_device_buffer(const void *host_pointer, float *device,
     return true;
 }
 
+const float *coherent_current_device(const void *host_pointer,
+                                     cudaStream_t stream) {
+    Region *region = host_pointer ? find_base(host_pointer) : nullptr;
+    if (!region || region->owner != Owner::Device) {
+        return nullptr;   // not ours, or the mirror holds the current values
+    }
+    if (region->lazy) {
+        if (is_alias(*region)) {
+            return source_device(region->lazy, 0);
+        }
+        materialise_lazy(region->lazy, stream);
+    }
+    ensure_device_buffer(*region);
+    materialise_zero(*region, stream);
+    return region->device;
+}
+
 bool coherent_owns(const void *host_pointer) {
     return host_pointer && find_base(host_pointer) != nullptr;
 }

@@ -127,6 +127,14 @@ int coherent_make_host_owned(const void *host_pointer);
 int coherent_prepare_host_io(const void *pointer, size_t bytes,
                              bool host_writes);
 
+// Where the current contents of a mirror can be read without changing who
+// owns them: the device buffer (pending zero fills and definitions are
+// computed first, on `stream`), or nullptr when the mirror itself is current
+// (or the memory is not ours).  The pointer is valid for work enqueued on the
+// stream before the next call into this layer.
+const float *coherent_current_device(const void *host_pointer,
+                                     cudaStream_t stream);
+
 // Device memory owned by the caller in which buffers may be placed
 // (coherent_place_device_buffer): this layer never pools or frees it.
 // add = false withdraws a range registered earlier (by its base address).

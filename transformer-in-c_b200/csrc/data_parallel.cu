@@ -30,6 +30,8 @@ struct NcclApi {
                       cudaStream_t) = nullptr;
     int (*group_start)() = nullptr;
     int (*group_end)() = nullptr;
+    int (*comm_get_async_error)(NcclComm, int *) = nullptr;
+    int (*comm_abort)(NcclComm) = nullptr;
     const char *(*error_string)(int) = nullptr;
     bool loaded = false;
 };
@@ -55,6 +57,9 @@ NcclApi &nccl() {
         a.group_start = reinterpret_cast<decltype(a.group_start)>(find("ncclGroupStart"));
         a.group_end = reinterpret_cast<decltype(a.group_end)>(find("ncclGroupEnd"));
         a.error_string = reinterpret_cast<decltype(a.error_string)>(find("ncclGetErrorString"));
+        a.comm_get_async_error = reinterpret_cast<decltype(a.comm_get_async_error)>(
+            find("ncclCommGetAsyncError"));
+        a.comm_abort = reinterpret_cast<decltype(a.comm_abort)>(find("ncclCommAbort"));
         a.loaded = a.get_unique_id && a.comm_init_rank && a.comm_destroy &&
                    a.all_reduce && a.group_start && a.group_end;
         return a;
@@ -131,6 +136,7 @@ struct DataParallel {
     size_t complete_floats = 0;  // arena floats they cover
     size_t sent_floats = 0;      // arena floats handed to NCCL this step
     unsigned long long arena_ranges = 0;
+    int error = 0;   // first asynchronous NCCL error seen; the exchange is over then
 };
 
 namespace {
@@ -316,6 +322,32 @@ void dp_destroy(DataParallel *dp) {
 
 int dp_world(const DataParallel *dp) {
     return dp ? dp->world : 1;
+}
+
+int dp_poll(DataParallel *dp) {
+    if (!dp || dp->error || !dp->comm || !nccl().comm_get_async_error) {
+        return dp ? dp->error : 0;
+    }
+    int status = kNcclSuccess;
+    if (nccl().comm_get_async_error(dp->comm, &status) != kNcclSuccess) {
+        status = 1;   // unhandled error querying the communicator
+    }
+    if (status != kNcclSuccess) {
+        fprintf(stderr, "vitb200: the gradient exchange failed: %s\n",
+                nccl().error_string ? nccl().error_string(status) : "NCCL error");
+        dp->error = status;
+        // Frees the communicator's resources and ends its kernels, so that
+        // this rank's stream drains instead of waiting for a peer for ever.
+        if (nccl().comm_abort) {
+            nccl().comm_abort(dp->comm);
+        }
+        dp->comm = nullptr;
+    }
+    return dp->error;
+}
+
+int dp_status(const DataParallel *dp) {
+    return dp ? dp->error : 0;
 }
 
 void dp_gradient_produced(DataParallel *dp, const void *host_grad,

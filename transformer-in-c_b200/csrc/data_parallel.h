@@ -44,6 +44,14 @@ DataParallel *dp_create(int rank, int world, const void *id128,
 void dp_destroy(DataParallel *dp);
 int dp_world(const DataParallel *dp);
 
+// Asks NCCL whether the communicator has failed asynchronously (a peer died,
+// a transport error).  On the first error the communicator is aborted, which
+// ends its kernels, and the error code is kept: dp_status() returns it from
+// then on and the optimiser slot declines.  Cheap; called at every
+// synchronise.  Returns the kept code (0 = healthy).
+int dp_poll(DataParallel *dp);
+int dp_status(const DataParallel *dp);
+
 // Called after the op that wrote `device_grad` (the gradient whose host mirror
 // is `host_grad`, `count` floats) has been enqueued on the compute stream.
 // Does nothing for buffers that are not known parameter gradients.

@@ -250,6 +250,14 @@ class Backend:
     def dp_shutdown(self):
         self.lib.vitb200_dp_shutdown(self.handle)
 
+    def dp_status(self):
+        """0, or the error NCCL reported asynchronously for the exchange (it
+        is polled at every synchronise; after an error the communicator has
+        been aborted and the backend no longer exchanges anything)."""
+        self.lib.vitb200_dp_status.restype = ctypes.c_int
+        self.lib.vitb200_dp_status.argtypes = [ctypes.c_void_p]
+        return int(self.lib.vitb200_dp_status(self.handle))
+
     def dp_counters(self):
         values = [ctypes.c_ulonglong() for _ in range(4)]
         self.lib.vitb200_dp_counters(self.handle,
@@ -623,6 +631,92 @@ class VitHost:
             raise KeyError(name)
         array = np.ctypeslib.as_array(data, shape=(int(count),))
         return array.reshape(int(rows.value), int(cols.value)).copy()
+
+
+class ExchangeError(RuntimeError):
+    """A rank of the data-parallel group is missing, late or gone."""
+
+
+class ExchangeGroup:
+    """Host-side failure detection around the gradient exchange.
+
+    NCCL's collectives (and ncclCommInitRank itself) block until every rank
+    takes part, so a rank that never starts, or leaves between two steps,
+    would leave the others waiting inside a kernel on their GPUs.  Everything
+    that can be learnt on the host is therefore checked on the host first,
+    through a small key/value store every rank can reach (anything with the
+    set / get / wait / check interface of torch.distributed's TCPStore or
+    FileStore):
+
+      rendezvous(make_id)   rank 0 publishes the 128 id bytes, every rank
+                            announces itself, and nobody proceeds to
+                            Backend.dp_init before all ranks have, within
+                            `timeout` seconds; otherwise ExchangeError names
+                            what is missing and no collective has been entered
+      before_step(step)     each rank records the step it is about to launch
+                            and checks, before launching anything, that no
+                            rank has announced its departure and that every
+                            rank has reached the previous step within
+                            `timeout` seconds
+      leave()               announces a departure; a rank calls it between
+                            steps, with none of its kernels or collectives in
+                            flight (after a synchronise)
+
+    Nothing here touches a GPU."""
+
+    def __init__(self, store, rank, world, timeout=30.0, prefix="vitb200"):
+        self.store, self.rank, self.world = store, int(rank), int(world)
+        self.timeout, self.prefix = float(timeout), prefix
+
+    def _key(self, *parts):
+        return "/".join([self.prefix, *[str(p) for p in parts]])
+
+    def _wait(self, keys, what):
+        import datetime
+        try:
+            self.store.wait(keys, datetime.timedelta(seconds=self.timeout))
+        except Exception as error:   # the stores raise their own timeout types
+            missing = [k for k in keys if not self.store.check([k])]
+            raise ExchangeError(
+                f"rank {self.rank}: {what} within {self.timeout:g} s "
+                f"(missing: {', '.join(missing) or 'unknown'})") from error
+
+    def rendezvous(self, make_id):
+        if self.rank == 0:
+            self.store.set(self._key("id"), bytes(make_id()))
+        self._wait([self._key("id")], "rank 0 never published the exchange id")
+        unique_id = bytes(self.store.get(self._key("id")))
+        self.store.set(self._key("joined", self.rank), b"1")
+        self._wait([self._key("joined", r) for r in range(self.world)],
+                   "not every rank joined the exchange")
+        return unique_id
+
+    def leave(self):
+        self.store.set(self._key("left", self.rank), b"1")
+
+    def before_step(self, step):
+        import time
+        self.store.set(self._key("step", self.rank), str(int(step)).encode())
+        deadline = time.monotonic() + self.timeout
+        for peer in range(self.world):
+            if peer == self.rank:
+                continue
+            while True:
+                if self.store.check([self._key("left", peer)]):
+                    raise ExchangeError(
+                        f"rank {self.rank}: rank {peer} has left the exchange "
+                        f"(noticed before step {step})")
+                reached = -1
+                if self.store.check([self._key("step", peer)]):
+                    reached = int(bytes(self.store.get(self._key("step", peer))))
+                if reached >= step - 1:
+                    break
+                if time.monotonic() > deadline:
+                    raise ExchangeError(
+                        f"rank {self.rank}: rank {peer} has not reached step "
+                        f"{step - 1} within {self.timeout:g} s (last seen at "
+                        f"step {reached})")
+                time.sleep(0.01)
 
 
 def synthetic_batch(batch, height, width, classes, seed):
