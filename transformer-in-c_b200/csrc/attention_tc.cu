@@ -298,7 +298,7 @@ attention_tc_kernel(const __grid_constant__ AttnMaps maps, const AttnParams p) {
             // instruction by instruction).  The descriptors are built once
             // (high word constant, low word = address field + leading offset)
             // and stepped by adding compile-time constants to the low word.
-            const bool leader = elect_one();
+            const uint32_t leader = elect_one() ? 1u : 0u;
             const uint32_t tmem_base = __shfl_sync(kFullMask, tmem_base_any, 0);
             const uint32_t update_instruction = tf32_instruction(kTileRows, HD, 0, 1);
             const uint32_t full_instruction = tf32_instruction(kTileRows, N, 0, 0);
@@ -346,8 +346,8 @@ attention_tc_kernel(const __grid_constant__ AttnMaps maps, const AttnParams p) {
 #pragma unroll
                     for (int ks = 0; ks < HD / 8; ++ks) {
                         constexpr int kRowBlock = kTileRows * 128, kColBlock = N * 128;
-                        if (leader) tcgen05_mma_tf32(
-                            d,
+                        tcgen05_mma_tf32_if(
+                            leader, d,
                             descriptor(a_low + (((ks / 4) * kRowBlock + (ks % 4) * 32) >> 4),
                                        kHighKMajor),
                             descriptor(b_low + (((ks / 4) * kColBlock + (ks % 4) * 32) >> 4),
@@ -355,16 +355,12 @@ attention_tc_kernel(const __grid_constant__ AttnMaps maps, const AttnParams p) {
                             instruction, ks > 0 ? 1u : 0u);
                     }
                 }
-                if (leader) {
-                    tcgen05_commit(&bars[kSsEmpty + s]);
-                    tcgen05_commit(&bars[kScoresFull + s]);
-                }
+                tcgen05_commit_if(leader, &bars[kSsEmpty + s]);
+                tcgen05_commit_if(leader, &bars[kScoresFull + s]);
                 if (++scores_j == tiles) {
                     // The item's resident operands have been read for the
                     // last time once these products retire.
-                    if (leader) {
-                        tcgen05_commit(&bars[kResidentEmpty + stage]);
-                    }
+                    tcgen05_commit_if(leader, &bars[kResidentEmpty + stage]);
                     scores_j = 0;
                     ++scores_it;
                 }
@@ -394,15 +390,13 @@ attention_tc_kernel(const __grid_constant__ AttnMaps maps, const AttnParams p) {
                                        accumulator * HD;
                     const uint32_t a = tmem_base + s * kBufferColumns + u * N;
                     const uint32_t b_low = ts_low + ((s * kTsStage + u * kOperandBytes) >> 4);
-                    if (leader) {
-                        tcgen05_mma_tf32_tmem_a(d, a, descriptor(b_low, kHighBox32),
-                                                update_instruction, first ? 0u : 1u);
-                    }
+                    tcgen05_mma_tf32_tmem_a_if(leader, d, a, descriptor(b_low, kHighBox32),
+                                               update_instruction, first ? 0u : 1u);
 #pragma unroll
                     for (int ks = 1; ks < N / 8; ++ks) {
-                        if (leader && ks < steps) {
-                            tcgen05_mma_tf32_tmem_a(
-                                d, a + 8 * ks,
+                        if (ks < steps) {
+                            tcgen05_mma_tf32_tmem_a_if(
+                                leader, d, a + 8 * ks,
                                 descriptor(b_low + (((ks / 4) * (kBlocks * 4096) +
                                                      (ks % 4) * 1024) >> 4),
                                            kHighBox32),
@@ -410,14 +404,10 @@ attention_tc_kernel(const __grid_constant__ AttnMaps maps, const AttnParams p) {
                         }
                     }
                 }
-                if (leader) {
-                    tcgen05_commit(&bars[kTsEmpty + s]);
-                    tcgen05_commit(&bars[kUpdateDone + s]);
-                }
+                tcgen05_commit_if(leader, &bars[kTsEmpty + s]);
+                tcgen05_commit_if(leader, &bars[kUpdateDone + s]);
                 if (++update_j == tiles) {
-                    if (leader) {
-                        tcgen05_commit(&bars[kAllDone + set]);
-                    }
+                    tcgen05_commit_if(leader, &bars[kAllDone + set]);
                     update_j = 0;
                     ++update_it;
                 }

@@ -30,6 +30,8 @@ constexpr size_t kBlockBytes = size_t(8) << 20;
 struct Staging {
     char *block[2] = {nullptr, nullptr};
     cudaEvent_t done[2] = {nullptr, nullptr};
+    bool busy[2] = {false, false};   // an upload from the block may be in flight
+    int next = 0;                    // block the next upload stages in
     bool ok = false;
     Staging() {
         ok = cudaHostAlloc(reinterpret_cast<void **>(&block[0]), kBlockBytes,
@@ -88,13 +90,15 @@ bool write_tensor(FILE *file, const float *device, const void *host, size_t byte
 
 bool read_tensor(FILE *file, float *device, size_t bytes, Staging &staging,
                  cudaStream_t stream) {
+    // The two blocks alternate across tensors as well: the file is read into
+    // one while the copy engine still empties the other.
     char *target = reinterpret_cast<char *>(device);
     size_t done = 0;
-    int slot = 0;
-    bool used[2] = {false, false};
     while (done < bytes) {
         const size_t chunk = bytes - done < kBlockBytes ? bytes - done : kBlockBytes;
-        if (used[slot] && cudaEventSynchronize(staging.done[slot]) != cudaSuccess) {
+        const int slot = staging.next;
+        if (staging.busy[slot] &&
+            cudaEventSynchronize(staging.done[slot]) != cudaSuccess) {
             return false;
         }
         if (fread(staging.block[slot], 1, chunk, file) != chunk ||
@@ -103,9 +107,9 @@ bool read_tensor(FILE *file, float *device, size_t bytes, Staging &staging,
             cudaEventRecord(staging.done[slot], stream) != cudaSuccess) {
             return false;
         }
-        used[slot] = true;
+        staging.busy[slot] = true;
+        staging.next = slot ^ 1;
         done += chunk;
-        slot ^= 1;
     }
     return true;
 }

@@ -156,20 +156,52 @@ __device__ __forceinline__ void tcgen05_mma_tf32(uint32_t tmem_d, uint64_t desc_
         : "memory");
 }
 
-// The same with the A operand in tensor memory: 128 lanes x 8 columns of
-// 32-bit cells per instruction, reduction index along the columns.
-__device__ __forceinline__ void tcgen05_mma_tf32_tmem_a(uint32_t tmem_d,
-                                                        uint32_t tmem_a,
-                                                        uint64_t desc_b,
-                                                        uint32_t idesc,
-                                                        uint32_t accumulate) {
+// The same, issued only by lanes whose `issue` flag is set.  The whole warp
+// executes the statement (no branch around it), so operands that every lane
+// computes alike stay in uniform registers, which is where the instruction
+// reads them from.
+__device__ __forceinline__ void tcgen05_mma_tf32_if(uint32_t issue, uint32_t tmem_d,
+                                                    uint64_t desc_a, uint64_t desc_b,
+                                                    uint32_t idesc,
+                                                    uint32_t accumulate) {
     asm volatile(
         "{\n\t"
-        ".reg .pred p;\n\t"
+        ".reg .pred p, q;\n\t"
         "setp.ne.b32 p, %4, 0;\n\t"
-        "tcgen05.mma.cta_group::1.kind::tf32 [%0], [%1], %2, %3, p;\n\t"
+        "setp.ne.b32 q, %5, 0;\n\t"
+        "@q tcgen05.mma.cta_group::1.kind::tf32 [%0], %1, %2, %3, p;\n\t"
         "}" ::"r"(tmem_d),
-        "r"(tmem_a), "l"(desc_b), "r"(idesc), "r"(accumulate)
+        "l"(desc_a), "l"(desc_b), "r"(idesc), "r"(accumulate), "r"(issue)
+        : "memory");
+}
+
+// A operand in tensor memory: 128 lanes x 8 columns of 32-bit cells per
+// instruction, reduction index along the columns.
+__device__ __forceinline__ void tcgen05_mma_tf32_tmem_a_if(uint32_t issue,
+                                                           uint32_t tmem_d,
+                                                           uint32_t tmem_a,
+                                                           uint64_t desc_b,
+                                                           uint32_t idesc,
+                                                           uint32_t accumulate) {
+    asm volatile(
+        "{\n\t"
+        ".reg .pred p, q;\n\t"
+        "setp.ne.b32 p, %4, 0;\n\t"
+        "setp.ne.b32 q, %5, 0;\n\t"
+        "@q tcgen05.mma.cta_group::1.kind::tf32 [%0], [%1], %2, %3, p;\n\t"
+        "}" ::"r"(tmem_d),
+        "r"(tmem_a), "l"(desc_b), "r"(idesc), "r"(accumulate), "r"(issue)
+        : "memory");
+}
+
+__device__ __forceinline__ void tcgen05_commit_if(uint32_t issue, uint64_t *bar) {
+    asm volatile(
+        "{\n\t"
+        ".reg .pred q;\n\t"
+        "setp.ne.b32 q, %1, 0;\n\t"
+        "@q tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];\n\t"
+        "}" ::"r"(smem_address(bar)),
+        "r"(issue)
         : "memory");
 }
 
