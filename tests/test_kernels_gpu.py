@@ -78,7 +78,8 @@ def test_gemm_fp32_forward_and_backward(lib, m, k, n):
     (1000, 512, 128), (4096, 128, 512), (333, 36, 44), (102400, 128, 128),
     (257, 1024, 256), (1568, 16, 128), (300, 16, 48), (100, 48, 16),
     (16, 16, 16), (50176, 16, 128), (1024, 256, 768), (300, 512, 512),
-    (2048, 256, 256), (4000, 1024, 256), (777, 288, 512),
+    (2048, 256, 256), (4000, 1024, 256), (777, 288, 512), (5000, 512, 2048),
+    (513, 512, 1536), (256, 256, 256), (39 * 256 + 7, 384, 1536),
 ])
 def test_gemm_tf32_tensor_cores(lib, m, k, n):
     """tcgen05 kind::tf32 path: operands keep 10 mantissa bits, accumulation is

@@ -56,6 +56,9 @@ constexpr int kOperandBytes = kTileM * kBlockK * 4;   // 16 KiB
 constexpr int kMaxStages = 6;
 constexpr int kSmemLimit = 227 * 1024 - 1024;   // leave room for static shared memory
 constexpr int kThreads = 192;
+// The tall tile has a group of four epilogue warps for each of its two
+// accumulators, so that both drain at the same time.
+constexpr int kThreadsTall = 320;
 constexpr int kBarrierBytes = 256;   // 2 x kMaxStages + 4 mbarriers, TMEM slot
 
 using namespace tc;
@@ -96,10 +99,18 @@ constexpr int kGeluSlope = 3;
 // compute-bound shapes (K >= 256) need from shared memory.  The launch code
 // guarantees one CTA per SM for it through the shared-memory request, so the
 // two allocations can never wait for each other.
+// TILE_M = 256 (with TILE_N = 256): the tile is two 128-row halves, one
+// accumulator each (all 512 columns), both multiplied by the same B tile, so
+// a CTA fetches (256 + 256) x K operand values for 256 x 256 outputs: a third
+// less operand traffic from L2 per multiply-add than the 128 x 256 tile, which
+// is what bounds the compute-bound shapes.  The accumulators are not
+// double-buffered across tiles then; instead the halves are: the epilogue
+// drains half 0 while the last MMAs of half 1 run, and the next tile's MMAs
+// start on half 0 while half 1 is still being drained.
 // SECOND is the epilogue variant (0 or a kSecond... / kGeluSlope constant): a
 // compile-time choice, so that no variant pays for another's registers.
-template <int TILE_N, int SECOND>
-__global__ void __launch_bounds__(kThreads)
+template <int TILE_M, int TILE_N, int SECOND>
+__global__ void __launch_bounds__(TILE_M == 2 * kTileM ? kThreadsTall : kThreads)
 gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a,
                const __grid_constant__ CUtensorMap map_b,
                const __grid_constant__ CUtensorMap map_d,
@@ -109,8 +120,12 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a,
     // padding (two CTAs with three stages each fill the SM to the last KiB):
     //   [stages x 32 KiB operand tiles][epilogue staging][barriers]
     extern __shared__ __align__(1024) uint8_t smem[];
-    constexpr int kStageBytes = kOperandBytes + TILE_N * kBlockK * 4;
+    constexpr int kHalves = TILE_M / kTileM;   // accumulators per tile
+    constexpr int kABytes = TILE_M * kBlockK * 4;
+    constexpr int kStageBytes = kABytes + TILE_N * kBlockK * 4;
     constexpr int kTmemColumns = 2 * TILE_N;
+    static_assert(TILE_M == kTileM || (TILE_M == 2 * kTileM && SECOND == 0),
+                  "the tall tile has the plain epilogue only");
     const int kStages = p.stages;
     uint8_t *staging = smem + kStages * kStageBytes;
     uint64_t *full_bar = reinterpret_cast<uint64_t *>(staging + p.staging_bytes);
@@ -165,7 +180,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a,
             int fill = 0;   // k-blocks loaded so far, across items
             for (int item = blockIdx.x; item < items && ok; item += gridDim.x) {
                 const int tile = item % tiles;
-                const int m0 = (tile / p.n_tiles) * kTileM;
+                const int m0 = (tile / p.n_tiles) * TILE_M;
                 const int n0 = (tile % p.n_tiles) * TILE_N;
                 const int kb_begin = (item / tiles) * p.k_blocks_per_split;
                 const int kb_end = min(p.k_blocks, kb_begin + p.k_blocks_per_split);
@@ -178,15 +193,16 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a,
                         break;
                     }
                     uint8_t *a_tile = smem + s * kStageBytes;
-                    uint8_t *b_tile = a_tile + kOperandBytes;
+                    uint8_t *b_tile = a_tile + kABytes;
                     const int k0 = kb * kBlockK;
                     mbarrier_expect_tx(&full_bar[s], kStageBytes);
                     if (p.a_mn_major) {
-                        for (int j = 0; j < 4; ++j) {
+                        for (int j = 0; j < TILE_M / 32; ++j) {
                             tma_load_2d(a_tile + j * 4096, &map_a, m0 + 32 * j, k0,
                                         &full_bar[s]);
                         }
                     } else {
+                        // One box of TILE_M rows (the map's box height).
                         tma_load_2d(a_tile, &map_a, k0, m0, &full_bar[s]);
                     }
                     if (p.b_mn_major) {
@@ -229,16 +245,10 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a,
                 const int tile_splits = item / tiles;
                 const int kb_begin = tile_splits * p.k_blocks_per_split;
                 const int kb_end = min(p.k_blocks, kb_begin + p.k_blocks_per_split);
-                const int buffer = local & 1;
-                const uint32_t buffer_phase = (local >> 1) & 1;
-                // The epilogue must have emptied this accumulator buffer.
-                ok = mbarrier_wait(&tmem_empty_bar[buffer], buffer_phase ^ 1);
-                if (!ok) {
-                    atomicExch(p.status, 4);
-                    break;
-                }
-                tcgen05_fence_after();
-                const uint32_t accumulator = tmem_base + buffer * TILE_N;
+                // One accumulator per tile, alternating between tiles; or, for
+                // the tall tile, one per 128-row half, both used by every tile.
+                const uint32_t buffer_phase =
+                    kHalves == 2 ? (local & 1) : ((local >> 1) & 1);
                 for (int kb = kb_begin; kb < kb_end; ++kb, ++drain) {
                     const int s = drain % kStages;
                     const uint32_t phase = (drain / kStages) & 1;
@@ -249,20 +259,41 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a,
                     }
                     tcgen05_fence_after();
                     const uint32_t a_base = smem_address(smem + s * kStageBytes);
-                    const uint32_t b_base = a_base + kOperandBytes;
+                    const uint32_t b_base = a_base + kABytes;
 #pragma unroll
-                    for (int ks = 0; ks < kBlockK / kMmaK; ++ks) {
-                        const uint64_t da = operand_descriptor(
-                            a_base + ks * a_step, a_lead, a_stride, a_layout);
-                        const uint64_t db = operand_descriptor(
-                            b_base + ks * b_step, b_lead, b_stride, b_layout);
-                        tcgen05_mma_tf32(accumulator, da, db, idesc,
-                                         (kb > kb_begin || ks > 0) ? 1u : 0u);
+                    for (int h = 0; h < kHalves; ++h) {
+                        const int buffer = kHalves == 2 ? h : (local & 1);
+                        if (kb == kb_begin) {
+                            // The epilogue must have emptied this accumulator.
+                            ok = mbarrier_wait(&tmem_empty_bar[buffer],
+                                               buffer_phase ^ 1);
+                            if (!ok) {
+                                atomicExch(p.status, 4);
+                                break;
+                            }
+                            tcgen05_fence_after();
+                        }
+                        const uint32_t accumulator = tmem_base + buffer * TILE_N;
+#pragma unroll
+                        for (int ks = 0; ks < kBlockK / kMmaK; ++ks) {
+                            const uint64_t da = operand_descriptor(
+                                a_base + h * kOperandBytes + ks * a_step, a_lead,
+                                a_stride, a_layout);
+                            const uint64_t db = operand_descriptor(
+                                b_base + ks * b_step, b_lead, b_stride, b_layout);
+                            tcgen05_mma_tf32(accumulator, da, db, idesc,
+                                             (kb > kb_begin || ks > 0) ? 1u : 0u);
+                        }
+                        if (kb == kb_end - 1) {
+                            // This half is complete: its rows can leave while
+                            // the other half's last products still run.
+                            tcgen05_commit(&tmem_full_bar[buffer]);
+                        }
+                    }
+                    if (!ok) {
+                        break;
                     }
                     tcgen05_commit(&empty_bar[s]);
-                }
-                if (ok) {
-                    tcgen05_commit(&tmem_full_bar[buffer]);
                 }
             }
         }
@@ -400,16 +431,23 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a,
         // Per warp: two 4 KiB blocks (one output double-buffered, or one buffer
         // for each of two outputs), or a single block when the load ring was
         // given the space instead.
-        const int buffers = outputs == 2 ? 1 : p.staging_bytes / (4 * 4096);
-        uint8_t *my_staging = staging + quarter * (p.staging_bytes / 4);
+        // The tall tile: warps 2-5 drain the upper half's accumulator, warps
+        // 6-9 the lower half's, each warp through one 4 KiB block.
+        const int half = kHalves == 2 ? (warp - 2) >> 2 : 0;
+        const int buffers =
+            kHalves == 2 ? 1 : (outputs == 2 ? 1 : p.staging_bytes / (4 * 4096));
+        uint8_t *my_staging = kHalves == 2
+            ? staging + (warp - 2) * 4096
+            : staging + quarter * (p.staging_bytes / 4);
         int local = 0;
         int stored = 0;   // blocks handed to TMA so far (selects the buffer)
         for (int item = blockIdx.x; item < items; item += gridDim.x, ++local) {
             const int tile = item % tiles;
-            const int m0 = (tile / p.n_tiles) * kTileM + quarter * 32;
+            const int m0 = (tile / p.n_tiles) * TILE_M + half * kTileM + quarter * 32;
             const int n0 = (tile % p.n_tiles) * TILE_N;
-            const int buffer = local & 1;
-            const uint32_t buffer_phase = (local >> 1) & 1;
+            const int buffer = kHalves == 2 ? half : (local & 1);
+            const uint32_t buffer_phase =
+                kHalves == 2 ? (local & 1) : ((local >> 1) & 1);
             ok = mbarrier_wait(&tmem_full_bar[buffer], buffer_phase);
             ok = __all_sync(0xffffffffu, ok);   // keep the warp in step
             if (!ok) {
@@ -730,11 +768,12 @@ int launch_gemm_tc(const TcGemm &g, cudaStream_t stream) {
     static bool configured = false;
     if (!configured) {
         const void *kernels[] = {
-            reinterpret_cast<const void *>(gemm_tc_kernel<128, 0>),
-            reinterpret_cast<const void *>(gemm_tc_kernel<128, kSecondGelu>),
-            reinterpret_cast<const void *>(gemm_tc_kernel<128, kSecondResidual>),
-            reinterpret_cast<const void *>(gemm_tc_kernel<128, kGeluSlope>),
-            reinterpret_cast<const void *>(gemm_tc_kernel<256, 0>)};
+            reinterpret_cast<const void *>(gemm_tc_kernel<128, 128, 0>),
+            reinterpret_cast<const void *>(gemm_tc_kernel<128, 128, kSecondGelu>),
+            reinterpret_cast<const void *>(gemm_tc_kernel<128, 128, kSecondResidual>),
+            reinterpret_cast<const void *>(gemm_tc_kernel<128, 128, kGeluSlope>),
+            reinterpret_cast<const void *>(gemm_tc_kernel<128, 256, 0>),
+            reinterpret_cast<const void *>(gemm_tc_kernel<256, 256, 0>)};
         for (const void *kernel : kernels) {
             if (cudaFuncSetAttribute(kernel,
                                      cudaFuncAttributeMaxDynamicSharedMemorySize,
@@ -755,6 +794,20 @@ int launch_gemm_tc(const TcGemm &g, cudaStream_t stream) {
         wide = g.n >= 256;
     }
     const int tile_n = wide ? 256 : kTileN;
+    // Tall tiles (256 x 256, two accumulator halves) on top of that when there
+    // are at least two full row tiles: a third less operand traffic from L2.
+    static const int forced_tile_m =
+        getenv("VITB200_TC_TILE_M") ? atoi(getenv("VITB200_TC_TILE_M")) : 0;
+    // (Not for the shortest reductions, where the double-buffered 128 x 256
+    // tile hides its epilogue completely and measured a few percent better.)
+    const bool long_enough = g.accumulate || g.k >= 384;
+    // A last row tile that is half empty costs a full one: only where that
+    // is a small share of the rows.
+    const bool fits = g.m % (2 * kTileM) == 0 || g.m % (2 * kTileM) > kTileM ||
+                      g.m >= 16 * kTileM;
+    const bool tall = wide && g.m >= 2 * kTileM && forced_tile_m != 128 &&
+                      ((long_enough && fits) || forced_tile_m == 256);
+    const int tile_m = tall ? 2 * kTileM : kTileM;
     CUtensorMap map_a, map_b, map_d;
     // K-major operand: rows = output index, inner = reduction index.
     // MN-major operand: rows = reduction index, inner = output index.
@@ -762,7 +815,7 @@ int launch_gemm_tc(const TcGemm &g, cudaStream_t stream) {
     const CUtensorMapSwizzle chunks32 = CU_TENSOR_MAP_SWIZZLE_128B_ATOM_32B;
     const bool ok_a = g.a_mn_major
         ? tensor_map(g.a, g.m, g.k, g.lda, 32, 32, chunks32, true, &map_a)
-        : tensor_map(g.a, g.k, g.m, g.lda, 32, kTileM, chunks16, true, &map_a);
+        : tensor_map(g.a, g.k, g.m, g.lda, 32, tile_m, chunks16, true, &map_a);
     const bool ok_b = g.b_mn_major
         ? tensor_map(g.b, g.n, g.k, g.ldb, 32, 32, chunks32, true, &map_b)
         : tensor_map(g.b, g.k, g.n, g.ldb, 32, tile_n, chunks16, true, &map_b);
@@ -784,7 +837,7 @@ int launch_gemm_tc(const TcGemm &g, cudaStream_t stream) {
     p.n = g.n;
     p.k_blocks = (g.k + kBlockK - 1) / kBlockK;
     p.n_tiles = (g.n + tile_n - 1) / tile_n;
-    const int m_tiles = (g.m + kTileM - 1) / kTileM;
+    const int m_tiles = (g.m + tile_m - 1) / tile_m;
     p.m_tiles = m_tiles;
     const int tiles = m_tiles * p.n_tiles;
     // Two persistent CTAs per SM, each with a 2-stage load ring and 32 KiB of
@@ -818,7 +871,7 @@ int launch_gemm_tc(const TcGemm &g, cudaStream_t stream) {
         // One CTA per SM (it owns all of tensor memory): four 48 KiB stages
         // and double-buffered staging, 224 KiB.
         ctas_per_sm = 1;
-        p.stages = 4;
+        p.stages = tall ? 3 : 4;   // 64 KiB stages when the tile is tall
         staging_bytes = 2 * kOperandBytes;
     }
     if (forced_staging == 1 && !(g.d2 && g.residual)) {
@@ -875,7 +928,7 @@ int launch_gemm_tc(const TcGemm &g, cudaStream_t stream) {
     // One persistent CTA per SM (the shared-memory ring fills an SM), fewer
     // when there is less work than SMs.
     const long long items = (long long)tiles * splits;
-    const int stage_bytes = kOperandBytes + tile_n * kBlockK * 4;
+    const int stage_bytes = (tile_m + tile_n) * kBlockK * 4;
     const int smem_bytes = p.stages * stage_bytes + staging_bytes + kBarrierBytes;
     const unsigned grid = unsigned(items < slots ? items : slots);
     if (g.column_partials && grid > unsigned(kGemmPartialRows)) {
@@ -889,20 +942,23 @@ int launch_gemm_tc(const TcGemm &g, cudaStream_t stream) {
             return -1;
         }
     }
-    if (wide) {
-        gemm_tc_kernel<256, 0><<<grid, kThreads, smem_bytes, stream>>>(
+    if (tall) {
+        gemm_tc_kernel<256, 256, 0><<<grid, kThreadsTall, smem_bytes, stream>>>(
+            map_a, map_b, map_d, map_d2, p);
+    } else if (wide) {
+        gemm_tc_kernel<128, 256, 0><<<grid, kThreads, smem_bytes, stream>>>(
             map_a, map_b, map_d, map_d2, p);
     } else if (second == kSecondGelu) {
-        gemm_tc_kernel<128, kSecondGelu><<<grid, kThreads, smem_bytes, stream>>>(
+        gemm_tc_kernel<128, 128, kSecondGelu><<<grid, kThreads, smem_bytes, stream>>>(
             map_a, map_b, map_d, map_d2, p);
     } else if (second == kSecondResidual) {
-        gemm_tc_kernel<128, kSecondResidual><<<grid, kThreads, smem_bytes, stream>>>(
-            map_a, map_b, map_d, map_d2, p);
+        gemm_tc_kernel<128, 128, kSecondResidual>
+            <<<grid, kThreads, smem_bytes, stream>>>(map_a, map_b, map_d, map_d2, p);
     } else if (second == kGeluSlope) {
-        gemm_tc_kernel<128, kGeluSlope><<<grid, kThreads, smem_bytes, stream>>>(
+        gemm_tc_kernel<128, 128, kGeluSlope><<<grid, kThreads, smem_bytes, stream>>>(
             map_a, map_b, map_d, map_d2, p);
     } else {
-        gemm_tc_kernel<128, 0><<<grid, kThreads, smem_bytes, stream>>>(
+        gemm_tc_kernel<128, 128, 0><<<grid, kThreads, smem_bytes, stream>>>(
             map_a, map_b, map_d, map_d2, p);
     }
     ++g_kernel_launches;
