@@ -103,7 +103,8 @@ def test_gemm_tf32_tensor_cores(lib, m, k, n):
 
 
 @pytest.mark.parametrize("precision", [FP32, TF32], ids=["fp32", "tf32"])
-@pytest.mark.parametrize("m,k,n", [(1600, 128, 384), (300, 64, 96), (1000, 512, 128)])
+@pytest.mark.parametrize("m,k,n", [(1600, 128, 384), (300, 64, 96), (1000, 512, 128),
+                                   (1000, 512, 512), (2304, 384, 1536)])
 @pytest.mark.parametrize("extra", ["bias", "bias+gelu", "bias+residual", "gelu"])
 def test_gemm_fused_epilogues(lib, m, k, n, extra, precision):
     """y = x w + bias with gelu(y) or residual + y produced by the same launch

@@ -124,8 +124,9 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a,
     constexpr int kABytes = TILE_M * kBlockK * 4;
     constexpr int kStageBytes = kABytes + TILE_N * kBlockK * 4;
     constexpr int kTmemColumns = 2 * TILE_N;
-    static_assert(TILE_M == kTileM || (TILE_M == 2 * kTileM && SECOND == 0),
-                  "the tall tile has the plain epilogue only");
+    static_assert(TILE_M == kTileM ||
+                      (TILE_M == 2 * kTileM && (SECOND == 0 || SECOND == kSecondGelu)),
+                  "the tall tile has the plain and the GELU epilogues only");
     const int kStages = p.stages;
     uint8_t *staging = smem + kStages * kStageBytes;
     uint64_t *full_bar = reinterpret_cast<uint64_t *>(staging + p.staging_bytes);
@@ -521,7 +522,8 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a,
                 float *first = reinterpret_cast<float *>(my_staging + slot * 4096);
                 // With 16 KiB of staging both outputs of a warp go through the
                 // same 4 KiB block, one after the other.
-                const bool shared_block = outputs == 2 && p.staging_bytes == kOperandBytes;
+                const bool shared_block =
+                    outputs == 2 && (kHalves == 2 || p.staging_bytes == kOperandBytes);
                 float *second = shared_block
                     ? first : reinterpret_cast<float *>(my_staging + 4096);
                 {
@@ -579,11 +581,18 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a,
                 asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
                 __syncwarp();
                 if (shared_block && SECOND == kSecondGelu) {
-                    // First output out, wait until the copy engine has read
-                    // the block, then the second output through the same block.
+                    // First output out; the second output's values are
+                    // computed while the copy engine reads the block, and go
+                    // through the same block once it has.
                     if (lane == 0) {
                         tma_store_2d(first, &map_d, col0, m0);
                         asm volatile("cp.async.bulk.commit_group;" ::: "memory");
+                    }
+#pragma unroll
+                    for (int e = 0; e < 32; ++e) {
+                        r[e] = __float_as_uint(gelu_value_fast(__uint_as_float(r[e])));
+                    }
+                    if (lane == 0) {
                         asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory");
                     }
                     __syncwarp();
@@ -594,10 +603,6 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a,
                         v.y = __uint_as_float(r[4 * c + 1]);
                         v.z = __uint_as_float(r[4 * c + 2]);
                         v.w = __uint_as_float(r[4 * c + 3]);
-                        v.x = gelu_value_fast(v.x);
-                        v.y = gelu_value_fast(v.y);
-                        v.z = gelu_value_fast(v.z);
-                        v.w = gelu_value_fast(v.w);
                         const int offset = lane * 32 + 4 * (c ^ (lane & 7));
                         *reinterpret_cast<float4 *>(second + offset) = v;
                     }
@@ -773,7 +778,8 @@ int launch_gemm_tc(const TcGemm &g, cudaStream_t stream) {
             reinterpret_cast<const void *>(gemm_tc_kernel<128, 128, kSecondResidual>),
             reinterpret_cast<const void *>(gemm_tc_kernel<128, 128, kGeluSlope>),
             reinterpret_cast<const void *>(gemm_tc_kernel<128, 256, 0>),
-            reinterpret_cast<const void *>(gemm_tc_kernel<256, 256, 0>)};
+            reinterpret_cast<const void *>(gemm_tc_kernel<256, 256, 0>),
+            reinterpret_cast<const void *>(gemm_tc_kernel<256, 256, kSecondGelu>)};
         for (const void *kernel : kernels) {
             if (cudaFuncSetAttribute(kernel,
                                      cudaFuncAttributeMaxDynamicSharedMemorySize,
@@ -787,13 +793,16 @@ int launch_gemm_tc(const TcGemm &g, cudaStream_t stream) {
     // deep reductions, one output, a multiple of 256 columns.
     static const int forced_tile =
         getenv("VITB200_TC_TILE_N") ? atoi(getenv("VITB200_TC_TILE_N")) : 0;
-    bool wide = !g.d2 && !g.gelu_input && g.k >= 256 && g.n % 256 == 0;
-    if (forced_tile == 128 || g.d2 || g.gelu_input) {
+    // (A product with the GELU as second output takes them only in the tall
+    // form below.)
+    const bool gelu_pair = g.d2 && !g.residual;
+    bool wide = (!g.d2 || gelu_pair) && !g.gelu_input && g.k >= 256 &&
+                g.n % 256 == 0;
+    if (forced_tile == 128 || (g.d2 && !gelu_pair) || g.gelu_input) {
         wide = false;
-    } else if (forced_tile == 256) {
+    } else if (forced_tile == 256 && !g.d2) {
         wide = g.n >= 256;
     }
-    const int tile_n = wide ? 256 : kTileN;
     // Tall tiles (256 x 256, two accumulator halves) on top of that when there
     // are at least two full row tiles: a third less operand traffic from L2.
     static const int forced_tile_m =
@@ -807,6 +816,10 @@ int launch_gemm_tc(const TcGemm &g, cudaStream_t stream) {
                       g.m >= 16 * kTileM;
     const bool tall = wide && g.m >= 2 * kTileM && forced_tile_m != 128 &&
                       ((long_enough && fits) || forced_tile_m == 256);
+    if (gelu_pair && !tall) {
+        wide = false;
+    }
+    const int tile_n = wide ? 256 : kTileN;
     const int tile_m = tall ? 2 * kTileM : kTileM;
     CUtensorMap map_a, map_b, map_d;
     // K-major operand: rows = output index, inner = reduction index.
@@ -942,7 +955,10 @@ int launch_gemm_tc(const TcGemm &g, cudaStream_t stream) {
             return -1;
         }
     }
-    if (tall) {
+    if (tall && second == kSecondGelu) {
+        gemm_tc_kernel<256, 256, kSecondGelu>
+            <<<grid, kThreadsTall, smem_bytes, stream>>>(map_a, map_b, map_d, map_d2, p);
+    } else if (tall) {
         gemm_tc_kernel<256, 256, 0><<<grid, kThreadsTall, smem_bytes, stream>>>(
             map_a, map_b, map_d, map_d2, p);
     } else if (wide) {
