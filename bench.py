@@ -614,6 +614,9 @@ def main():
     parser.add_argument("--no-cfg5", action="store_true",
                         help="leave out the data-parallel configuration's object")
     parser.add_argument("--cfg5-steps", type=int, default=3)
+    parser.add_argument("--no-tf32-peak", action="store_true",
+                        help="do not measure the TF32 matmul rate first (keeps "
+                             "library kernels out of a profiler's launch list)")
     parser.add_argument("--replica", type=int, default=0, help=argparse.SUPPRESS)
     parser.add_argument("--global-batch", type=int, default=-1,
                         help="images per optimiser step over all GPUs; 0 = one "
@@ -663,7 +666,8 @@ def main():
     # The TF32 roof, before the backend holds any memory.  With several ranks
     # only a single-GPU run measures it (the ranks would share the power and
     # the result would not be a per-GPU peak).
-    tf32_peak = measure_tf32_peak() if world == 1 else None
+    tf32_peak = (measure_tf32_peak()
+                 if world == 1 and not args.no_tf32_peak else None)
 
     host_lib = vh.load_host_library(HOST_LIBRARY)
     backend = vh.Backend()          # raises without the library or a B200

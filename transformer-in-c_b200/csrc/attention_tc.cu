@@ -108,7 +108,12 @@ struct AttnParams {
     float scale;    // 1 / sqrt(head_dim)
     float scale2;   // scale * log2(e)
     float *lse;               // [groups * seq]: written forward, read backward
-    const float *row_dots;    // [groups * seq]: rowsum(dO o O), backward
+    // [groups * seq]: D = rowsum(dO o O).  The query-gradient kernel computes
+    // and writes it (from out / dout below), the key/value-gradient kernel,
+    // which runs after it, reads it.
+    float *row_dots;
+    const float *out, *dout;  // query-gradient kernel: O and dO, for D
+    int out_ld, out_heads, dout_ld, dout_heads;
     int add0, add1;           // outputs accumulate
     int *status;
 };
@@ -714,11 +719,43 @@ attention_tc_kernel(const __grid_constant__ AttnMaps maps, const AttnParams p) {
                 const bool tile = it < my_items && j < tiles;
                 if (tile) {
                     if (fresh) {
+                        // This row's log-sum-exp and D = dO . O (both groups
+                        // compute it, one writes it for the kernel that
+                        // follows).  The loads are in flight while the
+                        // item's first scores are being computed.
                         const Item item = item_at(it);
                         const int q = item.m0 + row;
-                        const size_t at = size_t(item.group) * p.seq + q;
-                        row_lse = q < p.seq ? p.lse[at] : 0.0f;
-                        row_dot = q < p.seq ? p.row_dots[at] : 0.0f;
+                        row_lse = 0.0f;
+                        row_dot = 0.0f;
+                        if (q < p.seq && HD > 32) {
+                            // Wide heads: D was computed by the kernel before
+                            // this one (a row here is 256 bytes per operand;
+                            // fetching it per thread costs more than it saves).
+                            const size_t at = size_t(item.group) * p.seq + q;
+                            row_lse = p.lse[at];
+                            row_dot = p.row_dots[at];
+                        } else if (q < p.seq) {
+                            const size_t at = size_t(item.group) * p.seq + q;
+                            row_lse = p.lse[at];
+                            const float4 *o = reinterpret_cast<const float4 *>(
+                                p.out +
+                                (size_t(item.group / p.out_heads) * p.seq + q) * p.out_ld +
+                                size_t(item.group % p.out_heads) * HD);
+                            const float4 *g = reinterpret_cast<const float4 *>(
+                                p.dout +
+                                (size_t(item.group / p.dout_heads) * p.seq + q) * p.dout_ld +
+                                size_t(item.group % p.dout_heads) * HD);
+                            float part[4] = {0.0f, 0.0f, 0.0f, 0.0f};
+#pragma unroll
+                            for (int i = 0; i < HD / 4; ++i) {
+                                const float4 x = __ldg(o + i), y = __ldg(g + i);
+                                part[i & 3] += x.x * y.x + x.y * y.y + x.z * y.z + x.w * y.w;
+                            }
+                            row_dot = (part[0] + part[1]) + (part[2] + part[3]);
+                            if (wg == 0) {
+                                p.row_dots[at] = row_dot;
+                            }
+                        }
                         fresh = false;
                     }
                     wait(kScoresFull + wg, visit & 1, 25);
@@ -883,30 +920,44 @@ attention_tc_kernel(const __grid_constant__ AttnMaps maps, const AttnParams p) {
     }
 }
 
-// dots[g * seq + t] = sum_c dO[g, t, c] * O[g, t, c]; one warp per row.
-template <int HD>
+// dots[g * seq + t] = sum_c dO[g, t, c] * O[g, t, c] for 64-wide heads: sixteen
+// lanes per row (one float4 of each operand per lane: 256 contiguous bytes per
+// row), two rows per warp and load, four such pairs in flight.
 __global__ void __launch_bounds__(256)
 attention_row_dots_kernel(const float *__restrict__ out, const float *__restrict__ dout,
                           float *__restrict__ dots, size_t rows, int seq,
                           HeadLayout out_layout, HeadLayout dout_layout) {
+    constexpr int HD = 64;
     const int lane = threadIdx.x & 31;
+    const int part = lane & 15;
     const size_t warps = grid_threads() >> 5;
-    for (size_t r = global_thread() >> 5; r < rows; r += warps) {
-        const size_t group = r / size_t(seq), t = r % size_t(seq);
-        const size_t o_at =
-            (group / out_layout.heads) * seq * size_t(out_layout.ld) +
-            (group % out_layout.heads) * HD + t * size_t(out_layout.ld);
-        const size_t d_at =
-            (group / dout_layout.heads) * seq * size_t(dout_layout.ld) +
-            (group % dout_layout.heads) * HD + t * size_t(dout_layout.ld);
-        float sum = 0.0f;
+    for (size_t first = (global_thread() >> 5) * 8; first < rows; first += warps * 8) {
+        float sums[4];
 #pragma unroll
-        for (int c = 0; c < HD / 32; ++c) {
-            sum += out[o_at + 32 * c + lane] * dout[d_at + 32 * c + lane];
+        for (int i = 0; i < 4; ++i) {
+            const size_t r = first + 2 * i + (lane >> 4);
+            sums[i] = 0.0f;
+            if (r < rows) {
+                const size_t group = r / size_t(seq), t = r % size_t(seq);
+                const float4 x = __ldg(reinterpret_cast<const float4 *>(
+                    out + ((group / out_layout.heads) * seq + t) * size_t(out_layout.ld) +
+                    (group % out_layout.heads) * HD) + part);
+                const float4 y = __ldg(reinterpret_cast<const float4 *>(
+                    dout + ((group / dout_layout.heads) * seq + t) * size_t(dout_layout.ld) +
+                    (group % dout_layout.heads) * HD) + part);
+                sums[i] = x.x * y.x + x.y * y.y + x.z * y.z + x.w * y.w;
+            }
         }
-        sum = warp_sum(sum);
-        if (lane == 0) {
-            dots[r] = sum;
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+#pragma unroll
+            for (int offset = 8; offset > 0; offset >>= 1) {
+                sums[i] += __shfl_xor_sync(kFullMask, sums[i], offset);
+            }
+            const size_t r = first + 2 * i + (lane >> 4);
+            if (part == 0 && r < rows) {
+                dots[r] = sums[i];
+            }
         }
     }
 }
@@ -1131,8 +1182,8 @@ bool launch_attention_tc_backward(const float *q, const float *k, const float *v
     if (!operand_ok(q, in_layout, groups) || !operand_ok(k, in_layout, groups) ||
         !operand_ok(v, in_layout, groups) || !operand_ok(dout, dout_layout, groups) ||
         !operand_ok(dq, grad_layout, groups) || !operand_ok(dk, grad_layout, groups) ||
-        !operand_ok(dv, grad_layout, groups) || out_layout.heads < 1 ||
-        groups % size_t(out_layout.heads) != 0 ||
+        !operand_ok(dv, grad_layout, groups) || !operand_ok(out, out_layout, groups) ||
+        (reinterpret_cast<uintptr_t>(row_dots) & 3) != 0 ||
         in_layout.heads != dout_layout.heads || in_layout.heads != grad_layout.heads) {
         return false;
     }
@@ -1164,16 +1215,20 @@ bool launch_attention_tc_backward(const float *q, const float *k, const float *v
     }
     params.lse = const_cast<float *>(lse);
     params.row_dots = row_dots;
-    const size_t rows = groups * seq;
-    const unsigned dots_grid = unsigned(std::min<size_t>((rows + 7) / 8, 148 * 8));
-    if (hd == 32) {
-        attention_row_dots_kernel<32><<<dots_grid, 256, 0, stream>>>(
+    params.out = out;
+    params.dout = dout;
+    params.out_ld = out_layout.ld;
+    params.out_heads = out_layout.heads;
+    params.dout_ld = dout_layout.ld;
+    params.dout_heads = dout_layout.heads;
+    if (hd == 64) {
+        const size_t rows = groups * seq;
+        const unsigned dots_grid =
+            unsigned(std::min<size_t>((rows + 63) / 64, size_t(sm_count()) * 8));
+        attention_row_dots_kernel<<<dots_grid, 256, 0, stream>>>(
             out, dout, row_dots, rows, int(seq), out_layout, dout_layout);
-    } else {
-        attention_row_dots_kernel<64><<<dots_grid, 256, 0, stream>>>(
-            out, dout, row_dots, rows, int(seq), out_layout, dout_layout);
+        ++g_kernel_launches;
     }
-    ++g_kernel_launches;
     AttnParams query_params = params;
     query_params.add0 = add_q ? 1 : 0;
     AttnParams key_params = params;
