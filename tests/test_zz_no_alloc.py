@@ -78,3 +78,34 @@ def test_static_scratch_rejects_too_many_rows():
         _ptr(dummy), _ptr(dummy), None, ctypes.c_float(0.0), _ptr(dummy),
         _ptr(dummy), ctypes.c_size_t(MAX_ROWS + 1), ctypes.c_size_t(11), None)
     assert status == -2
+
+
+def test_static_calls_leave_the_device_memory_as_it_is_up_to_the_largest_size():
+    """What the entry point is for: once the library has resolved its array on
+    this device (the first call does that), further calls must not change the
+    amount of free device memory, including a call at the largest accepted
+    size, whose result again equals the scratch-taking entry point's."""
+    lib = _lib()
+    rng = np.random.RandomState(9)
+    rows, cols = MAX_ROWS, 11
+    logits = rng.randn(rows, cols) * 2
+    labels = rng.randint(0, cols, rows)
+    grad0 = np.zeros((rows, cols))
+    expected_loss, expected_grad = _run(lib, False, logits, labels, None, 0.1, grad0)
+    # Inputs and outputs are the caller's: they exist before the measurement.
+    z, t, g = _dev(logits), _dev(labels.astype(np.float32)), _dev(grad0)
+    loss = torch.zeros(1, device="cuda")
+    arguments = [_ptr(z), _ptr(t), None, ctypes.c_float(0.1), _ptr(loss), _ptr(g),
+                 ctypes.c_size_t(rows), ctypes.c_size_t(cols), None]
+    assert lib.vitb200_k_softmax_cross_entropy_static(*arguments) == 0   # warm-up
+    torch.cuda.synchronize()
+    free_before, _ = torch.cuda.mem_get_info()
+    for _ in range(3):
+        g.zero_()
+        assert lib.vitb200_k_softmax_cross_entropy_static(*arguments) == 0
+    torch.cuda.synchronize()
+    free_after, _ = torch.cuda.mem_get_info()
+    assert free_after == free_before
+    assert abs(loss.cpu().numpy()[0] - expected_loss) <= 1e-6 * max(1.0, abs(expected_loss))
+    scale = max(float(np.abs(expected_grad).max()), 1e-6)
+    assert float(np.abs(g.cpu().numpy() - expected_grad).max()) / scale <= 1e-6

@@ -1074,20 +1074,6 @@ constexpr int smem_bytes() {
     return bytes < kMinSmemBytes ? kMinSmemBytes : bytes;
 }
 
-int sm_count() {
-    static const int count = []() {
-        int device = 0, value = 0;
-        if (cudaGetDevice(&device) != cudaSuccess ||
-            cudaDeviceGetAttribute(&value, cudaDevAttrMultiProcessorCount, device) !=
-                cudaSuccess ||
-            value <= 0) {
-            return int(kSmCount);
-        }
-        return value;
-    }();
-    return count;
-}
-
 template <int HD, int MODE>
 bool launch(const AttnMaps &maps, AttnParams params, size_t groups,
             cudaStream_t stream) {
@@ -1108,7 +1094,7 @@ bool launch(const AttnMaps &maps, AttnParams params, size_t groups,
     }
     params.items = int(items);
     // One persistent CTA per SM (it owns the SM's tensor memory).
-    const unsigned grid = unsigned(std::min<size_t>(items, size_t(sm_count())));
+    const unsigned grid = unsigned(std::min<size_t>(items, size_t(device_sm_count())));
     attention_tc_kernel<HD, MODE><<<grid, kAttnThreads, bytes, stream>>>(maps, params);
     ++g_kernel_launches;
     return true;
@@ -1224,7 +1210,7 @@ bool launch_attention_tc_backward(const float *q, const float *k, const float *v
     if (hd == 64) {
         const size_t rows = groups * seq;
         const unsigned dots_grid =
-            unsigned(std::min<size_t>((rows + 63) / 64, size_t(sm_count()) * 8));
+            unsigned(std::min<size_t>((rows + 63) / 64, size_t(device_sm_count()) * 8));
         attention_row_dots_kernel<<<dots_grid, 256, 0, stream>>>(
             out, dout, row_dots, rows, int(seq), out_layout, dout_layout);
         ++g_kernel_launches;

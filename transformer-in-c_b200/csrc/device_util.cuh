@@ -11,11 +11,28 @@ constexpr unsigned kSmCount = 148;         // B200: 2 dies x 74 SMs
 constexpr unsigned kStreamBlocksPerSm = 8; // 2048 threads / 256
 constexpr unsigned kFullMask = 0xffffffffu;
 
+// Multiprocessors of the current device, asked once (148 on a B200, which is
+// also the answer when the query fails).  Persistent grids are sized by it.
+inline unsigned device_sm_count() {
+    static const unsigned count = []() -> unsigned {
+        int device = 0, value = 0;
+        if (cudaGetDevice(&device) != cudaSuccess ||
+            cudaDeviceGetAttribute(&value, cudaDevAttrMultiProcessorCount, device) !=
+                cudaSuccess ||
+            value <= 0) {
+            cudaGetLastError();
+            return kSmCount;
+        }
+        return unsigned(value);
+    }();
+    return count;
+}
+
 // Grid for a streaming kernel over `items` work items: enough blocks to cover
 // them once, capped at one full wave of resident blocks.
 inline unsigned stream_grid(size_t items) {
     const size_t wanted = (items + kStreamThreads - 1) / kStreamThreads;
-    const size_t wave = size_t(kSmCount) * kStreamBlocksPerSm;
+    const size_t wave = size_t(device_sm_count()) * kStreamBlocksPerSm;
     return static_cast<unsigned>(wanted < 1 ? 1 : (wanted < wave ? wanted : wave));
 }
 

@@ -38,6 +38,7 @@
 #include "tcgen05.cuh"
 
 #include <cuda.h>
+#include <algorithm>
 #include <cstdio>
 #include <cstdlib>
 #include <cstring>
@@ -899,7 +900,10 @@ int launch_gemm_tc(const TcGemm &g, cudaStream_t stream) {
         }
     }
     p.staging_bytes = staging_bytes;
-    const long long slots = 148LL * ctas_per_sm;
+    // One or two persistent CTAs on every multiprocessor (never more than
+    // the per-CTA partial rows provide for).
+    const long long slots =
+        std::min<long long>((long long)device_sm_count() * ctas_per_sm, kGemmPartialRows);
     int splits = 1;
     if (g.accumulate) {
         // Long reductions onto few output tiles (weight gradients) are cut
@@ -948,7 +952,6 @@ int launch_gemm_tc(const TcGemm &g, cudaStream_t stream) {
         return -1;
     }
     if (g.column_partials) {
-        static_assert(kGemmPartialRows == 148 * 2, "one row per CTA slot");
         if (cudaMemsetAsync(g.column_partials, 0,
                             size_t(kGemmPartialRows) * g.n * sizeof(float),
                             stream) != cudaSuccess) {
