@@ -221,6 +221,66 @@ __device__ __forceinline__ size_t group_offset(size_t group, int seq,
            (group % layout.heads) * HD;
 }
 
+// The same for a group index that is a block index: one 32-bit division.
+template <int HD>
+__device__ __forceinline__ size_t group_offset(unsigned group, int seq,
+                                               HeadLayout layout) {
+    const unsigned sample = group / unsigned(layout.heads);
+    const unsigned head = group - sample * unsigned(layout.heads);
+    return size_t(sample) * size_t(unsigned(seq) * unsigned(layout.ld)) +
+           head * HD;
+}
+
+// ---------------------------------------------------------------------------
+// Operands that are not rounded.  mma.sync reads the upper 19 bits of a TF32
+// operand register and ignores the rest, so an FP32 value handed over as it is
+// gets truncated: a relative error between 0 and 2^-10 that always points
+// toward zero.  Its mean (about 0.75 * 2^-11 per operand for mantissas spread
+// over [1, 2)) is a bias of every product and is taken out by a constant
+// factor on the result, folded into a scale the kernel applies anyway; what
+// remains is spread like the error of rounding to nearest.  The kernels for
+// whole groups use this to drop every cvt.rna from the instruction stream and
+// to stage their tiles with cp.async.
+constexpr float kTruncatedOperand = 1.0f + 0.75f / 2048.0f;
+constexpr float kTruncatedPair = kTruncatedOperand * kTruncatedOperand;
+constexpr float kLog2TruncatedPair = 2.0f * 0.75f / 2048.0f * 1.4426950408889634f;
+
+__device__ __forceinline__ void copy_async_16(float *target, const float *source,
+                                              bool valid) {
+    const uint32_t address = uint32_t(__cvta_generic_to_shared(target));
+    const int bytes = valid ? 16 : 0;   // 0: sixteen zero bytes, nothing is read
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;"
+                 :: "r"(address), "l"(source), "r"(bytes) : "memory");
+}
+
+__device__ __forceinline__ void copy_async_wait() {
+    asm volatile("cp.async.commit_group;\n\tcp.async.wait_group 0;" ::: "memory");
+}
+
+// Rows [0, 32) or [0, 64) of a matrix whose rows are `ld` floats apart (every
+// row a 16-row tile that starts below 8 * TILES can touch) go to a staged tile
+// as they are, without passing through registers; rows past `seq` become zero.
+template <int HD, int TILES>
+__device__ __forceinline__ void stage_async(float *tile,
+                                            const float *__restrict__ source,
+                                            int ld, int seq) {
+    constexpr int kVectors = HD / 4;
+    constexpr int kRowsPerPass = kThreads / kVectors;   // 8 or 16
+    constexpr int kRows = TILES <= 4 ? 32 : kTile;
+    const int r = threadIdx.x / kVectors;
+    const int c = (threadIdx.x % kVectors) * 4;
+    // Both layouts repeat every eight rows.
+    float *target = tile + tile_index<HD>(r, c);
+    const float *from = source + size_t(r) * ld + c;
+#pragma unroll
+    for (int j = 0; j < kRows / kRowsPerPass; ++j) {
+        const bool valid = r + j * kRowsPerPass < seq;
+        copy_async_16(target + j * kRowsPerPass * Shape<HD>::kPitch,
+                      valid ? from + size_t(j * kRowsPerPass) * ld : source,
+                      valid);
+    }
+}
+
 // c[16 x 64] += A B^T: A = rows (a0, a1) given as lane ranges, B = a staged
 // tile whose rows are the result's columns.
 // `live` (< TILES) restricts the work to the first `live` 8-row groups of the
@@ -263,7 +323,7 @@ __device__ __forceinline__ void product_rows(float (&c)[8][4],
 // (columns 2t, 2t+1 of tile s), B = a staged tile whose rows are the
 // contraction index.  Result element e of the lane's row range is
 // o[e % kOut][e / kOut] (row g) and o[e % kOut][2 + e / kOut] (row g + 8).
-template <int HD, int TILES, bool kPartial = false>
+template <int HD, int TILES, bool kPartial = false, bool kRounded = true>
 __device__ __forceinline__ void product_columns(float (&o)[HD / 8][4],
                                                 const float (&p)[8][4],
                                                 const float *tile, int g,
@@ -296,8 +356,10 @@ __device__ __forceinline__ void product_columns(float (&o)[HD / 8][4],
                     b1[i] = y.x; b1[i + 1] = y.y; b1[i + 2] = y.z; b1[i + 3] = y.w;
                 }
             }
-            const float a0 = to_tf32(p[s][0]), a1 = to_tf32(p[s][2]);
-            const float a2 = to_tf32(p[s][1]), a3 = to_tf32(p[s][3]);
+            const float a0 = kRounded ? to_tf32(p[s][0]) : p[s][0];
+            const float a1 = kRounded ? to_tf32(p[s][2]) : p[s][2];
+            const float a2 = kRounded ? to_tf32(p[s][1]) : p[s][1];
+            const float a3 = kRounded ? to_tf32(p[s][3]) : p[s][3];
 #pragma unroll
             for (int u = 0; u < S::kOut; ++u) {
                 mma_tf32(o[u], a0, a1, a2, a3, b0[u], b1[u]);
@@ -412,27 +474,24 @@ attention_warp_forward_kernel(const float *__restrict__ q,
     using S = Shape<HD>;
     __shared__ __align__(16) float k_tile[kTile * S::kPitch];
     __shared__ __align__(16) float v_tile[kTile * S::kPitch];
-    const size_t group = blockIdx.x;
+    const unsigned group = blockIdx.x;
     const size_t in_base = group_offset<HD>(group, seq, in_layout);
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     const int g = lane >> 2, t = lane & 3;
-    // All global loads of the block go out together: the K and V tiles and
-    // the query rows of this warp's (at most two) row tiles.  Rows past the
-    // end repeat the last row; their results are dropped.
+    // All global loads of the block go out together: the K and V tiles
+    // (asynchronous copies, unrounded) and the query rows of this warp's (at
+    // most two) row tiles.  Rows past the end repeat the last row; their
+    // results are dropped.
+    stage_async<HD, TILES>(k_tile, k + in_base, in_layout.ld, seq);
+    stage_async<HD, TILES>(v_tile, v + in_base, in_layout.ld, seq);
     float query[2][2][S::kRange];
-    {
-        Staged<HD> k_staged, v_staged;
-        stage_load<HD>(k_staged, k + in_base, in_layout.ld, seq);
-        stage_load<HD>(v_staged, v + in_base, in_layout.ld, seq);
 #pragma unroll
-        for (int pass = 0; pass < 2; ++pass) {
-            const int r0 = (warp + pass * kWarps) * 16 + g;
-            load_range_global(query[pass][0], q + in_base + size_t(min(r0, seq - 1)) * in_layout.ld + t * S::kRange, true);
-            load_range_global(query[pass][1], q + in_base + size_t(min(r0 + 8, seq - 1)) * in_layout.ld + t * S::kRange, true);
-        }
-        stage_store<HD>(k_staged, k_tile);
-        stage_store<HD>(v_staged, v_tile);
+    for (int pass = 0; pass < 2; ++pass) {
+        const int r0 = (warp + pass * kWarps) * 16 + g;
+        load_range_global(query[pass][0], q + in_base + size_t(min(r0, seq - 1)) * in_layout.ld + t * S::kRange, false);
+        load_range_global(query[pass][1], q + in_base + size_t(min(r0 + 8, seq - 1)) * in_layout.ld + t * S::kRange, false);
     }
+    copy_async_wait();
     __syncthreads();
     float *out_base = out + group_offset<HD>(group, seq, out_layout);
 #pragma unroll
@@ -448,13 +507,15 @@ attention_warp_forward_kernel(const float *__restrict__ q,
         clear(p);
         product_rows<HD, TILES>(p, a0, a1, k_tile, g, t);
         float inverse_a, inverse_b, lse_a, lse_b;
-        softmax_rows<TILES>(p, seq, t, scale * kLog2e, inverse_a, inverse_b,
-                            lse_a, lse_b);
+        softmax_rows<TILES>(p, seq, t, scale * (kLog2e * kTruncatedPair),
+                            inverse_a, inverse_b, lse_a, lse_b);
         float o[S::kOut][4];
         clear(o);
-        product_columns<HD, TILES>(o, p, v_tile, g, t);
+        product_columns<HD, TILES, false, false>(o, p, v_tile, g, t);
         // The probabilities were left unnormalised: scale the 16 x HD result
-        // instead of the 16 x 64 tile.
+        // instead of the 16 x 64 tile (and undo the truncation of P and V).
+        inverse_a *= kTruncatedPair;
+        inverse_b *= kTruncatedPair;
 #pragma unroll
         for (int u = 0; u < S::kOut; ++u) {
             o[u][0] *= inverse_a;
@@ -489,53 +550,43 @@ attention_warp_backward_kernel(
     __shared__ __align__(16) float g_tile[kTile * S::kPitch];
     __shared__ __align__(8) float row_lse[kTile];
     __shared__ __align__(8) float row_dot[kTile];
-    const size_t group = blockIdx.x;
+    const unsigned group = blockIdx.x;
     const size_t in_base = group_offset<HD>(group, seq, in_layout);
     const float *out_base = out + group_offset<HD>(group, seq, out_layout);
     const float *dout_base = dout + group_offset<HD>(group, seq, dout_layout);
     const size_t grad_base = group_offset<HD>(group, seq, grad_layout);
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     const int g = lane >> 2, t = lane & 3;
-    // All global loads of the block go out together: the four operand tiles,
-    // and the O and dO rows behind D_i = dO_i . O_i (in full precision) for
-    // this warp's (at most two) row tiles.
-    float row_dots[2][2];
+    // All global loads of the block go out together: the four operand tiles
+    // (asynchronous copies, unrounded) and the O rows behind D_i = dO_i . O_i
+    // for this warp's (at most two) row tiles; the dO rows of that product
+    // are the fragments the first pass reads from the staged tile anyway.
+    stage_async<HD, TILES>(q_tile, q + in_base, in_layout.ld, seq);
+    stage_async<HD, TILES>(k_tile, k + in_base, in_layout.ld, seq);
+    stage_async<HD, TILES>(v_tile, v + in_base, in_layout.ld, seq);
+    stage_async<HD, TILES>(g_tile, dout_base, dout_layout.ld, seq);
+    float out_rows[2][2][S::kRange];
     float sums[3][S::kRange] = {};   // column sums of dQ, dK, dV (this warp's tiles)
-    {
-        Staged<HD> staged[4];
-        stage_load<HD>(staged[0], q + in_base, in_layout.ld, seq);
-        stage_load<HD>(staged[1], k + in_base, in_layout.ld, seq);
-        stage_load<HD>(staged[2], v + in_base, in_layout.ld, seq);
-        stage_load<HD>(staged[3], dout_base, dout_layout.ld, seq);
 #pragma unroll
-        for (int pass = 0; pass < 2; ++pass) {
+    for (int pass = 0; pass < 2; ++pass) {
 #pragma unroll
-            for (int half = 0; half < 2; ++half) {
-                const int row = (warp + pass * kWarps) * 16 + g + 8 * half;
-                float o[S::kRange], d[S::kRange];
-                const int safe = min(row, seq - 1);
-                load_range_global(o, out_base + size_t(safe) * out_layout.ld + t * S::kRange, false);
-                load_range_global(d, dout_base + size_t(safe) * dout_layout.ld + t * S::kRange, false);
-                float dot = 0.0f;
-#pragma unroll
-                for (int e = 0; e < S::kRange; ++e) {
-                    dot = fmaf(o[e], d[e], dot);
-                }
-                row_dots[pass][half] = quad_sum(dot);
-            }
+        for (int half = 0; half < 2; ++half) {
+            const int row = (warp + pass * kWarps) * 16 + g + 8 * half;
+            load_range_global(out_rows[pass][half],
+                              out_base + size_t(min(row, seq - 1)) * out_layout.ld + t * S::kRange,
+                              false);
         }
-        stage_store<HD>(staged[0], q_tile);
-        stage_store<HD>(staged[1], k_tile);
-        stage_store<HD>(staged[2], v_tile);
-        stage_store<HD>(staged[3], g_tile);
     }
     // Rows past the end: P^T must vanish there (lse = +inf) and D is unused.
     for (int i = seq + threadIdx.x; i < kTile; i += kThreads) {
         row_lse[i] = FLT_MAX;
         row_dot[i] = 0.0f;
     }
+    copy_async_wait();
     __syncthreads();
-    const float scale2 = scale * kLog2e;
+    // Every product below has two truncated operands (see kTruncatedPair).
+    const float scale2 = scale * (kLog2e * kTruncatedPair);
+    const float scale_pair = scale * kTruncatedPair;
 #pragma unroll
     for (int pass = 0; pass < 2; ++pass) {
         const int m0 = (warp + pass * kWarps) * 16;
@@ -552,26 +603,38 @@ attention_warp_backward_kernel(
         float inverse_a, inverse_b, lse_a, lse_b;
         softmax_rows<TILES>(p, seq, t, scale2, inverse_a, inverse_b, lse_a,
                             lse_b);
-        const float dot_a = row_dots[pass][0], dot_b = row_dots[pass][1];
-        if (t == 0) {
-            if (r0 < seq) {
-                row_lse[r0] = lse_a;
-                row_dot[r0] = -scale * dot_a;
-            }
-            if (r1 < seq) {
-                row_lse[r1] = lse_b;
-                row_dot[r1] = -scale * dot_b;
-            }
-        }
         // dP = dO V^T, then dS = scale P (dP - D) in place over dP.
         load_range(a0, g_tile + tile_index<HD>(r0, t * S::kRange));
         load_range(a1, g_tile + tile_index<HD>(r1, t * S::kRange));
+        float dot_a = 0.0f, dot_b = 0.0f;
+#pragma unroll
+        for (int e = 0; e < S::kRange; ++e) {
+            dot_a = fmaf(out_rows[pass][0][e], a0[e], dot_a);
+            dot_b = fmaf(out_rows[pass][1][e], a1[e], dot_b);
+        }
+        dot_a = quad_sum(dot_a);
+        dot_b = quad_sum(dot_b);
+        if (t == 0) {
+            // What the second pass reads: the log-sum-exp lowered so that its
+            // P^T comes out scaled for the two products it feeds.
+            if (r0 < seq) {
+                row_lse[r0] = lse_a - kLog2TruncatedPair;
+                row_dot[r0] = -scale * dot_a;
+            }
+            if (r1 < seq) {
+                row_lse[r1] = lse_b - kLog2TruncatedPair;
+                row_dot[r1] = -scale * dot_b;
+            }
+        }
         float ds[8][4];
         clear(ds);
         product_rows<HD, TILES>(ds, a0, a1, v_tile, g, t);
-        // p holds exp2(.) without the 1 / sum: fold it into the row factor.
-        const float factor_a = scale * inverse_a, factor_b = scale * inverse_b;
-        const float offset_a = -dot_a * factor_a, offset_b = -dot_b * factor_b;
+        // p holds exp2(.) without the 1 / sum: fold it into the row factor,
+        // with one correction for dP and one for the product dS feeds.
+        const float offset_a = -dot_a * scale_pair * inverse_a;
+        const float offset_b = -dot_b * scale_pair * inverse_b;
+        const float factor_a = scale_pair * kTruncatedPair * inverse_a;
+        const float factor_b = scale_pair * kTruncatedPair * inverse_b;
 #pragma unroll
         for (int n = 0; n < TILES; ++n) {
             ds[n][0] = p[n][0] * fmaf(ds[n][0], factor_a, offset_a);
@@ -581,7 +644,7 @@ attention_warp_backward_kernel(
         }
         float result[S::kOut][4];
         clear(result);
-        product_columns<HD, TILES>(result, ds, k_tile, g, t);
+        product_columns<HD, TILES, false, false>(result, ds, k_tile, g, t);
         store_result<HD>(dq + grad_base, grad_layout.ld, r0, r1, seq, t, result,
                          add_q);
         if (column_partials) {
@@ -608,7 +671,7 @@ attention_warp_backward_kernel(
         }
         float result[S::kOut][4];
         clear(result);
-        product_columns<HD, TILES>(result, p, g_tile, g, t);   // dV = P^T dO
+        product_columns<HD, TILES, false, false>(result, p, g_tile, g, t);   // dV = P^T dO
         store_result<HD>(dv + grad_base, grad_layout.ld, r0, r1, seq, t, result,
                          add_v);
         if (column_partials) {
@@ -623,13 +686,13 @@ attention_warp_backward_kernel(
         for (int n = 0; n < TILES; ++n) {
             // row_dot holds -scale * D_i.
             const float2 dot = *reinterpret_cast<const float2 *>(row_dot + n * 8 + 2 * t);
-            ds[n][0] = p[n][0] * fmaf(ds[n][0], scale, dot.x);
-            ds[n][1] = p[n][1] * fmaf(ds[n][1], scale, dot.y);
-            ds[n][2] = p[n][2] * fmaf(ds[n][2], scale, dot.x);
-            ds[n][3] = p[n][3] * fmaf(ds[n][3], scale, dot.y);
+            ds[n][0] = p[n][0] * fmaf(ds[n][0], scale_pair, dot.x);
+            ds[n][1] = p[n][1] * fmaf(ds[n][1], scale_pair, dot.y);
+            ds[n][2] = p[n][2] * fmaf(ds[n][2], scale_pair, dot.x);
+            ds[n][3] = p[n][3] * fmaf(ds[n][3], scale_pair, dot.y);
         }
         clear(result);
-        product_columns<HD, TILES>(result, ds, q_tile, g, t);   // dK = dS^T Q
+        product_columns<HD, TILES, false, false>(result, ds, q_tile, g, t);   // dK = dS^T Q
         store_result<HD>(dk + grad_base, grad_layout.ld, r0, r1, seq, t, result,
                          add_k);
         if (column_partials) {

@@ -5,9 +5,11 @@
 
 attention  flash attention forward and backward: the tcgen05 kernels
            (vitb200_k_attention_tc*, head dimension 32 or 64) beside the
-           streaming mma.sync kernels (vitb200_k_attention_stream*), head-major
-           tensors, algorithmic TFLOP/s (4 S^2 hd forward, 8 S^2 hd backward
-           per group).
+           streaming mma.sync kernels (vitb200_k_attention_stream*) and, for
+           at most 64 tokens, the whole-group kernels (vitb200_k_attention
+           without a probability matrix); head-major tensors, algorithmic
+           TFLOP/s (4 S^2 hd forward, 8 S^2 hd backward per group) and GB/s
+           (16 / 32 bytes per element of Q).
 gemm       Y = X W forward, the gradient pair dX, dW, and the forward product
            with bias and with bias + GELU, TF32 operands on the tensor cores.
 
@@ -58,7 +60,18 @@ def attention(lib, groups, seq, head_dim, launches):
     scale = ctypes.c_float(1.0 / np.sqrt(head_dim))
     shape = (SIZE(groups), SIZE(seq), SIZE(head_dim), scale)
     head_major = (SIZE(0), SIZE(0), SIZE(1))
-    calls = {
+    calls = {}
+    if seq <= 64 and head_dim in (16, 32):
+        # One block per group, everything between the operand tiles and the
+        # results in registers (mma.sync); probabilities are not written.
+        calls["whole-group forward"] = lambda: lib.vitb200_k_attention(
+            pointer(q), pointer(k), pointer(v), None, pointer(out), *shape, TF32,
+            None)
+        calls["whole-group backward"] = lambda: lib.vitb200_k_attention_backward(
+            pointer(q), pointer(k), pointer(v), None, pointer(out), pointer(dout),
+            pointer(dq), pointer(dk), pointer(dv), pointer(dots), *shape, TF32,
+            None)
+    tcgen05 = {
         "tcgen05 forward": lambda: lib.vitb200_k_attention_tc(
             pointer(q), pointer(k), pointer(v), pointer(out), pointer(lse), *shape,
             *head_major, None),
@@ -66,6 +79,10 @@ def attention(lib, groups, seq, head_dim, launches):
             pointer(q), pointer(k), pointer(v), pointer(out), pointer(dout),
             pointer(lse), pointer(dq), pointer(dk), pointer(dv), pointer(dots),
             *shape, 0, SIZE(0), SIZE(0), SIZE(0), SIZE(1), None),
+    }
+    if head_dim in (32, 64):
+        calls.update(tcgen05)
+    calls.update({
         "streaming forward": lambda: lib.vitb200_k_attention_stream(
             pointer(q), pointer(k), pointer(v), pointer(out), pointer(lse), *shape,
             None),
@@ -73,15 +90,19 @@ def attention(lib, groups, seq, head_dim, launches):
             pointer(q), pointer(k), pointer(v), pointer(out), pointer(dout),
             pointer(lse), pointer(dq), pointer(dk), pointer(dv), pointer(dots),
             *shape, None),
-    }
+    })
     forward_flops = 4.0 * groups * seq * seq * head_dim
     for name, call in calls.items():
         if launches <= 1 and name.startswith("streaming"):
             continue
         ms = timed(call, launches)
         flops = forward_flops * (2.0 if "backward" in name else 1.0)
+        # Q, K, V read and O written forward; O, dO as well and three
+        # gradients written backward.
+        megabytes = rows * head_dim * 4 * (8 if "backward" in name else 4) / 1e6
         print(f"attention {groups} x {seq} x {head_dim} {name}: {ms:.3f} ms, "
-              f"{flops / ms / 1e9:.0f} TFLOP/s", flush=True)
+              f"{flops / ms / 1e9:.0f} TFLOP/s, {megabytes / ms:.0f} GB/s",
+              flush=True)
 
 
 def gemm(lib, m, k, n, launches):
