@@ -432,9 +432,10 @@ def run_reference(args, vh, config, batch, rank, world):
 
 def measure(vh, backend, host_lib, workload, config, batch, micro_batches, steps,
             warmup, rank, local_rank, world, tf32_peak):
-    """`warmup` untimed and 2 x `steps` timed optimiser steps of one workload
-    (one pass for the end-to-end rate, one for device time and the per-op
-    table); returns the fields of a bench line."""
+    """`warmup` untimed and 3 x `steps` timed optimiser steps of one workload
+    (one pass for the end-to-end rate, one for device time, one with an event
+    pair around every op for the per-op table); returns the fields of a bench
+    line."""
     import torch
     import torch.distributed as dist
     backend.set_gradient_accumulation(micro_batches)
@@ -475,10 +476,13 @@ def measure(vh, backend, host_lib, workload, config, batch, micro_batches, steps
     h2d_per_step = (moved["h2d_bytes"] - counters["h2d_bytes"]) / steps
     d2h_per_step = (moved["d2h_bytes"] - counters["d2h_bytes"]) / steps
 
-    # ---- value + per-op roofline: device-busy time over K steps ----------
+    # ---- value: device time over K steps --------------------------------
+    # Two CUDA events on the backend's stream around each stretch of device
+    # work (from the first kernel enqueued after a host synchronisation to the
+    # next synchronisation), summed over the K steps; nothing else is recorded
+    # in the stream, so chained launches stay chained.
     barrier()
     backend.device_busy_ms(reset=True)
-    backend.profile(True)
     launches = backend.kernel_launches()
     paths = backend.kernel_paths()
     with ClockSampler(local_rank) as clocks:
@@ -488,6 +492,13 @@ def measure(vh, backend, host_lib, workload, config, batch, micro_batches, steps
     barrier()
     launches = backend.kernel_launches() - launches
     paths = {k: v - paths[k] for k, v in backend.kernel_paths().items()}
+
+    # ---- per-op roofline: an event pair around every op -----------------
+    backend.profile(True)
+    for _ in range(steps):
+        step()
+    profiled_ms = backend.device_busy_ms(reset=True)
+    barrier()
     entries = backend.profile_entries()
     backend.profile(False)
     declined = backend.declined_ops() - declined
@@ -586,6 +597,7 @@ def measure(vh, backend, host_lib, workload, config, batch, micro_batches, steps
                 "ms_per_step": 1e3 * e2e_seconds / steps,
                 "ms_of_each_step_on_rank0": step_ms},
         "gpu_launches": launches,
+        "ms_per_step_with_op_events": profiled_ms / steps,
         "declined_ops": declined,
         "kernel_paths": paths,
         "roofline": roofline,

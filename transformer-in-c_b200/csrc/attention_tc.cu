@@ -192,6 +192,7 @@ attention_tc_kernel(const __grid_constant__ AttnMaps maps, const AttnParams p) {
     const int my_items = (p.items - int(blockIdx.x) + int(gridDim.x) - 1) / int(gridDim.x);
 
     if ((smem_address(smem) & 1023u) != 0) {
+        grid_dependency_wait();
         if (threadIdx.x == 0) {
             atomicExch(p.status, 16);
         }
@@ -214,6 +215,9 @@ attention_tc_kernel(const __grid_constant__ AttnMaps maps, const AttnParams p) {
     tcgen05_fence_after();
     const uint32_t tmem_base_any = *tmem_slot;
     const uint32_t tmem_base = tmem_base_any;
+    // Set-up is done; everything below reads or writes global memory.
+    grid_dependency_wait();
+    grid_dependency_release();
 
     // A wait that has run out marks the CTA as failed; from then on nobody
     // waits any more and every role runs its loops to their normal end, so no
@@ -928,6 +932,8 @@ attention_row_dots_kernel(const float *__restrict__ out, const float *__restrict
                           float *__restrict__ dots, size_t rows, int seq,
                           HeadLayout out_layout, HeadLayout dout_layout) {
     constexpr int HD = 64;
+    grid_dependency_wait();
+    grid_dependency_release();
     const int lane = threadIdx.x & 31;
     const int part = lane & 15;
     const size_t warps = grid_threads() >> 5;
@@ -1095,7 +1101,8 @@ bool launch(const AttnMaps &maps, AttnParams params, size_t groups,
     params.items = int(items);
     // One persistent CTA per SM (it owns the SM's tensor memory).
     const unsigned grid = unsigned(std::min<size_t>(items, size_t(device_sm_count())));
-    attention_tc_kernel<HD, MODE><<<grid, kAttnThreads, bytes, stream>>>(maps, params);
+    launch_chained(attention_tc_kernel<HD, MODE>, grid, kAttnThreads, bytes,
+                   stream, maps, params);
     ++g_kernel_launches;
     return true;
 }
@@ -1211,8 +1218,8 @@ bool launch_attention_tc_backward(const float *q, const float *k, const float *v
         const size_t rows = groups * seq;
         const unsigned dots_grid =
             unsigned(std::min<size_t>((rows + 63) / 64, size_t(device_sm_count()) * 8));
-        attention_row_dots_kernel<<<dots_grid, 256, 0, stream>>>(
-            out, dout, row_dots, rows, int(seq), out_layout, dout_layout);
+        launch_chained(attention_row_dots_kernel, dots_grid, 256, 0, stream, out,
+                       dout, row_dots, rows, int(seq), out_layout, dout_layout);
         ++g_kernel_launches;
     }
     AttnParams query_params = params;

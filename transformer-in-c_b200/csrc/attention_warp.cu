@@ -474,6 +474,8 @@ attention_warp_forward_kernel(const float *__restrict__ q,
     using S = Shape<HD>;
     __shared__ __align__(16) float k_tile[kTile * S::kPitch];
     __shared__ __align__(16) float v_tile[kTile * S::kPitch];
+    grid_dependency_wait();
+    grid_dependency_release();
     const unsigned group = blockIdx.x;
     const size_t in_base = group_offset<HD>(group, seq, in_layout);
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
@@ -550,6 +552,8 @@ attention_warp_backward_kernel(
     __shared__ __align__(16) float g_tile[kTile * S::kPitch];
     __shared__ __align__(8) float row_lse[kTile];
     __shared__ __align__(8) float row_dot[kTile];
+    grid_dependency_wait();
+    grid_dependency_release();
     const unsigned group = blockIdx.x;
     const size_t in_base = group_offset<HD>(group, seq, in_layout);
     const float *out_base = out + group_offset<HD>(group, seq, out_layout);
@@ -1237,9 +1241,9 @@ bool launch_attention_warp_forward(const float *q, const float *k,
     in_layout = resolve(in_layout, head_dim);
     out_layout = resolve(out_layout, head_dim);
 #define FORWARD(HD, TILES)                                                     \
-    attention_warp_forward_kernel<HD, TILES>                                   \
-        <<<unsigned(groups), kThreads, 0, stream>>>(                           \
-            q, k, v, out, int(seq), scale, in_layout, out_layout)
+    launch_chained(attention_warp_forward_kernel<HD, TILES>, unsigned(groups), \
+                   kThreads, 0, stream, q, k, v, out, int(seq), scale,         \
+                   in_layout, out_layout)
     VITB200_WARP_DISPATCH(head_dim, seq, FORWARD);
 #undef FORWARD
     ++g_kernel_launches;
@@ -1264,11 +1268,10 @@ bool launch_attention_warp_backward(const float *q, const float *k,
     dout_layout = resolve(dout_layout, head_dim);
     grad_layout = resolve(grad_layout, head_dim);
 #define BACKWARD(HD, TILES)                                                    \
-    attention_warp_backward_kernel<HD, TILES>                                  \
-        <<<unsigned(groups), kThreads, 0, stream>>>(                           \
-            q, k, v, out, dout, dq, dk, dv, int(seq), scale, add_q, add_k,     \
-            add_v, in_layout, out_layout, dout_layout, grad_layout,            \
-            column_partials)
+    launch_chained(attention_warp_backward_kernel<HD, TILES>, unsigned(groups),\
+                   kThreads, 0, stream, q, k, v, out, dout, dq, dk, dv,        \
+                   int(seq), scale, add_q, add_k, add_v, in_layout, out_layout,\
+                   dout_layout, grad_layout, column_partials)
     VITB200_WARP_DISPATCH(head_dim, seq, BACKWARD);
 #undef BACKWARD
     ++g_kernel_launches;

@@ -1788,6 +1788,11 @@ int op_zero_gradient(void *context, vitb200_tensor *tensor) {
     return 0;
 }
 
+// Largest gradient buffer that the batched zero fill covers.  Above it the
+// fill's own traffic outweighs the launch it saves, and a product that is the
+// first writer would rather skip the read (see coherent_mark_zero).
+constexpr size_t kBatchedZeroBytes = size_t(1) << 20;
+
 int op_zero_gradients(void *context, vitb200_tensor *const *tensors,
                       size_t count) {
     CudaBackend *backend = self(context);
@@ -1797,8 +1802,20 @@ int op_zero_gradients(void *context, vitb200_tensor *const *tensors,
             return -1;
         }
     }
+    std::vector<const void *> gradients(count);
     for (size_t i = 0; i < count; ++i) {
         coherent_mark_zero(tensors[i]->grad, backend->stream);
+        gradients[i] = tensors[i]->grad;
+    }
+    // The small ones (biases, layer-norm parameters, narrow weight matrices)
+    // are accumulated into by kernels that need the zeros in memory; writing
+    // them all now is one launch instead of a memset node before each.
+    static const bool batched = getenv("VITB200_NO_BATCHED_ZERO_FILL") == nullptr;
+    if (batched && count > 1) {
+        if (coherent_zero_fill_batch(gradients.data(), count, kBatchedZeroBytes,
+                                     backend->stream)) {
+            ++g_kernel_launches;
+        }
     }
     return 0;
 }

@@ -31,6 +31,9 @@ struct Region {
     float *device = nullptr;  // created on first device use
     Owner owner = Owner::Host;
     bool zero_pending = false;  // device contents are an unmaterialised zero fill
+    // The device buffer a batched fill (coherent_zero_fill_batch) has already
+    // zeroed for the pending fill; materialising it then costs nothing.
+    float *zeroed = nullptr;
     unsigned uploads = 0;       // host-to-device copies so far
     bool pinned = false;        // mirror registered with the driver
 };
@@ -318,10 +321,34 @@ bool is_alias(const Region &region) {
 
 void materialise_zero(Region &region, cudaStream_t stream) {
     if (region.zero_pending) {
-        check(cudaMemsetAsync(region.device, 0, region.bytes, stream),
-              "cudaMemsetAsync");
+        if (region.zeroed && region.zeroed == region.device) {
+            g_stats.zero_fills_batched += 1;
+        } else {
+            check(cudaMemsetAsync(region.device, 0, region.bytes, stream),
+                  "cudaMemsetAsync");
+            g_stats.zero_fills_materialised += 1;
+        }
         region.zero_pending = false;
-        g_stats.zero_fills_materialised += 1;
+        region.zeroed = nullptr;
+    }
+}
+
+// Up to kZeroBatch buffers cleared by one launch: a block per 4096 floats.
+constexpr int kZeroBatch = 120;
+constexpr unsigned kZeroFloatsPerBlock = 4096;
+
+struct ZeroBatch {
+    float *buffer[kZeroBatch];
+    unsigned floats[kZeroBatch];
+};
+
+__global__ void __launch_bounds__(256) zero_batch_kernel(const ZeroBatch batch) {
+    float *buffer = batch.buffer[blockIdx.y];
+    const unsigned floats = batch.floats[blockIdx.y];
+    const unsigned begin = blockIdx.x * kZeroFloatsPerBlock;
+    const unsigned end = min(floats, begin + kZeroFloatsPerBlock);
+    for (unsigned i = begin + threadIdx.x; i < end; i += blockDim.x) {
+        buffer[i] = 0.0f;
     }
 }
 
@@ -598,6 +625,7 @@ float *device_view(const void *host_pointer, Access access,
     if (region->zero_pending) {
         if (access == Access::Overwrite) {
             region->zero_pending = false;
+            region->zeroed = nullptr;
             g_stats.zero_fills_elided += 1;
         } else {
             materialise_zero(*region, stream);
@@ -663,7 +691,58 @@ bool coherent_mark_zero(const void *host_pointer, cudaStream_t stream) {
         }
     }
     region->zero_pending = true;
+    region->zeroed = nullptr;
     return true;
+}
+
+size_t coherent_zero_fill_batch(const void *const *host_pointers, size_t count,
+                                size_t max_bytes, cudaStream_t stream) {
+    ZeroBatch batch;
+    Region *members[kZeroBatch];
+    int filled = 0;
+    unsigned longest = 0;
+    size_t cleared = 0;
+    auto launch = [&]() {
+        if (filled == 0) {
+            return;
+        }
+        const dim3 grid((longest + kZeroFloatsPerBlock - 1) / kZeroFloatsPerBlock,
+                        unsigned(filled));
+        zero_batch_kernel<<<grid, 256, 0, stream>>>(batch);
+        check(cudaGetLastError(), "zero_batch_kernel");
+        for (int i = 0; i < filled; ++i) {
+            members[i]->zeroed = members[i]->device;
+        }
+        cleared += size_t(filled);
+        filled = 0;
+        longest = 0;
+    };
+    for (size_t i = 0; i < count; ++i) {
+        Region *region = host_pointers[i] ? find_base(host_pointers[i]) : nullptr;
+        // Only a plain pending fill over a buffer that already exists: no
+        // buffer is created for a gradient that nobody may write this step.
+        if (!region || !region->zero_pending || region->lazy || region->feeds ||
+            !region->device || region->zeroed == region->device ||
+            region->bytes == 0 || region->bytes > max_bytes) {
+            continue;
+        }
+        bool listed = false;   // the caller may name a buffer twice
+        for (int j = 0; j < filled; ++j) {
+            listed = listed || members[j] == region;
+        }
+        if (listed) {
+            continue;
+        }
+        members[filled] = region;
+        batch.buffer[filled] = region->device;
+        batch.floats[filled] = unsigned(region->bytes / sizeof(float));
+        longest = batch.floats[filled] > longest ? batch.floats[filled] : longest;
+        if (++filled == kZeroBatch) {
+            launch();
+        }
+    }
+    launch();
+    return cleared;
 }
 
 bool coherent_define_lazy(const void *output_host,
@@ -707,6 +786,7 @@ bool coherent_define_lazy(const void *output_host,
     }
     output->lazy = lazy;
     output->zero_pending = false;
+    output->zeroed = nullptr;
     if (output->owner != Owner::Device) {
         protect(*output, PROT_NONE);
         output->owner = Owner::Device;

@@ -36,6 +36,7 @@ struct CoherenceStats {
     size_t faults_served;
     size_t zero_fills_elided;
     size_t zero_fills_materialised;
+    size_t zero_fills_batched;   // materialised for free after a batched fill
     size_t lazy_defined;
     size_t lazy_materialised;
     size_t lazy_dropped;
@@ -63,6 +64,16 @@ float *device_view(const void *host_pointer, Access access, cudaStream_t stream)
 // device_view_accumulate is told to store instead of add.  Returns false for
 // memory we did not allocate.
 bool coherent_mark_zero(const void *host_pointer, cudaStream_t stream);
+
+// One kernel launch that writes the zeros of every listed buffer whose
+// contents are a pending zero fill, which already has device memory and which
+// holds at most `max_bytes`.  The fills stay pending (a kernel that overwrites
+// the buffer still skips the read), but materialising one later is free.  For
+// the many small gradients that are accumulated into: one launch per step
+// instead of one memset node in front of every accumulating kernel.  Returns
+// the number of buffers cleared.
+size_t coherent_zero_fill_batch(const void *const *host_pointers, size_t count,
+                                size_t max_bytes, cudaStream_t stream);
 
 // Device pointer for a buffer the caller is about to add into.  *was_zero is
 // set when the buffer's current contents are a pending zero fill, in which

@@ -2,6 +2,8 @@
 #pragma once
 
 #include <cstddef>
+#include <cstdlib>
+#include <utility>
 #include <cuda_runtime.h>
 
 namespace vitb200 {
@@ -34,6 +36,55 @@ inline unsigned stream_grid(size_t items) {
     const size_t wanted = (items + kStreamThreads - 1) / kStreamThreads;
     const size_t wave = size_t(device_sm_count()) * kStreamBlocksPerSm;
     return static_cast<unsigned>(wanted < 1 ? 1 : (wanted < wave ? wanted : wave));
+}
+
+// ---------------------------------------------------------------------------
+// Chained launches (programmatic dependent launch).  A kernel launched through
+// launch_chained may be scheduled while its predecessor in the stream is still
+// running: its blocks become resident as the predecessor's leave, run whatever
+// does not touch global memory, and park in grid_dependency_wait() until the
+// predecessor has completed and its writes are visible.  That takes the launch
+// latency and the block set-up out of the gap between two dependent kernels.
+//
+// Rules for a kernel launched this way: every thread calls
+// grid_dependency_wait() before its first access to global memory and before it
+// can return (a grid whose blocks left without waiting would count as complete
+// while its predecessors still run, and its successor's wait would pass too
+// early).  grid_dependency_release() right after it lets the successor's
+// blocks become resident from then on; they park in their own wait.
+__device__ __forceinline__ void grid_dependency_wait() {
+    asm volatile("griddepcontrol.wait;" ::: "memory");
+}
+
+__device__ __forceinline__ void grid_dependency_release() {
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+}
+
+// VITB200_CHAINED_LAUNCHES=0 turns the attribute off (plain stream order).
+inline bool chained_launches_enabled() {
+    static const bool enabled = []() {
+        const char *value = getenv("VITB200_CHAINED_LAUNCHES");
+        return !(value && value[0] == '0');
+    }();
+    return enabled;
+}
+
+template <typename... Params, typename... Args>
+inline cudaError_t launch_chained(void (*kernel)(Params...), dim3 grid,
+                                  dim3 block, size_t shared_bytes,
+                                  cudaStream_t stream, Args &&...args) {
+    cudaLaunchConfig_t config = {};
+    config.gridDim = grid;
+    config.blockDim = block;
+    config.dynamicSmemBytes = shared_bytes;
+    config.stream = stream;
+    cudaLaunchAttribute attribute;
+    attribute.id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attribute.val.programmaticStreamSerializationAllowed =
+        chained_launches_enabled() ? 1 : 0;
+    config.attrs = &attribute;
+    config.numAttrs = 1;
+    return cudaLaunchKernelEx(&config, kernel, std::forward<Args>(args)...);
 }
 
 __device__ __forceinline__ size_t global_thread() {

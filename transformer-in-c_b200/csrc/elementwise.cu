@@ -187,6 +187,8 @@ gelu_backward_sums_kernel(const float *__restrict__ x,
 __global__ void take_column_sums_kernel(float *__restrict__ out,
                                         float *__restrict__ sums, size_t cols,
                                         bool add) {
+    grid_dependency_wait();
+    grid_dependency_release();
     for (size_t c = global_thread(); c < cols; c += grid_threads()) {
         out[c] = (add ? out[c] : 0.0f) + sums[c];
         sums[c] = 0.0f;
@@ -283,8 +285,8 @@ void launch_gelu_backward_sums(const float *x, const float *dy, float *dx,
 
 void launch_take_column_sums(float *out, float *sums, size_t cols, bool add,
                              cudaStream_t stream) {
-    take_column_sums_kernel<<<stream_grid(cols), kStreamThreads, 0, stream>>>(
-        out, sums, cols, add);
+    launch_chained(take_column_sums_kernel, stream_grid(cols), kStreamThreads,
+                   0, stream, out, sums, cols, add);
     ++g_kernel_launches;
 }
 

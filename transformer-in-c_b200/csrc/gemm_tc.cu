@@ -140,6 +140,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a,
     const int lane = threadIdx.x & 31;
     if ((smem_address(smem) & 1023u) != 0) {
         // Never expected; without the alignment the MMA would read garbage.
+        grid_dependency_wait();
         if (threadIdx.x == 0) {
             atomicExch(p.status, 6);
         }
@@ -173,6 +174,10 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a,
     __syncthreads();
     tcgen05_fence_after();
     const uint32_t tmem_base = tmem_base_slot;
+    // Barriers and tensor memory are set up; from here on global memory is
+    // touched, so the kernel before this one in the stream has to be complete.
+    grid_dependency_wait();
+    grid_dependency_release();
     const int tiles = p.m_tiles * p.n_tiles;
     const int items = tiles * p.splits;
     bool ok = true;
@@ -959,26 +964,28 @@ int launch_gemm_tc(const TcGemm &g, cudaStream_t stream) {
         }
     }
     if (tall && second == kSecondGelu) {
-        gemm_tc_kernel<256, 256, kSecondGelu>
-            <<<grid, kThreadsTall, smem_bytes, stream>>>(map_a, map_b, map_d, map_d2, p);
+        launch_chained(gemm_tc_kernel<256, 256, kSecondGelu>, grid,
+                       kThreadsTall, smem_bytes, stream, map_a, map_b, map_d,
+                       map_d2, p);
     } else if (tall) {
-        gemm_tc_kernel<256, 256, 0><<<grid, kThreadsTall, smem_bytes, stream>>>(
-            map_a, map_b, map_d, map_d2, p);
+        launch_chained(gemm_tc_kernel<256, 256, 0>, grid, kThreadsTall,
+                       smem_bytes, stream, map_a, map_b, map_d, map_d2, p);
     } else if (wide) {
-        gemm_tc_kernel<128, 256, 0><<<grid, kThreads, smem_bytes, stream>>>(
-            map_a, map_b, map_d, map_d2, p);
+        launch_chained(gemm_tc_kernel<128, 256, 0>, grid, kThreads, smem_bytes,
+                       stream, map_a, map_b, map_d, map_d2, p);
     } else if (second == kSecondGelu) {
-        gemm_tc_kernel<128, 128, kSecondGelu><<<grid, kThreads, smem_bytes, stream>>>(
-            map_a, map_b, map_d, map_d2, p);
+        launch_chained(gemm_tc_kernel<128, 128, kSecondGelu>, grid, kThreads,
+                       smem_bytes, stream, map_a, map_b, map_d, map_d2, p);
     } else if (second == kSecondResidual) {
-        gemm_tc_kernel<128, 128, kSecondResidual>
-            <<<grid, kThreads, smem_bytes, stream>>>(map_a, map_b, map_d, map_d2, p);
+        launch_chained(gemm_tc_kernel<128, 128, kSecondResidual>, grid,
+                       kThreads, smem_bytes, stream, map_a, map_b, map_d,
+                       map_d2, p);
     } else if (second == kGeluSlope) {
-        gemm_tc_kernel<128, 128, kGeluSlope><<<grid, kThreads, smem_bytes, stream>>>(
-            map_a, map_b, map_d, map_d2, p);
+        launch_chained(gemm_tc_kernel<128, 128, kGeluSlope>, grid, kThreads,
+                       smem_bytes, stream, map_a, map_b, map_d, map_d2, p);
     } else {
-        gemm_tc_kernel<128, 128, 0><<<grid, kThreads, smem_bytes, stream>>>(
-            map_a, map_b, map_d, map_d2, p);
+        launch_chained(gemm_tc_kernel<128, 128, 0>, grid, kThreads, smem_bytes,
+                       stream, map_a, map_b, map_d, map_d2, p);
     }
     ++g_kernel_launches;
     ++g_tc_products;

@@ -68,6 +68,8 @@ layer_norm_kernel(const float *__restrict__ x, const float *__restrict__ gamma,
                   const float *__restrict__ beta, float epsilon,
                   float *__restrict__ y, size_t rows, size_t cols,
                   const float *__restrict__ addend, float *__restrict__ sum) {
+    grid_dependency_wait();
+    grid_dependency_release();
     // With `addend`: the input is x + addend (the residual add the host issued
     // just before, reference src/vit.c:520-523), which is also stored to `sum`.
     constexpr int R = RowsInFlight<NV>::value;
@@ -142,6 +144,8 @@ layer_norm_backward_kernel(const float *__restrict__ x,
                            float *__restrict__ dgamma, float *__restrict__ dbeta,
                            size_t rows, size_t cols, const float *base,
                            float *__restrict__ dx_sums) {
+    grid_dependency_wait();
+    grid_dependency_release();
     __shared__ float4 fold[kWarpsPerBlock][32];
     const int lane = threadIdx.x & 31;
     const int warp_in_block = threadIdx.x >> 5;
@@ -360,17 +364,17 @@ void launch_layer_norm(const float *x, const float *gamma, const float *beta,
                                                               epsilon, y, rows,
                                                               cols);
     } else if (slots <= 1) {
-        layer_norm_kernel<1><<<grid, block, 0, stream>>>(x, gamma, beta, epsilon,
-                                                         y, rows, cols, addend, sum);
+        launch_chained(layer_norm_kernel<1>, grid, block, 0, stream, x, gamma,
+                       beta, epsilon, y, rows, cols, addend, sum);
     } else if (slots <= 2) {
-        layer_norm_kernel<2><<<grid, block, 0, stream>>>(x, gamma, beta, epsilon,
-                                                         y, rows, cols, addend, sum);
+        launch_chained(layer_norm_kernel<2>, grid, block, 0, stream, x, gamma,
+                       beta, epsilon, y, rows, cols, addend, sum);
     } else if (slots <= 4) {
-        layer_norm_kernel<4><<<grid, block, 0, stream>>>(x, gamma, beta, epsilon,
-                                                         y, rows, cols, addend, sum);
+        launch_chained(layer_norm_kernel<4>, grid, block, 0, stream, x, gamma,
+                       beta, epsilon, y, rows, cols, addend, sum);
     } else {
-        layer_norm_kernel<8><<<grid, block, 0, stream>>>(x, gamma, beta, epsilon,
-                                                         y, rows, cols, addend, sum);
+        launch_chained(layer_norm_kernel<8>, grid, block, 0, stream, x, gamma,
+                       beta, epsilon, y, rows, cols, addend, sum);
     }
     ++g_kernel_launches;
 }
@@ -390,17 +394,21 @@ void launch_layer_norm_backward(const float *x, const float *gamma,
             launch_column_sums(dx, dx_sums, rows, cols, cols, stream);
         }
     } else if (slots <= 1) {
-        layer_norm_backward_kernel<1><<<grid, block, 0, stream>>>(
-            x, gamma, epsilon, dy, dx, dgamma, dbeta, rows, cols, base, dx_sums);
+        launch_chained(layer_norm_backward_kernel<1>, grid, block, 0, stream, x,
+                       gamma, epsilon, dy, dx, dgamma, dbeta, rows, cols, base,
+                       dx_sums);
     } else if (slots <= 2) {
-        layer_norm_backward_kernel<2><<<grid, block, 0, stream>>>(
-            x, gamma, epsilon, dy, dx, dgamma, dbeta, rows, cols, base, dx_sums);
+        launch_chained(layer_norm_backward_kernel<2>, grid, block, 0, stream, x,
+                       gamma, epsilon, dy, dx, dgamma, dbeta, rows, cols, base,
+                       dx_sums);
     } else if (slots <= 4) {
-        layer_norm_backward_kernel<4><<<grid, block, 0, stream>>>(
-            x, gamma, epsilon, dy, dx, dgamma, dbeta, rows, cols, base, dx_sums);
+        launch_chained(layer_norm_backward_kernel<4>, grid, block, 0, stream, x,
+                       gamma, epsilon, dy, dx, dgamma, dbeta, rows, cols, base,
+                       dx_sums);
     } else {
-        layer_norm_backward_kernel<8><<<grid, block, 0, stream>>>(
-            x, gamma, epsilon, dy, dx, dgamma, dbeta, rows, cols, base, dx_sums);
+        launch_chained(layer_norm_backward_kernel<8>, grid, block, 0, stream, x,
+                       gamma, epsilon, dy, dx, dgamma, dbeta, rows, cols, base,
+                       dx_sums);
     }
     ++g_kernel_launches;
 }

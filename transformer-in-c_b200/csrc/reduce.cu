@@ -19,6 +19,8 @@ template <int V>
 __global__ void __launch_bounds__(kLanesX *kLanesY)
 column_sums_kernel(const float *__restrict__ in, float *__restrict__ out,
                    size_t rows, size_t cols, size_t ld, size_t rows_per_block) {
+    grid_dependency_wait();
+    grid_dependency_release();
     __shared__ float partial[kLanesY][kLanesX * V + 1];
     const size_t col = (size_t(blockIdx.x) * kLanesX + threadIdx.x) * V;
     const size_t row_begin = size_t(blockIdx.y) * rows_per_block;
@@ -94,11 +96,11 @@ void launch_column_sums(const float *in, float *out, size_t rows, size_t cols,
     const dim3 grid(grid_x, static_cast<unsigned>(slices));
     const dim3 block(kLanesX, kLanesY);
     if (vec) {
-        column_sums_kernel<4><<<grid, block, 0, stream>>>(in, out, rows, cols,
-                                                          ld, rows_per_block);
+        launch_chained(column_sums_kernel<4>, grid, block, 0, stream, in, out,
+                       rows, cols, ld, rows_per_block);
     } else {
-        column_sums_kernel<1><<<grid, block, 0, stream>>>(in, out, rows, cols,
-                                                          ld, rows_per_block);
+        launch_chained(column_sums_kernel<1>, grid, block, 0, stream, in, out,
+                       rows, cols, ld, rows_per_block);
     }
     ++g_kernel_launches;
 }
