@@ -431,7 +431,7 @@ def run_reference(args, vh, config, batch, rank, world):
 
 
 def measure(vh, backend, host_lib, workload, config, batch, micro_batches, steps,
-            warmup, rank, local_rank, world, tf32_peak):
+            warmup, rank, local_rank, world, tf32_peak, strict_synchronize=False):
     """`warmup` untimed and 3 x `steps` timed optimiser steps of one workload
     (one pass for the end-to-end rate, one for device time, one with an event
     pair around every op for the per-op table); returns the fields of a bench
@@ -462,6 +462,12 @@ def measure(vh, backend, host_lib, workload, config, batch, micro_batches, steps
         step()
 
     # ---- e2e: host buffers in, loss out, wall clock ----------------------
+    # The way a training program would run it: the `synchronize` slot deferred
+    # (vitb200_set_deferred_synchronize), so that the host's part of the next
+    # step (zeroing, the memcpy of the next batch into the input tensor, its
+    # upload) overlaps the device's backward pass of this one.  Each step still
+    # returns its own loss; the barrier below waits for the device.
+    backend.set_deferred_synchronize(0 if strict_synchronize else 1)
     barrier()
     counters = backend.memory_counters()
     start = time.perf_counter()
@@ -471,6 +477,7 @@ def measure(vh, backend, host_lib, workload, config, batch, micro_batches, steps
         step_ends.append(time.perf_counter())
     barrier()
     e2e_seconds = time.perf_counter() - start
+    backend.set_deferred_synchronize(0)
     step_ms = [round(1e3 * (b - a), 3) for a, b in zip([start] + step_ends, step_ends)]
     moved = backend.memory_counters()
     h2d_per_step = (moved["h2d_bytes"] - counters["h2d_bytes"]) / steps
@@ -595,6 +602,7 @@ def measure(vh, backend, host_lib, workload, config, batch, micro_batches, steps
                 "h2d_bytes_per_step": h2d_per_step,
                 "d2h_bytes_per_step": d2h_per_step,
                 "ms_per_step": 1e3 * e2e_seconds / steps,
+                "synchronize_slot": "waits" if strict_synchronize else "deferred",
                 "ms_of_each_step_on_rank0": step_ms},
         "gpu_launches": launches,
         "ms_per_step_with_op_events": profiled_ms / steps,
@@ -629,6 +637,9 @@ def main():
     parser.add_argument("--no-tf32-peak", action="store_true",
                         help="do not measure the TF32 matmul rate first (keeps "
                              "library kernels out of a profiler's launch list)")
+    parser.add_argument("--strict-synchronize", action="store_true",
+                        help="end-to-end pass with a `synchronize` slot that "
+                             "waits for the device, as the reference's does")
     parser.add_argument("--replica", type=int, default=0, help=argparse.SUPPRESS)
     parser.add_argument("--global-batch", type=int, default=-1,
                         help="images per optimiser step over all GPUs; 0 = one "
@@ -692,7 +703,7 @@ def main():
     backend.enable()
     line = measure(vh, backend, host_lib, args.workload, config, batch,
                    micro_batches, args.steps, args.warmup, rank, local_rank,
-                   world, tf32_peak)
+                   world, tf32_peak, args.strict_synchronize)
     if tf32_peak:
         line["tf32_peak"] = tf32_peak
     if rank == 0 and not args.no_cpu_baseline and world == 1:
@@ -723,7 +734,7 @@ def main():
         line["cfg5"] = measure(
             vh, backend, host_lib, "cfg5", cfg5_config, cfg5_batch,
             micro_batch_count("cfg5", cfg5_batch), args.cfg5_steps, 3, rank,
-            local_rank, world, tf32_peak)
+            local_rank, world, tf32_peak, args.strict_synchronize)
     backend.disable()
     backend.dp_shutdown()
     backend.close()

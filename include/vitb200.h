@@ -189,6 +189,19 @@ int vitb200_dp_status(CudaBackend *backend);
  * 1 restores plain steps.  0 on success, -1 on a bad argument. */
 int vitb200_set_gradient_accumulation(CudaBackend *backend, int micro_batches);
 
+/* What the op table's `synchronize` slot does.  0 (default): it waits for the
+ * device, like cuda_backend_synchronize of the reference (src/cuda_backend.cu).
+ * 1: it only launches what the backend was holding back and returns.  Results
+ * stay correct either way, because every host access to a tensor the device
+ * owns is caught (page protection) and waits for what it needs, and the loss
+ * of a training step is copied back ahead of time; what changes is that the
+ * host code after the slot (the end of one vit_model_train_batch_smoothed and
+ * the start of the next: zeroing, the memcpy of the next batch) runs while the
+ * device finishes the backward pass and the optimiser step.  A caller that
+ * uses `synchronize` to time the device must leave this off or call
+ * vitb200_device_busy_ms.  Returns the previous setting, -1 without a device. */
+int vitb200_set_deferred_synchronize(CudaBackend *backend, int on);
+
 /* Operand precision of the dense products issued through the op table:
  * VITB200_PRECISION_AUTO (default: TF32 tensor cores for products of at least
  * 16 Mi multiply-adds whose layout TMA can describe, FP32 FMA otherwise),

@@ -474,6 +474,45 @@ def test_host_writes_and_reads_stay_coherent(vit_host_module, host_lib, backend)
     backend.disable()
 
 
+def test_deferred_synchronize_changes_timing_not_results(vit_host_module, host_lib,
+                                                         backend):
+    """With the `synchronize` slot deferred the host runs ahead of the device
+    (it refills the input tensors while the backward pass of the step before is
+    still running); page protection and the prefetched loss keep every value
+    the host sees equal to the run that waits in the slot, up to the order of
+    the floating-point atomics inside the kernels (two runs of either kind
+    differ by as much: 1e-6 relative).  A different batch every step: an upload
+    that overtook, or was overtaken by, the host's next write would move the
+    losses in the second decimal."""
+    vh = vit_host_module
+    config, batch, steps = (1, 28, 28, 4, 64, 4, 2, 11), 96, 6
+    batches = [vh.synthetic_batch(batch, 28, 28, 11, 700 + i) for i in range(steps)]
+    backend.enable()
+    results = []
+    for deferred in (0, 1):
+        assert backend.set_deferred_synchronize(deferred) in (0, 1)
+        gpu = vh.VitHost(host_lib, config, batch)
+        before = backend.memory_counters()
+        losses = [gpu.train_step(images, labels, LR, WD, None, 0.1)
+                  for images, labels in batches]
+        moved = backend.memory_counters()
+        # Nothing but the batch, the labels and the loss crosses the bus.
+        assert (moved["d2h_bytes"] - before["d2h_bytes"]) == 4 * steps
+        results.append((losses, gpu.parameters(0), gpu.parameters(2)))
+        gpu.close()
+    assert backend.set_deferred_synchronize(0) == 1
+    strict, deferred = results
+    np.testing.assert_allclose(deferred[0], strict[0], rtol=2e-5, atol=0)
+    assert np.abs(np.diff(strict[0])).min() > 1e-3
+    for which in (1, 2):
+        for name in strict[which]:
+            ours = drop_key_bias(name, deferred[which][name], config[4])
+            theirs = drop_key_bias(name, strict[which][name], config[4])
+            assert max_relative(ours, theirs) <= 5e-3, name
+    assert backend.tensor_core_status() == 0
+    backend.disable()
+
+
 def test_tensors_allocated_before_enable_fall_back_to_cpu(vit_host_module,
                                                           host_lib, backend):
     """Ops on calloc'ed tensors are declined (non-zero return), so the host

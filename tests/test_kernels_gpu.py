@@ -80,6 +80,8 @@ def test_gemm_fp32_forward_and_backward(lib, m, k, n):
     (16, 16, 16), (50176, 16, 128), (1024, 256, 768), (300, 512, 512),
     (2048, 256, 256), (4000, 1024, 256), (777, 288, 512), (5000, 512, 2048),
     (513, 512, 1536), (256, 256, 256), (39 * 256 + 7, 384, 1536),
+    # Several rounds of tiles over the persistent grid, ragged last row tile.
+    (40013, 128, 384), (50017, 512, 128), (38000, 64, 256),
 ])
 def test_gemm_tf32_tensor_cores(lib, m, k, n):
     """tcgen05 kind::tf32 path: operands keep 10 mantissa bits, accumulation is
@@ -104,7 +106,8 @@ def test_gemm_tf32_tensor_cores(lib, m, k, n):
 
 @pytest.mark.parametrize("precision", [FP32, TF32], ids=["fp32", "tf32"])
 @pytest.mark.parametrize("m,k,n", [(1600, 128, 384), (300, 64, 96), (1000, 512, 128),
-                                   (1000, 512, 512), (2304, 384, 1536)])
+                                   (1000, 512, 512), (2304, 384, 1536),
+                                   (40013, 128, 512)])
 @pytest.mark.parametrize("extra", ["bias", "bias+gelu", "bias+residual", "gelu"])
 def test_gemm_fused_epilogues(lib, m, k, n, extra, precision):
     """y = x w + bias with gelu(y) or residual + y produced by the same launch
@@ -134,7 +137,7 @@ def test_gemm_fused_epilogues(lib, m, k, n, extra, precision):
 
 @pytest.mark.parametrize("m,k,n", [
     (1600, 512, 128), (300, 96, 64), (130, 48, 32), (4096, 2048, 512),
-    (25600, 512, 128), (129, 132, 36),
+    (25600, 512, 128), (129, 132, 36), (40013, 512, 128),
 ])
 @pytest.mark.parametrize("with_sums", [False, True], ids=["plain", "sums"])
 def test_gemm_backward_through_gelu(lib, m, k, n, with_sums):

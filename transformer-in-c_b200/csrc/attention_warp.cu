@@ -465,7 +465,7 @@ __device__ __forceinline__ void softmax_rows(float (&s)[8][4], int seq, int t,
 }
 
 template <int HD, int TILES>
-__global__ void __launch_bounds__(kThreads)
+__global__ void __launch_bounds__(kThreads, HD == 16 ? 16 : 8)
 attention_warp_forward_kernel(const float *__restrict__ q,
                               const float *__restrict__ k,
                               const float *__restrict__ v,

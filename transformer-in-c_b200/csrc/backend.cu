@@ -177,6 +177,7 @@ struct CudaBackend {
     double busy_ms = 0.0;
     // Optional per-op timing (vitb200_profile_enable).
     bool profiling = false;
+    bool deferred_synchronize = false;   // see vitb200_set_deferred_synchronize
     std::vector<OpStat> op_stats;
     std::vector<PendingOp> pending_ops;
     std::vector<cudaEvent_t> free_events;
@@ -1947,6 +1948,11 @@ int op_softmax_cross_entropy(void *context, const vitb200_tensor *logits,
         launch_softmax_cross_entropy(z, t, w, label_smoothing, l, g, row_losses,
                                      logits->rows, logits->cols, backend->stream);
     }
+    if (backend->deferred_synchronize) {
+        // The host reads the loss at the end of the step: send it on its way
+        // now, so that the read waits for the forward pass only.
+        coherent_prefetch_host(loss->data, backend->stream);
+    }
     return 0;
 }
 
@@ -2130,8 +2136,25 @@ int op_adamw_step_parameters(void *context,
     return 0;
 }
 
+// With deferred synchronisation the slot only launches what was held back:
+// nothing the host can observe depends on the wait, because every host access
+// to memory the device owns faults and waits for exactly what it needs
+// (coherence.cu), and the step's loss is prefetched.  The host then prepares
+// the next step (zeroing, the copy of the next batch into the input tensor)
+// while the device is still in the backward pass of this one.
 void op_synchronize(void *context) {
-    settle_timers(self(context));
+    CudaBackend *backend = self(context);
+    if (backend->deferred_synchronize) {
+        flush_pending(backend);
+        if (const int code = gemm_tc_status()) {
+            fprintf(stderr,
+                    "vitb200: a tensor-core kernel gave up waiting (code %d)\n",
+                    code);
+            abort();
+        }
+        return;
+    }
+    settle_timers(backend);
 }
 
 // Every op slot goes through this wrapper, which counts the calls the slot
@@ -2983,6 +3006,23 @@ extern "C" double vitb200_device_busy_ms(CudaBackend *backend, int reset) {
         backend->busy_ms = 0.0;
     }
     return ms;
+}
+
+int poll_exchange() {
+    CudaBackend *backend = g_flush_backend;
+    return backend && backend->dp && dp_world(backend->dp) > 1
+               ? dp_poll(backend->dp) : 0;
+}
+
+extern "C" int vitb200_set_deferred_synchronize(CudaBackend *backend, int on) {
+    if (!cuda_backend_available(backend)) {
+        return -1;
+    }
+    settle_timers(backend);
+    const int before = backend->deferred_synchronize ? 1 : 0;
+    backend->deferred_synchronize = on != 0;
+    coherent_set_wait_poll(on ? poll_exchange : nullptr);
+    return before;
 }
 
 extern "C" void vitb200_profile_enable(CudaBackend *backend, int on) {

@@ -36,6 +36,16 @@ struct Region {
     float *zeroed = nullptr;
     unsigned uploads = 0;       // host-to-device copies so far
     bool pinned = false;        // mirror registered with the driver
+    // A page-locked mirror is uploaded by DMA that may still be reading it
+    // after the call returns: recorded behind the copy, waited for before the
+    // host gets to write the mirror again.
+    cudaEvent_t uploaded = nullptr;
+    bool upload_in_flight = false;
+    // Copy of the device contents on its way to page-locked staging memory
+    // (coherent_prefetch_host); valid until the device writes the buffer again.
+    void *staging = nullptr;
+    cudaEvent_t fetched = nullptr;
+    bool prefetched = false;
 };
 
 // Process-global on purpose: the host keeps the release function inside every
@@ -48,7 +58,10 @@ std::map<uintptr_t, Region> &registry() {
 
 CoherenceStats g_stats = {};
 cudaStream_t g_stream = nullptr;
+cudaStream_t g_copy_stream = nullptr;   // device-to-host prefetches
+cudaEvent_t g_produced = nullptr;       // orders a prefetch behind its producer
 void (*g_flush)(void) = nullptr;
+int (*g_wait_poll)(void) = nullptr;
 struct sigaction g_previous_action;
 bool g_handler_installed = false;
 size_t g_page = 4096;
@@ -56,6 +69,10 @@ size_t g_page = 4096;
 // Mirrors at least this large give their pages back to the kernel while the
 // device owns the contents; they are re-populated on copy-back.
 constexpr size_t kDropPagesThreshold = size_t(1) << 21;
+
+// Largest buffer coherent_prefetch_host stages (it is meant for scalars and
+// short vectors the host is known to read next).
+constexpr size_t kPrefetchLimitBytes = 4096;
 
 [[noreturn]] void die(const char *what, const char *detail) {
     fprintf(stderr, "vitb200: %s failed: %s\n", what, detail);
@@ -354,6 +371,29 @@ __global__ void __launch_bounds__(256) zero_batch_kernel(const ZeroBatch batch) 
 
 // Brings the mirror up to date and hands ownership back to the host side.
 // `for_write` selects HOST (exclusive) over SHARED (both valid).
+// Blocks until the event has happened.  With a poll hook installed the wait
+// spins and gives the hook a chance to notice that the event can never happen
+// (a dead peer of a gradient exchange); the hook's non-zero answer ends it.
+void wait_for(cudaEvent_t event) {
+    if (g_wait_poll) {
+        unsigned spins = 0;
+        while (cudaEventQuery(event) == cudaErrorNotReady) {
+            if ((++spins & 1023u) == 0 && g_wait_poll() != 0) {
+                break;
+            }
+        }
+        cudaGetLastError();
+    }
+    check(cudaEventSynchronize(event), "cudaEventSynchronize");
+}
+
+void wait_for_upload(Region &region) {
+    if (region.upload_in_flight) {
+        wait_for(region.uploaded);
+        region.upload_in_flight = false;
+    }
+}
+
 void serve_host_access(Region &region, bool for_write) {
     if (region.feeds && for_write) {
         materialise_readers(region, g_stream);
@@ -361,6 +401,24 @@ void serve_host_access(Region &region, bool for_write) {
     if (region.owner == Owner::Device) {
         if (g_flush) {
             g_flush();
+        }
+        if (region.prefetched && !region.lazy && !region.zero_pending) {
+            // The contents are already on their way: wait for that copy alone,
+            // not for everything queued behind the kernel that produced them.
+            wait_for(region.fetched);
+            region.prefetched = false;
+            protect(region, PROT_READ | PROT_WRITE);
+            memcpy(region.mirror, region.staging, region.bytes);
+            g_stats.device_to_host_copies += 1;
+            g_stats.device_to_host_bytes += region.bytes;
+            g_stats.prefetched_reads += 1;
+            if (for_write) {
+                region.owner = Owner::Host;
+            } else {
+                protect(region, PROT_READ);
+                region.owner = Owner::Shared;
+            }
+            return;
         }
         if (region.lazy) {
             materialise_lazy(region.lazy, g_stream);
@@ -389,6 +447,7 @@ void serve_host_access(Region &region, bool for_write) {
         if (g_flush) {
             g_flush();
         }
+        wait_for_upload(region);
         protect(region, PROT_READ | PROT_WRITE);
         region.owner = Owner::Host;
     }
@@ -494,6 +553,17 @@ void coherent_release(void *context, void *memory) {
     }
     Region region = it->second;
     regions.erase(it);
+    wait_for_upload(region);
+    if (region.uploaded) {
+        cudaEventDestroy(region.uploaded);
+    }
+    if (region.fetched) {
+        cudaEventSynchronize(region.fetched);
+        cudaEventDestroy(region.fetched);
+    }
+    if (region.staging) {
+        cudaFreeHost(region.staging);
+    }
     if (region.pinned) {
         cudaHostUnregister(region.mirror);
     }
@@ -651,8 +721,20 @@ float *device_view(const void *host_pointer, Access access,
         check(cudaMemcpyAsync(region->device, region->mirror, region->bytes,
                               cudaMemcpyHostToDevice, stream),
               "cudaMemcpyAsync(host to device)");
+        if (region->pinned) {
+            if (!region->uploaded) {
+                check(cudaEventCreateWithFlags(&region->uploaded,
+                                               cudaEventDisableTiming),
+                      "cudaEventCreate");
+            }
+            check(cudaEventRecord(region->uploaded, stream), "cudaEventRecord");
+            region->upload_in_flight = true;
+        }
         g_stats.host_to_device_copies += 1;
         g_stats.host_to_device_bytes += region->bytes;
+    }
+    if (access != Access::Read) {
+        region->prefetched = false;
     }
     if (access == Access::Read) {
         if (region->owner == Owner::Host) {
@@ -692,7 +774,40 @@ bool coherent_mark_zero(const void *host_pointer, cudaStream_t stream) {
     }
     region->zero_pending = true;
     region->zeroed = nullptr;
+    region->prefetched = false;
     return true;
+}
+
+bool coherent_prefetch_host(const void *host_pointer, cudaStream_t stream) {
+    Region *region = host_pointer ? find_base(host_pointer) : nullptr;
+    if (!region || region->owner != Owner::Device || !region->device ||
+        region->lazy || region->zero_pending || region->bytes == 0 ||
+        region->bytes > kPrefetchLimitBytes) {
+        return false;
+    }
+    if (!g_copy_stream) {
+        check(cudaStreamCreateWithFlags(&g_copy_stream, cudaStreamNonBlocking),
+              "cudaStreamCreate");
+        check(cudaEventCreateWithFlags(&g_produced, cudaEventDisableTiming),
+              "cudaEventCreate");
+    }
+    if (!region->staging) {
+        check(cudaMallocHost(&region->staging, region->bytes), "cudaMallocHost");
+        check(cudaEventCreateWithFlags(&region->fetched, cudaEventDisableTiming),
+              "cudaEventCreate");
+    }
+    check(cudaEventRecord(g_produced, stream), "cudaEventRecord");
+    check(cudaStreamWaitEvent(g_copy_stream, g_produced, 0), "cudaStreamWaitEvent");
+    check(cudaMemcpyAsync(region->staging, region->device, region->bytes,
+                          cudaMemcpyDeviceToHost, g_copy_stream),
+          "cudaMemcpyAsync(device to host)");
+    check(cudaEventRecord(region->fetched, g_copy_stream), "cudaEventRecord");
+    region->prefetched = true;
+    return true;
+}
+
+void coherent_set_wait_poll(int (*poll)(void)) {
+    g_wait_poll = poll;
 }
 
 size_t coherent_zero_fill_batch(const void *const *host_pointers, size_t count,

@@ -37,6 +37,7 @@ struct CoherenceStats {
     size_t zero_fills_elided;
     size_t zero_fills_materialised;
     size_t zero_fills_batched;   // materialised for free after a batched fill
+    size_t prefetched_reads;     // host reads served from a prefetched copy
     size_t lazy_defined;
     size_t lazy_materialised;
     size_t lazy_dropped;
@@ -122,6 +123,15 @@ bool coherent_lazy_source(const void *output_host, LazyMaterialise function,
 // source when it is an alias.  nullptr for an alias whose source has moved on
 // (the alias then reads a kept copy that has no address of its own).
 const void *coherent_alias_root(const void *host_pointer);
+// Starts copying the buffer's device contents (as of everything enqueued on
+// `stream` so far) to page-locked staging memory on a stream of its own.  A
+// host read that follows waits for that copy only, not for the work enqueued
+// after this call; a device write to the buffer in between cancels it.  For
+// buffers of at most 4096 bytes that the device owns; false otherwise.
+bool coherent_prefetch_host(const void *host_pointer, cudaStream_t stream);
+// Called every ~1000 spins while a host access waits for the device; a
+// non-zero answer ends the spinning (the wait then blocks in the driver).
+void coherent_set_wait_poll(int (*poll)(void));
 // True while the buffer is a pending zero fill (see coherent_mark_zero).
 bool coherent_is_zero_pending(const void *host_pointer);
 

@@ -128,6 +128,8 @@ def load_backend_library():
         [ctypes.POINTER(ctypes.c_ulonglong)] * 3
     lib.vitb200_elision_counters.restype = None
     lib.vitb200_elision_counters.argtypes = [ctypes.POINTER(_size_t)] * 5
+    lib.vitb200_set_deferred_synchronize.restype = ctypes.c_int
+    lib.vitb200_set_deferred_synchronize.argtypes = [ctypes.c_void_p, ctypes.c_int]
     lib.vitb200_timer_begin.restype = ctypes.c_int
     lib.vitb200_timer_begin.argtypes = [ctypes.c_void_p]
     lib.vitb200_timer_end.restype = ctypes.c_float
@@ -341,6 +343,11 @@ class Backend:
         names = ["tensor_core_products", "wide_tile_products", "fma_products",
                  "tensor_core_attention", "streaming_attention"]
         return {n: int(v.value) for n, v in zip(names, values)}
+
+    def set_deferred_synchronize(self, on):
+        """The `synchronize` slot stops waiting for the device (host accesses
+        still wait for what they read); returns the previous setting."""
+        return int(self.lib.vitb200_set_deferred_synchronize(self.handle, int(on)))
 
     def device_busy_ms(self, reset=False):
         return float(self.lib.vitb200_device_busy_ms(self.handle, int(reset)))
