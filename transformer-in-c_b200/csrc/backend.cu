@@ -834,6 +834,10 @@ int op_residual_backward(void *context, vitb200_tensor *left,
         left->grad == right->grad) {
         return -1;
     }
+    // Never parameter gradients in this model; a gradient exchange is told if
+    // they ever are (it counts writers to know when a gradient is complete).
+    dp_gradient_touched(backend->dp, left->grad);
+    dp_gradient_touched(backend->dp, right->grad);
     bool add_a = true, add_b = true;
     const float *g = view(backend, output->grad, Access::Read);
     // A branch gradient that is still a pending zero fill simply becomes the
@@ -873,6 +877,7 @@ int op_accumulate_gradient(void *context, vitb200_tensor *destination,
         destination->grad == source->grad) {
         return -1;
     }
+    dp_gradient_touched(backend->dp, destination->grad);
     bool add = true;
     const float *src = view(backend, source->grad, Access::Read);
     if (alias_if_zero(backend, destination->grad, source->grad)) {
@@ -1158,6 +1163,7 @@ int op_gelu_backward(void *context, const vitb200_tensor *input,
     if (!ours({input->data, input->grad, output->grad})) {
         return -1;
     }
+    dp_gradient_touched(backend->dp, input->grad);
     const float *x = view(backend, input->data, Access::Read);
     const float *dy = view(backend, output->grad, Access::Read);
     bool add = true;
@@ -1911,6 +1917,7 @@ int op_gather_rows_backward(void *context, vitb200_tensor *source,
     if (!ours({source->grad, destination->grad})) {
         return -1;
     }
+    dp_gradient_touched(backend->dp, source->grad);
     float *s = view(backend, source->grad, Access::ReadWrite);
     const float *d = view(backend, destination->grad, Access::Read);
     {

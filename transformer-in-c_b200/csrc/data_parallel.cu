@@ -90,6 +90,9 @@ struct Gradient {
     int expected_producers = 0;  // producers seen in the previous step
     bool overlap = false;   // the producer count is known: safe to reduce early
     bool reduced = false;   // handed to NCCL, or complete inside the arena, this step
+    // Written by an op that does not report through dp_gradient_produced: its
+    // writers cannot be counted, so it is exchanged at the optimiser call.
+    bool other_writers = false;
     size_t offset = 0;      // arena mode: position inside the arena, in floats
     size_t slot = 0;        // arena mode: floats reserved (a multiple of a page)
 };
@@ -350,6 +353,26 @@ int dp_status(const DataParallel *dp) {
     return dp ? dp->error : 0;
 }
 
+void dp_gradient_touched(DataParallel *dp, const void *host_grad) {
+    if (!dp || dp->world == 1) {
+        return;
+    }
+    auto found = dp->gradients.find(host_grad);
+    if (found == dp->gradients.end()) {
+        return;
+    }
+    Gradient &gradient = found->second;
+    if (gradient.reduced) {
+        // Its sum is already on the wire without this contribution.
+        fprintf(stderr,
+                "vitb200: a parameter gradient was written by an op outside the "
+                "exchange's bookkeeping after its all-reduce had started\n");
+        abort();
+    }
+    gradient.other_writers = true;
+    gradient.overlap = false;
+}
+
 void dp_gradient_produced(DataParallel *dp, const void *host_grad,
                           float *device_grad, size_t count) {
     if (!dp || dp->world == 1) {
@@ -448,7 +471,7 @@ float dp_before_optimizer(DataParallel *dp, const void *const *host_grads,
         // Once two steps in a row have written a gradient the same number of
         // times (one op per micro-batch), it is exchanged as soon as the last
         // of those ops has been enqueued.
-        gradient.overlap = dp->optimizer_calls >= 2 &&
+        gradient.overlap = dp->optimizer_calls >= 2 && !gradient.other_writers &&
                            gradient.producers_this_step >= 1 &&
                            gradient.producers_this_step ==
                                gradient.expected_producers;

@@ -58,6 +58,15 @@ int dp_status(const DataParallel *dp);
 void dp_gradient_produced(DataParallel *dp, const void *host_grad,
                           float *device_grad, size_t count);
 
+// Called by ops that add into a gradient buffer without being one of the
+// counted producers above (residual_backward, accumulate_gradient,
+// gather_rows_backward, gelu_backward).  Does nothing for buffers that are not
+// known parameter gradients (this model's never are).  A parameter gradient
+// written this way is from then on exchanged at the optimiser call, when all
+// its writers are certain to have run; if its exchange had already started
+// the process is stopped, because the sum on the wire lacks this write.
+void dp_gradient_touched(DataParallel *dp, const void *host_grad);
+
 // Called by the optimiser slot with the full parameter list, before the norm
 // and update kernels are enqueued: reduces whatever has not been reduced yet,
 // makes the compute stream wait for the exchange, and remembers the list for
