@@ -784,6 +784,7 @@ int launch_gemm_tc(const TcGemm &g, cudaStream_t stream) {
             reinterpret_cast<const void *>(gemm_tc_kernel<128, 128, kSecondResidual>),
             reinterpret_cast<const void *>(gemm_tc_kernel<128, 128, kGeluSlope>),
             reinterpret_cast<const void *>(gemm_tc_kernel<128, 256, 0>),
+            reinterpret_cast<const void *>(gemm_tc_kernel<128, 256, kSecondGelu>),
             reinterpret_cast<const void *>(gemm_tc_kernel<256, 256, 0>),
             reinterpret_cast<const void *>(gemm_tc_kernel<256, 256, kSecondGelu>)};
         for (const void *kernel : kernels) {
@@ -820,9 +821,20 @@ int launch_gemm_tc(const TcGemm &g, cudaStream_t stream) {
     // is a small share of the rows.
     const bool fits = g.m % (2 * kTileM) == 0 || g.m % (2 * kTileM) > kTileM ||
                       g.m >= 16 * kTileM;
-    const bool tall = wide && g.m >= 2 * kTileM && forced_tile_m != 128 &&
-                      ((long_enough && fits) || forced_tile_m == 256);
-    if (gelu_pair && !tall) {
+    bool tall = wide && g.m >= 2 * kTileM && forced_tile_m != 128 &&
+                ((long_enough && fits) || forced_tile_m == 256);
+    // The GELU pair's epilogue (two stores and a GELU per element) takes
+    // longer than the tile's products: the tall tile, whose accumulators are
+    // not double-buffered across tiles, leaves it exposed; the 128 x 256 tile
+    // hides the next tile's products behind it (measured 3 to 10 % faster at
+    // [100864,512]x[512,2048] and [65600,384]x[384,1536]).
+    static const bool gelu_pair_tall = getenv("VITB200_TC_GELU_TALL") != nullptr;
+    if (gelu_pair && tall && !gelu_pair_tall) {
+        tall = false;
+    }
+    if (gelu_pair && !long_enough) {
+        // Short reductions: two CTAs per SM on 128 x 128 tiles measured
+        // better (0.192 against 0.204 ms at [100864,256]x[256,1024]).
         wide = false;
     }
     const int tile_n = wide ? 256 : kTileN;
@@ -969,6 +981,9 @@ int launch_gemm_tc(const TcGemm &g, cudaStream_t stream) {
                        map_d2, p);
     } else if (tall) {
         launch_chained(gemm_tc_kernel<256, 256, 0>, grid, kThreadsTall,
+                       smem_bytes, stream, map_a, map_b, map_d, map_d2, p);
+    } else if (wide && second == kSecondGelu) {
+        launch_chained(gemm_tc_kernel<128, 256, kSecondGelu>, grid, kThreads,
                        smem_bytes, stream, map_a, map_b, map_d, map_d2, p);
     } else if (wide) {
         launch_chained(gemm_tc_kernel<128, 256, 0>, grid, kThreads, smem_bytes,
