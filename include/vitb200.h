@@ -77,6 +77,16 @@ void vitb200_elision_counters(size_t *zero_fills_elided,
                               size_t *lazy_defined, size_t *lazy_materialised,
                               size_t *lazy_dropped);
 
+/* Zero fills that had to be written because a kernel needed the zeros in
+ * memory: issued one by one as memset nodes in front of that kernel
+ * (`memsets`), or found already done by the one launch per
+ * ops_zero_gradients call that clears every small gradient buffer
+ * (`batched`).  prefetched_reads: host reads served from a copy that was
+ * started ahead of time (the loss of a step with the synchronize slot
+ * deferred).  Any pointer may be NULL. */
+void vitb200_zero_fill_counters(size_t *memsets, size_t *batched,
+                                size_t *prefetched_reads);
+
 /* Ops the backend merged into a neighbour since it was created: bias / GELU
  * ops carried by a product's epilogue, head split / merge ops absorbed by the
  * attention kernels, and bias gradients taken from column sums that the

@@ -493,11 +493,22 @@ def test_deferred_synchronize_changes_timing_not_results(vit_host_module, host_l
         assert backend.set_deferred_synchronize(deferred) in (0, 1)
         gpu = vh.VitHost(host_lib, config, batch)
         before = backend.memory_counters()
+        fills_before = backend.zero_fill_counters()
         losses = [gpu.train_step(images, labels, LR, WD, None, 0.1)
                   for images, labels in batches]
         moved = backend.memory_counters()
         # Nothing but the batch, the labels and the loss crosses the bus.
         assert (moved["d2h_bytes"] - before["d2h_bytes"]) == 4 * steps
+        fills = backend.zero_fill_counters()
+        # With the slot deferred every loss read is served by its prefetch.
+        assert (fills["prefetched_reads"] - fills_before["prefetched_reads"] ==
+                (steps if deferred else 0))
+        # From the second step on (the buffers exist by then) the zeros every
+        # accumulating kernel needs come from the batched fill: no memset
+        # nodes between the kernels of a step.  All gradients of this model
+        # are below the batched fill's size limit.
+        assert fills["batched"] - fills_before["batched"] >= 15 * (steps - 1)
+        assert fills["memsets"] - fills_before["memsets"] <= 60
         results.append((losses, gpu.parameters(0), gpu.parameters(2)))
         gpu.close()
     assert backend.set_deferred_synchronize(0) == 1

@@ -2405,6 +2405,14 @@ extern "C" void cuda_backend_disable_device_execution(CudaBackend *backend) {
     backend->enabled = 0;
 }
 
+extern "C" void vitb200_zero_fill_counters(size_t *memsets, size_t *batched,
+                                           size_t *prefetched_reads) {
+    const CoherenceStats s = coherence_stats();
+    if (memsets) *memsets = s.zero_fills_materialised;
+    if (batched) *batched = s.zero_fills_batched;
+    if (prefetched_reads) *prefetched_reads = s.prefetched_reads;
+}
+
 extern "C" unsigned long long vitb200_kernel_launches(void) {
     return g_kernel_launches;
 }
@@ -3029,6 +3037,7 @@ extern "C" int vitb200_set_deferred_synchronize(CudaBackend *backend, int on) {
     const int before = backend->deferred_synchronize ? 1 : 0;
     backend->deferred_synchronize = on != 0;
     coherent_set_wait_poll(on ? poll_exchange : nullptr);
+    coherent_set_overlapped_uploads(on != 0);
     return before;
 }
 

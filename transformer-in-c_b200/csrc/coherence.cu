@@ -46,6 +46,11 @@ struct Region {
     void *staging = nullptr;
     cudaEvent_t fetched = nullptr;
     bool prefetched = false;
+    // Overlapped uploads (see upload_beside_compute): the device buffer the
+    // previous upload went to, and the point of the compute stream after
+    // which nothing reads it any more.
+    float *spare = nullptr;
+    cudaEvent_t spare_free = nullptr;
 };
 
 // Process-global on purpose: the host keeps the release function inside every
@@ -62,6 +67,7 @@ cudaStream_t g_copy_stream = nullptr;   // device-to-host prefetches
 cudaEvent_t g_produced = nullptr;       // orders a prefetch behind its producer
 void (*g_flush)(void) = nullptr;
 int (*g_wait_poll)(void) = nullptr;
+bool g_overlap_uploads = false;
 struct sigaction g_previous_action;
 bool g_handler_installed = false;
 size_t g_page = 4096;
@@ -73,6 +79,9 @@ constexpr size_t kDropPagesThreshold = size_t(1) << 21;
 // Largest buffer coherent_prefetch_host stages (it is meant for scalars and
 // short vectors the host is known to read next).
 constexpr size_t kPrefetchLimitBytes = 4096;
+
+// Smallest input an upload beside the compute stream is set up for.
+constexpr size_t kOverlapUploadBytes = size_t(1) << 18;
 
 [[noreturn]] void die(const char *what, const char *detail) {
     fprintf(stderr, "vitb200: %s failed: %s\n", what, detail);
@@ -564,6 +573,13 @@ void coherent_release(void *context, void *memory) {
     if (region.staging) {
         cudaFreeHost(region.staging);
     }
+    if (region.spare) {
+        // Its last readers are in the compute stream, which is also where a
+        // pooled buffer's next user will be.
+        recycle(region.spare, region.mapped);
+        g_stats.device_bytes -= region.mapped;
+        cudaEventDestroy(region.spare_free);
+    }
     if (region.pinned) {
         cudaHostUnregister(region.mirror);
     }
@@ -654,6 +670,54 @@ bool coherent_owns(const void *host_pointer) {
     return host_pointer && find_base(host_pointer) != nullptr;
 }
 
+void ensure_copy_stream() {
+    if (!g_copy_stream) {
+        check(cudaStreamCreateWithFlags(&g_copy_stream, cudaStreamNonBlocking),
+              "cudaStreamCreate");
+        check(cudaEventCreateWithFlags(&g_produced, cudaEventDisableTiming),
+              "cudaEventCreate");
+    }
+}
+
+// The upload of a large, repeatedly rewritten input (the image batch) taken off
+// the compute stream: with the host running ahead of the device, the copy then
+// happens while the previous step's backward pass runs instead of between the
+// optimiser and the next forward pass.  The input gets two device buffers used
+// in turn.  The one written now held the batch before last; its readers were
+// all enqueued before the previous upload, which left an event behind them on
+// the compute stream (spare_free) that the copy waits for.  The compute stream
+// waits for the copy, and leaves the same kind of event for the buffer that has
+// just been retired.
+void upload_beside_compute(Region &region, cudaStream_t stream) {
+    ensure_copy_stream();
+    if (!region.spare) {
+        void *memory = nullptr;
+        check(cudaMalloc(&memory, region.mapped), "cudaMalloc");
+        region.spare = static_cast<float *>(memory);
+        g_stats.device_bytes += region.mapped;
+        check(cudaEventCreateWithFlags(&region.spare_free, cudaEventDisableTiming),
+              "cudaEventCreate");
+    } else {
+        check(cudaStreamWaitEvent(g_copy_stream, region.spare_free, 0),
+              "cudaStreamWaitEvent");
+    }
+    float *retired = region.device;
+    region.device = region.spare;
+    region.spare = retired;
+    check(cudaMemcpyAsync(region.device, region.mirror, region.bytes,
+                          cudaMemcpyHostToDevice, g_copy_stream),
+          "cudaMemcpyAsync(host to device)");
+    if (!region.uploaded) {
+        check(cudaEventCreateWithFlags(&region.uploaded, cudaEventDisableTiming),
+              "cudaEventCreate");
+    }
+    check(cudaEventRecord(region.uploaded, g_copy_stream), "cudaEventRecord");
+    region.upload_in_flight = true;
+    check(cudaStreamWaitEvent(stream, region.uploaded, 0), "cudaStreamWaitEvent");
+    // Everything that reads the retired buffer is in the stream by now.
+    check(cudaEventRecord(region.spare_free, stream), "cudaEventRecord");
+}
+
 float *device_view(const void *host_pointer, Access access,
                    cudaStream_t stream) {
     Region *region = host_pointer ? find_base(host_pointer) : nullptr;
@@ -718,17 +782,23 @@ float *device_view(const void *host_pointer, Access access,
                 cudaGetLastError();   // stay pageable; clear the error state
             }
         }
-        check(cudaMemcpyAsync(region->device, region->mirror, region->bytes,
-                              cudaMemcpyHostToDevice, stream),
-              "cudaMemcpyAsync(host to device)");
-        if (region->pinned) {
-            if (!region->uploaded) {
-                check(cudaEventCreateWithFlags(&region->uploaded,
-                                               cudaEventDisableTiming),
-                      "cudaEventCreate");
+        if (g_overlap_uploads && region->pinned && access == Access::Read &&
+            region->bytes >= kOverlapUploadBytes && !region->lazy &&
+            !region->feeds && !region->zero_pending && !is_external(region->device)) {
+            upload_beside_compute(*region, stream);
+        } else {
+            check(cudaMemcpyAsync(region->device, region->mirror, region->bytes,
+                                  cudaMemcpyHostToDevice, stream),
+                  "cudaMemcpyAsync(host to device)");
+            if (region->pinned) {
+                if (!region->uploaded) {
+                    check(cudaEventCreateWithFlags(&region->uploaded,
+                                                   cudaEventDisableTiming),
+                          "cudaEventCreate");
+                }
+                check(cudaEventRecord(region->uploaded, stream), "cudaEventRecord");
+                region->upload_in_flight = true;
             }
-            check(cudaEventRecord(region->uploaded, stream), "cudaEventRecord");
-            region->upload_in_flight = true;
         }
         g_stats.host_to_device_copies += 1;
         g_stats.host_to_device_bytes += region->bytes;
@@ -785,12 +855,7 @@ bool coherent_prefetch_host(const void *host_pointer, cudaStream_t stream) {
         region->bytes > kPrefetchLimitBytes) {
         return false;
     }
-    if (!g_copy_stream) {
-        check(cudaStreamCreateWithFlags(&g_copy_stream, cudaStreamNonBlocking),
-              "cudaStreamCreate");
-        check(cudaEventCreateWithFlags(&g_produced, cudaEventDisableTiming),
-              "cudaEventCreate");
-    }
+    ensure_copy_stream();
     if (!region->staging) {
         check(cudaMallocHost(&region->staging, region->bytes), "cudaMallocHost");
         check(cudaEventCreateWithFlags(&region->fetched, cudaEventDisableTiming),
@@ -808,6 +873,10 @@ bool coherent_prefetch_host(const void *host_pointer, cudaStream_t stream) {
 
 void coherent_set_wait_poll(int (*poll)(void)) {
     g_wait_poll = poll;
+}
+
+void coherent_set_overlapped_uploads(bool on) {
+    g_overlap_uploads = on;
 }
 
 size_t coherent_zero_fill_batch(const void *const *host_pointers, size_t count,

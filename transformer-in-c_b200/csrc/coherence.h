@@ -132,6 +132,10 @@ bool coherent_prefetch_host(const void *host_pointer, cudaStream_t stream);
 // Called every ~1000 spins while a host access waits for the device; a
 // non-zero answer ends the spinning (the wait then blocks in the driver).
 void coherent_set_wait_poll(int (*poll)(void));
+// Uploads of large page-locked inputs that are rewritten again and again (the
+// image batch) go through a copy stream and a second device buffer from now
+// on, so that they overlap whatever the compute stream is still busy with.
+void coherent_set_overlapped_uploads(bool on);
 // True while the buffer is a pending zero fill (see coherent_mark_zero).
 bool coherent_is_zero_pending(const void *host_pointer);
 

@@ -128,6 +128,8 @@ def load_backend_library():
         [ctypes.POINTER(ctypes.c_ulonglong)] * 3
     lib.vitb200_elision_counters.restype = None
     lib.vitb200_elision_counters.argtypes = [ctypes.POINTER(_size_t)] * 5
+    lib.vitb200_zero_fill_counters.restype = None
+    lib.vitb200_zero_fill_counters.argtypes = [ctypes.POINTER(_size_t)] * 3
     lib.vitb200_set_deferred_synchronize.restype = ctypes.c_int
     lib.vitb200_set_deferred_synchronize.argtypes = [ctypes.c_void_p, ctypes.c_int]
     lib.vitb200_timer_begin.restype = ctypes.c_int
@@ -291,6 +293,12 @@ class Backend:
         names = ["zero_fills_elided", "zero_fills_materialised", "lazy_defined",
                  "lazy_materialised", "lazy_dropped"]
         return {n: int(v.value) for n, v in zip(names, values)}
+
+    def zero_fill_counters(self):
+        values = [_size_t() for _ in range(3)]
+        self.lib.vitb200_zero_fill_counters(*[ctypes.byref(v) for v in values])
+        return {n: int(v.value)
+                for n, v in zip(["memsets", "batched", "prefetched_reads"], values)}
 
     def augment(self, settings, state, source, destination=None):
         """vitb200_data_augmentation_apply on host arrays.  `settings` maps the
