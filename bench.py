@@ -458,6 +458,10 @@ def measure(vh, backend, host_lib, workload, config, batch, micro_batches, steps
         return host.train_step_raw(images, labels, LR, WD, None, SMOOTHING)
 
     declined = backend.declined_ops()
+    # The warm-up already runs the way the end-to-end pass does (see below), so
+    # that its one-time set-up (a second device buffer for the batch, staging
+    # memory for the loss) is not part of the timed steps.
+    backend.set_deferred_synchronize(0 if strict_synchronize else 1)
     for _ in range(warmup):
         step()
 

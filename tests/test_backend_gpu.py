@@ -203,7 +203,7 @@ def test_matches_committed_reference_fixtures(path, vit_host_module, host_lib,
 
 @pytest.mark.parametrize("config,small,copies,bias_from_producer", [
     ((1, 28, 28, 4, 128, 8, 4, 11), 32, 64, 4),    # cfg 2: batch 2048
-    ((1, 28, 28, 2, 256, 8, 6, 11), 4, 128, 3),    # cfg 3: batch 512, S = 197
+    ((1, 28, 28, 2, 256, 8, 6, 11), 4, 128, 4),    # cfg 3: batch 512, S = 197
 ], ids=["cfg2", "cfg3"])
 def test_bench_size_batch_is_the_small_batch_replicated(config, small, copies,
                                                         bias_from_producer,
@@ -247,8 +247,8 @@ def test_bench_size_batch_is_the_small_batch_replicated(config, small, copies,
         assert max_relative(ours, theirs) <= 2e-3, name
     # At this size everything that can ride on a neighbour does: per block the
     # attention kernels absorb merge_heads and split_heads_backward, and the
-    # bias gradients come from their producers' column sums (all four with
-    # the whole-group attention kernels, three with the streaming ones).
+    # bias gradients come from their producers' column sums (the QKV bias
+    # from the attention backward kernels, whole-group or tcgen05).
     layers = config[6]
     assert fused["head_layouts"] - fused_before["head_layouts"] == 2 * layers
     assert (fused["bias_gradients"] - fused_before["bias_gradients"] ==

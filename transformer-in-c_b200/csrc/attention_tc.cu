@@ -115,6 +115,13 @@ struct AttnParams {
     const float *out, *dout;  // query-gradient kernel: O and dO, for D
     int out_ld, out_heads, dout_ld, dout_heads;
     int add0, add1;           // outputs accumulate
+    // Gradient kernels, optional: [gridDim.x][partial_ld] sums over the rows
+    // of everything this CTA stores, output `i` at column partial_column[i] +
+    // the head's offset (the bias gradient of the projection that produced Q,
+    // K and V is the column sum of their gradients).  Zeroed by the caller.
+    float *column_partials;
+    int partial_ld;
+    int partial_column[2];
     int *status;
 };
 
@@ -449,7 +456,7 @@ attention_tc_kernel(const __grid_constant__ AttnMaps maps, const AttnParams p) {
         // 128-byte swizzle the store map expects and hands it to the copy
         // engine.  Rows past the end of the group are clipped by the map.
         auto store_block = [&](uint32_t (&r)[32], const CUtensorMap *map, const Item &item,
-                               int column, bool add) {
+                               int column, bool add, int partial_column) {
             if (staged) {
                 if (lane == 0) {
                     asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory");
@@ -477,6 +484,24 @@ attention_tc_kernel(const __grid_constant__ AttnMaps maps, const AttnParams p) {
                                  item.m0 + quarter * 32, item.sample);
                 }
                 asm volatile("cp.async.bulk.commit_group;" ::: "memory");
+            }
+            if (MODE != kForward && p.column_partials) {
+                // Column sums of the block's live rows, lane = column (the
+                // swizzle keeps a row's 32 words in 32 different banks), read
+                // while the copy engine reads the block too.
+                const int live = min(32, p.seq - (item.m0 + quarter * 32));
+                float sum = 0.0f;
+#pragma unroll
+                for (int i = 0; i < 32; ++i) {
+                    if (i < live) {
+                        sum += staging[i * 32 + 4 * ((lane >> 2) ^ (i & 7)) + (lane & 3)];
+                    }
+                }
+                if (live > 0) {
+                    atomicAdd(p.column_partials + size_t(blockIdx.x) * p.partial_ld +
+                                  partial_column + item.col0 + column + lane,
+                              sum);
+                }
             }
         };
         auto publish_block = [&]() {
@@ -562,7 +587,7 @@ attention_tc_kernel(const __grid_constant__ AttnMaps maps, const AttnParams p) {
                 }
                 release_results(it);
                 if (block < kBlocks) {
-                    store_block(r, &maps.out[0], item, 32 * block, false);
+                    store_block(r, &maps.out[0], item, 32 * block, false, 0);
                 }
             };
             // One loop body for "transform the group's next tile" and "finish
@@ -709,7 +734,8 @@ attention_tc_kernel(const __grid_constant__ AttnMaps maps, const AttnParams p) {
                     release_results(it);
 #pragma unroll
                     for (int block = 0; block < kBlocks; ++block) {
-                        store_block(r[block], &maps.out[0], item, 32 * block, p.add0 != 0);
+                        store_block(r[block], &maps.out[0], item, 32 * block, p.add0 != 0,
+                                    p.partial_column[0]);
                     }
                 } else {
                     release_results(it);
@@ -845,7 +871,8 @@ attention_tc_kernel(const __grid_constant__ AttnMaps maps, const AttnParams p) {
 #pragma unroll
                 for (int block = 0; block < kBlocks; ++block) {
                     store_block(r[block], &maps.out[wg], item, 32 * block,
-                                (wg ? p.add1 : p.add0) != 0);
+                                (wg ? p.add1 : p.add0) != 0,
+                                wg ? p.partial_column[1] : p.partial_column[0]);
                 }
             };
             int ahead_it = 0, ahead_j = wg - 2;
@@ -1157,6 +1184,10 @@ bool launch_attention_tc_forward(const float *q, const float *k, const float *v,
                     : launch<64, kForward>(maps, params, groups, stream);
 }
 
+size_t attention_tc_partial_rows() {
+    return device_sm_count();
+}
+
 bool launch_attention_tc_backward(const float *q, const float *k, const float *v,
                                   const float *out, const float *dout,
                                   const float *lse, float *dq, float *dk, float *dv,
@@ -1164,9 +1195,13 @@ bool launch_attention_tc_backward(const float *q, const float *k, const float *v
                                   size_t head_dim, float scale, bool add_q,
                                   bool add_k, bool add_v, cudaStream_t stream,
                                   HeadLayout in_layout, HeadLayout out_layout,
-                                  HeadLayout dout_layout, HeadLayout grad_layout) {
+                                  HeadLayout dout_layout, HeadLayout grad_layout,
+                                  float *column_partials) {
     if (!attention_tc_supported(seq, head_dim) || groups == 0) {
         return false;
+    }
+    if (column_partials && (add_q || add_k || add_v)) {
+        return false;   // the sums would lack what the outputs already hold
     }
     in_layout = resolved(in_layout, head_dim);
     out_layout = resolved(out_layout, head_dim);
@@ -1227,6 +1262,22 @@ bool launch_attention_tc_backward(const float *q, const float *k, const float *v
     AttnParams key_params = params;
     key_params.add0 = add_v ? 1 : 0;
     key_params.add1 = add_k ? 1 : 0;
+    if (column_partials) {
+        // Rows of the partial matrix: one per CTA of either kernel's grid,
+        // columns in the order of the projected gradient, [dQ | dK | dV].
+        const int d_model = grad_layout.heads * hd;
+        if (cudaMemsetAsync(column_partials, 0,
+                            size_t(attention_tc_partial_rows()) * 3 * d_model *
+                                sizeof(float),
+                            stream) != cudaSuccess) {
+            return false;
+        }
+        query_params.column_partials = key_params.column_partials = column_partials;
+        query_params.partial_ld = key_params.partial_ld = 3 * d_model;
+        query_params.partial_column[0] = 0;
+        key_params.partial_column[0] = 2 * d_model;   // dV
+        key_params.partial_column[1] = d_model;       // dK
+    }
     if (hd == 32) {
         return launch<32, kGradQuery>(query_maps, query_params, groups, stream) &&
                launch<32, kGradKeyValue>(key_maps, key_params, groups, stream);

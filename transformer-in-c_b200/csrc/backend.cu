@@ -530,13 +530,21 @@ bool long_attention_backward(CudaBackend *backend, const float *q, const float *
                              bool add_v, HeadLayout in_layout = HeadLayout(),
                              HeadLayout out_layout = HeadLayout(),
                              HeadLayout dout_layout = HeadLayout(),
-                             HeadLayout grad_layout = HeadLayout()) {
+                             HeadLayout grad_layout = HeadLayout(),
+                             float *column_partials = nullptr,
+                             bool *partials_written = nullptr) {
+    if (partials_written) {
+        *partials_written = false;
+    }
     if (tc_attention_wanted(seq, head_dim) &&
         launch_attention_tc_backward(q, k, v, out, dout, lse, dq, dk, dv, row_dots,
                                      groups, seq, head_dim, scale, add_q, add_k,
                                      add_v, backend->stream, in_layout, out_layout,
-                                     dout_layout, grad_layout)) {
+                                     dout_layout, grad_layout, column_partials)) {
         backend->tc_attention_launches += 1;
+        if (partials_written) {
+            *partials_written = column_partials != nullptr;
+        }
         return true;
     }
     if (launch_attention_stream_backward(q, k, v, out, dout, lse, dq, dk, dv,
@@ -573,7 +581,8 @@ void run_attention(CudaBackend *backend, const PendingAttention &pending,
     }
 }
 
-void run_attention_backward(CudaBackend *backend,
+// Returns whether `column_partials` (when given) was filled.
+bool run_attention_backward(CudaBackend *backend,
                             const PendingAttentionBackward &pending, float *dq,
                             float *dk, float *dv, bool add_q, bool add_k,
                             bool add_v, HeadLayout grad_layout,
@@ -581,6 +590,7 @@ void run_attention_backward(CudaBackend *backend,
     OpScope scope(backend, "multi_head_attention_backward", pending.bytes,
                   pending.flops);
     const size_t groups = pending.batch * pending.heads;
+    bool partials_written = column_partials != nullptr;
     if (pending.kind == 3) {
         float *dots = scratch<float>(backend, backend->rows_scratch,
                                      groups * pending.seq);
@@ -589,7 +599,7 @@ void run_attention_backward(CudaBackend *backend,
             pending.lse, dq, dk, dv, dots, groups, pending.seq,
             pending.head_dim, pending.scale, add_q, add_k, add_v,
             pending.in_layout, pending.out_layout, pending.dout_layout,
-            grad_layout);
+            grad_layout, column_partials, &partials_written);
     } else if (pending.kind == 2) {
         launch_attention_warp_backward(
             pending.q, pending.k, pending.v, pending.out, pending.dout, dq, dk,
@@ -604,7 +614,9 @@ void run_attention_backward(CudaBackend *backend,
             pending.scale, add_q, add_k, add_v, true, backend->stream,
             pending.in_layout, pending.out_layout, pending.dout_layout,
             grad_layout);
+        partials_written = false;
     }
+    return partials_written;
 }
 
 // Held-back attention kernels, in their plain form: results go to the
@@ -1365,13 +1377,21 @@ int op_split_heads_backward(void *context, vitb200_tensor *projected,
         // writes: the QKV bias gradient the host asks for next
         // (reference src/vit.c:588-591) then sums [batch, 3d] instead of
         // [batch * seq, 3d].
-        float *partials = pending.kind == 2
+        // (Whole-group kernels: one row per sample.  tcgen05 kernels: one row
+        // per CTA of their persistent grid.)
+        const bool from_tc = pending.kind == 3 &&
+                             tc_attention_wanted(seq, pending.head_dim);
+        const size_t partial_rows =
+            pending.kind == 2 ? batch : (from_tc ? attention_tc_partial_rows() : 0);
+        float *partials = partial_rows
             ? scratch<float>(backend, backend->column_partials,
-                             batch * 3 * d_model)
+                             partial_rows * 3 * d_model)
             : nullptr;
-        run_attention_backward(backend, pending, p, p + d_model,
-                               p + 2 * d_model, false, false, false,
-                               grad_layout, partials);
+        if (!run_attention_backward(backend, pending, p, p + d_model,
+                                    p + 2 * d_model, false, false, false,
+                                    grad_layout, partials)) {
+            partials = nullptr;
+        }
         const vitb200_tensor *parts[3] = {query, key, value};
         for (size_t which = 0; which < 3; ++which) {
             if (!define_head_view(backend, parts[which]->grad, projected->grad,
@@ -1387,7 +1407,7 @@ int op_split_heads_backward(void *context, vitb200_tensor *projected,
         backend->fused_head_layouts += 1;
         if (partials) {
             column_memo_commit(backend, p, batch * seq, 3 * d_model, partials,
-                               batch);
+                               partial_rows);
         }
         return 0;
     }

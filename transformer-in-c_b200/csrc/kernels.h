@@ -235,7 +235,13 @@ bool launch_attention_tc_backward(const float *q, const float *k, const float *v
                                   HeadLayout in_layout = HeadLayout(),
                                   HeadLayout out_layout = HeadLayout(),
                                   HeadLayout dout_layout = HeadLayout(),
-                                  HeadLayout grad_layout = HeadLayout());
+                                  HeadLayout grad_layout = HeadLayout(),
+                                  float *column_partials = nullptr);
+// column_partials (optional, token-major gradients that are overwritten): the
+// kernels leave attention_tc_partial_rows() rows of 3 * heads * head_dim
+// column sums of what they wrote, in the order [dQ | dK | dV] of the projected
+// gradient; their column sums are the column sums of that gradient.
+size_t attention_tc_partial_rows();
 // recompute = true: `probabilities` is not read; P is rebuilt from Q and K.
 bool launch_attention_small_backward(const float *q, const float *k,
                                      const float *v, const float *probabilities,
