@@ -18,17 +18,20 @@ line also carries a "cfg5" object: the data-parallel configuration (d 512, 12
 layers, global batch 4096) measured the same way at the same GPU count, so a
 run at 1, 2, 4 and 8 GPUs yields its strong-scaling curve.
 
-Timed quantities
+Timed quantities (three passes of K steps each, after W warm-up steps)
   e2e    wall clock over K steps called with HOST buffers: per step the host
          copies images + labels in, the backend uploads them, and the loss is
-         read back (one device->host sync per step).
-  value  the same K steps, counting only the time the device stream was busy
-         between the first kernel after the uploads and the final synchronise
-         (CUDA events on the backend's stream): throughput with the batch
-         already resident in HBM.
-  roofline  the op with the largest share of device time, timed with CUDA
-         event pairs around each of its launches inside the same K steps;
-         achieved = its algorithmic bytes (or flops) / that time.
+         read back.  The `synchronize` slot is deferred in this pass
+         (vitb200_set_deferred_synchronize; --strict-synchronize turns that
+         off), so the host's share of a step overlaps the device's backward
+         pass of the step before; the pass ends with a device synchronise.
+  value  K more steps, counting only the time the device stream was busy
+         between the first op after the uploads and the synchronise that ends
+         the step (two CUDA events on the backend's stream, nothing else in
+         it): throughput with the batch already resident in HBM.
+  roofline  K more steps with a CUDA event pair around every op; the op with
+         the largest share is reported: achieved = its algorithmic bytes (or
+         flops) / that time.  ms_per_step_with_op_events is this pass's step.
 """
 import argparse
 import ctypes
