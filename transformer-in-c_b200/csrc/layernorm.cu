@@ -136,8 +136,12 @@ layer_norm_kernel(const float *__restrict__ x, const float *__restrict__ gamma,
     }
 }
 
+// Rows of 257 to 512 columns (NV = 4) would take 150 registers, i.e. one
+// block of eight warps per SM; capped at 128 (eight spilled words) two blocks
+// fit, which took the kernel from 0.55 to 0.66 of the copy rate at 384
+// columns.  The same trade at NV = 2 (three blocks, 29 spilled words) lost.
 template <int NV>
-__global__ void __launch_bounds__(kWarpsPerBlock * 32)
+__global__ void __launch_bounds__(kWarpsPerBlock * 32, NV == 4 ? 2 : 1)
 layer_norm_backward_kernel(const float *__restrict__ x,
                            const float *__restrict__ gamma, float epsilon,
                            const float *__restrict__ dy, float *dx,
