@@ -531,7 +531,8 @@ def measure(vh, backend, host_lib, workload, config, batch, micro_batches, steps
     # timed inside a long step).
     tensor_peak = tf32_peak["sustained_tflops"] if tf32_peak else 0.44 * bf16_peak
     tensor_source = ("TF32 matmul measured by this run" if tf32_peak
-                     else "0.44 x recorded BF16 rate (TF32 not measured at this GPU count)")
+                     else "0.44 x recorded BF16 rate (TF32 rate not measured by this run: "
+                          "several ranks, or --no-tf32-peak)")
     top = max(entries, key=lambda e: e["ms"])
     kernel_name = top["name"]
     traffic_kernel = None
