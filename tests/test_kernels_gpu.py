@@ -82,6 +82,8 @@ def test_gemm_fp32_forward_and_backward(lib, m, k, n):
     (513, 512, 1536), (256, 256, 256), (39 * 256 + 7, 384, 1536),
     # Several rounds of tiles over the persistent grid, ragged last row tile.
     (40013, 128, 384), (50017, 512, 128), (38000, 64, 256),
+    # 256-wide tiles whose last column tile is half outside the matrix.
+    (1024, 384, 1152), (4000, 1536, 384), (2100, 256, 640), (6000, 384, 384),
 ])
 def test_gemm_tf32_tensor_cores(lib, m, k, n):
     """tcgen05 kind::tf32 path: operands keep 10 mantissa bits, accumulation is
@@ -107,7 +109,7 @@ def test_gemm_tf32_tensor_cores(lib, m, k, n):
 @pytest.mark.parametrize("precision", [FP32, TF32], ids=["fp32", "tf32"])
 @pytest.mark.parametrize("m,k,n", [(1600, 128, 384), (300, 64, 96), (1000, 512, 128),
                                    (1000, 512, 512), (2304, 384, 1536),
-                                   (40013, 128, 512)])
+                                   (40013, 128, 512), (2304, 384, 1152)])
 @pytest.mark.parametrize("extra", ["bias", "bias+gelu", "bias+residual", "gelu"])
 def test_gemm_fused_epilogues(lib, m, k, n, extra, precision):
     """y = x w + bias with gelu(y) or residual + y produced by the same launch
