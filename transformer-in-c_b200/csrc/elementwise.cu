@@ -14,6 +14,8 @@ namespace {
 __global__ void add_kernel(const float *__restrict__ a,
                            const float *__restrict__ b, float *__restrict__ out,
                            size_t n) {
+    grid_dependency_wait();
+    grid_dependency_release();
     const size_t vectors = n / 4;
     const float4 *a4 = reinterpret_cast<const float4 *>(a);
     const float4 *b4 = reinterpret_cast<const float4 *>(b);
@@ -32,6 +34,8 @@ __global__ void add_kernel(const float *__restrict__ a,
 __global__ void accumulate_kernel(float *__restrict__ dst,
                                   const float *__restrict__ src, size_t n,
                                   bool add) {
+    grid_dependency_wait();
+    grid_dependency_release();
     const size_t vectors = n / 4;
     float4 *d4 = reinterpret_cast<float4 *>(dst);
     const float4 *s4 = reinterpret_cast<const float4 *>(src);
@@ -50,6 +54,8 @@ __global__ void accumulate2_kernel(float *__restrict__ dst_a,
                                    float *__restrict__ dst_b,
                                    const float *__restrict__ src, size_t n,
                                    bool add_a, bool add_b) {
+    grid_dependency_wait();
+    grid_dependency_release();
     const size_t vectors = n / 4;
     float4 *a4 = reinterpret_cast<float4 *>(dst_a);
     float4 *b4 = reinterpret_cast<float4 *>(dst_b);
@@ -73,6 +79,8 @@ __global__ void accumulate2_kernel(float *__restrict__ dst_a,
 __global__ void bias_add_vec_kernel(const float *in,
                                     const float *__restrict__ bias, float *out,
                                     size_t rows, size_t cols) {
+    grid_dependency_wait();
+    grid_dependency_release();
     const size_t row_vectors = cols / 4;
     const size_t vectors = rows * row_vectors;
     const float4 *i4 = reinterpret_cast<const float4 *>(in);
@@ -88,6 +96,8 @@ __global__ void bias_add_vec_kernel(const float *in,
 __global__ void bias_add_scalar_kernel(const float *in,
                                        const float *__restrict__ bias,
                                        float *out, size_t rows, size_t cols) {
+    grid_dependency_wait();
+    grid_dependency_release();
     const size_t n = rows * cols;
     for (size_t i = global_thread(); i < n; i += grid_threads()) {
         out[i] = in[i] + __ldg(bias + i % cols);
@@ -96,6 +106,8 @@ __global__ void bias_add_scalar_kernel(const float *in,
 
 __global__ void gelu_kernel(const float *__restrict__ in,
                             float *__restrict__ out, size_t n) {
+    grid_dependency_wait();
+    grid_dependency_release();
     const size_t vectors = n / 4;
     const float4 *i4 = reinterpret_cast<const float4 *>(in);
     float4 *o4 = reinterpret_cast<float4 *>(out);
@@ -113,6 +125,8 @@ __global__ void gelu_backward_kernel(const float *__restrict__ x,
                                      const float *__restrict__ dy,
                                      float *__restrict__ dx, size_t n,
                                      bool add) {
+    grid_dependency_wait();
+    grid_dependency_release();
     const size_t vectors = n / 4;
     const float4 *x4 = reinterpret_cast<const float4 *>(x);
     const float4 *g4 = reinterpret_cast<const float4 *>(dy);
@@ -145,6 +159,8 @@ gelu_backward_sums_kernel(const float *__restrict__ x,
                           const float *__restrict__ dy, float *__restrict__ dx,
                           float *__restrict__ partials, size_t rows,
                           size_t cols, bool add) {
+    grid_dependency_wait();
+    grid_dependency_release();
     __shared__ float4 fold[kStreamThreads];
     const unsigned row_threads = unsigned(cols / 4);
     const unsigned rows_per_block = kStreamThreads / row_threads;
@@ -198,6 +214,8 @@ __global__ void take_column_sums_kernel(float *__restrict__ out,
 __global__ void scale_by_device_scalar_kernel(float *__restrict__ values,
                                               size_t n,
                                               const float *__restrict__ scale) {
+    grid_dependency_wait();
+    grid_dependency_release();
     const float s = __ldg(scale);
     if (s == 1.0f) {
         return;
@@ -218,47 +236,47 @@ __global__ void scale_by_device_scalar_kernel(float *__restrict__ values,
 
 void launch_add(const float *a, const float *b, float *out, size_t n,
                 cudaStream_t stream) {
-    add_kernel<<<stream_grid(n / 4 + 1), kStreamThreads, 0, stream>>>(a, b, out,
-                                                                      n);
+    launch_chained(add_kernel, stream_grid(n / 4 + 1), kStreamThreads, 0,
+                   stream, a, b, out, n);
     ++g_kernel_launches;
 }
 
 void launch_accumulate(float *dst, const float *src, size_t n, bool add,
                        cudaStream_t stream) {
-    accumulate_kernel<<<stream_grid(n / 4 + 1), kStreamThreads, 0, stream>>>(
-        dst, src, n, add);
+    launch_chained(accumulate_kernel, stream_grid(n / 4 + 1), kStreamThreads, 0,
+                   stream, dst, src, n, add);
     ++g_kernel_launches;
 }
 
 void launch_accumulate2(float *dst_a, float *dst_b, const float *src, size_t n,
                         bool add_a, bool add_b, cudaStream_t stream) {
-    accumulate2_kernel<<<stream_grid(n / 4 + 1), kStreamThreads, 0, stream>>>(
-        dst_a, dst_b, src, n, add_a, add_b);
+    launch_chained(accumulate2_kernel, stream_grid(n / 4 + 1), kStreamThreads,
+                   0, stream, dst_a, dst_b, src, n, add_a, add_b);
     ++g_kernel_launches;
 }
 
 void launch_bias_add(const float *in, const float *bias, float *out,
                      size_t rows, size_t cols, cudaStream_t stream) {
     if (cols % 4 == 0) {
-        bias_add_vec_kernel<<<stream_grid(rows * cols / 4), kStreamThreads, 0,
-                              stream>>>(in, bias, out, rows, cols);
+        launch_chained(bias_add_vec_kernel, stream_grid(rows * cols / 4),
+                       kStreamThreads, 0, stream, in, bias, out, rows, cols);
     } else {
-        bias_add_scalar_kernel<<<stream_grid(rows * cols), kStreamThreads, 0,
-                                 stream>>>(in, bias, out, rows, cols);
+        launch_chained(bias_add_scalar_kernel, stream_grid(rows * cols),
+                       kStreamThreads, 0, stream, in, bias, out, rows, cols);
     }
     ++g_kernel_launches;
 }
 
 void launch_gelu(const float *in, float *out, size_t n, cudaStream_t stream) {
-    gelu_kernel<<<stream_grid(n / 4 + 1), kStreamThreads, 0, stream>>>(in, out,
-                                                                       n);
+    launch_chained(gelu_kernel, stream_grid(n / 4 + 1), kStreamThreads, 0,
+                   stream, in, out, n);
     ++g_kernel_launches;
 }
 
 void launch_gelu_backward(const float *x, const float *dy, float *dx, size_t n,
                           bool add, cudaStream_t stream) {
-    gelu_backward_kernel<<<stream_grid(n / 4 + 1), kStreamThreads, 0, stream>>>(
-        x, dy, dx, n, add);
+    launch_chained(gelu_backward_kernel, stream_grid(n / 4 + 1), kStreamThreads,
+                   0, stream, x, dy, dx, n, add);
     ++g_kernel_launches;
 }
 
@@ -277,9 +295,10 @@ size_t gelu_backward_sums_blocks(size_t rows, size_t cols) {
 void launch_gelu_backward_sums(const float *x, const float *dy, float *dx,
                                float *partials, size_t rows, size_t cols,
                                bool add, cudaStream_t stream) {
-    gelu_backward_sums_kernel<<<unsigned(gelu_backward_sums_blocks(rows, cols)),
-                                kStreamThreads, 0, stream>>>(
-        x, dy, dx, partials, rows, cols, add);
+    launch_chained(gelu_backward_sums_kernel,
+                   unsigned(gelu_backward_sums_blocks(rows, cols)),
+                   kStreamThreads, 0, stream, x, dy, dx, partials, rows, cols,
+                   add);
     ++g_kernel_launches;
 }
 
@@ -292,8 +311,8 @@ void launch_take_column_sums(float *out, float *sums, size_t cols, bool add,
 
 void launch_scale_by_device_scalar(float *values, size_t n, const float *scale,
                                    cudaStream_t stream) {
-    scale_by_device_scalar_kernel<<<stream_grid(n / 4 + 1), kStreamThreads, 0,
-                                    stream>>>(values, n, scale);
+    launch_chained(scale_by_device_scalar_kernel, stream_grid(n / 4 + 1),
+                   kStreamThreads, 0, stream, values, n, scale);
     ++g_kernel_launches;
 }
 

@@ -23,6 +23,8 @@ constexpr int kPitch = kTileM + 4;
 
 __global__ void __launch_bounds__(256)
 gemm_simt_kernel(GemmOperands op, int k_per_split) {
+    grid_dependency_wait();
+    grid_dependency_release();
     __shared__ __align__(16) float a_tile[kTileK][kPitch];
     __shared__ __align__(16) float b_tile[kTileK][kPitch];
     const int tid = threadIdx.x;
@@ -136,8 +138,8 @@ void launch_gemm_simt(const GemmOperands &operands, cudaStream_t stream) {
     int k_per_split = (operands.k + splits - 1) / splits;
     k_per_split = (k_per_split + kTileK - 1) / kTileK * kTileK;
     splits = (operands.k + k_per_split - 1) / k_per_split;
-    gemm_simt_kernel<<<dim3(grid_x, grid_y, splits), 256, 0, stream>>>(
-        operands, k_per_split);
+    launch_chained(gemm_simt_kernel, dim3(grid_x, grid_y, splits), 256, 0,
+                   stream, operands, k_per_split);
     ++g_kernel_launches;
 }
 

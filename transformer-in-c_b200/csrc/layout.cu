@@ -42,6 +42,8 @@ __global__ void split_heads_kernel(const float *__restrict__ projected,
                                    float *__restrict__ q, float *__restrict__ k,
                                    float *__restrict__ v, size_t batch,
                                    size_t seq, size_t d_model, size_t heads) {
+    grid_dependency_wait();
+    grid_dependency_release();
     using T = typename Vec<V>::type;
     const size_t head_dim = d_model / heads;
     const size_t total = batch * seq * d_model / V;
@@ -64,6 +66,8 @@ __global__ void split_heads_backward_kernel(float *__restrict__ projected_grad,
                                             size_t batch, size_t seq,
                                             size_t d_model, size_t heads,
                                             bool add) {
+    grid_dependency_wait();
+    grid_dependency_release();
     using T = typename Vec<V>::type;
     const size_t head_dim = d_model / heads;
     const size_t row_vectors = 3 * d_model / V;
@@ -90,6 +94,8 @@ template <int V>
 __global__ void merge_heads_kernel(const float *__restrict__ attended,
                                    float *__restrict__ merged, size_t batch,
                                    size_t seq, size_t d_model, size_t heads) {
+    grid_dependency_wait();
+    grid_dependency_release();
     using T = typename Vec<V>::type;
     const size_t head_dim = d_model / heads;
     const size_t row_vectors = d_model / V;
@@ -114,6 +120,8 @@ __global__ void merge_heads_backward_kernel(float *__restrict__ attended_grad,
                                             size_t batch, size_t seq,
                                             size_t d_model, size_t heads,
                                             bool add) {
+    grid_dependency_wait();
+    grid_dependency_release();
     using T = typename Vec<V>::type;
     const size_t head_dim = d_model / heads;
     const size_t total = batch * seq * d_model / V;
@@ -134,6 +142,8 @@ __global__ void head_view_kernel(const float *__restrict__ matrix,
                                  float *__restrict__ view, size_t batch,
                                  size_t seq, size_t d_model, size_t heads,
                                  size_t row_floats, size_t col0) {
+    grid_dependency_wait();
+    grid_dependency_release();
     using T = typename Vec<V>::type;
     const size_t head_dim = d_model / heads;
     const size_t total = batch * seq * d_model / V;
@@ -151,6 +161,8 @@ __global__ void extract_patches_kernel(const float *__restrict__ images,
                                        size_t batch, size_t channels,
                                        size_t height, size_t width,
                                        size_t patch) {
+    grid_dependency_wait();
+    grid_dependency_release();
     using T = typename Vec<V>::type;
     const size_t per_row = width / patch;
     const size_t per_image = (height / patch) * per_row;
@@ -178,6 +190,8 @@ __global__ void token_embedding_kernel(const float *__restrict__ patch_tokens,
                                        const float *__restrict__ positional,
                                        float *__restrict__ tokens, size_t batch,
                                        size_t seq, size_t d_model) {
+    grid_dependency_wait();
+    grid_dependency_release();
     using T = typename Vec<V>::type;
     const size_t row_vectors = d_model / V;
     const size_t total = batch * seq * row_vectors;
@@ -202,6 +216,8 @@ __global__ void token_patch_grad_kernel(float *__restrict__ patch_grad,
                                         const float *__restrict__ tokens_grad,
                                         size_t batch, size_t seq,
                                         size_t d_model, bool add) {
+    grid_dependency_wait();
+    grid_dependency_release();
     using T = typename Vec<V>::type;
     const size_t row_vectors = d_model / V;
     const size_t patches = seq - 1;
@@ -223,6 +239,8 @@ __global__ void gather_rows_kernel(const float *__restrict__ strided,
                                    float *__restrict__ compact,
                                    float *__restrict__ strided_out, size_t rows,
                                    size_t cols, size_t row_stride) {
+    grid_dependency_wait();
+    grid_dependency_release();
     using T = typename Vec<V>::type;
     const size_t row_vectors = cols / V;
     const size_t total = rows * row_vectors;
@@ -246,11 +264,11 @@ __global__ void gather_rows_kernel(const float *__restrict__ strided,
 #define VITB200_LAUNCH_V(vectorisable, kernel, items, ...)                     \
     do {                                                                       \
         if (vectorisable) {                                                    \
-            kernel<4><<<stream_grid((items) / 4), kStreamThreads, 0, stream>>>(\
-                __VA_ARGS__);                                                  \
+            launch_chained(kernel<4>, stream_grid((items) / 4),                \
+                           kStreamThreads, 0, stream, __VA_ARGS__);            \
         } else {                                                               \
-            kernel<1><<<stream_grid(items), kStreamThreads, 0, stream>>>(      \
-                __VA_ARGS__);                                                  \
+            launch_chained(kernel<1>, stream_grid(items), kStreamThreads, 0,   \
+                           stream, __VA_ARGS__);                               \
         }                                                                      \
         ++g_kernel_launches;                                                   \
     } while (0)
@@ -339,13 +357,13 @@ void launch_token_embedding_backward(float *patch_grad, float *cls_grad,
 void launch_gather_rows(const float *source, float *destination, size_t rows,
                         size_t cols, size_t row_stride, cudaStream_t stream) {
     if (cols % 4 == 0) {
-        gather_rows_kernel<4, false>
-            <<<stream_grid(rows * cols / 4), kStreamThreads, 0, stream>>>(
-                source, destination, nullptr, rows, cols, row_stride);
+        launch_chained(gather_rows_kernel<4, false>,
+                       stream_grid(rows * cols / 4), kStreamThreads, 0, stream,
+                       source, destination, nullptr, rows, cols, row_stride);
     } else {
-        gather_rows_kernel<1, false>
-            <<<stream_grid(rows * cols), kStreamThreads, 0, stream>>>(
-                source, destination, nullptr, rows, cols, row_stride);
+        launch_chained(gather_rows_kernel<1, false>, stream_grid(rows * cols),
+                       kStreamThreads, 0, stream, source, destination, nullptr,
+                       rows, cols, row_stride);
     }
     ++g_kernel_launches;
 }
@@ -355,15 +373,15 @@ void launch_gather_rows_backward(float *source_grad,
                                  size_t cols, size_t row_stride,
                                  cudaStream_t stream) {
     if (cols % 4 == 0) {
-        gather_rows_kernel<4, true>
-            <<<stream_grid(rows * cols / 4), kStreamThreads, 0, stream>>>(
-                nullptr, const_cast<float *>(destination_grad), source_grad,
-                rows, cols, row_stride);
+        launch_chained(gather_rows_kernel<4, true>,
+                       stream_grid(rows * cols / 4), kStreamThreads, 0, stream,
+                       nullptr, const_cast<float *>(destination_grad),
+                       source_grad, rows, cols, row_stride);
     } else {
-        gather_rows_kernel<1, true>
-            <<<stream_grid(rows * cols), kStreamThreads, 0, stream>>>(
-                nullptr, const_cast<float *>(destination_grad), source_grad,
-                rows, cols, row_stride);
+        launch_chained(gather_rows_kernel<1, true>, stream_grid(rows * cols),
+                       kStreamThreads, 0, stream, nullptr,
+                       const_cast<float *>(destination_grad), source_grad, rows,
+                       cols, row_stride);
     }
     ++g_kernel_launches;
 }

@@ -23,6 +23,8 @@ __global__ void cross_entropy_rows_kernel(
     const float *__restrict__ class_weights, float label_smoothing,
     float *__restrict__ logits_grad, float *__restrict__ row_losses,
     size_t rows, size_t cols) {
+    grid_dependency_wait();
+    grid_dependency_release();
     const int lane = threadIdx.x & 31;
     const size_t warp = (size_t(blockIdx.x) * blockDim.x + threadIdx.x) >> 5;
     const size_t warps = (size_t(gridDim.x) * blockDim.x) >> 5;
@@ -62,6 +64,8 @@ __global__ void cross_entropy_rows_kernel(
 
 __global__ void mean_of_rows_kernel(const float *__restrict__ row_losses,
                                     float *__restrict__ loss, size_t rows) {
+    grid_dependency_wait();
+    grid_dependency_release();
     __shared__ float partial[32];
     float sum = 0.0f;
     for (size_t i = threadIdx.x; i < rows; i += blockDim.x) {
@@ -143,11 +147,11 @@ void launch_softmax_cross_entropy(const float *logits, const float *targets,
                                   float *logits_grad, float *row_losses,
                                   size_t rows, size_t cols,
                                   cudaStream_t stream) {
-    cross_entropy_rows_kernel<<<stream_grid(rows * 32), kStreamThreads, 0,
-                                stream>>>(logits, targets, class_weights,
-                                          label_smoothing, logits_grad,
-                                          row_losses, rows, cols);
-    mean_of_rows_kernel<<<1, 1024, 0, stream>>>(row_losses, loss, rows);
+    launch_chained(cross_entropy_rows_kernel, stream_grid(rows * 32),
+                   kStreamThreads, 0, stream, logits, targets, class_weights,
+                   label_smoothing, logits_grad, row_losses, rows, cols);
+    launch_chained(mean_of_rows_kernel, 1, 1024, 0, stream, row_losses, loss,
+                   rows);
     g_kernel_launches += 2;
 }
 

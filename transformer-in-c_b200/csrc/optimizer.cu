@@ -60,6 +60,8 @@ __device__ __forceinline__ float block_sum(float value, float *scratch) {
 __global__ void __launch_bounds__(kThreads)
 squared_norm_partials_kernel(const ParameterSlice *__restrict__ slices,
                              unsigned slices_n, float *__restrict__ partials) {
+    grid_dependency_wait();
+    grid_dependency_release();
     __shared__ float scratch[32];
     const BlockRange range = locate(slices, slices_n, blockIdx.x);
     const float *g = range.slice->grad;
@@ -93,6 +95,8 @@ __global__ void clip_scale_kernel(const float *__restrict__ partials,
                                   unsigned count, float max_norm,
                                   float inverse_world,
                                   float *__restrict__ scale_out) {
+    grid_dependency_wait();
+    grid_dependency_release();
     __shared__ double scratch[32];
     double sum = 0.0;
     for (unsigned i = threadIdx.x; i < count; i += blockDim.x) {
@@ -121,6 +125,8 @@ __global__ void clip_scale_kernel(const float *__restrict__ partials,
 __global__ void __launch_bounds__(kThreads)
 scale_gradients_kernel(const ParameterSlice *__restrict__ slices,
                        unsigned slices_n, const float *__restrict__ scale) {
+    grid_dependency_wait();
+    grid_dependency_release();
     const float s = scale[0];
     if (s == 1.0f) {
         return;
@@ -152,6 +158,8 @@ __global__ void __launch_bounds__(kThreads)
 adamw_kernel(const ParameterSlice *__restrict__ slices, unsigned slices_n,
              const float *__restrict__ scale_pointer, float lr, float beta1,
              float beta2, float epsilon) {
+    grid_dependency_wait();
+    grid_dependency_release();
     const float scale = scale_pointer ? scale_pointer[0] : 1.0f;
     const BlockRange range = locate(slices, slices_n, blockIdx.x);
     const ParameterSlice s = *range.slice;
@@ -190,6 +198,8 @@ __global__ void adamw_single_kernel(float *__restrict__ value,
                                     size_t n, float lr, float beta1, float beta2,
                                     float epsilon, float weight_decay,
                                     float correction1, float correction2) {
+    grid_dependency_wait();
+    grid_dependency_release();
     for (size_t i = global_thread(); i < n; i += grid_threads()) {
         adamw_element(value[i], grad[i], m[i], v[i], 1.0f, lr, beta1, beta2,
                       epsilon, weight_decay, correction1, correction2);
@@ -202,19 +212,18 @@ void launch_gradient_clip_scale(const ParameterSlice *slices, unsigned slices_n,
                                 unsigned total_blocks, float max_norm,
                                 float inverse_world, float *partials,
                                 float *scale_out, cudaStream_t stream) {
-    squared_norm_partials_kernel<<<total_blocks, kThreads, 0, stream>>>(
-        slices, slices_n, partials);
-    clip_scale_kernel<<<1, 1024, 0, stream>>>(partials, total_blocks, max_norm,
-                                              inverse_world, scale_out);
+    launch_chained(squared_norm_partials_kernel, total_blocks, kThreads, 0,
+                   stream, slices, slices_n, partials);
+    launch_chained(clip_scale_kernel, 1, 1024, 0, stream, partials,
+                   total_blocks, max_norm, inverse_world, scale_out);
     g_kernel_launches += 2;
 }
 
 void launch_scale_gradients(const ParameterSlice *slices, unsigned slices_n,
                             unsigned total_blocks, const float *scale,
                             cudaStream_t stream) {
-    scale_gradients_kernel<<<total_blocks, kThreads, 0, stream>>>(slices,
-                                                                  slices_n,
-                                                                  scale);
+    launch_chained(scale_gradients_kernel, total_blocks, kThreads, 0, stream,
+                   slices, slices_n, scale);
     ++g_kernel_launches;
 }
 
@@ -222,9 +231,8 @@ void launch_adamw(const ParameterSlice *slices, unsigned slices_n,
                   unsigned total_blocks, const float *scale, float lr,
                   float beta1, float beta2, float epsilon,
                   cudaStream_t stream) {
-    adamw_kernel<<<total_blocks, kThreads, 0, stream>>>(slices, slices_n, scale,
-                                                        lr, beta1, beta2,
-                                                        epsilon);
+    launch_chained(adamw_kernel, total_blocks, kThreads, 0, stream, slices,
+                   slices_n, scale, lr, beta1, beta2, epsilon);
     ++g_kernel_launches;
 }
 
@@ -232,9 +240,9 @@ void launch_adamw_single(float *value, float *grad, float *m, float *v,
                          size_t n, float lr, float beta1, float beta2,
                          float epsilon, float weight_decay, float correction1,
                          float correction2, cudaStream_t stream) {
-    adamw_single_kernel<<<stream_grid(n), kStreamThreads, 0, stream>>>(
-        value, grad, m, v, n, lr, beta1, beta2, epsilon, weight_decay,
-        correction1, correction2);
+    launch_chained(adamw_single_kernel, stream_grid(n), kStreamThreads, 0,
+                   stream, value, grad, m, v, n, lr, beta1, beta2, epsilon,
+                   weight_decay, correction1, correction2);
     ++g_kernel_launches;
 }
 
