@@ -125,6 +125,29 @@ struct ColumnSumMemo {
     size_t partial_rows = 0;
 };
 
+// Device memory that column sums are gathered in: `clean` = known to be all
+// zero.  The buffers circulate between the two current ones of the backend
+// (the running sums a producer adds into, the per-CTA partial rows), the
+// bias-gradient reductions that wait for their batched launch, and a free list.
+struct SumBuffer {
+    float *memory = nullptr;
+    size_t floats = 0;
+    bool clean = false;
+};
+
+// A bias gradient whose column sums exist (as one running row, or as a few
+// hundred partial rows) and which only has to be folded into the gradient
+// buffer: held back so that up to kColumnSumBatch of them share a launch.
+struct PendingColumnSum {
+    SumBuffer source;
+    bool running = false;   // one running row (cleared by the launch), not partial rows
+    size_t rows = 0, cols = 0;
+    float *destination = nullptr;
+    bool add = false;
+    const void *host_gradient = nullptr;
+    size_t count = 0;
+};
+
 // A residual add held back for one op: the layer norm that the host applies
 // to the sum next (reference src/vit.c:520-523, and the next block's first
 // layer norm after :534) computes the sum itself.
@@ -187,15 +210,16 @@ struct CudaBackend {
     // Ops that launched work so far (see ColumnSumMemo).
     unsigned long long epoch = 0;
     ColumnSumMemo column_memo;
-    Scratch column_sums;       // all zero whenever !column_sums_dirty
-    Scratch column_partials;
+    SumBuffer running_sums;    // what a producer adds its column sums into
+    SumBuffer partial_sums;    // per-CTA / per-sample partial rows
+    std::vector<SumBuffer> free_running, free_partial;
+    std::vector<PendingColumnSum> pending_sums;
     // Batch augmentation: device staging for plain host buffers, the
     // per-sample table (pinned host copy + device copy) and the plane means.
     Scratch augment_source, augment_destination, augment_table, augment_means;
     void *augment_host_table = nullptr;
     size_t augment_host_bytes = 0;
     cudaEvent_t augment_table_read = nullptr;
-    bool column_sums_dirty = false;
     unsigned long long memo_hits = 0;
     PendingGemm pending;
     PendingAttention pending_attention;
@@ -300,9 +324,16 @@ private:
 void flush_attention(CudaBackend *backend);
 
 void flush_input_gradient(CudaBackend *backend);
+void flush_column_sums(CudaBackend *backend);
 
 // Launches the held-back product, with whatever was attached to it.
-void flush_pending(CudaBackend *backend) {
+// keep_column_sums: the caller is an op of the backward pass that neither
+// reads nor writes a bias gradient, so bias-gradient reductions that are
+// waiting for their batched launch may go on waiting.
+void flush_pending(CudaBackend *backend, bool keep_column_sums = false) {
+    if (!keep_column_sums) {
+        flush_column_sums(backend);
+    }
     // Every op starts here: whatever it does may change the matrix a memo
     // describes.  The few ops that provably do not put the memo back.
     backend->column_memo.valid = false;
@@ -405,8 +436,6 @@ void free_scratch(Scratch &buffer) {
     buffer = Scratch{};
 }
 
-void flush_pending(CudaBackend *backend);
-
 // A tensor is about to go (its region still exists).  Ops that were recorded
 // but held back keep raw pointers into tensors, so they are launched now,
 // while every buffer they name is still there; then the log-sum-exp buffer
@@ -420,7 +449,8 @@ void release_hook(const void *host_pointer) {
     if (backend->pending.active || backend->pending_attention.active ||
         backend->pending_attention_backward.active ||
         backend->pending_residual.active ||
-        backend->pending_input_gradient.active) {
+        backend->pending_input_gradient.active ||
+        !backend->pending_sums.empty()) {
         flush_pending(backend);
     }
     dp_tensor_released(backend->dp, host_pointer);
@@ -645,6 +675,51 @@ void flush_attention(CudaBackend *backend) {
     }
 }
 
+// A buffer of at least `floats` floats from a free list, or a new one.
+SumBuffer acquire_sum_buffer(CudaBackend *backend, std::vector<SumBuffer> &list,
+                             size_t floats, bool zeroed) {
+    SumBuffer buffer;
+    for (size_t i = 0; i < list.size(); ++i) {
+        if (list[i].floats >= floats) {
+            buffer = list[i];
+            list.erase(list.begin() + long(i));
+            break;
+        }
+    }
+    if (!buffer.memory) {
+        const size_t grown = floats + floats / 2;
+        void *memory = nullptr;
+        check(cudaMalloc(&memory, grown * sizeof(float)), "cudaMalloc");
+        buffer.memory = static_cast<float *>(memory);
+        buffer.floats = grown;
+        buffer.clean = false;
+    }
+    if (zeroed && !buffer.clean) {
+        check(cudaMemsetAsync(buffer.memory, 0, buffer.floats * sizeof(float),
+                              backend->stream),
+              "cudaMemsetAsync");
+        buffer.clean = true;
+    }
+    return buffer;
+}
+
+void retire_sum_buffer(std::vector<SumBuffer> &list, SumBuffer buffer) {
+    if (buffer.memory) {
+        list.push_back(buffer);
+    }
+}
+
+// The current partial-rows buffer, at least `floats` long (contents
+// undefined: its users overwrite or clear what they need).
+float *partial_sums_buffer(CudaBackend *backend, size_t floats) {
+    if (backend->partial_sums.floats < floats) {
+        retire_sum_buffer(backend->free_partial, backend->partial_sums);
+        backend->partial_sums =
+            acquire_sum_buffer(backend, backend->free_partial, floats, false);
+    }
+    return backend->partial_sums.memory;
+}
+
 // A zeroed buffer of `cols` floats for a producer to add column sums into, or
 // nullptr if the width is not worth it.
 float *column_memo_begin(CudaBackend *backend, size_t cols) {
@@ -652,15 +727,17 @@ float *column_memo_begin(CudaBackend *backend, size_t cols) {
     if (cols == 0 || cols > 16384) {
         return nullptr;
     }
-    const size_t before = backend->column_sums.bytes;
-    float *sums = scratch<float>(backend, backend->column_sums, cols);
-    if (backend->column_sums.bytes != before || backend->column_sums_dirty) {
-        check(cudaMemsetAsync(backend->column_sums.memory, 0,
-                              backend->column_sums.bytes, backend->stream),
+    SumBuffer &running = backend->running_sums;
+    if (running.floats < cols) {
+        retire_sum_buffer(backend->free_running, running);
+        running = acquire_sum_buffer(backend, backend->free_running, cols, true);
+    } else if (!running.clean) {
+        check(cudaMemsetAsync(running.memory, 0, running.floats * sizeof(float),
+                              backend->stream),
               "cudaMemsetAsync");
     }
-    backend->column_sums_dirty = true;
-    return sums;
+    running.clean = false;   // the producer is about to add into it
+    return running.memory;
 }
 
 // Call after the producer's OpScope has closed.
@@ -684,6 +761,45 @@ bool column_memo_matches(CudaBackend *backend, const float *data, size_t rows,
     return memo.valid && memo.data == data && memo.rows == rows &&
            memo.cols == cols && memo.epoch == backend->epoch &&
            memo.uploads == coherence_stats().host_to_device_copies;
+}
+
+// Partial rows up to this many are folded by the batched launch (one block
+// per 128 columns walks all of them); taller ones keep their own launch.
+constexpr size_t kDeferredSumRows = 512;
+
+// One launch for all the bias gradients that are waiting to be folded out of
+// their column sums, then what each of them owes the gradient exchange.
+void flush_column_sums(CudaBackend *backend) {
+    if (backend->pending_sums.empty()) {
+        return;
+    }
+    std::vector<PendingColumnSum> waiting;
+    waiting.swap(backend->pending_sums);
+    for (size_t first = 0; first < waiting.size(); first += kColumnSumBatch) {
+        const size_t count = std::min(waiting.size() - first, size_t(kColumnSumBatch));
+        ColumnSumJob jobs[kColumnSumBatch];
+        double bytes = 0.0;
+        for (size_t i = 0; i < count; ++i) {
+            const PendingColumnSum &item = waiting[first + i];
+            jobs[i].source = item.source.memory;
+            jobs[i].destination = item.destination;
+            jobs[i].rows = unsigned(item.rows);
+            jobs[i].cols = unsigned(item.cols);
+            jobs[i].add = item.add ? 1 : 0;
+            jobs[i].clear = item.running ? 1 : 0;
+            bytes += 4.0 * double(item.rows + 1) * double(item.cols);
+        }
+        OpScope scope(backend, "bias_add_backward", bytes, 0.0);
+        launch_column_sums_batch(jobs, int(count), backend->stream);
+    }
+    for (const PendingColumnSum &item : waiting) {
+        dp_gradient_produced(backend->dp, item.host_gradient, item.destination,
+                             item.count);
+        SumBuffer buffer = item.source;
+        buffer.clean = item.running;   // the launch cleared a running row
+        retire_sum_buffer(item.running ? backend->free_running : backend->free_partial,
+                          buffer);
+    }
 }
 
 // destination += source where destination is a pending zero fill: make it an
@@ -731,7 +847,7 @@ int op_gemm(void *context, const vitb200_tensor *left,
 int op_gemm_backward(void *context, vitb200_tensor *left, vitb200_tensor *right,
                      const vitb200_tensor *output) {
     CudaBackend *backend = self(context);
-    flush_pending(backend);
+    flush_pending(backend, true);
     if (!ours({left->data, left->grad, right->data, right->grad,
                output->grad}) ||
         !fits_int(left->rows) || !fits_int(left->cols) ||
@@ -840,7 +956,7 @@ int op_residual_backward(void *context, vitb200_tensor *left,
                          vitb200_tensor *right, const vitb200_tensor *output) {
     CudaBackend *backend = self(context);
     const ColumnSumMemo memo = backend->column_memo;
-    flush_pending(backend);
+    flush_pending(backend, true);
     // One pass updates both branches, which needs them to be distinct.
     if (!ours({left->grad, right->grad, output->grad}) ||
         left->grad == right->grad) {
@@ -884,7 +1000,7 @@ int op_accumulate_gradient(void *context, vitb200_tensor *destination,
                            const vitb200_tensor *source) {
     CudaBackend *backend = self(context);
     const ColumnSumMemo memo = backend->column_memo;
-    flush_pending(backend);
+    flush_pending(backend, true);
     if (!ours({destination->grad, source->grad}) ||
         destination->grad == source->grad) {
         return -1;
@@ -940,7 +1056,7 @@ int op_bias_add_backward(void *context, const vitb200_tensor *output,
                          vitb200_tensor *bias_grad) {
     CudaBackend *backend = self(context);
     const ColumnSumMemo memo = backend->column_memo;
-    flush_pending(backend);
+    flush_pending(backend, true);
     backend->column_memo = memo;   // checked against the launch count below
     if (!ours({output->grad, bias_grad->grad})) {
         return -1;
@@ -951,22 +1067,51 @@ int op_bias_add_backward(void *context, const vitb200_tensor *output,
         const ColumnSumMemo used = backend->column_memo;
         backend->column_memo.valid = false;
         backend->memo_hits += 1;
+        const bool running = used.partial_rows == 0;
+        SumBuffer &current = running ? backend->running_sums : backend->partial_sums;
+        // Folding the sums into the gradient is held back so that several
+        // biases share one launch (flush_column_sums).  An earlier reduction
+        // into the same gradient goes first.
+        for (const PendingColumnSum &waiting : backend->pending_sums) {
+            if (waiting.host_gradient == bias_grad->grad) {
+                flush_column_sums(backend);
+                break;
+            }
+        }
+        static const bool batched = getenv("VITB200_NO_BATCHED_BIAS_SUMS") == nullptr;
+        if (batched && output->cols % 4 == 0 && used.partial_rows <= kDeferredSumRows &&
+            current.memory && (running || used.partials == current.memory)) {
+            PendingColumnSum job;
+            job.running = running;
+            job.source = current;
+            current = SumBuffer{};   // the next producer takes another buffer
+            job.rows = running ? 1 : used.partial_rows;
+            job.cols = output->cols;
+            job.add = true;
+            job.destination = accumulate_view(backend, bias_grad->grad, &job.add);
+            job.host_gradient = bias_grad->grad;
+            job.count = numel(bias_grad);
+            backend->pending_sums.push_back(job);
+            if (backend->pending_sums.size() >= size_t(kColumnSumBatch)) {
+                flush_column_sums(backend);
+            }
+            return 0;
+        }
         float *db = nullptr;
-        if (used.partial_rows) {
+        if (!running) {
             db = view(backend, bias_grad->grad, Access::ReadWrite);
             OpScope scope(backend, "bias_add_backward",
                           4.0 * double(used.partial_rows * output->cols), 0.0);
             launch_column_sums(used.partials, db, used.partial_rows,
                                output->cols, output->cols, backend->stream);
         } else {
-            backend->column_sums_dirty = false;
             bool add = true;
             db = accumulate_view(backend, bias_grad->grad, &add);
-            float *sums = static_cast<float *>(backend->column_sums.memory);
             OpScope scope(backend, "bias_add_backward", 8.0 * double(output->cols),
                           0.0);
-            launch_take_column_sums(db, sums, output->cols, add,
+            launch_take_column_sums(db, current.memory, output->cols, add,
                                     backend->stream);
+            current.clean = true;   // the kernel leaves zeros behind
         }
         dp_gradient_produced(backend->dp, bias_grad->grad, db, numel(bias_grad));
         return 0;
@@ -1031,7 +1176,7 @@ int op_layer_norm_backward(void *context, const vitb200_tensor *input,
                            vitb200_tensor *gamma_grad,
                            vitb200_tensor *beta_grad) {
     CudaBackend *backend = self(context);
-    flush_pending(backend);
+    flush_pending(backend, true);
     if (!ours({input->data, gamma->data, output->grad, input_grad->grad,
                gamma_grad->grad, beta_grad->grad}) ||
         output->grad == input_grad->grad) {
@@ -1140,11 +1285,11 @@ bool gelu_backward_through_product(CudaBackend *backend,
         return false;
     }
     backend->pending_input_gradient.active = false;
-    flush_pending(backend);
+    flush_pending(backend, true);
     bool add = true;
     float *dh = accumulate_view(backend, input->grad, &add);   // add == false
-    float *sums = scratch<float>(backend, backend->column_partials,
-                                 size_t(kGemmPartialRows) * input->cols);
+    float *sums = partial_sums_buffer(backend,
+                                      size_t(kGemmPartialRows) * input->cols);
     {
         OpScope scope(backend, "gemm_backward",
                       4.0 * (double(held.m) * held.n + double(held.k) * held.n +
@@ -1171,7 +1316,7 @@ int op_gelu_backward(void *context, const vitb200_tensor *input,
         gelu_backward_through_product(backend, input, output)) {
         return 0;
     }
-    flush_pending(backend);
+    flush_pending(backend, true);
     if (!ours({input->data, input->grad, output->grad})) {
         return -1;
     }
@@ -1184,8 +1329,7 @@ int op_gelu_backward(void *context, const vitb200_tensor *input,
     size_t partial_rows = 0;
     if (gelu_backward_sums_supported(input->cols)) {
         partial_rows = gelu_backward_sums_blocks(input->rows, input->cols);
-        sums = scratch<float>(backend, backend->column_partials,
-                              partial_rows * input->cols);
+        sums = partial_sums_buffer(backend, partial_rows * input->cols);
     }
     {
         OpScope scope(backend, "gelu_backward", 16.0 * double(numel(input)),
@@ -1350,7 +1494,7 @@ int op_split_heads_backward(void *context, vitb200_tensor *projected,
                             size_t seq, size_t d_model, size_t heads) {
     CudaBackend *backend = self(context);
     if (!ours({projected->grad, query->grad, key->grad, value->grad})) {
-        flush_pending(backend);
+        flush_pending(backend, true);
         return -1;
     }
     // The attention backward pass that produces the three gradients is still
@@ -1368,7 +1512,7 @@ int op_split_heads_backward(void *context, vitb200_tensor *projected,
         coherent_is_zero_pending(projected->grad)) {
         const PendingAttentionBackward pending = held;
         held.active = false;
-        flush_pending(backend);
+        flush_pending(backend, true);
         float *p = view(backend, projected->grad, Access::Overwrite);
         HeadLayout grad_layout;
         grad_layout.ld = int(3 * d_model);
@@ -1384,8 +1528,7 @@ int op_split_heads_backward(void *context, vitb200_tensor *projected,
         const size_t partial_rows =
             pending.kind == 2 ? batch : (from_tc ? attention_tc_partial_rows() : 0);
         float *partials = partial_rows
-            ? scratch<float>(backend, backend->column_partials,
-                             partial_rows * 3 * d_model)
+            ? partial_sums_buffer(backend, partial_rows * 3 * d_model)
             : nullptr;
         if (!run_attention_backward(backend, pending, p, p + d_model,
                                     p + 2 * d_model, false, false, false,
@@ -1411,7 +1554,7 @@ int op_split_heads_backward(void *context, vitb200_tensor *projected,
         }
         return 0;
     }
-    flush_pending(backend);
+    flush_pending(backend, true);
     bool add = true;
     float *p = accumulate_view(backend, projected->grad, &add);
     const float *q = view(backend, query->grad, Access::Read);
@@ -1470,7 +1613,7 @@ int op_merge_heads_backward(void *context, vitb200_tensor *attended,
                             const vitb200_tensor *merged, size_t batch,
                             size_t seq, size_t d_model, size_t heads) {
     CudaBackend *backend = self(context);
-    flush_pending(backend);
+    flush_pending(backend, true);
     if (!ours({attended->grad, merged->grad})) {
         return -1;
     }
@@ -1689,7 +1832,7 @@ int op_attention_backward(void *context, const vitb200_tensor *query,
                           vitb200_tensor *query_grad, vitb200_tensor *key_grad,
                           vitb200_tensor *value_grad) {
     CudaBackend *backend = self(context);
-    flush_pending(backend);
+    flush_pending(backend, true);
     if (!ours({query->data, key->data, value->data, probabilities->data,
                output->data, output->grad, query_grad->grad, key_grad->grad,
                value_grad->grad}) ||
@@ -1891,7 +2034,7 @@ int op_token_embedding_backward(void *context, vitb200_tensor *patch_tokens,
                                 vitb200_tensor *cls, vitb200_tensor *pos,
                                 const vitb200_tensor *tokens, size_t batch) {
     CudaBackend *backend = self(context);
-    flush_pending(backend);
+    flush_pending(backend, true);
     if (!ours({patch_tokens->grad, cls->grad, pos->grad, tokens->grad})) {
         return -1;
     }
@@ -1933,7 +2076,7 @@ int op_gather_rows_backward(void *context, vitb200_tensor *source,
                             const vitb200_tensor *destination,
                             size_t row_stride) {
     CudaBackend *backend = self(context);
-    flush_pending(backend);
+    flush_pending(backend, true);
     if (!ours({source->grad, destination->grad})) {
         return -1;
     }
@@ -2328,8 +2471,16 @@ extern "C" void cuda_backend_free(CudaBackend *backend) {
     free_scratch(backend->norm_partials);
     free_scratch(backend->clip_scale);
     free_scratch(backend->slice_table);
-    free_scratch(backend->column_sums);
-    free_scratch(backend->column_partials);
+    backend->free_running.push_back(backend->running_sums);
+    backend->free_partial.push_back(backend->partial_sums);
+    for (std::vector<SumBuffer> *list : {&backend->free_running, &backend->free_partial}) {
+        for (const SumBuffer &buffer : *list) {
+            if (buffer.memory) {
+                cudaFree(buffer.memory);
+            }
+        }
+        list->clear();
+    }
     free_scratch(backend->augment_source);
     free_scratch(backend->augment_destination);
     free_scratch(backend->augment_table);

@@ -80,6 +80,19 @@ void launch_gather_rows_backward(float *source_grad,
                                  size_t cols, size_t row_stride,
                                  cudaStream_t stream);
 
+// Up to kColumnSumBatch small column sums in one launch: destination[c] (+)=
+// sum over rows of source[r * cols + c].  cols a multiple of 4, both pointers
+// 16-byte aligned, rows small (every job is served by cols / 128 blocks).
+// clear: the source is zeroed afterwards.
+struct ColumnSumJob {
+    const float *source;
+    float *destination;
+    unsigned rows, cols;
+    int add, clear;
+};
+constexpr int kColumnSumBatch = 8;
+void launch_column_sums_batch(const ColumnSumJob *jobs, int count,
+                              cudaStream_t stream);
 // ---- reductions over rows (reduce.cu) ------------------------------------
 // out[c] += sum_r in[r * ld + c] for c < cols.
 void launch_column_sums(const float *in, float *out, size_t rows, size_t cols,

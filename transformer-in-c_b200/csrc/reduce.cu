@@ -70,7 +70,72 @@ column_sums_kernel(const float *__restrict__ in, float *__restrict__ out,
     }
 }
 
+struct ColumnSumBatch {
+    ColumnSumJob job[kColumnSumBatch];
+};
+
+// Several small column sums in one launch: block (x, j) sums 128 columns of
+// job j (a multiple of four columns wide, a few hundred rows at most), 32
+// column lanes of four floats by eight row lanes, folded through shared
+// memory.  The result replaces or is added to the destination; a one-row
+// source that is a running accumulator is cleared for its next user.
+__global__ void __launch_bounds__(256)
+column_sums_batch_kernel(const ColumnSumBatch batch) {
+    grid_dependency_wait();
+    grid_dependency_release();
+    __shared__ float4 fold[8][32];
+    const ColumnSumJob job = batch.job[blockIdx.y];
+    const unsigned lane = threadIdx.x & 31, row_lane = threadIdx.x >> 5;
+    const unsigned col = (blockIdx.x * 32 + lane) * 4;
+    float4 sum = make_float4(0.f, 0.f, 0.f, 0.f);
+    if (col < job.cols) {
+        for (unsigned row = row_lane; row < job.rows; row += 8) {
+            const float4 v = *reinterpret_cast<const float4 *>(
+                job.source + size_t(row) * job.cols + col);
+            sum.x += v.x; sum.y += v.y; sum.z += v.z; sum.w += v.w;
+        }
+    }
+    fold[row_lane][lane] = sum;
+    __syncthreads();
+    if (row_lane == 0 && col < job.cols) {
+#pragma unroll
+        for (int other = 1; other < 8; ++other) {
+            const float4 v = fold[other][lane];
+            sum.x += v.x; sum.y += v.y; sum.z += v.z; sum.w += v.w;
+        }
+        float4 *target = reinterpret_cast<float4 *>(job.destination + col);
+        if (job.add) {
+            const float4 old = *target;
+            sum.x += old.x; sum.y += old.y; sum.z += old.z; sum.w += old.w;
+        }
+        *target = sum;
+        if (job.clear) {
+            for (unsigned row = 0; row < job.rows; ++row) {
+                *reinterpret_cast<float4 *>(const_cast<float *>(job.source) +
+                                            size_t(row) * job.cols + col) =
+                    make_float4(0.f, 0.f, 0.f, 0.f);
+            }
+        }
+    }
+}
+
 }  // namespace
+
+void launch_column_sums_batch(const ColumnSumJob *jobs, int count,
+                              cudaStream_t stream) {
+    if (count <= 0) {
+        return;
+    }
+    ColumnSumBatch batch = {};
+    unsigned widest = 0;
+    for (int j = 0; j < count; ++j) {
+        batch.job[j] = jobs[j];
+        widest = jobs[j].cols > widest ? jobs[j].cols : widest;
+    }
+    launch_chained(column_sums_batch_kernel, dim3((widest + 127) / 128, count),
+                   256, 0, stream, batch);
+    ++g_kernel_launches;
+}
 
 void launch_column_sums(const float *in, float *out, size_t rows, size_t cols,
                         size_t ld, cudaStream_t stream) {
