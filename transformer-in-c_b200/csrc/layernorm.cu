@@ -140,8 +140,11 @@ layer_norm_kernel(const float *__restrict__ x, const float *__restrict__ gamma,
 // block of eight warps per SM; capped at 128 (eight spilled words) two blocks
 // fit, which took the kernel from 0.55 to 0.66 of the copy rate at 384
 // columns.  The same trade at NV = 2 (three blocks, 29 spilled words) lost.
+// The other widths name the block counts they reach anyway (four at 64
+// registers, two at 118): with a bound of one the compiler spends more
+// registers and a block of the 128-column kernel no longer fits.
 template <int NV>
-__global__ void __launch_bounds__(kWarpsPerBlock * 32, NV == 4 ? 2 : 1)
+__global__ void __launch_bounds__(kWarpsPerBlock * 32, NV == 1 ? 4 : (NV <= 4 ? 2 : 1))
 layer_norm_backward_kernel(const float *__restrict__ x,
                            const float *__restrict__ gamma, float epsilon,
                            const float *__restrict__ dy, float *dx,
